@@ -1,0 +1,548 @@
+// CPU oracle for the TurboQuant KV-cache hot path. TEST INFRASTRUCTURE ONLY.
+//
+// This file restates, in plain scalar C++ with a C ABI, the arithmetic the
+// reference project (fxslava/ascend-micro-harness) defines in its CPU golden
+// models for the two operators this library accelerates:
+//
+//   * reshape_and_cache  (aligned 16-token writer, and the 1..16-token scatter
+//     writer) -- rotation, power-of-two scale, signed INT4 codes, page layout;
+//   * paged split-K decode attention -- query rotation, FP64 full-context and
+//     per-split references, the log-sum-exp merge, the page partition.
+//
+// Every function cites the reference file:line it follows. Nothing here is
+// used by the product path: only the test suite, the smoke check and the CPU
+// baseline leg of the benchmark may call it. Parity of this restatement is
+// pinned against the reference's own headers compiled in place (see
+// ref_bridge.cpp) and against the committed golden vectors those produce.
+//
+// Build: g++ -O2 -std=c++17 -shared -fPIC -pthread tq_oracle.cpp -o libtq_oracle.so
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <limits>
+#include <thread>
+#include <vector>
+
+namespace {
+
+constexpr int kGroup = 32;        // inner Hadamard width (tests/common/turboquant_oracle.hpp:51)
+constexpr int kStrip = 16;        // strip height R (tests/common/turboquant_scatter_oracle.hpp:49)
+constexpr float kMasked = -3.0e38f;  // kernels/ops/turboquant/turboquant_decode_tail.hpp:72
+
+inline int parity(unsigned v) { return __builtin_popcount(v) & 1; }
+// H[i][j] = (-1)^popcount(i & j)  (tests/common/turboquant_oracle.hpp:68-72)
+inline int hsign(int i, int j) { return parity(static_cast<unsigned>(i & j)) ? -1 : 1; }
+
+inline float bf16_to_f32(std::uint16_t raw)
+{
+    const std::uint32_t bits = static_cast<std::uint32_t>(raw) << 16;
+    float v;
+    std::memcpy(&v, &bits, 4);
+    return v;
+}
+
+// Round-to-nearest-even narrowing (tests/common/turboquant_scatter_oracle.hpp:64-71).
+inline std::uint16_t f32_to_bf16(float value)
+{
+    std::uint32_t bits;
+    std::memcpy(&bits, &value, 4);
+    if ((bits & 0x7f800000u) == 0x7f800000u && (bits & 0x7fffffu))
+        return static_cast<std::uint16_t>((bits >> 16) | 0x40u);
+    return static_cast<std::uint16_t>((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);
+}
+
+// y = M x with M = (H_G (x) I32) diag(s) (I_G (x) H32), un-normalised, in the
+// factored order of tests/common/turboquant_oracle.hpp:382-410. T is long long
+// for the integer writer and double for non-integer bf16 activations.
+template <class T>
+void rotate_factored(int d, const int* signs, const T* x, T* y)
+{
+    const int groups = d / kGroup;
+    std::vector<T> z(static_cast<std::size_t>(d));
+    for (int g = 0; g < groups; ++g)
+        for (int o = 0; o < kGroup; ++o) {
+            T acc = 0;
+            for (int i = 0; i < kGroup; ++i) acc += static_cast<T>(hsign(o, i)) * x[g * kGroup + i];
+            z[g * kGroup + o] = acc;
+        }
+    for (int c1 = 0; c1 < groups; ++c1)
+        for (int c0 = 0; c0 < kGroup; ++c0) {
+            T acc = 0;
+            for (int g = 0; g < groups; ++g) {
+                const int ch = g * kGroup + c0;
+                acc += static_cast<T>(hsign(c1, g) * signs[ch]) * z[ch];
+            }
+            y[c1 * kGroup + c0] = acc;
+        }
+}
+
+// The radix-2 cascade of tests/common/rotate_butterfly_oracle.hpp:130-142 in
+// FP32: stage s computes out[i] = in[i^s] + ((i&s) ? -in[i] : in[i]).
+// ingress (y = Pi x): strides 1..16, sign diagonal, strides 32..d/2.
+// egress  (y = x Pi): strides 32..d/2, sign diagonal, strides 1..16.
+void butterfly_f32(int d, const float* signs, const float* x, float* y, bool ingress,
+                   float scale)
+{
+    std::vector<float> v(x, x + d), n(static_cast<std::size_t>(d));
+    auto stage = [&](int s) {
+        for (int i = 0; i < d; ++i) n[i] = v[i ^ s] + ((i & s) ? -v[i] : v[i]);
+        v.swap(n);
+    };
+    auto sign = [&]() {
+        for (int i = 0; i < d; ++i) v[i] *= signs[i];
+    };
+    if (ingress) {
+        for (int s = 1; s < kGroup; s <<= 1) stage(s);
+        sign();
+        for (int s = kGroup; s < d; s <<= 1) stage(s);
+    } else {
+        for (int s = kGroup; s < d; s <<= 1) stage(s);
+        sign();
+        for (int s = 1; s < kGroup; s <<= 1) stage(s);
+    }
+    for (int i = 0; i < d; ++i) y[i] = v[i] * scale;
+}
+
+// Round half to even of y / 2^shift (tests/common/turboquant_oracle.hpp:100-111).
+long long rint_even_shift(long long y, int shift)
+{
+    if (shift <= 0) return y << (-shift);
+    const long long den = 1LL << shift;
+    long long q = y / den;
+    const long long rem = y % den;
+    if (rem == 0) return q;
+    const long long twice = 2 * (rem < 0 ? -rem : rem);
+    if (twice > den || (twice == den && (q % 2 != 0))) q += (y >= 0 ? 1 : -1);
+    return q;
+}
+
+inline void put_nibble(std::uint8_t* base, std::size_t index, int q)
+{
+    const std::uint8_t nib = static_cast<std::uint8_t>(q & 0xF);
+    std::uint8_t& b = base[index / 2];
+    b = (index % 2 == 0) ? static_cast<std::uint8_t>((b & 0xF0u) | nib)
+                         : static_cast<std::uint8_t>((b & 0x0Fu) | (nib << 4));
+}
+
+inline int get_nibble(const std::uint8_t* base, std::size_t index)
+{
+    const int raw = (base[index / 2] >> ((index % 2) * 4)) & 15;
+    return raw >= 8 ? raw - 16 : raw;
+}
+
+// Power-of-two quantiser for one rotated row held as exact integers
+// (tests/common/turboquant_oracle.hpp:412-439). floor_at_one selects the
+// aligned writer's absmax floor; without it an all-zero row takes the scatter
+// writer's branch scale = 1, codes 0
+// (tests/common/turboquant_scatter_oracle.hpp:192-200).
+void quantise_int_row(int d, const long long* y, float inv_sqrt_len, bool floor_at_one, int* q,
+                      float* scale)
+{
+    long long m = floor_at_one ? 1 : 0;
+    for (int c = 0; c < d; ++c) m = std::max(m, y[c] < 0 ? -y[c] : y[c]);
+    if (m == 0) {
+        *scale = 1.0f;
+        for (int c = 0; c < d; ++c) q[c] = 0;
+        return;
+    }
+    int e = 0;
+    while ((1LL << (e + 1)) <= m) ++e;
+    *scale = std::ldexp(1.0f, e - 2) * inv_sqrt_len;
+    for (int c = 0; c < d; ++c) {
+        long long v = rint_even_shift(y[c], e - 2);
+        q[c] = static_cast<int>(v > 7 ? 7 : v);
+    }
+}
+
+// The same quantiser for a non-integer FP32 row: the exponent comes from the
+// FP32 bit pattern of absmax and the product y * 2^(2-e) is exact, so one
+// round-half-even is the only rounding
+// (kernels/ops/turboquant/turboquant_reshape_and_cache_a8.cpp:1136-1158,:1207-1209).
+void quantise_f32_row(int d, const float* y, float inv_sqrt_len, bool floor_at_one, int* q,
+                      float* scale)
+{
+    float m = floor_at_one ? 1.0f : 0.0f;
+    for (int c = 0; c < d; ++c) m = std::fmax(m, std::fabs(y[c]));
+    if (m == 0.0f) {
+        *scale = 1.0f;
+        for (int c = 0; c < d; ++c) q[c] = 0;
+        return;
+    }
+    const int e = std::ilogb(m);
+    *scale = std::ldexp(1.0f, e - 2) * inv_sqrt_len;
+    for (int c = 0; c < d; ++c) {
+        const double scaled = std::fmin(std::ldexp(static_cast<double>(y[c]), 2 - e), 7.0);
+        q[c] = static_cast<int>(std::nearbyint(scaled));
+    }
+}
+
+template <class F>
+void parallel_for(int n, int threads, F&& body)
+{
+    if (threads <= 1 || n <= 1) {
+        for (int i = 0; i < n; ++i) body(i);
+        return;
+    }
+    threads = std::min(threads, n);
+    std::vector<std::thread> pool;
+    for (int t = 0; t < threads; ++t)
+        pool.emplace_back([&, t]() {
+            for (int i = t; i < n; i += threads) body(i);
+        });
+    for (auto& th : pool) th.join();
+}
+
+struct Geometry {
+    int H, d, S, P;
+    std::size_t head_bytes() const { return static_cast<std::size_t>(S) * d / 2; }
+    std::size_t key_nibble(int page, int head, int tok, int ch) const
+    {  // tests/common/turboquant_scatter_oracle.hpp:107-112
+        return ((static_cast<std::size_t>(page) * H + head) * S + tok) * d + ch;
+    }
+    std::size_t value_nibble(int page, int head, int tok, int ch) const
+    {  // tests/common/turboquant_scatter_oracle.hpp:114-124
+        return (static_cast<std::size_t>(page) * H + head) * S * d +
+               static_cast<std::size_t>(tok / kStrip) * (kStrip * d) +
+               static_cast<std::size_t>(ch) * kStrip + tok % kStrip;
+    }
+    std::size_t scale_index(int plane, int page, int head, int tok) const
+    {  // tests/common/turboquant_oracle.hpp:342-346
+        return ((static_cast<std::size_t>(plane) * P + page) * H + head) * S + tok;
+    }
+};
+
+// One input element as the exact value the device reads.
+inline double load_act(int dtype, const void* base, std::size_t index)
+{
+    if (dtype == 0) return static_cast<const std::int8_t*>(base)[index];
+    return bf16_to_f32(static_cast<const std::uint16_t*>(base)[index]);
+}
+
+bool row_is_integer(int d, const double* x)
+{
+    for (int c = 0; c < d; ++c)
+        if (x[c] != std::nearbyint(x[c]) || std::fabs(x[c]) > 32768.0) return false;
+    return true;
+}
+
+// Rotate + quantise one (token, head, plane) row into codes and a scale.
+void process_row(int dtype, const void* src, std::size_t row_offset, int d, const int* signs,
+                 float inv_sqrt_len, bool floor_at_one, int* q, float* scale)
+{
+    std::vector<double> x(static_cast<std::size_t>(d));
+    for (int c = 0; c < d; ++c) x[c] = load_act(dtype, src, row_offset + c);
+    if (row_is_integer(d, x.data())) {
+        std::vector<long long> xi(static_cast<std::size_t>(d)), yi(static_cast<std::size_t>(d));
+        for (int c = 0; c < d; ++c) xi[c] = static_cast<long long>(x[c]);
+        rotate_factored<long long>(d, signs, xi.data(), yi.data());
+        quantise_int_row(d, yi.data(), inv_sqrt_len, floor_at_one, q, scale);
+        return;
+    }
+    // Non-integer bf16 activations: the rotation is evaluated in FP64 (exact
+    // for bf16 operands of comparable exponent) and narrowed once to FP32, the
+    // type the device accumulates in. Not bit-pinned by the reference: its
+    // validation only demands bit equality for integer-valued inputs
+    // (tests/npu/validation/test_turboquant_bf16_validation.cpp:3-17).
+    std::vector<double> y(static_cast<std::size_t>(d));
+    rotate_factored<double>(d, signs, x.data(), y.data());
+    std::vector<float> yf(static_cast<std::size_t>(d));
+    for (int c = 0; c < d; ++c) yf[c] = static_cast<float>(y[c]);
+    quantise_f32_row(d, yf.data(), inv_sqrt_len, floor_at_one, q, scale);
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---------------------------------------------------------------- rotation
+// Resident rotation blocks T[s][g][c0][i] = (s?-1:1) signs[g*32+c0] H32[c0][i]
+// (tests/common/turboquant_oracle.hpp:157-171). out holds 2*(d/32) blocks.
+void tqo_build_tables_i8(int d, const int* signs, std::int8_t* out)
+{
+    const int groups = d / kGroup;
+    for (int s = 0; s < 2; ++s)
+        for (int g = 0; g < groups; ++g)
+            for (int c0 = 0; c0 < kGroup; ++c0)
+                for (int i = 0; i < kGroup; ++i)
+                    out[((static_cast<std::size_t>(s) * groups + g) * kGroup + c0) * kGroup + i] =
+                        static_cast<std::int8_t>((s ? -1 : 1) * signs[g * kGroup + c0] *
+                                                 hsign(c0, i));
+}
+
+// Writer fixture sign diagonal (tests/common/turboquant_oracle.hpp:77-80).
+int tqo_pi_sign_writer(int channel)
+{
+    return ((channel * channel + 3 * channel + 1) % 7 < 3) ? -1 : 1;
+}
+
+// Decode fixture sign diagonal (tests/common/paged_decode_oracle.hpp:148-152).
+int tqo_pi_sign_decode(int channel)
+{
+    const unsigned x = static_cast<unsigned>(channel);
+    return ((x * 2654435761u) >> 13) & 1u ? -1 : 1;
+}
+
+void tqo_rotate_int(int d, const int* signs, const long long* x, long long* y)
+{
+    rotate_factored<long long>(d, signs, x, y);
+}
+
+// Dense definition of the same matrix, for the factorisation self-check
+// (tests/cpu/test_reshape_and_cache_a8_probe.cpp:150-167).
+void tqo_rotate_dense_int(int d, const int* signs, const long long* x, long long* y)
+{
+    for (int r = 0; r < d; ++r) {
+        long long acc = 0;
+        for (int c = 0; c < d; ++c)
+            acc += static_cast<long long>(hsign(r / kGroup, c / kGroup) *
+                                          signs[(c / kGroup) * kGroup + r % kGroup] *
+                                          hsign(r % kGroup, c % kGroup)) * x[c];
+        y[r] = acc;
+    }
+}
+
+void tqo_butterfly_f32(int d, const float* signs, const float* x, float* y, int ingress,
+                       float scale)
+{
+    butterfly_f32(d, signs, x, y, ingress != 0, scale);
+}
+
+// Query rotation as the decode path defines it: q_rot = bf16(Pi q), Pi = M/sqrt(d)
+// (tests/common/paged_decode_oracle.hpp:481-514). Evaluated as the FP32 ingress
+// cascade followed by one multiply, so the result is reproducible bit for bit.
+void tqo_rotate_query_bf16(int rows, int d, const float* signs, float inv_sqrt_len,
+                           const std::uint16_t* q, std::uint16_t* q_rot)
+{
+    std::vector<float> x(static_cast<std::size_t>(d)), y(static_cast<std::size_t>(d));
+    for (int r = 0; r < rows; ++r) {
+        for (int c = 0; c < d; ++c) x[c] = bf16_to_f32(q[static_cast<std::size_t>(r) * d + c]);
+        butterfly_f32(d, signs, x.data(), y.data(), true, inv_sqrt_len);
+        for (int c = 0; c < d; ++c) q_rot[static_cast<std::size_t>(r) * d + c] = f32_to_bf16(y[c]);
+    }
+}
+
+// ------------------------------------------------------- aligned writer
+// tq_oracle::compute_oracle_reference (tests/common/turboquant_oracle.hpp:476-513)
+// with the slot contract of page_of_slots (:278-287). dtype 0 = int8, 1 = bf16.
+// Caches are updated in place for the pages a strip owns; page_written (may be
+// null) receives one flag per page. Returns the first strip that violates the
+// slot contract, or -1.
+int tqo_reshape_and_cache(int dtype, const void* key, const void* value,
+                          const std::int32_t* slots, const int* signs, int T, int H, int d,
+                          int S, int P, float inv_sqrt_len, std::uint8_t* key_cache,
+                          std::uint8_t* value_cache, float* scale_cache,
+                          std::uint8_t* page_written, int threads)
+{
+    if (T <= 0 || H <= 0 || S != kStrip || d % kGroup != 0 || T % S != 0) return -2;
+    const Geometry g{H, d, S, P};
+    const int strips = T / S;
+    std::vector<int> page_of(static_cast<std::size_t>(strips), -1);
+    int bad = -1;
+    for (int s = 0; s < strips; ++s) {
+        const std::int32_t* ss = slots + static_cast<std::size_t>(s) * S;
+        bool ok = ss[0] >= 0 && ss[0] % S == 0;
+        for (int i = 1; ok && i < S; ++i) ok = ss[i] == ss[0] + i;
+        const int page = ok ? ss[0] / S : -1;
+        if (ok && page < P) page_of[s] = page;
+        else if (bad < 0) bad = s;
+    }
+    parallel_for(strips, threads, [&](int s) {
+        const int page = page_of[s];
+        if (page < 0) return;
+        if (page_written) page_written[page] = 1;
+        std::vector<int> q(static_cast<std::size_t>(d));
+        for (int plane = 0; plane < 2; ++plane) {
+            const void* src = plane == 0 ? key : value;
+            std::uint8_t* cache = plane == 0 ? key_cache : value_cache;
+            for (int head = 0; head < H; ++head)
+                for (int t = 0; t < S; ++t) {
+                    const std::size_t row =
+                        (static_cast<std::size_t>(s) * S + t) * H * d + static_cast<std::size_t>(head) * d;
+                    float scale;
+                    process_row(dtype, src, row, d, signs, inv_sqrt_len, true, q.data(), &scale);
+                    for (int c = 0; c < d; ++c)
+                        put_nibble(cache, plane == 0 ? g.key_nibble(page, head, t, c)
+                                                     : g.value_nibble(page, head, t, c), q[c]);
+                    scale_cache[g.scale_index(plane, page, head, t)] = scale;
+                }
+        }
+    });
+    return bad;
+}
+
+// ------------------------------------------------------- scatter writer
+// tq_scatter::compute_reference (tests/common/turboquant_scatter_oracle.hpp:291-342)
+// over the run discovery of the device kernel
+// (kernels/ops/turboquant/turboquant_reshape_scatter_aiv.cpp:693-730):
+// request r owns tokens cu_seqlens[r]..cu_seqlens[r+1] (or token r when
+// cu_seqlens is null), slot < 0 is a padded token, every other nibble and
+// scale of the caches is preserved. key/value are bf16 [tokens][H*d].
+int tqo_reshape_scatter(const std::uint16_t* key, const std::uint16_t* value,
+                        const std::int32_t* slots, const float* signs_f,
+                        const std::int32_t* cu_seqlens, int num_requests, int H, int d, int S,
+                        int P, float inv_sqrt_len, std::uint8_t* key_cache,
+                        std::uint8_t* value_cache, float* scale_cache)
+{
+    if (S % kStrip != 0 || d % kGroup != 0) return -2;
+    const Geometry g{H, d, S, P};
+    std::vector<int> q(static_cast<std::size_t>(d));
+    std::vector<float> x(static_cast<std::size_t>(d)), y(static_cast<std::size_t>(d));
+    for (int r = 0; r < num_requests; ++r) {
+        const int begin = cu_seqlens ? cu_seqlens[r] : r;
+        const int end = cu_seqlens ? cu_seqlens[r + 1] : r + 1;
+        for (int tok = begin; tok < end; ++tok) {
+            const int slot = slots[tok];
+            if (slot < 0) continue;
+            const int page = slot / S, tib = slot % S;
+            if (page >= P) return -3;
+            for (int head = 0; head < H; ++head)
+                for (int plane = 0; plane < 2; ++plane) {
+                    const std::size_t row =
+                        static_cast<std::size_t>(tok) * H * d + static_cast<std::size_t>(head) * d;
+                    // quantise_row (tests/common/turboquant_scatter_oracle.hpp:185-217):
+                    // the FP32 ingress cascade, then the quantiser with no absmax floor.
+                    const std::uint16_t* src = plane == 0 ? key : value;
+                    for (int c = 0; c < d; ++c) x[c] = bf16_to_f32(src[row + c]);
+                    butterfly_f32(d, signs_f, x.data(), y.data(), true, 1.0f);
+                    float scale;
+                    quantise_f32_row(d, y.data(), inv_sqrt_len, false, q.data(), &scale);
+                    std::uint8_t* cache = plane == 0 ? key_cache : value_cache;
+                    for (int c = 0; c < d; ++c)
+                        put_nibble(cache, plane == 0 ? g.key_nibble(page, head, tib, c)
+                                                     : g.value_nibble(page, head, tib, c), q[c]);
+                    scale_cache[g.scale_index(plane, page, head, tib)] = scale;
+                }
+        }
+    }
+    return 0;
+}
+
+// -------------------------------------------------------------- decode
+// Page partition (include/turboquant_splitk_contract.hpp:129-136).
+void tqo_partition(std::uint32_t pages, std::uint32_t splits, std::uint32_t split,
+                   std::uint32_t* begin, std::uint32_t* count)
+{
+    const std::uint32_t width = (pages + splits - 1u) / splits;
+    const std::uint32_t b = split * width;
+    const std::uint32_t remaining = b < pages ? pages - b : 0u;
+    *begin = b;
+    *count = remaining < width ? remaining : width;
+}
+
+// FP64 softmax attention of one sequence over logical tokens [tok_begin, tok_end)
+// clipped to ctx_len, reading the packed caches through the block table. This is
+// splitk_decode_test::Fixture::Reference (tests/common/splitk_decode_fixture.hpp:193-248)
+// and ReferenceAicPartial (tests/common/aic_splitk_decode_fixture.hpp:32-77) with
+// runtime head_size, page size and query-row count:
+//   score[t] = (sum_c q_rot[c] Kq[t][c]) kscale[t] softmax_scale
+//   m = max score (-3e38 when the range holds no live token), l = sum exp(score-m)
+//   acc[c] = sum_t exp(score-m) vscale[t] Vq[c][t]
+// q_rot is bf16 [rows][d]; outputs are m[rows], l[rows], acc[rows][d] in FP64.
+void tqo_decode_partial(const std::uint16_t* q_rot, int rows, const std::uint8_t* key_cache,
+                        const std::uint8_t* value_cache, const float* scale_cache,
+                        const std::int32_t* block_table, int H, int head, int d, int S, int P,
+                        int ctx_len, int tok_begin, int tok_end, float softmax_scale, double* m,
+                        double* l, double* acc)
+{
+    const Geometry g{H, d, S, P};
+    const int hi = std::min(tok_end, ctx_len);
+    std::vector<double> scores(static_cast<std::size_t>(std::max(0, hi - tok_begin)));
+    for (int r = 0; r < rows; ++r) {
+        m[r] = static_cast<double>(kMasked);
+        l[r] = 0.0;
+        for (int c = 0; c < d; ++c) acc[static_cast<std::size_t>(r) * d + c] = 0.0;
+        for (int t = tok_begin; t < hi; ++t) {
+            const int page = block_table[t / S], tib = t % S;
+            double dot = 0.0;
+            for (int c = 0; c < d; ++c)
+                dot += static_cast<double>(bf16_to_f32(q_rot[static_cast<std::size_t>(r) * d + c])) *
+                       get_nibble(key_cache, g.key_nibble(page, head, tib, c));
+            const double s = dot * scale_cache[g.scale_index(0, page, head, tib)] *
+                             static_cast<double>(softmax_scale);
+            scores[t - tok_begin] = s;
+            m[r] = std::max(m[r], s);
+        }
+        for (int t = tok_begin; t < hi; ++t) {
+            const int page = block_table[t / S], tib = t % S;
+            const double p = std::exp(scores[t - tok_begin] - m[r]);
+            l[r] += p;
+            const double pv = p * scale_cache[g.scale_index(1, page, head, tib)];
+            for (int c = 0; c < d; ++c)
+                acc[static_cast<std::size_t>(r) * d + c] +=
+                    pv * get_nibble(value_cache, g.value_nibble(page, head, tib, c));
+        }
+    }
+}
+
+// Log-sum-exp merge of partial states in FP64
+// (routines/routine_probe_l2_atomic_sync.hpp:116-121; neutral element -3e38/0/0
+// as in tests/cpu/test_splitk_decode_probe.cpp:48-61). state = {m, l, acc[d]}.
+void tqo_lse_merge(int d, double* m, double* l, double* acc, double m2, double l2,
+                   const double* acc2)
+{
+    const double mn = std::max(*m, m2);
+    const double a = std::exp(*m - mn), b = std::exp(m2 - mn);
+    *l = *l * a + l2 * b;
+    for (int c = 0; c < d; ++c) acc[c] = acc[c] * a + acc2[c] * b;
+    *m = mn;
+}
+
+// Whole decode for a batch: rotate q (bf16 [B][Hq][d]) once, attend over every
+// live token, emit FP64 context [B][Hq][d].
+//   output_stage 0: acc / l in the rotated basis
+//   output_stage 1: (acc / l) Pi  -- the egress rotation, here as a dense FP64
+//                   product (tests/common/single_token_decode_oracle.hpp:339-349)
+//   output_stage 2: stage 1 divided by 1 + exp(-gate)
+//                   (tests/common/paged_decode_oracle.hpp:598-617)
+// block_tables is int32 [B][max_blocks]; context_lens int32 [B]; gate (may be
+// null unless stage 2) FP32 [B][Hq][d]. A sequence with no live token yields 0.
+void tqo_decode(const std::uint16_t* q, const std::uint8_t* key_cache,
+                const std::uint8_t* value_cache, const float* scale_cache,
+                const std::int32_t* block_tables, const std::int32_t* context_lens,
+                const float* signs, const float* gate, int B, int Hq, int Hkv, int d, int S,
+                int P, int max_blocks, float inv_sqrt_len, float softmax_scale, int output_stage,
+                double* out, int threads)
+{
+    const int group = Hq / Hkv;
+    parallel_for(B * Hkv, threads, [&](int item) {
+        const int b = item / Hkv, kvh = item % Hkv;
+        std::vector<std::uint16_t> qrot(static_cast<std::size_t>(group) * d);
+        tqo_rotate_query_bf16(group, d, signs, inv_sqrt_len,
+                              q + (static_cast<std::size_t>(b) * Hq + kvh * group) * d, qrot.data());
+        std::vector<double> m(group), l(group), acc(static_cast<std::size_t>(group) * d);
+        tqo_decode_partial(qrot.data(), group, key_cache, value_cache, scale_cache,
+                           block_tables + static_cast<std::size_t>(b) * max_blocks, Hkv, kvh, d, S, P,
+                           context_lens[b], 0, context_lens[b], softmax_scale, m.data(), l.data(),
+                           acc.data());
+        for (int r = 0; r < group; ++r) {
+            double* o = out + (static_cast<std::size_t>(b) * Hq + kvh * group + r) * d;
+            std::vector<double> n(static_cast<std::size_t>(d));
+            for (int c = 0; c < d; ++c)
+                n[c] = l[r] > 0.0 ? acc[static_cast<std::size_t>(r) * d + c] / l[r] : 0.0;
+            if (output_stage == 0) {
+                for (int c = 0; c < d; ++c) o[c] = n[c];
+                continue;
+            }
+            for (int oc = 0; oc < d; ++oc) {
+                double sum = 0.0;  // ctx[oc] = sum_c n[c] Pi[c][oc]
+                for (int c = 0; c < d; ++c) {
+                    const int c1 = c / kGroup, c0 = c % kGroup, gg = oc / kGroup, i = oc % kGroup;
+                    sum += n[c] * (hsign(c1, gg) * hsign(c0, i)) *
+                           static_cast<double>(signs[gg * kGroup + c0]);
+                }
+                sum *= static_cast<double>(inv_sqrt_len);
+                if (output_stage == 2) {
+                    const double gt = gate[(static_cast<std::size_t>(b) * Hq + kvh * group + r) * d + oc];
+                    sum /= 1.0 + std::exp(-gt);
+                }
+                o[oc] = sum;
+            }
+        }
+    });
+}
+
+int tqo_hardware_threads() { return static_cast<int>(std::thread::hardware_concurrency()); }
+
+}  // extern "C"
