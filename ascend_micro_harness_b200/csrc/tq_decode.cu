@@ -1,0 +1,752 @@
+// Paged split-K decode attention over the 4-bit strip cache, and the log-sum-exp
+// combine that merges the per-split partial states.
+//
+// Arithmetic (reference: tests/common/paged_decode_oracle.hpp:516-596,
+// tests/common/aic_splitk_decode_fixture.hpp:32-77):
+//   q_rot   = bf16(Pi q),  Pi = M / sqrt(d)           rotated once per query row
+//   score_t = (sum_c q_rot[c] Kq[t][c]) * kscale[t] * softmax_scale
+//   tokens >= seq_len are overwritten with -3e38, fully dead strips are dropped
+//   online softmax (m, l);  acc[c] += p_t * vscale[t] * Vq[c][t]
+//   partial record per (item, split, row) = { m x8, l x8, acc[d] }
+//   (include/turboquant_splitk_contract.hpp:23-27), empty range = (-3e38, 0, 0).
+//
+// Mapping onto the SM:
+//   * one CTA per (sequence, KV head, split, 8-row query tile); its page range
+//     is the reference Partition (include/turboquant_splitk_contract.hpp:129-136);
+//     four warps each own every fourth 32-token tile of the range and keep their
+//     own (m, l, acc), merged through shared memory at the end;
+//   * every warp streams its tiles through a private three-stage cp.async ring:
+//     whole packed key strips, value strips and both scale runs, resolved through
+//     the block table one tile ahead, so every KV byte crosses HBM once for all
+//     query rows of the GQA group;
+//   * tokens are the M dimension of both contractions. scores^T = K (16 tokens x d)
+//     times q_rot^T (d x 8 rows): the packed key row a thread copies out of shared
+//     memory IS its A fragment after in-register int4 -> bf16 expansion (mask,
+//     xor-magic, one packed subtract per two codes); no per-element scale is
+//     applied, the key scale multiplies the 16 score columns and the value scale
+//     folds into P, as the reference does;
+//   * acc^T = V^T (d channels x 16 tokens) times P^T: the value strip is already
+//     channel-major, so 16 bytes of it are the A fragment of two channels. P is
+//     carried as a bf16 hi + lo pair (two MMAs) so the accumulator keeps FP32-grade
+//     weights; P^T reaches its B-fragment layout with movmatrix.
+#include <cuda_fp16.h>
+#include <stdexcept>
+
+#include "tq_common.cuh"
+
+namespace tq {
+
+constexpr int kDecWarps = 4;
+constexpr int kTileStrips = 2;   // strips per pipeline stage of one warp
+constexpr int kStages = 3;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct DecodeParams {
+    const uint16_t* q;        // [items*rows][D] bf16
+    const void* signs;
+    uint32_t sign_source;
+    const uint8_t* key_cache;
+    const uint8_t* value_cache;
+    const float* scale_cache;
+    const int32_t* table;     // block table rows
+    const int32_t* context_lens;  // null: fixed_ctx applies
+    uint16_t* q_rot;          // optional export [items*splits][rows_stride][D]
+    float* workspace;
+    uint32_t items, H, rows, rows_stride, S, P;
+    uint32_t table_stride, splits, page_begin, page_count, fixed_ctx;
+    float inv_sqrt_len, softmax_scale;
+    uint32_t* status;
+};
+
+template <int D>
+struct DecodeSmem {
+    static constexpr int kStripBytes = kStrip * D / 2;
+    static constexpr int kStageBytes = kTileStrips * (2 * kStripBytes + 2 * kStrip * 4);
+    static constexpr int kQBytes = 2 * 8 * D * 4;
+    static constexpr int kRingBytes = kDecWarps * kStages * kStageBytes;
+    static constexpr int kMergeBytes = kDecWarps * 8 * (D + 2) * 4;
+    static constexpr int kTotal = kQBytes + (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes);
+};
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
+{
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+// Two packed INT4 codes (bits 0-3 and 16-19 of x) -> two exact bf16 integers.
+// (x & 0x000F000F) ^ 0x43084308 is bf16(128 + (code ^ 8)); minus 136 is the
+// sign-extended code.
+__device__ __forceinline__ uint32_t dq2(uint32_t x)
+{
+    uint32_t t;
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x43084308, 0x6A;\n" : "=r"(t) : "r"(x));
+    asm("sub.rn.bf16x2 %0, %1, %2;\n" : "=r"(t) : "r"(t), "r"(0x43084308u));
+    return t;
+}
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a)
+{
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+
+__device__ __forceinline__ float ex2f(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    return static_cast<uint32_t>(f32_to_bf16_bits(lo)) |
+           (static_cast<uint32_t>(f32_to_bf16_bits(hi)) << 16);
+}
+
+// Which token of a strip rides in MMA row i (0..7; rows 8..15 carry token + 8).
+// Chosen so that after movmatrix a thread's P^T pair covers tokens (qd, qd+4),
+// the pair one mask extracts from a value word.
+__device__ __forceinline__ int token_of_row(int i) { return (i >> 1) + 4 * (i & 1); }
+
+template <int D>
+__global__ void __launch_bounds__(kDecWarps * 32)
+tq_decode_partial_kernel(const DecodeParams p)
+{
+    using L = DecodeSmem<D>;
+    constexpr int kRecord = 16 + D;
+    constexpr int MT = D / 16;    // 16-channel m-tiles of the value contraction
+    constexpr int WPT = D / 32;   // packed words per thread per key row
+    extern __shared__ __align__(16) uint8_t smem[];
+    float* qbuf = reinterpret_cast<float*>(smem);            // [2][8][D]
+    uint8_t* ring = smem + L::kQBytes;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = lane >> 2, qd = lane & 3;
+
+    const uint32_t row_tiles = (p.rows + 7u) / 8u;
+    uint32_t lin = blockIdx.x;
+    const uint32_t split = lin % p.splits;
+    lin /= p.splits;
+    const uint32_t row_tile = lin % row_tiles;
+    const uint32_t item = lin / row_tiles;
+    const uint32_t seq = item / p.H, head = item % p.H;
+    const int rows_here = min(8u, p.rows - row_tile * 8u);
+
+    // ---- this CTA's strip range
+    const uint32_t SP = p.S / kStrip;  // strips per page
+    uint32_t ctx, page_count;
+    if (p.context_lens != nullptr) {
+        const int32_t c = p.context_lens[seq];
+        ctx = c > 0 ? static_cast<uint32_t>(c) : 0u;
+        const uint32_t cap = p.table_stride * p.S;
+        if (ctx > cap) {
+            ctx = cap;
+            if (tid == 0) report(p.status, TQ_STATUS_BAD_PAGE);
+        }
+        page_count = (ctx + p.S - 1u) / p.S;
+    } else {
+        ctx = p.fixed_ctx;
+        page_count = p.page_count;
+    }
+    const uint32_t width = (page_count + p.splits - 1u) / p.splits;
+    const uint32_t rb = split * width;
+    const uint32_t remaining = rb < page_count ? page_count - rb : 0u;
+    const uint32_t rc = remaining < width ? remaining : width;
+    uint32_t s0 = (p.page_begin + rb) * SP;
+    uint32_t s1 = s0 + rc * SP;
+    const uint32_t live_strips = (ctx + kStrip - 1u) / kStrip;
+    if (s1 > live_strips) s1 = live_strips;
+    const bool empty = s1 <= s0;
+
+    float* rec_base = p.workspace +
+                      ((static_cast<size_t>(item) * p.splits + split) * p.rows_stride + row_tile * 8u) *
+                          kRecord;
+
+    if (empty) {
+        // The exact neutral element, so every partition holds a record.
+        for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
+            const int c = i % kRecord;
+            rec_base[i] = c < 8 ? kMaskedScore : 0.0f;
+        }
+        return;
+    }
+
+    // ---- rotate the query rows once: FP32 ingress cascade, scale, round to bf16
+    // (stage order of tests/common/rotate_butterfly_oracle.hpp:44-48).
+    {
+        const uint16_t* qsrc = p.q + (static_cast<size_t>(item) * p.rows + row_tile * 8u) * D;
+        for (int i = tid; i < 8 * D; i += blockDim.x) {
+            const int row = i / D;
+            qbuf[i] = row < rows_here ? bf16_bits_to_f32(qsrc[i]) : 0.0f;
+        }
+        __syncthreads();
+        int cur = 0;
+        for (int s = 1; s < D; s <<= 1) {
+            const float* in = qbuf + cur * 8 * D;
+            float* out = qbuf + (cur ^ 1) * 8 * D;
+            for (int i = tid; i < 8 * D; i += blockDim.x) {
+                const int c = i % D, row = i / D;
+                float mine = in[i], other = in[row * D + (c ^ s)];
+                if (s == kGroup) {  // the sign diagonal sits before the first outer stage
+                    mine *= sign_is_negative(p.signs, p.sign_source, c) ? -1.0f : 1.0f;
+                    other *= sign_is_negative(p.signs, p.sign_source, c ^ s) ? -1.0f : 1.0f;
+                }
+                out[i] = other + ((c & s) ? -mine : mine);
+            }
+            __syncthreads();
+            cur ^= 1;
+        }
+        // qbuf[cur] holds Pi*sqrt(d) q; narrow. Left in place as bf16-exact floats.
+        float* fin = qbuf + cur * 8 * D;
+        for (int i = tid; i < 8 * D; i += blockDim.x) {
+            const uint16_t b = f32_to_bf16_bits(fin[i] * p.inv_sqrt_len);
+            fin[i] = bf16_bits_to_f32(b);
+            if (p.q_rot != nullptr && i / D < rows_here)
+                p.q_rot[((static_cast<size_t>(item) * p.splits + split) * p.rows_stride +
+                         row_tile * 8u) * D + i] = b;
+        }
+        __syncthreads();
+        qbuf = fin;
+    }
+
+    // ---- q_rot^T as B fragments, in the contraction order the key words deliver.
+    uint32_t bq[2 * WPT][2];
+#pragma unroll
+    for (int wi = 0; wi < WPT; ++wi)
+#pragma unroll
+        for (int kh = 0; kh < 2; ++kh) {
+            const float* qr = qbuf + r * D + qd * (D / 4) + wi * 8 + 2 * kh;
+            bq[wi * 2 + kh][0] = pack_bf16x2(qr[0], qr[4]);
+            bq[wi * 2 + kh][1] = pack_bf16x2(qr[1], qr[5]);
+        }
+
+    // ---- per-warp pipeline over tiles warp, warp+4, ...
+    const uint32_t tiles = (s1 - s0 + kTileStrips - 1u) / kTileStrips;
+    const uint32_t my_tiles = tiles > static_cast<uint32_t>(warp)
+                                  ? (tiles - warp + kDecWarps - 1u) / kDecWarps : 0u;
+    const int32_t* table_row = p.table + static_cast<size_t>(seq) * p.table_stride;
+    uint8_t* my_ring = ring + warp * kStages * L::kStageBytes;
+    const size_t head_block = static_cast<size_t>(p.S) * D / 2;  // bytes of one (page, head)
+    const size_t scale_plane = static_cast<size_t>(p.P) * p.H * p.S;
+
+    auto strip_of = [&](uint32_t j, int ts) { return s0 + (warp + j * kDecWarps) * kTileStrips + ts; };
+    auto load_pages = [&](uint32_t j, int32_t (&pg)[kTileStrips]) {
+#pragma unroll
+        for (int ts = 0; ts < kTileStrips; ++ts) {
+            const uint32_t s = strip_of(j, ts);
+            pg[ts] = (j < my_tiles && s < s1) ? __ldg(table_row + s / SP) : -1;
+        }
+    };
+    auto issue = [&](uint32_t j, const int32_t (&pg)[kTileStrips]) {
+        uint8_t* st = my_ring + (j % kStages) * L::kStageBytes;
+#pragma unroll
+        for (int ts = 0; ts < kTileStrips; ++ts) {
+            if (pg[ts] < 0) continue;
+            uint32_t page = static_cast<uint32_t>(pg[ts]);
+            if (page >= p.P) {
+                if (lane == 0) report(p.status, TQ_STATUS_BAD_PAGE);
+                page = 0;
+            }
+            const uint32_t sip = strip_of(j, ts) % SP;
+            const size_t off = (static_cast<size_t>(page) * p.H + head) * head_block +
+                               static_cast<size_t>(sip) * L::kStripBytes;
+            uint8_t* kdst = st + ts * L::kStripBytes;
+            uint8_t* vdst = st + (kTileStrips + ts) * L::kStripBytes;
+#pragma unroll
+            for (int i = 0; i < L::kStripBytes / 512; ++i) {
+                cp_async16(kdst + i * 512 + lane * 16, p.key_cache + off + i * 512 + lane * 16);
+                cp_async16(vdst + i * 512 + lane * 16, p.value_cache + off + i * 512 + lane * 16);
+            }
+            if (lane < 8) {
+                const int plane = lane >> 2, part = lane & 3;
+                const float* src = p.scale_cache + plane * scale_plane +
+                                   (static_cast<size_t>(page) * p.H + head) * p.S + sip * kStrip + part * 4;
+                float* dst = reinterpret_cast<float*>(st + 2 * kTileStrips * L::kStripBytes) +
+                             (plane * kTileStrips + ts) * kStrip + part * 4;
+                cp_async16(dst, src);
+            }
+        }
+    };
+
+    float m_run[2] = {kMaskedScore, kMaskedScore}, l_run[2] = {0.f, 0.f};
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+
+    int32_t pg_next[kTileStrips];
+    for (uint32_t j = 0; j < kStages - 1; ++j) {
+        load_pages(j, pg_next);
+        if (j < my_tiles) issue(j, pg_next);
+        cp_async_commit();
+    }
+    load_pages(kStages - 1, pg_next);
+
+    const int tok_lo = token_of_row(r);  // token (within a strip) of this thread's low row
+    const float sscale = p.softmax_scale;
+
+    for (uint32_t j = 0; j < my_tiles; ++j) {
+        if (j + kStages - 1 < my_tiles) issue(j + kStages - 1, pg_next);
+        cp_async_commit();
+        load_pages(j + kStages, pg_next);
+        cp_async_wait<kStages - 1>();
+        __syncwarp();
+
+        const uint8_t* st = my_ring + (j % kStages) * L::kStageBytes;
+        const float* scales = reinterpret_cast<const float*>(st + 2 * kTileStrips * L::kStripBytes);
+
+        // -- scores^T for the tile's strips
+        float sc[kTileStrips][4];
+        bool live[kTileStrips][2];
+        float mx[2] = {kMaskedScore, kMaskedScore};
+#pragma unroll
+        for (int ts = 0; ts < kTileStrips; ++ts) {
+            const uint32_t strip = strip_of(j, ts);
+            const uint32_t tbase = strip * kStrip;
+            live[ts][0] = strip < s1 && tbase + tok_lo < ctx;
+            live[ts][1] = strip < s1 && tbase + tok_lo + 8 < ctx;
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint8_t* krow = st + ts * L::kStripBytes + tok_lo * (D / 2) + qd * (D / 8);
+#pragma unroll
+            for (int w4 = 0; w4 < WPT / 4; ++w4) {
+                const uint4 lo = *reinterpret_cast<const uint4*>(krow + w4 * 16);
+                const uint4 hi = *reinterpret_cast<const uint4*>(krow + 8 * (D / 2) + w4 * 16);
+                const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int wi = w4 * 4 + k;
+#pragma unroll
+                    for (int kh = 0; kh < 2; ++kh)
+                        mma_bf16_16816(c, dq2(wl[k] >> (8 * kh)), dq2(wh[k] >> (8 * kh)),
+                                       dq2(wl[k] >> (8 * kh + 4)), dq2(wh[k] >> (8 * kh + 4)),
+                                       bq[wi * 2 + kh][0], bq[wi * 2 + kh][1]);
+                }
+            }
+            const float ks_lo = scales[ts * kStrip + tok_lo] * sscale;
+            const float ks_hi = scales[ts * kStrip + tok_lo + 8] * sscale;
+            // Dead lanes are overwritten, never multiplied: their scale may be a NaN.
+            sc[ts][0] = live[ts][0] ? c[0] * ks_lo : kMaskedScore;
+            sc[ts][1] = live[ts][0] ? c[1] * ks_lo : kMaskedScore;
+            sc[ts][2] = live[ts][1] ? c[2] * ks_hi : kMaskedScore;
+            sc[ts][3] = live[ts][1] ? c[3] * ks_hi : kMaskedScore;
+            mx[0] = fmaxf(mx[0], fmaxf(sc[ts][0], sc[ts][2]));
+            mx[1] = fmaxf(mx[1], fmaxf(sc[ts][1], sc[ts][3]));
+        }
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], 4));
+            mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], 8));
+            mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], 16));
+        }
+        // -- online softmax update
+        float alpha[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const float m_new = fmaxf(m_run[q], mx[q]);
+            alpha[q] = ex2f((m_run[q] - m_new) * kLog2e);
+            m_run[q] = m_new;
+            l_run[q] *= alpha[q];
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            acc[mt][0] *= alpha[0];
+            acc[mt][1] *= alpha[1];
+            acc[mt][2] *= alpha[0];
+            acc[mt][3] *= alpha[1];
+        }
+        // -- P, then acc^T += V^T P^T
+#pragma unroll
+        for (int ts = 0; ts < kTileStrips; ++ts) {
+            if (strip_of(j, ts) >= s1) continue;  // warp-uniform
+            const float vs_lo = scales[(kTileStrips + ts) * kStrip + tok_lo];
+            const float vs_hi = scales[(kTileStrips + ts) * kStrip + tok_lo + 8];
+            float pw[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float pr = ex2f((sc[ts][i] - m_run[i & 1]) * kLog2e);
+                l_run[i & 1] += pr;
+                pw[i] = live[ts][i >> 1] ? pr * (i < 2 ? vs_lo : vs_hi) : 0.0f;
+            }
+            const uint32_t h0 = pack_bf16x2(pw[0], pw[1]), h1 = pack_bf16x2(pw[2], pw[3]);
+            const uint32_t l0 = pack_bf16x2(pw[0] - bf16_bits_to_f32(h0 & 0xFFFFu),
+                                            pw[1] - bf16_bits_to_f32(h0 >> 16));
+            const uint32_t l1 = pack_bf16x2(pw[2] - bf16_bits_to_f32(h1 & 0xFFFFu),
+                                            pw[3] - bf16_bits_to_f32(h1 >> 16));
+            const uint32_t bh0 = movmatrix_trans(h0), bh1 = movmatrix_trans(h1);
+            const uint32_t bl0 = movmatrix_trans(l0), bl1 = movmatrix_trans(l1);
+            const uint8_t* vrow = st + (kTileStrips + ts) * L::kStripBytes + (2 * r) * 8;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const uint4 v = *reinterpret_cast<const uint4*>(vrow + mt * 128);
+                const uint32_t a0 = dq2(v.x >> (4 * qd)), a2 = dq2(v.y >> (4 * qd));
+                const uint32_t a1 = dq2(v.z >> (4 * qd)), a3 = dq2(v.w >> (4 * qd));
+                mma_bf16_16816(acc[mt], a0, a1, a2, a3, bh0, bh1);
+                mma_bf16_16816(acc[mt], a0, a1, a2, a3, bl0, bl1);
+            }
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+
+    // ---- warp-level l, then merge the four warps through shared memory.
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 4);
+        l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 8);
+        l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 16);
+    }
+    __syncthreads();  // every warp is done with its ring; reuse it
+    float* merge = reinterpret_cast<float*>(ring) + warp * 8 * (D + 2);
+    if (r == 0) {
+        merge[(qd * 2 + 0) * (D + 2) + 0] = m_run[0];
+        merge[(qd * 2 + 0) * (D + 2) + 1] = l_run[0];
+        merge[(qd * 2 + 1) * (D + 2) + 0] = m_run[1];
+        merge[(qd * 2 + 1) * (D + 2) + 1] = l_run[1];
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        const int ch = mt * 16 + 2 * r;
+        merge[(qd * 2 + 0) * (D + 2) + 2 + ch] = acc[mt][0];
+        merge[(qd * 2 + 1) * (D + 2) + 2 + ch] = acc[mt][1];
+        merge[(qd * 2 + 0) * (D + 2) + 2 + ch + 1] = acc[mt][2];
+        merge[(qd * 2 + 1) * (D + 2) + 2 + ch + 1] = acc[mt][3];
+    }
+    __syncthreads();
+    const float* mg = reinterpret_cast<const float*>(ring);
+    for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
+        const int q = i / kRecord, c = i % kRecord;
+        float mm = kMaskedScore;
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, mg[(w * 8 + q) * (D + 2)]);
+        float out;
+        if (c < 8) {
+            out = mm;
+        } else {
+            const int src = c < 16 ? 1 : 2 + (c - 16);
+            out = 0.f;
+#pragma unroll
+            for (int w = 0; w < kDecWarps; ++w) {
+                const float* rw = mg + (w * 8 + q) * (D + 2);
+                out += rw[src] * ex2f((rw[0] - mm) * kLog2e);
+            }
+        }
+        rec_base[i] = out;
+    }
+}
+
+// ------------------------------------------------------------------ combine
+struct CombineParams {
+    const float* workspace;
+    const float* signs;
+    const float* gate;
+    void* output;
+    uint32_t rows, rows_stride, splits, output_stage, out_dtype;
+    float inv_sqrt_len;
+};
+
+// One CTA per (item, row): merge `splits` records, normalise, optionally rotate
+// back with the egress cascade (routines/routine_vector_egress_rotate.hpp:186-277)
+// and gate, narrow to bf16. D threads, one channel each.
+template <int D>
+__global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
+{
+    constexpr int kRecord = 16 + D;
+    __shared__ float buf[2][D];
+    const uint32_t item = blockIdx.x / p.rows, row = blockIdx.x % p.rows;
+    const int c = threadIdx.x;
+    const float* base = p.workspace + (static_cast<size_t>(item) * p.splits * p.rows_stride + row) * kRecord;
+    const size_t split_stride = static_cast<size_t>(p.rows_stride) * kRecord;
+    float m = kMaskedScore, l = 0.f, a = 0.f;
+    for (uint32_t k = 0; k < p.splits; ++k) {
+        const float* rec = base + k * split_stride;
+        const float mk = rec[0], lk = rec[8], ak = rec[16 + c];
+        const float mn = fmaxf(m, mk);
+        const float wa = ex2f((m - mn) * kLog2e), wb = ex2f((mk - mn) * kLog2e);
+        l = l * wa + lk * wb;
+        a = a * wa + ak * wb;
+        m = mn;
+    }
+    float v = l > 0.f ? a / l : 0.f;
+    if (p.output_stage != TQ_OUT_ROTATED) {
+        int cur = 0;
+        buf[0][c] = v;
+        __syncthreads();
+        auto stage = [&](int s) {
+            const float mine = buf[cur][c], other = buf[cur][c ^ s];
+            buf[cur ^ 1][c] = other + ((c & s) ? -mine : mine);
+            __syncthreads();
+            cur ^= 1;
+        };
+        for (int s = kGroup; s < D; s <<= 1) stage(s);
+        buf[cur][c] *= p.signs[c];
+        __syncthreads();
+        for (int s = 1; s < kGroup; s <<= 1) stage(s);
+        v = buf[cur][c] * p.inv_sqrt_len;
+        if (p.output_stage == TQ_OUT_GATED)
+            v = v / (1.0f + __expf(-p.gate[static_cast<size_t>(blockIdx.x) * D + c]));
+    }
+    const size_t at = static_cast<size_t>(blockIdx.x) * D + c;
+    if (p.out_dtype == TQ_DTYPE_F32) static_cast<float*>(p.output)[at] = v;
+    else if (p.out_dtype == TQ_DTYPE_F16) static_cast<__half*>(p.output)[at] = __float2half_rn(v);
+    else static_cast<uint16_t*>(p.output)[at] = f32_to_bf16_bits(v);
+}
+
+template <int D>
+static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
+{
+    // Opt in to the large dynamic shared-memory carve-out once per device. The
+    // flags race benignly: setting the attribute twice is harmless.
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorNoDevice;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(tq_decode_partial_kernel<D>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             DecodeSmem<D>::kTotal);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    const uint64_t grid = static_cast<uint64_t>(p.items) * ((p.rows + 7u) / 8u) * p.splits;
+    if (grid == 0) return cudaSuccess;
+    if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
+    tq_decode_partial_kernel<D><<<static_cast<unsigned>(grid), kDecWarps * 32,
+                                  DecodeSmem<D>::kTotal, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace tq
+
+using namespace tq;
+
+extern "C" uint32_t tq_decode_choose_splits(uint32_t batch, uint32_t num_kv_heads,
+                                            uint32_t block_size, uint32_t max_context,
+                                            uint32_t sm_count)
+{
+    // Enough CTAs to fill the machine a few times over, never more splits than
+    // pages, never so many that a split has less than ~8 strips to amortise its
+    // prologue. Contexts of at most 512 tokens run un-split.
+    if (batch == 0 || num_kv_heads == 0 || block_size == 0) return 1;
+    const uint32_t pages = (max_context + block_size - 1u) / block_size;
+    if (max_context <= 512u || pages <= 1u) return 1;
+    const uint64_t items = static_cast<uint64_t>(batch) * num_kv_heads;
+    const uint64_t target = 4ull * (sm_count ? sm_count : 148u);
+    uint64_t s = (target + items - 1) / items;
+    const uint64_t by_len = (static_cast<uint64_t>(max_context) + 127u) / 128u;
+    if (s > by_len) s = by_len;
+    if (s > pages) s = pages;
+    if (s > 16) s = 16;
+    if (s < 1) s = 1;
+    return static_cast<uint32_t>(s);
+}
+
+extern "C" size_t tq_decode_workspace_floats(uint32_t batch, uint32_t num_heads,
+                                             uint32_t num_kv_heads, uint32_t head_size,
+                                             uint32_t splits)
+{
+    if (num_kv_heads == 0) return 0;
+    const size_t rows = num_heads / num_kv_heads;
+    return static_cast<size_t>(batch) * num_kv_heads * splits * rows * (16u + head_size);
+}
+
+extern "C" int tq_decode_splitk_partials(void* stream, const uint16_t* q, const void* signs,
+                                         uint32_t sign_source, const int8_t* key_cache,
+                                         const int8_t* value_cache, const float* scale_cache,
+                                         const uint32_t* table, uint16_t* q_rot, float* workspace,
+                                         uint32_t requests, uint32_t heads, uint32_t rows,
+                                         uint32_t head_size, uint32_t block_size,
+                                         uint32_t cache_pages, uint32_t seq_pages, uint32_t splits,
+                                         uint32_t page_begin, uint32_t page_count, uint32_t seq_len,
+                                         float inv_sqrt_len, float softmax_scale, uint32_t* status)
+{
+    // Geometry rules of the reference launcher
+    // (kernels/ops/turboquant/turboquant_paged_decode_attention.cpp:1747-1759).
+    if (!requests || !heads || !splits || splits > 16 || !seq_pages || !block_size ||
+        block_size % kStrip != 0 || seq_pages > cache_pages || page_begin > seq_pages ||
+        page_count > seq_pages - page_begin || rows == 0 || rows > 16 ||
+        (head_size != 128 && head_size != 256) ||
+        (sign_source != TQ_SIGNS_F32 && sign_source != TQ_SIGNS_TABLES_BF16))
+        return TQ_ERR_INVALID_ARGUMENT;
+    if (seq_len != 0u) {
+        if (static_cast<uint64_t>(seq_len) > static_cast<uint64_t>(cache_pages) * block_size)
+            return TQ_ERR_INVALID_ARGUMENT;  // seq_len exceeds the allocated cache
+        const uint64_t window_end = static_cast<uint64_t>(page_begin + page_count) * block_size;
+        if (static_cast<uint64_t>(seq_len) > window_end)
+            return TQ_ERR_INVALID_ARGUMENT;  // live tokens past the end of the page window
+    }
+    if (!q || !signs || !key_cache || !value_cache || !scale_cache || !table || !workspace)
+        return TQ_ERR_INVALID_ARGUMENT;
+    DecodeParams p{};
+    p.q = q;
+    p.signs = signs;
+    p.sign_source = sign_source;
+    p.key_cache = reinterpret_cast<const uint8_t*>(key_cache);
+    p.value_cache = reinterpret_cast<const uint8_t*>(value_cache);
+    p.scale_cache = scale_cache;
+    p.table = reinterpret_cast<const int32_t*>(table);
+    p.context_lens = nullptr;
+    p.q_rot = q_rot;
+    p.workspace = workspace;
+    p.items = requests * heads;
+    p.H = heads;
+    p.rows = rows;
+    p.rows_stride = 16;
+    p.S = block_size;
+    p.P = cache_pages;
+    p.table_stride = seq_pages;
+    p.splits = splits;
+    p.page_begin = page_begin;
+    p.page_count = page_count;
+    p.fixed_ctx = seq_len ? seq_len : seq_pages * block_size;
+    p.inv_sqrt_len = inv_sqrt_len;
+    p.softmax_scale = softmax_scale;
+    p.status = status;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const cudaError_t e = head_size == 128 ? launch_partial<128>(s, p) : launch_partial<256>(s, p);
+    return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
+
+extern "C" int tq_splitk_combine(void* stream, const float* workspace, const float* pi_signs,
+                                 const float* gate, void* output, uint32_t out_dtype,
+                                 uint32_t items, uint32_t rows, uint32_t rows_stride,
+                                 uint32_t head_size, uint32_t splits, uint32_t output_stage,
+                                 float inv_sqrt_len, uint32_t* /*status*/)
+{
+    if (!rows || rows > rows_stride || !splits || splits > 16 || output_stage > TQ_OUT_GATED ||
+        out_dtype > TQ_DTYPE_F32 ||
+        (head_size != 128 && head_size != 256))
+        return TQ_ERR_INVALID_ARGUMENT;
+    if (!workspace || !output || (output_stage != TQ_OUT_ROTATED && !pi_signs) ||
+        (output_stage == TQ_OUT_GATED && !gate))
+        return TQ_ERR_INVALID_ARGUMENT;
+    if (items == 0) return TQ_OK;
+    CombineParams p{workspace, pi_signs, gate, output, rows, rows_stride, splits, output_stage,
+                    out_dtype, inv_sqrt_len};
+    const uint64_t grid = static_cast<uint64_t>(items) * rows;
+    if (grid > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (head_size == 128)
+        tq_combine_kernel<128><<<static_cast<unsigned>(grid), 128, 0, s>>>(p);
+    else
+        tq_combine_kernel<256><<<static_cast<unsigned>(grid), 256, 0, s>>>(p);
+    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
+
+static uint32_t resolve_splits(uint32_t splits, uint32_t batch, uint32_t num_kv_heads,
+                               uint32_t block_size, uint32_t max_blocks, uint32_t hint)
+{
+    if (splits != 0) return splits;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess)
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return tq_decode_choose_splits(batch, num_kv_heads, block_size,
+                                   hint ? hint : max_blocks * block_size,
+                                   static_cast<uint32_t>(sms));
+}
+
+extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
+                                       const int8_t* key_cache, const int8_t* value_cache,
+                                       const float* scale_cache, const int32_t* block_tables,
+                                       const int32_t* context_lens, const float* pi_signs,
+                                       float* workspace, uint32_t batch, uint32_t num_heads,
+                                       uint32_t num_kv_heads, uint32_t head_size,
+                                       uint32_t block_size, uint32_t num_blocks,
+                                       uint32_t max_blocks, uint32_t splits,
+                                       uint32_t max_context_hint, float inv_sqrt_len,
+                                       float softmax_scale, uint32_t* status)
+{
+    if (!num_heads || !num_kv_heads || num_heads % num_kv_heads != 0 || !block_size ||
+        block_size % kStrip != 0 || !num_blocks || !max_blocks || splits > 16 ||
+        (head_size != 128 && head_size != 256))
+        return TQ_ERR_INVALID_ARGUMENT;
+    const uint32_t rows = num_heads / num_kv_heads;
+    if (rows > 16) return TQ_ERR_INVALID_ARGUMENT;
+    if (batch == 0) return TQ_OK;
+    if (!query || !key_cache || !value_cache || !scale_cache || !block_tables || !context_lens ||
+        !pi_signs || !workspace)
+        return TQ_ERR_INVALID_ARGUMENT;
+    DecodeParams p{};
+    p.q = query;
+    p.signs = pi_signs;
+    p.sign_source = TQ_SIGNS_F32;
+    p.key_cache = reinterpret_cast<const uint8_t*>(key_cache);
+    p.value_cache = reinterpret_cast<const uint8_t*>(value_cache);
+    p.scale_cache = scale_cache;
+    p.table = block_tables;
+    p.context_lens = context_lens;
+    p.q_rot = nullptr;
+    p.workspace = workspace;
+    p.items = batch * num_kv_heads;
+    p.H = num_kv_heads;
+    p.rows = rows;
+    p.rows_stride = rows;
+    p.S = block_size;
+    p.P = num_blocks;
+    p.table_stride = max_blocks;
+    p.splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint);
+    p.page_begin = 0;
+    p.page_count = 0;
+    p.fixed_ctx = 0;
+    p.inv_sqrt_len = inv_sqrt_len;
+    p.softmax_scale = softmax_scale;
+    p.status = status;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const cudaError_t e = head_size == 128 ? launch_partial<128>(s, p) : launch_partial<256>(s, p);
+    return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
+
+extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_t* key_cache,
+                                const int8_t* value_cache, const float* scale_cache,
+                                const int32_t* block_tables, const int32_t* context_lens,
+                                const float* pi_signs, const float* gate, float* workspace,
+                                void* output, uint32_t out_dtype, uint32_t batch, uint32_t num_heads,
+                                uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                                uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                                uint32_t max_context_hint, uint32_t output_stage,
+                                float inv_sqrt_len, float softmax_scale, uint32_t* status)
+{
+    if (output_stage > TQ_OUT_GATED || !output || (output_stage == TQ_OUT_GATED && !gate))
+        return TQ_ERR_INVALID_ARGUMENT;
+    if (splits > 16) return TQ_ERR_INVALID_ARGUMENT;
+    splits = resolve_splits(splits, batch, num_kv_heads ? num_kv_heads : 1, block_size ? block_size : 16,
+                            max_blocks, max_context_hint);
+    const int st = tq_decode_splitk_export(stream, query, key_cache, value_cache, scale_cache,
+                                           block_tables, context_lens, pi_signs, workspace, batch,
+                                           num_heads, num_kv_heads, head_size, block_size,
+                                           num_blocks, max_blocks, splits, max_context_hint,
+                                           inv_sqrt_len, softmax_scale, status);
+    if (st != TQ_OK || batch == 0) return st;
+    const uint32_t rows = num_heads / num_kv_heads;
+    return tq_splitk_combine(stream, workspace, pi_signs, gate, output, out_dtype,
+                             batch * num_kv_heads, rows, rows, head_size, splits, output_stage,
+                             inv_sqrt_len, status);
+}
+
+// kernels/ops/turboquant/turboquant_paged_decode_attention.cpp:1727-1766. The
+// reference decoder is compiled for d = 256 and 16 packed query rows per head;
+// pi_table is its 16 resident bf16 blocks, of which only the sign diagonal is
+// data (the 1/sqrt(d) magnitude of its entries is the constant 1/16).
+extern "C" void launch_turboquant_paged_decode_splitk_aic(
+    void* stream, uint16_t* q, uint16_t* pi_table, int8_t* key, int8_t* value, float* scales,
+    uint32_t* table, uint16_t* qrot, float* workspace, uint32_t requests, uint32_t heads,
+    uint32_t block_size, uint32_t cache_pages, uint32_t seq_pages, uint32_t splits,
+    uint32_t page_begin, uint32_t page_count, uint32_t seq_len)
+{
+    if (block_size > 128u) throw std::invalid_argument("invalid AIC temporal split geometry");
+    const int st = tq_decode_splitk_partials(stream, q, pi_table, TQ_SIGNS_TABLES_BF16, key, value,
+                                             scales, table, qrot, workspace, requests, heads, 16,
+                                             256, block_size, cache_pages, seq_pages, splits,
+                                             page_begin, page_count, seq_len, 0.0625f, 1.0f,
+                                             nullptr);
+    if (st == TQ_ERR_INVALID_ARGUMENT)
+        throw std::invalid_argument("invalid AIC temporal split geometry");
+    if (st != TQ_OK) throw std::runtime_error("paged_decode_splitk_aic: launch failed");
+}

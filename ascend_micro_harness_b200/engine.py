@@ -1,0 +1,129 @@
+"""Host-side mirror of the operator surface over the C ABI. torch supplies device
+memory and streams only; every computation happens in libtq_b200.so."""
+from __future__ import annotations
+
+import torch
+
+from ._lib import TqError, load_library
+
+SIGNS_F32, SIGNS_TABLES_I8, SIGNS_TABLES_BF16 = 0, 1, 2
+OUT_ROTATED, OUT_UNROTATED, OUT_GATED = 0, 1, 2
+STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_WAIT_EXPIRED = 1, 2, 4
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("the engine takes device tensors only")
+    if not t.is_contiguous():
+        raise ValueError("the engine takes contiguous tensors only")
+    return t.data_ptr()
+
+
+def _stream(stream):
+    s = torch.cuda.current_stream() if stream is None else stream
+    return s.cuda_stream
+
+
+def _out_dtype(t):
+    return {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[t.dtype]
+
+
+def _check(status, what):
+    if status != 0:
+        raise TqError(status, what)
+
+
+def reshape_and_cache(key, value, key_cache, value_cache, scale_cache, slot_mapping, signs, *,
+                      num_kv_heads, head_size, block_size, num_blocks, inv_sqrt_len,
+                      sign_source=SIGNS_F32, status=None, stream=None):
+    """Aligned writer (reference: launch_turboquant_reshape_and_cache_{a8,bf16}).
+    key/value: [T, H*d] int8 or bfloat16."""
+    lib = load_library()
+    in_dtype = {torch.int8: 0, torch.bfloat16: 1}[key.dtype]
+    if value.dtype != key.dtype:
+        raise ValueError("key and value must share a dtype")
+    num_tokens = key.numel() // (num_kv_heads * head_size)
+    _check(lib.tq_reshape_and_cache(
+        _stream(stream), _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache),
+        _ptr(scale_cache), _ptr(slot_mapping), _ptr(signs), sign_source, in_dtype, num_tokens,
+        num_kv_heads, head_size, block_size, num_blocks, inv_sqrt_len, _ptr(status)),
+        "tq_reshape_and_cache")
+
+
+def reshape_scatter(key, value, key_cache, value_cache, scale_cache, slot_mapping, pi_signs,
+                    cu_seqlens, *, num_requests, num_kv_heads, head_size, block_size, num_blocks,
+                    inv_sqrt_len, item_begin=0, item_count=None, status=None, stream=None):
+    """Scatter writer (reference: launch_turboquant_reshape_scatter_aiv)."""
+    lib = load_library()
+    if item_count is None:
+        item_count = num_requests * num_kv_heads
+    _check(lib.tq_reshape_scatter(
+        _stream(stream), _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache),
+        _ptr(scale_cache), _ptr(slot_mapping), _ptr(pi_signs), _ptr(cu_seqlens), num_requests,
+        num_kv_heads, head_size, block_size, num_blocks, item_begin, item_count, inv_sqrt_len,
+        _ptr(status)), "tq_reshape_scatter")
+
+
+def decode_workspace_floats(batch, num_heads, num_kv_heads, head_size, splits):
+    return load_library().tq_decode_workspace_floats(batch, num_heads, num_kv_heads, head_size,
+                                                     splits)
+
+
+def choose_splits(batch, num_kv_heads, block_size, max_context, sm_count=148):
+    return load_library().tq_decode_choose_splits(batch, num_kv_heads, block_size, max_context,
+                                                  sm_count)
+
+
+def decode_splitk(query, key_cache, value_cache, scale_cache, block_tables, context_lens,
+                  pi_signs, output, *, num_heads, num_kv_heads, head_size, block_size, num_blocks,
+                  inv_sqrt_len, softmax_scale=1.0, splits=0, max_context_hint=0, workspace=None,
+                  gate=None, output_stage=OUT_ROTATED, status=None, stream=None):
+    """Paged split-K decode over query / block_tables / context_lens."""
+    lib = load_library()
+    batch = query.numel() // (num_heads * head_size)
+    max_blocks = block_tables.shape[-1]
+    _check(lib.tq_decode_splitk(
+        _stream(stream), _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache),
+        _ptr(block_tables), _ptr(context_lens), _ptr(pi_signs), _ptr(gate), _ptr(workspace),
+        _ptr(output), _out_dtype(output), batch, num_heads, num_kv_heads, head_size, block_size,
+        num_blocks, max_blocks, splits, max_context_hint, output_stage, inv_sqrt_len, softmax_scale,
+        _ptr(status)), "tq_decode_splitk")
+
+
+def decode_splitk_export(query, key_cache, value_cache, scale_cache, block_tables, context_lens,
+                         pi_signs, workspace, *, num_heads, num_kv_heads, head_size, block_size,
+                         num_blocks, inv_sqrt_len, splits, softmax_scale=1.0, max_context_hint=0,
+                         status=None, stream=None):
+    """The export half of decode_splitk: per-split partial records into the workspace."""
+    lib = load_library()
+    batch = query.numel() // (num_heads * head_size)
+    _check(lib.tq_decode_splitk_export(
+        _stream(stream), _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache),
+        _ptr(block_tables), _ptr(context_lens), _ptr(pi_signs), _ptr(workspace), batch, num_heads,
+        num_kv_heads, head_size, block_size, num_blocks, block_tables.shape[-1], splits,
+        max_context_hint, inv_sqrt_len, softmax_scale, _ptr(status)), "tq_decode_splitk_export")
+
+
+def decode_splitk_partials(q, signs, key_cache, value_cache, scale_cache, table, q_rot,
+                           workspace, *, requests, heads, rows, head_size, block_size,
+                           cache_pages, seq_pages, splits, page_begin, page_count, seq_len,
+                           inv_sqrt_len, softmax_scale=1.0, sign_source=SIGNS_F32, status=None,
+                           stream=None):
+    lib = load_library()
+    _check(lib.tq_decode_splitk_partials(
+        _stream(stream), _ptr(q), _ptr(signs), sign_source, _ptr(key_cache), _ptr(value_cache),
+        _ptr(scale_cache), _ptr(table), _ptr(q_rot), _ptr(workspace), requests, heads, rows,
+        head_size, block_size, cache_pages, seq_pages, splits, page_begin, page_count, seq_len,
+        inv_sqrt_len, softmax_scale, _ptr(status)), "tq_decode_splitk_partials")
+
+
+def splitk_combine(workspace, pi_signs, gate, output, *, items, rows, rows_stride, head_size,
+                   splits, output_stage, inv_sqrt_len, status=None, stream=None):
+    lib = load_library()
+    _check(lib.tq_splitk_combine(
+        _stream(stream), _ptr(workspace), _ptr(pi_signs), _ptr(gate), _ptr(output),
+        _out_dtype(output), items, rows,
+        rows_stride, head_size, splits, output_stage, inv_sqrt_len, _ptr(status)),
+        "tq_splitk_combine")

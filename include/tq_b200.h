@@ -1,0 +1,218 @@
+/* tq_b200 -- C ABI of the B200-native TurboQuant KV-cache engine.
+ *
+ * Two families of entry points live in libtq_b200.so:
+ *
+ *   tq_*      the engine's own interface: status-returning, never throws.
+ *   launch_*  the operator surface of fxslava/ascend-micro-harness, symbol for
+ *             symbol and argument for argument, so that project's C++ host
+ *             code links against this library unchanged. Like the originals
+ *             they return void and report a refused geometry by throwing
+ *             std::invalid_argument across the boundary.
+ *
+ * Conventions shared by every entry point (they are the reference launchers'
+ * conventions): `stream` is an opaque stream handle (here a cudaStream_t, may
+ * be null for the default stream); every pointer except `stream` is DEVICE
+ * memory owned by the caller; nothing is allocated, nothing synchronises, the
+ * call returns once the work is queued on the stream.
+ *
+ * Cache formats (reference: reports/qwen35_turboquant_rfc.md:104-115 and
+ * tests/common/turboquant_oracle.hpp:31-38), P pages of S tokens, H KV heads,
+ * head size d, strip height 16:
+ *   key_cache, value_cache : int8[P*H*S*d/2], two signed INT4 codes per byte,
+ *       low nibble first.
+ *       key   nibble index = ((page*H + head)*S + token)*d + channel
+ *       value nibble index = ((page*H + head)*S)*d + (token/16)*(16*d)
+ *                            + channel*16 + token%16
+ *   scale_cache : float[2*P*H*S], index ((kv*P + page)*H + head)*S + token,
+ *       kv 0 = key plane, 1 = value plane.
+ */
+#ifndef TQ_B200_H
+#define TQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------ status codes */
+#define TQ_OK 0
+#define TQ_ERR_INVALID_ARGUMENT 1 /* geometry the kernels do not serve          */
+#define TQ_ERR_PARTIAL_STRIP 2    /* num_tokens not a whole number of strips    */
+#define TQ_ERR_LAUNCH 3           /* the CUDA runtime refused the launch        */
+#define TQ_ERR_NO_DEVICE 4        /* no CUDA device / kernel image unusable     */
+
+/* Bits a kernel ORs into the optional device status word. */
+#define TQ_STATUS_BAD_SLOT 0x1u     /* a strip's slots break the one-strip-one-page run */
+#define TQ_STATUS_BAD_PAGE 0x2u     /* a page index left the cache                      */
+#define TQ_STATUS_WAIT_EXPIRED 0x4u /* a bounded wait on a copy ran out                 */
+
+/* Activation element type of reshape_and_cache. */
+#define TQ_IN_INT8 0u
+#define TQ_IN_BF16 1u
+
+/* Where the rotation's sign diagonal comes from. The rotation is
+ *   M = (H_{d/32} (x) I32) diag(s) (I_{d/32} (x) H32)
+ * (kernels/ops/turboquant/turboquant_reshape_and_cache_a8.cpp:42-54); only s is
+ * data. TABLES_* read it out of the reference's resident 32x32 blocks
+ * (tests/common/turboquant_oracle.hpp:146-171): block g, row c0, column 0. */
+#define TQ_SIGNS_F32 0u         /* float[d], negative = -1                      */
+#define TQ_SIGNS_TABLES_I8 1u   /* int8  2*(d/32) row-major 32x32 blocks         */
+#define TQ_SIGNS_TABLES_BF16 2u /* the same blocks widened to bf16               */
+
+/* Decode output stages (kernels/ops/turboquant/fused_decode/common/turboquant_layout.h:139-147). */
+#define TQ_OUT_ROTATED 0u   /* acc / l, still in the cache's rotated basis      */
+#define TQ_OUT_UNROTATED 1u /* (acc / l) Pi                                     */
+#define TQ_OUT_GATED 2u     /* stage 1 divided by 1 + exp(-gate)                */
+
+/* Element type of the decode output. */
+#define TQ_DTYPE_BF16 0u
+#define TQ_DTYPE_F16 1u
+#define TQ_DTYPE_F32 2u
+
+const char* tq_version(void);
+const char* tq_status_string(int status);
+
+/* ------------------------------------------------------- reshape_and_cache
+ * Aligned writer: num_tokens is a whole number of 16-token strips and each
+ * strip fills 16 consecutive slots starting on a strip boundary of one page.
+ * Replaces launch_turboquant_reshape_and_cache_{a8,bf16}
+ * (kernels/ops/turboquant/turboquant_reshape_and_cache_a8.cpp:1578-1630,
+ *  kernels/ops/turboquant/turboquant_reshape_and_cache_bf16.cpp:1993-2059).
+ * key/value: [num_tokens][H*d] int8 or bf16. status may be null. */
+int tq_reshape_and_cache(void* stream, const void* key, const void* value, int8_t* key_cache,
+                         int8_t* value_cache, float* scale_cache, const int32_t* slot_mapping,
+                         const void* signs, uint32_t sign_source, uint32_t in_dtype,
+                         uint32_t num_tokens, uint32_t num_kv_heads, uint32_t head_size,
+                         uint32_t block_size, uint32_t num_blocks, float inv_sqrt_len,
+                         uint32_t* status);
+
+/* Scatter writer: 1..16 bf16 tokens per request at arbitrary slots, key rows
+ * written whole, value strips read-modify-written so unowned nibbles survive.
+ * Replaces launch_turboquant_reshape_scatter_aiv
+ * (kernels/ops/turboquant/vllm_integration_layer/op_adapter/turboquant_torch_adpt.h:40-46).
+ * cu_seqlens may be null (request r owns token r); slot < 0 = padded token. */
+int tq_reshape_scatter(void* stream, const uint16_t* key, const uint16_t* value,
+                       int8_t* key_cache, int8_t* value_cache, float* scale_cache,
+                       const int32_t* slot_mapping, const float* pi_signs,
+                       const int32_t* cu_seqlens, uint32_t num_requests, uint32_t num_kv_heads,
+                       uint32_t head_size, uint32_t block_size, uint32_t num_blocks,
+                       uint32_t item_begin, uint32_t item_count, float inv_sqrt_len,
+                       uint32_t* status);
+
+/* ------------------------------------------------------ paged split-K decode
+ * One decode step for `batch` sequences: rotate each query once, stream the
+ * sequence's packed pages through shared memory, online softmax per split,
+ * log-sum-exp merge of the per-split (m, l, acc) partials through `workspace`.
+ * The surface is the query / block_tables / context_lens one of
+ * include/turboquant_fused_decode_opt.hpp:149-158 over the strip cache of the
+ * AIC decoder (kernels/ops/turboquant/turboquant_paged_decode_attention.cpp:1727-1766).
+ *
+ *   query         bf16 [batch][num_heads][d], original basis
+ *   block_tables  int32 [batch][max_blocks], logical -> physical page
+ *   context_lens  int32 [batch], live tokens per sequence
+ *   pi_signs      float [d]
+ *   gate          float [batch][num_heads][d], read only by TQ_OUT_GATED
+ *   workspace     float [tq_decode_workspace_floats(...)]; unused when the
+ *                 launch resolves to one split
+ *   output        [batch][num_heads][d] of out_dtype (TQ_DTYPE_*)
+ *   splits        1..16, or 0 to choose from context lengths and SM count;
+ *                 max_context_hint (0 = max_blocks*block_size) feeds that choice
+ *                 since context_lens lives on the device
+ *   softmax_scale multiplies every score (the AIC decoder uses 1) */
+int tq_decode_splitk(void* stream, const uint16_t* query, const int8_t* key_cache,
+                     const int8_t* value_cache, const float* scale_cache,
+                     const int32_t* block_tables, const int32_t* context_lens,
+                     const float* pi_signs, const float* gate, float* workspace,
+                     void* output, uint32_t out_dtype, uint32_t batch, uint32_t num_heads,
+                     uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                     uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                     uint32_t max_context_hint, uint32_t output_stage, float inv_sqrt_len,
+                     float softmax_scale, uint32_t* status);
+
+/* The first half of tq_decode_splitk on its own: every (sequence, KV head, split)
+ * exports its partial record into `workspace`, nothing is merged. Followed by
+ * tq_splitk_combine(items = batch*num_kv_heads, rows = rows_stride =
+ * num_heads/num_kv_heads) it is tq_decode_splitk. `splits` must be resolved by
+ * the caller (tq_decode_choose_splits) when the combine is called separately. */
+int tq_decode_splitk_export(void* stream, const uint16_t* query, const int8_t* key_cache,
+                            const int8_t* value_cache, const float* scale_cache,
+                            const int32_t* block_tables, const int32_t* context_lens,
+                            const float* pi_signs, float* workspace, uint32_t batch,
+                            uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                            uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                            uint32_t splits, uint32_t max_context_hint, float inv_sqrt_len,
+                            float softmax_scale, uint32_t* status);
+
+/* Split count the launcher would pick for splits == 0. */
+uint32_t tq_decode_choose_splits(uint32_t batch, uint32_t num_kv_heads, uint32_t block_size,
+                                 uint32_t max_context, uint32_t sm_count);
+
+/* Floats of workspace a decode launch with this many splits needs:
+ * batch * num_kv_heads * splits partitions of (num_heads/num_kv_heads) rows,
+ * each row {m x8, l x8, acc[d]}, the record of
+ * include/turboquant_splitk_contract.hpp:23-27 with kChannels -> head_size. */
+size_t tq_decode_workspace_floats(uint32_t batch, uint32_t num_heads, uint32_t num_kv_heads,
+                                  uint32_t head_size, uint32_t splits);
+
+/* Per-split export only, no merge: the contract of
+ * launch_turboquant_paged_decode_splitk_aic (16 query rows per KV head, records
+ * of 16 + d floats, partitions of 16 rows; q_rot may be null). */
+int tq_decode_splitk_partials(void* stream, const uint16_t* q, const void* signs,
+                              uint32_t sign_source, const int8_t* key_cache,
+                              const int8_t* value_cache, const float* scale_cache,
+                              const uint32_t* table, uint16_t* q_rot, float* workspace,
+                              uint32_t requests, uint32_t heads, uint32_t rows,
+                              uint32_t head_size, uint32_t block_size, uint32_t cache_pages,
+                              uint32_t seq_pages, uint32_t splits, uint32_t page_begin,
+                              uint32_t page_count, uint32_t seq_len, float inv_sqrt_len,
+                              float softmax_scale, uint32_t* status);
+
+/* Log-sum-exp merge of `splits` partitions per (item,row) and the egress
+ * (routines/routine_probe_l2_atomic_sync.hpp:467-498;
+ *  routines/routine_vector_egress_rotate.hpp:186-277). Records as above. */
+int tq_splitk_combine(void* stream, const float* workspace, const float* pi_signs,
+                      const float* gate, void* output, uint32_t out_dtype, uint32_t items,
+                      uint32_t rows, uint32_t rows_stride, uint32_t head_size, uint32_t splits,
+                      uint32_t output_stage, float inv_sqrt_len, uint32_t* status);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+/* ------------------------------------------------ reference-named launchers
+ * Declared for C++ callers only: they throw std::invalid_argument. Signatures
+ * are those of the reference (file:line beside each). */
+#ifdef __cplusplus
+extern "C" {
+/* kernels/ops/turboquant/turboquant_reshape_and_cache_a8.cpp:1578-1585 */
+void launch_turboquant_reshape_and_cache_a8(
+    void* stream, const int8_t* key, const int8_t* value, int8_t* key_cache, int8_t* value_cache,
+    float* scale_cache, const int32_t* slot_mapping, const float* pi_signs, const int32_t* tables,
+    uint32_t num_tokens, uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+    uint32_t num_blocks, uint32_t tokens_per_core, float inv_sqrt_len, bool reuse_mode4_flags);
+/* kernels/ops/turboquant/turboquant_reshape_and_cache_bf16.cpp:1993-2000 */
+void launch_turboquant_reshape_and_cache_bf16(
+    void* stream, const uint16_t* key, const uint16_t* value, int8_t* key_cache,
+    int8_t* value_cache, float* scale_cache, const int32_t* slot_mapping, const float* pi_signs,
+    const int32_t* tables, uint32_t num_tokens, uint32_t num_kv_heads, uint32_t head_size,
+    uint32_t block_size, uint32_t num_blocks, uint32_t tokens_per_core, float inv_sqrt_len,
+    bool reuse_mode4_flags);
+/* kernels/ops/turboquant/turboquant_reshape_scatter_aiv.cpp:760-766 */
+void launch_turboquant_reshape_scatter_aiv(
+    void* stream, uint32_t block_dim, uint16_t* key, uint16_t* value, int8_t* key_cache,
+    int8_t* value_cache, float* scale_cache, int32_t* slot_mapping, float* pi_signs,
+    int32_t* cu_seqlens, int32_t* launch_probe, uint32_t num_requests, uint32_t num_kv_heads,
+    uint32_t head_size, uint32_t block_size, uint32_t num_blocks, uint32_t item_begin,
+    uint32_t item_count, float inv_sqrt_len);
+/* kernels/ops/turboquant/turboquant_paged_decode_attention.cpp:1727-1745 */
+void launch_turboquant_paged_decode_splitk_aic(
+    void* stream, uint16_t* q, uint16_t* pi_table, int8_t* key, int8_t* value, float* scales,
+    uint32_t* table, uint16_t* qrot, float* workspace, uint32_t requests, uint32_t heads,
+    uint32_t block_size, uint32_t cache_pages, uint32_t seq_pages, uint32_t splits,
+    uint32_t page_begin, uint32_t page_count, uint32_t seq_len);
+}
+#endif
+
+#endif /* TQ_B200_H */
