@@ -48,5 +48,51 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_acl_shim(force: bool = False) -> str:
+    """libtq_acl_shim.so: the ACL runtime surface of the reference harnesses over CUDA."""
+    src = os.path.join(CSRC, "acl_shim.cpp")
+    if force or _stale(ACL_LIB, [src]):
+        cmd = [_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-o", ACL_LIB, src,
+               "-lcudart"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
+    return ACL_LIB
+
+
+# The reference's own device validation programs, compiled from where they lie in a
+# checkout of the reference against this library and the ACL shim. Outputs go to
+# oracle/_ref/ only; nothing of the reference is copied into this tree.
+REFERENCE_HARNESSES = [
+    "tests/npu/validation/test_turboquant_a8_validation.cpp",
+    "tests/npu/validation/test_turboquant_bf16_validation.cpp",
+    "tests/npu/validation/test_turboquant_decode_splitk_aic_validation.cpp",
+]
+
+
+def build_reference_harness(ref_root: str = "/root/reference") -> list[str]:
+    if not os.path.exists(os.path.join(ref_root, REFERENCE_HARNESSES[0])):
+        return []
+    build()
+    build_acl_shim()
+    out_dir = os.path.join(PKG, "..", "oracle", "_ref")
+    os.makedirs(out_dir, exist_ok=True)
+    cxx = shutil.which("g++") or "g++"
+    built = []
+    for rel in REFERENCE_HARNESSES:
+        exe = os.path.join(out_dir, os.path.splitext(os.path.basename(rel))[0])
+        cmd = [cxx, "-O2", "-std=c++17", f"-I{ref_root}/tests/host_stubs", f"-I{ref_root}",
+               os.path.join(ref_root, rel), "-o", exe, f"-L{PKG}", "-ltq_b200", "-ltq_acl_shim",
+               "-Wl,-rpath,$ORIGIN/../../ascend_micro_harness_b200", "-pthread"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"building {rel} failed:\n" + res.stdout + res.stderr)
+        built.append(exe)
+    return built
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_acl_shim(force="--force" in sys.argv))
+    if "--harness" in sys.argv:
+        print(build_reference_harness())

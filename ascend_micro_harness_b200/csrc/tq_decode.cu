@@ -164,6 +164,11 @@ tq_decode_partial_kernel(const DecodeParams p)
     uint32_t s1 = s0 + rc * SP;
     const uint32_t live_strips = (ctx + kStrip - 1u) / kStrip;
     if (s1 > live_strips) s1 = live_strips;
+    // A split whose page range is empty takes no part at all; one whose pages all
+    // lie past the live tokens still rotates and publishes its query (the rotation
+    // does not depend on the cache) and then exports the neutral element
+    // (kernels/ops/turboquant/turboquant_paged_decode_attention.cpp:1626-1637).
+    const bool no_pages = rc == 0u;
     const bool empty = s1 <= s0;
 
     float* rec_base = p.workspace +
@@ -171,12 +176,11 @@ tq_decode_partial_kernel(const DecodeParams p)
                           kRecord;
 
     if (empty) {
-        // The exact neutral element, so every partition holds a record.
         for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
             const int c = i % kRecord;
             rec_base[i] = c < 8 ? kMaskedScore : 0.0f;
         }
-        return;
+        if (no_pages || p.q_rot == nullptr) return;
     }
 
     // ---- rotate the query rows once: FP32 ingress cascade, scale, round to bf16
@@ -216,6 +220,7 @@ tq_decode_partial_kernel(const DecodeParams p)
         __syncthreads();
         qbuf = fin;
     }
+    if (empty) return;
 
     // ---- q_rot^T as B fragments, in the contraction order the key words deliver.
     uint32_t bq[2 * WPT][2];

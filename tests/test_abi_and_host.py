@@ -1,0 +1,82 @@
+"""The C-ABI library: it loads, exports every symbol include/tq_b200.h declares, and its
+host-side logic (split choice, workspace sizing, geometry refusal) behaves as specified.
+No kernel is launched here."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "tq_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b((?:tq|launch)_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    import ascend_micro_harness_b200 as tq
+    lib = tq.load_library()
+    names = declared_symbols()
+    assert len(names) >= 13
+    for n in names:
+        assert hasattr(lib, n), f"libtq_b200.so does not export {n}"
+    from ascend_micro_harness_b200 import _lib
+    assert set(names) == set(_lib.SIGNATURES), "Python signature table and header disagree"
+    assert b"sm_100a" in lib.tq_version()
+
+
+def test_acl_shim_exports_the_sixteen_calls():
+    path = os.path.join(ROOT, "ascend_micro_harness_b200", "libtq_acl_shim.so")
+    if not os.path.exists(path):
+        from ascend_micro_harness_b200 import build
+        build.build_acl_shim()
+    lib = C.CDLL(path)
+    for n in ("aclInit aclFinalize aclrtSetDevice aclrtResetDevice aclrtCreateStream aclrtDestroyStream "
+              "aclrtSynchronizeStream aclrtMalloc aclrtFree aclrtMemcpy aclrtMemset aclrtCreateEvent "
+              "aclrtDestroyEvent aclrtRecordEvent aclrtSynchronizeEvent aclrtEventElapsedTime").split():
+        assert hasattr(lib, n)
+
+
+def test_split_choice():
+    import ascend_micro_harness_b200 as tq
+    assert tq.choose_splits(64, 8, 16, 256) == 1            # short contexts run un-split
+    assert tq.choose_splits(1, 8, 16, 4096) == 16           # one sequence: fill the machine
+    assert tq.choose_splits(1, 8, 16, 1024) == 8            # ... but keep >= 128 tokens per split
+    assert 1 <= tq.choose_splits(64, 8, 16, 32768) <= 4     # a big batch needs few splits
+    assert tq.choose_splits(4096, 8, 16, 32768) == 1
+    for b in (1, 3, 64, 1000):
+        for ctx in (1, 600, 5000, 70000):
+            s = tq.choose_splits(b, 8, 16, ctx)
+            assert 1 <= s <= 16 and s <= max(1, (ctx + 15) // 16)
+
+
+def test_workspace_sizing():
+    import ascend_micro_harness_b200 as tq
+    assert tq.decode_workspace_floats(64, 32, 8, 128, 4) == 64 * 8 * 4 * 4 * (16 + 128)
+    assert tq.decode_workspace_floats(2, 64, 4, 256, 8) == 2 * 4 * 8 * 16 * 272
+
+
+def test_geometry_is_refused_before_any_launch():
+    from ascend_micro_harness_b200._lib import load_library
+    lib = load_library()
+    p = C.c_void_p(16)   # never dereferenced: every call below is refused on the host
+    # 24 tokens is not a whole number of strips (reference: a8.cpp:1606-1609)
+    assert lib.tq_reshape_and_cache(None, p, p, p, p, p, p, p, 0, 0, 24, 1, 128, 16, 4, 0.1, None) == 2
+    assert lib.tq_reshape_and_cache(None, p, p, p, p, p, p, p, 0, 0, 32, 1, 96, 16, 4, 0.1, None) == 1
+    assert lib.tq_reshape_and_cache(None, p, p, p, p, p, p, p, 0, 0, 32, 1, 128, 24, 4, 0.1, None) == 1
+    assert lib.tq_reshape_and_cache(None, p, p, p, p, p, p, p, 0, 0, 0, 1, 128, 16, 4, 0.1, None) == 0
+    # decode: heads not a multiple of KV heads; 17 splits; bad head size
+    args = [None, p, p, p, p, p, p, p, p, p, p, 0]
+    assert lib.tq_decode_splitk(*args, 2, 30, 8, 128, 16, 8, 4, 1, 0, 0, 0.1, 1.0, None) == 1
+    assert lib.tq_decode_splitk(*args, 2, 32, 8, 128, 16, 8, 4, 17, 0, 0, 0.1, 1.0, None) == 1
+    assert lib.tq_decode_splitk(*args, 2, 32, 8, 64, 16, 8, 4, 1, 0, 0, 0.1, 1.0, None) == 1
+    # AIC contract: page window past the sequence, seq_len past the window
+    # (reference: turboquant_paged_decode_attention.cpp:1747-1759)
+    part = [None, p, p, 2, p, p, p, p, p, p]
+    assert lib.tq_decode_splitk_partials(*part, 1, 1, 16, 256, 128, 8, 4, 2, 3, 2, 0, 0.0625, 1.0, None) == 1
+    assert lib.tq_decode_splitk_partials(*part, 1, 1, 16, 256, 128, 8, 4, 2, 0, 2, 300, 0.0625, 1.0, None) == 1
+    assert lib.tq_decode_splitk_partials(*part, 1, 1, 16, 256, 128, 8, 4, 17, 0, 2, 0, 0.0625, 1.0, None) == 1
+    assert lib.tq_status_string(2).decode().startswith("num_tokens")
