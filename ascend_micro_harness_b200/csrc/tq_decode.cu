@@ -37,9 +37,12 @@
 namespace tq {
 
 constexpr int kDecWarps = 4;
+constexpr int kDecCtasPerSm = 4;
 constexpr int kTileStrips = 2;   // strips per pipeline stage of one warp
 constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr uint32_t kWaitLimit = 1u << 17;  // bounded mbarrier wait, about 0.1 s
 
 struct DecodeParams {
     const uint16_t* q;        // [items*rows][D] bf16
@@ -58,37 +61,99 @@ struct DecodeParams {
     uint32_t* status;
 };
 
+// Shared-memory plan of one CTA. A key strip is stored as four 4-token row groups;
+// odd groups are shifted by kKeyPad bytes so that the two token rows one quarter-warp
+// reads (tokens t and t+4) fall into different banks.
 template <int D>
 struct DecodeSmem {
+    static constexpr int kRowBytes = D / 2;
     static constexpr int kStripBytes = kStrip * D / 2;
-    static constexpr int kStageBytes = kTileStrips * (2 * kStripBytes + 2 * kStrip * 4);
-    static constexpr int kQBytes = 2 * 8 * D * 4;
+    static constexpr int kKeyPad = D == 128 ? 64 : 16;
+    static constexpr int kKeyGroup = 4 * kRowBytes;                 // 4 token rows
+    static constexpr int kKeyStride = 2 * kKeyGroup + kKeyPad;      // two groups + pad
+    static constexpr int kKeyBytes = 2 * kKeyStride;                // one padded key strip
+    static constexpr int kStripStage = kKeyBytes + kStripBytes + 2 * kStrip * 4;
+    static constexpr int kStageBytes = kTileStrips * kStripStage;
     static constexpr int kRingBytes = kDecWarps * kStages * kStageBytes;
+    static constexpr int kQBytes = 2 * 8 * D * 4;
     static constexpr int kMergeBytes = kDecWarps * 8 * (D + 2) * 4;
-    static constexpr int kTotal = kQBytes + (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes);
+    static constexpr int kBody = kRingBytes > kQBytes ? (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes)
+                                                      : (kQBytes > kMergeBytes ? kQBytes : kMergeBytes);
+    static constexpr int kBarOffset = kBody;                        // kDecWarps*kStages mbarriers
+    static constexpr int kTotal = kBody + kDecWarps * kStages * 8 + 64;
+    static constexpr uint32_t kStripTx = 2 * kStripBytes + 2 * kStrip * 4;  // bytes one strip brings
 };
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
+// ---- mbarrier / bulk-copy primitives (all waits bounded)
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
 {
-    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src));
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait()
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
+{
+    for (uint32_t i = 0; i < kWaitLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// 1-D bulk copy global -> shared, completion counted in bytes on `bar`. Both
+// addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
 }
 
-// Two packed INT4 codes (bits 0-3 and 16-19 of x) -> two exact bf16 integers.
-// (x & 0x000F000F) ^ 0x43084308 is bf16(128 + (code ^ 8)); minus 136 is the
-// sign-extended code.
-__device__ __forceinline__ uint32_t dq2(uint32_t x)
+// Two packed INT4 codes -> two exact f16 integers. The low variant takes the codes
+// at bits 0-3 / 16-19 of x, the high variant those at bits 4-7 / 20-23:
+//   (x & 0x000F000F) ^ 0x64086408 = f16(1024 + (code ^ 8));  minus 1032 = code
+//   (x & 0x00F000F0) ^ 0x64806480 = f16(1024 + 16 (code ^ 8)); /16 minus 72 = code
+__device__ __forceinline__ uint32_t dq_lo(uint32_t x)
 {
     uint32_t t;
-    asm("lop3.b32 %0, %1, 0x000F000F, 0x43084308, 0x6A;\n" : "=r"(t) : "r"(x));
-    asm("sub.rn.bf16x2 %0, %1, %2;\n" : "=r"(t) : "r"(t), "r"(0x43084308u));
+    asm("lop3.b32 %0, %1, 0x000F000F, 0x64086408, 0x6A;\n" : "=r"(t) : "r"(x));
+    asm("sub.rn.f16x2 %0, %1, %2;\n" : "=r"(t) : "r"(t), "r"(0x64086408u));
     return t;
+}
+__device__ __forceinline__ uint32_t dq_hi(uint32_t x)
+{
+    uint32_t t;
+    asm("lop3.b32 %0, %1, 0x00F000F0, 0x64806480, 0x6A;\n" : "=r"(t) : "r"(x));
+    // 0x2C00 = 1/16, 0xD480 = -72
+    asm("fma.rn.f16x2 %0, %1, %2, %3;\n" : "=r"(t) : "r"(t), "r"(0x2C002C00u), "r"(0xD480D480u));
+    return t;
+}
+
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a)
@@ -105,28 +170,36 @@ __device__ __forceinline__ float ex2f(float x)
     return y;
 }
 
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi)
 {
-    return static_cast<uint32_t>(f32_to_bf16_bits(lo)) |
-           (static_cast<uint32_t>(f32_to_bf16_bits(hi)) << 16);
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+__device__ __forceinline__ float2 unpack_f16x2(uint32_t v)
+{
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
 }
 
-// Which token of a strip rides in MMA row i (0..7; rows 8..15 carry token + 8).
-// Chosen so that after movmatrix a thread's P^T pair covers tokens (qd, qd+4),
-// the pair one mask extracts from a value word.
-__device__ __forceinline__ int token_of_row(int i) { return (i >> 1) + 4 * (i & 1); }
+// Which tokens of a strip ride in MMA rows i (c0,c1) and i+8 (c2,c3). Chosen so
+// that after movmatrix a thread's P^T pairs cover tokens (t, t+4) of one value word,
+// the pairs one mask extracts, and a byte permute replaces the shifts.
+__device__ __forceinline__ int token_row_lo(int i) { return ((i >> 2) << 3) + (((i >> 1) & 1) << 1) + ((i & 1) << 2); }
+__device__ __forceinline__ int token_row_hi(int i) { return token_row_lo(i) + 1; }
 
-template <int D>
-__global__ void __launch_bounds__(kDecWarps * 32)
+template <int D, bool PRECISE>
+__global__ void __launch_bounds__(kDecWarps * 32, kDecCtasPerSm)
 tq_decode_partial_kernel(const DecodeParams p)
 {
     using L = DecodeSmem<D>;
     constexpr int kRecord = 16 + D;
     constexpr int MT = D / 16;    // 16-channel m-tiles of the value contraction
     constexpr int WPT = D / 32;   // packed words per thread per key row
-    extern __shared__ __align__(16) uint8_t smem[];
-    float* qbuf = reinterpret_cast<float*>(smem);            // [2][8][D]
-    uint8_t* ring = smem + L::kQBytes;
+    extern __shared__ __align__(128) uint8_t smem[];
+    float* qbuf = reinterpret_cast<float*>(smem);            // [2][8][D], prologue only
+    uint8_t* ring = smem;                                    // aliases qbuf after the prologue
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+    __shared__ float row_unscale[8];                         // per query row: 2^-k * softmax_scale * log2e
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, qd = lane & 3;
@@ -208,7 +281,7 @@ tq_decode_partial_kernel(const DecodeParams p)
             __syncthreads();
             cur ^= 1;
         }
-        // qbuf[cur] holds Pi*sqrt(d) q; narrow. Left in place as bf16-exact floats.
+        // qbuf[cur] holds Pi*sqrt(d) q; narrow to bf16 (the pinned operand), publish it.
         float* fin = qbuf + cur * 8 * D;
         for (int i = tid; i < 8 * D; i += blockDim.x) {
             const uint16_t b = f32_to_bf16_bits(fin[i] * p.inv_sqrt_len);
@@ -222,16 +295,35 @@ tq_decode_partial_kernel(const DecodeParams p)
     }
     if (empty) return;
 
-    // ---- q_rot^T as B fragments, in the contraction order the key words deliver.
+    // ---- the MMAs run in f16: scale every query row by a power of two so its largest
+    // entry sits at 2^14 (exact for all but entries 2^28 below the largest), and undo
+    // it in the score scale. Two rows per warp.
+    for (int row = warp * 2; row < warp * 2 + 2; ++row) {
+        float am = 0.f;
+        for (int c = lane; c < D; c += 32) am = fmaxf(am, fabsf(qbuf[row * D + c]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        // 2^(14 - e) and its inverse from the exponent field; a zero row keeps scale 1
+        const int e_bits = __float_as_int(am) & 0x7F800000;
+        const float up = am > 0.f ? __int_as_float((141 << 23) - e_bits + (127 << 23)) : 1.0f;
+        const float down = am > 0.f ? __int_as_float(e_bits - (14 << 23)) : 1.0f;
+        for (int c = lane; c < D; c += 32) qbuf[row * D + c] *= up;
+        if (lane == 0) row_unscale[row] = down * p.softmax_scale * kLog2e;
+    }
+    __syncthreads();
+
+    // ---- q_rot^T as f16 B fragments, in the contraction order the key words deliver.
     uint32_t bq[2 * WPT][2];
 #pragma unroll
     for (int wi = 0; wi < WPT; ++wi)
 #pragma unroll
         for (int kh = 0; kh < 2; ++kh) {
             const float* qr = qbuf + r * D + qd * (D / 4) + wi * 8 + 2 * kh;
-            bq[wi * 2 + kh][0] = pack_bf16x2(qr[0], qr[4]);
-            bq[wi * 2 + kh][1] = pack_bf16x2(qr[1], qr[5]);
+            bq[wi * 2 + kh][0] = pack_f16x2(qr[0], qr[4]);
+            bq[wi * 2 + kh][1] = pack_f16x2(qr[1], qr[5]);
         }
+    const float unscale0 = row_unscale[qd * 2], unscale1 = row_unscale[qd * 2 + 1];
+    __syncthreads();  // everyone is done with qbuf: the ring may overwrite it
 
     // ---- per-warp pipeline over tiles warp, warp+4, ...
     const uint32_t tiles = (s1 - s0 + kTileStrips - 1u) / kTileStrips;
@@ -239,8 +331,20 @@ tq_decode_partial_kernel(const DecodeParams p)
                                   ? (tiles - warp + kDecWarps - 1u) / kDecWarps : 0u;
     const int32_t* table_row = p.table + static_cast<size_t>(seq) * p.table_stride;
     uint8_t* my_ring = ring + warp * kStages * L::kStageBytes;
+    const uint32_t my_ring_s = smem_u32(my_ring);
+    const uint32_t my_bar = smem_u32(bars + warp * kStages);
     const size_t head_block = static_cast<size_t>(p.S) * D / 2;  // bytes of one (page, head)
     const size_t scale_plane = static_cast<size_t>(p.P) * p.H * p.S;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(my_bar + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    // generic-proxy writes of the prologue are ordered before the async-proxy writes
+    // of the bulk copies that reuse the same shared memory
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    __syncwarp();
 
     auto strip_of = [&](uint32_t j, int ts) { return s0 + (warp + j * kDecWarps) * kTileStrips + ts; };
     auto load_pages = [&](uint32_t j, int32_t (&pg)[kTileStrips]) {
@@ -250,33 +354,40 @@ tq_decode_partial_kernel(const DecodeParams p)
             pg[ts] = (j < my_tiles && s < s1) ? __ldg(table_row + s / SP) : -1;
         }
     };
+    // One warp instruction issues every copy of the tile: lane = ts*8 + piece, pieces
+    // 0..3 the four key row groups, 4 the value strip, 5 / 6 the key / value scales.
     auto issue = [&](uint32_t j, const int32_t (&pg)[kTileStrips]) {
-        uint8_t* st = my_ring + (j % kStages) * L::kStageBytes;
+        const uint32_t stage = j % kStages;
+        const uint32_t bar = my_bar + 8 * stage;
+        uint32_t nstrips = 0;
 #pragma unroll
-        for (int ts = 0; ts < kTileStrips; ++ts) {
-            if (pg[ts] < 0) continue;
-            uint32_t page = static_cast<uint32_t>(pg[ts]);
-            if (page >= p.P) {
-                if (lane == 0) report(p.status, TQ_STATUS_BAD_PAGE);
-                page = 0;
-            }
-            const uint32_t sip = strip_of(j, ts) % SP;
-            const size_t off = (static_cast<size_t>(page) * p.H + head) * head_block +
-                               static_cast<size_t>(sip) * L::kStripBytes;
-            uint8_t* kdst = st + ts * L::kStripBytes;
-            uint8_t* vdst = st + (kTileStrips + ts) * L::kStripBytes;
-#pragma unroll
-            for (int i = 0; i < L::kStripBytes / 512; ++i) {
-                cp_async16(kdst + i * 512 + lane * 16, p.key_cache + off + i * 512 + lane * 16);
-                cp_async16(vdst + i * 512 + lane * 16, p.value_cache + off + i * 512 + lane * 16);
-            }
-            if (lane < 8) {
-                const int plane = lane >> 2, part = lane & 3;
-                const float* src = p.scale_cache + plane * scale_plane +
-                                   (static_cast<size_t>(page) * p.H + head) * p.S + sip * kStrip + part * 4;
-                float* dst = reinterpret_cast<float*>(st + 2 * kTileStrips * L::kStripBytes) +
-                             (plane * kTileStrips + ts) * kStrip + part * 4;
-                cp_async16(dst, src);
+        for (int ts = 0; ts < kTileStrips; ++ts) nstrips += pg[ts] >= 0;
+        if (lane == 0) mbar_expect_tx(bar, nstrips * L::kStripTx);
+        __syncwarp();
+        const int ts = lane >> 3, piece = lane & 7;
+        if (ts < kTileStrips && piece < 7) {
+            const int32_t pgv = ts == 0 ? pg[0] : pg[kTileStrips - 1];
+            if (pgv >= 0) {
+                uint32_t page = static_cast<uint32_t>(pgv);
+                if (page >= p.P) {
+                    report(p.status, TQ_STATUS_BAD_PAGE);
+                    page = 0;
+                }
+                const uint32_t sip = strip_of(j, ts) % SP;
+                const size_t off = (static_cast<size_t>(page) * p.H + head) * head_block +
+                                   static_cast<size_t>(sip) * L::kStripBytes;
+                const uint32_t st = my_ring_s + stage * L::kStageBytes + ts * L::kStripStage;
+                if (piece < 4) {
+                    bulk_g2s(st + (piece >> 1) * L::kKeyStride + (piece & 1) * (L::kKeyGroup + L::kKeyPad),
+                             p.key_cache + off + piece * L::kKeyGroup, L::kKeyGroup, bar);
+                } else if (piece == 4) {
+                    bulk_g2s(st + L::kKeyBytes, p.value_cache + off, L::kStripBytes, bar);
+                } else {
+                    const int plane = piece - 5;
+                    const float* src = p.scale_cache + plane * scale_plane +
+                                       (static_cast<size_t>(page) * p.H + head) * p.S + sip * kStrip;
+                    bulk_g2s(st + L::kKeyBytes + L::kStripBytes + plane * kStrip * 4, src, kStrip * 4, bar);
+                }
             }
         }
     };
@@ -287,122 +398,165 @@ tq_decode_partial_kernel(const DecodeParams p)
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+    // Running power-of-two normaliser of the value scales: P is carried in f16, so
+    // it is kept in [0, 1] by dividing the value scale by the largest seen so far.
+    float vnorm = 0.f, inv_vnorm = 0.f;
 
     int32_t pg_next[kTileStrips];
     for (uint32_t j = 0; j < kStages - 1; ++j) {
         load_pages(j, pg_next);
         if (j < my_tiles) issue(j, pg_next);
-        cp_async_commit();
     }
     load_pages(kStages - 1, pg_next);
 
-    const int tok_lo = token_of_row(r);  // token (within a strip) of this thread's low row
-    const float sscale = p.softmax_scale;
+    const int tok_lo = token_row_lo(r), tok_hi = token_row_hi(r);
+    const int koff_lo = (tok_lo >> 3) * L::kKeyStride + ((tok_lo >> 2) & 1) * (L::kKeyGroup + L::kKeyPad) +
+                        (tok_lo & 3) * L::kRowBytes + qd * (D / 8);
+    const int koff_hi = koff_lo + L::kRowBytes;   // tok_hi = tok_lo + 1, same row group
+    // byte-permute selector that brings this thread's value-token pairs to bits 0-7 / 16-23
+    const uint32_t vsel = qd == 0 ? 0x3210u : qd == 1 ? 0x4321u : qd == 2 ? 0x7654u : 0x0765u;
+    bool broken = false;
 
-    for (uint32_t j = 0; j < my_tiles; ++j) {
+    for (uint32_t j = 0; j < my_tiles && !broken; ++j) {
         if (j + kStages - 1 < my_tiles) issue(j + kStages - 1, pg_next);
-        cp_async_commit();
         load_pages(j + kStages, pg_next);
-        cp_async_wait<kStages - 1>();
-        __syncwarp();
+        if (!mbar_wait_bounded(my_bar + 8 * (j % kStages), (j / kStages) & 1u)) {
+            if (lane == 0) report(p.status, TQ_STATUS_WAIT_EXPIRED);
+            broken = true;
+            break;
+        }
 
         const uint8_t* st = my_ring + (j % kStages) * L::kStageBytes;
-        const float* scales = reinterpret_cast<const float*>(st + 2 * kTileStrips * L::kStripBytes);
+        // warp-uniform: the tile reaches past this split's strips or past the live tokens
+        const bool tail = strip_of(j, kTileStrips - 1) >= s1 ||
+                          (strip_of(j, kTileStrips - 1) + 1u) * kStrip > ctx;
 
-        // -- scores^T for the tile's strips
+        // -- scores^T for the tile's strips, in log2 units
         float sc[kTileStrips][4];
         bool live[kTileStrips][2];
         float mx[2] = {kMaskedScore, kMaskedScore};
+        float vmax = 0.f;
 #pragma unroll
         for (int ts = 0; ts < kTileStrips; ++ts) {
-            const uint32_t strip = strip_of(j, ts);
-            const uint32_t tbase = strip * kStrip;
-            live[ts][0] = strip < s1 && tbase + tok_lo < ctx;
-            live[ts][1] = strip < s1 && tbase + tok_lo + 8 < ctx;
+            const uint8_t* ss = st + ts * L::kStripStage;
+            const float* scales = reinterpret_cast<const float*>(ss + L::kKeyBytes + L::kStripBytes);
             float c[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint8_t* krow = st + ts * L::kStripBytes + tok_lo * (D / 2) + qd * (D / 8);
 #pragma unroll
             for (int w4 = 0; w4 < WPT / 4; ++w4) {
-                const uint4 lo = *reinterpret_cast<const uint4*>(krow + w4 * 16);
-                const uint4 hi = *reinterpret_cast<const uint4*>(krow + 8 * (D / 2) + w4 * 16);
+                const uint4 lo = *reinterpret_cast<const uint4*>(ss + koff_lo + w4 * 16);
+                const uint4 hi = *reinterpret_cast<const uint4*>(ss + koff_hi + w4 * 16);
                 const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int wi = w4 * 4 + k;
-#pragma unroll
-                    for (int kh = 0; kh < 2; ++kh)
-                        mma_bf16_16816(c, dq2(wl[k] >> (8 * kh)), dq2(wh[k] >> (8 * kh)),
-                                       dq2(wl[k] >> (8 * kh + 4)), dq2(wh[k] >> (8 * kh + 4)),
-                                       bq[wi * 2 + kh][0], bq[wi * 2 + kh][1]);
+                    const uint32_t xl8 = wl[k] >> 8, xh8 = wh[k] >> 8;
+                    mma_f16_16816(c, dq_lo(wl[k]), dq_lo(wh[k]), dq_hi(wl[k]), dq_hi(wh[k]),
+                                  bq[wi * 2][0], bq[wi * 2][1]);
+                    mma_f16_16816(c, dq_lo(xl8), dq_lo(xh8), dq_hi(xl8), dq_hi(xh8),
+                                  bq[wi * 2 + 1][0], bq[wi * 2 + 1][1]);
                 }
             }
-            const float ks_lo = scales[ts * kStrip + tok_lo] * sscale;
-            const float ks_hi = scales[ts * kStrip + tok_lo + 8] * sscale;
-            // Dead lanes are overwritten, never multiplied: their scale may be a NaN.
-            sc[ts][0] = live[ts][0] ? c[0] * ks_lo : kMaskedScore;
-            sc[ts][1] = live[ts][0] ? c[1] * ks_lo : kMaskedScore;
-            sc[ts][2] = live[ts][1] ? c[2] * ks_hi : kMaskedScore;
-            sc[ts][3] = live[ts][1] ? c[3] * ks_hi : kMaskedScore;
+            const float ks_lo = scales[tok_lo], ks_hi = scales[tok_hi];
+            sc[ts][0] = c[0] * (ks_lo * unscale0);
+            sc[ts][1] = c[1] * (ks_lo * unscale1);
+            sc[ts][2] = c[2] * (ks_hi * unscale0);
+            sc[ts][3] = c[3] * (ks_hi * unscale1);
+            live[ts][0] = live[ts][1] = true;
+            if (tail) {
+                // Dead lanes are overwritten, never multiplied: their scale may be a NaN.
+                const uint32_t strip = strip_of(j, ts);
+                live[ts][0] = strip < s1 && strip * kStrip + tok_lo < ctx;
+                live[ts][1] = strip < s1 && strip * kStrip + tok_hi < ctx;
+                if (!live[ts][0]) sc[ts][0] = sc[ts][1] = kMaskedScore;
+                if (!live[ts][1]) sc[ts][2] = sc[ts][3] = kMaskedScore;
+            }
             mx[0] = fmaxf(mx[0], fmaxf(sc[ts][0], sc[ts][2]));
             mx[1] = fmaxf(mx[1], fmaxf(sc[ts][1], sc[ts][3]));
+            const float vs_lo = scales[kStrip + tok_lo], vs_hi = scales[kStrip + tok_hi];
+            vmax = fmaxf(vmax, fmaxf(live[ts][0] ? fabsf(vs_lo) : 0.f, live[ts][1] ? fabsf(vs_hi) : 0.f));
         }
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], 4));
-            mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], 8));
-            mx[q] = fmaxf(mx[q], __shfl_xor_sync(0xffffffffu, mx[q], 16));
+        for (int o = 4; o <= 16; o <<= 1) {
+            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+            vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
         }
-        // -- online softmax update
-        float alpha[2];
+        // -- online softmax update; the accumulator is rescaled only when something moved
+        float alpha[2] = {1.f, 1.f};
+        bool moved = false;
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const float m_new = fmaxf(m_run[q], mx[q]);
-            alpha[q] = ex2f((m_run[q] - m_new) * kLog2e);
-            m_run[q] = m_new;
-            l_run[q] *= alpha[q];
+        for (int q = 0; q < 2; ++q)
+            if (mx[q] > m_run[q]) {
+                alpha[q] = ex2f(m_run[q] - mx[q]);
+                m_run[q] = mx[q];
+                moved = true;
+            }
+        float vratio = 1.f;
+        if (vmax > vnorm) {  // warp-uniform: value scales depend on the token only
+            // the power of two above vmax; the ratio old/new is exact
+            const float nv = __int_as_float((__float_as_int(vmax) & 0x7F800000) + (1 << 23));
+            inv_vnorm = __int_as_float((254 << 23) - __float_as_int(nv));
+            vratio = vnorm * inv_vnorm;
+            vnorm = nv;
+            moved = true;
         }
+        if (__any_sync(0xffffffffu, moved)) {
+            l_run[0] *= alpha[0];
+            l_run[1] *= alpha[1];
+            const float a0 = alpha[0] * vratio, a1 = alpha[1] * vratio;
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            acc[mt][0] *= alpha[0];
-            acc[mt][1] *= alpha[1];
-            acc[mt][2] *= alpha[0];
-            acc[mt][3] *= alpha[1];
+            for (int mt = 0; mt < MT; ++mt) {
+                acc[mt][0] *= a0;
+                acc[mt][1] *= a1;
+                acc[mt][2] *= a0;
+                acc[mt][3] *= a1;
+            }
         }
         // -- P, then acc^T += V^T P^T
 #pragma unroll
         for (int ts = 0; ts < kTileStrips; ++ts) {
-            if (strip_of(j, ts) >= s1) continue;  // warp-uniform
-            const float vs_lo = scales[(kTileStrips + ts) * kStrip + tok_lo];
-            const float vs_hi = scales[(kTileStrips + ts) * kStrip + tok_lo + 8];
+            if (tail && strip_of(j, ts) >= s1) continue;  // warp-uniform
+            const uint8_t* ss = st + ts * L::kStripStage;
+            const float* scales = reinterpret_cast<const float*>(ss + L::kKeyBytes + L::kStripBytes);
+            const float vs_lo = scales[kStrip + tok_lo] * inv_vnorm;
+            const float vs_hi = scales[kStrip + tok_hi] * inv_vnorm;
             float pw[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float pr = ex2f((sc[ts][i] - m_run[i & 1]) * kLog2e);
+                const float pr = ex2f(sc[ts][i] - m_run[i & 1]);
                 l_run[i & 1] += pr;
-                pw[i] = live[ts][i >> 1] ? pr * (i < 2 ? vs_lo : vs_hi) : 0.0f;
+                pw[i] = pr * (i < 2 ? vs_lo : vs_hi);
             }
-            const uint32_t h0 = pack_bf16x2(pw[0], pw[1]), h1 = pack_bf16x2(pw[2], pw[3]);
-            const uint32_t l0 = pack_bf16x2(pw[0] - bf16_bits_to_f32(h0 & 0xFFFFu),
-                                            pw[1] - bf16_bits_to_f32(h0 >> 16));
-            const uint32_t l1 = pack_bf16x2(pw[2] - bf16_bits_to_f32(h1 & 0xFFFFu),
-                                            pw[3] - bf16_bits_to_f32(h1 >> 16));
+            if (tail) {
+                if (!live[ts][0]) pw[0] = pw[1] = 0.f;
+                if (!live[ts][1]) pw[2] = pw[3] = 0.f;
+            }
+            const uint32_t h0 = pack_f16x2(pw[0], pw[1]), h1 = pack_f16x2(pw[2], pw[3]);
             const uint32_t bh0 = movmatrix_trans(h0), bh1 = movmatrix_trans(h1);
-            const uint32_t bl0 = movmatrix_trans(l0), bl1 = movmatrix_trans(l1);
-            const uint8_t* vrow = st + (kTileStrips + ts) * L::kStripBytes + (2 * r) * 8;
+            uint32_t bl0 = 0, bl1 = 0;
+            if constexpr (PRECISE) {
+                const float2 f0 = unpack_f16x2(h0), f1 = unpack_f16x2(h1);
+                bl0 = movmatrix_trans(pack_f16x2(pw[0] - f0.x, pw[1] - f0.y));
+                bl1 = movmatrix_trans(pack_f16x2(pw[2] - f1.x, pw[3] - f1.y));
+            }
+            const uint8_t* vrow = ss + L::kKeyBytes + (2 * r) * 8;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 const uint4 v = *reinterpret_cast<const uint4*>(vrow + mt * 128);
-                const uint32_t a0 = dq2(v.x >> (4 * qd)), a2 = dq2(v.y >> (4 * qd));
-                const uint32_t a1 = dq2(v.z >> (4 * qd)), a3 = dq2(v.w >> (4 * qd));
-                mma_bf16_16816(acc[mt], a0, a1, a2, a3, bh0, bh1);
-                mma_bf16_16816(acc[mt], a0, a1, a2, a3, bl0, bl1);
+                const uint32_t ya = __byte_perm(v.x, v.y, vsel), yb = __byte_perm(v.z, v.w, vsel);
+                const uint32_t a0 = dq_lo(ya), a2 = dq_hi(ya), a1 = dq_lo(yb), a3 = dq_hi(yb);
+                mma_f16_16816(acc[mt], a0, a1, a2, a3, bh0, bh1);
+                if constexpr (PRECISE) mma_f16_16816(acc[mt], a0, a1, a2, a3, bl0, bl1);
             }
         }
         __syncwarp();
     }
-    cp_async_wait<0>();
+    if (broken) {
+        // give copies still in flight a bounded chance to land before the CTA retires
+        for (int s = 0; s < kStages; ++s) mbar_try_wait(my_bar + 8 * s, 0);
+    }
 
-    // ---- warp-level l, then merge the four warps through shared memory.
+    // ---- warp-level l, value normaliser out of acc, merge the warps through shared memory.
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
         l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 4);
@@ -420,12 +574,13 @@ tq_decode_partial_kernel(const DecodeParams p)
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
         const int ch = mt * 16 + 2 * r;
-        merge[(qd * 2 + 0) * (D + 2) + 2 + ch] = acc[mt][0];
-        merge[(qd * 2 + 1) * (D + 2) + 2 + ch] = acc[mt][1];
-        merge[(qd * 2 + 0) * (D + 2) + 2 + ch + 1] = acc[mt][2];
-        merge[(qd * 2 + 1) * (D + 2) + 2 + ch + 1] = acc[mt][3];
+        merge[(qd * 2 + 0) * (D + 2) + 2 + ch] = acc[mt][0] * vnorm;
+        merge[(qd * 2 + 1) * (D + 2) + 2 + ch] = acc[mt][1] * vnorm;
+        merge[(qd * 2 + 0) * (D + 2) + 2 + ch + 1] = acc[mt][2] * vnorm;
+        merge[(qd * 2 + 1) * (D + 2) + 2 + ch + 1] = acc[mt][3] * vnorm;
     }
     __syncthreads();
+    // m is kept in log2 units inside the kernel; records carry natural units.
     const float* mg = reinterpret_cast<const float*>(ring);
     for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
         const int q = i / kRecord, c = i % kRecord;
@@ -434,14 +589,14 @@ tq_decode_partial_kernel(const DecodeParams p)
         for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, mg[(w * 8 + q) * (D + 2)]);
         float out;
         if (c < 8) {
-            out = mm;
+            out = mm > -1.0e37f ? mm * kLn2 : kMaskedScore;
         } else {
             const int src = c < 16 ? 1 : 2 + (c - 16);
             out = 0.f;
 #pragma unroll
             for (int w = 0; w < kDecWarps; ++w) {
                 const float* rw = mg + (w * 8 + q) * (D + 2);
-                out += rw[src] * ex2f((rw[0] - mm) * kLog2e);
+                out += rw[src] * ex2f(rw[0] - mm);
             }
         }
         rec_base[i] = out;
@@ -505,7 +660,7 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
     else static_cast<uint16_t*>(p.output)[at] = f32_to_bf16_bits(v);
 }
 
-template <int D>
+template <int D, bool PRECISE>
 static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
 {
     // Opt in to the large dynamic shared-memory carve-out once per device. The
@@ -514,7 +669,7 @@ static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorNoDevice;
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(tq_decode_partial_kernel<D>,
+        cudaError_t e = cudaFuncSetAttribute(tq_decode_partial_kernel<D, PRECISE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              DecodeSmem<D>::kTotal);
         if (e != cudaSuccess) return e;
@@ -523,7 +678,7 @@ static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
     const uint64_t grid = static_cast<uint64_t>(p.items) * ((p.rows + 7u) / 8u) * p.splits;
     if (grid == 0) return cudaSuccess;
     if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
-    tq_decode_partial_kernel<D><<<static_cast<unsigned>(grid), kDecWarps * 32,
+    tq_decode_partial_kernel<D, PRECISE><<<static_cast<unsigned>(grid), kDecWarps * 32,
                                   DecodeSmem<D>::kTotal, stream>>>(p);
     return cudaGetLastError();
 }
@@ -615,7 +770,7 @@ extern "C" int tq_decode_splitk_partials(void* stream, const uint16_t* q, const 
     p.softmax_scale = softmax_scale;
     p.status = status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const cudaError_t e = head_size == 128 ? launch_partial<128>(s, p) : launch_partial<256>(s, p);
+    const cudaError_t e = head_size == 128 ? launch_partial<128, true>(s, p) : launch_partial<256, true>(s, p);
     return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 
@@ -704,7 +859,7 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
     p.softmax_scale = softmax_scale;
     p.status = status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const cudaError_t e = head_size == 128 ? launch_partial<128>(s, p) : launch_partial<256>(s, p);
+    const cudaError_t e = head_size == 128 ? launch_partial<128, true>(s, p) : launch_partial<256, true>(s, p);
     return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 

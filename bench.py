@@ -343,7 +343,8 @@ def run_profile_case(args):
     """A small case of one kernel for an ncu capture: inputs larger than L2 but well under
     a GB on the device, two warm-up launches and three captured ones.
       decode  : 64 sequences x 2048..4096 tokens (about 0.2 GB of cache)
-      reshape : bf16 prefill of 65536 tokens x 8 KV heads x 128 (0.27 GB)"""
+      reshape : bf16 prefill of 65536 tokens x 8 KV heads x 128 (0.27 GB)
+      reshape_a8 : the same prefill with int8 activations (0.13 GB)"""
     import torch
     import ascend_micro_harness_b200 as tq
     dev = torch.device("cuda", 0)
@@ -369,8 +370,12 @@ def run_profile_case(args):
         T, H = 65536, 8
         g = torch.Generator(device=dev)
         g.manual_seed(2)
-        k = torch.randn((T, H * D), device=dev, generator=g).bfloat16()
-        v = torch.randn((T, H * D), device=dev, generator=g).bfloat16()
+        if args.profile == "reshape_a8":
+            k = torch.randint(-127, 128, (T, H * D), device=dev, generator=g, dtype=torch.int8)
+            v = torch.randint(-127, 128, (T, H * D), device=dev, generator=g, dtype=torch.int8)
+        else:
+            k = torch.randn((T, H * D), device=dev, generator=g).bfloat16()
+            v = torch.randn((T, H * D), device=dev, generator=g).bfloat16()
         P = T // S
         kc = torch.empty(P * H * S * D // 2, dtype=torch.uint8, device=dev)
         vc = torch.empty_like(kc)
@@ -382,7 +387,8 @@ def run_profile_case(args):
             tq.reshape_and_cache(k, v, kc, vc, sc, slots, signs, num_kv_heads=H, head_size=D,
                                  block_size=S, num_blocks=P, inv_sqrt_len=0.0883883)
         torch.cuda.synchronize()
-        print(json.dumps({"profile": "reshape", "bytes": 2 * T * H * D * 2 + T * H * D + 2 * T * H * 4}))
+        print(json.dumps({"profile": args.profile,
+                          "bytes": 2 * T * H * D * k.element_size() + T * H * D + 2 * T * H * 4}))
 
 
 def cpu_baseline_decode(w, args, sample=BATCH):
@@ -464,7 +470,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile", default=None, choices=["decode", "reshape"],
+    ap.add_argument("--profile", default=None, choices=["decode", "reshape", "reshape_a8"],
                     help="run a small case of one kernel (for ncu), print no bench line")
     args = ap.parse_args()
     if args.profile:
