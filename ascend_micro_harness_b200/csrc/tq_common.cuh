@@ -61,6 +61,42 @@ __device__ __forceinline__ void fwht_inplace(T (&x)[N])
             }
 }
 
+// y = Pi x * sqrt(d) for one row spread over a warp: lane l holds the K = d/32
+// consecutive channels l*K .. l*K+K-1. FP32 radix-2 cascade in the stage order of the
+// reference's host model (tests/common/rotate_butterfly_oracle.hpp:44-48,:130-142):
+// strides 1..16, the sign diagonal, strides 32..d/2, each stage
+// out[i] = in[i ^ s] + ((i & s) ? -in[i] : in[i]) -- so the result is reproducible
+// bit for bit, integer-valued rows or not.
+template <int K>
+__device__ __forceinline__ void cascade_ingress(float (&v)[K], const float (&sgn)[K], int lane)
+{
+    auto stage = [&](int s) {
+        if (s < K) {
+#pragma unroll
+            for (int i = 0; i < K; ++i)
+                if ((i & s) == 0) {
+                    const float a = v[i], b = v[i + s];
+                    v[i] = b + a;
+                    v[i + s] = a - b;
+                }
+        } else {
+            const int lm = s / K;
+            const bool upper = (lane & lm) != 0;
+#pragma unroll
+            for (int i = 0; i < K; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[i], lm);
+                v[i] = other + (upper ? -v[i] : v[i]);
+            }
+        }
+    };
+#pragma unroll
+    for (int s = 1; s < kGroup; s <<= 1) stage(s);
+#pragma unroll
+    for (int i = 0; i < K; ++i) v[i] *= sgn[i];
+#pragma unroll
+    for (int s = kGroup; s < 32 * K; s <<= 1) stage(s);
+}
+
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t raw)
 {
     return __uint_as_float(static_cast<uint32_t>(raw) << 16);

@@ -31,6 +31,7 @@
 //     weights; P^T reaches its B-fragment layout with movmatrix.
 #include <cuda_fp16.h>
 #include <stdexcept>
+#include <type_traits>
 
 #include "tq_common.cuh"
 
@@ -42,7 +43,6 @@ constexpr int kTileStrips = 2;   // strips per pipeline stage of one warp
 constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr uint32_t kWaitLimit = 1u << 17;  // bounded mbarrier wait, about 0.1 s
 
 struct DecodeParams {
     const uint16_t* q;        // [items*rows][D] bf16
@@ -57,73 +57,51 @@ struct DecodeParams {
     float* workspace;
     uint32_t items, H, rows, rows_stride, S, P;
     uint32_t table_stride, splits, page_begin, page_count, fixed_ctx;
+    uint32_t sp_shift;        // log2(strips per page); pages hold 16 * 2^k tokens
     float inv_sqrt_len, softmax_scale;
     uint32_t* status;
 };
 
-// Shared-memory plan of one CTA. A key strip is stored as four 4-token row groups;
-// odd groups are shifted by kKeyPad bytes so that the two token rows one quarter-warp
-// reads (tokens t and t+4) fall into different banks.
+// Shared-memory plan of one CTA. A key strip is stored in 16-byte chunks whose
+// position is swizzled by one bit of the token row, so that the two token rows one
+// quarter-warp reads (tokens t and t+4) fall into different banks.
 template <int D>
 struct DecodeSmem {
     static constexpr int kRowBytes = D / 2;
     static constexpr int kStripBytes = kStrip * D / 2;
-    static constexpr int kKeyPad = D == 128 ? 64 : 16;
-    static constexpr int kKeyGroup = 4 * kRowBytes;                 // 4 token rows
-    static constexpr int kKeyStride = 2 * kKeyGroup + kKeyPad;      // two groups + pad
-    static constexpr int kKeyBytes = 2 * kKeyStride;                // one padded key strip
-    static constexpr int kStripStage = kKeyBytes + kStripBytes + 2 * kStrip * 4;
+    static constexpr int kStripStage = 2 * kStripBytes + 2 * kStrip * 4;   // K, V, both scale runs
     static constexpr int kStageBytes = kTileStrips * kStripStage;
     static constexpr int kRingBytes = kDecWarps * kStages * kStageBytes;
     static constexpr int kQBytes = 2 * 8 * D * 4;
     static constexpr int kMergeBytes = kDecWarps * 8 * (D + 2) * 4;
     static constexpr int kBody = kRingBytes > kQBytes ? (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes)
                                                       : (kQBytes > kMergeBytes ? kQBytes : kMergeBytes);
-    static constexpr int kBarOffset = kBody;                        // kDecWarps*kStages mbarriers
-    static constexpr int kTotal = kBody + kDecWarps * kStages * 8 + 64;
-    static constexpr uint32_t kStripTx = 2 * kStripBytes + 2 * kStrip * 4;  // bytes one strip brings
+    static constexpr int kTotal = kBody;
+    // 16-byte chunk `c` of token row `row` lands at this chunk index of the strip.
+    __host__ __device__ static constexpr int key_chunk(int row, int c)
+    {
+        return D == 128 ? ((row * 4 + c) ^ (((row >> 2) & 1) << 2)) : ((row * 8 + c) ^ ((row >> 2) & 1));
+    }
 };
 
-// ---- mbarrier / bulk-copy primitives (all waits bounded)
+// ---- per-thread asynchronous copies. A bulk (TMA) copy per strip was measured
+// here first: with the 1 KiB scattered strips of a 16-token page it costs more issue
+// slots than it saves, because a copy whose operands differ per lane is serialised
+// lane by lane (about 14 instructions per copy); 16-byte cp.async with per-lane
+// precomputed offsets is 5 instructions per strip.
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
 {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gmem_src)
 {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_dst), "l"(gmem_src));
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
 {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\n"
-        "selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
-{
-    for (uint32_t i = 0; i < kWaitLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-// 1-D bulk copy global -> shared, completion counted in bytes on `bar`. Both
-// addresses 16-byte aligned, size a multiple of 16.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
-{
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
-        "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
 // Two packed INT4 codes -> two exact f16 integers. The low variant takes the codes
@@ -198,7 +176,6 @@ tq_decode_partial_kernel(const DecodeParams p)
     extern __shared__ __align__(128) uint8_t smem[];
     float* qbuf = reinterpret_cast<float*>(smem);            // [2][8][D], prologue only
     uint8_t* ring = smem;                                    // aliases qbuf after the prologue
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
     __shared__ float row_unscale[8];                         // per query row: 2^-k * softmax_scale * log2e
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -256,60 +233,50 @@ tq_decode_partial_kernel(const DecodeParams p)
         if (no_pages || p.q_rot == nullptr) return;
     }
 
-    // ---- rotate the query rows once: FP32 ingress cascade, scale, round to bf16
-    // (stage order of tests/common/rotate_butterfly_oracle.hpp:44-48).
+    // ---- rotate the query rows once: each warp takes two rows through the FP32
+    // ingress cascade, scales, rounds to bf16 (the pinned operand) and publishes it.
+    // The MMAs run in f16, so every row is then scaled by a power of two that puts its
+    // largest entry at 2^14 (exact for all entries within 2^-28 of the largest); the
+    // inverse goes into the per-row score factor together with softmax_scale * log2(e).
     {
-        const uint16_t* qsrc = p.q + (static_cast<size_t>(item) * p.rows + row_tile * 8u) * D;
-        for (int i = tid; i < 8 * D; i += blockDim.x) {
-            const int row = i / D;
-            qbuf[i] = row < rows_here ? bf16_bits_to_f32(qsrc[i]) : 0.0f;
-        }
-        __syncthreads();
-        int cur = 0;
-        for (int s = 1; s < D; s <<= 1) {
-            const float* in = qbuf + cur * 8 * D;
-            float* out = qbuf + (cur ^ 1) * 8 * D;
-            for (int i = tid; i < 8 * D; i += blockDim.x) {
-                const int c = i % D, row = i / D;
-                float mine = in[i], other = in[row * D + (c ^ s)];
-                if (s == kGroup) {  // the sign diagonal sits before the first outer stage
-                    mine *= sign_is_negative(p.signs, p.sign_source, c) ? -1.0f : 1.0f;
-                    other *= sign_is_negative(p.signs, p.sign_source, c ^ s) ? -1.0f : 1.0f;
-                }
-                out[i] = other + ((c & s) ? -mine : mine);
+        constexpr int K = D / 32;
+        float sgn[K];
+#pragma unroll
+        for (int i = 0; i < K; ++i)
+            sgn[i] = sign_is_negative(p.signs, p.sign_source, lane * K + i) ? -1.0f : 1.0f;
+        for (int row = warp * 2; row < warp * 2 + 2; ++row) {
+            float v[K];
+#pragma unroll
+            for (int i = 0; i < K; ++i) v[i] = 0.f;
+            if (row < rows_here) {
+                const uint16_t* qsrc =
+                    p.q + (static_cast<size_t>(item) * p.rows + row_tile * 8u + row) * D + lane * K;
+#pragma unroll
+                for (int i = 0; i < K; ++i) v[i] = bf16_bits_to_f32(qsrc[i]);
             }
-            __syncthreads();
-            cur ^= 1;
+            cascade_ingress<K>(v, sgn, lane);
+            float am = 0.f;
+#pragma unroll
+            for (int i = 0; i < K; ++i) {
+                const uint16_t bits = f32_to_bf16_bits(v[i] * p.inv_sqrt_len);
+                v[i] = bf16_bits_to_f32(bits);
+                am = fmaxf(am, fabsf(v[i]));
+                if (p.q_rot != nullptr && row < rows_here)
+                    p.q_rot[((static_cast<size_t>(item) * p.splits + split) * p.rows_stride +
+                             row_tile * 8u + row) * D + lane * K + i] = bits;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            // 2^(14 - e) and 2^(e - 14) from the exponent field; a zero row keeps 1
+            const int e_bits = __float_as_int(am) & 0x7F800000;
+            const float up = am > 0.f ? __int_as_float((268 << 23) - e_bits) : 1.0f;
+            const float down = am > 0.f ? __int_as_float(e_bits - (14 << 23)) : 1.0f;
+#pragma unroll
+            for (int i = 0; i < K; ++i) qbuf[row * D + lane * K + i] = v[i] * up;
+            if (lane == 0) row_unscale[row] = down * p.softmax_scale * kLog2e;
         }
-        // qbuf[cur] holds Pi*sqrt(d) q; narrow to bf16 (the pinned operand), publish it.
-        float* fin = qbuf + cur * 8 * D;
-        for (int i = tid; i < 8 * D; i += blockDim.x) {
-            const uint16_t b = f32_to_bf16_bits(fin[i] * p.inv_sqrt_len);
-            fin[i] = bf16_bits_to_f32(b);
-            if (p.q_rot != nullptr && i / D < rows_here)
-                p.q_rot[((static_cast<size_t>(item) * p.splits + split) * p.rows_stride +
-                         row_tile * 8u) * D + i] = b;
-        }
-        __syncthreads();
-        qbuf = fin;
     }
     if (empty) return;
-
-    // ---- the MMAs run in f16: scale every query row by a power of two so its largest
-    // entry sits at 2^14 (exact for all but entries 2^28 below the largest), and undo
-    // it in the score scale. Two rows per warp.
-    for (int row = warp * 2; row < warp * 2 + 2; ++row) {
-        float am = 0.f;
-        for (int c = lane; c < D; c += 32) am = fmaxf(am, fabsf(qbuf[row * D + c]));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-        // 2^(14 - e) and its inverse from the exponent field; a zero row keeps scale 1
-        const int e_bits = __float_as_int(am) & 0x7F800000;
-        const float up = am > 0.f ? __int_as_float((141 << 23) - e_bits + (127 << 23)) : 1.0f;
-        const float down = am > 0.f ? __int_as_float(e_bits - (14 << 23)) : 1.0f;
-        for (int c = lane; c < D; c += 32) qbuf[row * D + c] *= up;
-        if (lane == 0) row_unscale[row] = down * p.softmax_scale * kLog2e;
-    }
     __syncthreads();
 
     // ---- q_rot^T as f16 B fragments, in the contraction order the key words deliver.
@@ -322,7 +289,8 @@ tq_decode_partial_kernel(const DecodeParams p)
             bq[wi * 2 + kh][0] = pack_f16x2(qr[0], qr[4]);
             bq[wi * 2 + kh][1] = pack_f16x2(qr[1], qr[5]);
         }
-    const float unscale0 = row_unscale[qd * 2], unscale1 = row_unscale[qd * 2 + 1];
+    // scores are kept as raw * key_scale; the per-row factor enters inside the exponent
+    const float rfac[2] = {row_unscale[qd * 2], row_unscale[qd * 2 + 1]};
     __syncthreads();  // everyone is done with qbuf: the ring may overwrite it
 
     // ---- per-warp pipeline over tiles warp, warp+4, ...
@@ -332,67 +300,59 @@ tq_decode_partial_kernel(const DecodeParams p)
     const int32_t* table_row = p.table + static_cast<size_t>(seq) * p.table_stride;
     uint8_t* my_ring = ring + warp * kStages * L::kStageBytes;
     const uint32_t my_ring_s = smem_u32(my_ring);
-    const uint32_t my_bar = smem_u32(bars + warp * kStages);
     const size_t head_block = static_cast<size_t>(p.S) * D / 2;  // bytes of one (page, head)
     const size_t scale_plane = static_cast<size_t>(p.P) * p.H * p.S;
+    const uint32_t sp_shift = p.sp_shift;                        // strips per page = 1 << sp_shift
+    constexpr uint32_t kTileStep = kDecWarps * kTileStrips;      // strips between a warp's tiles
 
-    if (lane == 0) {
+    // Block-table entries of the tile whose first strip is `strip` (-1 past the range).
+    auto load_pages = [&](uint32_t strip, int32_t (&pg)[kTileStrips]) {
 #pragma unroll
-        for (int s = 0; s < kStages; ++s) mbar_init(my_bar + 8 * s, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        for (int ts = 0; ts < kTileStrips; ++ts)
+            pg[ts] = strip + ts < s1 ? __ldg(table_row + ((strip + ts) >> sp_shift)) : -1;
+    };
+    // Per-lane copy plan, fixed for the whole kernel: lane l moves 16-byte chunks
+    // l, l+32, ... of the key strip (to their swizzled places) and of the value strip,
+    // lanes 0..7 the two 64-byte scale runs.
+    constexpr int kChunksPerLane = L::kStripBytes / 16 / 32;     // 2 (d=128) or 4 (d=256)
+    constexpr int kChunksPerRow = L::kRowBytes / 16;
+    uint32_t kdst[kChunksPerLane];
+#pragma unroll
+    for (int i = 0; i < kChunksPerLane; ++i) {
+        const int c = i * 32 + lane;
+        kdst[i] = L::key_chunk(c / kChunksPerRow, c % kChunksPerRow) * 16;
     }
-    // generic-proxy writes of the prologue are ordered before the async-proxy writes
-    // of the bulk copies that reuse the same shared memory
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    __syncwarp();
-
-    auto strip_of = [&](uint32_t j, int ts) { return s0 + (warp + j * kDecWarps) * kTileStrips + ts; };
-    auto load_pages = [&](uint32_t j, int32_t (&pg)[kTileStrips]) {
+    const uint8_t* ksrc0 = p.key_cache + head * head_block + lane * 16;
+    const uint8_t* vsrc0 = p.value_cache + head * head_block + lane * 16;
+    const float* ssrc0 = p.scale_cache + (lane >> 2) * scale_plane + static_cast<size_t>(head) * p.S + (lane & 3) * 4;
+    const size_t page_stride = static_cast<size_t>(p.H) * head_block;
+    const size_t page_stride_scale = static_cast<size_t>(p.H) * p.S;
+    auto issue = [&](uint32_t strip, uint32_t stage, const int32_t (&pg)[kTileStrips]) {
 #pragma unroll
         for (int ts = 0; ts < kTileStrips; ++ts) {
-            const uint32_t s = strip_of(j, ts);
-            pg[ts] = (j < my_tiles && s < s1) ? __ldg(table_row + s / SP) : -1;
-        }
-    };
-    // One warp instruction issues every copy of the tile: lane = ts*8 + piece, pieces
-    // 0..3 the four key row groups, 4 the value strip, 5 / 6 the key / value scales.
-    auto issue = [&](uint32_t j, const int32_t (&pg)[kTileStrips]) {
-        const uint32_t stage = j % kStages;
-        const uint32_t bar = my_bar + 8 * stage;
-        uint32_t nstrips = 0;
-#pragma unroll
-        for (int ts = 0; ts < kTileStrips; ++ts) nstrips += pg[ts] >= 0;
-        if (lane == 0) mbar_expect_tx(bar, nstrips * L::kStripTx);
-        __syncwarp();
-        const int ts = lane >> 3, piece = lane & 7;
-        if (ts < kTileStrips && piece < 7) {
-            const int32_t pgv = ts == 0 ? pg[0] : pg[kTileStrips - 1];
-            if (pgv >= 0) {
-                uint32_t page = static_cast<uint32_t>(pgv);
-                if (page >= p.P) {
-                    report(p.status, TQ_STATUS_BAD_PAGE);
-                    page = 0;
-                }
-                const uint32_t sip = strip_of(j, ts) % SP;
-                const size_t off = (static_cast<size_t>(page) * p.H + head) * head_block +
-                                   static_cast<size_t>(sip) * L::kStripBytes;
-                const uint32_t st = my_ring_s + stage * L::kStageBytes + ts * L::kStripStage;
-                if (piece < 4) {
-                    bulk_g2s(st + (piece >> 1) * L::kKeyStride + (piece & 1) * (L::kKeyGroup + L::kKeyPad),
-                             p.key_cache + off + piece * L::kKeyGroup, L::kKeyGroup, bar);
-                } else if (piece == 4) {
-                    bulk_g2s(st + L::kKeyBytes, p.value_cache + off, L::kStripBytes, bar);
-                } else {
-                    const int plane = piece - 5;
-                    const float* src = p.scale_cache + plane * scale_plane +
-                                       (static_cast<size_t>(page) * p.H + head) * p.S + sip * kStrip;
-                    bulk_g2s(st + L::kKeyBytes + L::kStripBytes + plane * kStrip * 4, src, kStrip * 4, bar);
-                }
+            if (pg[ts] < 0) continue;   // warp-uniform
+            uint32_t page = static_cast<uint32_t>(pg[ts]);
+            if (page >= p.P) {
+                if (lane == 0) report(p.status, TQ_STATUS_BAD_PAGE);
+                page = 0;
             }
+            const uint32_t sip = (strip + ts) & ((1u << sp_shift) - 1u);
+            const size_t off = page * page_stride + static_cast<size_t>(sip) * L::kStripBytes;
+            const uint32_t dst = my_ring_s + stage * L::kStageBytes + ts * L::kStripStage;
+#pragma unroll
+            for (int i = 0; i < kChunksPerLane; ++i) {
+                cp_async16(dst + kdst[i], ksrc0 + off + i * 512);
+                cp_async16(dst + L::kStripBytes + i * 512 + lane * 16, vsrc0 + off + i * 512);
+            }
+            if (lane < 8)
+                cp_async16(dst + 2 * L::kStripBytes + lane * 16,
+                           ssrc0 + page * page_stride_scale + sip * kStrip);
         }
     };
 
+    // Online-softmax state for query rows qd*2 and qd*2+1, in units of raw * key_scale.
     float m_run[2] = {kMaskedScore, kMaskedScore}, l_run[2] = {0.f, 0.f};
+    float m_fac[2] = {0.f, 0.f};   // m_run * rfac, the exponent offset (0 while m_run is the sentinel)
     float acc[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -402,49 +362,44 @@ tq_decode_partial_kernel(const DecodeParams p)
     // it is kept in [0, 1] by dividing the value scale by the largest seen so far.
     float vnorm = 0.f, inv_vnorm = 0.f;
 
+    const uint32_t strip_first = s0 + warp * kTileStrips;   // first strip of this warp's tile 0
     int32_t pg_next[kTileStrips];
     for (uint32_t j = 0; j < kStages - 1; ++j) {
-        load_pages(j, pg_next);
-        if (j < my_tiles) issue(j, pg_next);
+        load_pages(strip_first + j * kTileStep, pg_next);
+        issue(strip_first + j * kTileStep, j, pg_next);
+        cp_async_commit();
     }
-    load_pages(kStages - 1, pg_next);
+    load_pages(strip_first + (kStages - 1) * kTileStep, pg_next);
 
     const int tok_lo = token_row_lo(r), tok_hi = token_row_hi(r);
-    const int koff_lo = (tok_lo >> 3) * L::kKeyStride + ((tok_lo >> 2) & 1) * (L::kKeyGroup + L::kKeyPad) +
-                        (tok_lo & 3) * L::kRowBytes + qd * (D / 8);
-    const int koff_hi = koff_lo + L::kRowBytes;   // tok_hi = tok_lo + 1, same row group
+    // this thread's chunks of its two key rows (d=128: one chunk each; d=256: two)
+    int koff_lo[WPT / 4], koff_hi[WPT / 4];
+#pragma unroll
+    for (int w4 = 0; w4 < WPT / 4; ++w4) {
+        koff_lo[w4] = L::key_chunk(tok_lo, qd * (WPT / 4) + w4) * 16;
+        koff_hi[w4] = L::key_chunk(tok_hi, qd * (WPT / 4) + w4) * 16;
+    }
     // byte-permute selector that brings this thread's value-token pairs to bits 0-7 / 16-23
     const uint32_t vsel = qd == 0 ? 0x3210u : qd == 1 ? 0x4321u : qd == 2 ? 0x7654u : 0x0765u;
-    bool broken = false;
 
-    for (uint32_t j = 0; j < my_tiles && !broken; ++j) {
-        if (j + kStages - 1 < my_tiles) issue(j + kStages - 1, pg_next);
-        load_pages(j + kStages, pg_next);
-        if (!mbar_wait_bounded(my_bar + 8 * (j % kStages), (j / kStages) & 1u)) {
-            if (lane == 0) report(p.status, TQ_STATUS_WAIT_EXPIRED);
-            broken = true;
-            break;
-        }
-
-        const uint8_t* st = my_ring + (j % kStages) * L::kStageBytes;
-        // warp-uniform: the tile reaches past this split's strips or past the live tokens
-        const bool tail = strip_of(j, kTileStrips - 1) >= s1 ||
-                          (strip_of(j, kTileStrips - 1) + 1u) * kStrip > ctx;
-
-        // -- scores^T for the tile's strips, in log2 units
-        float sc[kTileStrips][4];
+    // One tile: scores^T for its strips, the online-softmax update, then acc^T += V^T P^T.
+    // TAIL tiles reach past the split's strips or past the live tokens and mask by
+    // overwriting (a dead slot's scale may be a NaN); full tiles carry no masking code.
+    auto compute_tile = [&](const uint8_t* st, uint32_t strip_t, auto tail_tag) {
+        constexpr bool TAIL = decltype(tail_tag)::value;
+        float sc[kTileStrips][4], vs[kTileStrips][2];
         bool live[kTileStrips][2];
         float mx[2] = {kMaskedScore, kMaskedScore};
         float vmax = 0.f;
 #pragma unroll
         for (int ts = 0; ts < kTileStrips; ++ts) {
             const uint8_t* ss = st + ts * L::kStripStage;
-            const float* scales = reinterpret_cast<const float*>(ss + L::kKeyBytes + L::kStripBytes);
+            const float* scales = reinterpret_cast<const float*>(ss + 2 * L::kStripBytes);
             float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int w4 = 0; w4 < WPT / 4; ++w4) {
-                const uint4 lo = *reinterpret_cast<const uint4*>(ss + koff_lo + w4 * 16);
-                const uint4 hi = *reinterpret_cast<const uint4*>(ss + koff_hi + w4 * 16);
+                const uint4 lo = *reinterpret_cast<const uint4*>(ss + koff_lo[w4]);
+                const uint4 hi = *reinterpret_cast<const uint4*>(ss + koff_hi[w4]);
                 const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -457,23 +412,22 @@ tq_decode_partial_kernel(const DecodeParams p)
                 }
             }
             const float ks_lo = scales[tok_lo], ks_hi = scales[tok_hi];
-            sc[ts][0] = c[0] * (ks_lo * unscale0);
-            sc[ts][1] = c[1] * (ks_lo * unscale1);
-            sc[ts][2] = c[2] * (ks_hi * unscale0);
-            sc[ts][3] = c[3] * (ks_hi * unscale1);
-            live[ts][0] = live[ts][1] = true;
-            if (tail) {
-                // Dead lanes are overwritten, never multiplied: their scale may be a NaN.
-                const uint32_t strip = strip_of(j, ts);
+            vs[ts][0] = scales[kStrip + tok_lo];
+            vs[ts][1] = scales[kStrip + tok_hi];
+            sc[ts][0] = c[0] * ks_lo;
+            sc[ts][1] = c[1] * ks_lo;
+            sc[ts][2] = c[2] * ks_hi;
+            sc[ts][3] = c[3] * ks_hi;
+            if constexpr (TAIL) {
+                const uint32_t strip = strip_t + ts;
                 live[ts][0] = strip < s1 && strip * kStrip + tok_lo < ctx;
                 live[ts][1] = strip < s1 && strip * kStrip + tok_hi < ctx;
-                if (!live[ts][0]) sc[ts][0] = sc[ts][1] = kMaskedScore;
-                if (!live[ts][1]) sc[ts][2] = sc[ts][3] = kMaskedScore;
+                if (!live[ts][0]) { sc[ts][0] = sc[ts][1] = kMaskedScore; vs[ts][0] = 0.f; }
+                if (!live[ts][1]) { sc[ts][2] = sc[ts][3] = kMaskedScore; vs[ts][1] = 0.f; }
             }
             mx[0] = fmaxf(mx[0], fmaxf(sc[ts][0], sc[ts][2]));
             mx[1] = fmaxf(mx[1], fmaxf(sc[ts][1], sc[ts][3]));
-            const float vs_lo = scales[kStrip + tok_lo], vs_hi = scales[kStrip + tok_hi];
-            vmax = fmaxf(vmax, fmaxf(live[ts][0] ? fabsf(vs_lo) : 0.f, live[ts][1] ? fabsf(vs_hi) : 0.f));
+            vmax = fmaxf(vmax, fmaxf(fabsf(vs[ts][0]), fabsf(vs[ts][1])));
         }
 #pragma unroll
         for (int o = 4; o <= 16; o <<= 1) {
@@ -481,65 +435,59 @@ tq_decode_partial_kernel(const DecodeParams p)
             mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
             vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
         }
-        // -- online softmax update; the accumulator is rescaled only when something moved
-        float alpha[2] = {1.f, 1.f};
-        bool moved = false;
+        // -- online softmax update; the accumulator is rescaled only when something moved.
+        // rfac > 0, so the maximum can be taken before the per-row factor is applied.
+        const bool grow = mx[0] > m_run[0] || mx[1] > m_run[1] || vmax > vnorm;
+        if (__any_sync(0xffffffffu, grow)) {
+            float alpha[2];
 #pragma unroll
-        for (int q = 0; q < 2; ++q)
-            if (mx[q] > m_run[q]) {
-                alpha[q] = ex2f(m_run[q] - mx[q]);
-                m_run[q] = mx[q];
-                moved = true;
+            for (int q = 0; q < 2; ++q) {
+                const float m_new = fmaxf(m_run[q], mx[q]);
+                alpha[q] = ex2f((m_run[q] - m_new) * rfac[q]);
+                m_run[q] = m_new;
+                m_fac[q] = m_new * rfac[q];
+                l_run[q] *= alpha[q];
             }
-        float vratio = 1.f;
-        if (vmax > vnorm) {  // warp-uniform: value scales depend on the token only
-            // the power of two above vmax; the ratio old/new is exact
-            const float nv = __int_as_float((__float_as_int(vmax) & 0x7F800000) + (1 << 23));
-            inv_vnorm = __int_as_float((254 << 23) - __float_as_int(nv));
-            vratio = vnorm * inv_vnorm;
-            vnorm = nv;
-            moved = true;
-        }
-        if (__any_sync(0xffffffffu, moved)) {
-            l_run[0] *= alpha[0];
-            l_run[1] *= alpha[1];
-            const float a0 = alpha[0] * vratio, a1 = alpha[1] * vratio;
+            if (vmax > vnorm) {  // warp-uniform: value scales depend on the token only
+                // the power of two above vmax; the ratio old/new is exact
+                const float nv = __int_as_float((__float_as_int(vmax) & 0x7F800000) + (1 << 23));
+                inv_vnorm = __int_as_float((254 << 23) - __float_as_int(nv));
+                alpha[0] *= vnorm * inv_vnorm;
+                alpha[1] *= vnorm * inv_vnorm;
+                vnorm = nv;
+            }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                acc[mt][0] *= a0;
-                acc[mt][1] *= a1;
-                acc[mt][2] *= a0;
-                acc[mt][3] *= a1;
+                acc[mt][0] *= alpha[0];
+                acc[mt][1] *= alpha[1];
+                acc[mt][2] *= alpha[0];
+                acc[mt][3] *= alpha[1];
             }
         }
         // -- P, then acc^T += V^T P^T
 #pragma unroll
         for (int ts = 0; ts < kTileStrips; ++ts) {
-            if (tail && strip_of(j, ts) >= s1) continue;  // warp-uniform
+            if constexpr (TAIL) {
+                if (strip_t + ts >= s1) continue;  // warp-uniform
+            }
             const uint8_t* ss = st + ts * L::kStripStage;
-            const float* scales = reinterpret_cast<const float*>(ss + L::kKeyBytes + L::kStripBytes);
-            const float vs_lo = scales[kStrip + tok_lo] * inv_vnorm;
-            const float vs_hi = scales[kStrip + tok_hi] * inv_vnorm;
+            const float vs_lo = vs[ts][0] * inv_vnorm, vs_hi = vs[ts][1] * inv_vnorm;
             float pw[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const float pr = ex2f(sc[ts][i] - m_run[i & 1]);
+                const float pr = ex2f(fmaf(sc[ts][i], rfac[i & 1], -m_fac[i & 1]));
                 l_run[i & 1] += pr;
                 pw[i] = pr * (i < 2 ? vs_lo : vs_hi);
             }
-            if (tail) {
-                if (!live[ts][0]) pw[0] = pw[1] = 0.f;
-                if (!live[ts][1]) pw[2] = pw[3] = 0.f;
-            }
             const uint32_t h0 = pack_f16x2(pw[0], pw[1]), h1 = pack_f16x2(pw[2], pw[3]);
             const uint32_t bh0 = movmatrix_trans(h0), bh1 = movmatrix_trans(h1);
-            uint32_t bl0 = 0, bl1 = 0;
+            [[maybe_unused]] uint32_t bl0 = 0, bl1 = 0;
             if constexpr (PRECISE) {
                 const float2 f0 = unpack_f16x2(h0), f1 = unpack_f16x2(h1);
                 bl0 = movmatrix_trans(pack_f16x2(pw[0] - f0.x, pw[1] - f0.y));
                 bl1 = movmatrix_trans(pack_f16x2(pw[2] - f1.x, pw[3] - f1.y));
             }
-            const uint8_t* vrow = ss + L::kKeyBytes + (2 * r) * 8;
+            const uint8_t* vrow = ss + L::kStripBytes + (2 * r) * 8;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
                 const uint4 v = *reinterpret_cast<const uint4*>(vrow + mt * 128);
@@ -549,12 +497,29 @@ tq_decode_partial_kernel(const DecodeParams p)
                 if constexpr (PRECISE) mma_f16_16816(acc[mt], a0, a1, a2, a3, bl0, bl1);
             }
         }
+    };
+
+    uint32_t stage = 0;
+    uint32_t strip_t = strip_first;   // first strip of the tile being computed
+#pragma unroll 1
+    for (uint32_t j = 0; j < my_tiles; ++j, strip_t += kTileStep) {
+        {
+            const uint32_t ahead = strip_t + (kStages - 1) * kTileStep;
+            issue(ahead, stage == 0 ? kStages - 1 : stage - 1, pg_next);
+            cp_async_commit();
+            load_pages(ahead + kTileStep, pg_next);
+        }
+        cp_async_wait<kStages - 1>();
+        __syncwarp();
+        const uint8_t* st = my_ring + stage * L::kStageBytes;
+        if (++stage == kStages) stage = 0;
+        if (strip_t + kTileStrips > s1 || (strip_t + kTileStrips) * kStrip > ctx)
+            compute_tile(st, strip_t, std::true_type{});
+        else
+            compute_tile(st, strip_t, std::false_type{});
         __syncwarp();
     }
-    if (broken) {
-        // give copies still in flight a bounded chance to land before the CTA retires
-        for (int s = 0; s < kStages; ++s) mbar_try_wait(my_bar + 8 * s, 0);
-    }
+    cp_async_wait<0>();
 
     // ---- warp-level l, value normaliser out of acc, merge the warps through shared memory.
 #pragma unroll
@@ -580,23 +545,25 @@ tq_decode_partial_kernel(const DecodeParams p)
         merge[(qd * 2 + 1) * (D + 2) + 2 + ch + 1] = acc[mt][3] * vnorm;
     }
     __syncthreads();
-    // m is kept in log2 units inside the kernel; records carry natural units.
+    // Inside the kernel m is in units of raw * key_scale; row_unscale turns a difference
+    // of such maxima into log2 units, and times ln 2 into the natural units of a record.
     const float* mg = reinterpret_cast<const float*>(ring);
     for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
         const int q = i / kRecord, c = i % kRecord;
+        const float rf = row_unscale[q];
         float mm = kMaskedScore;
 #pragma unroll
         for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, mg[(w * 8 + q) * (D + 2)]);
         float out;
         if (c < 8) {
-            out = mm > -1.0e37f ? mm * kLn2 : kMaskedScore;
+            out = mm > -1.0e37f ? mm * rf * kLn2 : kMaskedScore;
         } else {
             const int src = c < 16 ? 1 : 2 + (c - 16);
             out = 0.f;
 #pragma unroll
             for (int w = 0; w < kDecWarps; ++w) {
                 const float* rw = mg + (w * 8 + q) * (D + 2);
-                out += rw[src] * ex2f(rw[0] - mm);
+                out += rw[src] * ex2f((rw[0] - mm) * rf);
             }
         }
         rec_base[i] = out;
@@ -659,6 +626,19 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
     else if (p.out_dtype == TQ_DTYPE_F16) static_cast<__half*>(p.output)[at] = __float2half_rn(v);
     else static_cast<uint16_t*>(p.output)[at] = f32_to_bf16_bits(v);
 }
+
+// Pages of 16, 32, 64 or 128 tokens: the strip walk uses shifts, not divides.
+static bool page_size_ok(uint32_t block_size, uint32_t* sp_shift)
+{
+    const uint32_t sp = block_size / kStrip;
+    if (block_size % kStrip != 0 || sp == 0 || (sp & (sp - 1u)) != 0u) return false;
+    uint32_t sh = 0;
+    while ((1u << sh) < sp) ++sh;
+    *sp_shift = sh;
+    return true;
+}
+
+static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0u; }
 
 template <int D, bool PRECISE>
 static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
@@ -744,7 +724,12 @@ extern "C" int tq_decode_splitk_partials(void* stream, const uint16_t* q, const 
     }
     if (!q || !signs || !key_cache || !value_cache || !scale_cache || !table || !workspace)
         return TQ_ERR_INVALID_ARGUMENT;
+    uint32_t sp_shift = 0;
+    if (!page_size_ok(block_size, &sp_shift) || !aligned16(key_cache) || !aligned16(value_cache) ||
+        !aligned16(scale_cache))
+        return TQ_ERR_INVALID_ARGUMENT;
     DecodeParams p{};
+    p.sp_shift = sp_shift;
     p.q = q;
     p.signs = signs;
     p.sign_source = sign_source;
@@ -833,7 +818,12 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
     if (!query || !key_cache || !value_cache || !scale_cache || !block_tables || !context_lens ||
         !pi_signs || !workspace)
         return TQ_ERR_INVALID_ARGUMENT;
+    uint32_t sp_shift = 0;
+    if (!page_size_ok(block_size, &sp_shift) || !aligned16(key_cache) || !aligned16(value_cache) ||
+        !aligned16(scale_cache))
+        return TQ_ERR_INVALID_ARGUMENT;
     DecodeParams p{};
+    p.sp_shift = sp_shift;
     p.q = query;
     p.signs = pi_signs;
     p.sign_source = TQ_SIGNS_F32;
@@ -859,7 +849,7 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
     p.softmax_scale = softmax_scale;
     p.status = status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const cudaError_t e = head_size == 128 ? launch_partial<128, true>(s, p) : launch_partial<256, true>(s, p);
+    const cudaError_t e = head_size == 128 ? launch_partial<128, false>(s, p) : launch_partial<256, false>(s, p);
     return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 

@@ -9,22 +9,25 @@
 //   key page token-major, value page channel-major inside the strip.
 //
 // How this kernel computes it:
-//   * the 16 x d panel is read straight into MMA A-fragments with 64/128-bit
-//     loads; the contraction index of the MMA is permuted so that each thread's
-//     contiguous bytes ARE its fragment -- no shared-memory staging on the way in;
+//   * persistent warps walk the panels; each thread copies exactly the bytes that
+//     are its MMA A-fragments into a private two-stage shared-memory ring with
+//     cp.async (the MMA's contraction order is permuted so a thread's contiguous
+//     8/16 bytes ARE its fragment), one panel ahead of the arithmetic, and reads them
+//     back itself -- no cross-thread synchronisation on the way in;
 //   * the inner factor I_G (x) H32 is the only dense contraction: per 32-channel
 //     group, 4 (int8, m16n8k32) or 8 (bf16, m16n8k16) warp MMAs against +-1
 //     operands generated from popcount parity. Products of +-1 with int8 / small
 //     bf16 integers accumulate exactly in INT32 / FP32;
 //   * the MMA's output columns are permuted so each thread ends up with 8
-//     consecutive channels of every group: the sign diagonal and the outer
-//     H_G factor are then register-local (a log2(G)-stage butterfly), and one
+//     consecutive channels of every group: the sign diagonal and the outer H_G
+//     factor are register-local butterflies on packed f32x2 operations, and one
 //     thread's 8 codes are one 32-bit word of the key page;
 //   * fragment rows r and r+8 carry tokens 2r and 2r+1, so one thread owns both
 //     nibbles of every value-page byte it produces;
-//   * the scale comes from the exponent field of absmax by integer arithmetic,
-//     no division enters; the page is staged in shared memory and leaves as
-//     128-bit stores of the whole contiguous (page, head) block.
+//   * the scale comes from the exponent field of absmax by integer arithmetic, the
+//     rounding is one fused multiply-add onto 1.5 * 2^23 (no float-to-int
+//     conversion), codes pack by integer multiply-add; the page is staged in shared
+//     memory and leaves as 128-bit stores of the whole contiguous (page, head) block.
 #include <type_traits>
 
 #include "tq_common.cuh"
@@ -41,63 +44,93 @@ struct IngestParams {
     const void* signs;
     uint32_t sign_source;
     uint32_t num_strips, H, S, P;
+    uint32_t chunks;                 // num_strips * 2 * H, below 2^31
+    uint32_t div_mul, div_shift;     // exact division by 2H: see fast_div
     float inv_sqrt_len;
     uint32_t* status;
 };
 
 constexpr int kIngestWarps = 4;
-constexpr int kIngestCtasPerSm = 3;
+constexpr int kIngestCtasPerSm = 4;
 
-template <int D, bool BF16>
-struct Panel {
-    static constexpr int G = D / kGroup;
-    using Vec = typename std::conditional<BF16, uint4, uint2>::type;
-    Vec lo[G], hi[G];   // token 2r and token 2r+1, 8 channels per group
-    int32_t slot;       // slot of token (lane & 15) of the strip
-};
-
-// Issue the loads of one (strip, plane, head) panel: straight into what will be
-// the MMA A-fragments.
-template <int D, bool BF16>
-__device__ __forceinline__ void load_panel(Panel<D, BF16>& f, const IngestParams& p, uint64_t chunk,
-                                           int lane)
+// n / d for any 32-bit n with the precomputed (mul, shift) of divisor d >= 2
+// (round-up method: mul = floor(2^32 (2^l - d) / d) + 1, l = ceil(log2 d)).
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shift)
 {
-    constexpr int G = D / kGroup;
-    using Vec = typename Panel<D, BF16>::Vec;
-    using Elem = typename std::conditional<BF16, uint16_t, int8_t>::type;
-    const int r = lane >> 2, qd = lane & 3;
-    const uint32_t head = static_cast<uint32_t>(chunk % p.H);
-    const uint32_t plane = static_cast<uint32_t>((chunk / p.H) & 1u);
-    const uint32_t strip = static_cast<uint32_t>(chunk / (2u * p.H));
-    const size_t row_pitch = static_cast<size_t>(p.H) * D;  // elements
-    const Elem* base = static_cast<const Elem*>(plane == 0 ? p.key : p.value) +
-                       (static_cast<size_t>(strip) * kStrip + 2 * r) * row_pitch +
-                       static_cast<size_t>(head) * D + qd * 8;
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-        f.lo[g] = __ldg(reinterpret_cast<const Vec*>(base + g * kGroup));
-        f.hi[g] = __ldg(reinterpret_cast<const Vec*>(base + row_pitch + g * kGroup));
-    }
-    f.slot = __ldg(p.slots + static_cast<size_t>(strip) * kStrip + (lane & 15));
+    const uint32_t t = __umulhi(mul, n);
+    return (t + ((n - t) >> 1)) >> shift;
 }
 
-// Rotate, quantise, pack and store one panel.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_8(uint32_t dst, const void* src)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst), "l"(src));
+}
+
+struct PanelId {
+    uint32_t strip, plane, head;
+};
+__device__ __forceinline__ PanelId panel_of(const IngestParams& p, uint32_t chunk)
+{
+    PanelId id;
+    id.strip = fast_div(chunk, p.div_mul, p.div_shift);
+    const uint32_t rem = chunk - id.strip * 2u * p.H;
+    id.plane = rem >= p.H ? 1u : 0u;
+    id.head = rem - id.plane * p.H;
+    return id;
+}
+
+// Queue the copies of one panel: per 32-channel group the 8 channels of token 2r and
+// of token 2r+1 that this thread will feed to the MMA. Returns the slot of token
+// (lane & 15) of the strip, fetched alongside.
 template <int D, bool BF16>
-__device__ __forceinline__ void process_panel(const Panel<D, BF16>& f, const IngestParams& p,
-                                              uint64_t chunk, int lane,
+__device__ __forceinline__ int32_t stage_panel(const IngestParams& p, uint32_t chunk, int lane,
+                                               uint32_t stage_s)
+{
+    constexpr int G = D / kGroup;
+    constexpr int kElem = BF16 ? 2 : 1;
+    constexpr int kPiece = 8 * kElem;   // bytes of 8 channels
+    const int r = lane >> 2, qd = lane & 3;
+    const PanelId id = panel_of(p, chunk);
+    const size_t row_pitch = static_cast<size_t>(p.H) * D * kElem;  // bytes
+    const uint8_t* base = static_cast<const uint8_t*>(id.plane == 0 ? p.key : p.value) +
+                          (static_cast<size_t>(id.strip) * kStrip + 2 * r) * row_pitch +
+                          (static_cast<size_t>(id.head) * D + qd * 8) * kElem;
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t dst = stage_s + ((g * 2 + h) * 32 + lane) * kPiece;
+            const uint8_t* src = base + h * row_pitch + g * kGroup * kElem;
+            if constexpr (BF16) cp_async_16(dst, src);
+            else cp_async_8(dst, src);
+        }
+    return __ldg(p.slots + static_cast<size_t>(id.strip) * kStrip + (lane & 15));
+}
+
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+
+// Rotate, quantise, pack and store one panel whose fragments sit in `in` (this
+// thread's own bytes) and whose slot run is `slot`.
+template <int D, bool BF16>
+__device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t chunk, int lane,
+                                              const uint8_t* in, int32_t slot,
                                               const uint32_t (&bfrag)[BF16 ? 16 : 8],
                                               const float* sgn_s, uint32_t* stage)
 {
     constexpr int G = D / kGroup;
     constexpr int kPageWords = kStrip * D / 8;
+    constexpr int kPiece = BF16 ? 16 : 8;
     const int r = lane >> 2, qd = lane & 3;
-    const uint32_t head = static_cast<uint32_t>(chunk % p.H);
-    const uint32_t plane = static_cast<uint32_t>((chunk / p.H) & 1u);
+    const PanelId id = panel_of(p, chunk);
 
     // ---- the strip's page, from its slots; the contract is checked, not assumed
     // (tests/common/turboquant_oracle.hpp:278-287).
-    const int32_t slot0 = __shfl_sync(0xffffffffu, f.slot, 0);
-    const bool run_ok = (f.slot == slot0 + (lane & 15));
+    const int32_t slot0 = __shfl_sync(0xffffffffu, slot, 0);
+    const bool run_ok = (slot == slot0 + (lane & 15));
     const bool strip_ok = __all_sync(0xffffffffu, run_ok) && slot0 >= 0 && (slot0 % kStrip) == 0 &&
                           static_cast<uint32_t>(slot0) / p.S < p.P;
     if (!strip_ok) {
@@ -107,84 +140,79 @@ __device__ __forceinline__ void process_panel(const Panel<D, BF16>& f, const Ing
     const uint32_t page = static_cast<uint32_t>(slot0) / p.S;
     const uint32_t tok_in_page = static_cast<uint32_t>(slot0) % p.S;
 
-    // y[tt][g][e]: token 2r+tt, channel g*32 + qd*8 + e, as float (exact integers
-    // for int8 and integer-valued bf16 inputs).
-    float y[2][G][8];
+    // y[tt][g][ep]: token 2r+tt, channels g*32 + qd*8 + 2ep, +1 as one float pair
+    // (exact integers for int8 and integer-valued bf16 inputs).
+    float2 y[2][G][4];
     if constexpr (!BF16) {
         // The INT32 accumulator starts at the bit pattern of 1.5 * 2^23, so what comes
         // out, read as a float, is 12582912 + sum exactly; one FP32 subtract recovers
         // the sum without an integer-to-float conversion.
         constexpr int kBias = 0x4B400000;
+        const float2 unbias = f2(-12582912.0f, -12582912.0f);
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            const uint32_t a[4] = {f.lo[g].x, f.hi[g].x, f.lo[g].y, f.hi[g].y};
+            const uint2 lo = *reinterpret_cast<const uint2*>(in + ((g * 2 + 0) * 32 + lane) * kPiece);
+            const uint2 hi = *reinterpret_cast<const uint2*>(in + ((g * 2 + 1) * 32 + lane) * kPiece);
+            const uint32_t a[4] = {lo.x, hi.x, lo.y, hi.y};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 int c[4] = {kBias, kBias, kBias, kBias};
                 mma_s8_16832(c, a, bfrag[j * 2 + 0], bfrag[j * 2 + 1]);
-                y[0][g][j * 2 + 0] = __int_as_float(c[0]) - 12582912.0f;
-                y[0][g][j * 2 + 1] = __int_as_float(c[1]) - 12582912.0f;
-                y[1][g][j * 2 + 0] = __int_as_float(c[2]) - 12582912.0f;
-                y[1][g][j * 2 + 1] = __int_as_float(c[3]) - 12582912.0f;
+                y[0][g][j] = __fadd2_rn(f2(__int_as_float(c[0]), __int_as_float(c[1])), unbias);
+                y[1][g][j] = __fadd2_rn(f2(__int_as_float(c[2]), __int_as_float(c[3])), unbias);
             }
         }
     } else {
 #pragma unroll
         for (int g = 0; g < G; ++g) {
+            const uint4 lo = *reinterpret_cast<const uint4*>(in + ((g * 2 + 0) * 32 + lane) * kPiece);
+            const uint4 hi = *reinterpret_cast<const uint4*>(in + ((g * 2 + 1) * 32 + lane) * kPiece);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_bf16_16816(c, f.lo[g].x, f.hi[g].x, f.lo[g].y, f.hi[g].y, bfrag[j * 2 + 0],
-                               bfrag[j * 2 + 1]);
-                mma_bf16_16816(c, f.lo[g].z, f.hi[g].z, f.lo[g].w, f.hi[g].w, bfrag[8 + j * 2 + 0],
-                               bfrag[8 + j * 2 + 1]);
-                y[0][g][j * 2 + 0] = c[0];
-                y[0][g][j * 2 + 1] = c[1];
-                y[1][g][j * 2 + 0] = c[2];
-                y[1][g][j * 2 + 1] = c[3];
+                mma_bf16_16816(c, lo.x, hi.x, lo.y, hi.y, bfrag[j * 2 + 0], bfrag[j * 2 + 1]);
+                mma_bf16_16816(c, lo.z, hi.z, lo.w, hi.w, bfrag[8 + j * 2 + 0], bfrag[8 + j * 2 + 1]);
+                y[0][g][j] = f2(c[0], c[1]);
+                y[1][g][j] = f2(c[2], c[3]);
             }
         }
     }
 
     // ---- sign diagonal folded into the first stage of the outer factor H_G, then
-    // the remaining stages, per (token, e). All multiplies are by +-1: exact.
+    // the remaining stages, on packed pairs. All multiplies are by +-1: exact.
+    const float2 minus1 = f2(-1.0f, -1.0f);
     float amax[2] = {1.0f, 1.0f};  // the writer floors absmax at 1
-    {
-        float sgn[G][8];
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-            const float4 s0 = *reinterpret_cast<const float4*>(sgn_s + qd * (G * 8) + g * 8);
-            const float4 s1 = *reinterpret_cast<const float4*>(sgn_s + qd * (G * 8) + g * 8 + 4);
-            sgn[g][0] = s0.x; sgn[g][1] = s0.y; sgn[g][2] = s0.z; sgn[g][3] = s0.w;
-            sgn[g][4] = s1.x; sgn[g][5] = s1.y; sgn[g][6] = s1.z; sgn[g][7] = s1.w;
-        }
+    for (int ep = 0; ep < 4; ++ep) {
+        float2 sg[G];
 #pragma unroll
-        for (int tt = 0; tt < 2; ++tt)
+        for (int g = 0; g < G; ++g)
+            sg[g] = *reinterpret_cast<const float2*>(sgn_s + qd * (G * 8) + g * 8 + ep * 2);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                float x[G];
+        for (int tt = 0; tt < 2; ++tt) {
+            float2 x[G];
 #pragma unroll
-                for (int g = 0; g < G; g += 2) {
-                    const float a = sgn[g][e] * y[tt][g][e];
-                    x[g] = fmaf(sgn[g + 1][e], y[tt][g + 1][e], a);
-                    x[g + 1] = fmaf(-sgn[g + 1][e], y[tt][g + 1][e], a);
-                }
-#pragma unroll
-                for (int s = 2; s < G; s <<= 1)
-#pragma unroll
-                    for (int i = 0; i < G; ++i)
-                        if ((i & s) == 0) {
-                            const float a = x[i], bb = x[i + s];
-                            x[i] = a + bb;
-                            x[i + s] = a - bb;
-                        }
-#pragma unroll
-                for (int g = 0; g < G; g += 2) {
-                    y[tt][g][e] = x[g];
-                    y[tt][g + 1][e] = x[g + 1];
-                    amax[tt] = fmaxf(amax[tt], fmaxf(fabsf(x[g]), fabsf(x[g + 1])));
-                }
+            for (int g = 0; g < G; g += 2) {
+                const float2 a = __fmul2_rn(sg[g], y[tt][g][ep]);
+                const float2 b = __fmul2_rn(sg[g + 1], y[tt][g + 1][ep]);
+                x[g] = __fadd2_rn(a, b);
+                x[g + 1] = __ffma2_rn(b, minus1, a);
             }
+#pragma unroll
+            for (int s = 2; s < G; s <<= 1)
+#pragma unroll
+                for (int i = 0; i < G; ++i)
+                    if ((i & s) == 0) {
+                        const float2 a = x[i], b = x[i + s];
+                        x[i] = __fadd2_rn(a, b);
+                        x[i + s] = __ffma2_rn(b, minus1, a);
+                    }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                y[tt][g][ep] = x[g];
+                amax[tt] = fmaxf(amax[tt], fmaxf(fabsf(x[g].x), fabsf(x[g].y)));
+            }
+        }
     }
 #pragma unroll
     for (int tt = 0; tt < 2; ++tt) {
@@ -212,50 +240,59 @@ __device__ __forceinline__ void process_panel(const Panel<D, BF16>& f, const Ing
     constexpr float kMagic = 12582920.0f;           // 1.5 * 2^23 + 8
     constexpr float kMagicTop = 12582927.0f;        // 1.5 * 2^23 + 15
     constexpr uint32_t kMagicBits = 0x4B400000u;    // bits of 1.5 * 2^23
+    const float2 magic2 = f2(kMagic, kMagic);
     __syncwarp();  // the previous panel's copy-out has finished reading the stage
-    if (plane == 0) {
+    if (id.plane == 0) {
         // key page: token-major, row of D/8 words; this thread's word is g*4 + qd.
         // Horner over e = 7..0: w = sum (K + u_e) 16^e = K * 0x11111111 + packed.
         constexpr uint32_t kHorner = kMagicBits * 0x11111111u;
 #pragma unroll
-        for (int tt = 0; tt < 2; ++tt)
+        for (int tt = 0; tt < 2; ++tt) {
+            const float2 inv2 = f2(inv[tt], inv[tt]);
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 uint32_t w = 0;
 #pragma unroll
-                for (int e = 7; e >= 0; --e) {
-                    const float rr = fminf(fmaf(y[tt][g][e], inv[tt], kMagic), kMagicTop);
-                    w = w * 16u + __float_as_uint(rr);
+                for (int ep = 3; ep >= 0; --ep) {
+                    const float2 rr = __ffma2_rn(y[tt][g][ep], inv2, magic2);
+                    w = w * 16u + __float_as_uint(fminf(rr.y, kMagicTop));
+                    w = w * 16u + __float_as_uint(fminf(rr.x, kMagicTop));
                 }
                 stage[(2 * r + tt) * (D / 8) + ((g * 4 + qd) ^ (r & 3) * 4)] = (w - kHorner) ^ 0x88888888u;
             }
+        }
     } else {
         // value page: byte (channel*8 + r) = u(token 2r) + 16 u(token 2r+1); the store
         // keeps the low byte, to which 17 * 0x4B400000 contributes nothing.
         uint8_t* sb = reinterpret_cast<uint8_t*>(stage);
+        const float2 inv0 = f2(inv[0], inv[0]), inv1 = f2(inv[1], inv[1]);
 #pragma unroll
         for (int g = 0; g < G; ++g)
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const float r0 = fminf(fmaf(y[0][g][e], inv[0], kMagic), kMagicTop);
-                const float r1 = fminf(fmaf(y[1][g][e], inv[1], kMagic), kMagicTop);
-                const uint32_t byte = __float_as_uint(r1) * 16u + __float_as_uint(r0);
-                sb[(g * kGroup + qd * 8 + e) * 8 + r] = static_cast<uint8_t>(byte);
+            for (int ep = 0; ep < 4; ++ep) {
+                const float2 r0 = __ffma2_rn(y[0][g][ep], inv0, magic2);
+                const float2 r1 = __ffma2_rn(y[1][g][ep], inv1, magic2);
+                const uint32_t b0 = __float_as_uint(fminf(r1.x, kMagicTop)) * 16u +
+                                    __float_as_uint(fminf(r0.x, kMagicTop));
+                const uint32_t b1 = __float_as_uint(fminf(r1.y, kMagicTop)) * 16u +
+                                    __float_as_uint(fminf(r0.y, kMagicTop));
+                sb[(g * kGroup + qd * 8 + ep * 2) * 8 + r] = static_cast<uint8_t>(b0);
+                sb[(g * kGroup + qd * 8 + ep * 2 + 1) * 8 + r] = static_cast<uint8_t>(b1);
             }
     }
     __syncwarp();
 
     // ---- whole contiguous block out with 128-bit stores.
-    uint8_t* cache = plane == 0 ? p.key_cache : p.value_cache;
+    uint8_t* cache = id.plane == 0 ? p.key_cache : p.value_cache;
     const size_t block_bytes = static_cast<size_t>(kStrip) * D / 2;
-    uint8_t* dst = cache + (static_cast<size_t>(page) * p.H + head) * (static_cast<size_t>(p.S) * D / 2) +
+    uint8_t* dst = cache + (static_cast<size_t>(page) * p.H + id.head) * (static_cast<size_t>(p.S) * D / 2) +
                    static_cast<size_t>(tok_in_page / kStrip) * block_bytes;
     const uint4* s4 = reinterpret_cast<const uint4*>(stage);
 #pragma unroll
     for (int i = 0; i < kPageWords / 4 / 32; ++i) {
         const int unit = i * 32 + lane;  // 16-byte unit of the page
         uint4 v;
-        if (plane == 0) {
+        if (id.plane == 0) {
             // undo the store swizzle: unit = row * (D/32) + chunk, chunk ^= (row/2) & 3
             const int row = unit / (D / 32), chunk16 = unit % (D / 32);
             v = s4[row * (D / 32) + (chunk16 ^ ((row >> 1) & 3))];
@@ -270,7 +307,7 @@ __device__ __forceinline__ void process_panel(const Panel<D, BF16>& f, const Ing
     }
 
     if (qd == 0) {
-        const size_t at = ((static_cast<size_t>(plane) * p.P + page) * p.H + head) * p.S +
+        const size_t at = ((static_cast<size_t>(id.plane) * p.P + page) * p.H + id.head) * p.S +
                           tok_in_page + 2 * r;
         *reinterpret_cast<float2*>(p.scale_cache + at) =
             make_float2(pow2[0] * p.inv_sqrt_len, pow2[1] * p.inv_sqrt_len);
@@ -278,15 +315,18 @@ __device__ __forceinline__ void process_panel(const Panel<D, BF16>& f, const Ing
 }
 
 // Persistent: every warp walks panels warp_global, warp_global + warps_total, ...
-// with the next panel's loads in flight while the current one is processed.
+// with the next panel's bytes in flight while the current one is processed.
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kIngestWarps * 32, kIngestCtasPerSm)
 tq_ingest_kernel(const IngestParams p)
 {
     constexpr int G = D / kGroup;
     constexpr int kPageWords = kStrip * D / 8;
-    __shared__ __align__(16) uint32_t stage_all[kIngestWarps][kPageWords];
-    __shared__ __align__(16) float sgn_s[4 * G * 8];
+    constexpr int kInBytes = kStrip * D * (BF16 ? 2 : 1);   // one panel of activations
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    // per warp: two input stages, one output stage; then the sign table
+    uint8_t* warp_base = smem_raw + (threadIdx.x >> 5) * (2 * kInBytes + kPageWords * 4);
+    float* sgn_s = reinterpret_cast<float*>(smem_raw + kIngestWarps * (2 * kInBytes + kPageWords * 4));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, qd = lane & 3;
@@ -302,7 +342,7 @@ tq_ingest_kernel(const IngestParams p)
     uint32_t bfrag[BF16 ? 16 : 8];
     if constexpr (!BF16) {
         // contraction slot k of the low half is input channel (k/4)*8 + k%4, of the
-        // high half (k/4)*8 + 4 + k%4 -- the order the 8-byte loads deliver.
+        // high half (k/4)*8 + 4 + k%4 -- the order the 8-byte pieces deliver.
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const unsigned c0 = (r >> 1) * 8 + j * 2 + (r & 1);
@@ -333,36 +373,47 @@ tq_ingest_kernel(const IngestParams p)
     }
     __syncthreads();
 
-    const uint64_t total = static_cast<uint64_t>(p.num_strips) * 2u * p.H;
-    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kIngestWarps;
-    uint64_t c0 = static_cast<uint64_t>(blockIdx.x) * kIngestWarps + warp;
-    uint32_t* stage = stage_all[warp];
+    const uint32_t stride = gridDim.x * kIngestWarps;
+    uint32_t c = blockIdx.x * kIngestWarps + warp;
+    const uint32_t in_s = static_cast<uint32_t>(__cvta_generic_to_shared(warp_base));
+    uint32_t* stage = reinterpret_cast<uint32_t*>(warp_base + 2 * kInBytes);
 
-    Panel<D, BF16> pa, pb;
-    if (c0 < total) load_panel<D, BF16>(pa, p, c0, lane);
-    while (c0 < total) {
-        const uint64_t c1 = c0 + stride;
-        if (c1 < total) load_panel<D, BF16>(pb, p, c1, lane);
-        process_panel<D, BF16>(pa, p, c0, lane, bfrag, sgn_s, stage);
-        if (c1 >= total) break;
-        c0 = c1 + stride;
-        if (c0 < total) load_panel<D, BF16>(pa, p, c0, lane);
-        process_panel<D, BF16>(pb, p, c1, lane, bfrag, sgn_s, stage);
+    int32_t slot_cur = 0, slot_nxt = 0;
+    if (c < p.chunks) slot_cur = stage_panel<D, BF16>(p, c, lane, in_s);
+    asm volatile("cp.async.commit_group;\n" ::);
+    uint32_t buf = 0;
+#pragma unroll 1
+    for (; c < p.chunks; c += stride, buf ^= 1u) {
+        const uint32_t cn = c + stride;
+        if (cn < p.chunks) slot_nxt = stage_panel<D, BF16>(p, cn, lane, in_s + (buf ^ 1u) * kInBytes);
+        asm volatile("cp.async.commit_group;\n" ::);
+        asm volatile("cp.async.wait_group 1;\n" ::: "memory");   // this thread's own bytes of panel c
+        process_panel<D, BF16>(p, c, lane, warp_base + buf * kInBytes, slot_cur, bfrag, sgn_s, stage);
+        slot_cur = slot_nxt;
     }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 }
 
 template <int D, bool BF16>
 static cudaError_t launch_ingest(cudaStream_t stream, const IngestParams& p)
 {
-    const uint64_t chunks = static_cast<uint64_t>(p.num_strips) * 2u * p.H;
-    uint64_t blocks = (chunks + kIngestWarps - 1) / kIngestWarps;
+    constexpr int kInBytes = kStrip * D * (BF16 ? 2 : 1);
+    constexpr int kSmem = kIngestWarps * (2 * kInBytes + kStrip * D / 2) + 4 * (D / kGroup) * 8 * 4;
+    uint32_t blocks = (p.chunks + kIngestWarps - 1) / kIngestWarps;
     if (blocks == 0) return cudaSuccess;
     int dev = 0, sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess)
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const uint64_t resident = static_cast<uint64_t>(sms) * kIngestCtasPerSm;
+    if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorNoDevice;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    static bool configured[64] = {};   // benign race: the attribute is idempotent
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(tq_ingest_kernel<D, BF16>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    const uint32_t resident = static_cast<uint32_t>(sms) * kIngestCtasPerSm;
     if (blocks > resident) blocks = resident;  // persistent: one resident wave
-    tq_ingest_kernel<D, BF16><<<static_cast<unsigned>(blocks), kIngestWarps * 32, 0, stream>>>(p);
+    tq_ingest_kernel<D, BF16><<<blocks, kIngestWarps * 32, kSmem, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -386,6 +437,14 @@ extern "C" int tq_reshape_and_cache(void* stream, const void* key, const void* v
     if (num_tokens == 0) return TQ_OK;
     if (!key || !value || !key_cache || !value_cache || !scale_cache || !slot_mapping || !signs)
         return TQ_ERR_INVALID_ARGUMENT;
+    // 16-byte accesses on every operand; panels are indexed in 32 bits
+    const uintptr_t align = reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value) |
+                            reinterpret_cast<uintptr_t>(key_cache) |
+                            reinterpret_cast<uintptr_t>(value_cache) |
+                            reinterpret_cast<uintptr_t>(scale_cache);
+    const uint64_t chunks = static_cast<uint64_t>(num_tokens / kStrip) * 2u * num_kv_heads;
+    if ((align & 15u) != 0u || chunks >= 0x7FFFFFFFull || num_kv_heads > 0x10000u)
+        return TQ_ERR_INVALID_ARGUMENT;
 
     IngestParams p;
     p.key = key;
@@ -400,6 +459,14 @@ extern "C" int tq_reshape_and_cache(void* stream, const void* key, const void* v
     p.H = num_kv_heads;
     p.S = block_size;
     p.P = num_blocks;
+    p.chunks = static_cast<uint32_t>(chunks);
+    {
+        const uint32_t d = 2u * num_kv_heads;   // >= 2
+        uint32_t l = 0;
+        while ((1ull << l) < d) ++l;
+        p.div_mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d)) / d + 1ull);
+        p.div_shift = l - 1u;
+    }
     p.inv_sqrt_len = inv_sqrt_len;
     p.status = status;
 

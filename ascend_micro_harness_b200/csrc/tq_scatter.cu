@@ -79,30 +79,7 @@ __global__ void __launch_bounds__(kScatterWarps * 32) tq_scatter_kernel(const Sc
                         v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
                     }
                 }
-                // One cascade stage at channel stride s: out[i] = in[i^s] +- in[i].
-                auto stage = [&](int s) {
-                    if (s < K) {
-#pragma unroll
-                        for (int i = 0; i < K; ++i)
-                            if ((i & s) == 0) {
-                                const float a = v[i], b = v[i + s];
-                                v[i] = b + a;
-                                v[i + s] = a - b;
-                            }
-                    } else {
-                        const int lm = s / K;
-                        const bool upper = (lane & lm) != 0;
-#pragma unroll
-                        for (int i = 0; i < K; ++i) {
-                            const float other = __shfl_xor_sync(0xffffffffu, v[i], lm);
-                            v[i] = other + (upper ? -v[i] : v[i]);
-                        }
-                    }
-                };
-                for (int s = 1; s < kGroup; s <<= 1) stage(s);
-#pragma unroll
-                for (int i = 0; i < K; ++i) v[i] *= sgn[i];
-                for (int s = kGroup; s < D; s <<= 1) stage(s);
+                cascade_ingress<K>(v, sgn, lane);
 
                 float amax = 0.0f;
 #pragma unroll
