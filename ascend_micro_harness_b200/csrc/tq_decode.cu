@@ -880,6 +880,66 @@ extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_
                              inv_sqrt_len, status);
 }
 
+// ------------------------------------------------- decode without a caller workspace
+// Split-K partials normally live in a workspace the caller allocates. Some hosts have
+// no way to provide one: a serving process that handed every free byte of HBM to its
+// KV-cache pool at start-up (a later cudaMalloc simply fails), or an attention backend
+// embedded in a runtime whose allocator it may not call from the launch path. For
+// them the partials go into this fixed array, which every GPU that loads the library
+// carries until the process exits: 8 MiB, enough for e.g. 64 sequences x 8 KV heads
+// x 4 splits x 4 query rows per KV head at head size 128.
+static __device__ __align__(256) float g_static_workspace[TQ_STATIC_WORKSPACE_FLOATS];
+
+// In host code `g_static_workspace` is only a handle for the device symbol, not a
+// device address: the address is looked up once per device, with that device current.
+static float* static_workspace_address(int* status)
+{
+    static float* address[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        *status = TQ_ERR_NO_DEVICE;
+        return nullptr;
+    }
+    if (address[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_workspace) != cudaSuccess || ptr == nullptr) {
+            *status = TQ_ERR_NO_DEVICE;
+            return nullptr;
+        }
+        address[dev] = static_cast<float*>(ptr);
+    }
+    *status = TQ_OK;
+    return address[dev];
+}
+
+extern "C" int tq_decode_splitk_static(void* stream, const uint16_t* query, const int8_t* key_cache,
+                                       const int8_t* value_cache, const float* scale_cache,
+                                       const int32_t* block_tables, const int32_t* context_lens,
+                                       const float* pi_signs, const float* gate, void* output,
+                                       uint32_t out_dtype, uint32_t batch, uint32_t num_heads,
+                                       uint32_t num_kv_heads, uint32_t head_size,
+                                       uint32_t block_size, uint32_t num_blocks,
+                                       uint32_t max_blocks, uint32_t splits,
+                                       uint32_t max_context_hint, uint32_t output_stage,
+                                       float inv_sqrt_len, float softmax_scale, uint32_t* status)
+{
+    if (!num_kv_heads || !block_size || splits > 16) return TQ_ERR_INVALID_ARGUMENT;
+    // Resolve the split count first: it decides how much of the array the launch needs.
+    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint);
+    const size_t need = tq_decode_workspace_floats(batch, num_heads, num_kv_heads, head_size, splits);
+    if (need > static_cast<size_t>(TQ_STATIC_WORKSPACE_FLOATS)) return TQ_ERR_WORKSPACE_TOO_SMALL;
+    int st = TQ_OK;
+    float* workspace = static_workspace_address(&st);
+    if (workspace == nullptr) return st;
+    // Every partition the combine reads is written by this launch first (empty splits
+    // export the neutral element), so nothing in the array has to start at zero.
+    return tq_decode_splitk(stream, query, key_cache, value_cache, scale_cache, block_tables,
+                            context_lens, pi_signs, gate, workspace, output, out_dtype, batch,
+                            num_heads, num_kv_heads, head_size, block_size, num_blocks, max_blocks,
+                            splits, max_context_hint, output_stage, inv_sqrt_len, softmax_scale,
+                            status);
+}
+
 // kernels/ops/turboquant/turboquant_paged_decode_attention.cpp:1727-1766. The
 // reference decoder is compiled for d = 256 and 16 packed query rows per head;
 // pi_table is its 16 resident bf16 blocks, of which only the sign diagonal is

@@ -33,6 +33,8 @@ extern "C" const char* tq_status_string(int status)
     case TQ_ERR_PARTIAL_STRIP: return "num_tokens is not a whole number of 16-token strips";
     case TQ_ERR_LAUNCH: return "the CUDA runtime refused the launch";
     case TQ_ERR_NO_DEVICE: return "no usable CUDA device";
+    case TQ_ERR_WORKSPACE_TOO_SMALL:
+        return "the launch needs more split-K workspace than the built-in array holds";
     default: return "unknown status";
     }
 }

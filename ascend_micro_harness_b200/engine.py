@@ -92,6 +92,28 @@ def decode_splitk(query, key_cache, value_cache, scale_cache, block_tables, cont
         _ptr(status)), "tq_decode_splitk")
 
 
+STATIC_WORKSPACE_FLOATS = 2 * 1024 * 1024
+
+
+def decode_splitk_static(query, key_cache, value_cache, scale_cache, block_tables, context_lens,
+                         pi_signs, output, *, num_heads, num_kv_heads, head_size, block_size,
+                         num_blocks, inv_sqrt_len, softmax_scale=1.0, splits=0, max_context_hint=0,
+                         gate=None, output_stage=OUT_ROTATED, status=None, stream=None):
+    """decode_splitk for callers that cannot allocate device memory at launch time (all HBM
+    already given to a cache pool, or an allocator they may not call): the split-K partials
+    go into the library's own fixed 8 MiB array. Raises TqError(5) when the launch needs more
+    than STATIC_WORKSPACE_FLOATS floats. Calls on one device share that array: keep them
+    ordered, and make the first call on a device before any stream capture."""
+    lib = load_library()
+    batch = query.numel() // (num_heads * head_size)
+    _check(lib.tq_decode_splitk_static(
+        _stream(stream), _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache),
+        _ptr(block_tables), _ptr(context_lens), _ptr(pi_signs), _ptr(gate), _ptr(output),
+        _out_dtype(output), batch, num_heads, num_kv_heads, head_size, block_size, num_blocks,
+        block_tables.shape[-1], splits, max_context_hint, output_stage, inv_sqrt_len,
+        softmax_scale, _ptr(status)), "tq_decode_splitk_static")
+
+
 def decode_splitk_export(query, key_cache, value_cache, scale_cache, block_tables, context_lens,
                          pi_signs, workspace, *, num_heads, num_kv_heads, head_size, block_size,
                          num_blocks, inv_sqrt_len, splits, softmax_scale=1.0, max_context_hint=0,

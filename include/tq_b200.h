@@ -42,6 +42,7 @@ extern "C" {
 #define TQ_ERR_PARTIAL_STRIP 2    /* num_tokens not a whole number of strips    */
 #define TQ_ERR_LAUNCH 3           /* the CUDA runtime refused the launch        */
 #define TQ_ERR_NO_DEVICE 4        /* no CUDA device / kernel image unusable     */
+#define TQ_ERR_WORKSPACE_TOO_SMALL 5 /* the launch needs more than the built-in workspace holds */
 
 /* Bits a kernel ORs into the optional device status word. */
 #define TQ_STATUS_BAD_SLOT 0x1u     /* a strip's slots break the one-strip-one-page run */
@@ -155,6 +156,35 @@ uint32_t tq_decode_choose_splits(uint32_t batch, uint32_t num_kv_heads, uint32_t
  * include/turboquant_splitk_contract.hpp:23-27 with kChannels -> head_size. */
 size_t tq_decode_workspace_floats(uint32_t batch, uint32_t num_heads, uint32_t num_kv_heads,
                                   uint32_t head_size, uint32_t splits);
+
+/* tq_decode_splitk for callers that cannot hand over a workspace. It has no
+ * counterpart in the reference. Meant for hosts that cannot allocate device memory
+ * when a decode step is launched: a serving process whose KV-cache pool took all
+ * free HBM at start-up, or a backend that must not call its host runtime's allocator
+ * from the launch path. The split-K partials go into a fixed 8 MiB array inside the
+ * library (TQ_STATIC_WORKSPACE_FLOATS floats, resident on every GPU that loads the
+ * library until the process exits); the call itself allocates and frees nothing.
+ *   - Limit: batch * num_kv_heads * splits * (num_heads / num_kv_heads) * (16 + head_size)
+ *     floats must fit; otherwise TQ_ERR_WORKSPACE_TOO_SMALL is returned and nothing runs.
+ *     With splits == 0 the limit is checked against the split count the launcher picks.
+ *   - The first call on each device looks up the array's device address (one CUDA
+ *     runtime query, made with that device current). Make that first call before any
+ *     stream capture begins.
+ *   - All calls share the one array and it keeps whatever the last call left in it.
+ *     Nothing needs clearing (each launch writes every record it later reads), but two
+ *     calls whose kernels can overlap on the GPU -- different streams, no ordering --
+ *     race on it: keep calls on one device ordered.
+ * Arguments are those of tq_decode_splitk without `workspace`. */
+#define TQ_STATIC_WORKSPACE_FLOATS (2u * 1024u * 1024u)
+int tq_decode_splitk_static(void* stream, const uint16_t* query, const int8_t* key_cache,
+                            const int8_t* value_cache, const float* scale_cache,
+                            const int32_t* block_tables, const int32_t* context_lens,
+                            const float* pi_signs, const float* gate, void* output,
+                            uint32_t out_dtype, uint32_t batch, uint32_t num_heads,
+                            uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                            uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                            uint32_t max_context_hint, uint32_t output_stage,
+                            float inv_sqrt_len, float softmax_scale, uint32_t* status);
 
 /* Per-split export only, no merge: the contract of
  * launch_turboquant_paged_decode_splitk_aic (16 query rows per KV head, records
