@@ -127,7 +127,7 @@ __device__ __forceinline__ uint32_t dq_hi(uint32_t x)
 __device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                               uint32_t a3, uint32_t b0, uint32_t b1)
 {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
         "{%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -325,8 +325,11 @@ tq_decode_partial_kernel(const DecodeParams p)
     const uint8_t* ksrc0 = p.key_cache + head * head_block + lane * 16;
     const uint8_t* vsrc0 = p.value_cache + head * head_block + lane * 16;
     const float* ssrc0 = p.scale_cache + (lane >> 2) * scale_plane + static_cast<size_t>(head) * p.S + (lane & 3) * 4;
-    const size_t page_stride = static_cast<size_t>(p.H) * head_block;
-    const size_t page_stride_scale = static_cast<size_t>(p.H) * p.S;
+    // strides fit 32 bits (one page of one cache), so a page's offset is one widening
+    // multiply-add on the lane's base pointer
+    const uint32_t page_stride = p.H * static_cast<uint32_t>(head_block);
+    const uint32_t page_stride_scale = p.H * p.S;
+    const uint32_t sip_mask = (1u << sp_shift) - 1u;
     auto issue = [&](uint32_t strip, uint32_t stage, const int32_t (&pg)[kTileStrips]) {
 #pragma unroll
         for (int ts = 0; ts < kTileStrips; ++ts) {
@@ -336,17 +339,18 @@ tq_decode_partial_kernel(const DecodeParams p)
                 if (lane == 0) report(p.status, TQ_STATUS_BAD_PAGE);
                 page = 0;
             }
-            const uint32_t sip = (strip + ts) & ((1u << sp_shift) - 1u);
-            const size_t off = page * page_stride + static_cast<size_t>(sip) * L::kStripBytes;
+            const uint32_t sip = (strip + ts) & sip_mask;
+            const uint8_t* ksrc = ksrc0 + static_cast<size_t>(page) * page_stride + sip * L::kStripBytes;
+            const uint8_t* vsrc = vsrc0 + static_cast<size_t>(page) * page_stride + sip * L::kStripBytes;
             const uint32_t dst = my_ring_s + stage * L::kStageBytes + ts * L::kStripStage;
 #pragma unroll
             for (int i = 0; i < kChunksPerLane; ++i) {
-                cp_async16(dst + kdst[i], ksrc0 + off + i * 512);
-                cp_async16(dst + L::kStripBytes + i * 512 + lane * 16, vsrc0 + off + i * 512);
+                cp_async16(dst + kdst[i], ksrc + i * 512);
+                cp_async16(dst + L::kStripBytes + i * 512 + lane * 16, vsrc + i * 512);
             }
             if (lane < 8)
                 cp_async16(dst + 2 * L::kStripBytes + lane * 16,
-                           ssrc0 + page * page_stride_scale + sip * kStrip);
+                           ssrc0 + static_cast<size_t>(page) * page_stride_scale + sip * kStrip);
         }
     };
 
