@@ -58,6 +58,7 @@ struct DecodeParams {
     uint32_t items, H, rows, rows_stride, S, P;
     uint32_t table_stride, splits, page_begin, page_count, fixed_ctx;
     uint32_t sp_shift;        // log2(strips per page); pages hold 16 * 2^k tokens
+    uint32_t chunk_pages;     // 0: every sequence uses `splits`; else at most ceil(pages/chunk)
     float inv_sqrt_len, softmax_scale;
     uint32_t* status;
 };
@@ -206,7 +207,15 @@ tq_decode_partial_kernel(const DecodeParams p)
         ctx = p.fixed_ctx;
         page_count = p.page_count;
     }
-    const uint32_t width = (page_count + p.splits - 1u) / p.splits;
+    // Ragged batches: a sequence takes only as many of the launch's splits as it has
+    // chunks of chunk_pages pages, so CTAs carry similar amounts of work; the splits it
+    // does not use fall out of the partition as empty ranges and export the neutral element.
+    uint32_t eff_splits = p.splits;
+    if (p.chunk_pages != 0u) {
+        const uint32_t chunks = (page_count + p.chunk_pages - 1u) / p.chunk_pages;
+        eff_splits = chunks < 1u ? 1u : (chunks < p.splits ? chunks : p.splits);
+    }
+    const uint32_t width = (page_count + eff_splits - 1u) / eff_splits;
     const uint32_t rb = split * width;
     const uint32_t remaining = rb < page_count ? page_count - rb : 0u;
     const uint32_t rc = remaining < width ? remaining : width;
@@ -671,25 +680,35 @@ static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
 
 using namespace tq;
 
+// Split plan for a launch that leaves the choice to the library. Work is cut into chunks
+// of a power-of-two number of tokens such that the batch yields about 32 CTAs per SM
+// (fine enough to balance ragged contexts, 256..8192 tokens so a chunk amortises its
+// prologue); the launch's split count is what the longest context needs, at most 16.
+static void decode_plan(uint32_t batch, uint32_t num_kv_heads, uint32_t block_size,
+                        uint32_t max_context, uint32_t sm_count, uint32_t* splits,
+                        uint32_t* chunk_pages)
+{
+    *splits = 1;
+    *chunk_pages = 0;
+    if (batch == 0 || num_kv_heads == 0 || block_size == 0 || max_context <= 256u) return;
+    const uint64_t items = static_cast<uint64_t>(batch) * num_kv_heads;
+    const uint64_t target = 32ull * (sm_count ? sm_count : 148u);
+    const uint64_t want = items * max_context / target;
+    uint64_t chunk = 256;
+    while (chunk < want && chunk < 8192u) chunk <<= 1;
+    while ((max_context + chunk - 1u) / chunk > 16u) chunk <<= 1;   // very long contexts
+    if (chunk < block_size) chunk = block_size;
+    *chunk_pages = static_cast<uint32_t>(chunk / block_size);
+    *splits = static_cast<uint32_t>((max_context + chunk - 1u) / chunk);
+}
+
 extern "C" uint32_t tq_decode_choose_splits(uint32_t batch, uint32_t num_kv_heads,
                                             uint32_t block_size, uint32_t max_context,
                                             uint32_t sm_count)
 {
-    // Enough CTAs to fill the machine a few times over, never more splits than
-    // pages, never so many that a split has less than ~8 strips to amortise its
-    // prologue. Contexts of at most 512 tokens run un-split.
-    if (batch == 0 || num_kv_heads == 0 || block_size == 0) return 1;
-    const uint32_t pages = (max_context + block_size - 1u) / block_size;
-    if (max_context <= 512u || pages <= 1u) return 1;
-    const uint64_t items = static_cast<uint64_t>(batch) * num_kv_heads;
-    const uint64_t target = 4ull * (sm_count ? sm_count : 148u);
-    uint64_t s = (target + items - 1) / items;
-    const uint64_t by_len = (static_cast<uint64_t>(max_context) + 127u) / 128u;
-    if (s > by_len) s = by_len;
-    if (s > pages) s = pages;
-    if (s > 16) s = 16;
-    if (s < 1) s = 1;
-    return static_cast<uint32_t>(s);
+    uint32_t splits, chunk_pages;
+    decode_plan(batch, num_kv_heads, block_size, max_context, sm_count, &splits, &chunk_pages);
+    return splits;
 }
 
 extern "C" size_t tq_decode_workspace_floats(uint32_t batch, uint32_t num_heads,
@@ -790,30 +809,34 @@ extern "C" int tq_splitk_combine(void* stream, const float* workspace, const flo
 }
 
 static uint32_t resolve_splits(uint32_t splits, uint32_t batch, uint32_t num_kv_heads,
-                               uint32_t block_size, uint32_t max_blocks, uint32_t hint)
+                               uint32_t block_size, uint32_t max_blocks, uint32_t hint,
+                               uint32_t* chunk_pages = nullptr)
 {
-    if (splits != 0) return splits;
+    if (chunk_pages) *chunk_pages = 0;
+    if (splits != 0) return splits;   // explicit: every sequence uses the reference Partition
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess)
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    return tq_decode_choose_splits(batch, num_kv_heads, block_size,
-                                   hint ? hint : max_blocks * block_size,
-                                   static_cast<uint32_t>(sms));
+    uint32_t s = 1, c = 0;
+    decode_plan(batch, num_kv_heads, block_size, hint ? hint : max_blocks * block_size,
+                static_cast<uint32_t>(sms), &s, &c);
+    if (chunk_pages) *chunk_pages = c;
+    return s;
 }
 
-extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
-                                       const int8_t* key_cache, const int8_t* value_cache,
-                                       const float* scale_cache, const int32_t* block_tables,
-                                       const int32_t* context_lens, const float* pi_signs,
-                                       float* workspace, uint32_t batch, uint32_t num_heads,
-                                       uint32_t num_kv_heads, uint32_t head_size,
-                                       uint32_t block_size, uint32_t num_blocks,
-                                       uint32_t max_blocks, uint32_t splits,
-                                       uint32_t max_context_hint, float inv_sqrt_len,
-                                       float softmax_scale, uint32_t* status)
+// The export stage with its split plan resolved: `splits` partitions per sequence in the
+// workspace, of which a sequence uses ceil(pages / chunk_pages) when chunk_pages != 0.
+static int decode_export_planned(void* stream, const uint16_t* query, const int8_t* key_cache,
+                                 const int8_t* value_cache, const float* scale_cache,
+                                 const int32_t* block_tables, const int32_t* context_lens,
+                                 const float* pi_signs, float* workspace, uint32_t batch,
+                                 uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                                 uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                                 uint32_t splits, uint32_t chunk_pages, float inv_sqrt_len,
+                                 float softmax_scale, uint32_t* status)
 {
     if (!num_heads || !num_kv_heads || num_heads % num_kv_heads != 0 || !block_size ||
-        block_size % kStrip != 0 || !num_blocks || !max_blocks || splits > 16 ||
+        block_size % kStrip != 0 || !num_blocks || !max_blocks || !splits || splits > 16 ||
         (head_size != 128 && head_size != 256))
         return TQ_ERR_INVALID_ARGUMENT;
     const uint32_t rows = num_heads / num_kv_heads;
@@ -845,7 +868,8 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
     p.S = block_size;
     p.P = num_blocks;
     p.table_stride = max_blocks;
-    p.splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint);
+    p.splits = splits;
+    p.chunk_pages = chunk_pages;
     p.page_begin = 0;
     p.page_count = 0;
     p.fixed_ctx = 0;
@@ -855,6 +879,51 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const cudaError_t e = head_size == 128 ? launch_partial<128, false>(s, p) : launch_partial<256, false>(s, p);
     return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
+
+extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
+                                       const int8_t* key_cache, const int8_t* value_cache,
+                                       const float* scale_cache, const int32_t* block_tables,
+                                       const int32_t* context_lens, const float* pi_signs,
+                                       float* workspace, uint32_t batch, uint32_t num_heads,
+                                       uint32_t num_kv_heads, uint32_t head_size,
+                                       uint32_t block_size, uint32_t num_blocks,
+                                       uint32_t max_blocks, uint32_t splits,
+                                       uint32_t max_context_hint, float inv_sqrt_len,
+                                       float softmax_scale, uint32_t* status)
+{
+    if (!num_kv_heads || !block_size || splits > 16) return TQ_ERR_INVALID_ARGUMENT;
+    uint32_t chunk_pages = 0;
+    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
+                            &chunk_pages);
+    return decode_export_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
+                                 context_lens, pi_signs, workspace, batch, num_heads, num_kv_heads,
+                                 head_size, block_size, num_blocks, max_blocks, splits, chunk_pages,
+                                 inv_sqrt_len, softmax_scale, status);
+}
+
+static int decode_planned(void* stream, const uint16_t* query, const int8_t* key_cache,
+                          const int8_t* value_cache, const float* scale_cache,
+                          const int32_t* block_tables, const int32_t* context_lens,
+                          const float* pi_signs, const float* gate, float* workspace, void* output,
+                          uint32_t out_dtype, uint32_t batch, uint32_t num_heads,
+                          uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                          uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                          uint32_t chunk_pages, uint32_t output_stage, float inv_sqrt_len,
+                          float softmax_scale, uint32_t* status)
+{
+    if (output_stage > TQ_OUT_GATED || !output || (output_stage == TQ_OUT_GATED && !gate))
+        return TQ_ERR_INVALID_ARGUMENT;
+    const int st = decode_export_planned(stream, query, key_cache, value_cache, scale_cache,
+                                         block_tables, context_lens, pi_signs, workspace, batch,
+                                         num_heads, num_kv_heads, head_size, block_size, num_blocks,
+                                         max_blocks, splits, chunk_pages, inv_sqrt_len,
+                                         softmax_scale, status);
+    if (st != TQ_OK || batch == 0) return st;
+    const uint32_t rows = num_heads / num_kv_heads;
+    return tq_splitk_combine(stream, workspace, pi_signs, gate, output, out_dtype,
+                             batch * num_kv_heads, rows, rows, head_size, splits, output_stage,
+                             inv_sqrt_len, status);
 }
 
 extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_t* key_cache,
@@ -867,21 +936,14 @@ extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_
                                 uint32_t max_context_hint, uint32_t output_stage,
                                 float inv_sqrt_len, float softmax_scale, uint32_t* status)
 {
-    if (output_stage > TQ_OUT_GATED || !output || (output_stage == TQ_OUT_GATED && !gate))
-        return TQ_ERR_INVALID_ARGUMENT;
-    if (splits > 16) return TQ_ERR_INVALID_ARGUMENT;
-    splits = resolve_splits(splits, batch, num_kv_heads ? num_kv_heads : 1, block_size ? block_size : 16,
-                            max_blocks, max_context_hint);
-    const int st = tq_decode_splitk_export(stream, query, key_cache, value_cache, scale_cache,
-                                           block_tables, context_lens, pi_signs, workspace, batch,
-                                           num_heads, num_kv_heads, head_size, block_size,
-                                           num_blocks, max_blocks, splits, max_context_hint,
-                                           inv_sqrt_len, softmax_scale, status);
-    if (st != TQ_OK || batch == 0) return st;
-    const uint32_t rows = num_heads / num_kv_heads;
-    return tq_splitk_combine(stream, workspace, pi_signs, gate, output, out_dtype,
-                             batch * num_kv_heads, rows, rows, head_size, splits, output_stage,
-                             inv_sqrt_len, status);
+    if (!num_kv_heads || !block_size || splits > 16) return TQ_ERR_INVALID_ARGUMENT;
+    uint32_t chunk_pages = 0;
+    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
+                            &chunk_pages);
+    return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
+                          context_lens, pi_signs, gate, workspace, output, out_dtype, batch, num_heads,
+                          num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,
+                          chunk_pages, output_stage, inv_sqrt_len, softmax_scale, status);
 }
 
 // ------------------------------------------------- decode without a caller workspace
@@ -929,7 +991,9 @@ extern "C" int tq_decode_splitk_static(void* stream, const uint16_t* query, cons
 {
     if (!num_kv_heads || !block_size || splits > 16) return TQ_ERR_INVALID_ARGUMENT;
     // Resolve the split count first: it decides how much of the array the launch needs.
-    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint);
+    uint32_t chunk_pages = 0;
+    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
+                            &chunk_pages);
     const size_t need = tq_decode_workspace_floats(batch, num_heads, num_kv_heads, head_size, splits);
     if (need > static_cast<size_t>(TQ_STATIC_WORKSPACE_FLOATS)) return TQ_ERR_WORKSPACE_TOO_SMALL;
     int st = TQ_OK;
@@ -937,11 +1001,10 @@ extern "C" int tq_decode_splitk_static(void* stream, const uint16_t* query, cons
     if (workspace == nullptr) return st;
     // Every partition the combine reads is written by this launch first (empty splits
     // export the neutral element), so nothing in the array has to start at zero.
-    return tq_decode_splitk(stream, query, key_cache, value_cache, scale_cache, block_tables,
-                            context_lens, pi_signs, gate, workspace, output, out_dtype, batch,
-                            num_heads, num_kv_heads, head_size, block_size, num_blocks, max_blocks,
-                            splits, max_context_hint, output_stage, inv_sqrt_len, softmax_scale,
-                            status);
+    return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
+                          context_lens, pi_signs, gate, workspace, output, out_dtype, batch, num_heads,
+                          num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,
+                          chunk_pages, output_stage, inv_sqrt_len, softmax_scale, status);
 }
 
 // kernels/ops/turboquant/turboquant_paged_decode_attention.cpp:1727-1766. The

@@ -183,7 +183,7 @@ def run_ours(args):
 
     def export():
         tq.decode_splitk_export(dq, w["key_cache"], w["value_cache"], w["scale_cache"], w["tables"],
-                                dctx, w["signs"], ws, num_heads=HQ, splits=splits,
+                                dctx, w["signs"], ws, num_heads=HQ, splits=0,
                                 softmax_scale=scale, max_context_hint=int(ctx.max()), status=status,
                                 **geom)
 
@@ -263,7 +263,7 @@ def run_ours(args):
             "metric": "splitk_4bit_decode_kv_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int4 codes, bf16 x bf16 -> f32", "data": "synthetic",
+            "vs_baseline": None, "dtype": "int4 codes, f16 x f16 -> f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "q_heads": HQ, "kv_heads": HKV,
                        "head_dim": D, "page_tokens": S, "splits": int(splits),
                        "kv_bytes_per_gpu": my_bytes,
@@ -362,7 +362,7 @@ def run_profile_case(args):
                                     w["tables"], dctx, w["signs"], ws, num_heads=HQ,
                                     num_kv_heads=HKV, head_size=D, block_size=S,
                                     num_blocks=w["total_pages"], inv_sqrt_len=w["inv"],
-                                    splits=splits, softmax_scale=float(1.0 / np.sqrt(D)),
+                                    splits=0, softmax_scale=float(1.0 / np.sqrt(D)),
                                     max_context_hint=int(w["ctx"].max()))
         torch.cuda.synchronize()
         print(json.dumps({"profile": "decode", "kv_bytes": kv_bytes(w["ctx"]), "splits": int(splits)}))

@@ -41,14 +41,17 @@ def test_acl_shim_exports_the_sixteen_calls():
 
 
 def test_split_choice():
+    """The plan cuts work into power-of-two chunks of 256..8192 tokens, about 32 CTAs per SM;
+    the launch's split count is what the longest context needs, at most 16."""
     import ascend_micro_harness_b200 as tq
     assert tq.choose_splits(64, 8, 16, 256) == 1            # short contexts run un-split
     assert tq.choose_splits(1, 8, 16, 4096) == 16           # one sequence: fill the machine
-    assert tq.choose_splits(1, 8, 16, 1024) == 8            # ... but keep >= 128 tokens per split
-    assert 1 <= tq.choose_splits(64, 8, 16, 32768) <= 4     # a big batch needs few splits
-    assert tq.choose_splits(4096, 8, 16, 32768) == 1
+    assert tq.choose_splits(1, 8, 16, 1024) == 4            # ... but keep 256 tokens per split
+    assert tq.choose_splits(64, 8, 16, 32768) == 8          # ragged batch: 4096-token chunks
+    assert tq.choose_splits(4096, 8, 16, 32768) == 4        # plenty of sequences: 8192-token chunks
+    assert tq.choose_splits(128, 8, 16, 65536) == 8
     for b in (1, 3, 64, 1000):
-        for ctx in (1, 600, 5000, 70000):
+        for ctx in (1, 600, 5000, 70000, 1 << 20):
             s = tq.choose_splits(b, 8, 16, ctx)
             assert 1 <= s <= 16 and s <= max(1, (ctx + 15) // 16)
 
