@@ -692,7 +692,10 @@ static void decode_plan(uint32_t batch, uint32_t num_kv_heads, uint32_t block_si
     *chunk_pages = 0;
     if (batch == 0 || num_kv_heads == 0 || block_size == 0 || max_context <= 256u) return;
     const uint64_t items = static_cast<uint64_t>(batch) * num_kv_heads;
-    const uint64_t target = 32ull * (sm_count ? sm_count : 148u);
+#ifndef TQ_PLAN_CTAS_PER_SM
+#define TQ_PLAN_CTAS_PER_SM 32
+#endif
+    const uint64_t target = static_cast<uint64_t>(TQ_PLAN_CTAS_PER_SM) * (sm_count ? sm_count : 148u);
     const uint64_t want = items * max_context / target;
     uint64_t chunk = 256;
     while (chunk < want && chunk < 8192u) chunk <<= 1;
