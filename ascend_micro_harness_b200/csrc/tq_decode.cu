@@ -682,8 +682,10 @@ using namespace tq;
 
 // Split plan for a launch that leaves the choice to the library. Work is cut into chunks
 // of a power-of-two number of tokens such that the batch yields about 32 CTAs per SM
-// (fine enough to balance ragged contexts, 256..8192 tokens so a chunk amortises its
-// prologue); the launch's split count is what the longest context needs, at most 16.
+// (fine enough to balance ragged contexts; measured best among 16/32/64/128 on the ragged
+// batch of 64). A chunk is 256..8192 tokens, and at least 1024 once the batch alone has a
+// CTA per SM, so that it amortises the per-CTA query rotation and merge; the launch's
+// split count is what the longest context needs, at most 16.
 static void decode_plan(uint32_t batch, uint32_t num_kv_heads, uint32_t block_size,
                         uint32_t max_context, uint32_t sm_count, uint32_t* splits,
                         uint32_t* chunk_pages)
@@ -692,12 +694,9 @@ static void decode_plan(uint32_t batch, uint32_t num_kv_heads, uint32_t block_si
     *chunk_pages = 0;
     if (batch == 0 || num_kv_heads == 0 || block_size == 0 || max_context <= 256u) return;
     const uint64_t items = static_cast<uint64_t>(batch) * num_kv_heads;
-#ifndef TQ_PLAN_CTAS_PER_SM
-#define TQ_PLAN_CTAS_PER_SM 32
-#endif
-    const uint64_t target = static_cast<uint64_t>(TQ_PLAN_CTAS_PER_SM) * (sm_count ? sm_count : 148u);
+    const uint64_t target = 32ull * (sm_count ? sm_count : 148u);
     const uint64_t want = items * max_context / target;
-    uint64_t chunk = 256;
+    uint64_t chunk = items >= (sm_count ? sm_count : 148u) ? 1024 : 256;
     while (chunk < want && chunk < 8192u) chunk <<= 1;
     while ((max_context + chunk - 1u) / chunk > 16u) chunk <<= 1;   // very long contexts
     if (chunk < block_size) chunk = block_size;

@@ -300,9 +300,11 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# dram bytes per algorithmic byte of the decode kernel from the committed ncu capture
-# (profiles/decode_partial_ragged.md); None until a capture exists.
-DECODE_TRAFFIC_BYTES_PER_ALGORITHMIC_BYTE = None
+# dram bytes (read + write) per algorithmic byte of the decode export kernel, from the ncu
+# capture of the small ragged case (profiles/decode_partial_kernel_small_ragged.md):
+# 224.51 MB + 6.39 MB over 223.39 MB. Traffic grows with the cache bytes read, so the full
+# launch is scaled by its algorithmic bytes.
+DECODE_TRAFFIC_BYTES_PER_ALGORITHMIC_BYTE = 1.0336
 
 
 def side_measurements(torch, tq, dev, args):
