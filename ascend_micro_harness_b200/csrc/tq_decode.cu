@@ -20,15 +20,18 @@
 //     the block table one tile ahead, so every KV byte crosses HBM once for all
 //     query rows of the GQA group;
 //   * tokens are the M dimension of both contractions. scores^T = K (16 tokens x d)
-//     times q_rot^T (d x 8 rows): the packed key row a thread copies out of shared
-//     memory IS its A fragment after in-register int4 -> bf16 expansion (mask,
-//     xor-magic, one packed subtract per two codes); no per-element scale is
-//     applied, the key scale multiplies the 16 score columns and the value scale
-//     folds into P, as the reference does;
-//   * acc^T = V^T (d channels x 16 tokens) times P^T: the value strip is already
-//     channel-major, so 16 bytes of it are the A fragment of two channels. P is
-//     carried as a bf16 hi + lo pair (two MMAs) so the accumulator keeps FP32-grade
-//     weights; P^T reaches its B-fragment layout with movmatrix.
+//     times q_rot^T (d x 8 rows) runs on the integer tensor path: a packed key word
+//     becomes two s8 operand registers (16 * code) with a shift and two masks, and
+//     q_rot, scaled per row by a power of two, is a fixed-point integer split into
+//     8-bit limbs (one MMA chain per limb). No per-element scale is applied: the key
+//     scale multiplies the 16 score columns and the value scale folds into P, as the
+//     reference does;
+//   * acc^T = V^T (d channels x 16 tokens) times P^T in f16 with FP32 accumulation:
+//     the value strip is already channel-major, so 16 bytes of it are the A fragment
+//     of two channels after in-register int4 -> f16 expansion (mask, xor-magic, one
+//     packed subtract per two codes). P is kept in [0, 1] by a running power-of-two
+//     normaliser of the value scales; the reference-contract entry carries it as a
+//     hi + lo pair (two MMAs). P^T reaches its B-fragment layout with movmatrix.
 #include <cuda_fp16.h>
 #include <stdexcept>
 #include <type_traits>
@@ -133,6 +136,26 @@ __device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32
         "{%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// D = A (16 tokens x 32 channels, s8) * B (32 channels x 8 query rows) + C on the integer
+// tensor path. B is one 8-bit limb of the fixed-point query: the top limb is signed, the
+// lower limbs unsigned. D and C are separate so a chain can start from a constant C.
+__device__ __forceinline__ void mma_s8_limb(bool b_signed, int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                            uint32_t a3, uint32_t b0, uint32_t b1, const int (&c)[4])
+{
+    if (b_signed)   // a constant after unrolling
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+            "{%8,%9}, {%10,%11,%12,%13};\n"
+            : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]),
+              "r"(c[3]));
+    else
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+            "{%8,%9}, {%10,%11,%12,%13};\n"
+            : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]),
+              "r"(c[3]));
 }
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a)
@@ -244,9 +267,15 @@ tq_decode_partial_kernel(const DecodeParams p)
 
     // ---- rotate the query rows once: each warp takes two rows through the FP32
     // ingress cascade, scales, rounds to bf16 (the pinned operand) and publishes it.
-    // The MMAs run in f16, so every row is then scaled by a power of two that puts its
-    // largest entry at 2^14 (exact for all entries within 2^-28 of the largest); the
-    // inverse goes into the per-row score factor together with softmax_scale * log2(e).
+    // The key contraction runs on the integer tensor path, so every row then becomes
+    // fixed point: its entries times the power of two that puts the largest below
+    // 2^(8 NL - 1), rounded to an integer of NL 8-bit limbs (NL = 2: 2^-16 of the row
+    // maximum, far inside the tolerance of the native path; NL = 3: 2^-24, FP32 grade,
+    // for the entry point that is checked against the reference's partial records).
+    // The inverse power goes into the per-row score factor together with
+    // softmax_scale * log2(e) and the 1/16 of the key operand (see compute_tile).
+    constexpr int NL = PRECISE ? 3 : 2;
+    int* qfix = reinterpret_cast<int*>(qbuf);
     {
         constexpr int K = D / 32;
         float sgn[K];
@@ -276,28 +305,42 @@ tq_decode_partial_kernel(const DecodeParams p)
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-            // 2^(14 - e) and 2^(e - 14) from the exponent field; a zero row keeps 1
+            // 2^(top - e) and 2^(e - top) from the exponent field of the row maximum,
+            // top = 8 NL - 2; a row below 1e-25 scores as zero
+            constexpr int kTop = 8 * NL - 2;
+            const bool tiny = !(am >= 1.0e-25f);
             const int e_bits = __float_as_int(am) & 0x7F800000;
-            const float up = am > 0.f ? __int_as_float((268 << 23) - e_bits) : 1.0f;
-            const float down = am > 0.f ? __int_as_float(e_bits - (14 << 23)) : 1.0f;
+            const float up = tiny ? 0.0f : __int_as_float(((254 + kTop) << 23) - e_bits);
+            const float down = tiny ? 1.0f : __int_as_float(e_bits - (kTop << 23));
 #pragma unroll
-            for (int i = 0; i < K; ++i) qbuf[row * D + lane * K + i] = v[i] * up;
-            if (lane == 0) row_unscale[row] = down * p.softmax_scale * kLog2e;
+            for (int i = 0; i < K; ++i) qfix[row * D + lane * K + i] = __float2int_rn(v[i] * up);
+            if (lane == 0) row_unscale[row] = down * 0.0625f * p.softmax_scale * kLog2e;
         }
     }
     if (empty) return;
     __syncthreads();
 
-    // ---- q_rot^T as f16 B fragments, in the contraction order the key words deliver.
-    uint32_t bq[2 * WPT][2];
+    // ---- limbs of q_rot^T as B fragments of the integer MMA. Word wi of a key row holds
+    // channels qd*(D/4) + wi*8 + n, n = 0..7: the even n feed contraction slots qd*4 + n/2
+    // (b0), the odd n slots 16 + qd*4 + n/2 (b1).
+    uint32_t bq[NL][WPT][2];
 #pragma unroll
-    for (int wi = 0; wi < WPT; ++wi)
+    for (int wi = 0; wi < WPT; ++wi) {
+        const int* qr = qfix + r * D + qd * (D / 4) + wi * 8;
+        int qv[8];
 #pragma unroll
-        for (int kh = 0; kh < 2; ++kh) {
-            const float* qr = qbuf + r * D + qd * (D / 4) + wi * 8 + 2 * kh;
-            bq[wi * 2 + kh][0] = pack_f16x2(qr[0], qr[4]);
-            bq[wi * 2 + kh][1] = pack_f16x2(qr[1], qr[5]);
-        }
+        for (int n = 0; n < 8; ++n) qv[n] = qr[n];
+#pragma unroll
+        for (int l = 0; l < NL; ++l)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t w = 0;
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    w |= ((static_cast<uint32_t>(qv[2 * e + h]) >> (8 * l)) & 0xFFu) << (8 * e);
+                bq[l][wi][h] = w;
+            }
+    }
     // scores are kept as raw * key_scale; the per-row factor enters inside the exponent
     const float rfac[2] = {row_unscale[qd * 2], row_unscale[qd * 2 + 1]};
     __syncthreads();  // everyone is done with qbuf: the ring may overwrite it
@@ -395,6 +438,18 @@ tq_decode_partial_kernel(const DecodeParams p)
     // byte-permute selector that brings this thread's value-token pairs to bits 0-7 / 16-23
     const uint32_t vsel = qd == 0 ? 0x3210u : qd == 1 ? 0x4321u : qd == 2 ? 0x7654u : 0x0765u;
 
+    // Integer accumulators of one limb stay below 2^22 in magnitude at d = 128
+    // (128 channels x |16 code| <= 128 x limb <= 255), so a chain that starts at the bit
+    // pattern of 1.5 * 2^23 ends, read as a float, at 12582912 + sum exactly and one FP32
+    // subtract recovers the sum; d = 256 can exceed that range and converts instead.
+    constexpr bool kBiasedAcc = D == 128;
+    const int cinit[4] = {kBiasedAcc ? 0x4B400000 : 0, kBiasedAcc ? 0x4B400000 : 0,
+                          kBiasedAcc ? 0x4B400000 : 0, kBiasedAcc ? 0x4B400000 : 0};
+    auto limb_value = [](int v) {
+        if constexpr (kBiasedAcc) return __int_as_float(v) - 12582912.0f;
+        else return __int2float_rn(v);
+    };
+
     // One tile: scores^T for its strips, the online-softmax update, then acc^T += V^T P^T.
     // TAIL tiles reach past the split's strips or past the live tokens and mask by
     // overwriting (a dead slot's scale may be a NaN); full tiles carry no masking code.
@@ -408,7 +463,9 @@ tq_decode_partial_kernel(const DecodeParams p)
         for (int ts = 0; ts < kTileStrips; ++ts) {
             const uint8_t* ss = st + ts * L::kStripStage;
             const float* scales = reinterpret_cast<const float*>(ss + 2 * L::kStripBytes);
-            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            // A operand: 16 * code as a signed byte. The odd channels of a word are its
+            // high nibbles already in place (mask), the even ones move up by four bits.
+            int ci[NL][4];
 #pragma unroll
             for (int w4 = 0; w4 < WPT / 4; ++w4) {
                 const uint4 lo = *reinterpret_cast<const uint4*>(ss + koff_lo[w4]);
@@ -417,12 +474,25 @@ tq_decode_partial_kernel(const DecodeParams p)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int wi = w4 * 4 + k;
-                    const uint32_t xl8 = wl[k] >> 8, xh8 = wh[k] >> 8;
-                    mma_f16_16816(c, dq_lo(wl[k]), dq_lo(wh[k]), dq_hi(wl[k]), dq_hi(wh[k]),
-                                  bq[wi * 2][0], bq[wi * 2][1]);
-                    mma_f16_16816(c, dq_lo(xl8), dq_lo(xh8), dq_hi(xl8), dq_hi(xh8),
-                                  bq[wi * 2 + 1][0], bq[wi * 2 + 1][1]);
+                    const uint32_t a0 = (wl[k] << 4) & 0xF0F0F0F0u, a1 = (wh[k] << 4) & 0xF0F0F0F0u;
+                    const uint32_t a2 = wl[k] & 0xF0F0F0F0u, a3 = wh[k] & 0xF0F0F0F0u;
+#pragma unroll
+                    for (int l = 0; l < NL; ++l) {
+                        if (wi == 0)
+                            mma_s8_limb(l == NL - 1, ci[l], a0, a1, a2, a3, bq[l][wi][0], bq[l][wi][1], cinit);
+                        else
+                            mma_s8_limb(l == NL - 1, ci[l], a0, a1, a2, a3, bq[l][wi][0], bq[l][wi][1], ci[l]);
+                    }
                 }
+            }
+            // limbs -> one float per score: sum_l 256^l * c_l
+            float c[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float f = limb_value(ci[NL - 1][i]);
+#pragma unroll
+                for (int l = NL - 2; l >= 0; --l) f = fmaf(f, 256.0f, limb_value(ci[l][i]));
+                c[i] = f;
             }
             const float ks_lo = scales[tok_lo], ks_hi = scales[tok_hi];
             vs[ts][0] = scales[kStrip + tok_lo];

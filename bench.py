@@ -272,7 +272,7 @@ def run_ours(args):
             "metric": "splitk_4bit_decode_kv_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int4 codes, f16 x f16 -> f32", "data": "synthetic",
+            "vs_baseline": None, "dtype": "int4 codes; QK s8 x s8 -> s32, PV f16 x f16 -> f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "q_heads": HQ, "kv_heads": HKV,
                        "head_dim": D, "page_tokens": S, "splits": int(splits),
                        "kv_bytes_per_gpu": my_bytes,
