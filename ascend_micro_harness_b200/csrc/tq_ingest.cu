@@ -52,6 +52,10 @@ struct IngestParams {
 
 constexpr int kIngestWarps = 4;
 constexpr int kIngestCtasPerSm = 4;
+// Floats per quad position in the shared sign table: d/4 signs plus two of padding, so
+// that the four positions a warp reads at once sit in different banks.
+template <int D>
+constexpr int kSignPitchOf = D / 4 + 2;
 
 // n / d for any 32-bit n with the precomputed (mul, shift) of divisor d >= 2
 // (round-up method: mul = floor(2^32 (2^l - d) / d) + 1, l = ceil(log2 d)).
@@ -124,6 +128,7 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
     constexpr int G = D / kGroup;
     constexpr int kPageWords = kStrip * D / 8;
     constexpr int kPiece = BF16 ? 16 : 8;
+    constexpr int kSignPitch = kSignPitchOf<D>;
     const int r = lane >> 2, qd = lane & 3;
     const PanelId id = panel_of(p, chunk);
 
@@ -187,7 +192,7 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
         float2 sg[G];
 #pragma unroll
         for (int g = 0; g < G; ++g)
-            sg[g] = *reinterpret_cast<const float2*>(sgn_s + qd * (G * 8) + g * 8 + ep * 2);
+            sg[g] = *reinterpret_cast<const float2*>(sgn_s + qd * kSignPitch + g * 8 + ep * 2);
 #pragma unroll
         for (int tt = 0; tt < 2; ++tt) {
             float2 x[G];
@@ -276,8 +281,11 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
                                     __float_as_uint(fminf(r0.x, kMagicTop));
                 const uint32_t b1 = __float_as_uint(fminf(r1.y, kMagicTop)) * 16u +
                                     __float_as_uint(fminf(r0.y, kMagicTop));
-                sb[(g * kGroup + qd * 8 + ep * 2) * 8 + r] = static_cast<uint8_t>(b0);
-                sb[(g * kGroup + qd * 8 + ep * 2 + 1) * 8 + r] = static_cast<uint8_t>(b1);
+                // channels c, c+1 fill one 16-byte unit (index c/2); units of quad positions
+                // qd and qd^2 would share banks, so bit 0 of the unit index takes qd's bit 1
+                const int unit = ((g * kGroup + qd * 8 + ep * 2) >> 1) ^ (qd >> 1);
+                sb[unit * 16 + r] = static_cast<uint8_t>(b0);
+                sb[unit * 16 + 8 + r] = static_cast<uint8_t>(b1);
             }
     }
     __syncwarp();
@@ -297,7 +305,7 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
             const int row = unit / (D / 32), chunk16 = unit % (D / 32);
             v = s4[row * (D / 32) + (chunk16 ^ ((row >> 1) & 3))];
         } else {
-            v = s4[unit];
+            v = s4[unit ^ ((unit >> 3) & 1)];   // undo the store swizzle
             v.x ^= 0x88888888u;  // u -> two's-complement nibble
             v.y ^= 0x88888888u;
             v.z ^= 0x88888888u;
@@ -334,7 +342,8 @@ tq_ingest_kernel(const IngestParams p)
     // sign diagonal per quad position: sgn_s[qd][g*8 + e] for channel g*32 + qd*8 + e
     for (int i = threadIdx.x; i < 4 * G * 8; i += blockDim.x) {
         const int q = i / (G * 8), k = i % (G * 8);
-        sgn_s[i] = sign_is_negative(p.signs, p.sign_source, (k / 8) * kGroup + q * 8 + (k % 8)) ? -1.0f : 1.0f;
+        sgn_s[q * kSignPitchOf<D> + k] =
+            sign_is_negative(p.signs, p.sign_source, (k / 8) * kGroup + q * 8 + (k % 8)) ? -1.0f : 1.0f;
     }
 
     // +-1 B fragments of H32, once per thread. Column n of tile j is output channel
@@ -398,7 +407,7 @@ template <int D, bool BF16>
 static cudaError_t launch_ingest(cudaStream_t stream, const IngestParams& p)
 {
     constexpr int kInBytes = kStrip * D * (BF16 ? 2 : 1);
-    constexpr int kSmem = kIngestWarps * (2 * kInBytes + kStrip * D / 2) + 4 * (D / kGroup) * 8 * 4;
+    constexpr int kSmem = kIngestWarps * (2 * kInBytes + kStrip * D / 2) + 4 * kSignPitchOf<D> * 4;
     uint32_t blocks = (p.chunks + kIngestWarps - 1) / kIngestWarps;
     if (blocks == 0) return cudaSuccess;
     int dev = 0, sms = 148;
