@@ -512,16 +512,19 @@ tq_decode_partial_kernel(const DecodeParams p)
             mx[1] = fmaxf(mx[1], fmaxf(sc[ts][1], sc[ts][3]));
             vmax = fmaxf(vmax, fmaxf(fabsf(vs[ts][0]), fabsf(vs[ts][1])));
         }
-#pragma unroll
-        for (int o = 4; o <= 16; o <<= 1) {
-            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
-            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
-            vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
-        }
-        // -- online softmax update; the accumulator is rescaled only when something moved.
-        // rfac > 0, so the maximum can be taken before the per-row factor is applied.
+        // -- online softmax update. m_run and vnorm are uniform over the lanes that share
+        // them, so "did anything grow" can be asked of every lane's own four scores first;
+        // only a tile that raises a row maximum or the value normaliser pays for the
+        // reductions and the rescale of the accumulator (rfac > 0: the maximum can be taken
+        // before the per-row factor is applied).
         const bool grow = mx[0] > m_run[0] || mx[1] > m_run[1] || vmax > vnorm;
         if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+            for (int o = 4; o <= 16; o <<= 1) {
+                mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+                mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+                vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+            }
             float alpha[2];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
