@@ -41,9 +41,13 @@
 namespace tq {
 
 constexpr int kDecWarps = 4;
-constexpr int kDecCtasPerSm = 4;
 constexpr int kTileStrips = 2;   // strips per pipeline stage of one warp
-constexpr int kStages = 3;
+#ifndef TQ_D256_STAGES
+#define TQ_D256_STAGES 2
+#endif
+#ifndef TQ_D256_CTAS
+#define TQ_D256_CTAS 3
+#endif
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -71,6 +75,11 @@ struct DecodeParams {
 // quarter-warp reads (tokens t and t+4) fall into different banks.
 template <int D>
 struct DecodeSmem {
+    // Ring depth and resident CTAs per SM. d = 128: three stages of 2 strips for each of four
+    // warps are 51 KiB, four CTAs fit and the kernel stays under 128 registers. d = 256 doubles
+    // both the strips and the accumulator registers: two stages, three CTAs of up to 168 registers.
+    static constexpr int kStages = D == 128 ? 3 : TQ_D256_STAGES;
+    static constexpr int kCtasPerSm = D == 128 ? 4 : TQ_D256_CTAS;
     static constexpr int kRowBytes = D / 2;
     static constexpr int kStripBytes = kStrip * D / 2;
     static constexpr int kStripStage = 2 * kStripBytes + 2 * kStrip * 4;   // K, V, both scale runs
@@ -190,10 +199,11 @@ __device__ __forceinline__ int token_row_lo(int i) { return ((i >> 2) << 3) + ((
 __device__ __forceinline__ int token_row_hi(int i) { return token_row_lo(i) + 1; }
 
 template <int D, bool PRECISE>
-__global__ void __launch_bounds__(kDecWarps * 32, kDecCtasPerSm)
+__global__ void __launch_bounds__(kDecWarps * 32, DecodeSmem<D>::kCtasPerSm)
 tq_decode_partial_kernel(const DecodeParams p)
 {
     using L = DecodeSmem<D>;
+    constexpr int kStages = L::kStages;
     constexpr int kRecord = 16 + D;
     constexpr int MT = D / 16;    // 16-channel m-tiles of the value contraction
     constexpr int WPT = D / 32;   // packed words per thread per key row

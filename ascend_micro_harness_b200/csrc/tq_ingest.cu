@@ -51,7 +51,13 @@ struct IngestParams {
 };
 
 constexpr int kIngestWarps = 4;
-constexpr int kIngestCtasPerSm = 4;
+#ifndef TQ_D256_INGEST_CTAS
+#define TQ_D256_INGEST_CTAS 3
+#endif
+// Resident CTAs per SM: a thread holds a 16 x d / 32 slice of the rotated panel in
+// registers (64 floats at d = 128, 128 at d = 256), which fixes the register budget.
+template <int D>
+constexpr int kIngestCtasPerSm = D == 128 ? 4 : TQ_D256_INGEST_CTAS;
 // Floats per quad position in the shared sign table: d/4 signs plus two of padding, so
 // that the four positions a warp reads at once sit in different banks.
 template <int D>
@@ -325,7 +331,7 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
 // Persistent: every warp walks panels warp_global, warp_global + warps_total, ...
 // with the next panel's bytes in flight while the current one is processed.
 template <int D, bool BF16>
-__global__ void __launch_bounds__(kIngestWarps * 32, kIngestCtasPerSm)
+__global__ void __launch_bounds__(kIngestWarps * 32, kIngestCtasPerSm<D>)
 tq_ingest_kernel(const IngestParams p)
 {
     constexpr int G = D / kGroup;
@@ -420,7 +426,7 @@ static cudaError_t launch_ingest(cudaStream_t stream, const IngestParams& p)
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    const uint32_t resident = static_cast<uint32_t>(sms) * kIngestCtasPerSm;
+    const uint32_t resident = static_cast<uint32_t>(sms) * kIngestCtasPerSm<D>;
     if (blocks > resident) blocks = resident;  // persistent: one resident wave
     tq_ingest_kernel<D, BF16><<<blocks, kIngestWarps * 32, kSmem, stream>>>(p);
     return cudaGetLastError();
