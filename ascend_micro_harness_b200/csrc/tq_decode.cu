@@ -86,7 +86,8 @@ struct DecodeSmem {
     static constexpr int kStageBytes = kTileStrips * kStripStage;
     static constexpr int kRingBytes = kDecWarps * kStages * kStageBytes;
     static constexpr int kQBytes = 2 * 8 * D * 4;
-    static constexpr int kMergeBytes = kDecWarps * 8 * (D + 2) * 4;
+    static constexpr int kMergePitch = D + 4;   // floats per merged row: {m, l, acc[d]} + pad, see the epilogue
+    static constexpr int kMergeBytes = kDecWarps * 8 * kMergePitch * 4;
     static constexpr int kBody = kRingBytes > kQBytes ? (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes)
                                                       : (kQBytes > kMergeBytes ? kQBytes : kMergeBytes);
     static constexpr int kTotal = kBody;
@@ -179,6 +180,13 @@ __device__ __forceinline__ float ex2f(float x)
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
 }
 
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi)
@@ -518,9 +526,9 @@ tq_decode_partial_kernel(const DecodeParams p)
                 if (!live[ts][0]) { sc[ts][0] = sc[ts][1] = kMaskedScore; vs[ts][0] = 0.f; }
                 if (!live[ts][1]) { sc[ts][2] = sc[ts][3] = kMaskedScore; vs[ts][1] = 0.f; }
             }
-            mx[0] = fmaxf(mx[0], fmaxf(sc[ts][0], sc[ts][2]));
-            mx[1] = fmaxf(mx[1], fmaxf(sc[ts][1], sc[ts][3]));
-            vmax = fmaxf(vmax, fmaxf(fabsf(vs[ts][0]), fabsf(vs[ts][1])));
+            mx[0] = max3(mx[0], sc[ts][0], sc[ts][2]);
+            mx[1] = max3(mx[1], sc[ts][1], sc[ts][3]);
+            vmax = max3(vmax, fabsf(vs[ts][0]), fabsf(vs[ts][1]));
         }
         // -- online softmax update. m_run and vnorm are uniform over the lanes that share
         // them, so "did anything grow" can be asked of every lane's own four scores first;
@@ -625,20 +633,23 @@ tq_decode_partial_kernel(const DecodeParams p)
         l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 16);
     }
     __syncthreads();  // every warp is done with its ring; reuse it
-    float* merge = reinterpret_cast<float*>(ring) + warp * 8 * (D + 2);
+    // Row pitch d + 4 floats: a lane stores its two adjacent channels of a row as one
+    // 8-byte word, and with this pitch the 16 lanes of a half-warp hit 16 different banks pairs.
+    constexpr int kPitch = L::kMergePitch;
+    float* merge = reinterpret_cast<float*>(ring) + warp * 8 * kPitch;
     if (r == 0) {
-        merge[(qd * 2 + 0) * (D + 2) + 0] = m_run[0];
-        merge[(qd * 2 + 0) * (D + 2) + 1] = l_run[0];
-        merge[(qd * 2 + 1) * (D + 2) + 0] = m_run[1];
-        merge[(qd * 2 + 1) * (D + 2) + 1] = l_run[1];
+        merge[(qd * 2 + 0) * kPitch + 0] = m_run[0];
+        merge[(qd * 2 + 0) * kPitch + 1] = l_run[0];
+        merge[(qd * 2 + 1) * kPitch + 0] = m_run[1];
+        merge[(qd * 2 + 1) * kPitch + 1] = l_run[1];
     }
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
         const int ch = mt * 16 + 2 * r;
-        merge[(qd * 2 + 0) * (D + 2) + 2 + ch] = acc[mt][0] * vnorm;
-        merge[(qd * 2 + 1) * (D + 2) + 2 + ch] = acc[mt][1] * vnorm;
-        merge[(qd * 2 + 0) * (D + 2) + 2 + ch + 1] = acc[mt][2] * vnorm;
-        merge[(qd * 2 + 1) * (D + 2) + 2 + ch + 1] = acc[mt][3] * vnorm;
+        *reinterpret_cast<float2*>(merge + (qd * 2 + 0) * kPitch + 2 + ch) =
+            make_float2(acc[mt][0] * vnorm, acc[mt][2] * vnorm);
+        *reinterpret_cast<float2*>(merge + (qd * 2 + 1) * kPitch + 2 + ch) =
+            make_float2(acc[mt][1] * vnorm, acc[mt][3] * vnorm);
     }
     __syncthreads();
     // Inside the kernel m is in units of raw * key_scale; row_unscale turns a difference
@@ -649,7 +660,7 @@ tq_decode_partial_kernel(const DecodeParams p)
         const float rf = row_unscale[q];
         float mm = kMaskedScore;
 #pragma unroll
-        for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, mg[(w * 8 + q) * (D + 2)]);
+        for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, mg[(w * 8 + q) * kPitch]);
         float out;
         if (c < 8) {
             out = mm > -1.0e37f ? mm * rf * kLn2 : kMaskedScore;
@@ -658,7 +669,7 @@ tq_decode_partial_kernel(const DecodeParams p)
             out = 0.f;
 #pragma unroll
             for (int w = 0; w < kDecWarps; ++w) {
-                const float* rw = mg + (w * 8 + q) * (D + 2);
+                const float* rw = mg + (w * 8 + q) * kPitch;
                 out += rw[src] * ex2f((rw[0] - mm) * rf);
             }
         }

@@ -123,6 +123,14 @@ __device__ __forceinline__ int32_t stage_panel(const IngestParams& p, uint32_t c
 
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 
+// max(a, |b|, |c|) in one three-input instruction.
+__device__ __forceinline__ float max3_abs(float a, float b, float c)
+{
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(fabsf(b)), "f"(fabsf(c)));
+    return r;
+}
+
 // Rotate, quantise, pack and store one panel whose fragments sit in `in` (this
 // thread's own bytes) and whose slot run is `slot`.
 template <int D, bool BF16>
@@ -221,7 +229,7 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
 #pragma unroll
             for (int g = 0; g < G; ++g) {
                 y[tt][g][ep] = x[g];
-                amax[tt] = fmaxf(amax[tt], fmaxf(fabsf(x[g].x), fabsf(x[g].y)));
+                amax[tt] = max3_abs(amax[tt], x[g].x, x[g].y);
             }
         }
     }
