@@ -699,16 +699,27 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
     const int c = threadIdx.x;
     const float* base = p.workspace + (static_cast<size_t>(item) * p.splits * p.rows_stride + row) * kRecord;
     const size_t split_stride = static_cast<size_t>(p.rows_stride) * kRecord;
+    // All records are fetched before the first one is merged, so the loads overlap instead
+    // of forming a chain of dependent round trips to L2 (at most 16 splits).
+    float mk[16], lk[16], ak[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k)
+        if (static_cast<uint32_t>(k) < p.splits) {
+            const float* rec = base + k * split_stride;
+            mk[k] = rec[0];
+            lk[k] = rec[8];
+            ak[k] = rec[16 + c];
+        }
     float m = kMaskedScore, l = 0.f, a = 0.f;
-    for (uint32_t k = 0; k < p.splits; ++k) {
-        const float* rec = base + k * split_stride;
-        const float mk = rec[0], lk = rec[8], ak = rec[16 + c];
-        const float mn = fmaxf(m, mk);
-        const float wa = ex2f((m - mn) * kLog2e), wb = ex2f((mk - mn) * kLog2e);
-        l = l * wa + lk * wb;
-        a = a * wa + ak * wb;
-        m = mn;
-    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k)
+        if (static_cast<uint32_t>(k) < p.splits) {
+            const float mn = fmaxf(m, mk[k]);
+            const float wa = ex2f((m - mn) * kLog2e), wb = ex2f((mk[k] - mn) * kLog2e);
+            l = l * wa + lk[k] * wb;
+            a = a * wa + ak[k] * wb;
+            m = mn;
+        }
     float v = l > 0.f ? a / l : 0.f;
     if (p.output_stage != TQ_OUT_ROTATED) {
         int cur = 0;

@@ -60,24 +60,37 @@ __global__ void __launch_bounds__(kScatterWarps * 32) tq_scatter_kernel(const Sc
                 continue;
             }
             const size_t row = (static_cast<size_t>(tok) * p.H + head) * D + lane * K;
+            const size_t head_base = (static_cast<size_t>(page) * p.H + head) * p.S * (D / 2);
+            // Everything the token needs from memory is requested up front: both activation
+            // rows and the value-strip bytes whose other nibble has to survive.
+            uint32_t raw[2][K / 2];
 #pragma unroll
             for (int plane = 0; plane < 2; ++plane) {
                 const uint16_t* src = (plane == 0 ? p.key : p.value) + row;
-                float v[K];
                 if constexpr (K == 4) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(src);
-                    v[0] = __uint_as_float(raw.x << 16);
-                    v[1] = __uint_as_float(raw.x & 0xFFFF0000u);
-                    v[2] = __uint_as_float(raw.y << 16);
-                    v[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+                    const uint2 w = *reinterpret_cast<const uint2*>(src);
+                    raw[plane][0] = w.x;
+                    raw[plane][1] = w.y;
                 } else {
-                    const uint4 raw = *reinterpret_cast<const uint4*>(src);
-                    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+                    const uint4 w = *reinterpret_cast<const uint4*>(src);
+                    raw[plane][0] = w.x;
+                    raw[plane][1] = w.y;
+                    raw[plane][2] = w.z;
+                    raw[plane][3] = w.w;
+                }
+            }
+            uint8_t* strip = p.value_cache + head_base + static_cast<size_t>(tib / kStrip) * (kStrip * D / 2);
+            const uint32_t t = tib % kStrip;
+            uint32_t old_bytes[K];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        v[2 * i] = __uint_as_float(w[i] << 16);
-                        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-                    }
+            for (int i = 0; i < K; ++i) old_bytes[i] = strip[(lane * K + i) * 8 + t / 2];
+#pragma unroll
+            for (int plane = 0; plane < 2; ++plane) {
+                float v[K];
+#pragma unroll
+                for (int i = 0; i < K / 2; ++i) {
+                    v[2 * i] = __uint_as_float(raw[plane][i] << 16);
+                    v[2 * i + 1] = __uint_as_float(raw[plane][i] & 0xFFFF0000u);
                 }
                 cascade_ingress<K>(v, sgn, lane);
 
@@ -99,20 +112,17 @@ __global__ void __launch_bounds__(kScatterWarps * 32) tq_scatter_kernel(const Sc
                     const int q = __float2int_rn(fminf(v[i] * inv, 7.0f));
                     codes |= (static_cast<uint32_t>(q) & 0xFu) << (4 * i);
                 }
-                const size_t head_base = (static_cast<size_t>(page) * p.H + head) * p.S * (D / 2);
                 if (plane == 0) {
                     uint8_t* dst = p.key_cache + head_base + static_cast<size_t>(tib) * (D / 2) + lane * (K / 2);
                     if constexpr (K == 4) *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(codes);
                     else *reinterpret_cast<uint32_t*>(dst) = codes;
                 } else {
-                    uint8_t* strip = p.value_cache + head_base + static_cast<size_t>(tib / kStrip) * (kStrip * D / 2);
-                    const uint32_t t = tib % kStrip;
 #pragma unroll
                     for (int i = 0; i < K; ++i) {
-                        uint8_t* b = strip + (lane * K + i) * 8 + t / 2;
                         const uint32_t nib = (codes >> (4 * i)) & 0xFu;
-                        const uint32_t old = *b;
-                        *b = static_cast<uint8_t>((t & 1u) ? ((old & 0x0Fu) | (nib << 4)) : ((old & 0xF0u) | nib));
+                        const uint32_t old = old_bytes[i];
+                        strip[(lane * K + i) * 8 + t / 2] =
+                            static_cast<uint8_t>((t & 1u) ? ((old & 0x0Fu) | (nib << 4)) : ((old & 0xF0u) | nib));
                     }
                 }
                 if (lane == 0)
