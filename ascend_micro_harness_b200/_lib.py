@@ -16,6 +16,8 @@ SIGNATURES = {
     "tq_status_string": (C.c_char_p, [C.c_int]),
     "tq_reshape_and_cache": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
                                        u32, u32, f32, vp]),
+    "tq_reshape_and_cache_warp_mma": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
+                                       u32, u32, f32, vp]),
     "tq_reshape_scatter": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
                                      u32, u32, f32, vp]),
     "tq_decode_splitk": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,

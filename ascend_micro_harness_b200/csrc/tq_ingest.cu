@@ -30,25 +30,9 @@
 //     memory and leaves as 128-bit stores of the whole contiguous (page, head) block.
 #include <type_traits>
 
-#include "tq_common.cuh"
+#include "tq_ingest.cuh"
 
 namespace tq {
-
-struct IngestParams {
-    const void* key;
-    const void* value;
-    uint8_t* key_cache;
-    uint8_t* value_cache;
-    float* scale_cache;
-    const int32_t* slots;
-    const void* signs;
-    uint32_t sign_source;
-    uint32_t num_strips, H, S, P;
-    uint32_t chunks;                 // num_strips * 2 * H, below 2^31
-    uint32_t div_mul, div_shift;     // exact division by 2H: see fast_div
-    float inv_sqrt_len;
-    uint32_t* status;
-};
 
 constexpr int kIngestWarps = 4;
 #ifndef TQ_D256_INGEST_CTAS
@@ -62,14 +46,6 @@ constexpr int kIngestCtasPerSm = D == 128 ? 4 : TQ_D256_INGEST_CTAS;
 // that the four positions a warp reads at once sit in different banks.
 template <int D>
 constexpr int kSignPitchOf = D / 4 + 2;
-
-// n / d for any 32-bit n with the precomputed (mul, shift) of divisor d >= 2
-// (round-up method: mul = floor(2^32 (2^l - d) / d) + 1, l = ceil(log2 d)).
-__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shift)
-{
-    const uint32_t t = __umulhi(mul, n);
-    return (t + ((n - t) >> 1)) >> shift;
-}
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src)
 {
@@ -442,12 +418,15 @@ static cudaError_t launch_ingest(cudaStream_t stream, const IngestParams& p)
 
 }  // namespace tq
 
-extern "C" int tq_reshape_and_cache(void* stream, const void* key, const void* value,
-                                    int8_t* key_cache, int8_t* value_cache, float* scale_cache,
-                                    const int32_t* slot_mapping, const void* signs,
-                                    uint32_t sign_source, uint32_t in_dtype, uint32_t num_tokens,
-                                    uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
-                                    uint32_t num_blocks, float inv_sqrt_len, uint32_t* status)
+// Head size 128 goes to the tcgen05 writer unless `warp_mma_only`; head size 256 and the
+// explicit warp-MMA entry use the kernel in this file.
+static int reshape_and_cache(void* stream, const void* key, const void* value,
+                             int8_t* key_cache, int8_t* value_cache, float* scale_cache,
+                             const int32_t* slot_mapping, const void* signs,
+                             uint32_t sign_source, uint32_t in_dtype, uint32_t num_tokens,
+                             uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                             uint32_t num_blocks, float inv_sqrt_len, uint32_t* status,
+                             bool warp_mma_only)
 {
     using namespace tq;
     if (num_kv_heads == 0 || num_blocks == 0 || block_size == 0 || block_size % kStrip != 0 ||
@@ -495,9 +474,37 @@ extern "C" int tq_reshape_and_cache(void* stream, const void* key, const void* v
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t err;
-    if (head_size == 128)
+    if (head_size == 128 && !warp_mma_only)
+        err = launch_ingest_umma(s, p, in_dtype == TQ_IN_BF16);
+    else if (head_size == 128)
         err = in_dtype == TQ_IN_BF16 ? launch_ingest<128, true>(s, p) : launch_ingest<128, false>(s, p);
     else
         err = in_dtype == TQ_IN_BF16 ? launch_ingest<256, true>(s, p) : launch_ingest<256, false>(s, p);
     return err == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
+
+extern "C" int tq_reshape_and_cache(void* stream, const void* key, const void* value,
+                                    int8_t* key_cache, int8_t* value_cache, float* scale_cache,
+                                    const int32_t* slot_mapping, const void* signs,
+                                    uint32_t sign_source, uint32_t in_dtype, uint32_t num_tokens,
+                                    uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                                    uint32_t num_blocks, float inv_sqrt_len, uint32_t* status)
+{
+    return reshape_and_cache(stream, key, value, key_cache, value_cache, scale_cache, slot_mapping,
+                             signs, sign_source, in_dtype, num_tokens, num_kv_heads, head_size,
+                             block_size, num_blocks, inv_sqrt_len, status, false);
+}
+
+extern "C" int tq_reshape_and_cache_warp_mma(void* stream, const void* key, const void* value,
+                                             int8_t* key_cache, int8_t* value_cache,
+                                             float* scale_cache, const int32_t* slot_mapping,
+                                             const void* signs, uint32_t sign_source,
+                                             uint32_t in_dtype, uint32_t num_tokens,
+                                             uint32_t num_kv_heads, uint32_t head_size,
+                                             uint32_t block_size, uint32_t num_blocks,
+                                             float inv_sqrt_len, uint32_t* status)
+{
+    return reshape_and_cache(stream, key, value, key_cache, value_cache, scale_cache, slot_mapping,
+                             signs, sign_source, in_dtype, num_tokens, num_kv_heads, head_size,
+                             block_size, num_blocks, inv_sqrt_len, status, true);
 }

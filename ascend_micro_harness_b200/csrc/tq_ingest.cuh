@@ -1,0 +1,35 @@
+// Shared between the two aligned-writer kernels (warp-MMA and tcgen05).
+#pragma once
+
+#include "tq_common.cuh"
+
+namespace tq {
+
+struct IngestParams {
+    const void* key;
+    const void* value;
+    uint8_t* key_cache;
+    uint8_t* value_cache;
+    float* scale_cache;
+    const int32_t* slots;
+    const void* signs;
+    uint32_t sign_source;
+    uint32_t num_strips, H, S, P;
+    uint32_t chunks;                 // num_strips * 2 * H, below 2^31
+    uint32_t div_mul, div_shift;     // exact division by 2H: see fast_div
+    float inv_sqrt_len;
+    uint32_t* status;
+};
+
+// n / d for any 32-bit n with the precomputed (mul, shift) of divisor d >= 2
+// (round-up method: mul = floor(2^32 (2^l - d) / d) + 1, l = ceil(log2 d)).
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shift)
+{
+    const uint32_t t = __umulhi(mul, n);
+    return (t + ((n - t) >> 1)) >> shift;
+}
+
+// The tcgen05 writer for head size 128 (tq_ingest_umma.cu). `bf16` selects the element type.
+cudaError_t launch_ingest_umma(cudaStream_t stream, const IngestParams& p, bool bf16);
+
+}  // namespace tq

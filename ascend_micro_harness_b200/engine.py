@@ -37,15 +37,17 @@ def _check(status, what):
 
 def reshape_and_cache(key, value, key_cache, value_cache, scale_cache, slot_mapping, signs, *,
                       num_kv_heads, head_size, block_size, num_blocks, inv_sqrt_len,
-                      sign_source=SIGNS_F32, status=None, stream=None):
+                      sign_source=SIGNS_F32, status=None, stream=None, warp_mma=False):
     """Aligned writer (reference: launch_turboquant_reshape_and_cache_{a8,bf16}).
-    key/value: [T, H*d] int8 or bfloat16."""
+    key/value: [T, H*d] int8 or bfloat16. Head size 128 runs on the tcgen05 kernel;
+    warp_mma=True selects the warp-MMA kernel (the one head size 256 always uses)."""
     lib = load_library()
     in_dtype = {torch.int8: 0, torch.bfloat16: 1}[key.dtype]
     if value.dtype != key.dtype:
         raise ValueError("key and value must share a dtype")
     num_tokens = key.numel() // (num_kv_heads * head_size)
-    _check(lib.tq_reshape_and_cache(
+    fn = lib.tq_reshape_and_cache_warp_mma if warp_mma else lib.tq_reshape_and_cache
+    _check(fn(
         _stream(stream), _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache),
         _ptr(scale_cache), _ptr(slot_mapping), _ptr(signs), sign_source, in_dtype, num_tokens,
         num_kv_heads, head_size, block_size, num_blocks, inv_sqrt_len, _ptr(status)),

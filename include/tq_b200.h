@@ -89,6 +89,16 @@ int tq_reshape_and_cache(void* stream, const void* key, const void* value, int8_
                          uint32_t block_size, uint32_t num_blocks, float inv_sqrt_len,
                          uint32_t* status);
 
+/* tq_reshape_and_cache serves head size 128 with the tcgen05 kernel and head size 256
+ * with the warp-MMA kernel. This entry forces the warp-MMA kernel for either head size:
+ * same arguments, same bytes out (kept for comparison and as the fallback build target). */
+int tq_reshape_and_cache_warp_mma(void* stream, const void* key, const void* value,
+                                  int8_t* key_cache, int8_t* value_cache, float* scale_cache,
+                                  const int32_t* slot_mapping, const void* signs,
+                                  uint32_t sign_source, uint32_t in_dtype, uint32_t num_tokens,
+                                  uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                                  uint32_t num_blocks, float inv_sqrt_len, uint32_t* status);
+
 /* Scatter writer: 1..16 bf16 tokens per request at arbitrary slots, key rows
  * written whole, value strips read-modify-written so unowned nibbles survive.
  * Replaces launch_turboquant_reshape_scatter_aiv

@@ -8,6 +8,16 @@ from tests import helpers as hp
 pytestmark = pytest.mark.gpu
 
 CANARY = 0xAA
+WARP_MMA = False
+
+
+@pytest.fixture(params=["tcgen05", "warp_mma"], autouse=True)
+def ingest_kernel(request):
+    """Every case runs on both aligned-writer kernels: the tcgen05 one (head size 128) and
+    the warp-MMA one (any head size, forced through its own entry point)."""
+    global WARP_MMA
+    WARP_MMA = request.param == "warp_mma"
+    yield
 
 
 def run_device(cuda, key, value, slots, signs, H, d, S, P, sign_source="f32", status=False):
@@ -37,7 +47,8 @@ def run_device(cuda, key, value, slots, signs, H, d, S, P, sign_source="f32", st
             src = tq.SIGNS_TABLES_BF16
     st = torch.zeros(1, dtype=torch.int32, device=cuda) if status else None
     tq.reshape_and_cache(k, v, kc, vc, sc, sl, sg, num_kv_heads=H, head_size=d, block_size=S,
-                         num_blocks=P, inv_sqrt_len=hp.inv_sqrt_len(d), sign_source=src, status=st)
+                         num_blocks=P, inv_sqrt_len=hp.inv_sqrt_len(d), sign_source=src, status=st,
+                         warp_mma=WARP_MMA)
     torch.cuda.synchronize()
     out = kc.cpu().numpy(), vc.cpu().numpy(), sc.cpu().numpy()
     return out + ((int(st.item()),) if status else ())
