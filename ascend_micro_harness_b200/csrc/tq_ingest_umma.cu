@@ -10,16 +10,17 @@
 // How: M is a dense +-1 matrix, so a tile of 128 tokens of one (plane, head) is ONE
 // 128 x 128 x 128 tensor-core product instead of MMAs plus register butterflies:
 //   * a persistent CTA of 128 threads builds M once in shared memory (K-major,
-//     128-byte swizzle), then walks tiles; the activations of the next tile stream into
-//     the other half of a two-stage ring with 16-byte cp.async while this one is worked on;
+//     128-byte swizzle), then walks tiles; the activations of the next tile are requested
+//     with 16-byte cp.async as soon as the tensor core has consumed the current ones, and
+//     three or four such CTAs share an SM so that one CTA's waits are another's work;
 //   * key plane:   D[token][channel] = X M^T  -- a thread reads its token's 128 rotated
 //     channels out of tensor memory, so absmax, scale, rounding and the packing of the
 //     token's 64-byte page row are all thread-local;
-//   * value plane: the same product gives the per-token scales, and the product with the
-//     operands swapped, D'[channel][token] = M X^T (same two shared-memory tiles), hands
-//     every thread one channel with its 128 tokens: the 8 bytes a channel owns in each
-//     channel-major 16-token strip are thread-local too, and a warp's stores are 256
-//     contiguous bytes;
+//   * value plane: the same product gives the per-token scales; then the product with the
+//     operands swapped, D'[channel][token] = M X^T (same two shared-memory tiles, same
+//     tensor-memory columns), hands every thread one channel with its 128 tokens: the 8
+//     bytes a channel owns in each channel-major 16-token strip are thread-local too, and
+//     a warp's stores are 256 contiguous bytes;
 //   * int8 tiles accumulate in INT32 on top of the bit pattern of 1.5 * 2^23 written into
 //     tensor memory beforehand, so an accumulator read back as a float is 12582912 + y
 //     exactly and no integer-to-float conversion is issued; bf16 tiles accumulate in FP32
@@ -34,7 +35,7 @@ namespace {
 
 constexpr int kTileTokens = 128;
 constexpr int kThreads = 128;
-constexpr uint32_t kTmemCols = 256;          // two 128-column FP32/INT32 accumulators
+constexpr uint32_t kTmemCols = 128;          // one 128 x 128 FP32/INT32 accumulator
 constexpr long long kWaitBudget = 2000000000LL;   // clock cycles, about a second
 
 constexpr float kBias = 12582912.0f;         // 1.5 * 2^23
@@ -55,11 +56,13 @@ struct Cfg {
     // N / 8 at bit 17, M / 16 at bit 24
     static constexpr uint32_t kIdesc = ((BF16 ? 1u : 2u) << 4) | (1u << 7) | (1u << 10) |
                                        ((128u >> 3) << 17) | ((128u >> 4) << 24);
-    // M, two activation stages, per-token quantiser constants, strip offsets, barrier, flags;
-    // 1 KiB of slack for aligning the tiles. At least 80 KiB is requested so that no more
-    // than two CTAs -- 2 x 256 tensor-memory columns -- share an SM.
-    static constexpr int kUsed = 3 * kTileBytes + 2 * kTileTokens * 4 + 8 * 8 + 64;
-    static constexpr int kSmem = (kUsed + 1024) > 80 * 1024 ? (kUsed + 1024) : 80 * 1024;
+    // M, one activation tile, per-token quantiser constants, strip offsets, barrier, flags;
+    // 1 KiB of slack for aligning the tiles. Resident CTAs per SM: 4 x 128 tensor-memory
+    // columns is all an SM has, and the bf16 tiles (64 KiB) allow three; the int8 request is
+    // padded to 48 KiB so that a fifth CTA never lands on an SM and stalls in its allocation.
+    static constexpr int kCtasPerSm = BF16 ? 3 : 4;
+    static constexpr int kUsed = 2 * kTileBytes + 2 * kTileTokens * 4 + 8 * 8 + 64;
+    static constexpr int kSmem = (kUsed + 1024) > 48 * 1024 ? (kUsed + 1024) : 48 * 1024;
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p)
@@ -110,31 +113,43 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity)
     return ok != 0;
 }
 
-#define TQ_R8(v, o) "=r"(v[o]), "=r"(v[o + 1]), "=r"(v[o + 2]), "=r"(v[o + 3]), "=r"(v[o + 4]), \
+#define TQ_W8(v, o) "=r"(v[o]), "=r"(v[o + 1]), "=r"(v[o + 2]), "=r"(v[o + 3]), "=r"(v[o + 4]), \
                     "=r"(v[o + 5]), "=r"(v[o + 6]), "=r"(v[o + 7])
+#define TQ_RW8(v, o) "+r"(v[o]), "+r"(v[o + 1]), "+r"(v[o + 2]), "+r"(v[o + 3]), "+r"(v[o + 4]), \
+                     "+r"(v[o + 5]), "+r"(v[o + 6]), "+r"(v[o + 7])
 
-// 32 lanes x 32 columns: lane i of the warp receives columns col .. col+31 of its row. The
-// wait sits in the same statement, so no use of the registers can be scheduled before it.
+// 32 lanes x 32 (16) columns: lane i of the warp receives columns col .. of its row. The
+// load is asynchronous; tmem_arrived() is the wait, and it names the registers as in-out
+// operands so that no use of them can be scheduled ahead of it.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
 {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
-        "tcgen05.wait::ld.sync.aligned;\n"
-        : TQ_R8(v, 0), TQ_R8(v, 8), TQ_R8(v, 16), TQ_R8(v, 24)
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : TQ_W8(v, 0), TQ_W8(v, 8), TQ_W8(v, 16), TQ_W8(v, 24)
         : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_arrived(uint32_t (&v)[32])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
+                 : TQ_RW8(v, 0), TQ_RW8(v, 8), TQ_RW8(v, 16), TQ_RW8(v, 24)
+                 :: "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
 {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
-        "tcgen05.wait::ld.sync.aligned;\n"
-        : TQ_R8(v, 0), TQ_R8(v, 8)
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : TQ_W8(v, 0), TQ_W8(v, 8)
         : "r"(taddr) : "memory");
 }
-#undef TQ_R8
+__device__ __forceinline__ void tmem_arrived(uint32_t (&v)[16])
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" : TQ_RW8(v, 0), TQ_RW8(v, 8) :: "memory");
+}
+#undef TQ_W8
+#undef TQ_RW8
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 // The same 32-bit value into 32 columns of every lane of the warp's quarter.
@@ -196,15 +211,15 @@ __device__ __forceinline__ uint32_t pack8(const float (&r)[8])
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(kThreads, 2) tq_ingest_umma_kernel(const IngestParams p)
+__global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umma_kernel(const IngestParams p)
 {
     using C = Cfg<BF16>;
     extern __shared__ uint8_t smem_raw[];
     // tiles on a 1024-byte boundary: the swizzle is a function of address bits 4..9
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
     uint8_t* m_tile = base;
-    uint8_t* x_tile = base + C::kTileBytes;                                   // two stages
-    float* inv_s = reinterpret_cast<float*>(base + 3 * C::kTileBytes);        // per token: 2^(2-e)
+    uint8_t* x_tile = base + C::kTileBytes;
+    float* inv_s = reinterpret_cast<float*>(base + 2 * C::kTileBytes);        // per token: 2^(2-e)
     float* add_s = inv_s + kTileTokens;                                       // per token: rounding addend
     unsigned long long* strip_off = reinterpret_cast<unsigned long long*>(add_s + kTileTokens);  // [8]
     uint64_t* mbar = reinterpret_cast<uint64_t*>(strip_off + 8);
@@ -260,56 +275,50 @@ __global__ void __launch_bounds__(kThreads, 2) tq_ingest_umma_kernel(const Inges
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t acc0 = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lanes
-    const uint32_t acc1 = acc0 + 128u;
+    const uint32_t acc = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lanes
+    const uint32_t mbar_s = smem_addr(mbar), x_tile_s = smem_addr(x_tile), m_tile_s = smem_addr(m_tile);
 
     // ---- per-thread copy plan: 16-byte chunk `chunk` of rows r0, r0 + R, ...
     constexpr int kChunksPerRow = C::kRowBytes / 16;        // 8 or 16
     constexpr int kRowsPerPass = kThreads / kChunksPerRow;  // 16 or 8
     const int chunk = tid % kChunksPerRow, r0 = tid / kChunksPerRow;
-    const uint32_t dst0 = (chunk >> 3) * C::kBlockBytes + r0 * 128 + (((chunk & 7) ^ (r0 & 7)) << 4);
-    const uint32_t x_tile_s = smem_addr(x_tile);
+    const uint32_t dst0 = x_tile_s + (chunk >> 3) * C::kBlockBytes + r0 * 128 + (((chunk & 7) ^ (r0 & 7)) << 4);
+    const size_t src0 = static_cast<size_t>(r0) * row_pitch + chunk * 16;
+    const size_t pass_pitch = static_cast<size_t>(kRowsPerPass) * row_pitch;
 
-    auto load_tile = [&](uint32_t tile, uint32_t stage) {
+    auto load_tile = [&](uint32_t tile) {
         const TileId id = tile_of(p, tile);
         const uint32_t first = id.tok_tile * kTileTokens;
-        const uint32_t live = min(static_cast<uint32_t>(kTileTokens), num_tokens - first);
-        const uint8_t* src = static_cast<const uint8_t*>(id.plane == 0 ? p.key : p.value) +
-                             static_cast<size_t>(first) * row_pitch +
-                             static_cast<size_t>(id.head) * C::kRowBytes + chunk * 16;
-        const uint32_t dst = x_tile_s + stage * C::kTileBytes + dst0;
+        const uint32_t live = num_tokens - first;
+        const uint8_t* tile_src = static_cast<const uint8_t*>(id.plane == 0 ? p.key : p.value) +
+                                  static_cast<size_t>(first) * row_pitch +
+                                  static_cast<size_t>(id.head) * C::kRowBytes;
+        if (live >= static_cast<uint32_t>(kTileTokens)) {
+            const uint8_t* src = tile_src + src0;
 #pragma unroll
-        for (int pass = 0; pass < kTileTokens / kRowsPerPass; ++pass) {
-            // rows past the last token of a short final tile re-read its last row;
-            // what they produce is never stored
-            const uint32_t row = min(static_cast<uint32_t>(pass * kRowsPerPass + r0), live - 1u);
-            cp16(dst + pass * kRowsPerPass * 128, src + static_cast<size_t>(row) * row_pitch);
+            for (int pass = 0; pass < kTileTokens / kRowsPerPass; ++pass)
+                cp16(dst0 + pass * kRowsPerPass * 128, src + pass * pass_pitch);
+        } else {
+            // a short final tile: rows past its last token re-read that token's row; what
+            // they produce is never stored
+#pragma unroll 1
+            for (int pass = 0; pass < kTileTokens / kRowsPerPass; ++pass) {
+                const uint32_t row = min(static_cast<uint32_t>(pass * kRowsPerPass + r0), live - 1u);
+                cp16(dst0 + pass * kRowsPerPass * 128, tile_src + static_cast<size_t>(row) * row_pitch + chunk * 16);
+            }
         }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
 
-    uint32_t tile = blockIdx.x;
-    if (tile < tiles) load_tile(tile, 0);
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
-
-    uint32_t parity = 0, it = 0;
+    // One product into the accumulator columns, then the bounded wait for it.
+    // transposed = false: D[token][channel] = X M^T; true: D'[channel][token] = M X^T.
+    uint32_t parity = 0;
     bool healthy = true;
-#pragma unroll 1
-    for (; tile < tiles; tile += gridDim.x, ++it) {
-        const uint32_t stage = it & 1u;
-        const uint32_t next = tile + gridDim.x;
-        if (next < tiles) load_tile(next, stage ^ 1u);
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-        asm volatile("cp.async.wait_group 1;\n" ::: "memory");   // this thread's part of `tile`
-
-        const TileId id = tile_of(p, tile);
+    auto product = [&](bool transposed) {
         if constexpr (!BF16) {
             // INT32 accumulators start at the bit pattern of 1.5 * 2^23
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_fill32(acc0 + c * 32, kBiasBits);
-            if (id.plane == 1) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_fill32(acc1 + c * 32, kBiasBits);
-            }
+            for (int c = 0; c < 4; ++c) tmem_fill32(acc + c * 32, kBiasBits);
             tmem_wait_st();
         }
         fence_async_smem();      // cp.async and st.shared data -> visible to the tensor core
@@ -317,46 +326,45 @@ __global__ void __launch_bounds__(kThreads, 2) tq_ingest_umma_kernel(const Inges
         __syncthreads();
         if (tid == 0) {
             fence_after_sync();
-            const uint32_t xs = x_tile_s + stage * C::kTileBytes, ms = smem_addr(m_tile);
 #pragma unroll
             for (int k = 0; k < C::kKSteps; ++k) {
                 const uint32_t off = (k >> 2) * C::kBlockBytes + (k & 3) * 32;
-                // D[token][channel] += X[token][k..] M[channel][k..]
-                umma<BF16>(tmem_base, umma_desc(xs + off), umma_desc(ms + off),
-                           (!BF16 || k > 0) ? 1u : 0u);
+                const uint64_t dx = umma_desc(x_tile_s + off), dm = umma_desc(m_tile_s + off);
+                umma<BF16>(tmem_base, transposed ? dm : dx, transposed ? dx : dm, (!BF16 || k > 0) ? 1u : 0u);
             }
-            if (id.plane == 1) {
-#pragma unroll
-                for (int k = 0; k < C::kKSteps; ++k) {
-                    const uint32_t off = (k >> 2) * C::kBlockBytes + (k & 3) * 32;
-                    // D'[channel][token] += M[channel][k..] X[token][k..]
-                    umma<BF16>(tmem_base + 128u, umma_desc(ms + off), umma_desc(xs + off),
-                               (!BF16 || k > 0) ? 1u : 0u);
-                }
-            }
-            umma_commit(smem_addr(mbar));
+            umma_commit(mbar_s);
         }
-        // ---- bounded wait for the products
-        {
-            const long long t0 = clock64();
-            bool done = mbar_try_wait(smem_addr(mbar), parity);
-            while (!done) {
-                if (clock64() - t0 > kWaitBudget) break;
-                done = mbar_try_wait(smem_addr(mbar), parity);
-            }
-            if (!done) {
-                healthy = false;
-                *abort_flag = 1u;
-                report(p.status, TQ_STATUS_WAIT_EXPIRED);
-            }
-            parity ^= 1u;
+        const long long t0 = clock64();
+        bool done = mbar_try_wait(mbar_s, parity);
+        while (!done) {
+            if (clock64() - t0 > kWaitBudget) break;
+            done = mbar_try_wait(mbar_s, parity);
         }
+        if (!done) {
+            healthy = false;
+            *abort_flag = 1u;
+            report(p.status, TQ_STATUS_WAIT_EXPIRED);
+        }
+        parity ^= 1u;
         fence_after_sync();
+    };
 
-        // ---- this thread's token of the tile (both planes need its scale)
+    uint32_t tile = blockIdx.x;
+    if (tile < tiles) load_tile(tile);
+
+#pragma unroll 1
+    for (; tile < tiles; tile += gridDim.x) {
+        const TileId id = tile_of(p, tile);
+        // ---- this thread's token of the tile: its slot is requested before anything waits
         const uint32_t tok = id.tok_tile * kTileTokens + tid;
         const bool tok_live = tok < num_tokens;
         const int32_t slot = tok_live ? __ldg(p.slots + tok) : -1;
+
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");   // this thread's part of the tile
+        product(false);
+        const uint32_t next = tile + gridDim.x;
+        if (id.plane == 0 && next < tiles) load_tile(next);       // the tile is consumed: refill
+
         const int32_t slot0 = __shfl_sync(0xffffffffu, slot, lane & 16);
         const bool run_ok = slot == slot0 + (lane & 15);
         const uint32_t votes = __ballot_sync(0xffffffffu, run_ok);
@@ -370,25 +378,42 @@ __global__ void __launch_bounds__(kThreads, 2) tq_ingest_umma_kernel(const Inges
         const size_t block_off = (static_cast<size_t>(page) * p.H + id.head) * (static_cast<size_t>(p.S) * 64u) +
                                  static_cast<size_t>(tok_in_page / kStrip) * 1024u;
 
-        // ---- pass 1 over D[token][.]: absmax of the token, its power-of-two scale
+        // ---- pass 1 over D[token][.]: absmax of the token, its power-of-two scale.
+        // Tensor-memory reads run one 32-column chunk ahead of the arithmetic.
+        uint32_t va[32], vb[32];
         float amax;
         {
-            float hi = BF16 ? 0.0f : kBias, lo = kBias;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(acc0 + c * 32, v);
+            float hi0 = BF16 ? 0.0f : kBias, hi1 = hi0, lo0 = kBias, lo1 = kBias;
+            auto fold = [&](const uint32_t (&v)[32]) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
+                for (int j = 0; j < 32; j += 4) {
                     const float a = __uint_as_float(v[j]), b = __uint_as_float(v[j + 1]);
+                    const float c = __uint_as_float(v[j + 2]), d = __uint_as_float(v[j + 3]);
                     if constexpr (BF16) {
-                        hi = max3f(hi, fabsf(a), fabsf(b));
+                        hi0 = max3f(hi0, fabsf(a), fabsf(b));
+                        hi1 = max3f(hi1, fabsf(c), fabsf(d));
                     } else {
-                        hi = max3f(hi, a, b);
-                        lo = min3f(lo, a, b);
+                        hi0 = max3f(hi0, a, b);
+                        hi1 = max3f(hi1, c, d);
+                        lo0 = min3f(lo0, a, b);
+                        lo1 = min3f(lo1, c, d);
                     }
                 }
-            }
+            };
+            tmem_ld32(acc + 0, va);
+            tmem_arrived(va);
+            tmem_ld32(acc + 32, vb);
+            fold(va);
+            tmem_arrived(vb);
+            tmem_ld32(acc + 64, va);
+            fold(vb);
+            tmem_arrived(va);
+            tmem_ld32(acc + 96, vb);
+            fold(va);
+            tmem_arrived(vb);
+            if (id.plane == 0) tmem_ld32(acc + 0, va);   // first chunk of pass 2
+            fold(vb);
+            const float hi = fmaxf(hi0, hi1), lo = fminf(lo0, lo1);
             amax = BF16 ? hi : fmaxf(hi - kBias, kBias - lo);
             amax = fmaxf(amax, 1.0f);   // the writer floors absmax at 1
         }
@@ -405,10 +430,8 @@ __global__ void __launch_bounds__(kThreads, 2) tq_ingest_umma_kernel(const Inges
             // ---- key page: the token's row, 32 channels (16 bytes) per tensor-memory read
             uint4* dst = reinterpret_cast<uint4*>(p.key_cache + block_off + static_cast<size_t>(lane & 15) * 64u);
             const float2 inv2 = make_float2(inv, inv), add2 = make_float2(addend, addend);
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(acc0 + c * 32, v);
+            const bool store = strip_ok && healthy;
+            auto emit = [&](const uint32_t (&v)[32], int c) {
                 uint32_t w[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -423,29 +446,47 @@ __global__ void __launch_bounds__(kThreads, 2) tq_ingest_umma_kernel(const Inges
                     }
                     w[j] = pack8(r);
                 }
-                if (strip_ok && healthy) __stcs(dst + c, make_uint4(w[0], w[1], w[2], w[3]));
-            }
+                if (store) __stcs(dst + c, make_uint4(w[0], w[1], w[2], w[3]));
+            };
+            tmem_arrived(va);
+            tmem_ld32(acc + 32, vb);
+            emit(va, 0);
+            tmem_arrived(vb);
+            tmem_ld32(acc + 64, va);
+            emit(vb, 1);
+            tmem_arrived(va);
+            tmem_ld32(acc + 96, vb);
+            emit(va, 2);
+            tmem_arrived(vb);
+            emit(vb, 3);
         } else {
-            // ---- value page: publish the per-token constants, then work per channel
+            // ---- value page: publish the per-token constants, swap the operands, then
+            // work per channel
             inv_s[tid] = inv;
             add_s[tid] = addend;
             if ((lane & 15) == 0)
                 strip_off[tid >> 4] = strip_ok ? static_cast<unsigned long long>(block_off) : ~0ull;
-            __syncthreads();
+            product(true);   // its barrier also publishes the constants and ends pass 1's reads
+            if (next < tiles) load_tile(next);
             const bool store = healthy;
-#pragma unroll 1
-            for (int s = 0; s < 8; ++s) {
-                uint32_t v[16];
-                tmem_ld16(acc1 + s * 16, v);
+            uint32_t ua[16], ub[16];
+            auto emit = [&](const uint32_t (&v)[16], int s) {
                 uint32_t w[2];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const float4 i0 = *reinterpret_cast<const float4*>(inv_s + s * 16 + h * 8);
                     const float4 i1 = *reinterpret_cast<const float4*>(inv_s + s * 16 + h * 8 + 4);
-                    const float4 a0 = *reinterpret_cast<const float4*>(add_s + s * 16 + h * 8);
-                    const float4 a1 = *reinterpret_cast<const float4*>(add_s + s * 16 + h * 8 + 4);
                     const float iv[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
-                    const float ad[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                    float ad[8];
+                    if constexpr (BF16) {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) ad[e] = kMagic;
+                    } else {
+                        const float4 a0 = *reinterpret_cast<const float4*>(add_s + s * 16 + h * 8);
+                        const float4 a1 = *reinterpret_cast<const float4*>(add_s + s * 16 + h * 8 + 4);
+                        ad[0] = a0.x; ad[1] = a0.y; ad[2] = a0.z; ad[3] = a0.w;
+                        ad[4] = a1.x; ad[5] = a1.y; ad[6] = a1.z; ad[7] = a1.w;
+                    }
                     float r[8];
 #pragma unroll
                     for (int e = 0; e < 8; e += 2) {
@@ -462,6 +503,16 @@ __global__ void __launch_bounds__(kThreads, 2) tq_ingest_umma_kernel(const Inges
                 if (store && off != ~0ull)
                     __stcs(reinterpret_cast<uint2*>(p.value_cache + off + static_cast<size_t>(tid) * 8u),
                            make_uint2(w[0], w[1]));
+            };
+            tmem_ld16(acc + 0, ua);
+#pragma unroll
+            for (int s = 0; s < 8; s += 2) {
+                tmem_arrived(ua);
+                tmem_ld16(acc + (s + 1) * 16, ub);
+                emit(ua, s);
+                tmem_arrived(ub);
+                if (s + 2 < 8) tmem_ld16(acc + (s + 2) * 16, ua);
+                emit(ub, s + 1);
             }
         }
         // every read of tensor memory and of the per-token constants is done before the next
@@ -493,7 +544,7 @@ cudaError_t launch(cudaStream_t stream, const IngestParams& p)
     }
     const uint64_t tiles = static_cast<uint64_t>((p.num_strips + 7u) / 8u) * 2u * p.H;
     if (tiles == 0) return cudaSuccess;
-    const uint32_t resident = static_cast<uint32_t>(sms) * 2u;   // persistent: one resident wave
+    const uint32_t resident = static_cast<uint32_t>(sms) * C::kCtasPerSm;   // persistent: one resident wave
     const uint32_t blocks = tiles < resident ? static_cast<uint32_t>(tiles) : resident;
     tq_ingest_umma_kernel<BF16><<<blocks, kThreads, C::kSmem, stream>>>(p);
     return cudaGetLastError();
