@@ -9,10 +9,12 @@
 //
 // How: M is a dense +-1 matrix, so a tile of 128 tokens of one (plane, head) is ONE
 // 128 x 128 x 128 tensor-core product instead of MMAs plus register butterflies:
-//   * a persistent CTA of 128 threads builds M once in shared memory (K-major,
-//     128-byte swizzle), then walks tiles; the activations of the next tile are requested
-//     with 16-byte cp.async as soon as the tensor core has consumed the current ones, and
-//     three or four such CTAs share an SM so that one CTA's waits are another's work;
+//   * a persistent CTA builds M once in shared memory (K-major, 128-byte swizzle); its two
+//     groups of 128 threads then walk tiles independently, each with its own tile buffer,
+//     128 tensor-memory columns, completion barrier and named CTA barrier. The activations
+//     of a group's next tile are requested with 16-byte cp.async as soon as the tensor core
+//     has consumed the current ones; four groups share an SM, so one group's waits are
+//     another's work;
 //   * key plane:   D[token][channel] = X M^T  -- a thread reads its token's 128 rotated
 //     channels out of tensor memory, so absmax, scale, rounding and the packing of the
 //     token's 64-byte page row are all thread-local;
@@ -34,8 +36,11 @@ namespace tq {
 namespace {
 
 constexpr int kTileTokens = 128;
-constexpr int kThreads = 128;
-constexpr uint32_t kTmemCols = 128;          // one 128 x 128 FP32/INT32 accumulator
+constexpr int kGroups = 2;                   // independent 128-thread groups per CTA, one tile each
+constexpr int kGroupThreads = 128;
+constexpr int kThreads = kGroups * kGroupThreads;
+constexpr uint32_t kGroupCols = 128;         // one 128 x 128 FP32/INT32 accumulator per group
+constexpr uint32_t kTmemCols = kGroups * kGroupCols;
 constexpr long long kWaitBudget = 2000000000LL;   // clock cycles, about a second
 
 constexpr float kBias = 12582912.0f;         // 1.5 * 2^23
@@ -56,13 +61,14 @@ struct Cfg {
     // N / 8 at bit 17, M / 16 at bit 24
     static constexpr uint32_t kIdesc = ((BF16 ? 1u : 2u) << 4) | (1u << 7) | (1u << 10) |
                                        ((128u >> 3) << 17) | ((128u >> 4) << 24);
-    // M, one activation tile, per-token quantiser constants, strip offsets, barrier, flags;
-    // 1 KiB of slack for aligning the tiles. Resident CTAs per SM: 4 x 128 tensor-memory
-    // columns is all an SM has, and the bf16 tiles (64 KiB) allow three; the int8 request is
-    // padded to 48 KiB so that a fifth CTA never lands on an SM and stalls in its allocation.
-    static constexpr int kCtasPerSm = BF16 ? 3 : 4;
-    static constexpr int kUsed = 2 * kTileBytes + 2 * kTileTokens * 4 + 8 * 8 + 64;
-    static constexpr int kSmem = (kUsed + 1024) > 48 * 1024 ? (kUsed + 1024) : 48 * 1024;
+    // Per CTA: M once; per group one activation tile, the per-token quantiser constants,
+    // the strip offsets and a barrier; 1 KiB of slack for aligning the tiles. Two CTAs per
+    // SM: 2 x 256 tensor-memory columns is all an SM has, so the request is padded to
+    // 80 KiB and a third CTA can never land on an SM and stall in its allocation.
+    static constexpr int kCtasPerSm = 2;
+    static constexpr int kGroupBytes = kTileBytes + 2 * kTileTokens * 4 + 8 * 8 + 64;
+    static constexpr int kUsed = kTileBytes + kGroups * kGroupBytes + 64;
+    static constexpr int kSmem = (kUsed + 1024) > 80 * 1024 ? (kUsed + 1024) : 80 * 1024;
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p)
@@ -185,16 +191,19 @@ __device__ __forceinline__ float min3f(float a, float b, float c)
     return r;
 }
 
+// Work is dealt out as (128-token tile, head) items; a group does the key plane and then
+// the value plane of its item, so every group carries the same mix of the cheaper key
+// tiles and the dearer value tiles whatever the grid size. Unit u of a group is plane
+// u & 1 of its (u >> 1)-th item.
 struct TileId {
     uint32_t tok_tile, plane, head;
 };
-__device__ __forceinline__ TileId tile_of(const IngestParams& p, uint32_t tile)
+__device__ __forceinline__ TileId tile_of(const IngestParams& p, uint32_t item, uint32_t plane)
 {
     TileId id;
-    id.tok_tile = fast_div(tile, p.div_mul, p.div_shift);
-    const uint32_t rem = tile - id.tok_tile * 2u * p.H;
-    id.plane = rem >= p.H ? 1u : 0u;
-    id.head = rem - id.plane * p.H;
+    id.tok_tile = fast_div(2u * item, p.div_mul, p.div_shift);   // item / H with the 2H divider
+    id.head = item - id.tok_tile * p.H;
+    id.plane = plane;
     return id;
 }
 
@@ -210,6 +219,12 @@ __device__ __forceinline__ uint32_t pack8(const float (&r)[8])
     return (w - kHorner) ^ 0x88888888u;
 }
 
+// All 128 threads of one group (named barrier 1 + group).
+__device__ __forceinline__ void group_sync(int group)
+{
+    asm volatile("bar.sync %0, %1;\n" ::"r"(group + 1), "r"(kGroupThreads) : "memory");
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umma_kernel(const IngestParams p)
 {
@@ -217,42 +232,47 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
     extern __shared__ uint8_t smem_raw[];
     // tiles on a 1024-byte boundary: the swizzle is a function of address bits 4..9
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
+    const int group = threadIdx.x / kGroupThreads, tid = threadIdx.x % kGroupThreads;
+    const int warp = tid >> 5, lane = tid & 31;   // warp within the group = its tensor-memory lane quarter
     uint8_t* m_tile = base;
-    uint8_t* x_tile = base + C::kTileBytes;
-    float* inv_s = reinterpret_cast<float*>(base + 2 * C::kTileBytes);        // per token: 2^(2-e)
+    uint8_t* x_tile = base + C::kTileBytes + group * C::kTileBytes;
+    uint8_t* small = base + (1 + kGroups) * C::kTileBytes + group * (2 * kTileTokens * 4 + 8 * 8 + 64);
+    float* inv_s = reinterpret_cast<float*>(small);                           // per token: 2^(2-e)
     float* add_s = inv_s + kTileTokens;                                       // per token: rounding addend
     unsigned long long* strip_off = reinterpret_cast<unsigned long long*>(add_s + kTileTokens);  // [8]
     uint64_t* mbar = reinterpret_cast<uint64_t*>(strip_off + 8);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 1);
-    uint32_t* abort_flag = tmem_slot + 1;
+    uint32_t* shared_words = reinterpret_cast<uint32_t*>(base + (1 + kGroups) * C::kTileBytes +
+                                                         kGroups * (2 * kTileTokens * 4 + 8 * 8 + 64));
+    uint32_t* tmem_slot = shared_words;
+    uint32_t* abort_flag = shared_words + 1;
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t tiles = ((p.num_strips + 7u) / 8u) * 2u * p.H;
+    const uint32_t items = ((p.num_strips + 7u) / 8u) * p.H;
     const uint32_t num_tokens = p.num_strips * kStrip;
     const size_t row_pitch = static_cast<size_t>(p.H) * C::kRowBytes;         // bytes between tokens
 
-    // ---- one-time set-up: barrier, tensor memory, the rotation matrix
+    // ---- one-time set-up: barriers, tensor memory, the rotation matrix
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(mbar)));
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        *abort_flag = 0u;
+        if (group == 0) *abort_flag = 0u;
     }
-    if (warp == 0) {
+    if (threadIdx.x < 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(smem_addr(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     {
         // Row `tid` of M: output channel c1*32 + c0 against input channel g*32 + i is
-        // H4[c1][g] * s[g*32 + c0] * H32[c0][i]; true = -1.
+        // H4[c1][g] * s[g*32 + c0] * H32[c0][i]; true = -1. Each group writes half the row.
         const unsigned c1 = tid >> 5, c0 = tid & 31;
         bool gneg[4];
 #pragma unroll
         for (int g = 0; g < 4; ++g)
             gneg[g] = hneg(c1, g) != sign_is_negative(p.signs, p.sign_source, g * kGroup + c0);
         constexpr int kPerChunk = 16 / C::kElem;   // elements in a 16-byte chunk
+        constexpr int kChunks = C::kRowBytes / 16;
 #pragma unroll 1
-        for (int q = 0; q < C::kRowBytes / 16; ++q) {
+        for (int q = group * (kChunks / kGroups); q < (group + 1) * (kChunks / kGroups); ++q) {
             uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -271,23 +291,25 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
                 make_uint4(w[0], w[1], w[2], w[3]);
         }
     }
+    fence_async_smem();
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t acc = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lanes
+    const uint32_t tmem_group = tmem_base + static_cast<uint32_t>(group) * kGroupCols;
+    const uint32_t acc = tmem_group + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lanes
     const uint32_t mbar_s = smem_addr(mbar), x_tile_s = smem_addr(x_tile), m_tile_s = smem_addr(m_tile);
 
     // ---- per-thread copy plan: 16-byte chunk `chunk` of rows r0, r0 + R, ...
     constexpr int kChunksPerRow = C::kRowBytes / 16;        // 8 or 16
-    constexpr int kRowsPerPass = kThreads / kChunksPerRow;  // 16 or 8
+    constexpr int kRowsPerPass = kGroupThreads / kChunksPerRow;  // 16 or 8
     const int chunk = tid % kChunksPerRow, r0 = tid / kChunksPerRow;
     const uint32_t dst0 = x_tile_s + (chunk >> 3) * C::kBlockBytes + r0 * 128 + (((chunk & 7) ^ (r0 & 7)) << 4);
     const size_t src0 = static_cast<size_t>(r0) * row_pitch + chunk * 16;
     const size_t pass_pitch = static_cast<size_t>(kRowsPerPass) * row_pitch;
 
-    auto load_tile = [&](uint32_t tile) {
-        const TileId id = tile_of(p, tile);
+    auto load_tile = [&](uint32_t item, uint32_t plane) {
+        const TileId id = tile_of(p, item, plane);
         const uint32_t first = id.tok_tile * kTileTokens;
         const uint32_t live = num_tokens - first;
         const uint8_t* tile_src = static_cast<const uint8_t*>(id.plane == 0 ? p.key : p.value) +
@@ -323,14 +345,14 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
         }
         fence_async_smem();      // cp.async and st.shared data -> visible to the tensor core
         fence_before_sync();
-        __syncthreads();
+        group_sync(group);
         if (tid == 0) {
             fence_after_sync();
 #pragma unroll
             for (int k = 0; k < C::kKSteps; ++k) {
                 const uint32_t off = (k >> 2) * C::kBlockBytes + (k & 3) * 32;
                 const uint64_t dx = umma_desc(x_tile_s + off), dm = umma_desc(m_tile_s + off);
-                umma<BF16>(tmem_base, transposed ? dm : dx, transposed ? dx : dm, (!BF16 || k > 0) ? 1u : 0u);
+                umma<BF16>(tmem_group, transposed ? dm : dx, transposed ? dx : dm, (!BF16 || k > 0) ? 1u : 0u);
             }
             umma_commit(mbar_s);
         }
@@ -349,12 +371,13 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
         fence_after_sync();
     };
 
-    uint32_t tile = blockIdx.x;
-    if (tile < tiles) load_tile(tile);
+    const uint32_t item_step = gridDim.x * kGroups;
+    uint32_t item = blockIdx.x * kGroups + group;
+    if (item < items) load_tile(item, 0);
 
 #pragma unroll 1
-    for (; tile < tiles; tile += gridDim.x) {
-        const TileId id = tile_of(p, tile);
+    for (uint32_t unit = 0; item < items; ++unit, item += (unit & 1u) ? 0u : item_step) {
+        const TileId id = tile_of(p, item, unit & 1u);
         // ---- this thread's token of the tile: its slot is requested before anything waits
         const uint32_t tok = id.tok_tile * kTileTokens + tid;
         const bool tok_live = tok < num_tokens;
@@ -362,8 +385,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
 
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");   // this thread's part of the tile
         product(false);
-        const uint32_t next = tile + gridDim.x;
-        if (id.plane == 0 && next < tiles) load_tile(next);       // the tile is consumed: refill
+        if (id.plane == 0) load_tile(item, 1);                    // the tile is consumed: refill
 
         const int32_t slot0 = __shfl_sync(0xffffffffu, slot, lane & 16);
         const bool run_ok = slot == slot0 + (lane & 15);
@@ -467,7 +489,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
             if ((lane & 15) == 0)
                 strip_off[tid >> 4] = strip_ok ? static_cast<unsigned long long>(block_off) : ~0ull;
             product(true);   // its barrier also publishes the constants and ends pass 1's reads
-            if (next < tiles) load_tile(next);
+            if (item + item_step < items) load_tile(item + item_step, 0);
             const bool store = healthy;
             uint32_t ua[16], ub[16];
             auto emit = [&](const uint32_t (&v)[16], int s) {
@@ -515,16 +537,16 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
                 emit(ub, s + 1);
             }
         }
-        // every read of tensor memory and of the per-token constants is done before the next
-        // tile's products overwrite them
+        // every read of tensor memory and of the per-token constants is done before the
+        // group's next products overwrite them
         fence_before_sync();
-        __syncthreads();
+        group_sync(group);
         if (*abort_flag != 0u) break;
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     fence_before_sync();
     __syncthreads();
-    if (warp == 0)
+    if (threadIdx.x < 32)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
@@ -542,10 +564,11 @@ cudaError_t launch(cudaStream_t stream, const IngestParams& p)
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    const uint64_t tiles = static_cast<uint64_t>((p.num_strips + 7u) / 8u) * 2u * p.H;
+    const uint64_t tiles = static_cast<uint64_t>((p.num_strips + 7u) / 8u) * p.H;   // (tile, head) items
     if (tiles == 0) return cudaSuccess;
     const uint32_t resident = static_cast<uint32_t>(sms) * C::kCtasPerSm;   // persistent: one resident wave
-    const uint32_t blocks = tiles < resident ? static_cast<uint32_t>(tiles) : resident;
+    const uint64_t wanted = (tiles + kGroups - 1) / kGroups;
+    const uint32_t blocks = wanted < resident ? static_cast<uint32_t>(wanted) : resident;
     tq_ingest_umma_kernel<BF16><<<blocks, kThreads, C::kSmem, stream>>>(p);
     return cudaGetLastError();
 }
