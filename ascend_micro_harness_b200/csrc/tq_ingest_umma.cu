@@ -42,6 +42,7 @@ constexpr int kThreads = kGroups * kGroupThreads;
 constexpr uint32_t kGroupCols = 128;         // one 128 x 128 FP32/INT32 accumulator per group
 constexpr uint32_t kTmemCols = kGroups * kGroupCols;
 constexpr long long kWaitBudget = 2000000000LL;   // clock cycles, about a second
+constexpr uint32_t kSuspendHintNs = 20000u;       // one poll may sleep this long before it returns
 
 constexpr float kBias = 12582912.0f;         // 1.5 * 2^23
 constexpr uint32_t kBiasBits = 0x4B400000u;
@@ -113,9 +114,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity)
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(mbar), "r"(parity), "r"(kSuspendHintNs) : "memory");
     return ok != 0;
 }
 
@@ -356,11 +357,12 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
             }
             umma_commit(mbar_s);
         }
-        const long long t0 = clock64();
         bool done = mbar_try_wait(mbar_s, parity);
-        while (!done) {
-            if (clock64() - t0 > kWaitBudget) break;
-            done = mbar_try_wait(mbar_s, parity);
+        if (!done) {
+            const long long t0 = clock64();
+            do {
+                done = mbar_try_wait(mbar_s, parity);
+            } while (!done && clock64() - t0 < kWaitBudget);
         }
         if (!done) {
             healthy = false;

@@ -70,7 +70,7 @@ class ClockSampler:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.index)], stdout=self.out, stderr=subprocess.DEVNULL)
+                 "-lms", "20", "-i", str(self.index)], stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
