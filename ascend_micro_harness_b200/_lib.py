@@ -33,6 +33,13 @@ SIGNATURES = {
                                             vp]),
     "tq_splitk_combine": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, f32,
                                     vp]),
+    "tq_hadamard16": (C.c_int, [vp, vp, vp, u32, u32]),
+    "tq_lloydmax4_quantize": (C.c_int, [vp, vp, vp, vp, C.c_size_t]),
+    "tq_icdf_quantize": (C.c_int, [vp, vp, u32, vp, C.c_size_t]),
+    "tq_reshape_and_cache_lloydmax": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
+                                                u32, f32, vp]),
+    "tq_decode_lloydmax_export": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
+                                            u32, u32, u32, f32, vp]),
     # reference-named launchers (C++ callers; listed so their export is checked)
     "launch_turboquant_reshape_and_cache_a8": (None, None),
     "launch_turboquant_reshape_and_cache_bf16": (None, None),

@@ -685,6 +685,7 @@ struct CombineParams {
     void* output;
     uint32_t rows, rows_stride, splits, output_stage, out_dtype;
     float inv_sqrt_len;
+    uint32_t block16;   // 1: the rotation is block-diagonal H16 / 4 (Lloyd-Max cache variant)
 };
 
 // One CTA per (item, row): merge `splits` records, normalise, optionally rotate
@@ -731,11 +732,16 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
             __syncthreads();
             cur ^= 1;
         };
-        for (int s = kGroup; s < D; s <<= 1) stage(s);
-        buf[cur][c] *= p.signs[c];
-        __syncthreads();
-        for (int s = 1; s < kGroup; s <<= 1) stage(s);
-        v = buf[cur][c] * p.inv_sqrt_len;
+        if (p.block16 != 0u) {
+            for (int s = 1; s < 16; s <<= 1) stage(s);
+            v = buf[cur][c] * 0.25f;
+        } else {
+            for (int s = kGroup; s < D; s <<= 1) stage(s);
+            buf[cur][c] *= p.signs[c];
+            __syncthreads();
+            for (int s = 1; s < kGroup; s <<= 1) stage(s);
+            v = buf[cur][c] * p.inv_sqrt_len;
+        }
         if (p.output_stage == TQ_OUT_GATED)
             v = v / (1.0f + __expf(-p.gate[static_cast<size_t>(blockIdx.x) * D + c]));
     }
@@ -899,12 +905,12 @@ extern "C" int tq_splitk_combine(void* stream, const float* workspace, const flo
         out_dtype > TQ_DTYPE_F32 ||
         (head_size != 128 && head_size != 256))
         return TQ_ERR_INVALID_ARGUMENT;
-    if (!workspace || !output || (output_stage != TQ_OUT_ROTATED && !pi_signs) ||
-        (output_stage == TQ_OUT_GATED && !gate))
+    // pi_signs == nullptr selects the block-diagonal H16 / 4 egress of the Lloyd-Max variant
+    if (!workspace || !output || (output_stage == TQ_OUT_GATED && !gate))
         return TQ_ERR_INVALID_ARGUMENT;
     if (items == 0) return TQ_OK;
     CombineParams p{workspace, pi_signs, gate, output, rows, rows_stride, splits, output_stage,
-                    out_dtype, inv_sqrt_len};
+                    out_dtype, inv_sqrt_len, pi_signs == nullptr ? 1u : 0u};
     const uint64_t grid = static_cast<uint64_t>(items) * rows;
     if (grid > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);

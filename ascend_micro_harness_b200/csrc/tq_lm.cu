@@ -1,0 +1,472 @@
+// The cache variant built from the reference's stand-alone routines -- block-diagonal
+// 16x16 Sylvester Hadamard rotation, per-token RMS scale, 16-level Lloyd-Max codes -- in
+// the same planes as the power-of-two cache (key token-major, value channel-major per
+// 16-token strip, planar FP32 scales):
+//   writer   y = x H16 per 16-channel block, y_rot = y / 4,
+//            scale = sqrt(sum y_rot^2) * inv_sqrt_len + 1e-20
+//            (kernels/ops/turboquant/baseline/common/turboquant_codec_950.h:194-207),
+//            code = lloydmax(y_rot * (1 / scale))
+//            (include/routines/routine_vector_lloydmax_quantize.hpp:32-38), unsigned, low
+//            nibble first (tests/common/lloydmax_oracle.hpp:65-69);
+//   decode   q_rot = bf16((q H16 per block) / 4), score = sum q_rot centroid[K] * kscale *
+//            softmax_scale, acc += p * vscale * centroid[V], per-split {m x8, l x8, acc[d]}
+//            records in the layout of include/turboquant_splitk_contract.hpp:23-27, merged by
+//            the ordinary combine kernel with the block-diagonal egress.
+// The reference pins the stages (Hadamard tile, codec), not this composite; sums of squares
+// are taken in FP64 so that integer-valued inputs determine every scale bit and every code.
+#include <cuda_fp16.h>
+
+#include "tq_lloydmax.cuh"
+
+namespace tq {
+
+// ------------------------------------------------------------------- writer
+struct LmWriterParams {
+    const void* key;
+    const void* value;
+    uint8_t* key_cache;
+    uint8_t* value_cache;
+    float* scale_cache;
+    const int32_t* slots;
+    uint32_t num_strips, H, S, P, bf16;
+    float inv_sqrt_len;
+    uint32_t* status;
+};
+
+// One warp per (strip, plane, head) panel: lane = (channel half, token). A lane rotates
+// and quantises d/2 channels of its token; the value page's byte (channel, token pair) is
+// assembled after one exchange with the neighbouring token's lane.
+template <int D>
+__global__ void __launch_bounds__(128) tq_lm_writer_kernel(const LmWriterParams p)
+{
+    constexpr int kHalf = D / 2;            // channels per lane
+    constexpr int kBlocks = kHalf / 16;     // Hadamard blocks per lane
+    constexpr int kWords = kHalf / 8;       // packed words per lane
+    __shared__ __align__(16) uint8_t stage_all[4][kStrip * D / 2];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = lane & 15, hsel = lane >> 4;
+    uint8_t* stage = stage_all[warp];
+    const uint64_t panels = static_cast<uint64_t>(p.num_strips) * 2u * p.H;
+    for (uint64_t panel = static_cast<uint64_t>(blockIdx.x) * 4u + warp; panel < panels;
+         panel += static_cast<uint64_t>(gridDim.x) * 4u) {
+        const uint32_t strip = static_cast<uint32_t>(panel / (2u * p.H));
+        const uint32_t rem = static_cast<uint32_t>(panel % (2u * p.H));
+        const uint32_t plane = rem >= p.H ? 1u : 0u, head = rem - plane * p.H;
+        // the strip's slot run, checked as in the power-of-two writer
+        const int32_t slot = __ldg(p.slots + static_cast<size_t>(strip) * kStrip + t);
+        const int32_t slot0 = __shfl_sync(0xffffffffu, slot, 0);
+        const bool ok = __all_sync(0xffffffffu, slot == slot0 + t) && slot0 >= 0 &&
+                        (slot0 % kStrip) == 0 && static_cast<uint32_t>(slot0) / p.S < p.P;
+        if (!ok) {
+            if (lane == 0) report(p.status, TQ_STATUS_BAD_SLOT);
+            continue;
+        }
+        const uint32_t page = static_cast<uint32_t>(slot0) / p.S, tip = static_cast<uint32_t>(slot0) % p.S;
+
+        // ---- this lane's d/2 channels of token t
+        float y[kHalf];
+        const size_t row = (static_cast<size_t>(strip) * kStrip + t) * p.H * D + static_cast<size_t>(head) * D +
+                           hsel * kHalf;
+        if (p.bf16 != 0u) {
+            const uint4* src = reinterpret_cast<const uint4*>(
+                static_cast<const uint16_t*>(plane == 0 ? p.key : p.value) + row);
+#pragma unroll
+            for (int i = 0; i < kHalf / 8; ++i) {
+                const uint4 raw = __ldg(src + i);
+                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    y[i * 8 + 2 * j] = __uint_as_float(w[j] << 16);
+                    y[i * 8 + 2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+                }
+            }
+        } else {
+            const uint4* src = reinterpret_cast<const uint4*>(
+                static_cast<const int8_t*>(plane == 0 ? p.key : p.value) + row);
+#pragma unroll
+            for (int i = 0; i < kHalf / 16; ++i) {
+                const uint4 raw = __ldg(src + i);
+                const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b)
+                        y[i * 16 + j * 4 + b] = static_cast<float>(static_cast<int8_t>(w[j] >> (8 * b)));
+            }
+        }
+        double s2 = 0.0;
+#pragma unroll
+        for (int b = 0; b < kBlocks; ++b) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = y[b * 16 + i];
+            hadamard16_inplace(v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                y[b * 16 + i] = v[i];
+                s2 += static_cast<double>(v[i]) * static_cast<double>(v[i]);
+            }
+        }
+        s2 += __shfl_xor_sync(0xffffffffu, s2, 16);   // the other half of the token's channels
+        const float root = static_cast<float>(sqrt(s2));
+        const float scale = __fadd_rn(__fmul_rn(__fmul_rn(root, 0.25f), p.inv_sqrt_len), 1e-20f);
+        const float inv = __fdiv_rn(1.0f, scale);
+        uint32_t words[kWords];
+#pragma unroll
+        for (int w = 0; w < kWords; ++w) {
+            uint32_t packed = 0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                packed |= lloydmax4_code(__fmul_rn(__fmul_rn(y[w * 8 + e], 0.25f), inv)) << (4 * e);
+            words[w] = packed;
+        }
+        if (hsel == 0)
+            p.scale_cache[((static_cast<size_t>(plane) * p.P + page) * p.H + head) * p.S + tip + t] = scale;
+
+        uint8_t* dst = (plane == 0 ? p.key_cache : p.value_cache) +
+                       (static_cast<size_t>(page) * p.H + head) * (static_cast<size_t>(p.S) * D / 2) +
+                       static_cast<size_t>(tip / kStrip) * (kStrip * D / 2);
+        __syncwarp();   // the previous panel's copy-out has finished reading the stage
+        if (plane == 0) {
+            // key page, token-major: the lane's d/4 bytes of row t
+            uint4* srow = reinterpret_cast<uint4*>(stage + t * (D / 2) + hsel * (D / 4));
+#pragma unroll
+            for (int i = 0; i < kWords / 4; ++i)
+                srow[i] = make_uint4(words[4 * i], words[4 * i + 1], words[4 * i + 2], words[4 * i + 3]);
+        } else {
+            // value page, channel-major: byte (channel, t / 2) = code(t even) | code(t odd) << 4.
+            // The even-token lane assembles the first half of its channels, the odd one the rest.
+#pragma unroll
+            for (int w = 0; w < kWords; ++w) {
+                const uint32_t other = __shfl_xor_sync(0xffffffffu, words[w], 1);
+                const bool mine = ((w < kWords / 2) == ((t & 1) == 0));
+                const uint32_t even = (t & 1) ? other : words[w], odd = (t & 1) ? words[w] : other;
+                if (mine) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const uint32_t byte = ((even >> (4 * e)) & 0xFu) | (((odd >> (4 * e)) & 0xFu) << 4);
+                        stage[(hsel * kHalf + w * 8 + e) * 8 + (t >> 1)] = static_cast<uint8_t>(byte);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        const uint4* s4 = reinterpret_cast<const uint4*>(stage);
+#pragma unroll
+        for (int i = 0; i < kStrip * D / 2 / 16 / 32; ++i)
+            __stcs(reinterpret_cast<uint4*>(dst) + i * 32 + lane, s4[i * 32 + lane]);
+    }
+}
+
+// ------------------------------------------------------------------- decode
+struct LmDecodeParams {
+    const uint16_t* q;            // [batch][Hq][D] bf16
+    const uint8_t* key_cache;
+    const uint8_t* value_cache;
+    const float* scale_cache;
+    const int32_t* table;
+    const int32_t* context_lens;
+    float* workspace;             // [item][split][rows]{m x8, l x8, acc[D]}
+    uint32_t items, H, rows, S, P, table_stride, splits;
+    float softmax_scale;
+    uint32_t* status;
+};
+
+constexpr float kLmLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One CTA per (sequence, KV head, split); up to 8 query rows (the GQA group). Four warps
+// take the strips of the split's page range in turn; a strip's 1 KiB key block, 1 KiB value
+// block and two scale runs go through a per-warp shared-memory buffer, codes become f16
+// centroids through a 256-entry byte -> (centroid, centroid) table, both contractions are
+// f16 tensor-core MMAs with tokens as the M dimension.
+template <int D>
+__global__ void __launch_bounds__(128) tq_lm_decode_kernel(const LmDecodeParams p)
+{
+    constexpr int kRecord = 16 + D;
+    constexpr int kStripBytes = kStrip * D / 2;
+    constexpr int MT = D / 16;
+    constexpr int kChunks = D / 2 / 16 / 4;   // 16-byte chunks of a key row per thread: 1 or 2
+    constexpr int kBufBytes = 2 * kStripBytes + 128;
+    constexpr int kLoopBytes = 4 * kBufBytes + 8 * D * 4;          // strip buffers + rotated query
+    constexpr int kMergeBytes = 4 * 8 * (D + 2) * 4;               // reuses them after the strip loop
+    __shared__ uint32_t lut[256];
+    __shared__ __align__(16) uint8_t raw[kLoopBytes > kMergeBytes ? kLoopBytes : kMergeBytes];
+    uint8_t (*bufs)[kBufBytes] = reinterpret_cast<uint8_t (*)[kBufBytes]>(raw);
+    float (*qs)[D] = reinterpret_cast<float (*)[D]>(raw + 4 * kBufBytes);
+    float (*merge)[8][D + 2] = reinterpret_cast<float (*)[8][D + 2]>(raw);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, qd = lane & 3;
+    const uint32_t split = blockIdx.x % p.splits, item = blockIdx.x / p.splits;
+    const uint32_t seq = item / p.H, head = item % p.H;
+
+    // byte -> packed (centroid[low nibble], centroid[high nibble]) as f16
+    for (int i = tid; i < 256; i += blockDim.x) {
+        const __half2 h = __floats2half2_rn(lloydmax4_centroid(i & 15), lloydmax4_centroid(i >> 4));
+        lut[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    // q_rot: FP32 butterfly inside each 16-channel block, / 4, bf16
+    for (int i = tid; i < 8 * (D / 16); i += blockDim.x) {
+        const int row = i / (D / 16), blk = i % (D / 16);
+        float v[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+            v[k] = row < static_cast<int>(p.rows)
+                       ? bf16_bits_to_f32(p.q[(static_cast<size_t>(item) * p.rows + row) * D + blk * 16 + k])
+                       : 0.f;
+        hadamard16_inplace(v);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) qs[row][blk * 16 + k] = bf16_bits_to_f32(f32_to_bf16_bits(v[k] * 0.25f));
+    }
+    __syncthreads();
+
+    // page range of this split (include/turboquant_splitk_contract.hpp:129-136)
+    const int32_t c0 = p.context_lens[seq];
+    const uint32_t ctx = c0 > 0 ? min(static_cast<uint32_t>(c0), p.table_stride * p.S) : 0u;
+    const uint32_t pages = (ctx + p.S - 1u) / p.S;
+    const uint32_t width = (pages + p.splits - 1u) / p.splits;
+    const uint32_t pb = min(split * width, pages), pe = min(pb + width, pages);
+    const uint32_t SP = p.S / kStrip;
+    const uint32_t s0 = pb * SP, s1 = min(pe * SP, (ctx + kStrip - 1u) / kStrip);
+
+    // B fragments of q_rot^T: MMA j of a key row takes this thread's bytes 2j, 2j+1, i.e.
+    // channels qd*(D/4) + 4j .. 4j+3
+    uint32_t bq[D / 16][2];
+#pragma unroll
+    for (int j = 0; j < D / 16; ++j) {
+        const float* qr = &qs[r][qd * (D / 4) + 4 * j];
+        const __half2 lo = __floats2half2_rn(qr[0], qr[1]), hi = __floats2half2_rn(qr[2], qr[3]);
+        bq[j][0] = *reinterpret_cast<const uint32_t*>(&lo);
+        bq[j][1] = *reinterpret_cast<const uint32_t*>(&hi);
+    }
+
+    float m_run[2] = {kMaskedScore, kMaskedScore}, l_run[2] = {0.f, 0.f};
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+
+    uint8_t* buf = bufs[warp];
+    const float fac = p.softmax_scale * kLmLog2e;
+    const int32_t* table_row = p.table + static_cast<size_t>(seq) * p.table_stride;
+    for (uint32_t strip = s0 + warp; strip < s1; strip += 4u) {
+        int32_t pg = __ldg(table_row + strip / SP);
+        if (pg < 0 || static_cast<uint32_t>(pg) >= p.P) {
+            if (lane == 0) report(p.status, TQ_STATUS_BAD_PAGE);
+            pg = 0;
+        }
+        const size_t block = (static_cast<size_t>(pg) * p.H + head) * (static_cast<size_t>(p.S) * D / 2) +
+                             static_cast<size_t>(strip % SP) * kStripBytes;
+        __syncwarp();
+        {
+            const uint4* ks = reinterpret_cast<const uint4*>(p.key_cache + block);
+            const uint4* vs = reinterpret_cast<const uint4*>(p.value_cache + block);
+            uint4* bk = reinterpret_cast<uint4*>(buf);
+#pragma unroll
+            for (int i = 0; i < kStripBytes / 16 / 32; ++i) {
+                bk[i * 32 + lane] = __ldg(ks + i * 32 + lane);
+                bk[kStripBytes / 16 + i * 32 + lane] = __ldg(vs + i * 32 + lane);
+            }
+            if (lane < 8) {
+                const size_t sc = ((static_cast<size_t>(lane >> 2) * p.P + pg) * p.H + head) * p.S +
+                                  (strip % SP) * kStrip + (lane & 3) * 4;
+                reinterpret_cast<float4*>(buf + 2 * kStripBytes)[lane] =
+                    __ldg(reinterpret_cast<const float4*>(p.scale_cache + sc));
+            }
+        }
+        __syncwarp();
+        const float* scales = reinterpret_cast<const float*>(buf + 2 * kStripBytes);
+
+        // ---- scores^T: rows = tokens r and r+8, columns = query rows
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ch = 0; ch < kChunks; ++ch) {
+            const uint4 lo = *reinterpret_cast<const uint4*>(buf + r * (D / 2) + (qd * kChunks + ch) * 16);
+            const uint4 hi = *reinterpret_cast<const uint4*>(buf + (r + 8) * (D / 2) + (qd * kChunks + ch) * 16);
+            const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int j = ch * 8 + w * 2 + h;   // bytes 2j, 2j+1 of this thread's part of the row
+                    const uint32_t a0 = lut[(wl[w] >> (16 * h)) & 0xFFu], a2 = lut[(wl[w] >> (16 * h + 8)) & 0xFFu];
+                    const uint32_t a1 = lut[(wh[w] >> (16 * h)) & 0xFFu], a3 = lut[(wh[w] >> (16 * h + 8)) & 0xFFu];
+                    mma_f16(c, a0, a1, a2, a3, bq[j][0], bq[j][1]);
+                }
+        }
+        const uint32_t tok_lo = strip * kStrip + r, tok_hi = tok_lo + 8;
+        const bool live_lo = tok_lo < ctx, live_hi = tok_hi < ctx;
+        float sc[4];
+        sc[0] = live_lo ? c[0] * scales[r] : kMaskedScore;
+        sc[1] = live_lo ? c[1] * scales[r] : kMaskedScore;
+        sc[2] = live_hi ? c[2] * scales[r + 8] : kMaskedScore;
+        sc[3] = live_hi ? c[3] * scales[r + 8] : kMaskedScore;
+        const float vs_lo = live_lo ? scales[kStrip + r] : 0.f, vs_hi = live_hi ? scales[kStrip + r + 8] : 0.f;
+        float mx[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
+#pragma unroll
+        for (int o = 4; o <= 16; o <<= 1) {
+            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+        }
+        float alpha[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const float m_new = fmaxf(m_run[q], mx[q]);
+            alpha[q] = exp2f((m_run[q] - m_new) * fac);
+            m_run[q] = m_new;
+            l_run[q] *= alpha[q];
+        }
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            acc[mt][0] *= alpha[0];
+            acc[mt][1] *= alpha[1];
+            acc[mt][2] *= alpha[0];
+            acc[mt][3] *= alpha[1];
+        }
+        float pw[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const bool live = i < 2 ? live_lo : live_hi;
+            const float pr = live ? exp2f((sc[i] - m_run[i & 1]) * fac) : 0.f;
+            l_run[i & 1] += pr;
+            pw[i] = pr * (i < 2 ? vs_lo : vs_hi);
+        }
+        // P^T as the B operand: tokens 2qd, 2qd+1 (from rows r) and 8+2qd, 8+2qd+1 (rows r+8).
+        // Value scales can be any FP32, so P * scale is carried as an f16 hi + lo pair.
+        const __half2 h0 = __floats2half2_rn(pw[0], pw[1]), h1 = __floats2half2_rn(pw[2], pw[3]);
+        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+        const __half2 g0 = __floats2half2_rn(pw[0] - f0.x, pw[1] - f0.y), g1 = __floats2half2_rn(pw[2] - f1.x, pw[3] - f1.y);
+        uint32_t bh0, bh1, bl0, bl1;
+        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(bh0) : "r"(*reinterpret_cast<const uint32_t*>(&h0)));
+        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(bh1) : "r"(*reinterpret_cast<const uint32_t*>(&h1)));
+        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(bl0) : "r"(*reinterpret_cast<const uint32_t*>(&g0)));
+        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(bl1) : "r"(*reinterpret_cast<const uint32_t*>(&g1)));
+        // ---- acc^T += V^T P^T: rows = channels mt*16 + r and + 8, contraction = tokens
+        const uint8_t* vb = buf + kStripBytes;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            const uint8_t* c_lo = vb + (mt * 16 + r) * 8, *c_hi = vb + (mt * 16 + 8 + r) * 8;
+            const uint32_t a0 = lut[c_lo[qd]], a2 = lut[c_lo[4 + qd]];
+            const uint32_t a1 = lut[c_hi[qd]], a3 = lut[c_hi[4 + qd]];
+            mma_f16(acc[mt], a0, a1, a2, a3, bh0, bh1);
+            mma_f16(acc[mt], a0, a1, a2, a3, bl0, bl1);
+        }
+    }
+
+    // ---- merge the four warps, export the record
+    __syncthreads();   // every warp is done with its strip buffer: the merge area reuses them
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 4);
+        l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 8);
+        l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 16);
+    }
+    if (r == 0) {
+        merge[warp][qd * 2 + 0][0] = m_run[0];
+        merge[warp][qd * 2 + 0][1] = l_run[0];
+        merge[warp][qd * 2 + 1][0] = m_run[1];
+        merge[warp][qd * 2 + 1][1] = l_run[1];
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        merge[warp][qd * 2 + 0][2 + mt * 16 + r] = acc[mt][0];
+        merge[warp][qd * 2 + 1][2 + mt * 16 + r] = acc[mt][1];
+        merge[warp][qd * 2 + 0][2 + mt * 16 + 8 + r] = acc[mt][2];
+        merge[warp][qd * 2 + 1][2 + mt * 16 + 8 + r] = acc[mt][3];
+    }
+    __syncthreads();
+    float* rec = p.workspace + (static_cast<size_t>(item) * p.splits + split) * p.rows * kRecord;
+    for (int i = tid; i < static_cast<int>(p.rows) * kRecord; i += blockDim.x) {
+        const int q = i / kRecord, cc = i % kRecord;
+        float mm = kMaskedScore;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge[w][q][0]);
+        float out;
+        if (cc < 8) {
+            out = mm > -1.0e37f ? mm * p.softmax_scale : kMaskedScore;   // natural-log units
+        } else {
+            const int src = cc < 16 ? 1 : 2 + (cc - 16);
+            out = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) out += merge[w][q][src] * exp2f((merge[w][q][0] - mm) * fac);
+        }
+        rec[i] = out;
+    }
+}
+
+}  // namespace tq
+
+using namespace tq;
+
+extern "C" int tq_reshape_and_cache_lloydmax(void* stream, const void* key, const void* value,
+                                             int8_t* key_cache, int8_t* value_cache,
+                                             float* scale_cache, const int32_t* slot_mapping,
+                                             uint32_t in_dtype, uint32_t num_tokens,
+                                             uint32_t num_kv_heads, uint32_t head_size,
+                                             uint32_t block_size, uint32_t num_blocks,
+                                             float inv_sqrt_len, uint32_t* status)
+{
+    if (!num_kv_heads || !num_blocks || !block_size || block_size % kStrip != 0 ||
+        (head_size != 128 && head_size != 256) || in_dtype > TQ_IN_BF16)
+        return TQ_ERR_INVALID_ARGUMENT;
+    if (num_tokens % kStrip != 0) return TQ_ERR_PARTIAL_STRIP;
+    if (num_tokens == 0) return TQ_OK;
+    if (!key || !value || !key_cache || !value_cache || !scale_cache || !slot_mapping)
+        return TQ_ERR_INVALID_ARGUMENT;
+    const uintptr_t align = reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value) |
+                            reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache);
+    if (align & 15u) return TQ_ERR_INVALID_ARGUMENT;
+    LmWriterParams p{key, value, reinterpret_cast<uint8_t*>(key_cache), reinterpret_cast<uint8_t*>(value_cache),
+                     scale_cache, slot_mapping, num_tokens / kStrip, num_kv_heads, block_size, num_blocks,
+                     in_dtype == TQ_IN_BF16 ? 1u : 0u, inv_sqrt_len, status};
+    const uint64_t panels = static_cast<uint64_t>(p.num_strips) * 2u * num_kv_heads;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TQ_ERR_NO_DEVICE;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const uint64_t want = (panels + 3u) / 4u, cap = static_cast<uint64_t>(sms) * 8u;
+    const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (head_size == 128) tq_lm_writer_kernel<128><<<blocks, 128, 0, s>>>(p);
+    else tq_lm_writer_kernel<256><<<blocks, 128, 0, s>>>(p);
+    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
+
+extern "C" int tq_decode_lloydmax_export(void* stream, const uint16_t* query, const int8_t* key_cache,
+                                         const int8_t* value_cache, const float* scale_cache,
+                                         const int32_t* block_tables, const int32_t* context_lens,
+                                         float* workspace, uint32_t batch, uint32_t num_heads,
+                                         uint32_t num_kv_heads, uint32_t head_size,
+                                         uint32_t block_size, uint32_t num_blocks,
+                                         uint32_t max_blocks, uint32_t splits, float softmax_scale,
+                                         uint32_t* status)
+{
+    if (!num_heads || !num_kv_heads || num_heads % num_kv_heads != 0 || !block_size ||
+        block_size % kStrip != 0 || !num_blocks || !max_blocks || !splits || splits > 16 ||
+        (head_size != 128 && head_size != 256) || num_heads / num_kv_heads > 8)
+        return TQ_ERR_INVALID_ARGUMENT;
+    if (batch == 0) return TQ_OK;
+    if (!query || !key_cache || !value_cache || !scale_cache || !block_tables || !context_lens || !workspace)
+        return TQ_ERR_INVALID_ARGUMENT;
+    const uintptr_t align = reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache) |
+                            reinterpret_cast<uintptr_t>(scale_cache);
+    if (align & 15u) return TQ_ERR_INVALID_ARGUMENT;
+    LmDecodeParams p{query, reinterpret_cast<const uint8_t*>(key_cache),
+                     reinterpret_cast<const uint8_t*>(value_cache), scale_cache, block_tables, context_lens,
+                     workspace, batch * num_kv_heads, num_kv_heads, num_heads / num_kv_heads, block_size,
+                     num_blocks, max_blocks, splits, softmax_scale, status};
+    const uint64_t grid = static_cast<uint64_t>(p.items) * splits;
+    if (grid > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (head_size == 128) tq_lm_decode_kernel<128><<<static_cast<unsigned>(grid), 128, 0, s>>>(p);
+    else tq_lm_decode_kernel<256><<<static_cast<unsigned>(grid), 128, 0, s>>>(p);
+    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}

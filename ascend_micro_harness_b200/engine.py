@@ -151,3 +151,57 @@ def splitk_combine(workspace, pi_signs, gate, output, *, items, rows, rows_strid
         _out_dtype(output), items, rows,
         rows_stride, head_size, splits, output_stage, inv_sqrt_len, _ptr(status)),
         "tq_splitk_combine")
+
+
+# ------------------------------------------------------------ stand-alone routines
+def hadamard16(x_f16, out):
+    """Y = X x H16 on 16x16 FP16 tiles (reference: cube_hadamard16); out float32/float16/bfloat16."""
+    lib = load_library()
+    _check(lib.tq_hadamard16(_stream(None), _ptr(x_f16), _ptr(out), _out_dtype(out),
+                             x_f16.numel() // 256), "tq_hadamard16")
+
+
+def lloydmax4_quantize(x, packed, recon=None):
+    """16-level Lloyd-Max codes of float32 x, packed low nibble first; recon = centroids."""
+    lib = load_library()
+    _check(lib.tq_lloydmax4_quantize(_stream(None), _ptr(x), _ptr(packed), _ptr(recon), x.numel()),
+           "tq_lloydmax4_quantize")
+
+
+def icdf_quantize(x, packed):
+    """int4 codes of 14 sigmoid(x) - 7 for float16 / bfloat16 x, packed low nibble first."""
+    lib = load_library()
+    _check(lib.tq_icdf_quantize(_stream(None), _ptr(x), _out_dtype(x), _ptr(packed), x.numel()),
+           "tq_icdf_quantize")
+
+
+# --------------------------------------------------------- Lloyd-Max cache variant
+def reshape_and_cache_lloydmax(key, value, key_cache, value_cache, scale_cache, slot_mapping, *,
+                               num_kv_heads, head_size, block_size, num_blocks, inv_sqrt_len,
+                               status=None, stream=None):
+    """Aligned writer of the variant: block-diagonal H16, RMS scale, Lloyd-Max codes."""
+    lib = load_library()
+    in_dtype = {torch.int8: 0, torch.bfloat16: 1}[key.dtype]
+    num_tokens = key.numel() // (num_kv_heads * head_size)
+    _check(lib.tq_reshape_and_cache_lloydmax(
+        _stream(stream), _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache),
+        _ptr(scale_cache), _ptr(slot_mapping), in_dtype, num_tokens, num_kv_heads, head_size,
+        block_size, num_blocks, inv_sqrt_len, _ptr(status)), "tq_reshape_and_cache_lloydmax")
+
+
+def decode_lloydmax(query, key_cache, value_cache, scale_cache, block_tables, context_lens, output,
+                    workspace, *, num_heads, num_kv_heads, head_size, block_size, num_blocks, splits,
+                    softmax_scale=1.0, output_stage=OUT_ROTATED, status=None, stream=None):
+    """Paged split-K decode over a Lloyd-Max cache: export + combine."""
+    lib = load_library()
+    batch = query.numel() // (num_heads * head_size)
+    _check(lib.tq_decode_lloydmax_export(
+        _stream(stream), _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache),
+        _ptr(block_tables), _ptr(context_lens), _ptr(workspace), batch, num_heads, num_kv_heads,
+        head_size, block_size, num_blocks, block_tables.shape[-1], splits, softmax_scale,
+        _ptr(status)), "tq_decode_lloydmax_export")
+    rows = num_heads // num_kv_heads
+    _check(lib.tq_splitk_combine(
+        _stream(stream), _ptr(workspace), None, None, _ptr(output), _out_dtype(output),
+        batch * num_kv_heads, rows, rows, head_size, splits, output_stage, 0.0, _ptr(status)),
+        "tq_splitk_combine")

@@ -217,6 +217,51 @@ int tq_splitk_combine(void* stream, const float* workspace, const float* pi_sign
                       uint32_t rows, uint32_t rows_stride, uint32_t head_size, uint32_t splits,
                       uint32_t output_stage, float inv_sqrt_len, uint32_t* status);
 
+/* ------------------------------------------------------- stand-alone routines
+ * The reference's single-purpose routines that its cache operators do not call. */
+
+/* Y = X x H16 on `tiles` 16x16 tiles, X FP16 row-major, H16[k][c] = (-1)^popcount(k & c),
+ * FP32 accumulation; y is float, half or bf16 by out_dtype (TQ_DTYPE_*). Replaces
+ * cube_hadamard16 (routines/routine_cube_hadamard16.hpp:32-84; golden model
+ * include/sim_micro_testbed.hpp:181-198). */
+int tq_hadamard16(void* stream, const uint16_t* x_f16, void* y, uint32_t out_dtype, uint32_t tiles);
+
+/* 16-level Lloyd-Max codec for N(0,1)-scaled inputs: code = number of thresholds <= x
+ * (equality to the upper bin), unsigned codes packed low nibble first; recon (may be null) =
+ * centroid of the code. count a multiple of 8. Replaces lloydmax_quantize_vf
+ * (include/routines/routine_vector_lloydmax_quantize.hpp:18-38,:190-219;
+ * tests/common/lloydmax_oracle.hpp:65-69). */
+int tq_lloydmax4_quantize(void* stream, const float* x, uint8_t* packed, float* recon, size_t count);
+
+/* Inverse-CDF int4 quantiser: y = 14 sigmoid(x) - 7, round to nearest even, saturate to
+ * [-8, 7], two's-complement nibbles packed low first. x is FP16 or BF16 (TQ_DTYPE_F16 /
+ * TQ_DTYPE_BF16), count a multiple of 8. Replaces icdf_quantize_vf
+ * (routines/routine_vector_icdf_quantize.hpp:95-132; oracle tests/cpu/icdf_fixture.hpp:124-142). */
+int tq_icdf_quantize(void* stream, const uint16_t* x, uint32_t in_dtype, uint8_t* packed, size_t count);
+
+/* ---------------------------------------------------- Lloyd-Max cache variant
+ * The ingest and decode built from those routines: block-diagonal 16x16 Hadamard rotation,
+ * per-token RMS scale (kernels/ops/turboquant/baseline/common/turboquant_codec_950.h:194-207),
+ * 16-level Lloyd-Max codes, in the same planes and page layout as the power-of-two cache.
+ * The reference pins the stages, not this composite; integer-valued inputs determine every
+ * scale bit and code (sums of squares are taken in FP64). */
+int tq_reshape_and_cache_lloydmax(void* stream, const void* key, const void* value,
+                                  int8_t* key_cache, int8_t* value_cache, float* scale_cache,
+                                  const int32_t* slot_mapping, uint32_t in_dtype, uint32_t num_tokens,
+                                  uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                                  uint32_t num_blocks, float inv_sqrt_len, uint32_t* status);
+
+/* Split-K partial records of a decode over a Lloyd-Max cache, same workspace layout as
+ * tq_decode_splitk_export (rows per record = num_heads / num_kv_heads, at most 8). Merge them
+ * with tq_splitk_combine, passing pi_signs = NULL: that selects the block-diagonal egress. */
+int tq_decode_lloydmax_export(void* stream, const uint16_t* query, const int8_t* key_cache,
+                              const int8_t* value_cache, const float* scale_cache,
+                              const int32_t* block_tables, const int32_t* context_lens,
+                              float* workspace, uint32_t batch, uint32_t num_heads,
+                              uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                              uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                              float softmax_scale, uint32_t* status);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

@@ -173,6 +173,67 @@ class Oracle:
     def hardware_threads(self):
         return self.lib.tqo_hardware_threads()
 
+    # ------------------------------------------------------------ routines
+    def hadamard16(self, x_f16):
+        """Y = X x H16 per 16x16 tile; x_f16: FP16 bits [tiles][16][16] -> float32."""
+        x = _c(x_f16, np.uint16)
+        y = np.zeros(x.size, np.float32)
+        self.lib.tqo_hadamard16(_p(x), _p(y), C.c_int(x.size // 256))
+        return y.reshape(-1, 16, 16)
+
+    def lloydmax4_tables(self):
+        c, t = np.zeros(16, np.float32), np.zeros(15, np.float32)
+        self.lib.tqo_lloydmax4_tables(_p(c), _p(t))
+        return c, t
+
+    def lloydmax4_quantize(self, x):
+        """-> (packed bytes, centroid reconstruction)."""
+        x = _c(x, np.float32).reshape(-1)
+        packed = np.zeros(x.size // 2, np.uint8)
+        recon = np.zeros(x.size, np.float32)
+        self.lib.tqo_lloydmax4_quantize(_p(x), _p(packed), _p(recon), C.c_longlong(x.size))
+        return packed, recon
+
+    def icdf_quantize(self, x_bits, bf16):
+        x = _c(x_bits, np.uint16).reshape(-1)
+        packed = np.zeros(x.size // 2, np.uint8)
+        self.lib.tqo_icdf_quantize(_p(x), C.c_int(1 if bf16 else 0), _p(packed), C.c_longlong(x.size))
+        return packed
+
+    def reshape_and_cache_lm(self, key, value, slots, H, d, S, P, inv_sqrt_len, key_cache=None,
+                             value_cache=None, scale_cache=None):
+        """Aligned writer, block-diagonal H16 + RMS scale + Lloyd-Max codes."""
+        dtype = 0 if key.dtype == np.int8 else 1
+        key, value = np.ascontiguousarray(key), np.ascontiguousarray(value)
+        T = key.size // (H * d)
+        nbytes = P * H * S * d // 2
+        kc = np.zeros(nbytes, np.uint8) if key_cache is None else key_cache
+        vc = np.zeros(nbytes, np.uint8) if value_cache is None else value_cache
+        sc = np.zeros(2 * P * H * S, np.float32) if scale_cache is None else scale_cache
+        bad = self.lib.tqo_reshape_and_cache_lm(
+            C.c_int(dtype), _p(key), _p(value), _p(_c(slots, np.int32)), C.c_int(T), C.c_int(H),
+            C.c_int(d), C.c_int(S), C.c_int(P), C.c_float(inv_sqrt_len), _p(kc), _p(vc), _p(sc))
+        return kc, vc, sc, bad
+
+    def lm_rotate_query_bf16(self, q, d):
+        q = _c(q, np.uint16)
+        out = np.zeros_like(q)
+        self.lib.tqo_lm_rotate_query_bf16(C.c_int(q.size // d), C.c_int(d), _p(q), _p(out))
+        return out
+
+    def decode_lm(self, q, key_cache, value_cache, scale_cache, block_tables, context_lens, Hq,
+                  Hkv, d, S, P, softmax_scale=1.0, output_stage=0, threads=1):
+        q = _c(q, np.uint16)
+        B = q.size // (Hq * d)
+        bt = _c(block_tables, np.int32)
+        out = np.zeros((B, Hq, d))
+        self.lib.tqo_decode_lm(
+            _p(q), _p(key_cache), _p(value_cache), _p(_c(scale_cache, np.float32)), _p(bt),
+            _p(_c(context_lens, np.int32)), C.c_int(B), C.c_int(Hq), C.c_int(Hkv), C.c_int(d),
+            C.c_int(S), C.c_int(P), C.c_int(bt.shape[-1]), C.c_float(softmax_scale),
+            C.c_int(output_stage), _p(out), C.c_int(threads))
+        return out
+
 
 class Reference:
     """The reference project's own golden models (oracle/_ref/libtq_ref.so)."""
@@ -268,6 +329,29 @@ class Reference:
 
     def lloydmax4_code(self, x):
         return self.lib.ref_lloydmax4_code(C.c_float(x))
+
+    def lloydmax_fixture(self, n, rows, boundaries):
+        out = np.zeros(n * rows, np.float32)
+        self.lib.ref_lloydmax_fixture(C.c_uint(n), C.c_uint(rows), C.c_int(1 if boundaries else 0), _p(out))
+        return out
+
+    def lloydmax4_pack(self, x):
+        x = _c(x, np.float32)
+        out = np.zeros(x.size // 2, np.uint8)
+        self.lib.ref_lloydmax4_pack(_p(x), C.c_uint(x.size), _p(out))
+        return out
+
+    def hadamard16(self, x_f16):
+        x = _c(x_f16, np.uint16)
+        y = np.zeros(256, np.float32)
+        self.lib.ref_hadamard16(_p(x), _p(y))
+        return y.reshape(16, 16)
+
+    def icdf_fixture(self, bf16, tiles):
+        bits = np.zeros(tiles * 1024, np.uint16)
+        packed = np.zeros(tiles * 512, np.uint8)
+        self.lib.ref_icdf_fixture(C.c_int(1 if bf16 else 0), C.c_uint(tiles), _p(bits), _p(packed))
+        return bits, packed
 
 
 class RefDecodeFixture:

@@ -20,6 +20,9 @@
 #include <tests/common/turboquant_oracle.hpp>
 #include <tests/common/turboquant_scatter_oracle.hpp>
 #include <include/routines/routine_vector_lloydmax_quantize.hpp>
+#include <include/sim_micro_testbed.hpp>
+#include <tests/common/lloydmax_oracle.hpp>
+#include <tests/cpu/icdf_fixture.hpp>
 
 #include <cstdint>
 #include <cstring>
@@ -272,5 +275,36 @@ void ref_lloydmax4_tables(float* centroids16, float* thresholds15)
     std::memcpy(thresholds15, ascend_micro::LloydMaxCodebook<4>::thresholds, 15 * 4);
 }
 unsigned ref_lloydmax4_code(float x) { return ascend_micro::lloydmax_code<4>(x); }
+// the reference's probe fixture (normalised Hadamard of Box-Muller normals, optional
+// threshold-boundary probes) and its packing
+void ref_lloydmax_fixture(unsigned n, unsigned rows, int boundaries, float* out)
+{
+    const auto x = lloyd::fixture(n, rows, boundaries != 0, 4);
+    std::memcpy(out, x.data(), x.size() * sizeof(float));
+}
+void ref_lloydmax4_pack(const float* x, unsigned n, std::uint8_t* out)
+{
+    std::vector<unsigned> q(n);
+    for (unsigned i = 0; i < n; ++i) q[i] = ascend_micro::lloydmax_code<4>(x[i]);
+    const auto bytes = lloyd::pack(q, 4);
+    std::memcpy(out, bytes.data(), bytes.size());
+}
+
+// ------------------------------------------------------------------ ICDF int4
+// The probe fixture (tests/cpu/icdf_fixture.hpp:178-245): `tiles` tiles of 1024 FP16/BF16
+// inputs and the 512 packed oracle bytes of each.
+void ref_icdf_fixture(int bf16, unsigned tiles, std::uint16_t* in_bits, std::uint8_t* packed)
+{
+    const auto fx = icdf::make_fixture(bf16 != 0, tiles);
+    std::memcpy(in_bits, fx.in_bits.data(), fx.in_bits.size() * 2);
+    std::memcpy(packed, fx.oracle_packed.data(), fx.oracle_packed.size());
+}
+
+// ---------------------------------------------------------------- Hadamard 16
+void ref_hadamard16(const std::uint16_t* x_f16, float* y)
+{
+    const auto r = ascend_micro::sim::golden_hadamard16(x_f16);
+    std::memcpy(y, r.data(), 256 * sizeof(float));
+}
 
 }  // extern "C"

@@ -543,6 +543,241 @@ void tqo_decode(const std::uint16_t* q, const std::uint8_t* key_cache,
     });
 }
 
+// ===================================================================== routines
+// The single-purpose routines of the reference that the two operators above do not
+// call, and the ingest/decode variant built from them (block-diagonal H16 rotation,
+// RMS scale, 16-level Lloyd-Max codes).
+
+// Y = X x H16 for 16x16 tiles, X FP16 row-major, H16[k][c] = (-1)^popcount(k & c),
+// FP32 accumulation in k order (include/sim_micro_testbed.hpp:181-198).
+static float half_to_f32(std::uint16_t h)
+{
+    const std::uint32_t sign = (h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+    std::uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) bits = sign;
+        else {
+            int e = -1;
+            std::uint32_t m = man;
+            do { ++e; m <<= 1; } while (!(m & 0x400u));
+            bits = sign | static_cast<std::uint32_t>(127 - 15 - e) << 23 | (m & 0x3ffu) << 13;
+        }
+    } else if (exp == 31) bits = sign | 0x7f800000u | man << 13;
+    else bits = sign | (exp + 112u) << 23 | man << 13;
+    float v;
+    std::memcpy(&v, &bits, 4);
+    return v;
+}
+void tqo_hadamard16(const std::uint16_t* x_f16, float* y, int tiles)
+{
+    for (int t = 0; t < tiles; ++t)
+        for (int row = 0; row < 16; ++row)
+            for (int col = 0; col < 16; ++col) {
+                float sum = 0;
+                for (int k = 0; k < 16; ++k)
+                    sum += half_to_f32(x_f16[(t * 16 + row) * 16 + k]) * static_cast<float>(hsign(k, col));
+                y[(t * 16 + row) * 16 + col] = sum;
+            }
+}
+
+// 16-level Lloyd-Max codebook for N(0,1): Gaussian conditional-mean fixed point with
+// midpoint thresholds (include/routines/routine_vector_lloydmax_quantize.hpp:18-30).
+static const float kLmCentroids[16] = {
+    -2.732589571f, -2.069017227f, -1.618046386f, -1.256231197f, -0.942340456f, -0.656759119f,
+    -0.388048299f, -0.128395030f, 0.128395030f,  0.388048299f,  0.656759119f,  0.942340456f,
+    1.256231197f,  1.618046386f,  2.069017227f,  2.732589571f};
+static const float kLmThresholds[15] = {
+    -2.400803399f, -1.843531806f, -1.437138792f, -1.099285827f, -0.799549788f, -0.522403709f,
+    -0.258221665f, 0.f,           0.258221665f,  0.522403709f,  0.799549788f,  1.099285827f,
+    1.437138792f,  1.843531806f,  2.400803399f};
+// code = #{thresholds <= x}: equality goes to the upper bin (same header :32-38).
+static inline unsigned lm_code(float x)
+{
+    unsigned q = 0;
+    for (float t : kLmThresholds) q += x >= t;
+    return q;
+}
+void tqo_lloydmax4_tables(float* centroids16, float* thresholds15)
+{
+    std::memcpy(centroids16, kLmCentroids, sizeof kLmCentroids);
+    std::memcpy(thresholds15, kLmThresholds, sizeof kLmThresholds);
+}
+// codes packed low nibble first in element order (tests/common/lloydmax_oracle.hpp:65-69);
+// recon (optional) = centroid of the code.
+void tqo_lloydmax4_quantize(const float* x, std::uint8_t* packed, float* recon, long long n)
+{
+    for (long long i = 0; i < n; ++i) {
+        const unsigned q = lm_code(x[i]);
+        if ((i & 1) == 0) packed[i / 2] = static_cast<std::uint8_t>(q);
+        else packed[i / 2] |= static_cast<std::uint8_t>(q << 4);
+        if (recon) recon[i] = kLmCentroids[q];
+    }
+}
+
+// y = 14 sigmoid(x) - 7 evaluated exactly in double, rounded once to nearest-even and
+// saturated to [-8, 7]; byte j = element 2j low, 2j+1 high (tests/cpu/icdf_fixture.hpp:5-20).
+void tqo_icdf_quantize(const std::uint16_t* x, int is_bf16, std::uint8_t* packed, long long n)
+{
+    for (long long i = 0; i < n; ++i) {
+        const double v = is_bf16 ? bf16_to_f32(x[i]) : half_to_f32(x[i]);
+        const double y = 14.0 / (1.0 + std::exp(-v)) - 7.0;
+        int q = static_cast<int>(std::nearbyint(y));
+        q = std::max(-8, std::min(7, q));
+        const unsigned nib = static_cast<unsigned>(q) & 0xFu;
+        if ((i & 1) == 0) packed[i / 2] = static_cast<std::uint8_t>(nib);
+        else packed[i / 2] |= static_cast<std::uint8_t>(nib << 4);
+    }
+}
+
+// ---- the writer built from those routines (the variant the project brief words as
+// "block-diagonal 16x16 Sylvester Hadamard, per-token FP32 scale, 16-level Lloyd-Max"):
+//   y     = x H16 per 16-channel block (integers stay exact), y_rot = y / 4
+//   scale = sqrt(sum y_rot^2) * inv_sqrt_len + 1e-20
+//           (kernels/ops/turboquant/baseline/common/turboquant_codec_950.h:194-207)
+//   code  = lloydmax(y_rot * (1 / scale)), unsigned 0..15, low nibble first (the vendored codec
+//           also multiplies by a reciprocal, same file :197-207)
+// into the same planes as the power-of-two writer (key token-major, value channel-major
+// per 16-token strip, planar FP32 scales). sum y^2 is taken in double, so for integer
+// inputs every scale bit and every code is determined.
+static void lm_token(const float* x, int d, float inv_sqrt_len, unsigned* codes, float* scale_out)
+{
+    std::vector<float> y(d);
+    double s2 = 0;
+    for (int b = 0; b < d / 16; ++b)
+        for (int col = 0; col < 16; ++col) {
+            float sum = 0;
+            for (int k = 0; k < 16; ++k) sum += x[b * 16 + k] * static_cast<float>(hsign(k, col));
+            y[b * 16 + col] = sum;
+            s2 += static_cast<double>(sum) * sum;
+        }
+    const float root = static_cast<float>(std::sqrt(s2));
+    const float scale = root * 0.25f * inv_sqrt_len + 1e-20f;
+    const float inv = 1.0f / scale;
+    for (int c = 0; c < d; ++c) codes[c] = lm_code((y[c] * 0.25f) * inv);
+    *scale_out = scale;
+}
+int tqo_reshape_and_cache_lm(int dtype, const void* key, const void* value,
+                             const std::int32_t* slots, int num_tokens, int H, int d, int S, int P,
+                             float inv_sqrt_len, std::uint8_t* key_cache,
+                             std::uint8_t* value_cache, float* scale_cache)
+{
+    if (num_tokens % kStrip || d % 16 || S % kStrip) return -1;
+    int bad = 0;
+    std::vector<float> x(d);
+    std::vector<unsigned> codes(d);
+    for (int strip = 0; strip < num_tokens / kStrip; ++strip) {
+        const std::int32_t slot0 = slots[strip * kStrip];
+        bool ok = slot0 >= 0 && slot0 % kStrip == 0 && slot0 / S < P;
+        for (int i = 0; i < kStrip; ++i) ok = ok && slots[strip * kStrip + i] == slot0 + i;
+        if (!ok) { ++bad; continue; }
+        const std::size_t page = slot0 / S, tip = slot0 % S;
+        for (int plane = 0; plane < 2; ++plane)
+            for (int h = 0; h < H; ++h) {
+                std::uint8_t* cache = plane ? value_cache : key_cache;
+                const std::size_t head_base = (page * H + h) * static_cast<std::size_t>(S) * (d / 2);
+                for (int t = 0; t < kStrip; ++t) {
+                    const std::size_t row = (static_cast<std::size_t>(strip) * kStrip + t) * H * d +
+                                            static_cast<std::size_t>(h) * d;
+                    for (int c = 0; c < d; ++c)
+                        x[c] = dtype == 0
+                                   ? static_cast<float>(static_cast<const std::int8_t*>(plane ? value : key)[row + c])
+                                   : bf16_to_f32(static_cast<const std::uint16_t*>(plane ? value : key)[row + c]);
+                    float scale;
+                    lm_token(x.data(), d, inv_sqrt_len, codes.data(), &scale);
+                    scale_cache[((static_cast<std::size_t>(plane) * P + page) * H + h) * S + tip + t] = scale;
+                    for (int c = 0; c < d; ++c) {
+                        const std::size_t nib = plane == 0
+                            ? (tip + t) * static_cast<std::size_t>(d) + c
+                            : (tip / kStrip) * static_cast<std::size_t>(kStrip) * d + static_cast<std::size_t>(c) * kStrip + t;
+                        std::uint8_t& byte = cache[head_base + nib / 2];
+                        byte = (nib & 1) ? static_cast<std::uint8_t>((byte & 0x0F) | (codes[c] << 4))
+                                         : static_cast<std::uint8_t>((byte & 0xF0) | codes[c]);
+                    }
+                }
+            }
+    }
+    return bad;
+}
+
+// q_rot = bf16((q H16 per block) / 4), the FP32 butterfly over strides 1, 2, 4, 8 inside
+// each 16-channel block (out[i] = in[i ^ s] + ((i & s) ? -in[i] : in[i])).
+static void lm_rotate_block16(float* v, int d)
+{
+    std::vector<float> tmp(d);
+    for (int s = 1; s < 16; s <<= 1) {
+        for (int i = 0; i < d; ++i) tmp[i] = v[i ^ s] + ((i & s) ? -v[i] : v[i]);
+        std::copy(tmp.begin(), tmp.end(), v);
+    }
+}
+void tqo_lm_rotate_query_bf16(int rows, int d, const std::uint16_t* q, std::uint16_t* q_rot)
+{
+    std::vector<float> v(d);
+    for (int r = 0; r < rows; ++r) {
+        for (int c = 0; c < d; ++c) v[c] = bf16_to_f32(q[r * d + c]);
+        lm_rotate_block16(v.data(), d);
+        for (int c = 0; c < d; ++c) q_rot[r * d + c] = f32_to_bf16(v[c] * 0.25f);
+    }
+}
+
+// FP64 decode over a Lloyd-Max cache: score = sum_c q_rot[c] centroid[K] * kscale * softmax_scale,
+// acc += p * vscale * centroid[V], out = (acc / l) rotated back (output_stage 1) or not (0).
+void tqo_decode_lm(const std::uint16_t* q, const std::uint8_t* key_cache,
+                   const std::uint8_t* value_cache, const float* scale_cache,
+                   const std::int32_t* block_tables, const std::int32_t* context_lens, int B, int Hq,
+                   int Hkv, int d, int S, int P, int max_blocks, float softmax_scale,
+                   int output_stage, double* out, int threads)
+{
+    const int G = Hq / Hkv;
+    auto work = [&](int begin, int end) {
+        std::vector<std::uint16_t> qr(d);
+        std::vector<double> acc(d);
+        std::vector<float> ctx(d);
+        for (int item = begin; item < end; ++item) {
+            const int b = item / Hq, hq = item % Hq, h = hq / G;
+            tqo_lm_rotate_query_bf16(1, d, q + static_cast<std::size_t>(item) * d, qr.data());
+            const int n = std::max(0, context_lens[b]);
+            double m = -std::numeric_limits<double>::infinity(), l = 0;
+            std::fill(acc.begin(), acc.end(), 0.0);
+            for (int t = 0; t < n; ++t) {
+                const std::size_t page = block_tables[static_cast<std::size_t>(b) * max_blocks + t / S];
+                const int tip = t % S;
+                const std::size_t head_base = (page * Hkv + h) * static_cast<std::size_t>(S) * (d / 2);
+                double dot = 0;
+                for (int c = 0; c < d; ++c) {
+                    const std::size_t nib = static_cast<std::size_t>(tip) * d + c;
+                    const unsigned code = (key_cache[head_base + nib / 2] >> (4 * (nib & 1))) & 0xF;
+                    dot += static_cast<double>(bf16_to_f32(qr[c])) * kLmCentroids[code];
+                }
+                const double ks = scale_cache[((0 * static_cast<std::size_t>(P) + page) * Hkv + h) * S + tip];
+                const double vs = scale_cache[((1 * static_cast<std::size_t>(P) + page) * Hkv + h) * S + tip];
+                const double s = dot * ks * softmax_scale;
+                const double mn = std::max(m, s), a = std::exp(m - mn), pw = std::exp(s - mn);
+                l = l * a + pw;
+                for (int c = 0; c < d; ++c) {
+                    const std::size_t nib = static_cast<std::size_t>(tip / kStrip) * kStrip * d +
+                                            static_cast<std::size_t>(c) * kStrip + tip % kStrip;
+                    const unsigned code = (value_cache[head_base + nib / 2] >> (4 * (nib & 1))) & 0xF;
+                    acc[c] = acc[c] * a + pw * vs * kLmCentroids[code];
+                }
+                m = mn;
+            }
+            for (int c = 0; c < d; ++c) ctx[c] = l > 0 ? static_cast<float>(acc[c] / l) : 0.f;
+            if (output_stage == 1) {
+                lm_rotate_block16(ctx.data(), d);
+                for (int c = 0; c < d; ++c) ctx[c] *= 0.25f;
+            }
+            for (int c = 0; c < d; ++c) out[static_cast<std::size_t>(item) * d + c] = ctx[c];
+        }
+    };
+    const int total = B * Hq;
+    threads = std::max(1, std::min(threads, total));
+    std::vector<std::thread> pool;
+    for (int t = 0; t < threads; ++t)
+        pool.emplace_back(work, static_cast<int>(static_cast<long long>(total) * t / threads),
+                          static_cast<int>(static_cast<long long>(total) * (t + 1) / threads));
+    for (auto& th : pool) th.join();
+}
+
 int tqo_hardware_threads() { return static_cast<int>(std::thread::hardware_concurrency()); }
 
 }  // extern "C"

@@ -71,6 +71,18 @@ def main():
     np.savez_compressed(os.path.join(HERE, "contract.npz"), partition=part, lloydmax4_centroids=c,
                         lloydmax4_thresholds=t,
                         workspace_floats=np.array([r.workspace_floats(3, 4, 8)]))
+    # the stand-alone routines: the reference's Lloyd-Max probe fixture with its packed codes,
+    # dyadic Hadamard tiles through golden_hadamard16, the ICDF probe fixture with its oracle bytes
+    lm_x = r.lloydmax_fixture(128, 4, True)
+    rng = np.random.default_rng(16)
+    h16_x = (rng.integers(-64, 65, size=(6, 16, 16)) / 8).astype(np.float16)
+    h16_y = np.stack([r.hadamard16(h16_x[i].view(np.uint16)) for i in range(6)])
+    f16_bits, f16_packed = r.icdf_fixture(False, 2)
+    bf16_bits, bf16_packed = r.icdf_fixture(True, 2)
+    np.savez_compressed(os.path.join(HERE, "routines.npz"), lm_x=lm_x, lm_packed=r.lloydmax4_pack(lm_x),
+                        lm_centroids=c, lm_thresholds=t, h16_x=h16_x.view(np.uint16), h16_y=h16_y,
+                        icdf_f16_bits=f16_bits, icdf_f16_packed=f16_packed,
+                        icdf_bf16_bits=bf16_bits, icdf_bf16_packed=bf16_packed)
     for fn in sorted(os.listdir(HERE)):
         if fn.endswith(".npz"):
             print(fn, os.path.getsize(os.path.join(HERE, fn)))

@@ -1,0 +1,182 @@
+"""The stand-alone routine kernels and the Lloyd-Max cache variant on the GPU through the
+C ABI against the CPU oracle."""
+import numpy as np
+import pytest
+
+from tests import helpers as hp
+
+pytestmark = pytest.mark.gpu
+
+
+def test_hadamard16_tiles_bit_exact(cuda, oracle):
+    import torch
+    import ascend_micro_harness_b200 as tq
+    rng = np.random.default_rng(5)
+    x = (rng.integers(-256, 257, size=(333, 16, 16)) / 32).astype(np.float16)      # dyadic: exact sums
+    want = oracle.hadamard16(x.view(np.uint16))
+    xd = torch.from_numpy(x).to(cuda)
+    for dt in (torch.float32, torch.float16, torch.bfloat16):
+        y = torch.full((333, 16, 16), float("nan"), dtype=dt, device=cuda)
+        tq.hadamard16(xd, y)
+        torch.cuda.synchronize()
+        assert torch.equal(y.cpu(), torch.from_numpy(want).to(dt))
+    g = np.random.default_rng(6).standard_normal((64, 16, 16)).astype(np.float16)   # general inputs
+    y = torch.zeros((64, 16, 16), dtype=torch.float32, device=cuda)
+    tq.hadamard16(torch.from_numpy(g).to(cuda), y)
+    assert np.allclose(y.cpu().numpy(), oracle.hadamard16(g.view(np.uint16)), rtol=0, atol=2e-6 * 16 * 8)
+
+
+def test_lloydmax4_codes_and_reconstruction_bit_exact(cuda, oracle):
+    import torch
+    import ascend_micro_harness_b200 as tq
+    rng = np.random.default_rng(7)
+    _, t = oracle.lloydmax4_tables()
+    x = rng.standard_normal(1 << 16).astype(np.float32)
+    edge = np.concatenate([t, np.nextafter(t, np.inf, dtype=np.float32),
+                           np.nextafter(t, -np.inf, dtype=np.float32), np.float32([0.0, -0.0, 1e30, -1e30, np.nan])])
+    x[: edge.size] = edge
+    packed_want, recon_want = oracle.lloydmax4_quantize(x)
+    xd = torch.from_numpy(x).to(cuda)
+    packed = torch.zeros(x.size // 2, dtype=torch.uint8, device=cuda)
+    recon = torch.zeros(x.size, dtype=torch.float32, device=cuda)
+    tq.lloydmax4_quantize(xd, packed, recon)
+    torch.cuda.synchronize()
+    assert np.array_equal(packed.cpu().numpy(), packed_want)
+    assert np.array_equal(recon.cpu().numpy(), recon_want)
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_icdf_quantiser_matches_the_reference_fixture(cuda, oracle, bf16):
+    """The reference's own probe inputs (every value keeps 1/16 of margin to a rounding
+    boundary), regenerated through the golden file."""
+    import os
+    import torch
+    import ascend_micro_harness_b200 as tq
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "routines.npz"))
+    tag = "bf16" if bf16 else "f16"
+    bits, want = gold[f"icdf_{tag}_bits"], gold[f"icdf_{tag}_packed"]
+    x = torch.from_numpy(bits.view(np.int16)).to(cuda).view(torch.bfloat16 if bf16 else torch.float16)
+    packed = torch.zeros(bits.size // 2, dtype=torch.uint8, device=cuda)
+    tq.icdf_quantize(x, packed)
+    torch.cuda.synchronize()
+    assert np.array_equal(packed.cpu().numpy(), want)
+    assert np.array_equal(want, oracle.icdf_quantize(bits, bf16))
+
+
+def _lm_write(cuda, tq, torch, k, v, slots, H, d, S, P):
+    tdt = torch.int8 if k.dtype == np.int8 else torch.bfloat16
+    kd = torch.from_numpy(k.view(np.int8 if k.dtype == np.int8 else np.int16)).to(cuda)
+    vd = torch.from_numpy(v.view(np.int8 if v.dtype == np.int8 else np.int16)).to(cuda)
+    if tdt == torch.bfloat16:
+        kd, vd = kd.view(torch.bfloat16), vd.view(torch.bfloat16)
+    kc = torch.full((P * H * S * d // 2,), 0xAA, dtype=torch.uint8, device=cuda)
+    vc = torch.full_like(kc, 0xAA)
+    sc = torch.zeros(2 * P * H * S, dtype=torch.float32, device=cuda)
+    sc.view(torch.int32).fill_(0x7FC0BEEF)
+    st = torch.zeros(1, dtype=torch.int32, device=cuda)
+    tq.reshape_and_cache_lloydmax(kd, vd, kc, vc, sc, torch.from_numpy(slots).to(cuda), num_kv_heads=H,
+                                  head_size=d, block_size=S, num_blocks=P, inv_sqrt_len=hp.inv_sqrt_len(d),
+                                  status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    return kc.cpu().numpy(), vc.cpu().numpy(), sc.cpu().numpy()
+
+
+@pytest.mark.parametrize("d", [128, 256])
+@pytest.mark.parametrize("dtype", ["int8", "bf16"])
+def test_lloydmax_writer_bit_exact_on_integer_inputs(cuda, oracle, d, dtype):
+    import torch
+    import ascend_micro_harness_b200 as tq
+    rng = np.random.default_rng(d + len(dtype))
+    H, S, strips = 3, 32, 37
+    T = strips * 16
+    if dtype == "int8":
+        k, v = hp.int8_activations(rng, T, H, d)
+    else:
+        k, v = hp.gaussian_outlier_activations(rng, T, H, d, integer=True)
+    k[16:32] = 0                                   # an all-zero strip: scale 1e-20, code 8
+    slots, P = hp.fragmented_slots(strips, 16)
+    P = (P * 16 + S - 1) // S + 1
+    got = _lm_write(cuda, tq, torch, k, v, slots, H, d, S, P)
+    ekc = np.full(P * H * S * d // 2, 0xAA, np.uint8)
+    evc = np.full_like(ekc, 0xAA)
+    esc = np.zeros(2 * P * H * S, np.float32)
+    esc.view(np.uint32)[:] = 0x7FC0BEEF
+    _, _, _, bad = oracle.reshape_and_cache_lm(k, v, slots, H, d, S, P, hp.inv_sqrt_len(d), ekc, evc, esc)
+    assert bad == 0
+    assert np.array_equal(got[2].view(np.uint32), esc.view(np.uint32)), "scale bits"
+    assert np.array_equal(got[0], ekc), f"key codes differ in {(got[0] != ekc).sum()} bytes"
+    assert np.array_equal(got[1], evc), f"value codes differ in {(got[1] != evc).sum()} bytes"
+
+
+def test_lloydmax_writer_gaussian_inputs_within_one_code_at_ties(cuda, oracle):
+    """Non-integer inputs: the reference pins no accumulation order for this composite; codes
+    may differ only where the normalised value sits on a threshold."""
+    import torch
+    import ascend_micro_harness_b200 as tq
+    rng = np.random.default_rng(3)
+    H, d, S, strips = 8, 128, 16, 64
+    k, v = hp.gaussian_outlier_activations(rng, strips * 16, H, d)
+    slots, P = hp.page_permutation_slots(rng, strips, S)
+    got = _lm_write(cuda, tq, torch, k, v, slots, H, d, S, P)
+    ekc, evc, esc, _ = oracle.reshape_and_cache_lm(k, v, slots, H, d, S, P, hp.inv_sqrt_len(d))
+    assert np.allclose(got[2], esc, rtol=3e-7, atol=0)
+    for a, b in ((got[0], ekc), (got[1], evc)):
+        ca = np.stack([a & 15, a >> 4], 1).astype(np.int32)
+        cb = np.stack([b & 15, b >> 4], 1).astype(np.int32)
+        assert np.abs(ca - cb).max() <= 1
+        assert (ca != cb).mean() < 1e-4
+
+
+@pytest.mark.parametrize("d,S", [(128, 16), (256, 64)])
+def test_lloydmax_decode_matches_fp64_oracle(cuda, oracle, d, S):
+    import torch
+    import ascend_micro_harness_b200 as tq
+    rng = np.random.default_rng(d)
+    Hq, Hkv = 8, 2
+    ctx = np.array([1, 17, 300, 1023, 0, 513], np.int64)
+    pages = (ctx + S - 1) // S
+    P = int(pages.sum()) + 2
+    perm = rng.permutation(P)
+    tables = np.zeros((len(ctx), max(1, int(pages.max()))), np.int32)
+    kc = np.full(P * Hkv * S * d // 2, 0xAA, np.uint8)
+    vc = np.full_like(kc, 0xAA)
+    sc = np.full(2 * P * Hkv * S, np.nan, np.float32)
+    at = 0
+    for b, n in enumerate(pages):
+        tables[b, :n] = perm[at:at + n]
+        at += int(n)
+        if n == 0:
+            continue
+        T = int(n) * S
+        x = rng.standard_normal((2, T, Hkv * d)).astype(np.float32)
+        slots = (tables[b, :n, None] * S + np.arange(S)[None, :]).reshape(-1).astype(np.int32)
+        oracle.reshape_and_cache_lm(hp.bf16_from_f32(x[0]), hp.bf16_from_f32(x[1]), slots, Hkv, d, S, P,
+                                    hp.inv_sqrt_len(d), kc, vc, sc)
+        # dead slots of the last page: poison the scales again
+        dead = slots[int(ctx[b]):]
+        for kv in range(2):
+            for h in range(Hkv):
+                idx = ((kv * P + dead // S) * Hkv + h) * S + dead % S
+                sc[idx] = np.nan
+    q = hp.bf16_from_f32(rng.standard_normal((len(ctx), Hq, d)).astype(np.float32))
+    scale = float(1 / np.sqrt(d))
+    for stage in (0, 1):
+        want = oracle.decode_lm(q, kc, vc, sc, tables, ctx.astype(np.int32), Hq, Hkv, d, S, P, scale, stage,
+                                threads=8)
+        for splits in (1, 3):
+            ws = torch.full((len(ctx) * Hkv * splits * (Hq // Hkv) * (16 + d),), float("nan"), device=cuda)
+            out = torch.zeros((len(ctx), Hq, d), dtype=torch.float32, device=cuda)
+            st = torch.zeros(1, dtype=torch.int32, device=cuda)
+            tq.decode_lloydmax(torch.from_numpy(q.view(np.int16)).to(cuda).view(torch.bfloat16),
+                               torch.from_numpy(kc).to(cuda), torch.from_numpy(vc).to(cuda),
+                               torch.from_numpy(sc).to(cuda), torch.from_numpy(tables).to(cuda),
+                               torch.from_numpy(ctx.astype(np.int32)).to(cuda), out, ws, num_heads=Hq,
+                               num_kv_heads=Hkv, head_size=d, block_size=S, num_blocks=P, splits=splits,
+                               softmax_scale=scale, output_stage=stage, status=st)
+            torch.cuda.synchronize()
+            got = out.cpu().numpy()
+            assert int(st.item()) == 0 and np.isfinite(got).all()
+            err = np.abs(got - want) / (1e-3 + 2e-3 * np.abs(want))
+            assert err.max() <= 1.0, f"stage {stage} splits {splits}: {err.max():.2f}x the tolerance"
+            assert (got[4] == 0).all()
