@@ -83,3 +83,23 @@ def test_geometry_is_refused_before_any_launch():
     assert lib.tq_decode_splitk_partials(*part, 1, 1, 16, 256, 128, 8, 4, 2, 0, 2, 300, 0.0625, 1.0, None) == 1
     assert lib.tq_decode_splitk_partials(*part, 1, 1, 16, 256, 128, 8, 4, 17, 0, 2, 0, 0.0625, 1.0, None) == 1
     assert lib.tq_status_string(2).decode().startswith("num_tokens")
+
+
+def test_routine_and_lloydmax_entries_refuse_bad_arguments_on_the_host():
+    from ascend_micro_harness_b200._lib import load_library
+    lib = load_library()
+    p = C.c_void_p(16)   # never dereferenced
+    assert lib.tq_hadamard16(None, p, p, 3, 4) == 1               # no such output type
+    assert lib.tq_hadamard16(None, p, p, 2, 0) == 0               # nothing to do
+    assert lib.tq_lloydmax4_quantize(None, p, p, None, 12) == 1   # not a multiple of 8
+    assert lib.tq_lloydmax4_quantize(None, C.c_void_p(20), p, None, 16) == 1   # x not 16-byte aligned
+    assert lib.tq_icdf_quantize(None, p, 2, p, 16) == 1           # float32 input is not served
+    assert lib.tq_icdf_quantize(None, p, 1, p, 0) == 0
+    lm = [None, p, p, p, p, p, p]
+    assert lib.tq_reshape_and_cache_lloydmax(*lm, 1, 24, 1, 128, 16, 4, 0.1, None) == 2   # partial strip
+    assert lib.tq_reshape_and_cache_lloydmax(*lm, 1, 32, 1, 64, 16, 4, 0.1, None) == 1    # head size
+    assert lib.tq_reshape_and_cache_lloydmax(*lm, 2, 32, 1, 128, 16, 4, 0.1, None) == 1   # dtype
+    dec = [None, p, p, p, p, p, p, p]
+    assert lib.tq_decode_lloydmax_export(*dec, 1, 48, 4, 128, 16, 8, 4, 2, 1.0, None) == 1  # 12 rows per KV head
+    assert lib.tq_decode_lloydmax_export(*dec, 1, 32, 8, 128, 16, 8, 4, 17, 1.0, None) == 1  # 17 splits
+    assert lib.tq_decode_lloydmax_export(*dec, 0, 32, 8, 128, 16, 8, 4, 2, 1.0, None) == 0   # empty batch
