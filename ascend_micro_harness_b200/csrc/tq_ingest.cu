@@ -473,13 +473,15 @@ static int reshape_and_cache(void* stream, const void* key, const void* value,
     p.status = status;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    cudaError_t err;
-    if (head_size == 128 && !warp_mma_only)
-        err = launch_ingest_umma(s, p, in_dtype == TQ_IN_BF16);
-    else if (head_size == 128)
-        err = in_dtype == TQ_IN_BF16 ? launch_ingest<128, true>(s, p) : launch_ingest<128, false>(s, p);
-    else
-        err = in_dtype == TQ_IN_BF16 ? launch_ingest<256, true>(s, p) : launch_ingest<256, false>(s, p);
+    cudaError_t err = cudaErrorNotSupported;
+    if (head_size == 128 && !warp_mma_only) err = launch_ingest_umma(s, p, in_dtype == TQ_IN_BF16);
+    if (err == cudaErrorNotSupported) {
+        // head size 256, the explicit warp-MMA entry, or a driver without tensor maps
+        if (head_size == 128)
+            err = in_dtype == TQ_IN_BF16 ? launch_ingest<128, true>(s, p) : launch_ingest<128, false>(s, p);
+        else
+            err = in_dtype == TQ_IN_BF16 ? launch_ingest<256, true>(s, p) : launch_ingest<256, false>(s, p);
+    }
     return err == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 

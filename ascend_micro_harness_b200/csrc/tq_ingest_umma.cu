@@ -11,10 +11,11 @@
 // 128 x 128 x 128 tensor-core product instead of MMAs plus register butterflies:
 //   * a persistent CTA builds M once in shared memory (K-major, 128-byte swizzle); its two
 //     groups of 128 threads then walk tiles independently, each with its own tile buffer,
-//     128 tensor-memory columns, completion barrier and named CTA barrier. The activations
-//     of a group's next tile are requested with 16-byte cp.async as soon as the tensor core
-//     has consumed the current ones; four groups share an SM, so one group's waits are
-//     another's work;
+//     128 tensor-memory columns, completion barriers and named CTA barrier. The activations
+//     of a group's next tile are fetched by TMA (one 128-row x 128-byte box per K block,
+//     hardware 128-byte swizzle, rows past the last token filled with zeros) as soon as the
+//     tensor core has consumed the current ones; four groups share an SM, so one group's
+//     waits are another's work;
 //   * key plane:   D[token][channel] = X M^T  -- a thread reads its token's 128 rotated
 //     channels out of tensor memory, so absmax, scale, rounding and the packing of the
 //     token's 64-byte page row are all thread-local;
@@ -30,6 +31,8 @@
 // Every wait on the tensor core's completion barrier is bounded by a clock budget; when it
 // runs out the kernel stops storing, reports TQ_STATUS_WAIT_EXPIRED, frees its tensor
 // memory and returns.
+#include <cuda.h>   // CUtensorMap and the encode entry point's signature; nothing is linked from libcuda
+
 #include "tq_ingest.cuh"
 
 namespace tq {
@@ -173,9 +176,17 @@ __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fenc
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
-__device__ __forceinline__ void cp16(uint32_t dst, const void* src)
+// One 2-D box of the activation tensor into shared memory; completion is counted in bytes
+// on `mbar`. No multicast: the box goes to this CTA only.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t mbar)
 {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbar), "r"(bytes) : "memory");
 }
 
 // max(a, |b|, |c|) and the plain three-input forms.
@@ -227,7 +238,9 @@ __device__ __forceinline__ void group_sync(int group)
 }
 
 template <bool BF16>
-__global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umma_kernel(const IngestParams p)
+__global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm)
+tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap key_map,
+                      const __grid_constant__ CUtensorMap value_map)
 {
     using C = Cfg<BF16>;
     extern __shared__ uint8_t smem_raw[];
@@ -241,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
     float* inv_s = reinterpret_cast<float*>(small);                           // per token: 2^(2-e)
     float* add_s = inv_s + kTileTokens;                                       // per token: rounding addend
     unsigned long long* strip_off = reinterpret_cast<unsigned long long*>(add_s + kTileTokens);  // [8]
-    uint64_t* mbar = reinterpret_cast<uint64_t*>(strip_off + 8);
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(strip_off + 8);   // [0]: products done, [1]: tile landed
     uint32_t* shared_words = reinterpret_cast<uint32_t*>(base + (1 + kGroups) * C::kTileBytes +
                                                          kGroups * (2 * kTileTokens * 4 + 8 * 8 + 64));
     uint32_t* tmem_slot = shared_words;
@@ -254,6 +267,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
     // ---- one-time set-up: barriers, tensor memory, the rotation matrix
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(mbar)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(mbar + 1)));
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         if (group == 0) *abort_flag = 0u;
     }
@@ -299,55 +313,51 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_group = tmem_base + static_cast<uint32_t>(group) * kGroupCols;
     const uint32_t acc = tmem_group + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lanes
-    const uint32_t mbar_s = smem_addr(mbar), x_tile_s = smem_addr(x_tile), m_tile_s = smem_addr(m_tile);
+    const uint32_t mbar_s = smem_addr(mbar), tma_bar_s = smem_addr(mbar + 1);
+    const uint32_t x_tile_s = smem_addr(x_tile), m_tile_s = smem_addr(m_tile);
 
-    // ---- per-thread copy plan: 16-byte chunk `chunk` of rows r0, r0 + R, ...
-    constexpr int kChunksPerRow = C::kRowBytes / 16;        // 8 or 16
-    constexpr int kRowsPerPass = kGroupThreads / kChunksPerRow;  // 16 or 8
-    const int chunk = tid % kChunksPerRow, r0 = tid / kChunksPerRow;
-    const uint32_t dst0 = x_tile_s + (chunk >> 3) * C::kBlockBytes + r0 * 128 + (((chunk & 7) ^ (r0 & 7)) << 4);
-    const size_t src0 = static_cast<size_t>(r0) * row_pitch + chunk * 16;
-    const size_t pass_pitch = static_cast<size_t>(kRowsPerPass) * row_pitch;
-
+    // The group's thread 0 fetches a tile: one box per 128-byte K block, rows = the tile's 128
+    // tokens (past the end of the tensor: zeros, never stored), x = the head's first channel.
     auto load_tile = [&](uint32_t item, uint32_t plane) {
+        if (tid != 0) return;
         const TileId id = tile_of(p, item, plane);
-        const uint32_t first = id.tok_tile * kTileTokens;
-        const uint32_t live = num_tokens - first;
-        const uint8_t* tile_src = static_cast<const uint8_t*>(id.plane == 0 ? p.key : p.value) +
-                                  static_cast<size_t>(first) * row_pitch +
-                                  static_cast<size_t>(id.head) * C::kRowBytes;
-        if (live >= static_cast<uint32_t>(kTileTokens)) {
-            const uint8_t* src = tile_src + src0;
+        const CUtensorMap* map = plane == 0 ? &key_map : &value_map;
+        mbar_expect_tx(tma_bar_s, C::kTileBytes);
 #pragma unroll
-            for (int pass = 0; pass < kTileTokens / kRowsPerPass; ++pass)
-                cp16(dst0 + pass * kRowsPerPass * 128, src + pass * pass_pitch);
-        } else {
-            // a short final tile: rows past its last token re-read that token's row; what
-            // they produce is never stored
-#pragma unroll 1
-            for (int pass = 0; pass < kTileTokens / kRowsPerPass; ++pass) {
-                const uint32_t row = min(static_cast<uint32_t>(pass * kRowsPerPass + r0), live - 1u);
-                cp16(dst0 + pass * kRowsPerPass * 128, tile_src + static_cast<size_t>(row) * row_pitch + chunk * 16);
-            }
-        }
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        for (int blk = 0; blk < C::kBlocks; ++blk)
+            tma_load_2d(x_tile_s + blk * C::kBlockBytes, map,
+                        static_cast<int>(id.head * 128u + blk * (128 / C::kElem)),
+                        static_cast<int>(id.tok_tile * kTileTokens), tma_bar_s);
     };
 
     // One product into the accumulator columns, then the bounded wait for it.
     // transposed = false: D[token][channel] = X M^T; true: D'[channel][token] = M X^T.
-    uint32_t parity = 0;
+    uint32_t parity = 0, tma_parity = 0;
     bool healthy = true;
-    auto product = [&](bool transposed) {
+    auto bounded_wait = [&](uint32_t bar, uint32_t par) {
+        bool done = mbar_try_wait(bar, par);
+        if (!done) {
+            const long long t0 = clock64();
+            do {
+                done = mbar_try_wait(bar, par);
+            } while (!done && clock64() - t0 < kWaitBudget);
+        }
+        return done;
+    };
+    auto product = [&](bool transposed, bool fresh_tile) {
         if constexpr (!BF16) {
             // INT32 accumulators start at the bit pattern of 1.5 * 2^23
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_fill32(acc + c * 32, kBiasBits);
             tmem_wait_st();
         }
-        fence_async_smem();      // cp.async and st.shared data -> visible to the tensor core
         fence_before_sync();
         group_sync(group);
         if (tid == 0) {
+            if (fresh_tile) {   // the TMA boxes of this tile have landed (same proxy as the MMA reads)
+                if (!bounded_wait(tma_bar_s, tma_parity)) *abort_flag = 1u;
+                tma_parity ^= 1u;
+            }
             fence_after_sync();
 #pragma unroll
             for (int k = 0; k < C::kKSteps; ++k) {
@@ -357,14 +367,8 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
             }
             umma_commit(mbar_s);
         }
-        bool done = mbar_try_wait(mbar_s, parity);
-        if (!done) {
-            const long long t0 = clock64();
-            do {
-                done = mbar_try_wait(mbar_s, parity);
-            } while (!done && clock64() - t0 < kWaitBudget);
-        }
-        if (!done) {
+        const bool done = bounded_wait(mbar_s, parity);
+        if (!done || *abort_flag != 0u) {
             healthy = false;
             *abort_flag = 1u;
             report(p.status, TQ_STATUS_WAIT_EXPIRED);
@@ -385,8 +389,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
         const bool tok_live = tok < num_tokens;
         const int32_t slot = tok_live ? __ldg(p.slots + tok) : -1;
 
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");   // this thread's part of the tile
-        product(false);
+        product(false, true);
         if (id.plane == 0) load_tile(item, 1);                    // the tile is consumed: refill
 
         const int32_t slot0 = __shfl_sync(0xffffffffu, slot, lane & 16);
@@ -490,7 +493,7 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
             add_s[tid] = addend;
             if ((lane & 15) == 0)
                 strip_off[tid >> 4] = strip_ok ? static_cast<unsigned long long>(block_off) : ~0ull;
-            product(true);   // its barrier also publishes the constants and ends pass 1's reads
+            product(true, false);   // its barrier also publishes the constants and ends pass 1's reads
             if (item + item_step < items) load_tile(item + item_step, 0);
             const bool store = healthy;
             uint32_t ua[16], ub[16];
@@ -545,11 +548,46 @@ __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm) tq_ingest_umm
         group_sync(group);
         if (*abort_flag != 0u) break;
     }
-    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
     fence_before_sync();
     __syncthreads();
     if (threadIdx.x < 32)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+}
+
+// cuTensorMapEncodeTiled through the runtime's entry-point lookup (no link against libcuda).
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                 CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                 CUtensorMapFloatOOBfill);
+EncodeTiled encode_tiled()
+{
+    static EncodeTiled fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return reinterpret_cast<EncodeTiled>(ptr);
+    }();
+    return fn;
+}
+
+// The activation tensor [num_tokens][H * 128] as a 2-D map whose box is 128 rows of one
+// 128-byte K block, stored with the 128-byte swizzle the MMA descriptors expect.
+template <bool BF16>
+bool activation_map(CUtensorMap* map, const void* base, uint32_t num_tokens, uint32_t H)
+{
+    const EncodeTiled fn = encode_tiled();
+    if (fn == nullptr) return false;
+    constexpr uint32_t elem = BF16 ? 2 : 1;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(H) * 128u, num_tokens};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(H) * 128u * elem};
+    const cuuint32_t box[2] = {128u / elem, kTileTokens};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return fn(map, BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+              const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <bool BF16>
@@ -568,10 +606,14 @@ cudaError_t launch(cudaStream_t stream, const IngestParams& p)
     }
     const uint64_t tiles = static_cast<uint64_t>((p.num_strips + 7u) / 8u) * p.H;   // (tile, head) items
     if (tiles == 0) return cudaSuccess;
+    alignas(64) CUtensorMap key_map, value_map;
+    if (!activation_map<BF16>(&key_map, p.key, p.num_strips * kStrip, p.H) ||
+        !activation_map<BF16>(&value_map, p.value, p.num_strips * kStrip, p.H))
+        return cudaErrorNotSupported;
     const uint32_t resident = static_cast<uint32_t>(sms) * C::kCtasPerSm;   // persistent: one resident wave
     const uint64_t wanted = (tiles + kGroups - 1) / kGroups;
     const uint32_t blocks = wanted < resident ? static_cast<uint32_t>(wanted) : resident;
-    tq_ingest_umma_kernel<BF16><<<blocks, kThreads, C::kSmem, stream>>>(p);
+    tq_ingest_umma_kernel<BF16><<<blocks, kThreads, C::kSmem, stream>>>(p, key_map, value_map);
     return cudaGetLastError();
 }
 
