@@ -27,21 +27,25 @@ __device__ __forceinline__ float lloydmax4_centroid(unsigned q)
     return q >= 8u ? m : -m;
 }
 
-// code = #{thresholds <= x}, equality to the upper bin (same header :32-38). With
-// a = |x|: for x >= 0 (including -0) that is 8 + #{j : a >= t_j}; for x < 0 it is
-// #{j : a <= t_j}. A NaN compares false everywhere and gets code 0, as in the reference.
+// code = #{thresholds <= x}, equality to the upper bin (same header :32-38). With a = |x|
+// and n = #{j : a >= t_j} over the seven positive thresholds: for x >= 0 (including -0) the
+// code is 8 + n; for x < 0 it is #{j : a <= t_j} = 7 - #{j : a > t_j}, and a > t is
+// nextdown(a) >= t, so one three-step binary search serves both signs. A NaN compares false
+// everywhere and gets code 0, as in the reference.
 __device__ __forceinline__ unsigned lloydmax4_code(float x)
 {
-    const float a = fabsf(x);
     const bool nonneg = x >= 0.0f;
-    unsigned up = 0, down = 0;
-#pragma unroll
-    for (int j = 1; j < 8; ++j) {
-        const float t = lloydmax4_positive_threshold(j);
-        up += a >= t ? 1u : 0u;
-        down += a <= t ? 1u : 0u;
-    }
-    return nonneg ? 8u + up : down;
+    // |x|, stepped down by one ulp for negative x (x < 0 implies |x| > 0: no wrap)
+    const float a = __uint_as_float((__float_as_uint(x) & 0x7FFFFFFFu) - (x < 0.0f ? 1u : 0u));
+    const bool c4 = a >= lloydmax4_positive_threshold(4);
+    const float ta = c4 ? lloydmax4_positive_threshold(6) : lloydmax4_positive_threshold(2);
+    const bool c2 = a >= ta;
+    const float tb = c4 ? (c2 ? lloydmax4_positive_threshold(7) : lloydmax4_positive_threshold(5))
+                        : (c2 ? lloydmax4_positive_threshold(3) : lloydmax4_positive_threshold(1));
+    const bool c1 = a >= tb;
+    const unsigned n = (c4 ? 4u : 0u) + (c2 ? 2u : 0u) + (c1 ? 1u : 0u);
+    const unsigned code = nonneg ? 8u + n : 7u - n;
+    return x != x ? 0u : code;
 }
 
 // x <- x H16 for 16 values held by one thread (H16[k][c] = (-1)^popcount(k & c); symmetric),

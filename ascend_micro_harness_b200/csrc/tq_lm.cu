@@ -12,8 +12,10 @@
 //            softmax_scale, acc += p * vscale * centroid[V], per-split {m x8, l x8, acc[d]}
 //            records in the layout of include/turboquant_splitk_contract.hpp:23-27, merged by
 //            the ordinary combine kernel with the block-diagonal egress.
-// The reference pins the stages (Hadamard tile, codec), not this composite; sums of squares
-// are taken in FP64 so that integer-valued inputs determine every scale bit and every code.
+// The reference pins the stages (Hadamard tile, codec), not this composite. Its arithmetic is
+// fixed here operation by operation (butterfly order, squares summed four at a time in FP32,
+// the groups in FP64 per half of the channels, IEEE sqrt / divide / multiply without fusion),
+// so the CPU restatement reproduces every scale bit and every code for any finite input.
 #include <cuda_fp16.h>
 
 #include "tq_lloydmax.cuh"
@@ -102,12 +104,22 @@ __global__ void __launch_bounds__(128) tq_lm_writer_kernel(const LmWriterParams 
             for (int i = 0; i < 16; ++i) v[i] = y[b * 16 + i];
             hadamard16_inplace(v);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                y[b * 16 + i] = v[i];
-                s2 += static_cast<double>(v[i]) * static_cast<double>(v[i]);
+            for (int i = 0; i < 16; ++i) y[b * 16 + i] = v[i];
+            // squares summed four at a time in FP32 (exact for int8-range integers: 4 * 2032^2
+            // < 2^24), the groups in FP64, in channel order
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+                float q4 = __fmul_rn(v[i], v[i]);
+                q4 = __fadd_rn(q4, __fmul_rn(v[i + 1], v[i + 1]));
+                q4 = __fadd_rn(q4, __fmul_rn(v[i + 2], v[i + 2]));
+                q4 = __fadd_rn(q4, __fmul_rn(v[i + 3], v[i + 3]));
+                s2 += static_cast<double>(q4);
             }
         }
-        s2 += __shfl_xor_sync(0xffffffffu, s2, 16);   // the other half of the token's channels
+        {   // first half of the channels + second half, in that order on both lanes
+            const double other = __shfl_xor_sync(0xffffffffu, s2, 16);
+            s2 = hsel == 0 ? s2 + other : other + s2;
+        }
         const float root = static_cast<float>(sqrt(s2));
         const float scale = __fadd_rn(__fmul_rn(__fmul_rn(root, 0.25f), p.inv_sqrt_len), 1e-20f);
         const float inv = __fdiv_rn(1.0f, scale);

@@ -637,23 +637,37 @@ void tqo_icdf_quantize(const std::uint16_t* x, int is_bf16, std::uint8_t* packed
 //   code  = lloydmax(y_rot * (1 / scale)), unsigned 0..15, low nibble first (the vendored codec
 //           also multiplies by a reciprocal, same file :197-207)
 // into the same planes as the power-of-two writer (key token-major, value channel-major
-// per 16-token strip, planar FP32 scales). sum y^2 is taken in double, so for integer
-// inputs every scale bit and every code is determined.
+// per 16-token strip, planar FP32 scales). Every operation and its order is fixed (no fused
+// multiply-add), so the kernel reproduces scale bits and codes for any finite input.
 static void lm_token(const float* x, int d, float inv_sqrt_len, unsigned* codes, float* scale_out)
 {
-    std::vector<float> y(d);
-    double s2 = 0;
-    for (int b = 0; b < d / 16; ++b)
-        for (int col = 0; col < 16; ++col) {
-            float sum = 0;
-            for (int k = 0; k < 16; ++k) sum += x[b * 16 + k] * static_cast<float>(hsign(k, col));
-            y[b * 16 + col] = sum;
-            s2 += static_cast<double>(sum) * sum;
+    // y = x H16 per block as the radix-2 butterfly (strides 1, 2, 4, 8), the order the kernel
+    // uses; squares summed four at a time in FP32, the groups in FP64 per half of the channels
+    std::vector<float> y(x, x + d), tmp(d);
+    for (int s = 1; s < 16; s <<= 1) {
+        for (int i = 0; i < d; ++i) tmp[i] = (i & s) ? y[i ^ s] - y[i] : y[i ^ s] + y[i];
+        y = tmp;
+    }
+    double half[2] = {0, 0};
+    for (int h = 0; h < 2; ++h)
+        for (int g = h * (d / 8); g < (h + 1) * (d / 8); ++g) {
+            volatile float q4 = y[4 * g] * y[4 * g];
+            for (int i = 1; i < 4; ++i) {
+                volatile float sq = y[4 * g + i] * y[4 * g + i];
+                q4 = q4 + sq;
+            }
+            half[h] += static_cast<double>(q4);
         }
+    const double s2 = half[0] + half[1];
     const float root = static_cast<float>(std::sqrt(s2));
-    const float scale = root * 0.25f * inv_sqrt_len + 1e-20f;
+    volatile float scaled = root * 0.25f;
+    scaled = scaled * inv_sqrt_len;
+    const float scale = scaled + 1e-20f;
     const float inv = 1.0f / scale;
-    for (int c = 0; c < d; ++c) codes[c] = lm_code((y[c] * 0.25f) * inv);
+    for (int c = 0; c < d; ++c) {
+        volatile float yr = y[c] * 0.25f;
+        codes[c] = lm_code(yr * inv);
+    }
     *scale_out = scale;
 }
 int tqo_reshape_and_cache_lm(int dtype, const void* key, const void* value,

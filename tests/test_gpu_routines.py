@@ -109,9 +109,10 @@ def test_lloydmax_writer_bit_exact_on_integer_inputs(cuda, oracle, d, dtype):
     assert np.array_equal(got[1], evc), f"value codes differ in {(got[1] != evc).sum()} bytes"
 
 
-def test_lloydmax_writer_gaussian_inputs_within_one_code_at_ties(cuda, oracle):
-    """Non-integer inputs: the reference pins no accumulation order for this composite; codes
-    may differ only where the normalised value sits on a threshold."""
+def test_lloydmax_writer_gaussian_inputs_bit_exact(cuda, oracle):
+    """Non-integer inputs: the reference pins no accumulation order for this composite, so the
+    order is fixed here operation by operation and the CPU restatement follows it; scale bits
+    and codes are then determined for any finite input."""
     import torch
     import ascend_micro_harness_b200 as tq
     rng = np.random.default_rng(3)
@@ -119,13 +120,13 @@ def test_lloydmax_writer_gaussian_inputs_within_one_code_at_ties(cuda, oracle):
     k, v = hp.gaussian_outlier_activations(rng, strips * 16, H, d)
     slots, P = hp.page_permutation_slots(rng, strips, S)
     got = _lm_write(cuda, tq, torch, k, v, slots, H, d, S, P)
-    ekc, evc, esc, _ = oracle.reshape_and_cache_lm(k, v, slots, H, d, S, P, hp.inv_sqrt_len(d))
-    assert np.allclose(got[2], esc, rtol=3e-7, atol=0)
-    for a, b in ((got[0], ekc), (got[1], evc)):
-        ca = np.stack([a & 15, a >> 4], 1).astype(np.int32)
-        cb = np.stack([b & 15, b >> 4], 1).astype(np.int32)
-        assert np.abs(ca - cb).max() <= 1
-        assert (ca != cb).mean() < 1e-4
+    ekc = np.full(P * H * S * d // 2, 0xAA, np.uint8)
+    evc = np.full_like(ekc, 0xAA)
+    esc = np.zeros(2 * P * H * S, np.float32)
+    esc.view(np.uint32)[:] = 0x7FC0BEEF
+    oracle.reshape_and_cache_lm(k, v, slots, H, d, S, P, hp.inv_sqrt_len(d), ekc, evc, esc)
+    assert np.array_equal(got[2].view(np.uint32), esc.view(np.uint32)), "scale bits"
+    assert np.array_equal(got[0], ekc) and np.array_equal(got[1], evc)
 
 
 @pytest.mark.parametrize("d,S", [(128, 16), (256, 64)])
