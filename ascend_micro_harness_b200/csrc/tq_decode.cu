@@ -41,7 +41,6 @@
 namespace tq {
 
 constexpr int kDecWarps = 4;
-constexpr int kTileStrips = 2;   // strips per pipeline stage of one warp
 #ifndef TQ_D256_STAGES
 #define TQ_D256_STAGES 2
 #endif
@@ -75,10 +74,14 @@ struct DecodeParams {
 // quarter-warp reads (tokens t and t+4) fall into different banks.
 template <int D>
 struct DecodeSmem {
-    // Ring depth and resident CTAs per SM. d = 128: three stages of 2 strips for each of four
-    // warps are 51 KiB, four CTAs fit and the kernel stays under 128 registers. d = 256 doubles
-    // both the strips and the accumulator registers: two stages, three CTAs of up to 168 registers.
-    static constexpr int kStages = D == 128 ? 3 : TQ_D256_STAGES;
+    // Tile (strips per pipeline stage of one warp), ring depth and resident CTAs per SM.
+    // d = 128: two stages of 3 strips for each of four warps are 51 KiB, four CTAs fit and the
+    // kernel stays within 128 registers (measured against 3 stages of 2 strips: +1.7 %, the
+    // per-tile bookkeeping is spread over more strips; 6 stages of 1 strip: -8 %). d = 256
+    // doubles both the strips and the accumulator registers: two stages of 2 strips, three
+    // CTAs of up to 168 registers.
+    static constexpr int kTileStrips = D == 128 ? 3 : 2;
+    static constexpr int kStages = D == 128 ? 2 : TQ_D256_STAGES;
     static constexpr int kCtasPerSm = D == 128 ? 4 : TQ_D256_CTAS;
     static constexpr int kRowBytes = D / 2;
     static constexpr int kStripBytes = kStrip * D / 2;
@@ -212,6 +215,7 @@ tq_decode_partial_kernel(const DecodeParams p)
 {
     using L = DecodeSmem<D>;
     constexpr int kStages = L::kStages;
+    constexpr int kTileStrips = L::kTileStrips;
     constexpr int kRecord = 16 + D;
     constexpr int MT = D / 16;    // 16-channel m-tiles of the value contraction
     constexpr int WPT = D / 32;   // packed words per thread per key row
