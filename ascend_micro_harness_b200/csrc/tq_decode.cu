@@ -298,6 +298,10 @@ tq_decode_partial_kernel(const DecodeParams p)
     // softmax_scale * log2(e) and the 1/16 of the key operand (see compute_tile).
     constexpr int NL = PRECISE ? 3 : 2;
     int* qfix = reinterpret_cast<int*>(qbuf);
+    // A lane later reads the eight integers of its key word's channels, lanes (r, qd) at
+    // channel qd * d/4 + ...: rows are padded by 16 and quarters of a row by 4 words so that
+    // the eight lanes one 128-bit access serves together fall into eight different bank groups.
+    auto q_index = [](int row, int ch) { return row * (D + 16) + (ch / (D / 4)) * (D / 4 + 4) + ch % (D / 4); };
     {
         constexpr int K = D / 32;
         float sgn[K];
@@ -335,7 +339,7 @@ tq_decode_partial_kernel(const DecodeParams p)
             const float up = tiny ? 0.0f : __int_as_float(((254 + kTop) << 23) - e_bits);
             const float down = tiny ? 1.0f : __int_as_float(e_bits - (kTop << 23));
 #pragma unroll
-            for (int i = 0; i < K; ++i) qfix[row * D + lane * K + i] = __float2int_rn(v[i] * up);
+            for (int i = 0; i < K; ++i) qfix[q_index(row, lane * K + i)] = __float2int_rn(v[i] * up);
             if (lane == 0) row_unscale[row] = down * 0.0625f * p.softmax_scale * kLog2e;
         }
     }
@@ -348,7 +352,7 @@ tq_decode_partial_kernel(const DecodeParams p)
     uint32_t bq[NL][WPT][2];
 #pragma unroll
     for (int wi = 0; wi < WPT; ++wi) {
-        const int* qr = qfix + r * D + qd * (D / 4) + wi * 8;
+        const int* qr = qfix + q_index(r, qd * (D / 4) + wi * 8);
         int qv[8];
 #pragma unroll
         for (int n = 0; n < 8; ++n) qv[n] = qr[n];
@@ -356,11 +360,11 @@ tq_decode_partial_kernel(const DecodeParams p)
         for (int l = 0; l < NL; ++l)
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                uint32_t w = 0;
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    w |= ((static_cast<uint32_t>(qv[2 * e + h]) >> (8 * l)) & 0xFFu) << (8 * e);
-                bq[l][wi][h] = w;
+                // byte e of the word = limb l of channel 2e + h: three byte permutes
+                const uint32_t pick = static_cast<uint32_t>(l) | (static_cast<uint32_t>(4 + l) << 4);
+                const uint32_t lo = __byte_perm(qv[h], qv[2 + h], pick);
+                const uint32_t hi = __byte_perm(qv[4 + h], qv[6 + h], pick);
+                bq[l][wi][h] = __byte_perm(lo, hi, 0x5410u);
             }
     }
     // scores are kept as raw * key_scale; the per-row factor enters inside the exponent
@@ -460,11 +464,12 @@ tq_decode_partial_kernel(const DecodeParams p)
     // byte-permute selector that brings this thread's value-token pairs to bits 0-7 / 16-23
     const uint32_t vsel = qd == 0 ? 0x3210u : qd == 1 ? 0x4321u : qd == 2 ? 0x7654u : 0x0765u;
 
-    // Integer accumulators of one limb stay below 2^22 in magnitude at d = 128
-    // (128 channels x |16 code| <= 128 x limb <= 255), so a chain that starts at the bit
-    // pattern of 1.5 * 2^23 ends, read as a float, at 12582912 + sum exactly and one FP32
-    // subtract recovers the sum; d = 256 can exceed that range and converts instead.
-    constexpr bool kBiasedAcc = D == 128;
+    // Two limbs are combined in INT32 and converted once. With three limbs (the
+    // reference-contract entry) the sum no longer fits: at d = 128 an accumulator of one limb
+    // stays below 2^22 in magnitude (128 channels x |16 code| <= 128 x limb <= 255), so a chain
+    // that starts at the bit pattern of 1.5 * 2^23 ends, read as a float, at 12582912 + sum
+    // exactly and one FP32 subtract recovers it; d = 256 can exceed that range and converts.
+    constexpr bool kBiasedAcc = D == 128 && NL != 2;
     const int cinit[4] = {kBiasedAcc ? 0x4B400000 : 0, kBiasedAcc ? 0x4B400000 : 0,
                           kBiasedAcc ? 0x4B400000 : 0, kBiasedAcc ? 0x4B400000 : 0};
     auto limb_value = [](int v) {
@@ -511,6 +516,12 @@ tq_decode_partial_kernel(const DecodeParams p)
             float c[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
+                if constexpr (NL == 2) {
+                    // |c1| * 256 + |c0| < 2^31 at either head size: the two limbs combine in
+                    // INT32 and one conversion follows
+                    c[i] = __int2float_rn(ci[1][i] * 256 + ci[0][i]);
+                    continue;
+                }
                 float f = limb_value(ci[NL - 1][i]);
 #pragma unroll
                 for (int l = NL - 2; l >= 0; --l) f = fmaf(f, 256.0f, limb_value(ci[l][i]));
