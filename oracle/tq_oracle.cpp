@@ -335,37 +335,39 @@ int tqo_reshape_and_cache(int dtype, const void* key, const void* value,
                           std::uint8_t* value_cache, float* scale_cache,
                           std::uint8_t* page_written, int threads)
 {
-    if (T <= 0 || H <= 0 || S != kStrip || d % kGroup != 0 || T % S != 0) return -2;
+    // The reference's writer fixes the page at one strip (S = 16); a page of S = 16 k tokens
+    // holds k strips, each at a strip boundary of its page (the in-page offset of the
+    // project's later aligned-prefill design).
+    if (T <= 0 || H <= 0 || S <= 0 || S % kStrip != 0 || d % kGroup != 0 || T % kStrip != 0) return -2;
     const Geometry g{H, d, S, P};
-    const int strips = T / S;
-    std::vector<int> page_of(static_cast<std::size_t>(strips), -1);
+    const int strips = T / kStrip;
+    std::vector<int> slot_of(static_cast<std::size_t>(strips), -1);
     int bad = -1;
     for (int s = 0; s < strips; ++s) {
-        const std::int32_t* ss = slots + static_cast<std::size_t>(s) * S;
-        bool ok = ss[0] >= 0 && ss[0] % S == 0;
-        for (int i = 1; ok && i < S; ++i) ok = ss[i] == ss[0] + i;
-        const int page = ok ? ss[0] / S : -1;
-        if (ok && page < P) page_of[s] = page;
+        const std::int32_t* ss = slots + static_cast<std::size_t>(s) * kStrip;
+        bool ok = ss[0] >= 0 && ss[0] % kStrip == 0;
+        for (int i = 1; ok && i < kStrip; ++i) ok = ss[i] == ss[0] + i;
+        if (ok && ss[0] / S < P) slot_of[s] = ss[0];
         else if (bad < 0) bad = s;
     }
     parallel_for(strips, threads, [&](int s) {
-        const int page = page_of[s];
-        if (page < 0) return;
+        if (slot_of[s] < 0) return;
+        const int page = slot_of[s] / S, tip = slot_of[s] % S;
         if (page_written) page_written[page] = 1;
         std::vector<int> q(static_cast<std::size_t>(d));
         for (int plane = 0; plane < 2; ++plane) {
             const void* src = plane == 0 ? key : value;
             std::uint8_t* cache = plane == 0 ? key_cache : value_cache;
             for (int head = 0; head < H; ++head)
-                for (int t = 0; t < S; ++t) {
+                for (int t = 0; t < kStrip; ++t) {
                     const std::size_t row =
-                        (static_cast<std::size_t>(s) * S + t) * H * d + static_cast<std::size_t>(head) * d;
+                        (static_cast<std::size_t>(s) * kStrip + t) * H * d + static_cast<std::size_t>(head) * d;
                     float scale;
                     process_row(dtype, src, row, d, signs, inv_sqrt_len, true, q.data(), &scale);
                     for (int c = 0; c < d; ++c)
-                        put_nibble(cache, plane == 0 ? g.key_nibble(page, head, t, c)
-                                                     : g.value_nibble(page, head, t, c), q[c]);
-                    scale_cache[g.scale_index(plane, page, head, t)] = scale;
+                        put_nibble(cache, plane == 0 ? g.key_nibble(page, head, tip + t, c)
+                                                     : g.value_nibble(page, head, tip + t, c), q[c]);
+                    scale_cache[g.scale_index(plane, page, head, tip + t)] = scale;
                 }
         }
     });

@@ -107,6 +107,25 @@ def test_reference_geometry_ladder(cuda, oracle, strips, dtype):
     assert (kc[0::2] == CANARY).all()
 
 
+@pytest.mark.parametrize("S", [64, 128])
+@pytest.mark.parametrize("d", [128, 256])
+def test_large_pages_strips_at_in_page_offsets(cuda, oracle, S, d):
+    """Pages of 64 and 128 tokens (a serving stack's page sizes): strips land at every
+    in-page offset, pages are scattered, some pages stay partly unwritten."""
+    rng = np.random.default_rng(S + d)
+    H, strips = 2, 150
+    k, v = hp.gaussian_outlier_activations(rng, strips * 16, H, d, integer=True)
+    per_page = S // 16
+    P = (strips + per_page - 1) // per_page + 3
+    pages = rng.permutation(P)
+    where = rng.permutation(P * per_page)[:strips]            # (page, in-page strip) per strip
+    slots = ((pages[where // per_page] * S + (where % per_page) * 16)[:, None] +
+             np.arange(16)[None, :]).astype(np.int32).reshape(-1)
+    signs = hp.random_signs(rng, d)
+    got = run_device(cuda, k, v, slots, signs, H, d, S, P)
+    assert_identical(got, expect(oracle, k, v, slots, signs, H, d, S, P))
+
+
 def test_config2_bf16_integer_valued(cuda, oracle):
     """BASELINE config 2, bit-exact leg: 1024 tokens x 8 heads x 128, integer-valued bf16,
     seeded page permutation of 64 pages."""
