@@ -51,6 +51,11 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
 }
+// 16 bytes of which the first `bytes` come from memory and the rest are zeros.
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t dst, const void* src, uint32_t bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
 __device__ __forceinline__ void cp_async_8(uint32_t dst, const void* src)
 {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst), "l"(src));
@@ -69,10 +74,35 @@ __device__ __forceinline__ PanelId panel_of(const IngestParams& p, uint32_t chun
     return id;
 }
 
+// First token and token count of a strip. Dense launches: strip s holds tokens 16 s .. 16 s + 15.
+// Ragged launches: the request is found by bisection over the strips' prefix sum; the last
+// strip of a request may hold fewer than 16 tokens.
+struct StripRun {
+    uint32_t token0, count;
+};
+template <bool VARLEN>
+__device__ __forceinline__ StripRun strip_run(const IngestParams& p, uint32_t strip)
+{
+    if constexpr (!VARLEN) {
+        return {strip * kStrip, static_cast<uint32_t>(kStrip)};
+    } else {
+        uint32_t lo = 0, hi = p.num_requests;   // strip_begin[lo] <= strip < strip_begin[hi]
+        while (hi - lo > 1u) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (static_cast<uint32_t>(__ldg(p.strip_begin + mid)) <= strip) lo = mid;
+            else hi = mid;
+        }
+        const uint32_t begin = static_cast<uint32_t>(__ldg(p.cu_seqlens + lo));
+        const uint32_t len = static_cast<uint32_t>(__ldg(p.cu_seqlens + lo + 1)) - begin;
+        const uint32_t r = strip - static_cast<uint32_t>(__ldg(p.strip_begin + lo));
+        return {begin + r * kStrip, min(static_cast<uint32_t>(kStrip), len - r * kStrip)};
+    }
+}
+
 // Queue the copies of one panel: per 32-channel group the 8 channels of token 2r and
 // of token 2r+1 that this thread will feed to the MMA. Returns the slot of token
 // (lane & 15) of the strip, fetched alongside.
-template <int D, bool BF16>
+template <int D, bool BF16, bool VARLEN>
 __device__ __forceinline__ int32_t stage_panel(const IngestParams& p, uint32_t chunk, int lane,
                                                uint32_t stage_s)
 {
@@ -81,20 +111,36 @@ __device__ __forceinline__ int32_t stage_panel(const IngestParams& p, uint32_t c
     constexpr int kPiece = 8 * kElem;   // bytes of 8 channels
     const int r = lane >> 2, qd = lane & 3;
     const PanelId id = panel_of(p, chunk);
+    const StripRun run = strip_run<VARLEN>(p, id.strip);
     const size_t row_pitch = static_cast<size_t>(p.H) * D * kElem;  // bytes
-    const uint8_t* base = static_cast<const uint8_t*>(id.plane == 0 ? p.key : p.value) +
-                          (static_cast<size_t>(id.strip) * kStrip + 2 * r) * row_pitch +
-                          (static_cast<size_t>(id.head) * D + qd * 8) * kElem;
+    const uint8_t* strip_base = static_cast<const uint8_t*>(id.plane == 0 ? p.key : p.value) +
+                                static_cast<size_t>(run.token0) * row_pitch +
+                                (static_cast<size_t>(id.head) * D + qd * 8) * kElem;
+    const uint8_t* base = strip_base + static_cast<size_t>(2 * r) * row_pitch;
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const uint32_t dst = stage_s + ((g * 2 + h) * 32 + lane) * kPiece;
             const uint8_t* src = base + h * row_pitch + g * kGroup * kElem;
-            if constexpr (BF16) cp_async_16(dst, src);
-            else cp_async_8(dst, src);
+            if constexpr (VARLEN) {
+                // tokens past a short last strip read as zeros (from the strip's first row)
+                const bool live = static_cast<uint32_t>(2 * r + h) < run.count;
+                cp_async_16_zfill(dst, live ? src : strip_base, live ? 16u : 0u);
+            } else if constexpr (BF16) {
+                cp_async_16(dst, src);
+            } else {
+                cp_async_8(dst, src);
+            }
         }
-    return __ldg(p.slots + static_cast<size_t>(id.strip) * kStrip + (lane & 15));
+    const uint32_t t = lane & 15;
+    if constexpr (VARLEN) {
+        // slots of absent tokens are synthesised so that the run check sees a whole strip
+        const int32_t first = __ldg(p.slots + run.token0);
+        return t < run.count ? __ldg(p.slots + run.token0 + t) : first + static_cast<int32_t>(t);
+    } else {
+        return __ldg(p.slots + static_cast<size_t>(run.token0) + t);
+    }
 }
 
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
@@ -109,7 +155,7 @@ __device__ __forceinline__ float max3_abs(float a, float b, float c)
 
 // Rotate, quantise, pack and store one panel whose fragments sit in `in` (this
 // thread's own bytes) and whose slot run is `slot`.
-template <int D, bool BF16>
+template <int D, bool BF16, bool VARLEN>
 __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t chunk, int lane,
                                               const uint8_t* in, int32_t slot,
                                               const uint32_t (&bfrag)[BF16 ? 16 : 8],
@@ -121,6 +167,8 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
     constexpr int kSignPitch = kSignPitchOf<D>;
     const int r = lane >> 2, qd = lane & 3;
     const PanelId id = panel_of(p, chunk);
+    // tokens the strip really holds (16 except for the last strip of a ragged request)
+    const uint32_t live_tokens = VARLEN ? strip_run<VARLEN>(p, id.strip).count : static_cast<uint32_t>(kStrip);
 
     // ---- the strip's page, from its slots; the contract is checked, not assumed
     // (tests/common/turboquant_oracle.hpp:278-287).
@@ -293,6 +341,7 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
         if (id.plane == 0) {
             // undo the store swizzle: unit = row * (D/32) + chunk, chunk ^= (row/2) & 3
             const int row = unit / (D / 32), chunk16 = unit % (D / 32);
+            if (VARLEN && static_cast<uint32_t>(row) >= live_tokens) continue;   // key rows past a short strip stay
             v = s4[row * (D / 32) + (chunk16 ^ ((row >> 1) & 3))];
         } else {
             v = s4[unit ^ ((unit >> 3) & 1)];   // undo the store swizzle
@@ -307,14 +356,18 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
     if (qd == 0) {
         const size_t at = ((static_cast<size_t>(id.plane) * p.P + page) * p.H + id.head) * p.S +
                           tok_in_page + 2 * r;
-        *reinterpret_cast<float2*>(p.scale_cache + at) =
-            make_float2(pow2[0] * p.inv_sqrt_len, pow2[1] * p.inv_sqrt_len);
+        if (!VARLEN || static_cast<uint32_t>(2 * r + 1) < live_tokens) {
+            *reinterpret_cast<float2*>(p.scale_cache + at) =
+                make_float2(pow2[0] * p.inv_sqrt_len, pow2[1] * p.inv_sqrt_len);
+        } else if (static_cast<uint32_t>(2 * r) < live_tokens) {
+            p.scale_cache[at] = pow2[0] * p.inv_sqrt_len;
+        }
     }
 }
 
 // Persistent: every warp walks panels warp_global, warp_global + warps_total, ...
 // with the next panel's bytes in flight while the current one is processed.
-template <int D, bool BF16>
+template <int D, bool BF16, bool VARLEN = false>
 __global__ void __launch_bounds__(kIngestWarps * 32, kIngestCtasPerSm<D>)
 tq_ingest_kernel(const IngestParams p)
 {
@@ -378,22 +431,22 @@ tq_ingest_kernel(const IngestParams p)
     uint32_t* stage = reinterpret_cast<uint32_t*>(warp_base + 2 * kInBytes);
 
     int32_t slot_cur = 0, slot_nxt = 0;
-    if (c < p.chunks) slot_cur = stage_panel<D, BF16>(p, c, lane, in_s);
+    if (c < p.chunks) slot_cur = stage_panel<D, BF16, VARLEN>(p, c, lane, in_s);
     asm volatile("cp.async.commit_group;\n" ::);
     uint32_t buf = 0;
 #pragma unroll 1
     for (; c < p.chunks; c += stride, buf ^= 1u) {
         const uint32_t cn = c + stride;
-        if (cn < p.chunks) slot_nxt = stage_panel<D, BF16>(p, cn, lane, in_s + (buf ^ 1u) * kInBytes);
+        if (cn < p.chunks) slot_nxt = stage_panel<D, BF16, VARLEN>(p, cn, lane, in_s + (buf ^ 1u) * kInBytes);
         asm volatile("cp.async.commit_group;\n" ::);
         asm volatile("cp.async.wait_group 1;\n" ::: "memory");   // this thread's own bytes of panel c
-        process_panel<D, BF16>(p, c, lane, warp_base + buf * kInBytes, slot_cur, bfrag, sgn_s, stage);
+        process_panel<D, BF16, VARLEN>(p, c, lane, warp_base + buf * kInBytes, slot_cur, bfrag, sgn_s, stage);
         slot_cur = slot_nxt;
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool VARLEN = false>
 static cudaError_t launch_ingest(cudaStream_t stream, const IngestParams& p)
 {
     constexpr int kInBytes = kStrip * D * (BF16 ? 2 : 1);
@@ -405,14 +458,14 @@ static cudaError_t launch_ingest(cudaStream_t stream, const IngestParams& p)
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     static bool configured[64] = {};   // benign race: the attribute is idempotent
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(tq_ingest_kernel<D, BF16>,
+        cudaError_t e = cudaFuncSetAttribute(tq_ingest_kernel<D, BF16, VARLEN>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const uint32_t resident = static_cast<uint32_t>(sms) * kIngestCtasPerSm<D>;
     if (blocks > resident) blocks = resident;  // persistent: one resident wave
-    tq_ingest_kernel<D, BF16><<<blocks, kIngestWarps * 32, kSmem, stream>>>(p);
+    tq_ingest_kernel<D, BF16, VARLEN><<<blocks, kIngestWarps * 32, kSmem, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -509,4 +562,63 @@ extern "C" int tq_reshape_and_cache_warp_mma(void* stream, const void* key, cons
     return reshape_and_cache(stream, key, value, key_cache, value_cache, scale_cache, slot_mapping,
                              signs, sign_source, in_dtype, num_tokens, num_kv_heads, head_size,
                              block_size, num_blocks, inv_sqrt_len, status, true);
+}
+
+// The aligned writer over ragged requests: strips are cut per request, the last strip of a
+// request may hold fewer than 16 tokens (key plane: its rows only; value plane: the whole
+// channel-major strip with the missing tokens as zeros; scales: its tokens only).
+extern "C" int tq_reshape_and_cache_varlen(void* stream, const uint16_t* key, const uint16_t* value,
+                                           int8_t* key_cache, int8_t* value_cache,
+                                           float* scale_cache, const int32_t* slot_mapping,
+                                           const float* pi_signs, const int32_t* cu_seqlens,
+                                           const int32_t* strip_begin, uint32_t num_requests,
+                                           uint32_t total_strips, uint32_t num_kv_heads,
+                                           uint32_t head_size, uint32_t block_size,
+                                           uint32_t num_blocks, float inv_sqrt_len, uint32_t* status)
+{
+    using namespace tq;
+    if (num_kv_heads == 0 || num_blocks == 0 || block_size == 0 || block_size % kStrip != 0 ||
+        (head_size != 128 && head_size != 256))
+        return TQ_ERR_INVALID_ARGUMENT;
+    if (num_requests == 0 || total_strips == 0) return TQ_OK;
+    if (!key || !value || !key_cache || !value_cache || !scale_cache || !slot_mapping || !pi_signs ||
+        !cu_seqlens || !strip_begin)
+        return TQ_ERR_INVALID_ARGUMENT;
+    const uintptr_t align = reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value) |
+                            reinterpret_cast<uintptr_t>(key_cache) |
+                            reinterpret_cast<uintptr_t>(value_cache) |
+                            reinterpret_cast<uintptr_t>(scale_cache);
+    const uint64_t chunks = static_cast<uint64_t>(total_strips) * 2u * num_kv_heads;
+    if ((align & 15u) != 0u || chunks >= 0x7FFFFFFFull || num_kv_heads > 0x10000u)
+        return TQ_ERR_INVALID_ARGUMENT;
+    IngestParams p;
+    p.key = key;
+    p.value = value;
+    p.key_cache = reinterpret_cast<uint8_t*>(key_cache);
+    p.value_cache = reinterpret_cast<uint8_t*>(value_cache);
+    p.scale_cache = scale_cache;
+    p.slots = slot_mapping;
+    p.signs = pi_signs;
+    p.sign_source = TQ_SIGNS_F32;
+    p.num_strips = total_strips;
+    p.H = num_kv_heads;
+    p.S = block_size;
+    p.P = num_blocks;
+    p.chunks = static_cast<uint32_t>(chunks);
+    {
+        const uint32_t d2 = 2u * num_kv_heads;
+        uint32_t l = 0;
+        while ((1ull << l) < d2) ++l;
+        p.div_mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d2)) / d2 + 1ull);
+        p.div_shift = l - 1u;
+    }
+    p.inv_sqrt_len = inv_sqrt_len;
+    p.status = status;
+    p.cu_seqlens = cu_seqlens;
+    p.strip_begin = strip_begin;
+    p.num_requests = num_requests;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const cudaError_t err = head_size == 128 ? launch_ingest<128, true, true>(s, p)
+                                             : launch_ingest<256, true, true>(s, p);
+    return err == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }

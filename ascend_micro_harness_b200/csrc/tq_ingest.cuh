@@ -19,6 +19,11 @@ struct IngestParams {
     uint32_t div_mul, div_shift;     // exact division by 2H: see fast_div
     float inv_sqrt_len;
     uint32_t* status;
+    // ragged requests (the varlen entry only): request b owns tokens cu_seqlens[b] ..
+    // cu_seqlens[b+1] and strips strip_begin[b] .. strip_begin[b+1]
+    const int32_t* cu_seqlens = nullptr;
+    const int32_t* strip_begin = nullptr;
+    uint32_t num_requests = 0;
 };
 
 // n / d for any 32-bit n with the precomputed (mul, shift) of divisor d >= 2

@@ -54,6 +54,26 @@ def reshape_and_cache(key, value, key_cache, value_cache, scale_cache, slot_mapp
         "tq_reshape_and_cache")
 
 
+def reshape_and_cache_varlen(key, value, key_cache, value_cache, scale_cache, slot_mapping, signs,
+                             cu_seqlens, *, num_kv_heads, head_size, block_size, num_blocks,
+                             inv_sqrt_len, status=None, stream=None):
+    """Aligned writer over ragged requests. cu_seqlens: host sequence of num_requests + 1 token
+    offsets; the strips' prefix sum is formed here and uploaded with it."""
+    lib = load_library()
+    cu = [int(c) for c in cu_seqlens]
+    begin = [0]
+    for a, b in zip(cu[:-1], cu[1:]):
+        begin.append(begin[-1] + (b - a + 15) // 16)
+    dev = key.device
+    cu_d = torch.tensor(cu, dtype=torch.int32, device=dev)
+    begin_d = torch.tensor(begin, dtype=torch.int32, device=dev)
+    _check(lib.tq_reshape_and_cache_varlen(
+        _stream(stream), _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache),
+        _ptr(scale_cache), _ptr(slot_mapping), _ptr(signs), _ptr(cu_d), _ptr(begin_d), len(cu) - 1,
+        begin[-1], num_kv_heads, head_size, block_size, num_blocks, inv_sqrt_len, _ptr(status)),
+        "tq_reshape_and_cache_varlen")
+
+
 def reshape_scatter(key, value, key_cache, value_cache, scale_cache, slot_mapping, pi_signs,
                     cu_seqlens, *, num_requests, num_kv_heads, head_size, block_size, num_blocks,
                     inv_sqrt_len, item_begin=0, item_count=None, status=None, stream=None):

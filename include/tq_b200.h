@@ -99,6 +99,24 @@ int tq_reshape_and_cache_warp_mma(void* stream, const void* key, const void* val
                                   uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
                                   uint32_t num_blocks, float inv_sqrt_len, uint32_t* status);
 
+/* The aligned writer over ragged requests (bf16): request b owns tokens cu_seqlens[b] ..
+ * cu_seqlens[b+1] and the strips strip_begin[b] .. strip_begin[b+1] (the caller's prefix sum
+ * of ceil(length / 16); both arrays have num_requests + 1 device entries, total_strips =
+ * strip_begin[num_requests]). A strip never straddles a request boundary; the last strip of
+ * a request may hold n < 16 tokens: the key plane then receives n rows, the scale planes n
+ * entries, the value plane the whole channel-major strip with the missing tokens as zeros
+ * (so the 16 - n slots after the tail, which belong to the request's current page, are
+ * overwritten in the value plane). Each strip's slots must be consecutive and start on a
+ * strip boundary of a page. Follows the design note reports/qwen35_turboquant_rfc.md:564-650
+ * for the reference's aligned writer. */
+int tq_reshape_and_cache_varlen(void* stream, const uint16_t* key, const uint16_t* value,
+                                int8_t* key_cache, int8_t* value_cache, float* scale_cache,
+                                const int32_t* slot_mapping, const float* pi_signs,
+                                const int32_t* cu_seqlens, const int32_t* strip_begin,
+                                uint32_t num_requests, uint32_t total_strips, uint32_t num_kv_heads,
+                                uint32_t head_size, uint32_t block_size, uint32_t num_blocks,
+                                float inv_sqrt_len, uint32_t* status);
+
 /* Scatter writer: 1..16 bf16 tokens per request at arbitrary slots, key rows
  * written whole, value strips read-modify-written so unowned nibbles survive.
  * Replaces launch_turboquant_reshape_scatter_aiv

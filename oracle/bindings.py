@@ -113,6 +113,15 @@ class Oracle:
             _p(kc), _p(vc), _p(sc), _p(pw), C.c_int(threads))
         return kc, vc, sc, pw, bad
 
+    def reshape_and_cache_varlen(self, key, value, slots, signs, cu_seqlens, H, d, S, P, inv_sqrt_len,
+                                 key_cache, value_cache, scale_cache):
+        """Aligned writer over ragged requests (bf16 bits), in place on the given caches."""
+        cu = _c(cu_seqlens, np.int32)
+        return self.lib.tqo_reshape_and_cache_varlen(
+            _p(_c(key, np.uint16)), _p(_c(value, np.uint16)), _p(_c(slots, np.int32)),
+            _p(_c(signs, np.int32)), _p(cu), C.c_int(cu.size - 1), C.c_int(H), C.c_int(d), C.c_int(S),
+            C.c_int(P), C.c_float(inv_sqrt_len), _p(key_cache), _p(value_cache), _p(scale_cache))
+
     def reshape_scatter(self, key, value, slots, signs, cu_seqlens, num_requests, H, d, S, P,
                         inv_sqrt_len, key_cache, value_cache, scale_cache):
         """Scatter writer, in place on the given caches. key/value bf16 bits [tokens][H*d]."""

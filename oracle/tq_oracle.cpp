@@ -374,6 +374,60 @@ int tqo_reshape_and_cache(int dtype, const void* key, const void* value,
     return bad;
 }
 
+// ------------------------------------------------- aligned writer, ragged requests
+// The aligned writer over requests of any length (the project's design note for it:
+// reports/qwen35_turboquant_rfc.md:564-650): request b owns tokens cu_seqlens[b] ..
+// cu_seqlens[b+1]; its strips never straddle a request boundary; the last strip of a
+// request may hold n < 16 tokens. For such a strip the key plane receives n rows and the
+// scale planes n entries; the value plane receives the whole channel-major strip with the
+// missing tokens as zeros (a partial channel-major strip is not a contiguous region).
+// Each strip's slots must be consecutive and start on a strip boundary of a page.
+// bf16 input. Returns the number of strips that broke the slot contract.
+int tqo_reshape_and_cache_varlen(const std::uint16_t* key, const std::uint16_t* value,
+                                 const std::int32_t* slots, const int* signs,
+                                 const std::int32_t* cu_seqlens, int num_requests, int H, int d,
+                                 int S, int P, float inv_sqrt_len, std::uint8_t* key_cache,
+                                 std::uint8_t* value_cache, float* scale_cache)
+{
+    if (S % kStrip != 0 || d % kGroup != 0) return -2;
+    const Geometry g{H, d, S, P};
+    std::vector<int> q(static_cast<std::size_t>(d));
+    int bad = 0;
+    for (int b = 0; b < num_requests; ++b) {
+        const int begin = cu_seqlens[b], len = cu_seqlens[b + 1] - begin;
+        for (int r = 0; r * kStrip < len; ++r) {
+            const int t0 = begin + r * kStrip, n = std::min(kStrip, len - r * kStrip);
+            const std::int32_t slot0 = slots[t0];
+            bool ok = slot0 >= 0 && slot0 % kStrip == 0 && slot0 / S < P;
+            for (int i = 1; ok && i < n; ++i) ok = slots[t0 + i] == slot0 + i;
+            if (!ok) { ++bad; continue; }
+            const int page = slot0 / S, tip = slot0 % S;
+            for (int plane = 0; plane < 2; ++plane) {
+                const std::uint16_t* src = plane == 0 ? key : value;
+                std::uint8_t* cache = plane == 0 ? key_cache : value_cache;
+                for (int head = 0; head < H; ++head)
+                    for (int t = 0; t < kStrip; ++t) {
+                        if (t < n) {
+                            const std::size_t row = static_cast<std::size_t>(t0 + t) * H * d +
+                                                    static_cast<std::size_t>(head) * d;
+                            float scale;
+                            process_row(1, src, row, d, signs, inv_sqrt_len, true, q.data(), &scale);
+                            scale_cache[g.scale_index(plane, page, head, tip + t)] = scale;
+                        } else if (plane == 0) {
+                            continue;            // key rows past the tail stay as they were
+                        } else {
+                            std::fill(q.begin(), q.end(), 0);   // value strip: zero padding
+                        }
+                        for (int c = 0; c < d; ++c)
+                            put_nibble(cache, plane == 0 ? g.key_nibble(page, head, tip + t, c)
+                                                         : g.value_nibble(page, head, tip + t, c), q[c]);
+                    }
+            }
+        }
+    }
+    return bad;
+}
+
 // ------------------------------------------------------- scatter writer
 // tq_scatter::compute_reference (tests/common/turboquant_scatter_oracle.hpp:291-342)
 // over the run discovery of the device kernel

@@ -103,3 +103,15 @@ def test_routine_and_lloydmax_entries_refuse_bad_arguments_on_the_host():
     assert lib.tq_decode_lloydmax_export(*dec, 1, 48, 4, 128, 16, 8, 4, 2, 1.0, None) == 1  # 12 rows per KV head
     assert lib.tq_decode_lloydmax_export(*dec, 1, 32, 8, 128, 16, 8, 4, 17, 1.0, None) == 1  # 17 splits
     assert lib.tq_decode_lloydmax_export(*dec, 0, 32, 8, 128, 16, 8, 4, 2, 1.0, None) == 0   # empty batch
+
+
+def test_varlen_writer_refuses_bad_geometry_on_the_host():
+    from ascend_micro_harness_b200._lib import load_library
+    lib = load_library()
+    p = C.c_void_p(16)
+    args = [None, p, p, p, p, p, p, p, p, p]
+    assert lib.tq_reshape_and_cache_varlen(*args, 2, 3, 1, 96, 16, 4, 0.1, None) == 1    # head size
+    assert lib.tq_reshape_and_cache_varlen(*args, 2, 3, 1, 128, 24, 4, 0.1, None) == 1   # page not strips
+    assert lib.tq_reshape_and_cache_varlen(*args, 0, 0, 1, 128, 16, 4, 0.1, None) == 0   # nothing to do
+    bad = [None, C.c_void_p(8), p, p, p, p, p, p, p, p]
+    assert lib.tq_reshape_and_cache_varlen(*bad, 2, 3, 1, 128, 16, 4, 0.1, None) == 1    # key not aligned

@@ -200,3 +200,54 @@ def test_partial_strip_is_refused(cuda):
         tq.reshape_and_cache(z, z, c, c, s, sl, sg, num_kv_heads=1, head_size=128, block_size=16,
                              num_blocks=2, inv_sqrt_len=0.1)
     assert e.value.status == 2
+
+
+@pytest.mark.parametrize("d,S", [(128, 16), (128, 64), (256, 128)])
+def test_ragged_requests_with_tail_strips(cuda, oracle, d, S):
+    """The aligned writer over requests of any length: strips are cut per request, a short
+    last strip writes its own key rows and scales only and the whole value strip with zeros
+    for the missing tokens; everything else keeps its canary."""
+    import torch
+    import ascend_micro_harness_b200 as tq
+    if WARP_MMA:
+        pytest.skip("one kernel serves this entry")
+    rng = np.random.default_rng(d + S)
+    H = 2
+    lens = [1, 15, 16, 17, 79, 257, 33, 160]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    T = int(cu[-1])
+    k, v = hp.gaussian_outlier_activations(rng, T, H, d, integer=True)
+    per_page = S // 16
+    strips = [(n + 15) // 16 for n in lens]
+    # every request starts on a fresh page; its strips fill consecutive in-page positions
+    pages_needed = sum((s + per_page - 1) // per_page for s in strips)
+    P = pages_needed + 3
+    perm = rng.permutation(P)
+    slots = np.zeros(T, np.int32)
+    at = 0
+    for b, n in enumerate(lens):
+        for t in range(n):
+            page = perm[at + t // S]
+            slots[cu[b] + t] = page * S + t % S
+        at += (strips[b] + per_page - 1) // per_page
+    signs = hp.random_signs(rng, d)
+    kc = torch.full((P * H * S * d // 2,), CANARY, dtype=torch.uint8, device=cuda)
+    vc = torch.full_like(kc, CANARY)
+    sc = torch.zeros(2 * P * H * S, dtype=torch.float32, device=cuda)
+    sc.view(torch.int32).fill_(0x7FC0BEEF)
+    st = torch.zeros(1, dtype=torch.int32, device=cuda)
+    kd = torch.from_numpy(k.view(np.int16)).to(cuda).view(torch.bfloat16)
+    vd = torch.from_numpy(v.view(np.int16)).to(cuda).view(torch.bfloat16)
+    tq.reshape_and_cache_varlen(kd, vd, kc, vc, sc, torch.from_numpy(slots).to(cuda),
+                                torch.from_numpy(signs.astype(np.float32)).to(cuda), cu, num_kv_heads=H,
+                                head_size=d, block_size=S, num_blocks=P, inv_sqrt_len=hp.inv_sqrt_len(d),
+                                status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    ekc = np.full(P * H * S * d // 2, CANARY, np.uint8)
+    evc = np.full_like(ekc, CANARY)
+    esc = np.zeros(2 * P * H * S, np.float32)
+    esc.view(np.uint32)[:] = 0x7FC0BEEF
+    assert oracle.reshape_and_cache_varlen(k, v, slots, signs, cu, H, d, S, P, hp.inv_sqrt_len(d), ekc, evc,
+                                           esc) == 0
+    assert_identical((kc.cpu().numpy(), vc.cpu().numpy(), sc.cpu().numpy()), (ekc, evc, esc))
