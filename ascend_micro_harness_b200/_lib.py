@@ -24,6 +24,8 @@ SIGNATURES = {
                                      u32, u32, f32, vp]),
     "tq_decode_splitk": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                    u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
+    "tq_decode_splitk_elem": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
+                                        u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
     "tq_decode_splitk_static": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32,
                                           u32, u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
     "tq_decode_splitk_export": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,

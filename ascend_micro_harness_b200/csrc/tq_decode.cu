@@ -65,6 +65,7 @@ struct DecodeParams {
     uint32_t table_stride, splits, page_begin, page_count, fixed_ctx;
     uint32_t sp_shift;        // log2(strips per page); pages hold 16 * 2^k tokens
     uint32_t chunk_pages;     // 0: every sequence uses `splits`; else at most ceil(pages/chunk)
+    uint32_t q_f16;           // 1: the query is FP16 and its rotation stays FP32 (no bf16 rounding)
     float inv_sqrt_len, softmax_scale;
     uint32_t* status;
 };
@@ -316,18 +317,23 @@ tq_decode_partial_kernel(const DecodeParams p)
                 const uint16_t* qsrc =
                     p.q + (static_cast<size_t>(item) * p.rows + row_tile * 8u + row) * D + lane * K;
 #pragma unroll
-                for (int i = 0; i < K; ++i) v[i] = bf16_bits_to_f32(qsrc[i]);
+                for (int i = 0; i < K; ++i)
+                    v[i] = p.q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
             }
             cascade_ingress<K>(v, sgn, lane);
             float am = 0.f;
 #pragma unroll
             for (int i = 0; i < K; ++i) {
-                const uint16_t bits = f32_to_bf16_bits(v[i] * p.inv_sqrt_len);
-                v[i] = bf16_bits_to_f32(bits);
-                am = fmaxf(am, fabsf(v[i]));
-                if (p.q_rot != nullptr && row < rows_here)
-                    p.q_rot[((static_cast<size_t>(item) * p.splits + split) * p.rows_stride +
-                             row_tile * 8u + row) * D + lane * K + i] = bits;
+                float val = v[i] * p.inv_sqrt_len;
+                if (!p.q_f16) {   // the bf16 operand the reference pins (and publishes)
+                    const uint16_t bits = f32_to_bf16_bits(val);
+                    val = bf16_bits_to_f32(bits);
+                    if (p.q_rot != nullptr && row < rows_here)
+                        p.q_rot[((static_cast<size_t>(item) * p.splits + split) * p.rows_stride +
+                                 row_tile * 8u + row) * D + lane * K + i] = bits;
+                }
+                v[i] = val;
+                am = fmaxf(am, fabsf(val));
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
@@ -696,11 +702,12 @@ tq_decode_partial_kernel(const DecodeParams p)
 struct CombineParams {
     const float* workspace;
     const float* signs;
-    const float* gate;
+    const void* gate;
     void* output;
     uint32_t rows, rows_stride, splits, output_stage, out_dtype;
     float inv_sqrt_len;
     uint32_t block16;   // 1: the rotation is block-diagonal H16 / 4 (Lloyd-Max cache variant)
+    uint32_t gate_dtype; // TQ_DTYPE_* of `gate`
 };
 
 // One CTA per (item, row): merge `splits` records, normalise, optionally rotate
@@ -758,7 +765,13 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
             v = buf[cur][c] * p.inv_sqrt_len;
         }
         if (p.output_stage == TQ_OUT_GATED)
-            v = v / (1.0f + __expf(-p.gate[static_cast<size_t>(blockIdx.x) * D + c]));
+        {
+            const size_t gi = static_cast<size_t>(blockIdx.x) * D + c;
+            const float gt = p.gate_dtype == TQ_DTYPE_F32 ? static_cast<const float*>(p.gate)[gi]
+                             : p.gate_dtype == TQ_DTYPE_F16 ? __half2float(static_cast<const __half*>(p.gate)[gi])
+                                                            : bf16_bits_to_f32(static_cast<const uint16_t*>(p.gate)[gi]);
+            v = v / (1.0f + __expf(-gt));
+        }
     }
     const size_t at = static_cast<size_t>(blockIdx.x) * D + c;
     if (p.out_dtype == TQ_DTYPE_F32) static_cast<float*>(p.output)[at] = v;
@@ -910,14 +923,13 @@ extern "C" int tq_decode_splitk_partials(void* stream, const uint16_t* q, const 
     return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 
-extern "C" int tq_splitk_combine(void* stream, const float* workspace, const float* pi_signs,
-                                 const float* gate, void* output, uint32_t out_dtype,
-                                 uint32_t items, uint32_t rows, uint32_t rows_stride,
-                                 uint32_t head_size, uint32_t splits, uint32_t output_stage,
-                                 float inv_sqrt_len, uint32_t* /*status*/)
+static int splitk_combine(void* stream, const float* workspace, const float* pi_signs,
+                          const void* gate, uint32_t gate_dtype, void* output, uint32_t out_dtype,
+                          uint32_t items, uint32_t rows, uint32_t rows_stride, uint32_t head_size,
+                          uint32_t splits, uint32_t output_stage, float inv_sqrt_len)
 {
     if (!rows || rows > rows_stride || !splits || splits > 16 || output_stage > TQ_OUT_GATED ||
-        out_dtype > TQ_DTYPE_F32 ||
+        out_dtype > TQ_DTYPE_F32 || gate_dtype > TQ_DTYPE_F32 ||
         (head_size != 128 && head_size != 256))
         return TQ_ERR_INVALID_ARGUMENT;
     // pi_signs == nullptr selects the block-diagonal H16 / 4 egress of the Lloyd-Max variant
@@ -925,7 +937,7 @@ extern "C" int tq_splitk_combine(void* stream, const float* workspace, const flo
         return TQ_ERR_INVALID_ARGUMENT;
     if (items == 0) return TQ_OK;
     CombineParams p{workspace, pi_signs, gate, output, rows, rows_stride, splits, output_stage,
-                    out_dtype, inv_sqrt_len, pi_signs == nullptr ? 1u : 0u};
+                    out_dtype, inv_sqrt_len, pi_signs == nullptr ? 1u : 0u, gate_dtype};
     const uint64_t grid = static_cast<uint64_t>(items) * rows;
     if (grid > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -934,6 +946,16 @@ extern "C" int tq_splitk_combine(void* stream, const float* workspace, const flo
     else
         tq_combine_kernel<256><<<static_cast<unsigned>(grid), 256, 0, s>>>(p);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
+
+extern "C" int tq_splitk_combine(void* stream, const float* workspace, const float* pi_signs,
+                                 const float* gate, void* output, uint32_t out_dtype,
+                                 uint32_t items, uint32_t rows, uint32_t rows_stride,
+                                 uint32_t head_size, uint32_t splits, uint32_t output_stage,
+                                 float inv_sqrt_len, uint32_t* /*status*/)
+{
+    return splitk_combine(stream, workspace, pi_signs, gate, TQ_DTYPE_F32, output, out_dtype, items, rows,
+                          rows_stride, head_size, splits, output_stage, inv_sqrt_len);
 }
 
 static uint32_t resolve_splits(uint32_t splits, uint32_t batch, uint32_t num_kv_heads,
@@ -961,7 +983,7 @@ static int decode_export_planned(void* stream, const uint16_t* query, const int8
                                  uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
                                  uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
                                  uint32_t splits, uint32_t chunk_pages, float inv_sqrt_len,
-                                 float softmax_scale, uint32_t* status)
+                                 float softmax_scale, uint32_t* status, bool q_f16 = false)
 {
     if (!num_heads || !num_kv_heads || num_heads % num_kv_heads != 0 || !block_size ||
         block_size % kStrip != 0 || !num_blocks || !max_blocks || !splits || splits > 16 ||
@@ -998,6 +1020,7 @@ static int decode_export_planned(void* stream, const uint16_t* query, const int8
     p.table_stride = max_blocks;
     p.splits = splits;
     p.chunk_pages = chunk_pages;
+    p.q_f16 = q_f16 ? 1u : 0u;
     p.page_begin = 0;
     p.page_count = 0;
     p.fixed_ctx = 0;
@@ -1033,12 +1056,13 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
 static int decode_planned(void* stream, const uint16_t* query, const int8_t* key_cache,
                           const int8_t* value_cache, const float* scale_cache,
                           const int32_t* block_tables, const int32_t* context_lens,
-                          const float* pi_signs, const float* gate, float* workspace, void* output,
+                          const float* pi_signs, const void* gate, float* workspace, void* output,
                           uint32_t out_dtype, uint32_t batch, uint32_t num_heads,
                           uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
                           uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
                           uint32_t chunk_pages, uint32_t output_stage, float inv_sqrt_len,
-                          float softmax_scale, uint32_t* status)
+                          float softmax_scale, uint32_t* status, uint32_t gate_dtype = TQ_DTYPE_F32,
+                          bool q_f16 = false)
 {
     if (output_stage > TQ_OUT_GATED || !output || (output_stage == TQ_OUT_GATED && !gate))
         return TQ_ERR_INVALID_ARGUMENT;
@@ -1046,12 +1070,41 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
                                          block_tables, context_lens, pi_signs, workspace, batch,
                                          num_heads, num_kv_heads, head_size, block_size, num_blocks,
                                          max_blocks, splits, chunk_pages, inv_sqrt_len,
-                                         softmax_scale, status);
+                                         softmax_scale, status, q_f16);
     if (st != TQ_OK || batch == 0) return st;
     const uint32_t rows = num_heads / num_kv_heads;
-    return tq_splitk_combine(stream, workspace, pi_signs, gate, output, out_dtype,
-                             batch * num_kv_heads, rows, rows, head_size, splits, output_stage,
-                             inv_sqrt_len, status);
+    return splitk_combine(stream, workspace, pi_signs, gate, gate_dtype, output, out_dtype,
+                          batch * num_kv_heads, rows, rows, head_size, splits, output_stage,
+                          inv_sqrt_len);
+}
+
+// Query, gate and output in ONE 16-bit element type, FP16 or BF16, as the raw-query entry of
+// the reference's fused decoder takes them (include/turboquant_fused_decode_opt.hpp:118-131,
+// :160-169). A BF16 query is rotated and rounded to bf16 exactly as in tq_decode_splitk; an
+// FP16 query keeps its FP32 rotation (the fused decoder's rotated image is FP32) and is cut
+// to the 16-bit fixed point of the integer MMA directly.
+extern "C" int tq_decode_splitk_elem(void* stream, const void* query, const int8_t* key_cache,
+                                     const int8_t* value_cache, const float* scale_cache,
+                                     const int32_t* block_tables, const int32_t* context_lens,
+                                     const float* pi_signs, const void* gate, float* workspace,
+                                     void* output, uint32_t elem_dtype, uint32_t batch,
+                                     uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                                     uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                                     uint32_t splits, uint32_t max_context_hint,
+                                     uint32_t output_stage, float inv_sqrt_len, float softmax_scale,
+                                     uint32_t* status)
+{
+    if (!num_kv_heads || !block_size || splits > 16 ||
+        (elem_dtype != TQ_DTYPE_BF16 && elem_dtype != TQ_DTYPE_F16))
+        return TQ_ERR_INVALID_ARGUMENT;
+    uint32_t chunk_pages = 0;
+    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
+                            &chunk_pages);
+    return decode_planned(stream, static_cast<const uint16_t*>(query), key_cache, value_cache, scale_cache,
+                          block_tables, context_lens, pi_signs, gate, workspace, output, elem_dtype, batch,
+                          num_heads, num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,
+                          chunk_pages, output_stage, inv_sqrt_len, softmax_scale, status, elem_dtype,
+                          elem_dtype == TQ_DTYPE_F16);
 }
 
 extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_t* key_cache,

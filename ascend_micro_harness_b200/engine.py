@@ -114,6 +114,23 @@ def decode_splitk(query, key_cache, value_cache, scale_cache, block_tables, cont
         _ptr(status)), "tq_decode_splitk")
 
 
+def decode_splitk_elem(query, key_cache, value_cache, scale_cache, block_tables, context_lens,
+                       pi_signs, output, *, num_heads, num_kv_heads, head_size, block_size, num_blocks,
+                       inv_sqrt_len, softmax_scale=1.0, splits=0, max_context_hint=0, workspace=None,
+                       gate=None, output_stage=OUT_ROTATED, status=None, stream=None):
+    """decode_splitk with query, gate and output all bfloat16 or all float16."""
+    lib = load_library()
+    if output.dtype != query.dtype or (gate is not None and gate.dtype != query.dtype):
+        raise ValueError("query, gate and output share one element type")
+    batch = query.numel() // (num_heads * head_size)
+    _check(lib.tq_decode_splitk_elem(
+        _stream(stream), _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache),
+        _ptr(block_tables), _ptr(context_lens), _ptr(pi_signs), _ptr(gate), _ptr(workspace),
+        _ptr(output), _out_dtype(query), batch, num_heads, num_kv_heads, head_size, block_size,
+        num_blocks, block_tables.shape[-1], splits, max_context_hint, output_stage, inv_sqrt_len,
+        softmax_scale, _ptr(status)), "tq_decode_splitk_elem")
+
+
 STATIC_WORKSPACE_FLOATS = 2 * 1024 * 1024
 
 

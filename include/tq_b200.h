@@ -235,6 +235,22 @@ int tq_splitk_combine(void* stream, const float* workspace, const float* pi_sign
                       uint32_t rows, uint32_t rows_stride, uint32_t head_size, uint32_t splits,
                       uint32_t output_stage, float inv_sqrt_len, uint32_t* status);
 
+/* tq_decode_splitk with query, gate and output in ONE 16-bit element type (TQ_DTYPE_BF16 or
+ * TQ_DTYPE_F16), the form the raw-query entry of the reference's fused decoder takes them in
+ * (include/turboquant_fused_decode_opt.hpp:118-131,:160-169: raw_query and gate are the element
+ * type, output_stage 0 / 1 / 2). A BF16 query is rotated and rounded to bf16 as in
+ * tq_decode_splitk; an FP16 query keeps its FP32 rotation, as the fused decoder's rotated
+ * image is FP32. gate is read only by TQ_OUT_GATED. */
+int tq_decode_splitk_elem(void* stream, const void* query, const int8_t* key_cache,
+                          const int8_t* value_cache, const float* scale_cache,
+                          const int32_t* block_tables, const int32_t* context_lens,
+                          const float* pi_signs, const void* gate, float* workspace, void* output,
+                          uint32_t elem_dtype, uint32_t batch, uint32_t num_heads,
+                          uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                          uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                          uint32_t max_context_hint, uint32_t output_stage, float inv_sqrt_len,
+                          float softmax_scale, uint32_t* status);
+
 /* ------------------------------------------------------- stand-alone routines
  * The reference's single-purpose routines that its cache operators do not call. */
 

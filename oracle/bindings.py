@@ -165,12 +165,14 @@ class Oracle:
 
     def decode(self, q, key_cache, value_cache, scale_cache, block_tables, context_lens, signs,
                Hq, Hkv, d, S, P, inv_sqrt_len, softmax_scale=1.0, output_stage=0, gate=None,
-               threads=1):
+               threads=1, q_f16=False):
+        """q: bf16 bits, or FP16 bits with q_f16=True (rotation then stays FP32)."""
         q = _c(q, np.uint16)
         B = q.size // (Hq * d)
         bt = _c(block_tables, np.int32)
         out = np.zeros((B, Hq, d))
-        self.lib.tqo_decode(
+        fn = self.lib.tqo_decode_f16q if q_f16 else self.lib.tqo_decode
+        fn(
             _p(q), _p(key_cache), _p(value_cache), _p(_c(scale_cache, np.float32)), _p(bt),
             _p(_c(context_lens, np.int32)), _p(_c(signs, np.float32)),
             _p(None if gate is None else _c(gate, np.float32)), C.c_int(B), C.c_int(Hq),

@@ -43,6 +43,24 @@ inline float bf16_to_f32(std::uint16_t raw)
     return v;
 }
 
+inline float half_to_f32(std::uint16_t h)
+{
+    const std::uint32_t sign = (h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+    std::uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) bits = sign;
+        else {
+            int e = -1;
+            std::uint32_t m = man;
+            do { ++e; m <<= 1; } while (!(m & 0x400u));
+            bits = sign | static_cast<std::uint32_t>(127 - 15 - e) << 23 | (m & 0x3ffu) << 13;
+        }
+    } else if (exp == 31) bits = sign | 0x7f800000u | man << 13;
+    else bits = sign | (exp + 112u) << 23 | man << 13;
+    float v;
+    std::memcpy(&v, &bits, 4);
+    return v;
+}
 // Round-to-nearest-even narrowing (tests/common/turboquant_scatter_oracle.hpp:64-71).
 inline std::uint16_t f32_to_bf16(float value)
 {
@@ -496,11 +514,27 @@ void tqo_partition(std::uint32_t pages, std::uint32_t splits, std::uint32_t spli
 //   m = max score (-3e38 when the range holds no live token), l = sum exp(score-m)
 //   acc[c] = sum_t exp(score-m) vscale[t] Vq[c][t]
 // q_rot is bf16 [rows][d]; outputs are m[rows], l[rows], acc[rows][d] in FP64.
+static void decode_partial_f32q(const float* q_rot, int rows, const std::uint8_t* key_cache,
+                                const std::uint8_t* value_cache, const float* scale_cache,
+                                const std::int32_t* block_table, int H, int head, int d, int S, int P,
+                                int ctx_len, int tok_begin, int tok_end, float softmax_scale,
+                                double* m, double* l, double* acc);
 void tqo_decode_partial(const std::uint16_t* q_rot, int rows, const std::uint8_t* key_cache,
                         const std::uint8_t* value_cache, const float* scale_cache,
                         const std::int32_t* block_table, int H, int head, int d, int S, int P,
                         int ctx_len, int tok_begin, int tok_end, float softmax_scale, double* m,
                         double* l, double* acc)
+{
+    std::vector<float> qf(static_cast<std::size_t>(rows) * d);
+    for (std::size_t i = 0; i < qf.size(); ++i) qf[i] = bf16_to_f32(q_rot[i]);
+    decode_partial_f32q(qf.data(), rows, key_cache, value_cache, scale_cache, block_table, H, head, d, S,
+                        P, ctx_len, tok_begin, tok_end, softmax_scale, m, l, acc);
+}
+static void decode_partial_f32q(const float* q_rot, int rows, const std::uint8_t* key_cache,
+                                const std::uint8_t* value_cache, const float* scale_cache,
+                                const std::int32_t* block_table, int H, int head, int d, int S, int P,
+                                int ctx_len, int tok_begin, int tok_end, float softmax_scale,
+                                double* m, double* l, double* acc)
 {
     const Geometry g{H, d, S, P};
     const int hi = std::min(tok_end, ctx_len);
@@ -513,7 +547,7 @@ void tqo_decode_partial(const std::uint16_t* q_rot, int rows, const std::uint8_t
             const int page = block_table[t / S], tib = t % S;
             double dot = 0.0;
             for (int c = 0; c < d; ++c)
-                dot += static_cast<double>(bf16_to_f32(q_rot[static_cast<std::size_t>(r) * d + c])) *
+                dot += static_cast<double>(q_rot[static_cast<std::size_t>(r) * d + c]) *
                        get_nibble(key_cache, g.key_nibble(page, head, tib, c));
             const double s = dot * scale_cache[g.scale_index(0, page, head, tib)] *
                              static_cast<double>(softmax_scale);
@@ -554,24 +588,37 @@ void tqo_lse_merge(int d, double* m, double* l, double* acc, double m2, double l
 //                   (tests/common/paged_decode_oracle.hpp:598-617)
 // block_tables is int32 [B][max_blocks]; context_lens int32 [B]; gate (may be
 // null unless stage 2) FP32 [B][Hq][d]. A sequence with no live token yields 0.
-void tqo_decode(const std::uint16_t* q, const std::uint8_t* key_cache,
-                const std::uint8_t* value_cache, const float* scale_cache,
-                const std::int32_t* block_tables, const std::int32_t* context_lens,
-                const float* signs, const float* gate, int B, int Hq, int Hkv, int d, int S,
-                int P, int max_blocks, float inv_sqrt_len, float softmax_scale, int output_stage,
-                double* out, int threads)
+// q_f16 = 0: bf16 query, rotation rounded to bf16 (the operand the reference pins);
+// q_f16 = 1: FP16 query whose FP32 rotation is used as it is (the fused decoder keeps an FP32
+// rotated image, include/turboquant_fused_decode_opt.hpp:160-169).
+static void decode_impl(int q_f16, const std::uint16_t* q, const std::uint8_t* key_cache,
+                        const std::uint8_t* value_cache, const float* scale_cache,
+                        const std::int32_t* block_tables, const std::int32_t* context_lens,
+                        const float* signs, const float* gate, int B, int Hq, int Hkv, int d, int S,
+                        int P, int max_blocks, float inv_sqrt_len, float softmax_scale,
+                        int output_stage, double* out, int threads)
 {
     const int group = Hq / Hkv;
     parallel_for(B * Hkv, threads, [&](int item) {
         const int b = item / Hkv, kvh = item % Hkv;
-        std::vector<std::uint16_t> qrot(static_cast<std::size_t>(group) * d);
-        tqo_rotate_query_bf16(group, d, signs, inv_sqrt_len,
-                              q + (static_cast<std::size_t>(b) * Hq + kvh * group) * d, qrot.data());
+        const std::uint16_t* qsrc = q + (static_cast<std::size_t>(b) * Hq + kvh * group) * d;
+        std::vector<float> qrot(static_cast<std::size_t>(group) * d);
+        if (q_f16) {
+            std::vector<float> x(static_cast<std::size_t>(d));
+            for (int r = 0; r < group; ++r) {
+                for (int c = 0; c < d; ++c) x[c] = half_to_f32(qsrc[static_cast<std::size_t>(r) * d + c]);
+                butterfly_f32(d, signs, x.data(), qrot.data() + static_cast<std::size_t>(r) * d, true, inv_sqrt_len);
+            }
+        } else {
+            std::vector<std::uint16_t> bits(static_cast<std::size_t>(group) * d);
+            tqo_rotate_query_bf16(group, d, signs, inv_sqrt_len, qsrc, bits.data());
+            for (std::size_t i = 0; i < bits.size(); ++i) qrot[i] = bf16_to_f32(bits[i]);
+        }
         std::vector<double> m(group), l(group), acc(static_cast<std::size_t>(group) * d);
-        tqo_decode_partial(qrot.data(), group, key_cache, value_cache, scale_cache,
-                           block_tables + static_cast<std::size_t>(b) * max_blocks, Hkv, kvh, d, S, P,
-                           context_lens[b], 0, context_lens[b], softmax_scale, m.data(), l.data(),
-                           acc.data());
+        decode_partial_f32q(qrot.data(), group, key_cache, value_cache, scale_cache,
+                            block_tables + static_cast<std::size_t>(b) * max_blocks, Hkv, kvh, d, S, P,
+                            context_lens[b], 0, context_lens[b], softmax_scale, m.data(), l.data(),
+                            acc.data());
         for (int r = 0; r < group; ++r) {
             double* o = out + (static_cast<std::size_t>(b) * Hq + kvh * group + r) * d;
             std::vector<double> n(static_cast<std::size_t>(d));
@@ -599,6 +646,27 @@ void tqo_decode(const std::uint16_t* q, const std::uint8_t* key_cache,
     });
 }
 
+void tqo_decode(const std::uint16_t* q, const std::uint8_t* key_cache,
+                const std::uint8_t* value_cache, const float* scale_cache,
+                const std::int32_t* block_tables, const std::int32_t* context_lens,
+                const float* signs, const float* gate, int B, int Hq, int Hkv, int d, int S,
+                int P, int max_blocks, float inv_sqrt_len, float softmax_scale, int output_stage,
+                double* out, int threads)
+{
+    decode_impl(0, q, key_cache, value_cache, scale_cache, block_tables, context_lens, signs, gate, B, Hq,
+                Hkv, d, S, P, max_blocks, inv_sqrt_len, softmax_scale, output_stage, out, threads);
+}
+void tqo_decode_f16q(const std::uint16_t* q, const std::uint8_t* key_cache,
+                     const std::uint8_t* value_cache, const float* scale_cache,
+                     const std::int32_t* block_tables, const std::int32_t* context_lens,
+                     const float* signs, const float* gate, int B, int Hq, int Hkv, int d, int S,
+                     int P, int max_blocks, float inv_sqrt_len, float softmax_scale,
+                     int output_stage, double* out, int threads)
+{
+    decode_impl(1, q, key_cache, value_cache, scale_cache, block_tables, context_lens, signs, gate, B, Hq,
+                Hkv, d, S, P, max_blocks, inv_sqrt_len, softmax_scale, output_stage, out, threads);
+}
+
 // ===================================================================== routines
 // The single-purpose routines of the reference that the two operators above do not
 // call, and the ingest/decode variant built from them (block-diagonal H16 rotation,
@@ -606,24 +674,6 @@ void tqo_decode(const std::uint16_t* q, const std::uint8_t* key_cache,
 
 // Y = X x H16 for 16x16 tiles, X FP16 row-major, H16[k][c] = (-1)^popcount(k & c),
 // FP32 accumulation in k order (include/sim_micro_testbed.hpp:181-198).
-static float half_to_f32(std::uint16_t h)
-{
-    const std::uint32_t sign = (h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
-    std::uint32_t bits;
-    if (exp == 0) {
-        if (man == 0) bits = sign;
-        else {
-            int e = -1;
-            std::uint32_t m = man;
-            do { ++e; m <<= 1; } while (!(m & 0x400u));
-            bits = sign | static_cast<std::uint32_t>(127 - 15 - e) << 23 | (m & 0x3ffu) << 13;
-        }
-    } else if (exp == 31) bits = sign | 0x7f800000u | man << 13;
-    else bits = sign | (exp + 112u) << 23 | man << 13;
-    float v;
-    std::memcpy(&v, &bits, 4);
-    return v;
-}
 void tqo_hadamard16(const std::uint16_t* x_f16, float* y, int tiles)
 {
     for (int t = 0; t < tiles; ++t)

@@ -122,6 +122,44 @@ def test_output_stages(cuda, oracle, stage):
     assert_close(got, want)
 
 
+@pytest.mark.parametrize("elem", ["bf16", "f16"])
+@pytest.mark.parametrize("stage", [0, 2])
+def test_element_typed_entry(cuda, oracle, elem, stage):
+    """Query, gate and output in one 16-bit type (the fused decoder's raw-query form). The
+    output is the FP32 result narrowed once, so it is held to the tolerance plus half an ulp
+    of the element type."""
+    import torch
+    import ascend_micro_harness_b200 as tq
+    rng = np.random.default_rng(41 + stage)
+    Hq, Hkv, d, S = 16, 4, 128, 16
+    cache = hp.build_cache_from_gaussian(oracle, rng, [333, 1500, 64], Hkv, d, S)
+    tdt = torch.bfloat16 if elem == "bf16" else torch.float16
+    qt = torch.from_numpy(rng.standard_normal((3, Hq, d)).astype(np.float32)).to(tdt)
+    gt = torch.from_numpy(rng.standard_normal((3, Hq, d)).astype(np.float32)).to(tdt)
+    q_bits = qt.view(torch.int16).numpy().view(np.uint16)
+    want = oracle.decode(q_bits, cache["key_cache"], cache["value_cache"], cache["scale_cache"],
+                         cache["block_tables"], cache["context_lens"], cache["signs"].astype(np.float32),
+                         Hq, Hkv, d, S, cache["num_blocks"], hp.inv_sqrt_len(d), 0.09, stage,
+                         gt.float().numpy() if stage == 2 else None, threads=8, q_f16=(elem == "f16"))
+    splits = 3
+    ws = torch.full((tq.decode_workspace_floats(3, Hq, Hkv, d, splits),), float("nan"), device=cuda)
+    out = torch.zeros((3, Hq, d), dtype=tdt, device=cuda)
+    st = torch.zeros(1, dtype=torch.int32, device=cuda)
+    tq.decode_splitk_elem(qt.to(cuda), dev(cuda, cache["key_cache"]), dev(cuda, cache["value_cache"]),
+                          dev(cuda, cache["scale_cache"]), dev(cuda, cache["block_tables"]),
+                          dev(cuda, cache["context_lens"]), dev(cuda, cache["signs"].astype(np.float32)), out,
+                          num_heads=Hq, num_kv_heads=Hkv, head_size=d, block_size=S,
+                          num_blocks=cache["num_blocks"], inv_sqrt_len=hp.inv_sqrt_len(d), softmax_scale=0.09,
+                          splits=splits, workspace=ws, gate=gt.to(cuda) if stage == 2 else None,
+                          output_stage=stage, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    got = out.float().cpu().numpy()
+    half_ulp = (2.0 ** -9 if elem == "bf16" else 2.0 ** -12) * np.abs(want)
+    err = np.abs(got - want)
+    assert (err <= ABS_TOL + REL_TOL * np.abs(want) + half_ulp).all()
+
+
 def test_peaked_softmax_without_scale(cuda, oracle):
     """No softmax scale (the AIC decoder's convention): scores of std ~ sqrt(d)."""
     rng = np.random.default_rng(9)
