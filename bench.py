@@ -302,9 +302,9 @@ def run_ours(args):
 
 # dram bytes (read + write) per algorithmic byte of the decode export kernel, from the ncu
 # capture of the small ragged case (profiles/decode_partial_kernel_small_ragged.md):
-# 224.49 MB + 5.77 MB over 223.39 MB. Traffic grows with the cache bytes read, so the full
+# 224.52 MB + 7.53 MB over 223.39 MB. Traffic grows with the cache bytes read, so the full
 # launch is scaled by its algorithmic bytes.
-DECODE_TRAFFIC_BYTES_PER_ALGORITHMIC_BYTE = 1.0308
+DECODE_TRAFFIC_BYTES_PER_ALGORITHMIC_BYTE = 1.0387
 
 
 def side_measurements(torch, tq, dev, args):
