@@ -37,6 +37,7 @@ SIGNATURES = {
                                             vp]),
     "tq_splitk_combine": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, u32, f32,
                                     vp]),
+    "tq_rotate_query": (C.c_int, [vp, vp, vp, vp, u32, u32, f32]),
     "tq_hadamard16": (C.c_int, [vp, vp, vp, u32, u32]),
     "tq_lloydmax4_quantize": (C.c_int, [vp, vp, vp, vp, C.c_size_t]),
     "tq_icdf_quantize": (C.c_int, [vp, vp, u32, vp, C.c_size_t]),

@@ -10,7 +10,10 @@
 //     the upper bin, unsigned codes packed low nibble first, reconstruction = centroid;
 //   * the inverse-CDF int4 quantiser (routines/routine_vector_icdf_quantize.hpp:95-132;
 //     oracle tests/cpu/icdf_fixture.hpp:124-142): y = 14 sigmoid(x) - 7, round to nearest
-//     even, saturate to [-8, 7], two's-complement nibbles packed low first.
+//     even, saturate to [-8, 7], two's-complement nibbles packed low first;
+//   * the stand-alone query rotation Q_rot = Q Pi^T, rounded to bf16
+//     (routines/routine_cube_decode_score.hpp:202-223), which the decoders otherwise do in
+//     their own prologue.
 #include <cuda_fp16.h>
 
 #include "tq_lloydmax.cuh"
@@ -98,7 +101,47 @@ __global__ void __launch_bounds__(256) tq_icdf_kernel(const uint16_t* __restrict
     packed[g] = w;
 }
 
+// q_rot = bf16(Pi q): one warp per row, the FP32 ingress cascade of the decoders.
+template <int D>
+__global__ void __launch_bounds__(128) tq_rotate_query_kernel(const uint16_t* __restrict__ q,
+                                                              const float* __restrict__ signs,
+                                                              uint16_t* __restrict__ q_rot, uint32_t rows,
+                                                              float inv_sqrt_len)
+{
+    constexpr int K = D / 32;
+    const int lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * 4u + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float sgn[K], v[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) {
+        sgn[i] = signs[lane * K + i] < 0.0f ? -1.0f : 1.0f;
+        v[i] = bf16_bits_to_f32(q[static_cast<size_t>(row) * D + lane * K + i]);
+    }
+    cascade_ingress<K>(v, sgn, lane);
+#pragma unroll
+    for (int i = 0; i < K; ++i)
+        q_rot[static_cast<size_t>(row) * D + lane * K + i] = f32_to_bf16_bits(v[i] * inv_sqrt_len);
+}
+
 }  // namespace tq
+
+// Q_rot = Q Pi^T for `rows` bf16 query vectors, rounded to bf16: the operand the decoders pin
+// (routines/routine_cube_decode_score.hpp:202-223; tests/common/paged_decode_oracle.hpp:486-515).
+// The decode entry points rotate in the kernel; this is the stand-alone form.
+extern "C" int tq_rotate_query(void* stream, const uint16_t* query, const float* pi_signs,
+                               uint16_t* query_rot, uint32_t rows, uint32_t head_size,
+                               float inv_sqrt_len)
+{
+    if (head_size != 128 && head_size != 256) return TQ_ERR_INVALID_ARGUMENT;
+    if (rows == 0) return TQ_OK;
+    if (!query || !pi_signs || !query_rot) return TQ_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned blocks = (rows + 3u) / 4u;
+    if (head_size == 128) tq::tq_rotate_query_kernel<128><<<blocks, 128, 0, s>>>(query, pi_signs, query_rot, rows, inv_sqrt_len);
+    else tq::tq_rotate_query_kernel<256><<<blocks, 128, 0, s>>>(query, pi_signs, query_rot, rows, inv_sqrt_len);
+    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
 
 extern "C" int tq_hadamard16(void* stream, const uint16_t* x_f16, void* y, uint32_t out_dtype,
                              uint32_t tiles)

@@ -190,6 +190,13 @@ def splitk_combine(workspace, pi_signs, gate, output, *, items, rows, rows_strid
         "tq_splitk_combine")
 
 
+def rotate_query(query, pi_signs, query_rot, *, head_size, inv_sqrt_len, stream=None):
+    """query_rot = bf16(Pi query) for every head_size-long bf16 vector of `query`."""
+    lib = load_library()
+    _check(lib.tq_rotate_query(_stream(stream), _ptr(query), _ptr(pi_signs), _ptr(query_rot),
+                               query.numel() // head_size, head_size, inv_sqrt_len), "tq_rotate_query")
+
+
 # ------------------------------------------------------------ stand-alone routines
 def hadamard16(x_f16, out):
     """Y = X x H16 on 16x16 FP16 tiles (reference: cube_hadamard16); out float32/float16/bfloat16."""

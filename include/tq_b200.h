@@ -254,6 +254,13 @@ int tq_decode_splitk_elem(void* stream, const void* query, const int8_t* key_cac
 /* ------------------------------------------------------- stand-alone routines
  * The reference's single-purpose routines that its cache operators do not call. */
 
+/* Q_rot = Q Pi^T for `rows` bf16 vectors of head_size 128 or 256, rounded to bf16: the rotated
+ * operand the decoders pin (routines/routine_cube_decode_score.hpp:202-223;
+ * tests/common/paged_decode_oracle.hpp:486-515). tq_decode_* rotate inside the kernel; this
+ * is the stand-alone form of the same arithmetic. */
+int tq_rotate_query(void* stream, const uint16_t* query, const float* pi_signs, uint16_t* query_rot,
+                    uint32_t rows, uint32_t head_size, float inv_sqrt_len);
+
 /* Y = X x H16 on `tiles` 16x16 tiles, X FP16 row-major, H16[k][c] = (-1)^popcount(k & c),
  * FP32 accumulation; y is float, half or bf16 by out_dtype (TQ_DTYPE_*). Replaces
  * cube_hadamard16 (routines/routine_cube_hadamard16.hpp:32-84; golden model
