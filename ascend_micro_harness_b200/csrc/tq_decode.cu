@@ -41,12 +41,6 @@
 namespace tq {
 
 constexpr int kDecWarps = 4;
-#ifndef TQ_D256_STAGES
-#define TQ_D256_STAGES 2
-#endif
-#ifndef TQ_D256_CTAS
-#define TQ_D256_CTAS 3
-#endif
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -79,11 +73,12 @@ struct DecodeSmem {
     // d = 128: two stages of 3 strips for each of four warps are 51 KiB, four CTAs fit and the
     // kernel stays within 128 registers (measured against 3 stages of 2 strips: +1.7 %, the
     // per-tile bookkeeping is spread over more strips; 6 stages of 1 strip: -8 %). d = 256
-    // doubles both the strips and the accumulator registers: two stages of 2 strips, three
-    // CTAs of up to 168 registers.
-    static constexpr int kTileStrips = D == 128 ? 3 : 2;
-    static constexpr int kStages = D == 128 ? 2 : TQ_D256_STAGES;
-    static constexpr int kCtasPerSm = D == 128 ? 4 : TQ_D256_CTAS;
+    // doubles both the strips and the accumulator registers: three stages of 1 strip, three
+    // CTAs of up to 168 registers (measured against 2 stages of 2 strips: +13 %, the smaller
+    // tile leaves room in the register file; 2 CTAs of 255 registers: +7 %).
+    static constexpr int kTileStrips = D == 128 ? 3 : 1;
+    static constexpr int kStages = D == 128 ? 2 : 3;
+    static constexpr int kCtasPerSm = D == 128 ? 4 : 3;
     static constexpr int kRowBytes = D / 2;
     static constexpr int kStripBytes = kStrip * D / 2;
     static constexpr int kStripStage = 2 * kStripBytes + 2 * kStrip * 4;   // K, V, both scale runs
