@@ -13,9 +13,9 @@
 // Mapping onto the SM:
 //   * one CTA per (sequence, KV head, split, 8-row query tile); its page range
 //     is the reference Partition (include/turboquant_splitk_contract.hpp:129-136);
-//     four warps each own every fourth 32-token tile of the range and keep their
-//     own (m, l, acc), merged through shared memory at the end;
-//   * every warp streams its tiles through a private three-stage cp.async ring:
+//     four warps each own every fourth tile (3 strips at d = 128, 1 at d = 256) of the
+//     range and keep their own (m, l, acc), merged through shared memory at the end;
+//   * every warp streams its tiles through a private cp.async ring (2 or 3 stages):
 //     whole packed key strips, value strips and both scale runs, resolved through
 //     the block table one tile ahead, so every KV byte crosses HBM once for all
 //     query rows of the GQA group;
