@@ -26,6 +26,8 @@ SIGNATURES = {
                                    u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
     "tq_decode_splitk_elem": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                         u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
+    "tq_decode_splitk_mtp": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
+                                       u32, u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
     "tq_decode_splitk_static": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32,
                                           u32, u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
     "tq_decode_splitk_export": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,

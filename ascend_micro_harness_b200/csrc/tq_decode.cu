@@ -60,6 +60,7 @@ struct DecodeParams {
     uint32_t sp_shift;        // log2(strips per page); pages hold 16 * 2^k tokens
     uint32_t chunk_pages;     // 0: every sequence uses `splits`; else at most ceil(pages/chunk)
     uint32_t q_f16;           // 1: the query is FP16 and its rotation stays FP32 (no bf16 rounding)
+    uint32_t tokens_per_req;  // query tokens per request (1 + speculative): row = token * G + head-in-group
     float inv_sqrt_len, softmax_scale;
     uint32_t* status;
 };
@@ -309,8 +310,13 @@ tq_decode_partial_kernel(const DecodeParams p)
 #pragma unroll
             for (int i = 0; i < K; ++i) v[i] = 0.f;
             if (row < rows_here) {
+                // row = token * G + g of the request's (1 + speculative) query tokens; with one
+                // token per request this is (item * rows + row)
+                const uint32_t row_g = row_tile * 8u + row, grp = p.rows / p.tokens_per_req;
+                const uint32_t q_tok = row_g / grp, q_g = row_g - q_tok * grp;
                 const uint16_t* qsrc =
-                    p.q + (static_cast<size_t>(item) * p.rows + row_tile * 8u + row) * D + lane * K;
+                    p.q + ((static_cast<size_t>(seq) * p.tokens_per_req + q_tok) * (p.H * grp) +
+                           static_cast<size_t>(head) * grp + q_g) * D + lane * K;
 #pragma unroll
                 for (int i = 0; i < K; ++i)
                     v[i] = p.q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
@@ -478,6 +484,17 @@ tq_decode_partial_kernel(const DecodeParams p)
         else return __int2float_rn(v);
     };
 
+    // Speculative tokens: query token t of a request sees the context without the last
+    // (tokens_per_req - 1 - t) tokens. row_drop[q] is that count for this thread's two rows.
+    uint32_t row_drop[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const uint32_t row_g = row_tile * 8u + qd * 2 + q, grp = p.rows / p.tokens_per_req;
+        const uint32_t t = min(row_g / grp, p.tokens_per_req - 1u);
+        row_drop[q] = p.tokens_per_req - 1u - t;
+    }
+    const uint32_t ctx_all = ctx >= p.tokens_per_req - 1u ? ctx - (p.tokens_per_req - 1u) : 0u;   // tokens every row sees
+
     // One tile: scores^T for its strips, the online-softmax update, then acc^T += V^T P^T.
     // TAIL tiles reach past the split's strips or past the live tokens and mask by
     // overwriting (a dead slot's scale may be a NaN); full tiles carry no masking code.
@@ -541,6 +558,14 @@ tq_decode_partial_kernel(const DecodeParams p)
                 live[ts][1] = strip < s1 && strip * kStrip + tok_hi < ctx;
                 if (!live[ts][0]) { sc[ts][0] = sc[ts][1] = kMaskedScore; vs[ts][0] = 0.f; }
                 if (!live[ts][1]) { sc[ts][2] = sc[ts][3] = kMaskedScore; vs[ts][1] = 0.f; }
+                if (p.tokens_per_req > 1u) {   // the last tokens are hidden from the earlier query tokens
+                    const uint32_t t_lo = strip * kStrip + tok_lo, t_hi = strip * kStrip + tok_hi;
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        if (t_lo + row_drop[q] >= ctx) sc[ts][q] = kMaskedScore;
+                        if (t_hi + row_drop[q] >= ctx) sc[ts][2 + q] = kMaskedScore;
+                    }
+                }
             }
             mx[0] = max3(mx[0], sc[ts][0], sc[ts][2]);
             mx[1] = max3(mx[1], sc[ts][1], sc[ts][3]);
@@ -565,7 +590,9 @@ tq_decode_partial_kernel(const DecodeParams p)
                 const float m_new = fmaxf(m_run[q], mx[q]);
                 alpha[q] = ex2f((m_run[q] - m_new) * rfac[q]);
                 m_run[q] = m_new;
-                m_fac[q] = m_new * rfac[q];
+                // a row that has seen no live token yet keeps offset 0: its masked scores must
+                // still give exp2(-huge) = 0, not exp2(0)
+                m_fac[q] = m_new > -1.0e37f ? m_new * rfac[q] : 0.f;
                 l_run[q] *= alpha[q];
             }
             if (vmax > vnorm) {  // warp-uniform: value scales depend on the token only
@@ -633,7 +660,7 @@ tq_decode_partial_kernel(const DecodeParams p)
         __syncwarp();
         const uint8_t* st = my_ring + stage * L::kStageBytes;
         if (++stage == kStages) stage = 0;
-        if (strip_t + kTileStrips > s1 || (strip_t + kTileStrips) * kStrip > ctx)
+        if (strip_t + kTileStrips > s1 || (strip_t + kTileStrips) * kStrip > ctx_all)
             compute_tile(st, strip_t, std::true_type{});
         else
             compute_tile(st, strip_t, std::false_type{});
@@ -703,6 +730,7 @@ struct CombineParams {
     float inv_sqrt_len;
     uint32_t block16;   // 1: the rotation is block-diagonal H16 / 4 (Lloyd-Max cache variant)
     uint32_t gate_dtype; // TQ_DTYPE_* of `gate`
+    uint32_t tokens_per_req, kv_heads;   // output row of (item, row): see out_row below
 };
 
 // One CTA per (item, row): merge `splits` records, normalise, optionally rotate
@@ -715,6 +743,12 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
     __shared__ float buf[2][D];
     const uint32_t item = blockIdx.x / p.rows, row = blockIdx.x % p.rows;
     const int c = threadIdx.x;
+    // (item, row) = (sequence, KV head, query token, head in group) -> row of the [tokens][heads]
+    // output; with one query token per request this is blockIdx.x
+    const uint32_t grp = p.rows / p.tokens_per_req, o_tok = row / grp, o_g = row - o_tok * grp;
+    const uint32_t o_seq = item / p.kv_heads, o_head = item - o_seq * p.kv_heads;
+    const size_t out_row = (static_cast<size_t>(o_seq) * p.tokens_per_req + o_tok) * (p.kv_heads * grp) +
+                           static_cast<size_t>(o_head) * grp + o_g;
     const float* base = p.workspace + (static_cast<size_t>(item) * p.splits * p.rows_stride + row) * kRecord;
     const size_t split_stride = static_cast<size_t>(p.rows_stride) * kRecord;
     // All records are fetched before the first one is merged, so the loads overlap instead
@@ -761,14 +795,14 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
         }
         if (p.output_stage == TQ_OUT_GATED)
         {
-            const size_t gi = static_cast<size_t>(blockIdx.x) * D + c;
+            const size_t gi = out_row * D + c;
             const float gt = p.gate_dtype == TQ_DTYPE_F32 ? static_cast<const float*>(p.gate)[gi]
                              : p.gate_dtype == TQ_DTYPE_F16 ? __half2float(static_cast<const __half*>(p.gate)[gi])
                                                             : bf16_bits_to_f32(static_cast<const uint16_t*>(p.gate)[gi]);
             v = v / (1.0f + __expf(-gt));
         }
     }
-    const size_t at = static_cast<size_t>(blockIdx.x) * D + c;
+    const size_t at = out_row * D + c;
     if (p.out_dtype == TQ_DTYPE_F32) static_cast<float*>(p.output)[at] = v;
     else if (p.out_dtype == TQ_DTYPE_F16) static_cast<__half*>(p.output)[at] = __float2half_rn(v);
     else static_cast<uint16_t*>(p.output)[at] = f32_to_bf16_bits(v);
@@ -888,6 +922,7 @@ extern "C" int tq_decode_splitk_partials(void* stream, const uint16_t* q, const 
         !aligned16(scale_cache))
         return TQ_ERR_INVALID_ARGUMENT;
     DecodeParams p{};
+    p.tokens_per_req = 1;
     p.sp_shift = sp_shift;
     p.q = q;
     p.signs = signs;
@@ -921,7 +956,8 @@ extern "C" int tq_decode_splitk_partials(void* stream, const uint16_t* q, const 
 static int splitk_combine(void* stream, const float* workspace, const float* pi_signs,
                           const void* gate, uint32_t gate_dtype, void* output, uint32_t out_dtype,
                           uint32_t items, uint32_t rows, uint32_t rows_stride, uint32_t head_size,
-                          uint32_t splits, uint32_t output_stage, float inv_sqrt_len)
+                          uint32_t splits, uint32_t output_stage, float inv_sqrt_len,
+                          uint32_t tokens_per_req = 1, uint32_t kv_heads = 1)
 {
     if (!rows || rows > rows_stride || !splits || splits > 16 || output_stage > TQ_OUT_GATED ||
         out_dtype > TQ_DTYPE_F32 || gate_dtype > TQ_DTYPE_F32 ||
@@ -932,7 +968,8 @@ static int splitk_combine(void* stream, const float* workspace, const float* pi_
         return TQ_ERR_INVALID_ARGUMENT;
     if (items == 0) return TQ_OK;
     CombineParams p{workspace, pi_signs, gate, output, rows, rows_stride, splits, output_stage,
-                    out_dtype, inv_sqrt_len, pi_signs == nullptr ? 1u : 0u, gate_dtype};
+                    out_dtype, inv_sqrt_len, pi_signs == nullptr ? 1u : 0u, gate_dtype, tokens_per_req,
+                    kv_heads};
     const uint64_t grid = static_cast<uint64_t>(items) * rows;
     if (grid > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -978,14 +1015,15 @@ static int decode_export_planned(void* stream, const uint16_t* query, const int8
                                  uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
                                  uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
                                  uint32_t splits, uint32_t chunk_pages, float inv_sqrt_len,
-                                 float softmax_scale, uint32_t* status, bool q_f16 = false)
+                                 float softmax_scale, uint32_t* status, bool q_f16 = false,
+                                 uint32_t tokens_per_req = 1)
 {
     if (!num_heads || !num_kv_heads || num_heads % num_kv_heads != 0 || !block_size ||
         block_size % kStrip != 0 || !num_blocks || !max_blocks || !splits || splits > 16 ||
         (head_size != 128 && head_size != 256))
         return TQ_ERR_INVALID_ARGUMENT;
-    const uint32_t rows = num_heads / num_kv_heads;
-    if (rows > 16) return TQ_ERR_INVALID_ARGUMENT;
+    const uint32_t rows = num_heads / num_kv_heads * tokens_per_req;
+    if (rows > 16 || tokens_per_req == 0) return TQ_ERR_INVALID_ARGUMENT;
     if (batch == 0) return TQ_OK;
     if (!query || !key_cache || !value_cache || !scale_cache || !block_tables || !context_lens ||
         !pi_signs || !workspace)
@@ -995,6 +1033,7 @@ static int decode_export_planned(void* stream, const uint16_t* query, const int8
         !aligned16(scale_cache))
         return TQ_ERR_INVALID_ARGUMENT;
     DecodeParams p{};
+    p.tokens_per_req = 1;
     p.sp_shift = sp_shift;
     p.q = query;
     p.signs = pi_signs;
@@ -1016,6 +1055,7 @@ static int decode_export_planned(void* stream, const uint16_t* query, const int8
     p.splits = splits;
     p.chunk_pages = chunk_pages;
     p.q_f16 = q_f16 ? 1u : 0u;
+    p.tokens_per_req = tokens_per_req;
     p.page_begin = 0;
     p.page_count = 0;
     p.fixed_ctx = 0;
@@ -1057,7 +1097,7 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
                           uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
                           uint32_t chunk_pages, uint32_t output_stage, float inv_sqrt_len,
                           float softmax_scale, uint32_t* status, uint32_t gate_dtype = TQ_DTYPE_F32,
-                          bool q_f16 = false)
+                          bool q_f16 = false, uint32_t tokens_per_req = 1)
 {
     if (output_stage > TQ_OUT_GATED || !output || (output_stage == TQ_OUT_GATED && !gate))
         return TQ_ERR_INVALID_ARGUMENT;
@@ -1065,12 +1105,12 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
                                          block_tables, context_lens, pi_signs, workspace, batch,
                                          num_heads, num_kv_heads, head_size, block_size, num_blocks,
                                          max_blocks, splits, chunk_pages, inv_sqrt_len,
-                                         softmax_scale, status, q_f16);
+                                         softmax_scale, status, q_f16, tokens_per_req);
     if (st != TQ_OK || batch == 0) return st;
-    const uint32_t rows = num_heads / num_kv_heads;
+    const uint32_t rows = num_heads / num_kv_heads * tokens_per_req;
     return splitk_combine(stream, workspace, pi_signs, gate, gate_dtype, output, out_dtype,
                           batch * num_kv_heads, rows, rows, head_size, splits, output_stage,
-                          inv_sqrt_len);
+                          inv_sqrt_len, tokens_per_req, num_kv_heads);
 }
 
 // Query, gate and output in ONE 16-bit element type, FP16 or BF16, as the raw-query entry of
@@ -1120,6 +1160,33 @@ extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_
                           context_lens, pi_signs, gate, workspace, output, out_dtype, batch, num_heads,
                           num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,
                           chunk_pages, output_stage, inv_sqrt_len, softmax_scale, status);
+}
+
+// Several query tokens per request (a decode step that verifies speculative tokens): the
+// query is [batch * tokens_per_req][num_heads][d], token t of a request attends to
+// context_lens[b] - (tokens_per_req - 1 - t) tokens, and all tokens_per_req * (num_heads /
+// num_kv_heads) <= 16 rows of a KV head share one pass over its pages (the row tile of the
+// reference's draft for its GQA decoder, reports/qwen35_turboquant_rfc.md:221-236). The
+// workspace holds batch * num_kv_heads * splits * rows * (16 + d) floats.
+extern "C" int tq_decode_splitk_mtp(void* stream, const uint16_t* query, const int8_t* key_cache,
+                                    const int8_t* value_cache, const float* scale_cache,
+                                    const int32_t* block_tables, const int32_t* context_lens,
+                                    const float* pi_signs, const float* gate, float* workspace,
+                                    void* output, uint32_t out_dtype, uint32_t batch,
+                                    uint32_t tokens_per_req, uint32_t num_heads, uint32_t num_kv_heads,
+                                    uint32_t head_size, uint32_t block_size, uint32_t num_blocks,
+                                    uint32_t max_blocks, uint32_t splits, uint32_t max_context_hint,
+                                    uint32_t output_stage, float inv_sqrt_len, float softmax_scale,
+                                    uint32_t* status)
+{
+    if (!num_kv_heads || !block_size || splits > 16 || tokens_per_req == 0) return TQ_ERR_INVALID_ARGUMENT;
+    uint32_t chunk_pages = 0;
+    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
+                            &chunk_pages);
+    return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables, context_lens,
+                          pi_signs, gate, workspace, output, out_dtype, batch, num_heads, num_kv_heads,
+                          head_size, block_size, num_blocks, max_blocks, splits, chunk_pages, output_stage,
+                          inv_sqrt_len, softmax_scale, status, TQ_DTYPE_F32, false, tokens_per_req);
 }
 
 // ------------------------------------------------- decode without a caller workspace

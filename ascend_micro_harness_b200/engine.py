@@ -131,6 +131,23 @@ def decode_splitk_elem(query, key_cache, value_cache, scale_cache, block_tables,
         softmax_scale, _ptr(status)), "tq_decode_splitk_elem")
 
 
+def decode_splitk_mtp(query, key_cache, value_cache, scale_cache, block_tables, context_lens, pi_signs,
+                      output, *, tokens_per_req, num_heads, num_kv_heads, head_size, block_size, num_blocks,
+                      inv_sqrt_len, softmax_scale=1.0, splits=0, max_context_hint=0, workspace=None,
+                      gate=None, output_stage=OUT_ROTATED, status=None, stream=None):
+    """decode_splitk with tokens_per_req query tokens per request (speculative decoding):
+    query/output are [batch * tokens_per_req, num_heads, d]; token t sees the context without
+    its last tokens_per_req - 1 - t tokens."""
+    lib = load_library()
+    batch = query.numel() // (num_heads * head_size * tokens_per_req)
+    _check(lib.tq_decode_splitk_mtp(
+        _stream(stream), _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache),
+        _ptr(block_tables), _ptr(context_lens), _ptr(pi_signs), _ptr(gate), _ptr(workspace),
+        _ptr(output), _out_dtype(output), batch, tokens_per_req, num_heads, num_kv_heads, head_size,
+        block_size, num_blocks, block_tables.shape[-1], splits, max_context_hint, output_stage,
+        inv_sqrt_len, softmax_scale, _ptr(status)), "tq_decode_splitk_mtp")
+
+
 STATIC_WORKSPACE_FLOATS = 2 * 1024 * 1024
 
 

@@ -251,6 +251,23 @@ int tq_decode_splitk_elem(void* stream, const void* query, const int8_t* key_cac
                           uint32_t max_context_hint, uint32_t output_stage, float inv_sqrt_len,
                           float softmax_scale, uint32_t* status);
 
+/* Several query tokens per request (a step that verifies speculative tokens): query is
+ * [batch * tokens_per_req][num_heads][d], token t of request b attends to
+ * context_lens[b] - (tokens_per_req - 1 - t) tokens, output and gate are laid out like the
+ * query. All tokens_per_req * (num_heads / num_kv_heads) <= 16 rows of a KV head share one
+ * pass over its pages -- the row tile the reference drafts for its GQA decoder
+ * (reports/qwen35_turboquant_rfc.md:221-236). workspace: batch * num_kv_heads * splits * rows *
+ * (16 + d) floats with rows = tokens_per_req * num_heads / num_kv_heads. */
+int tq_decode_splitk_mtp(void* stream, const uint16_t* query, const int8_t* key_cache,
+                         const int8_t* value_cache, const float* scale_cache,
+                         const int32_t* block_tables, const int32_t* context_lens,
+                         const float* pi_signs, const float* gate, float* workspace, void* output,
+                         uint32_t out_dtype, uint32_t batch, uint32_t tokens_per_req,
+                         uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                         uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                         uint32_t splits, uint32_t max_context_hint, uint32_t output_stage,
+                         float inv_sqrt_len, float softmax_scale, uint32_t* status);
+
 /* ------------------------------------------------------- stand-alone routines
  * The reference's single-purpose routines that its cache operators do not call. */
 

@@ -160,6 +160,48 @@ def test_element_typed_entry(cuda, oracle, elem, stage):
     assert (err <= ABS_TOL + REL_TOL * np.abs(want) + half_ulp).all()
 
 
+@pytest.mark.parametrize("tpr,G,d", [(2, 6, 128), (3, 4, 128), (4, 4, 256), (2, 8, 256), (2, 1, 128)])
+def test_several_query_tokens_per_request(cuda, oracle, tpr, G, d):
+    """Speculative rows: token t of a request attends to the context without its last
+    tpr - 1 - t tokens; all tpr * G rows of a KV head share one pass over the pages. The
+    oracle is the ordinary decode run once per query token with that token's length."""
+    import torch
+    import ascend_micro_harness_b200 as tq
+    rng = np.random.default_rng(tpr * 100 + G)
+    Hkv, S = 2, 16
+    Hq = Hkv * G
+    ctx = [tpr, 16, 17 + tpr, 333, 1]          # includes a context shorter than the token count
+    B = len(ctx)
+    cache = hp.build_cache_from_gaussian(oracle, rng, ctx, Hkv, d, S)
+    q = hp.bf16_from_f32(rng.standard_normal((B, tpr, Hq, d)).astype(np.float32))
+    gate = rng.standard_normal((B, tpr, Hq, d)).astype(np.float32)
+    scale = float(1 / np.sqrt(d))
+    want = np.zeros((B, tpr, Hq, d))
+    for t in range(tpr):
+        lens = np.maximum(np.array(ctx) - (tpr - 1 - t), 0).astype(np.int32)
+        c2 = dict(cache, context_lens=lens)
+        want[:, t] = oracle_decode(oracle, np.ascontiguousarray(q[:, t]), c2, Hq, Hkv, d, S, 2,
+                                   np.ascontiguousarray(gate[:, t]), scale)
+    for splits in (1, 3, 0):
+        use = splits if splits else tq.choose_splits(B, Hkv, S, max(ctx))
+        ws = torch.full((B * Hkv * use * tpr * G * (16 + d),), float("nan"), device=cuda)
+        out = torch.zeros((B * tpr, Hq, d), dtype=torch.float32, device=cuda)
+        st = torch.zeros(1, dtype=torch.int32, device=cuda)
+        tq.decode_splitk_mtp(dev(cuda, q.reshape(B * tpr, Hq, d)), dev(cuda, cache["key_cache"]),
+                             dev(cuda, cache["value_cache"]), dev(cuda, cache["scale_cache"]),
+                             dev(cuda, cache["block_tables"]), dev(cuda, cache["context_lens"]),
+                             dev(cuda, cache["signs"].astype(np.float32)), out, tokens_per_req=tpr,
+                             num_heads=Hq, num_kv_heads=Hkv, head_size=d, block_size=S,
+                             num_blocks=cache["num_blocks"], inv_sqrt_len=hp.inv_sqrt_len(d),
+                             softmax_scale=scale, splits=splits, max_context_hint=max(ctx), workspace=ws,
+                             gate=dev(cuda, gate.reshape(B * tpr, Hq, d)), output_stage=2, status=st)
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        got = out.cpu().numpy().reshape(B, tpr, Hq, d)
+        assert np.isfinite(got).all()
+        assert_close(got, want)
+
+
 def test_peaked_softmax_without_scale(cuda, oracle):
     """No softmax scale (the AIC decoder's convention): scores of std ~ sqrt(d)."""
     rng = np.random.default_rng(9)
