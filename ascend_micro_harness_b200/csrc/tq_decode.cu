@@ -206,11 +206,16 @@ __device__ __forceinline__ float2 unpack_f16x2(uint32_t v)
 __device__ __forceinline__ int token_row_lo(int i) { return ((i >> 2) << 3) + (((i >> 1) & 1) << 1) + ((i & 1) << 2); }
 __device__ __forceinline__ int token_row_hi(int i) { return token_row_lo(i) + 1; }
 
-template <int D, bool PRECISE>
+// EXT compiles in the two extensions of the serving path -- f16 query elements and several
+// query tokens per request -- so that the plain instantiation carries neither their branches
+// nor their registers.
+template <int D, bool PRECISE, bool EXT>
 __global__ void __launch_bounds__(kDecWarps * 32, DecodeSmem<D>::kCtasPerSm)
 tq_decode_partial_kernel(const DecodeParams p)
 {
     using L = DecodeSmem<D>;
+    const uint32_t tokens_per_req = EXT ? p.tokens_per_req : 1u;
+    const bool q_f16 = EXT && p.q_f16 != 0u;
     constexpr int kStages = L::kStages;
     constexpr int kTileStrips = L::kTileStrips;
     constexpr int kRecord = 16 + D;
@@ -312,21 +317,21 @@ tq_decode_partial_kernel(const DecodeParams p)
             if (row < rows_here) {
                 // row = token * G + g of the request's (1 + speculative) query tokens; with one
                 // token per request this is (item * rows + row)
-                const uint32_t row_g = row_tile * 8u + row, grp = p.rows / p.tokens_per_req;
+                const uint32_t row_g = row_tile * 8u + row, grp = p.rows / tokens_per_req;
                 const uint32_t q_tok = row_g / grp, q_g = row_g - q_tok * grp;
                 const uint16_t* qsrc =
-                    p.q + ((static_cast<size_t>(seq) * p.tokens_per_req + q_tok) * (p.H * grp) +
+                    p.q + ((static_cast<size_t>(seq) * tokens_per_req + q_tok) * (p.H * grp) +
                            static_cast<size_t>(head) * grp + q_g) * D + lane * K;
 #pragma unroll
                 for (int i = 0; i < K; ++i)
-                    v[i] = p.q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
+                    v[i] = q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
             }
             cascade_ingress<K>(v, sgn, lane);
             float am = 0.f;
 #pragma unroll
             for (int i = 0; i < K; ++i) {
                 float val = v[i] * p.inv_sqrt_len;
-                if (!p.q_f16) {   // the bf16 operand the reference pins (and publishes)
+                if (!q_f16) {   // the bf16 operand the reference pins (and publishes)
                     const uint16_t bits = f32_to_bf16_bits(val);
                     val = bf16_bits_to_f32(bits);
                     if (p.q_rot != nullptr && row < rows_here)
@@ -489,11 +494,12 @@ tq_decode_partial_kernel(const DecodeParams p)
     uint32_t row_drop[2];
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
-        const uint32_t row_g = row_tile * 8u + qd * 2 + q, grp = p.rows / p.tokens_per_req;
-        const uint32_t t = min(row_g / grp, p.tokens_per_req - 1u);
-        row_drop[q] = p.tokens_per_req - 1u - t;
+        const uint32_t row_g = row_tile * 8u + qd * 2 + q, grp = p.rows / tokens_per_req;
+        const uint32_t t = min(row_g / grp, tokens_per_req - 1u);
+        row_drop[q] = tokens_per_req - 1u - t;
     }
-    const uint32_t ctx_all = ctx >= p.tokens_per_req - 1u ? ctx - (p.tokens_per_req - 1u) : 0u;   // tokens every row sees
+    const uint32_t drop_max = tokens_per_req - 1u;
+    const uint32_t ctx_all = ctx > drop_max ? ctx - drop_max : 0u;   // tokens every row sees
 
     // One tile: scores^T for its strips, the online-softmax update, then acc^T += V^T P^T.
     // TAIL tiles reach past the split's strips or past the live tokens and mask by
@@ -558,7 +564,7 @@ tq_decode_partial_kernel(const DecodeParams p)
                 live[ts][1] = strip < s1 && strip * kStrip + tok_hi < ctx;
                 if (!live[ts][0]) { sc[ts][0] = sc[ts][1] = kMaskedScore; vs[ts][0] = 0.f; }
                 if (!live[ts][1]) { sc[ts][2] = sc[ts][3] = kMaskedScore; vs[ts][1] = 0.f; }
-                if (p.tokens_per_req > 1u) {   // the last tokens are hidden from the earlier query tokens
+                if (tokens_per_req > 1u) {   // the last tokens are hidden from the earlier query tokens
                     const uint32_t t_lo = strip * kStrip + tok_lo, t_hi = strip * kStrip + tok_hi;
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
@@ -821,8 +827,8 @@ static bool page_size_ok(uint32_t block_size, uint32_t* sp_shift)
 
 static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0u; }
 
-template <int D, bool PRECISE>
-static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
+template <int D, bool PRECISE, bool EXT>
+static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p)
 {
     // Opt in to the large dynamic shared-memory carve-out once per device. The
     // flags race benignly: setting the attribute twice is harmless.
@@ -830,7 +836,7 @@ static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorNoDevice;
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(tq_decode_partial_kernel<D, PRECISE>,
+        cudaError_t e = cudaFuncSetAttribute(tq_decode_partial_kernel<D, PRECISE, EXT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              DecodeSmem<D>::kTotal);
         if (e != cudaSuccess) return e;
@@ -839,9 +845,16 @@ static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
     const uint64_t grid = static_cast<uint64_t>(p.items) * ((p.rows + 7u) / 8u) * p.splits;
     if (grid == 0) return cudaSuccess;
     if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
-    tq_decode_partial_kernel<D, PRECISE><<<static_cast<unsigned>(grid), kDecWarps * 32,
+    tq_decode_partial_kernel<D, PRECISE, EXT><<<static_cast<unsigned>(grid), kDecWarps * 32,
                                   DecodeSmem<D>::kTotal, stream>>>(p);
     return cudaGetLastError();
+}
+
+template <int D, bool PRECISE>
+static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
+{
+    if (p.q_f16 != 0u || p.tokens_per_req > 1u) return launch_partial_as<D, PRECISE, true>(stream, p);
+    return launch_partial_as<D, PRECISE, false>(stream, p);
 }
 
 }  // namespace tq

@@ -213,6 +213,26 @@ def test_peaked_softmax_without_scale(cuda, oracle):
     assert_close(got, want)
 
 
+def test_value_amplitude_scales_the_output(cuda, oracle):
+    """The tolerance is stated for unit-variance values. Values 64 times larger (a power of
+    two: same codes, scales shifted by six exponents) give 64 times the output, and the error
+    bound scales with them."""
+    rng = np.random.default_rng(21)
+    Hq, Hkv, d, S = 8, 2, 128, 16
+    cache = hp.build_cache_from_gaussian(oracle, rng, [700, 33], Hkv, d, S)
+    q = hp.bf16_from_f32(rng.standard_normal((2, Hq, d)).astype(np.float32))
+    base = run_decode(cuda, q, cache, Hq, Hkv, d, S, 2, softmax_scale=0.1)
+    loud = dict(cache)
+    sc = cache["scale_cache"].copy().reshape(2, -1)
+    sc[1] *= np.float32(64.0)   # the value plane of the planar scale cache
+    loud["scale_cache"] = sc.reshape(-1)
+    got = run_decode(cuda, q, loud, Hq, Hkv, d, S, 2, softmax_scale=0.1)
+    want = oracle_decode(oracle, q, loud, Hq, Hkv, d, S, softmax_scale=0.1)
+    err = np.abs(got - want)
+    assert (err <= 64.0 * ABS_TOL + REL_TOL * np.abs(want)).all()
+    assert np.allclose(got, 64.0 * base, rtol=1e-5, atol=64.0 * 1e-5)
+
+
 def run_partials(cuda, fx, splits, begin, count, seq_len, table_bf16):
     """The reference AIC contract: 16 rows, d=256, records of 272 floats."""
     import torch
