@@ -61,6 +61,8 @@ struct DecodeParams {
     uint32_t chunk_pages;     // 0: every sequence uses `splits`; else at most ceil(pages/chunk)
     uint32_t q_f16;           // 1: the query is FP16 and its rotation stays FP32 (no bf16 rounding)
     uint32_t tokens_per_req;  // query tokens per request (1 + speculative): row = token * G + head-in-group
+    const float* q_f32;       // non-null: the query is FP32 and already rotated (no rotation, no rounding)
+    uint32_t midrise;         // 1: a code c stands for (c + 0.5) * scale (uniform mid-rise grid)
     float inv_sqrt_len, softmax_scale;
     uint32_t* status;
 };
@@ -206,9 +208,9 @@ __device__ __forceinline__ float2 unpack_f16x2(uint32_t v)
 __device__ __forceinline__ int token_row_lo(int i) { return ((i >> 2) << 3) + (((i >> 1) & 1) << 1) + ((i & 1) << 2); }
 __device__ __forceinline__ int token_row_hi(int i) { return token_row_lo(i) + 1; }
 
-// EXT compiles in the two extensions of the serving path -- f16 query elements and several
-// query tokens per request -- so that the plain instantiation carries neither their branches
-// nor their registers.
+// EXT compiles in the extensions of the serving path -- f16 or pre-rotated FP32 query
+// elements, several query tokens per request, mid-rise codes -- so that the plain
+// instantiation carries neither their branches nor their registers.
 template <int D, bool PRECISE, bool EXT>
 __global__ void __launch_bounds__(kDecWarps * 32, DecodeSmem<D>::kCtasPerSm)
 tq_decode_partial_kernel(const DecodeParams p)
@@ -216,6 +218,8 @@ tq_decode_partial_kernel(const DecodeParams p)
     using L = DecodeSmem<D>;
     const uint32_t tokens_per_req = EXT ? p.tokens_per_req : 1u;
     const bool q_f16 = EXT && p.q_f16 != 0u;
+    const bool prerot = EXT && p.q_f32 != nullptr;
+    const bool midrise = EXT && p.midrise != 0u;
     constexpr int kStages = L::kStages;
     constexpr int kTileStrips = L::kTileStrips;
     constexpr int kRecord = 16 + D;
@@ -225,6 +229,7 @@ tq_decode_partial_kernel(const DecodeParams p)
     float* qbuf = reinterpret_cast<float*>(smem);            // [2][8][D], prologue only
     uint8_t* ring = smem;                                    // aliases qbuf after the prologue
     __shared__ float row_unscale[8];                         // per query row: 2^-k * softmax_scale * log2e
+    __shared__ int row_qsum8[8];                             // mid-rise codes: 8 * sum of the row's fixed-point query
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, qd = lane & 3;
@@ -309,7 +314,7 @@ tq_decode_partial_kernel(const DecodeParams p)
         float sgn[K];
 #pragma unroll
         for (int i = 0; i < K; ++i)
-            sgn[i] = sign_is_negative(p.signs, p.sign_source, lane * K + i) ? -1.0f : 1.0f;
+            sgn[i] = !prerot && sign_is_negative(p.signs, p.sign_source, lane * K + i) ? -1.0f : 1.0f;
         for (int row = warp * 2; row < warp * 2 + 2; ++row) {
             float v[K];
 #pragma unroll
@@ -319,19 +324,20 @@ tq_decode_partial_kernel(const DecodeParams p)
                 // token per request this is (item * rows + row)
                 const uint32_t row_g = row_tile * 8u + row, grp = p.rows / tokens_per_req;
                 const uint32_t q_tok = row_g / grp, q_g = row_g - q_tok * grp;
-                const uint16_t* qsrc =
-                    p.q + ((static_cast<size_t>(seq) * tokens_per_req + q_tok) * (p.H * grp) +
-                           static_cast<size_t>(head) * grp + q_g) * D + lane * K;
+                const size_t qoff = ((static_cast<size_t>(seq) * tokens_per_req + q_tok) * (p.H * grp) +
+                                     static_cast<size_t>(head) * grp + q_g) * D + lane * K;
+                const uint16_t* qsrc = p.q + qoff;
 #pragma unroll
                 for (int i = 0; i < K; ++i)
-                    v[i] = q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
+                    v[i] = prerot ? p.q_f32[qoff + i]
+                                  : q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
             }
-            cascade_ingress<K>(v, sgn, lane);
+            if (!prerot) cascade_ingress<K>(v, sgn, lane);
             float am = 0.f;
 #pragma unroll
             for (int i = 0; i < K; ++i) {
-                float val = v[i] * p.inv_sqrt_len;
-                if (!q_f16) {   // the bf16 operand the reference pins (and publishes)
+                float val = prerot ? v[i] : v[i] * p.inv_sqrt_len;
+                if (!q_f16 && !prerot) {   // the bf16 operand the reference pins (and publishes)
                     const uint16_t bits = f32_to_bf16_bits(val);
                     val = bf16_bits_to_f32(bits);
                     if (p.q_rot != nullptr && row < rows_here)
@@ -350,8 +356,19 @@ tq_decode_partial_kernel(const DecodeParams p)
             const int e_bits = __float_as_int(am) & 0x7F800000;
             const float up = tiny ? 0.0f : __int_as_float(((254 + kTop) << 23) - e_bits);
             const float down = tiny ? 1.0f : __int_as_float(e_bits - (kTop << 23));
+            int qsum = 0;
 #pragma unroll
-            for (int i = 0; i < K; ++i) qfix[q_index(row, lane * K + i)] = __float2int_rn(v[i] * up);
+            for (int i = 0; i < K; ++i) {
+                const int fx = __float2int_rn(v[i] * up);
+                qfix[q_index(row, lane * K + i)] = fx;
+                qsum += fx;
+            }
+            if (midrise) {
+                // sum_c q_c (16 code_c + 8): the half step of every code adds 8 * sum_c q_c to a raw score
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
+                if (lane == 0) row_qsum8[row] = 8 * qsum;
+            }
             if (lane == 0) row_unscale[row] = down * 0.0625f * p.softmax_scale * kLog2e;
         }
     }
@@ -381,6 +398,8 @@ tq_decode_partial_kernel(const DecodeParams p)
     }
     // scores are kept as raw * key_scale; the per-row factor enters inside the exponent
     const float rfac[2] = {row_unscale[qd * 2], row_unscale[qd * 2 + 1]};
+    const int qs8[2] = {midrise ? row_qsum8[qd * 2] : 0, midrise ? row_qsum8[qd * 2 + 1] : 0};
+    float ps[2] = {0.f, 0.f};   // mid-rise codes: running sum of P (as the value contraction sees it) per row
     __syncthreads();  // everyone is done with qbuf: the ring may overwrite it
 
     // ---- per-warp pipeline over tiles warp, warp+4, ...
@@ -543,7 +562,9 @@ tq_decode_partial_kernel(const DecodeParams p)
                 if constexpr (NL == 2) {
                     // |c1| * 256 + |c0| < 2^31 at either head size: the two limbs combine in
                     // INT32 and one conversion follows
-                    c[i] = __int2float_rn(ci[1][i] * 256 + ci[0][i]);
+                    int sum = ci[1][i] * 256 + ci[0][i];
+                    if constexpr (EXT) sum += qs8[i & 1];   // < 2^30 + 2^26
+                    c[i] = __int2float_rn(sum);
                     continue;
                 }
                 float f = limb_value(ci[NL - 1][i]);
@@ -616,6 +637,10 @@ tq_decode_partial_kernel(const DecodeParams p)
                 acc[mt][2] *= alpha[0];
                 acc[mt][3] *= alpha[1];
             }
+            if constexpr (EXT) {
+                ps[0] *= alpha[0];
+                ps[1] *= alpha[1];
+            }
         }
         // -- P, then acc^T += V^T P^T
 #pragma unroll
@@ -634,6 +659,13 @@ tq_decode_partial_kernel(const DecodeParams p)
             }
             const uint32_t h0 = pack_f16x2(pw[0], pw[1]), h1 = pack_f16x2(pw[2], pw[3]);
             const uint32_t bh0 = movmatrix_trans(h0), bh1 = movmatrix_trans(h1);
+            if constexpr (EXT) {
+                if (midrise) {   // the f16 values the MMA multiplies, so that acc and ps stay consistent
+                    const float2 f0 = unpack_f16x2(h0), f1 = unpack_f16x2(h1);
+                    ps[0] += f0.x + f1.x;
+                    ps[1] += f0.y + f1.y;
+                }
+            }
             [[maybe_unused]] uint32_t bl0 = 0, bl1 = 0;
             if constexpr (PRECISE) {
                 const float2 f0 = unpack_f16x2(h0), f1 = unpack_f16x2(h1);
@@ -681,6 +713,19 @@ tq_decode_partial_kernel(const DecodeParams p)
         l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 8);
         l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 16);
     }
+    // mid-rise codes: sum_t P_t (code_t + 0.5) = acc + 0.5 * sum_t P_t, the same for every channel
+    float half_p[2] = {0.f, 0.f};
+    if constexpr (EXT) {
+        if (midrise) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                ps[q] += __shfl_xor_sync(0xffffffffu, ps[q], 4);
+                ps[q] += __shfl_xor_sync(0xffffffffu, ps[q], 8);
+                ps[q] += __shfl_xor_sync(0xffffffffu, ps[q], 16);
+                half_p[q] = 0.5f * ps[q];
+            }
+        }
+    }
     __syncthreads();  // every warp is done with its ring; reuse it
     // Row pitch d + 4 floats: a lane stores its two adjacent channels of a row as one
     // 8-byte word, and with this pitch the 16 lanes of a half-warp hit 16 different banks pairs.
@@ -696,9 +741,9 @@ tq_decode_partial_kernel(const DecodeParams p)
     for (int mt = 0; mt < MT; ++mt) {
         const int ch = mt * 16 + 2 * r;
         *reinterpret_cast<float2*>(merge + (qd * 2 + 0) * kPitch + 2 + ch) =
-            make_float2(acc[mt][0] * vnorm, acc[mt][2] * vnorm);
+            make_float2((acc[mt][0] + half_p[0]) * vnorm, (acc[mt][2] + half_p[0]) * vnorm);
         *reinterpret_cast<float2*>(merge + (qd * 2 + 1) * kPitch + 2 + ch) =
-            make_float2(acc[mt][1] * vnorm, acc[mt][3] * vnorm);
+            make_float2((acc[mt][1] + half_p[1]) * vnorm, (acc[mt][3] + half_p[1]) * vnorm);
     }
     __syncthreads();
     // Inside the kernel m is in units of raw * key_scale; row_unscale turns a difference
@@ -853,7 +898,8 @@ static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p)
 template <int D, bool PRECISE>
 static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
 {
-    if (p.q_f16 != 0u || p.tokens_per_req > 1u) return launch_partial_as<D, PRECISE, true>(stream, p);
+    if (p.q_f16 != 0u || p.tokens_per_req > 1u || p.q_f32 != nullptr || p.midrise != 0u)
+        return launch_partial_as<D, PRECISE, true>(stream, p);
     return launch_partial_as<D, PRECISE, false>(stream, p);
 }
 
@@ -1029,7 +1075,8 @@ static int decode_export_planned(void* stream, const uint16_t* query, const int8
                                  uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
                                  uint32_t splits, uint32_t chunk_pages, float inv_sqrt_len,
                                  float softmax_scale, uint32_t* status, bool q_f16 = false,
-                                 uint32_t tokens_per_req = 1)
+                                 uint32_t tokens_per_req = 1, const float* query_rot_f32 = nullptr,
+                                 uint32_t midrise = 0)
 {
     if (!num_heads || !num_kv_heads || num_heads % num_kv_heads != 0 || !block_size ||
         block_size % kStrip != 0 || !num_blocks || !max_blocks || !splits || splits > 16 ||
@@ -1038,8 +1085,9 @@ static int decode_export_planned(void* stream, const uint16_t* query, const int8
     const uint32_t rows = num_heads / num_kv_heads * tokens_per_req;
     if (rows > 16 || tokens_per_req == 0) return TQ_ERR_INVALID_ARGUMENT;
     if (batch == 0) return TQ_OK;
-    if (!query || !key_cache || !value_cache || !scale_cache || !block_tables || !context_lens ||
-        !pi_signs || !workspace)
+    // a pre-rotated FP32 query replaces both the 16-bit query and the sign diagonal
+    if ((!query || !pi_signs) && !query_rot_f32) return TQ_ERR_INVALID_ARGUMENT;
+    if (!key_cache || !value_cache || !scale_cache || !block_tables || !context_lens || !workspace)
         return TQ_ERR_INVALID_ARGUMENT;
     uint32_t sp_shift = 0;
     if (!page_size_ok(block_size, &sp_shift) || !aligned16(key_cache) || !aligned16(value_cache) ||
@@ -1049,6 +1097,8 @@ static int decode_export_planned(void* stream, const uint16_t* query, const int8
     p.tokens_per_req = 1;
     p.sp_shift = sp_shift;
     p.q = query;
+    p.q_f32 = query_rot_f32;
+    p.midrise = midrise;
     p.signs = pi_signs;
     p.sign_source = TQ_SIGNS_F32;
     p.key_cache = reinterpret_cast<const uint8_t*>(key_cache);
@@ -1110,7 +1160,8 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
                           uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
                           uint32_t chunk_pages, uint32_t output_stage, float inv_sqrt_len,
                           float softmax_scale, uint32_t* status, uint32_t gate_dtype = TQ_DTYPE_F32,
-                          bool q_f16 = false, uint32_t tokens_per_req = 1)
+                          bool q_f16 = false, uint32_t tokens_per_req = 1,
+                          const float* query_rot_f32 = nullptr, uint32_t midrise = 0)
 {
     if (output_stage > TQ_OUT_GATED || !output || (output_stage == TQ_OUT_GATED && !gate))
         return TQ_ERR_INVALID_ARGUMENT;
@@ -1118,7 +1169,8 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
                                          block_tables, context_lens, pi_signs, workspace, batch,
                                          num_heads, num_kv_heads, head_size, block_size, num_blocks,
                                          max_blocks, splits, chunk_pages, inv_sqrt_len,
-                                         softmax_scale, status, q_f16, tokens_per_req);
+                                         softmax_scale, status, q_f16, tokens_per_req, query_rot_f32,
+                                         midrise);
     if (st != TQ_OK || batch == 0) return st;
     const uint32_t rows = num_heads / num_kv_heads * tokens_per_req;
     return splitk_combine(stream, workspace, pi_signs, gate, gate_dtype, output, out_dtype,
@@ -1200,6 +1252,35 @@ extern "C" int tq_decode_splitk_mtp(void* stream, const uint16_t* query, const i
                           pi_signs, gate, workspace, output, out_dtype, batch, num_heads, num_kv_heads,
                           head_size, block_size, num_blocks, max_blocks, splits, chunk_pages, output_stage,
                           inv_sqrt_len, softmax_scale, status, TQ_DTYPE_F32, false, tokens_per_req);
+}
+
+// The pre-rotated entry of the reference's fused decoder (launch_fused_decode_opt,
+// include/turboquant_fused_decode_opt.hpp:187-189: `queryRot` is the FP32 rotated image of
+// the query, the output stays in the rotated basis) over a cache in this library's native
+// layout. code_grid 0: a nibble is the integer c (dequantised value c * scale), the
+// TurboQuant cache; code_grid 1: the uniform mid-rise grid of the KV4/FP8 cache, a nibble c
+// stands for (c + 0.5) * scale (fused_decode/common/turboquant_mode.h:100-124 with b = c + 8),
+// which is how a cache brought over with tq_nz_kv4_import decodes. query_rot is
+// [batch][num_heads][head_size] FP32; nothing is rotated or rounded on the way in.
+extern "C" int tq_decode_splitk_prerotated(void* stream, const float* query_rot, const int8_t* key_cache,
+                                           const int8_t* value_cache, const float* scale_cache,
+                                           const int32_t* block_tables, const int32_t* context_lens,
+                                           float* workspace, void* output, uint32_t out_dtype,
+                                           uint32_t batch, uint32_t num_heads, uint32_t num_kv_heads,
+                                           uint32_t head_size, uint32_t block_size, uint32_t num_blocks,
+                                           uint32_t max_blocks, uint32_t splits, uint32_t max_context_hint,
+                                           uint32_t code_grid, float softmax_scale, uint32_t* status)
+{
+    if (!num_kv_heads || !block_size || splits > 16 || code_grid > 1u || (batch != 0 && !query_rot))
+        return TQ_ERR_INVALID_ARGUMENT;
+    uint32_t chunk_pages = 0;
+    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
+                            &chunk_pages);
+    return decode_planned(stream, nullptr, key_cache, value_cache, scale_cache, block_tables, context_lens,
+                          nullptr, nullptr, workspace, output, out_dtype, batch, num_heads, num_kv_heads,
+                          head_size, block_size, num_blocks, max_blocks, splits, chunk_pages,
+                          TQ_OUT_ROTATED, 1.0f, softmax_scale, status, TQ_DTYPE_F32, false, 1, query_rot,
+                          code_grid);
 }
 
 // ------------------------------------------------- decode without a caller workspace

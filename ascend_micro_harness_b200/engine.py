@@ -148,6 +148,39 @@ def decode_splitk_mtp(query, key_cache, value_cache, scale_cache, block_tables, 
         inv_sqrt_len, softmax_scale, _ptr(status)), "tq_decode_splitk_mtp")
 
 
+KV4_FP8_GAIN = 2.9832882881   # TurboQuantModeTraits<KV4_FP8>::kGain of the reference's fused decoder
+GRID_INTEGER, GRID_MIDRISE = 0, 1
+
+
+def nz_kv4_import(nz_key, nz_value, nz_scales, key_cache, value_cache, scale_cache, *, num_kv_heads,
+                  block_size, num_blocks, gain=KV4_FP8_GAIN, stream=None):
+    """Re-tiles a KV4/FP8 cache of the reference's fused decoder (NZ-tiled packed planes, head
+    size 256, per-slot scale records) into the native pools; codes are copied bit for bit and
+    scale_cache receives scale / gain. Decode the result with decode_splitk_prerotated(...,
+    code_grid=GRID_MIDRISE)."""
+    lib = load_library()
+    _check(lib.tq_nz_kv4_import(_stream(stream), _ptr(nz_key), _ptr(nz_value), _ptr(nz_scales),
+                                _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache), num_kv_heads,
+                                block_size, num_blocks, gain), "tq_nz_kv4_import")
+
+
+def decode_splitk_prerotated(query_rot, key_cache, value_cache, scale_cache, block_tables, context_lens,
+                             output, *, num_heads, num_kv_heads, head_size, block_size, num_blocks,
+                             softmax_scale=1.0, splits=0, max_context_hint=0, workspace=None,
+                             code_grid=GRID_INTEGER, status=None, stream=None):
+    """Decode with an FP32 query that is already in the cache's rotated basis (the fused
+    decoder's pre-rotated entry); the output stays in that basis. code_grid=GRID_MIDRISE reads
+    a nibble c as (c + 0.5) * scale, the grid of an imported KV4/FP8 cache."""
+    lib = load_library()
+    batch = query_rot.numel() // (num_heads * head_size)
+    _check(lib.tq_decode_splitk_prerotated(
+        _stream(stream), _ptr(query_rot), _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache),
+        _ptr(block_tables), _ptr(context_lens), _ptr(workspace), _ptr(output), _out_dtype(output),
+        batch, num_heads, num_kv_heads, head_size, block_size, num_blocks, block_tables.shape[-1],
+        splits, max_context_hint, code_grid, softmax_scale, _ptr(status)),
+        "tq_decode_splitk_prerotated")
+
+
 STATIC_WORKSPACE_FLOATS = 2 * 1024 * 1024
 
 

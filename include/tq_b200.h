@@ -268,6 +268,41 @@ int tq_decode_splitk_mtp(void* stream, const uint16_t* query, const int8_t* key_
                          uint32_t splits, uint32_t max_context_hint, uint32_t output_stage,
                          float inv_sqrt_len, float softmax_scale, uint32_t* status);
 
+/* ------------------------------------------- caches of the reference's fused decoder
+ * The reference's fused decoder (include/turboquant_fused_decode_opt.hpp) keeps a second
+ * cache format, KV4/FP8: head size 256, pages of 64 or 128 slots, packed planes NZ-tiled
+ * (NzTiledPackedByte, kernels/ops/turboquant/fused_decode/common/turboquant_layout.h:80-92),
+ * byte `column` = channel `column` (bits 3:0) | channel `column + 128` (bits 7:4), a nibble c
+ * (two's complement) standing for (c + 0.5) * scale / gain -- the uniform mid-rise grid of
+ * fused_decode/common/turboquant_mode.h:100-124 -- and ceil(2 H / 8) * 8 scale floats per slot,
+ * key scales first (fused_decode/common/turboquant_common.h:62-65). Such a cache is read in
+ * two steps: tq_nz_kv4_import re-tiles it into the native pools (codes copied bit for bit,
+ * scale_cache = scale / gain), tq_decode_splitk_prerotated decodes those with code_grid 1. */
+
+/* nz_key, nz_value: num_blocks * block_size * num_kv_heads * 128 bytes; nz_scales:
+ * num_blocks * block_size * ceil(2 num_kv_heads / 8) * 8 floats; key_cache, value_cache,
+ * scale_cache: native pools for head size 256 and the same page geometry. block_size 64 or
+ * 128. gain: 2.9832882881 for KV4/FP8 (TurboQuantModeTraits<KV4_FP8>::kGain). */
+int tq_nz_kv4_import(void* stream, const uint8_t* nz_key, const uint8_t* nz_value,
+                     const float* nz_scales, int8_t* key_cache, int8_t* value_cache,
+                     float* scale_cache, uint32_t num_kv_heads, uint32_t block_size,
+                     uint32_t num_blocks, float gain);
+
+/* The pre-rotated entry (launch_fused_decode_opt, include/turboquant_fused_decode_opt.hpp:
+ * 187-189): query_rot is the FP32 rotated image [batch][num_heads][head_size] of the query,
+ * nothing is rotated or rounded on the way in, the output [batch][num_heads][head_size] stays
+ * in the rotated basis. code_grid 0: nibble c decodes to c * scale (the TurboQuant cache);
+ * 1: to (c + 0.5) * scale (an imported KV4/FP8 cache). Workspace, splits, max_context_hint,
+ * status as for tq_decode_splitk. */
+int tq_decode_splitk_prerotated(void* stream, const float* query_rot, const int8_t* key_cache,
+                                const int8_t* value_cache, const float* scale_cache,
+                                const int32_t* block_tables, const int32_t* context_lens,
+                                float* workspace, void* output, uint32_t out_dtype, uint32_t batch,
+                                uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                                uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                                uint32_t splits, uint32_t max_context_hint, uint32_t code_grid,
+                                float softmax_scale, uint32_t* status);
+
 /* ------------------------------------------------------- stand-alone routines
  * The reference's single-purpose routines that its cache operators do not call. */
 

@@ -245,6 +245,38 @@ class Oracle:
             C.c_int(output_stage), _p(out), C.c_int(threads))
         return out
 
+    # ---- NZ-tiled KV4/FP8 cache (the fused decoder's format; head size 256)
+    KV4_GAIN = 2.9832882881
+
+    def nz_tiled_packed_byte(self, slot, head, column, H, packed=128):
+        self.lib.tqo_nz_tiled_packed_byte.restype = C.c_size_t
+        return self.lib.tqo_nz_tiled_packed_byte(C.c_size_t(slot), C.c_size_t(head), C.c_size_t(column),
+                                                 C.c_size_t(H), C.c_size_t(packed))
+
+    def nz_kv4_import(self, nz_key, nz_value, nz_scales, H, S, P, gain=KV4_GAIN):
+        """NZ-tiled pool -> (key_cache, value_cache, scale_cache) in the native layout."""
+        kc = np.zeros(P * H * S * 128, np.uint8)
+        vc = np.zeros_like(kc)
+        sc = np.zeros(2 * P * H * S, np.float32)
+        rc = self.lib.tqo_nz_kv4_import(_p(_c(nz_key, np.uint8)), _p(_c(nz_value, np.uint8)),
+                                        _p(_c(nz_scales, np.float32)), C.c_int(H), C.c_int(S),
+                                        C.c_int(P), C.c_float(gain), _p(kc), _p(vc), _p(sc))
+        assert rc == 0
+        return kc, vc, sc
+
+    def nz_kv4_decode(self, q_rot, nz_key, nz_value, nz_scales, block_tables, context_lens, Hq, H, S,
+                      softmax_scale=0.0625, gain=KV4_GAIN):
+        q = _c(q_rot, np.float32)
+        B = q.size // (Hq * 256)
+        bt = _c(block_tables, np.int32).reshape(B, -1)
+        out = np.zeros((B, Hq, 256), np.float32)
+        self.lib.tqo_nz_kv4_decode(_p(q), _p(_c(nz_key, np.uint8)), _p(_c(nz_value, np.uint8)),
+                                   _p(_c(nz_scales, np.float32)), _p(bt),
+                                   _p(_c(context_lens, np.int32)), C.c_int(B), C.c_int(Hq), C.c_int(H),
+                                   C.c_int(S), C.c_int(bt.shape[1]), C.c_float(softmax_scale),
+                                   C.c_float(gain), _p(out))
+        return out
+
 
 class Reference:
     """The reference project's own golden models (oracle/_ref/libtq_ref.so)."""
@@ -309,6 +341,18 @@ class Reference:
             _p(key_cache), _p(value_cache), _p(scale_cache), _p(k), _p(v))
         return rc, k, v
 
+    def fused_fixture(self, context, requests, kv_heads, group_heads, page_tokens):
+        return RefFusedFixture(self, context, requests, kv_heads, group_heads, page_tokens)
+
+    def kv4_gain(self):
+        self.lib.ref_kv4_gain.restype = C.c_float
+        return float(self.lib.ref_kv4_gain())
+
+    def nz_tiled_packed_byte(self, slot, head, column, H, packed=128):
+        self.lib.ref_nz_tiled_packed_byte.restype = C.c_uint64
+        return self.lib.ref_nz_tiled_packed_byte(C.c_uint64(slot), C.c_uint64(head), C.c_uint64(column),
+                                                 C.c_uint64(H), C.c_uint64(packed))
+
     def decode_fixture(self, n, batch, heads, rows, page_tokens, live=-1, fill=1):
         h = self.lib.ref_decode_fixture_new(C.c_int(n), C.c_int(batch), C.c_int(heads),
                                             C.c_int(rows), C.c_int(page_tokens), C.c_int(live),
@@ -363,6 +407,40 @@ class Reference:
         packed = np.zeros(tiles * 512, np.uint8)
         self.lib.ref_icdf_fixture(C.c_int(1 if bf16 else 0), C.c_uint(tiles), _p(bits), _p(packed))
         return bits, packed
+
+
+class RefFusedFixture:
+    """fused_decode_opt_test::Fixture: a KV4/FP8 NZ-tiled cache with its FP64 expected output."""
+    _KINDS = {"query": (0, np.float32), "key": (1, np.uint8), "value": (2, np.uint8),
+              "scales": (3, np.float32), "table": (4, np.int32), "lengths": (5, np.int32),
+              "expected": (6, np.float32)}
+
+    def __init__(self, ref, context, requests, kv_heads, group_heads, page_tokens):
+        self.ref = ref
+        ref.lib.ref_fused_fixture_new.restype = C.c_void_p
+        ref.lib.ref_fused_fixture_get.restype = C.c_size_t
+        self.h = C.c_void_p(ref.lib.ref_fused_fixture_new(C.c_int(context), C.c_int(requests),
+                                                          C.c_int(kv_heads), C.c_int(group_heads),
+                                                          C.c_int(page_tokens)))
+        dims = (C.c_int * 2)()
+        ref.lib.ref_fused_fixture_dims(self.h, dims)
+        self.pages, self.physical_pages = list(dims)
+        self.context, self.requests, self.kv_heads = context, requests, kv_heads
+        self.group_heads, self.page_tokens = group_heads, page_tokens
+
+    def get(self, name):
+        which, dt = self._KINDS[name]
+        n = self.ref.lib.ref_fused_fixture_get(self.h, C.c_int(which), None)
+        out = np.zeros(n // np.dtype(dt).itemsize, dt)
+        if n:
+            self.ref.lib.ref_fused_fixture_get(self.h, C.c_int(which), _p(out))
+        return out
+
+    def __del__(self):
+        try:
+            self.ref.lib.ref_fused_fixture_free(self.h)
+        except Exception:
+            pass
 
 
 class RefDecodeFixture:

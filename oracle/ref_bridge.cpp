@@ -12,6 +12,7 @@
 //   tests/common/aic_splitk_decode_fixture.hpp  split-K decode fixture + FP64 oracle
 //   include/turboquant_splitk_contract.hpp      Partition, workspace ABI
 //   include/routines/routine_vector_lloydmax_quantize.hpp  Lloyd-Max codebook
+//   tests/common/fused_decode_opt_fixture.hpp   KV4/FP8 NZ-tiled cache fixture + FP64 oracle
 //
 // The resulting library lives under oracle/_ref/ and is never linked into the
 // product. It doubles as the "reference" CPU baseline the benchmark times.
@@ -23,6 +24,7 @@
 #include <include/sim_micro_testbed.hpp>
 #include <tests/common/lloydmax_oracle.hpp>
 #include <tests/cpu/icdf_fixture.hpp>
+#include <tests/common/fused_decode_opt_fixture.hpp>
 
 #include <cstdint>
 #include <cstring>
@@ -305,6 +307,47 @@ void ref_hadamard16(const std::uint16_t* x_f16, float* y)
 {
     const auto r = ascend_micro::sim::golden_hadamard16(x_f16);
     std::memcpy(y, r.data(), 256 * sizeof(float));
+}
+
+// ------------------------------------------- fused decoder: KV4/FP8 NZ-tiled cache
+// fused_decode_opt_test::Fixture(context, requests, kv_heads, group_heads, page_tokens)
+// (tests/common/fused_decode_opt_fixture.hpp:247-318). Head size 256.
+void* ref_fused_fixture_new(int context, int requests, int kv_heads, int group_heads, int page_tokens)
+{
+    return new fused_decode_opt_test::Fixture(context, requests, kv_heads, group_heads, page_tokens);
+}
+void ref_fused_fixture_free(void* p) { delete static_cast<fused_decode_opt_test::Fixture*>(p); }
+// dims: pages per request, physical pages
+void ref_fused_fixture_dims(void* p, int* dims)
+{
+    const auto& f = *static_cast<fused_decode_opt_test::Fixture*>(p);
+    dims[0] = f.pages;
+    dims[1] = f.physical_pages;
+}
+// which: 0 query (f32, pre-rotated) 1 key 2 value 3 scales 4 table 5 lengths 6 expected
+std::size_t ref_fused_fixture_get(void* p, int which, void* out)
+{
+    const auto& f = *static_cast<fused_decode_opt_test::Fixture*>(p);
+    const void* src = nullptr;
+    std::size_t n = 0;
+    switch (which) {
+    case 0: src = f.query.data(); n = f.query.size() * 4; break;
+    case 1: src = f.key.data(); n = f.key.size(); break;
+    case 2: src = f.value.data(); n = f.value.size(); break;
+    case 3: src = f.scales.data(); n = f.scales.size() * 4; break;
+    case 4: src = f.table.data(); n = f.table.size() * 4; break;
+    case 5: src = f.lengths.data(); n = f.lengths.size() * 4; break;
+    case 6: src = f.expected.data(); n = f.expected.size() * 4; break;
+    default: return 0;
+    }
+    if (out) std::memcpy(out, src, n);
+    return n;
+}
+float ref_kv4_gain() { return vllm_ascend::turboquant::TurboQuantModeTraits<vllm_ascend::turboquant::TurboQuantMode::KV4_FP8>::kGain; }
+std::uint64_t ref_nz_tiled_packed_byte(std::uint64_t slot, std::uint64_t head, std::uint64_t column,
+                                       std::uint64_t H, std::uint64_t packed)
+{
+    return vllm_ascend::turboquant::NzTiledPackedByte(slot, head, column, H, packed);
 }
 
 }  // extern "C"

@@ -898,6 +898,128 @@ void tqo_decode_lm(const std::uint16_t* q, const std::uint8_t* key_cache,
     for (auto& th : pool) th.join();
 }
 
+// ------------------------------------------------ NZ-tiled KV4/FP8 cache (fused decoder's format)
+//
+// The cache the reference's fused decoder reads (head size 256 only,
+// include/turboquant_fused_decode_opt.hpp:10,:85-88):
+//   * packed planes: byte `column` (0..127) of (slot, kv head) holds channel `column` in bits
+//     3:0 and channel `column + 128` in bits 7:4 (tests/common/fused_decode_opt_fixture.hpp:
+//     286-293), at NzTiledPackedByte(slot, head, column, H, 128) inside the page
+//     (kernels/ops/turboquant/fused_decode/common/turboquant_layout.h:80-92): 64-row tiles,
+//     [tile][kv head][32-byte column group][row][byte];
+//   * a nibble is a two's-complement code c in [-8, 7] and stands for (c + 0.5) * scale / gain
+//     -- the uniform mid-rise grid b - 7.5 with b = c + 8, gain 2.9832882881
+//     (fused_decode/common/turboquant_mode.h:100-124; the decode multiplies the key scale by
+//     softmax_scale / gain and the value scale by 1 / gain,
+//     fused_decode/vector/turboquant_vector_service.h:592-593,:754-755);
+//   * scales: ceil(2H / 8) * 8 floats per slot, key scales of the H heads first, value scales
+//     after them (fused_decode/common/turboquant_common.h:62-65; fixture :283-284).
+static inline std::size_t nz_tiled_packed_byte(std::size_t slot, std::size_t head, std::size_t column,
+                                               std::size_t H, std::size_t packed_bytes)
+{
+    const std::size_t tile_row = slot % 64;
+    return (slot - tile_row) * H * packed_bytes + head * 64 * packed_bytes +
+           ((column / 32) * 64 + tile_row) * 32 + column % 32;
+}
+static inline int s4(unsigned nibble) { return static_cast<int>(nibble ^ 8u) - 8; }
+
+std::size_t tqo_nz_tiled_packed_byte(std::size_t slot, std::size_t head, std::size_t column,
+                                     std::size_t H, std::size_t packed_bytes)
+{
+    return nz_tiled_packed_byte(slot, head, column, H, packed_bytes);
+}
+
+// The import this library performs before it decodes such a cache: codes unchanged, re-paired
+// into the native planes (key: token-major, channels 2j | 2j+1 per byte; value: channel-major
+// inside each 16-token strip, tokens 2j | 2j+1 per byte), scale = FP32 (slot scale / gain),
+// planar. Pages keep their numbers. Returns 0, or -1 on a geometry the format does not have.
+int tqo_nz_kv4_import(const std::uint8_t* nz_key, const std::uint8_t* nz_value, const float* nz_scales,
+                      int H, int S, int P, float gain, std::uint8_t* key_cache,
+                      std::uint8_t* value_cache, float* scale_cache)
+{
+    constexpr int d = 256, packed = 128;
+    if (H < 1 || (S != 64 && S != 128) || P < 0) return -1;
+    const int slot_floats = (2 * H + 7) / 8 * 8;
+    std::vector<int> code(d);
+    for (int page = 0; page < P; ++page)
+        for (int row = 0; row < S; ++row)
+            for (int head = 0; head < H; ++head)
+                for (int plane = 0; plane < 2; ++plane) {
+                    const std::uint8_t* src = (plane ? nz_value : nz_key) +
+                                              static_cast<std::size_t>(page) * S * H * packed;
+                    for (int col = 0; col < packed; ++col) {
+                        const unsigned b = src[nz_tiled_packed_byte(row, head, col, H, packed)];
+                        code[col] = b & 15u;
+                        code[col + packed] = b >> 4;
+                    }
+                    const std::size_t block = (static_cast<std::size_t>(page) * H + head) * S * (d / 2);
+                    for (int ch = 0; ch < d; ++ch) {
+                        std::size_t nib;
+                        if (plane == 0) nib = static_cast<std::size_t>(row) * d + ch;
+                        else nib = static_cast<std::size_t>(row / kStrip) * (kStrip * d) + ch * kStrip + row % kStrip;
+                        std::uint8_t* dst = (plane ? value_cache : key_cache) + block + nib / 2;
+                        const unsigned shift = (nib & 1) ? 4u : 0u;
+                        *dst = static_cast<std::uint8_t>((*dst & ~(15u << shift)) | (code[ch] << shift));
+                    }
+                    const float sc = nz_scales[(static_cast<std::size_t>(page) * S + row) * slot_floats +
+                                               plane * H + head];
+                    scale_cache[((static_cast<std::size_t>(plane) * P + page) * H + head) * S + row] = sc / gain;
+                }
+    return 0;
+}
+
+// FP64 attention straight off the NZ-tiled cache with a pre-rotated FP32 query
+// [B][Hq][256] (the fused decoder's `queryRot`), output in the rotated basis, FP32
+// (the scalar FP64 sum of tests/common/fused_decode_opt_fixture.hpp:300-312, for arbitrary
+// cache contents). Scales enter as the FP32 quotient scale / gain, as in the import above.
+void tqo_nz_kv4_decode(const float* q_rot, const std::uint8_t* nz_key, const std::uint8_t* nz_value,
+                       const float* nz_scales, const std::int32_t* block_tables,
+                       const std::int32_t* context_lens, int B, int Hq, int H, int S, int max_blocks,
+                       float softmax_scale, float gain, float* out)
+{
+    constexpr int d = 256, packed = 128;
+    const int G = Hq / H, slot_floats = (2 * H + 7) / 8 * 8;
+    for (int b = 0; b < B; ++b)
+        for (int qh = 0; qh < Hq; ++qh) {
+            const int head = qh / G, ctx = std::max(0, context_lens[b]);
+            const float* q = q_rot + (static_cast<std::size_t>(b) * Hq + qh) * d;
+            float* o = out + (static_cast<std::size_t>(b) * Hq + qh) * d;
+            std::vector<double> score(ctx), acc(d, 0.0);
+            double m = -std::numeric_limits<double>::infinity();
+            auto plane_base = [&](const std::uint8_t* pool, int t) {
+                const std::size_t page = static_cast<std::size_t>(block_tables[b * max_blocks + t / S]);
+                return pool + page * S * H * packed;
+            };
+            auto scale_of = [&](int t, int plane) {
+                const std::size_t page = static_cast<std::size_t>(block_tables[b * max_blocks + t / S]);
+                return static_cast<double>(nz_scales[(page * S + t % S) * slot_floats + plane * H + head] / gain);
+            };
+            for (int t = 0; t < ctx; ++t) {
+                const std::uint8_t* kp = plane_base(nz_key, t);
+                double dot = 0.0;
+                for (int col = 0; col < packed; ++col) {
+                    const unsigned byte = kp[nz_tiled_packed_byte(t % S, head, col, H, packed)];
+                    dot += static_cast<double>(q[col]) * (s4(byte & 15u) + 0.5) +
+                           static_cast<double>(q[col + packed]) * (s4(byte >> 4) + 0.5);
+                }
+                score[t] = dot * scale_of(t, 0) * static_cast<double>(softmax_scale);
+                m = std::max(m, score[t]);
+            }
+            double l = 0.0;
+            for (int t = 0; t < ctx; ++t) {
+                const double p = std::exp(score[t] - m), vs = scale_of(t, 1);
+                l += p;
+                const std::uint8_t* vp = plane_base(nz_value, t);
+                for (int col = 0; col < packed; ++col) {
+                    const unsigned byte = vp[nz_tiled_packed_byte(t % S, head, col, H, packed)];
+                    acc[col] += p * vs * (s4(byte & 15u) + 0.5);
+                    acc[col + packed] += p * vs * (s4(byte >> 4) + 0.5);
+                }
+            }
+            for (int c = 0; c < d; ++c) o[c] = ctx > 0 ? static_cast<float>(acc[c] / l) : 0.0f;
+        }
+}
+
 int tqo_hardware_threads() { return static_cast<int>(std::thread::hardware_concurrency()); }
 
 }  // extern "C"

@@ -83,6 +83,19 @@ def main():
                         lm_centroids=c, lm_thresholds=t, h16_x=h16_x.view(np.uint16), h16_y=h16_y,
                         icdf_f16_bits=f16_bits, icdf_f16_packed=f16_packed,
                         icdf_bf16_bits=bf16_bits, icdf_bf16_packed=bf16_packed)
+    # the fused decoder's KV4/FP8 NZ-tiled cache fixture (ragged context, two page sizes) with
+    # its FP64 expected output, and a table of NzTiledPackedByte values
+    for name, (n, b, h, g, S) in {"fused_kv4_s64": (200, 2, 2, 4, 64), "fused_kv4_s128": (300, 1, 3, 2, 128)}.items():
+        fx = r.fused_fixture(n, b, h, g, S)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), query=fx.get("query"), key=fx.get("key"),
+                            value=fx.get("value"), scale_bits=fx.get("scales").view(np.uint32),
+                            table=fx.get("table")[:b * fx.pages].reshape(b, fx.pages),
+                            lengths=fx.get("lengths")[:b], expected=fx.get("expected"),
+                            dims=np.array([n, b, h, g, S, fx.pages, fx.physical_pages]),
+                            gain=np.float32(r.kv4_gain()),
+                            nz_bytes=np.array([[slot, head, col, H, r.nz_tiled_packed_byte(slot, head, col, H)]
+                                               for H in (1, 3) for slot in (0, 1, 63, 64, 127)
+                                               for head in range(H) for col in (0, 31, 32, 127)], np.int64))
     for fn in sorted(os.listdir(HERE)):
         if fn.endswith(".npz"):
             print(fn, os.path.getsize(os.path.join(HERE, fn)))
