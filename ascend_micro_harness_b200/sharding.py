@@ -10,7 +10,9 @@ from typing import List, Sequence
 def partition_sequences(context_lens: Sequence[int], world: int, policy: str = "lpt") -> List[List[int]]:
     """Sequence indices owned by each rank.
     'round_robin' suits uniform lengths; 'lpt' (longest processing time first) balances the
-    KV bytes of a ragged batch: sequences in decreasing length, each to the lightest rank."""
+    KV bytes of a ragged batch: sequences in decreasing length, each to the lightest rank;
+    'lpt_equal' does the same but no rank takes more than ceil(n / world) sequences, for
+    engines whose launch geometry is sized for a fixed batch per GPU."""
     if world <= 0:
         raise ValueError("world must be positive")
     shards: List[List[int]] = [[] for _ in range(world)]
@@ -18,11 +20,12 @@ def partition_sequences(context_lens: Sequence[int], world: int, policy: str = "
         for i in range(len(context_lens)):
             shards[i % world].append(i)
         return shards
-    if policy != "lpt":
+    if policy not in ("lpt", "lpt_equal"):
         raise ValueError(f"unknown policy {policy!r}")
+    cap = -(-len(context_lens) // world) if policy == "lpt_equal" else len(context_lens)
     load = [0] * world
     for i in sorted(range(len(context_lens)), key=lambda j: (-int(context_lens[j]), j)):
-        r = min(range(world), key=lambda k: (load[k], k))
+        r = min((k for k in range(world) if len(shards[k]) < cap), key=lambda k: (load[k], k))
         shards[r].append(i)
         load[r] += int(context_lens[i])
     for s in shards:

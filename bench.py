@@ -163,7 +163,13 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     tq.load_library()
 
-    w = build_workload(torch, dev, seed=4 + rank)
+    # The job's batch is BATCH sequences per GPU, generated as one stream (rank r's seed adds the
+    # r-th block of BATCH lengths, so one GPU sees the same batch at every N) and dealt to the
+    # GPUs by the sharding helper: longest first to the lightest GPU, BATCH sequences each.
+    from ascend_micro_harness_b200.sharding import partition_sequences
+    ctx_all = np.concatenate([context_lengths(4 + r) for r in range(world)])
+    mine = partition_sequences(ctx_all, world, "lpt_equal")[rank] if world > 1 else list(range(BATCH))
+    w = build_workload(torch, dev, seed=4 + rank, ctx=ctx_all[np.asarray(mine)])
     ctx = w["ctx"]
     splits = tq.choose_splits(BATCH, HKV, S, int(ctx.max()),
                               torch.cuda.get_device_properties(dev).multi_processor_count)
@@ -277,7 +283,7 @@ def run_ours(args):
                        "head_dim": D, "page_tokens": S, "splits": int(splits),
                        "kv_bytes_per_gpu": my_bytes,
                        "l2": "inputs larger than L2 (%.2f GB of cache read per step)" % (my_bytes / 1e9),
-                       "parallelism": f"sequences sharded over {world} GPU(s), no collective"},
+                       "parallelism": f"{BATCH * world} sequences dealt to {world} GPU(s) by total context (longest first, {BATCH} each), no collective"},
             "decode_us_per_step": round(kernel_ms * 1e3, 1),
             "e2e": {"value": round(total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9, 1),
                     "unit": "GB/s", "h2d_bytes_per_step": int(h2d),

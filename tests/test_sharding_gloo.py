@@ -51,3 +51,16 @@ def test_lpt_balances_a_ragged_batch(world):
     assert max(loads) - min(loads) <= max(ctx)                      # LPT bound
     rr = partition_sequences(ctx, world, "round_robin")
     assert all(len(s) in (64 // world, 64 // world + (64 % world > 0)) for s in rr)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_equal_count_lpt_keeps_the_batch_per_rank(world):
+    """The benchmark's dealing of 64 sequences per GPU: equal counts, loads within a few percent."""
+    from ascend_micro_harness_b200.sharding import partition_sequences
+    rng = np.random.default_rng(100 + world)
+    ctx = [int(c) for c in rng.integers(512, 32769, 64 * world)]
+    shards = partition_sequences(ctx, world, "lpt_equal")
+    assert sorted(i for s in shards for i in s) == list(range(64 * world))
+    assert all(len(s) == 64 for s in shards)
+    loads = [sum(ctx[i] for i in s) for s in shards]
+    assert max(loads) <= 1.02 * (sum(loads) / world)
