@@ -195,35 +195,99 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One CTA per (sequence, KV head, split); up to 8 query rows (the GQA group). Four warps
-// take the strips of the split's page range in turn; a strip's 1 KiB key block, 1 KiB value
-// block and two scale runs go through a per-warp shared-memory buffer, codes become f16
-// centroids through a 256-entry byte -> (centroid, centroid) table, both contractions are
-// f16 tensor-core MMAs with tokens as the M dimension.
-template <int D>
-__global__ void __launch_bounds__(128) tq_lm_decode_kernel(const LmDecodeParams p)
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
 {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gmem_src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_dst), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t lm_movmatrix_trans(uint32_t a)
+{
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ float lm_ex2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t lm_pack_f16x2(float lo, float hi)
+{
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+template <int D>
+struct LmDecodeSmem {
+    static constexpr int kStages = 2;
+    static constexpr int kStripBytes = kStrip * D / 2;
+    static constexpr int kBufBytes = 2 * kStripBytes + 128;          // key strip, value strip, two scale runs
+    static constexpr int kLutBytes = 256 * 32 * 4;                   // one copy of the table per bank
+    static constexpr int kRingBytes = 4 * kStages * kBufBytes;
+    static constexpr int kQueryBytes = 8 * D * 4;
+    static constexpr int kMergeBytes = 4 * 8 * (D + 2) * 4;          // reuses ring + query after the loop
+    static constexpr int kTotal = kLutBytes + kRingBytes + kQueryBytes;
+    static constexpr int kCtasPerSm = D == 128 ? 4 : 3;
+    static_assert(kMergeBytes <= kRingBytes + kQueryBytes, "the merge area must fit the ring");
+};
+
+// One CTA per (sequence, KV head, split); up to 8 query rows (the GQA group). Four warps
+// take the strips of the split's page range in turn, each through its own 2-stage cp.async
+// ring (a strip's key block, value block and two scale runs). Codes become f16 centroids
+// through a byte -> (centroid[low nibble], centroid[high nibble]) table that is kept 32
+// times in shared memory, entry e of lane l at word 32 e + l, so a lookup never leaves the
+// lane's own bank; both contractions are f16 tensor-core MMAs with tokens as the M
+// dimension. P carries the value scale relative to a running power-of-two normaliser, and
+// the accumulator is rescaled only by strips that raise a row maximum or that normaliser.
+template <int D>
+__global__ void __launch_bounds__(128, LmDecodeSmem<D>::kCtasPerSm) tq_lm_decode_kernel(const LmDecodeParams p)
+{
+    using L = LmDecodeSmem<D>;
     constexpr int kRecord = 16 + D;
-    constexpr int kStripBytes = kStrip * D / 2;
+    constexpr int kStripBytes = L::kStripBytes;
     constexpr int MT = D / 16;
     constexpr int kChunks = D / 2 / 16 / 4;   // 16-byte chunks of a key row per thread: 1 or 2
-    constexpr int kBufBytes = 2 * kStripBytes + 128;
-    constexpr int kLoopBytes = 4 * kBufBytes + 8 * D * 4;          // strip buffers + rotated query
-    constexpr int kMergeBytes = 4 * 8 * (D + 2) * 4;               // reuses them after the strip loop
-    __shared__ uint32_t lut[256];
-    __shared__ __align__(16) uint8_t raw[kLoopBytes > kMergeBytes ? kLoopBytes : kMergeBytes];
-    uint8_t (*bufs)[kBufBytes] = reinterpret_cast<uint8_t (*)[kBufBytes]>(raw);
-    float (*qs)[D] = reinterpret_cast<float (*)[D]>(raw + 4 * kBufBytes);
-    float (*merge)[8][D + 2] = reinterpret_cast<float (*)[8][D + 2]>(raw);
+    extern __shared__ __align__(128) uint8_t lm_smem[];
+    uint32_t* lut = reinterpret_cast<uint32_t*>(lm_smem);
+    uint8_t* ring = lm_smem + L::kLutBytes;
+    float (*qs)[D] = reinterpret_cast<float (*)[D]>(ring + L::kRingBytes);
+    float (*merge)[8][D + 2] = reinterpret_cast<float (*)[8][D + 2]>(ring);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, qd = lane & 3;
     const uint32_t split = blockIdx.x % p.splits, item = blockIdx.x / p.splits;
     const uint32_t seq = item / p.H, head = item % p.H;
 
-    // byte -> packed (centroid[low nibble], centroid[high nibble]) as f16
+    // page range of this split (include/turboquant_splitk_contract.hpp:129-136)
+    const int32_t c0 = p.context_lens[seq];
+    const uint32_t ctx = c0 > 0 ? min(static_cast<uint32_t>(c0), p.table_stride * p.S) : 0u;
+    const uint32_t pages = (ctx + p.S - 1u) / p.S;
+    const uint32_t width = (pages + p.splits - 1u) / p.splits;
+    const uint32_t pb = min(split * width, pages), pe = min(pb + width, pages);
+    const uint32_t SP = p.S / kStrip;
+    const uint32_t s0 = pb * SP, s1 = min(pe * SP, (ctx + kStrip - 1u) / kStrip);
+    float* rec = p.workspace + (static_cast<size_t>(item) * p.splits + split) * p.rows * kRecord;
+    if (s1 <= s0) {   // nothing to read: the neutral record
+        for (int i = tid; i < static_cast<int>(p.rows) * kRecord; i += blockDim.x)
+            rec[i] = (i % kRecord) < 8 ? kMaskedScore : 0.0f;
+        return;
+    }
+
+    // byte -> packed (centroid[low nibble], centroid[high nibble]) as f16: the 256 entries
+    // first (lane 0's copy), then the other 31 copies
     for (int i = tid; i < 256; i += blockDim.x) {
         const __half2 h = __floats2half2_rn(lloydmax4_centroid(i & 15), lloydmax4_centroid(i >> 4));
-        lut[i] = *reinterpret_cast<const uint32_t*>(&h);
+        lut[i * 32] = *reinterpret_cast<const uint32_t*>(&h);
     }
     // q_rot: FP32 butterfly inside each 16-channel block, / 4, bf16
     for (int i = tid; i < 8 * (D / 16); i += blockDim.x) {
@@ -239,15 +303,8 @@ __global__ void __launch_bounds__(128) tq_lm_decode_kernel(const LmDecodeParams 
         for (int k = 0; k < 16; ++k) qs[row][blk * 16 + k] = bf16_bits_to_f32(f32_to_bf16_bits(v[k] * 0.25f));
     }
     __syncthreads();
-
-    // page range of this split (include/turboquant_splitk_contract.hpp:129-136)
-    const int32_t c0 = p.context_lens[seq];
-    const uint32_t ctx = c0 > 0 ? min(static_cast<uint32_t>(c0), p.table_stride * p.S) : 0u;
-    const uint32_t pages = (ctx + p.S - 1u) / p.S;
-    const uint32_t width = (pages + p.splits - 1u) / p.splits;
-    const uint32_t pb = min(split * width, pages), pe = min(pb + width, pages);
-    const uint32_t SP = p.S / kStrip;
-    const uint32_t s0 = pb * SP, s1 = min(pe * SP, (ctx + kStrip - 1u) / kStrip);
+    for (int i = tid; i < 256 * 32; i += blockDim.x)
+        if ((i & 31) != 0) lut[i] = lut[i & ~31];
 
     // B fragments of q_rot^T: MMA j of a key row takes this thread's bytes 2j, 2j+1, i.e.
     // channels qd*(D/4) + 4j .. 4j+3
@@ -255,47 +312,67 @@ __global__ void __launch_bounds__(128) tq_lm_decode_kernel(const LmDecodeParams 
 #pragma unroll
     for (int j = 0; j < D / 16; ++j) {
         const float* qr = &qs[r][qd * (D / 4) + 4 * j];
-        const __half2 lo = __floats2half2_rn(qr[0], qr[1]), hi = __floats2half2_rn(qr[2], qr[3]);
-        bq[j][0] = *reinterpret_cast<const uint32_t*>(&lo);
-        bq[j][1] = *reinterpret_cast<const uint32_t*>(&hi);
+        bq[j][0] = lm_pack_f16x2(qr[0], qr[1]);
+        bq[j][1] = lm_pack_f16x2(qr[2], qr[3]);
     }
+    __syncthreads();   // the table is complete
 
+    // Online-softmax state for query rows 2qd and 2qd+1, in units of raw * key_scale.
+    const float fac = p.softmax_scale * kLmLog2e;
     float m_run[2] = {kMaskedScore, kMaskedScore}, l_run[2] = {0.f, 0.f};
+    float m_fac[2] = {0.f, 0.f};   // m_run * fac, the exponent offset (0 while m_run is the sentinel)
+    float vnorm = 0.f, inv_vnorm = 0.f;   // running power-of-two bound of the value scales
     float acc[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
 
-    uint8_t* buf = bufs[warp];
-    const float fac = p.softmax_scale * kLmLog2e;
+    uint8_t* my_ring = ring + warp * L::kStages * L::kBufBytes;
+    const uint32_t my_ring_s = smem_u32(my_ring);
+    const uint32_t* my_lut = lut + lane;   // entry e of this lane: my_lut[32 e]
     const int32_t* table_row = p.table + static_cast<size_t>(seq) * p.table_stride;
-    for (uint32_t strip = s0 + warp; strip < s1; strip += 4u) {
-        int32_t pg = __ldg(table_row + strip / SP);
+    const size_t head_block = static_cast<size_t>(p.S) * D / 2;
+    auto load_page = [&](uint32_t strip) { return strip < s1 ? __ldg(table_row + strip / SP) : -1; };
+    auto issue = [&](uint32_t strip, uint32_t stage, int32_t pg) {
+        if (pg < 0 && strip >= s1) return;   // warp-uniform: past the range
         if (pg < 0 || static_cast<uint32_t>(pg) >= p.P) {
             if (lane == 0) report(p.status, TQ_STATUS_BAD_PAGE);
             pg = 0;
         }
-        const size_t block = (static_cast<size_t>(pg) * p.H + head) * (static_cast<size_t>(p.S) * D / 2) +
+        const size_t block = (static_cast<size_t>(pg) * p.H + head) * head_block +
                              static_cast<size_t>(strip % SP) * kStripBytes;
-        __syncwarp();
-        {
-            const uint4* ks = reinterpret_cast<const uint4*>(p.key_cache + block);
-            const uint4* vs = reinterpret_cast<const uint4*>(p.value_cache + block);
-            uint4* bk = reinterpret_cast<uint4*>(buf);
+        const uint8_t* ks = p.key_cache + block + lane * 16;
+        const uint8_t* vs = p.value_cache + block + lane * 16;
+        const uint32_t dst = my_ring_s + stage * L::kBufBytes + lane * 16;
 #pragma unroll
-            for (int i = 0; i < kStripBytes / 16 / 32; ++i) {
-                bk[i * 32 + lane] = __ldg(ks + i * 32 + lane);
-                bk[kStripBytes / 16 + i * 32 + lane] = __ldg(vs + i * 32 + lane);
-            }
-            if (lane < 8) {
-                const size_t sc = ((static_cast<size_t>(lane >> 2) * p.P + pg) * p.H + head) * p.S +
-                                  (strip % SP) * kStrip + (lane & 3) * 4;
-                reinterpret_cast<float4*>(buf + 2 * kStripBytes)[lane] =
-                    __ldg(reinterpret_cast<const float4*>(p.scale_cache + sc));
-            }
+        for (int i = 0; i < kStripBytes / 16 / 32; ++i) {
+            cp_async16(dst + i * 512, ks + i * 512);
+            cp_async16(dst + kStripBytes + i * 512, vs + i * 512);
         }
+        if (lane < 8) {
+            const size_t sc = ((static_cast<size_t>(lane >> 2) * p.P + pg) * p.H + head) * p.S +
+                              (strip % SP) * kStrip + (lane & 3) * 4;
+            cp_async16(my_ring_s + stage * L::kBufBytes + 2 * kStripBytes + lane * 16, p.scale_cache + sc);
+        }
+    };
+
+    // byte k of a word as a table offset (in words): 32 * byte
+    auto entry = [&](uint32_t word, int k) { return my_lut[__byte_perm(word, 0u, 0x4440u | k) << 5]; };
+
+    issue(s0 + warp, 0, load_page(s0 + warp));
+    cp_async_commit();
+    int32_t pg_next = load_page(s0 + warp + 4u);
+    uint32_t stage = 0;
+#pragma unroll 1
+    for (uint32_t strip = s0 + warp; strip < s1; strip += 4u) {
+        issue(strip + 4u, stage ^ 1u, pg_next);
+        cp_async_commit();
+        pg_next = load_page(strip + 8u);
+        cp_async_wait<1>();
         __syncwarp();
+        const uint8_t* buf = my_ring + stage * L::kBufBytes;
+        stage ^= 1u;
         const float* scales = reinterpret_cast<const float*>(buf + 2 * kStripBytes);
 
         // ---- scores^T: rows = tokens r and r+8, columns = query rows
@@ -310,9 +387,8 @@ __global__ void __launch_bounds__(128) tq_lm_decode_kernel(const LmDecodeParams 
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int j = ch * 8 + w * 2 + h;   // bytes 2j, 2j+1 of this thread's part of the row
-                    const uint32_t a0 = lut[(wl[w] >> (16 * h)) & 0xFFu], a2 = lut[(wl[w] >> (16 * h + 8)) & 0xFFu];
-                    const uint32_t a1 = lut[(wh[w] >> (16 * h)) & 0xFFu], a3 = lut[(wh[w] >> (16 * h + 8)) & 0xFFu];
-                    mma_f16(c, a0, a1, a2, a3, bq[j][0], bq[j][1]);
+                    mma_f16(c, entry(wl[w], 2 * h), entry(wh[w], 2 * h), entry(wl[w], 2 * h + 1),
+                            entry(wh[w], 2 * h + 1), bq[j][0], bq[j][1]);
                 }
         }
         const uint32_t tok_lo = strip * kStrip + r, tok_hi = tok_lo + 8;
@@ -324,58 +400,66 @@ __global__ void __launch_bounds__(128) tq_lm_decode_kernel(const LmDecodeParams 
         sc[3] = live_hi ? c[3] * scales[r + 8] : kMaskedScore;
         const float vs_lo = live_lo ? scales[kStrip + r] : 0.f, vs_hi = live_hi ? scales[kStrip + r + 8] : 0.f;
         float mx[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
+        float vmax = fmaxf(fabsf(vs_lo), fabsf(vs_hi));
+        // m_run and vnorm are uniform over the lanes that share them: only a strip that raises
+        // a row maximum or the normaliser pays for the reductions and the rescale
+        const bool grow = mx[0] > m_run[0] || mx[1] > m_run[1] || vmax > vnorm;
+        if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-        for (int o = 4; o <= 16; o <<= 1) {
-            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
-            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
-        }
-        float alpha[2];
+            for (int o = 4; o <= 16; o <<= 1) {
+                mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+                mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+                vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+            }
+            float alpha[2];
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const float m_new = fmaxf(m_run[q], mx[q]);
-            alpha[q] = exp2f((m_run[q] - m_new) * fac);
-            m_run[q] = m_new;
-            l_run[q] *= alpha[q];
-        }
+            for (int q = 0; q < 2; ++q) {
+                const float m_new = fmaxf(m_run[q], mx[q]);
+                alpha[q] = lm_ex2((m_run[q] - m_new) * fac);
+                m_run[q] = m_new;
+                m_fac[q] = m_new > -1.0e37f ? m_new * fac : 0.f;
+                l_run[q] *= alpha[q];
+            }
+            if (vmax > vnorm) {   // warp-uniform: value scales depend on the token only
+                const float nv = __int_as_float((__float_as_int(vmax) & 0x7F800000) + (1 << 23));
+                inv_vnorm = __int_as_float((254 << 23) - __float_as_int(nv));
+                alpha[0] *= vnorm * inv_vnorm;
+                alpha[1] *= vnorm * inv_vnorm;
+                vnorm = nv;
+            }
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            acc[mt][0] *= alpha[0];
-            acc[mt][1] *= alpha[1];
-            acc[mt][2] *= alpha[0];
-            acc[mt][3] *= alpha[1];
+            for (int mt = 0; mt < MT; ++mt) {
+                acc[mt][0] *= alpha[0];
+                acc[mt][1] *= alpha[1];
+                acc[mt][2] *= alpha[0];
+                acc[mt][3] *= alpha[1];
+            }
         }
         float pw[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const bool live = i < 2 ? live_lo : live_hi;
-            const float pr = live ? exp2f((sc[i] - m_run[i & 1]) * fac) : 0.f;
+            const float pr = lm_ex2(fmaf(sc[i], fac, -m_fac[i & 1]));
             l_run[i & 1] += pr;
-            pw[i] = pr * (i < 2 ? vs_lo : vs_hi);
+            pw[i] = pr * ((i < 2 ? vs_lo : vs_hi) * inv_vnorm);
         }
-        // P^T as the B operand: tokens 2qd, 2qd+1 (from rows r) and 8+2qd, 8+2qd+1 (rows r+8).
-        // Value scales can be any FP32, so P * scale is carried as an f16 hi + lo pair.
-        const __half2 h0 = __floats2half2_rn(pw[0], pw[1]), h1 = __floats2half2_rn(pw[2], pw[3]);
-        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-        const __half2 g0 = __floats2half2_rn(pw[0] - f0.x, pw[1] - f0.y), g1 = __floats2half2_rn(pw[2] - f1.x, pw[3] - f1.y);
-        uint32_t bh0, bh1, bl0, bl1;
-        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(bh0) : "r"(*reinterpret_cast<const uint32_t*>(&h0)));
-        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(bh1) : "r"(*reinterpret_cast<const uint32_t*>(&h1)));
-        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(bl0) : "r"(*reinterpret_cast<const uint32_t*>(&g0)));
-        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(bl1) : "r"(*reinterpret_cast<const uint32_t*>(&g1)));
-        // ---- acc^T += V^T P^T: rows = channels mt*16 + r and + 8, contraction = tokens
-        const uint8_t* vb = buf + kStripBytes;
+        // P^T as the B operand: tokens 2qd, 2qd+1 (from rows r) and 8+2qd, 8+2qd+1 (rows r+8)
+        const uint32_t bh0 = lm_movmatrix_trans(lm_pack_f16x2(pw[0], pw[1]));
+        const uint32_t bh1 = lm_movmatrix_trans(lm_pack_f16x2(pw[2], pw[3]));
+        // ---- acc^T += V^T P^T: MMA rows r and r+8 = channels mt*16 + 2r and + 2r+1 (one
+        // 16-byte read), contraction = tokens: byte qd of a channel's first word holds tokens
+        // 2qd, 2qd+1, byte qd of its second word tokens 8+2qd, 8+2qd+1
+        const uint8_t* vrow = buf + kStripBytes + (2 * r) * 8;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-            const uint8_t* c_lo = vb + (mt * 16 + r) * 8, *c_hi = vb + (mt * 16 + 8 + r) * 8;
-            const uint32_t a0 = lut[c_lo[qd]], a2 = lut[c_lo[4 + qd]];
-            const uint32_t a1 = lut[c_hi[qd]], a3 = lut[c_hi[4 + qd]];
-            mma_f16(acc[mt], a0, a1, a2, a3, bh0, bh1);
-            mma_f16(acc[mt], a0, a1, a2, a3, bl0, bl1);
+            const uint4 v = *reinterpret_cast<const uint4*>(vrow + mt * 128);
+            mma_f16(acc[mt], entry(v.x, qd), entry(v.z, qd), entry(v.y, qd), entry(v.w, qd), bh0, bh1);
         }
+        __syncwarp();   // the stage is free for the copy two iterations ahead
     }
+    cp_async_wait<0>();
 
     // ---- merge the four warps, export the record
-    __syncthreads();   // every warp is done with its strip buffer: the merge area reuses them
+    __syncthreads();   // every warp is done with its ring: the merge area reuses it
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
         l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 4);
@@ -390,13 +474,13 @@ __global__ void __launch_bounds__(128) tq_lm_decode_kernel(const LmDecodeParams 
     }
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-        merge[warp][qd * 2 + 0][2 + mt * 16 + r] = acc[mt][0];
-        merge[warp][qd * 2 + 1][2 + mt * 16 + r] = acc[mt][1];
-        merge[warp][qd * 2 + 0][2 + mt * 16 + 8 + r] = acc[mt][2];
-        merge[warp][qd * 2 + 1][2 + mt * 16 + 8 + r] = acc[mt][3];
+        const int ch = mt * 16 + 2 * r;
+        *reinterpret_cast<float2*>(&merge[warp][qd * 2 + 0][2 + ch]) =
+            make_float2(acc[mt][0] * vnorm, acc[mt][2] * vnorm);
+        *reinterpret_cast<float2*>(&merge[warp][qd * 2 + 1][2 + ch]) =
+            make_float2(acc[mt][1] * vnorm, acc[mt][3] * vnorm);
     }
     __syncthreads();
-    float* rec = p.workspace + (static_cast<size_t>(item) * p.splits + split) * p.rows * kRecord;
     for (int i = tid; i < static_cast<int>(p.rows) * kRecord; i += blockDim.x) {
         const int q = i / kRecord, cc = i % kRecord;
         float mm = kMaskedScore;
@@ -409,10 +493,28 @@ __global__ void __launch_bounds__(128) tq_lm_decode_kernel(const LmDecodeParams 
             const int src = cc < 16 ? 1 : 2 + (cc - 16);
             out = 0.f;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) out += merge[w][q][src] * exp2f((merge[w][q][0] - mm) * fac);
+            for (int w = 0; w < 4; ++w) out += merge[w][q][src] * lm_ex2((merge[w][q][0] - mm) * fac);
         }
         rec[i] = out;
     }
+}
+
+template <int D>
+static cudaError_t launch_lm_decode(cudaStream_t stream, const LmDecodeParams& p, unsigned grid)
+{
+    // Opt in to the large dynamic shared-memory carve-out once per device.
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorNoDevice;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(tq_lm_decode_kernel<D>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   LmDecodeSmem<D>::kTotal);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    tq_lm_decode_kernel<D><<<grid, 128, LmDecodeSmem<D>::kTotal, stream>>>(p);
+    return cudaGetLastError();
 }
 
 }  // namespace tq
@@ -478,7 +580,7 @@ extern "C" int tq_decode_lloydmax_export(void* stream, const uint16_t* query, co
     const uint64_t grid = static_cast<uint64_t>(p.items) * splits;
     if (grid > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (head_size == 128) tq_lm_decode_kernel<128><<<static_cast<unsigned>(grid), 128, 0, s>>>(p);
-    else tq_lm_decode_kernel<256><<<static_cast<unsigned>(grid), 128, 0, s>>>(p);
-    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+    const cudaError_t e = head_size == 128 ? launch_lm_decode<128>(s, p, static_cast<unsigned>(grid))
+                                           : launch_lm_decode<256>(s, p, static_cast<unsigned>(grid));
+    return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
