@@ -361,12 +361,66 @@ def run_profile_case(args):
     a GB on the device, two warm-up launches and three captured ones.
       decode  : 64 sequences x 2048..4096 tokens (about 0.2 GB of cache)
       reshape : bf16 prefill of 65536 tokens x 8 KV heads x 128 (0.27 GB)
-      reshape_a8 : the same prefill with int8 activations (0.13 GB)"""
+      reshape_a8 : the same prefill with int8 activations (0.13 GB)
+      lm_decode  : the Lloyd-Max cache variant, 64 sequences x 2048..4096 tokens, 2 splits
+      lm_reshape : its bf16 writer on the 65536-token prefill
+      scatter    : the 1-token-per-sequence writer of a 64-sequence decode step
+      nz_import  : the KV4/FP8 NZ-tiled importer, 2048 pages x 128 slots x 4 heads (0.27 GB in)"""
     import torch
     import ascend_micro_harness_b200 as tq
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
-    if args.profile == "decode":
+    if args.profile == "lm_decode":
+        rng = np.random.default_rng(0)
+        ctx = rng.integers(2048, 4097, size=BATCH)
+        pages = (ctx + S - 1) // S
+        P = int(pages.sum()) + 8
+        tables = np.zeros((BATCH, int(pages.max())), np.int32)
+        perm, at = rng.permutation(P), 0
+        for b in range(BATCH):
+            tables[b, :pages[b]] = perm[at:at + pages[b]]
+            at += int(pages[b])
+        g = torch.Generator(device=dev)
+        g.manual_seed(1)
+        nb = P * HKV * S * D // 2
+        kc = torch.randint(0, 256, (nb,), dtype=torch.uint8, device=dev, generator=g)
+        vc = torch.randint(0, 256, (nb,), dtype=torch.uint8, device=dev, generator=g)
+        sc = (torch.rand(2 * P * HKV * S, device=dev, generator=g) * 0.05 + 0.05).contiguous()
+        q = torch.randn((BATCH, HQ, D), device=dev, generator=g).bfloat16()
+        splits = 2
+        ws = torch.zeros(BATCH * HKV * splits * (HQ // HKV) * (16 + D), device=dev)
+        out = torch.zeros((BATCH, HQ, D), device=dev)
+        dt, dc = torch.from_numpy(tables).to(dev), torch.from_numpy(ctx.astype(np.int32)).to(dev)
+        for _ in range(5):
+            tq.decode_lloydmax(q, kc, vc, sc, dt, dc, out, ws, num_heads=HQ, num_kv_heads=HKV,
+                               head_size=D, block_size=S, num_blocks=P, splits=splits,
+                               softmax_scale=float(1.0 / np.sqrt(D)), output_stage=1)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": "lm_decode", "kv_bytes": kv_bytes(ctx), "splits": splits}))
+    elif args.profile == "scatter":
+        w = build_workload(torch, dev, 11, context_lengths(11, BATCH, 2048, 4096))
+        dk, dv, dslots = w["hk"].to(dev), w["hv"].to(dev), w["hslots"].to(dev)
+        for _ in range(5):
+            tq.reshape_scatter(dk, dv, w["key_cache"], w["value_cache"], w["scale_cache"], dslots,
+                               w["signs"], None, num_requests=BATCH, num_kv_heads=HKV, head_size=D,
+                               block_size=S, num_blocks=w["total_pages"], inv_sqrt_len=w["inv"])
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": "scatter", "tokens": BATCH}))
+    elif args.profile == "nz_import":
+        P, H, SS = 2048, 4, 128
+        g = torch.Generator(device=dev)
+        g.manual_seed(3)
+        nzk = torch.randint(0, 256, (P * SS * H * 128,), dtype=torch.uint8, device=dev, generator=g)
+        nzv = torch.randint(0, 256, (P * SS * H * 128,), dtype=torch.uint8, device=dev, generator=g)
+        nzs = torch.rand(P * SS * 8, device=dev, generator=g) + 0.5
+        kc, vc = torch.empty_like(nzk), torch.empty_like(nzv)
+        sc = torch.empty(2 * P * H * SS, dtype=torch.float32, device=dev)
+        for _ in range(5):
+            tq.nz_kv4_import(nzk, nzv, nzs, kc, vc, sc, num_kv_heads=H, block_size=SS, num_blocks=P)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": "nz_import",
+                          "bytes": 2 * (2 * nzk.numel()) + P * SS * 8 * 4 + 2 * P * H * SS * 4}))
+    elif args.profile == "decode":
         ctx = context_lengths(11, BATCH, 2048, 4096)
         w = build_workload(torch, dev, 11, ctx)
         splits = tq.choose_splits(BATCH, HKV, S, int(w["ctx"].max()),
@@ -387,6 +441,7 @@ def run_profile_case(args):
         T, H = 65536, 8
         g = torch.Generator(device=dev)
         g.manual_seed(2)
+        lm = args.profile == "lm_reshape"
         if args.profile == "reshape_a8":
             k = torch.randint(-127, 128, (T, H * D), device=dev, generator=g, dtype=torch.int8)
             v = torch.randint(-127, 128, (T, H * D), device=dev, generator=g, dtype=torch.int8)
@@ -401,8 +456,12 @@ def run_profile_case(args):
         slots = (perm[:, None] * S + torch.arange(S, device=dev)[None, :]).reshape(-1).int().contiguous()
         signs = torch.ones(D, device=dev)
         for _ in range(5):
-            tq.reshape_and_cache(k, v, kc, vc, sc, slots, signs, num_kv_heads=H, head_size=D,
-                                 block_size=S, num_blocks=P, inv_sqrt_len=0.0883883)
+            if lm:
+                tq.reshape_and_cache_lloydmax(k, v, kc, vc, sc, slots, num_kv_heads=H, head_size=D,
+                                              block_size=S, num_blocks=P, inv_sqrt_len=0.0883883)
+            else:
+                tq.reshape_and_cache(k, v, kc, vc, sc, slots, signs, num_kv_heads=H, head_size=D,
+                                     block_size=S, num_blocks=P, inv_sqrt_len=0.0883883)
         torch.cuda.synchronize()
         print(json.dumps({"profile": args.profile,
                           "bytes": 2 * T * H * D * k.element_size() + T * H * D + 2 * T * H * 4}))
@@ -487,7 +546,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile", default=None, choices=["decode", "reshape", "reshape_a8"],
+    ap.add_argument("--profile", default=None, choices=["decode", "reshape", "reshape_a8", "lm_decode", "lm_reshape", "scatter", "nz_import"],
                     help="run a small case of one kernel (for ncu), print no bench line")
     args = ap.parse_args()
     if args.profile:
