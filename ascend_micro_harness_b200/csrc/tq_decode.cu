@@ -79,8 +79,17 @@ struct DecodeSmem {
     // doubles both the strips and the accumulator registers: three stages of 1 strip, three
     // CTAs of up to 168 registers (measured against 2 stages of 2 strips: +13 %, the smaller
     // tile leaves room in the register file; 2 CTAs of 255 registers: +7 %).
-    static constexpr int kTileStrips = D == 128 ? 3 : 1;
-    static constexpr int kStages = D == 128 ? 2 : 3;
+#ifndef TQ_D256_TILE
+#define TQ_D256_TILE 1
+#define TQ_D256_STAGES 3
+#define TQ_D256_QSMEM 0
+#endif
+    static constexpr int kTileStrips = D == 128 ? 3 : TQ_D256_TILE;
+    static constexpr int kStages = D == 128 ? 2 : TQ_D256_STAGES;
+    // d = 256: the query's B fragments (up to 3 limbs x 8 words x 2 registers per lane) can
+    // live in shared memory behind the ring instead of in 32..48 registers
+    static constexpr bool kQFragSmem = D == 256 && TQ_D256_QSMEM != 0;
+    static constexpr int kQFragBytes = kQFragSmem ? 3 * (D / 32) * 2 * 4 * 32 : 0;
     static constexpr int kCtasPerSm = D == 128 ? 4 : 3;
     static constexpr int kRowBytes = D / 2;
     static constexpr int kStripBytes = kStrip * D / 2;
@@ -92,7 +101,7 @@ struct DecodeSmem {
     static constexpr int kMergeBytes = kDecWarps * 8 * kMergePitch * 4;
     static constexpr int kBody = kRingBytes > kQBytes ? (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes)
                                                       : (kQBytes > kMergeBytes ? kQBytes : kMergeBytes);
-    static constexpr int kTotal = kBody;
+    static constexpr int kTotal = kBody + kQFragBytes;
     // 16-byte chunk `c` of token row `row` lands at this chunk index of the strip.
     __host__ __device__ static constexpr int key_chunk(int row, int c)
     {
@@ -378,7 +387,9 @@ tq_decode_partial_kernel(const DecodeParams p)
     // ---- limbs of q_rot^T as B fragments of the integer MMA. Word wi of a key row holds
     // channels qd*(D/4) + wi*8 + n, n = 0..7: the even n feed contraction slots qd*4 + n/2
     // (b0), the odd n slots 16 + qd*4 + n/2 (b1).
-    uint32_t bq[NL][WPT][2];
+    uint32_t bq[L::kQFragSmem ? 1 : NL][L::kQFragSmem ? 1 : WPT][2];
+    // [wi][limb][lane] pairs of registers; every warp holds the same fragments, warp 0 writes them
+    uint2* qfrag = reinterpret_cast<uint2*>(smem + L::kBody) + lane;
 #pragma unroll
     for (int wi = 0; wi < WPT; ++wi) {
         const int* qr = qfix + q_index(r, qd * (D / 4) + wi * 8);
@@ -393,7 +404,12 @@ tq_decode_partial_kernel(const DecodeParams p)
                 const uint32_t pick = static_cast<uint32_t>(l) | (static_cast<uint32_t>(4 + l) << 4);
                 const uint32_t lo = __byte_perm(qv[h], qv[2 + h], pick);
                 const uint32_t hi = __byte_perm(qv[4 + h], qv[6 + h], pick);
-                bq[l][wi][h] = __byte_perm(lo, hi, 0x5410u);
+                const uint32_t frag = __byte_perm(lo, hi, 0x5410u);
+                if constexpr (L::kQFragSmem) {
+                    if (warp == 0) reinterpret_cast<uint32_t*>(qfrag + (wi * NL + l) * 32)[h] = frag;
+                } else {
+                    bq[l][wi][h] = frag;
+                }
             }
     }
     // scores are kept as raw * key_scale; the per-row factor enters inside the exponent
@@ -548,10 +564,19 @@ tq_decode_partial_kernel(const DecodeParams p)
                     const uint32_t a2 = wl[k] & 0xF0F0F0F0u, a3 = wh[k] & 0xF0F0F0F0u;
 #pragma unroll
                     for (int l = 0; l < NL; ++l) {
+                        uint32_t b0, b1;
+                        if constexpr (L::kQFragSmem) {
+                            const uint2 fr = qfrag[(wi * NL + l) * 32];
+                            b0 = fr.x;
+                            b1 = fr.y;
+                        } else {
+                            b0 = bq[l][wi][0];
+                            b1 = bq[l][wi][1];
+                        }
                         if (wi == 0)
-                            mma_s8_limb(l == NL - 1, ci[l], a0, a1, a2, a3, bq[l][wi][0], bq[l][wi][1], cinit);
+                            mma_s8_limb(l == NL - 1, ci[l], a0, a1, a2, a3, b0, b1, cinit);
                         else
-                            mma_s8_limb(l == NL - 1, ci[l], a0, a1, a2, a3, bq[l][wi][0], bq[l][wi][1], ci[l]);
+                            mma_s8_limb(l == NL - 1, ci[l], a0, a1, a2, a3, b0, b1, ci[l]);
                     }
                 }
             }
