@@ -13,9 +13,9 @@
 // Mapping onto the SM:
 //   * one CTA per (sequence, KV head, split, 8-row query tile); its page range
 //     is the reference Partition (include/turboquant_splitk_contract.hpp:129-136);
-//     four warps each own every fourth tile (3 strips at d = 128, 1 at d = 256) of the
+//     four warps each own every fourth tile (3 strips at d = 128, 2 at d = 256) of the
 //     range and keep their own (m, l, acc), merged through shared memory at the end;
-//   * every warp streams its tiles through a private cp.async ring (2 or 3 stages):
+//   * every warp streams its tiles through a private 2-stage cp.async ring:
 //     whole packed key strips, value strips and both scale runs, resolved through
 //     the block table one tile ahead, so every KV byte crosses HBM once for all
 //     query rows of the GQA group;
@@ -76,19 +76,15 @@ struct DecodeSmem {
     // d = 128: two stages of 3 strips for each of four warps are 51 KiB, four CTAs fit and the
     // kernel stays within 128 registers (measured against 3 stages of 2 strips: +1.7 %, the
     // per-tile bookkeeping is spread over more strips; 6 stages of 1 strip: -8 %). d = 256
-    // doubles both the strips and the accumulator registers: three stages of 1 strip, three
-    // CTAs of up to 168 registers (measured against 2 stages of 2 strips: +13 %, the smaller
-    // tile leaves room in the register file; 2 CTAs of 255 registers: +7 %).
-#ifndef TQ_D256_TILE
-#define TQ_D256_TILE 1
-#define TQ_D256_STAGES 3
-#define TQ_D256_QSMEM 0
-#endif
-    static constexpr int kTileStrips = D == 128 ? 3 : TQ_D256_TILE;
-    static constexpr int kStages = D == 128 ? 2 : TQ_D256_STAGES;
-    // d = 256: the query's B fragments (up to 3 limbs x 8 words x 2 registers per lane) can
-    // live in shared memory behind the ring instead of in 32..48 registers
-    static constexpr bool kQFragSmem = D == 256 && TQ_D256_QSMEM != 0;
+    // doubles both the strips and the accumulator registers: three CTAs of up to 168 registers,
+    // two stages of 2 strips, and the query's B fragments (2..3 limbs x 8 words x 2 registers
+    // per lane) are kept in shared memory behind the ring and re-read per key word instead of
+    // occupying 32..48 registers (measured: fragments in registers with 3 stages of 1 strip
+    // 3913 GB/s, the same with the fragments in shared memory 4011, 2 stages of 2 strips 4195;
+    // with the fragments in registers the 2-strip tile had been 13 % slower than the 1-strip one).
+    static constexpr int kTileStrips = D == 128 ? 3 : 2;
+    static constexpr int kStages = 2;
+    static constexpr bool kQFragSmem = D == 256;
     static constexpr int kQFragBytes = kQFragSmem ? 3 * (D / 32) * 2 * 4 * 32 : 0;
     static constexpr int kCtasPerSm = D == 128 ? 4 : 3;
     static constexpr int kRowBytes = D / 2;
