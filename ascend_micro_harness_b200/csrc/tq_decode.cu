@@ -84,6 +84,7 @@ struct DecodeSmem {
     // with the fragments in registers the 2-strip tile had been 13 % slower than the 1-strip one).
     static constexpr int kTileStrips = D == 128 ? 3 : 2;
     static constexpr int kStages = 2;
+    // (at d = 128 the fragments are 16 registers and stay there: in shared memory -2.8 %)
     static constexpr bool kQFragSmem = D == 256;
     static constexpr int kQFragBytes = kQFragSmem ? 3 * (D / 32) * 2 * 4 * 32 : 0;
     static constexpr int kCtasPerSm = D == 128 ? 4 : 3;
