@@ -35,6 +35,9 @@ sys.path.insert(0, ROOT)
 BATCH, HQ, HKV, D, S = 64, 32, 8, 128, 16
 CTX_LO, CTX_HI = 512, 32768
 WORKLOAD = "ragged_decode_b64_h32x8_d128_ctx512-32768_fused_step"
+# The long-context configuration: 128 sequences of 65536 tokens in the whole job.
+LONG_BATCH, LONG_CTX = 128, 65536
+LONG_WORKLOAD = "long_context_decode_b128_h32x8_d128_ctx65536_fused_step"
 
 
 def kv_bytes(ctx_lens) -> int:
@@ -111,14 +114,15 @@ class ClockSampler:
 def build_workload(torch, dev, seed, ctx=None):
     """Seeded synthetic paged cache in HBM, generated directly in quantised form."""
     ctx = context_lengths(seed) if ctx is None else ctx
+    B = len(ctx)
     pages_per_seq = (ctx + 1 + S - 1) // S           # room for the token the step writes
     total_pages = int(pages_per_seq.sum()) + 64
     max_blocks = int(pages_per_seq.max())
     rng = np.random.default_rng(seed + 1)
     perm = rng.permutation(total_pages)
-    tables = np.zeros((BATCH, max_blocks), np.int32)
+    tables = np.zeros((B, max_blocks), np.int32)
     at = 0
-    for b in range(BATCH):
+    for b in range(B):
         n = int(pages_per_seq[b])
         tables[b, :n] = perm[at:at + n]
         at += n
@@ -132,10 +136,10 @@ def build_workload(torch, dev, seed, ctx=None):
     scale_cache = (torch.ldexp(torch.ones_like(e, dtype=torch.float32), e - 2) * inv).contiguous()
     signs = torch.where(torch.rand(D, device=dev, generator=g) < 0.5, -1.0, 1.0).float()
     # per-step host inputs (pinned): one new token per sequence, the query, slots, lengths
-    hk = torch.randn((BATCH, HKV * D), generator=torch.Generator().manual_seed(seed)).bfloat16().pin_memory()
-    hv = torch.randn((BATCH, HKV * D), generator=torch.Generator().manual_seed(seed + 2)).bfloat16().pin_memory()
-    hq = torch.randn((BATCH, HQ, D), generator=torch.Generator().manual_seed(seed + 3)).bfloat16().pin_memory()
-    slots = np.array([tables[b, ctx[b] // S] * S + ctx[b] % S for b in range(BATCH)], np.int32)
+    hk = torch.randn((B, HKV * D), generator=torch.Generator().manual_seed(seed)).bfloat16().pin_memory()
+    hv = torch.randn((B, HKV * D), generator=torch.Generator().manual_seed(seed + 2)).bfloat16().pin_memory()
+    hq = torch.randn((B, HQ, D), generator=torch.Generator().manual_seed(seed + 3)).bfloat16().pin_memory()
+    slots = np.array([tables[b, ctx[b] // S] * S + ctx[b] % S for b in range(B)], np.int32)
     hslots = torch.from_numpy(slots).pin_memory()
     hctx = torch.from_numpy((ctx + 1).astype(np.int32)).pin_memory()
     return dict(ctx=ctx + 1, total_pages=total_pages, max_blocks=max_blocks, inv=inv,
@@ -167,14 +171,23 @@ def run_ours(args):
     # r-th block of BATCH lengths, so one GPU sees the same batch at every N) and dealt to the
     # GPUs by the sharding helper: longest first to the lightest GPU, BATCH sequences each.
     from ascend_micro_harness_b200.sharding import partition_sequences
-    ctx_all = np.concatenate([context_lengths(4 + r) for r in range(world)])
-    mine = partition_sequences(ctx_all, world, "lpt_equal")[rank] if world > 1 else list(range(BATCH))
+    long_ctx = args.workload == "long"
+    if long_ctx:
+        # 128 sequences of 65536 tokens in all, dealt round robin: the batch per GPU shrinks as N grows
+        if LONG_BATCH % world != 0:
+            raise SystemExit("bench.py --workload long: the GPU count must divide 128")
+        ctx_all = np.full(LONG_BATCH, LONG_CTX, np.int64)
+        mine = partition_sequences(ctx_all, world, "round_robin")[rank]
+    else:
+        ctx_all = np.concatenate([context_lengths(4 + r) for r in range(world)])
+        mine = partition_sequences(ctx_all, world, "lpt_equal")[rank] if world > 1 else list(range(BATCH))
     w = build_workload(torch, dev, seed=4 + rank, ctx=ctx_all[np.asarray(mine)])
+    nseq = len(mine)   # sequences on this GPU
     ctx = w["ctx"]
-    splits = tq.choose_splits(BATCH, HKV, S, int(ctx.max()),
+    splits = tq.choose_splits(nseq, HKV, S, int(ctx.max()),
                               torch.cuda.get_device_properties(dev).multi_processor_count)
-    ws = torch.zeros(tq.decode_workspace_floats(BATCH, HQ, HKV, D, splits), dtype=torch.float32, device=dev)
-    out = torch.zeros((BATCH, HQ, D), dtype=torch.bfloat16, device=dev)
+    ws = torch.zeros(tq.decode_workspace_floats(nseq, HQ, HKV, D, splits), dtype=torch.float32, device=dev)
+    out = torch.zeros((nseq, HQ, D), dtype=torch.bfloat16, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     # Per-step host inputs live in ONE pinned staging buffer (k | v | q | slots | lens) with a
     # device twin, so the end-to-end step is one host->device copy, the three launches and one
@@ -191,14 +204,14 @@ def run_ours(args):
         at += n
     dev_in.copy_(host_in)
     dk, dv, dq, dslots, dctx = views
-    hout = torch.empty((BATCH, HQ, D), dtype=torch.bfloat16).pin_memory()
+    hout = torch.empty((nseq, HQ, D), dtype=torch.bfloat16).pin_memory()
     geom = dict(num_kv_heads=HKV, head_size=D, block_size=S, num_blocks=w["total_pages"],
                 inv_sqrt_len=w["inv"])
     scale = float(1.0 / np.sqrt(D))
 
     def scatter():
         tq.reshape_scatter(dk, dv, w["key_cache"], w["value_cache"], w["scale_cache"], dslots,
-                           w["signs"], None, num_requests=BATCH, status=status, **geom)
+                           w["signs"], None, num_requests=nseq, status=status, **geom)
 
     def export():
         tq.decode_splitk_export(dq, w["key_cache"], w["value_cache"], w["scale_cache"], w["tables"],
@@ -207,7 +220,7 @@ def run_ours(args):
                                 **geom)
 
     def combine():
-        tq.splitk_combine(ws, w["signs"], None, out, items=BATCH * HKV, rows=HQ // HKV,
+        tq.splitk_combine(ws, w["signs"], None, out, items=nseq * HKV, rows=HQ // HKV,
                           rows_stride=HQ // HKV, head_size=D, splits=splits,
                           output_stage=tq.OUT_UNROTATED, inv_sqrt_len=w["inv"])
 
@@ -302,13 +315,16 @@ def run_ours(args):
         line = {
             "metric": "splitk_4bit_decode_kv_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+            "scaling": "strong" if long_ctx else "weak",
             "vs_baseline": None, "dtype": "int4 codes; QK s8 x s8 -> s32, PV f16 x f16 -> f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_gpu": BATCH, "q_heads": HQ, "kv_heads": HKV,
+            "config": {"workload": LONG_WORKLOAD if long_ctx else WORKLOAD, "batch_per_gpu": nseq, "q_heads": HQ, "kv_heads": HKV,
                        "head_dim": D, "page_tokens": S, "splits": int(splits),
                        "kv_bytes_per_gpu": my_bytes,
                        "l2": "inputs larger than L2 (%.2f GB of cache read per step)" % (my_bytes / 1e9),
-                       "parallelism": f"{BATCH * world} sequences dealt to {world} GPU(s) by total context (longest first, {BATCH} each), no collective"},
+                       "parallelism": f"{nseq * world} sequences dealt to {world} GPU(s) "
+                                      + ("round robin" if long_ctx else "by total context (longest first)")
+                                      + f", {nseq} each, no collective"},
             "decode_us_per_step": round(kernel_ms * 1e3, 1),
             "e2e": {"value": round(total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9, 1),
                     "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
@@ -326,7 +342,7 @@ def run_ours(args):
             "extra": extra,
         }
         if world == 1:
-            line["cpu_baseline"] = cpu_baseline_decode(w, args)
+            line["cpu_baseline"] = cpu_baseline_decode(w, args, sample=2 if long_ctx else nseq)
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()
@@ -510,7 +526,7 @@ def cpu_baseline_decode(w, args, sample=BATCH):
     dt = time.perf_counter() - t0
     return {"value": round(kv_bytes(ctx) / dt / 1e9, 4), "unit": "GB/s", "cores": threads,
             "kind": "port", "seconds": round(dt, 2),
-            "sample": f"decode of the first {sample} of {BATCH} sequences "
+            "sample": f"decode of the first {sample} of {len(w['ctx'])} sequences "
                       f"({int(ctx.sum())} context tokens), FP64 oracle, {threads} threads"}
 
 
@@ -525,8 +541,9 @@ def run_reference(args):
     from oracle.bindings import Oracle
     o = Oracle()
     threads = max(1, o.hardware_threads())
-    sample = 4
-    ctx = context_lengths(4, BATCH)[:sample] + 1
+    long_ctx = args.workload == "long"
+    sample = 2 if long_ctx else 4
+    ctx = (np.full(sample, LONG_CTX, np.int64) if long_ctx else context_lengths(4, BATCH)[:sample]) + 1
     rng = np.random.default_rng(5)
     pages = (ctx + S - 1) // S
     P = int(pages.sum())
@@ -558,9 +575,10 @@ def run_reference(args):
     print(json.dumps({
         "impl": "reference", "metric": "splitk_4bit_decode_kv_hbm_gbs", "value": round(value, 4),
         "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": min(args.warmup, 1),
-        "ms_per_step": round(dt * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(dt * 1e3, 2), "higher_is_better": True,
+        "scaling": "strong" if long_ctx else "weak",
         "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample_txt},
+        "config": {"workload": LONG_WORKLOAD if long_ctx else WORKLOAD, "sample": sample_txt},
         "cpu_baseline": {"value": round(value, 4), "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": sample_txt},
         "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0,
@@ -573,6 +591,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="ragged", choices=["ragged", "long"],
+                    help="ragged: 64 sequences of 512..32768 tokens per GPU (the headline, weak scaling); "
+                         "long: 128 sequences of 65536 tokens in the whole job (strong scaling)")
     ap.add_argument("--profile", default=None, choices=["decode", "reshape", "reshape_a8", "lm_decode", "lm_reshape", "scatter", "nz_import"],
                     help="run a small case of one kernel (for ncu), print no bench line")
     args = ap.parse_args()
