@@ -115,3 +115,23 @@ def test_varlen_writer_refuses_bad_geometry_on_the_host():
     assert lib.tq_reshape_and_cache_varlen(*args, 0, 0, 1, 128, 16, 4, 0.1, None) == 0   # nothing to do
     bad = [None, C.c_void_p(8), p, p, p, p, p, p, p, p]
     assert lib.tq_reshape_and_cache_varlen(*bad, 2, 3, 1, 128, 16, 4, 0.1, None) == 1    # key not aligned
+
+
+def test_kv4_import_and_prerotated_decode_refuse_bad_arguments_on_the_host():
+    from ascend_micro_harness_b200._lib import load_library
+    lib = load_library()
+    p = C.c_void_p(16)   # never dereferenced
+    imp = [None, p, p, p, p, p, p]
+    assert lib.tq_nz_kv4_import(*imp, 2, 32, 4, 2.98) == 1     # pages are 64 or 128 slots
+    assert lib.tq_nz_kv4_import(*imp, 0, 64, 4, 2.98) == 1     # no KV head
+    assert lib.tq_nz_kv4_import(*imp, 2, 64, 4, 0.0) == 1      # the gain divides the scales
+    assert lib.tq_nz_kv4_import(*imp, 2, 128, 0, 2.98) == 0    # nothing to import
+    bad = [None, C.c_void_p(8), p, p, p, p, p]
+    assert lib.tq_nz_kv4_import(*bad, 2, 64, 4, 2.98) == 1     # packed plane not 16-byte aligned
+    dec = [None, p, p, p, p, p, p, p, p, 0]
+    assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 1, 0, 2, 0.0625, None) == 1   # no such grid
+    assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 17, 0, 1, 0.0625, None) == 1  # 17 splits
+    assert lib.tq_decode_splitk_prerotated(*dec, 2, 30, 8, 256, 64, 8, 4, 1, 0, 1, 0.0625, None) == 1   # heads % KV heads
+    assert lib.tq_decode_splitk_prerotated(*dec, 0, 32, 8, 256, 64, 8, 4, 1, 0, 1, 0.0625, None) == 0   # empty batch
+    nullq = [None, None, p, p, p, p, p, p, p, 0]
+    assert lib.tq_decode_splitk_prerotated(*nullq, 2, 32, 8, 256, 64, 8, 4, 1, 0, 1, 0.0625, None) == 1
