@@ -399,10 +399,17 @@ def side_measurements(torch, tq, dev, args):
     return out
 
 
+def _use_reference_geometry():
+    """Switch the module's workload constants to head size 256 with 16 query / 4 KV heads."""
+    global D, HQ, HKV
+    D, HQ, HKV = 256, 16, 4
+
+
 def run_profile_case(args):
     """A small case of one kernel for an ncu capture: inputs larger than L2 but well under
     a GB on the device, two warm-up launches and three captured ones.
       decode  : 64 sequences x 2048..4096 tokens (about 0.2 GB of cache)
+      decode_d256 : the same at head size 256 with 16 query / 4 KV heads
       reshape : bf16 prefill of 65536 tokens x 8 KV heads x 128 (0.27 GB)
       reshape_a8 : the same prefill with int8 activations (0.13 GB)
       lm_decode  : the Lloyd-Max cache variant, 64 sequences x 2048..4096 tokens, 2 splits
@@ -463,7 +470,10 @@ def run_profile_case(args):
         torch.cuda.synchronize()
         print(json.dumps({"profile": "nz_import",
                           "bytes": 2 * (2 * nzk.numel()) + P * SS * 8 * 4 + 2 * P * H * SS * 4}))
-    elif args.profile == "decode":
+    elif args.profile in ("decode", "decode_d256"):
+        if args.profile == "decode_d256":
+            # the reference kernels' own geometry: head size 256, 16 query / 4 KV heads
+            _use_reference_geometry()
         ctx = context_lengths(11, BATCH, 2048, 4096)
         w = build_workload(torch, dev, 11, ctx)
         splits = tq.choose_splits(BATCH, HKV, S, int(w["ctx"].max()),
@@ -479,7 +489,7 @@ def run_profile_case(args):
                                     splits=0, softmax_scale=float(1.0 / np.sqrt(D)),
                                     max_context_hint=int(w["ctx"].max()))
         torch.cuda.synchronize()
-        print(json.dumps({"profile": "decode", "kv_bytes": kv_bytes(w["ctx"]), "splits": int(splits)}))
+        print(json.dumps({"profile": args.profile, "kv_bytes": kv_bytes(w["ctx"]), "splits": int(splits)}))
     else:
         T, H = 65536, 8
         g = torch.Generator(device=dev)
@@ -594,7 +604,7 @@ def main():
     ap.add_argument("--workload", default="ragged", choices=["ragged", "long"],
                     help="ragged: 64 sequences of 512..32768 tokens per GPU (the headline, weak scaling); "
                          "long: 128 sequences of 65536 tokens in the whole job (strong scaling)")
-    ap.add_argument("--profile", default=None, choices=["decode", "reshape", "reshape_a8", "lm_decode", "lm_reshape", "scatter", "nz_import"],
+    ap.add_argument("--profile", default=None, choices=["decode", "decode_d256", "reshape", "reshape_a8", "lm_decode", "lm_reshape", "scatter", "nz_import"],
                     help="run a small case of one kernel (for ncu), print no bench line")
     args = ap.parse_args()
     if args.profile:
