@@ -410,6 +410,7 @@ def run_profile_case(args):
     a GB on the device, two warm-up launches and three captured ones.
       decode  : 64 sequences x 2048..4096 tokens (about 0.2 GB of cache)
       decode_d256 : the same at head size 256 with 16 query / 4 KV heads
+      config3 : batch 1, context 4096, split-K swept over 1/2/4/8/16/auto: prints microseconds per decode
       reshape : bf16 prefill of 65536 tokens x 8 KV heads x 128 (0.27 GB)
       reshape_a8 : the same prefill with int8 activations (0.13 GB)
       lm_decode  : the Lloyd-Max cache variant, 64 sequences x 2048..4096 tokens, 2 splits
@@ -420,7 +421,48 @@ def run_profile_case(args):
     import ascend_micro_harness_b200 as tq
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
-    if args.profile == "lm_decode":
+    if args.profile == "config3":
+        # batch 1, context 4096, shuffled table: microseconds per decode (export + combine) for
+        # explicit split counts and for the library's own choice, L2 flushed before every call
+        ctx_len, P = 4096, 4096 // S + 4
+        g = torch.Generator(device=dev)
+        g.manual_seed(1)
+        nb = P * HKV * S * D // 2
+        kc = torch.randint(0, 256, (nb,), dtype=torch.uint8, device=dev, generator=g)
+        vc = torch.randint(0, 256, (nb,), dtype=torch.uint8, device=dev, generator=g)
+        inv = float(np.float32(1.0) / np.sqrt(np.float32(D)))
+        e = torch.randint(0, 3, (2 * P * HKV * S,), device=dev, generator=g)
+        sc = (torch.ldexp(torch.ones_like(e, dtype=torch.float32), e - 2) * inv).contiguous()
+        signs = torch.ones(D, device=dev)
+        q = torch.randn((1, HQ, D), device=dev, generator=g).bfloat16()
+        tab = torch.randperm(P, device=dev, generator=g)[: ctx_len // S].int().reshape(1, -1).contiguous()
+        lens = torch.tensor([ctx_len], dtype=torch.int32, device=dev)
+        out = torch.zeros((1, HQ, D), dtype=torch.bfloat16, device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        res = {"profile": "config3", "kv_bytes": ctx_len * HKV * (D + 8), "us_per_decode": {}}
+        for splits in (1, 2, 4, 8, 16, 0):
+            n = splits if splits else tq.choose_splits(1, HKV, S, ctx_len)
+            ws = torch.zeros(tq.decode_workspace_floats(1, HQ, HKV, D, n), device=dev)
+
+            def call():
+                tq.decode_splitk(q, kc, vc, sc, tab, lens, signs, out, num_heads=HQ, num_kv_heads=HKV,
+                                 head_size=D, block_size=S, num_blocks=P, inv_sqrt_len=inv,
+                                 softmax_scale=inv, splits=splits, max_context_hint=ctx_len, workspace=ws,
+                                 output_stage=1)
+            for _ in range(5):
+                call()
+            ts = []
+            for _ in range(20):
+                flush.fill_(1)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                call()
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b) * 1e3)
+            res["us_per_decode"]["auto(%d)" % n if splits == 0 else str(splits)] = round(statistics.median(ts), 1)
+        print(json.dumps(res))
+    elif args.profile == "lm_decode":
         rng = np.random.default_rng(0)
         ctx = rng.integers(2048, 4097, size=BATCH)
         pages = (ctx + S - 1) // S
@@ -604,7 +646,7 @@ def main():
     ap.add_argument("--workload", default="ragged", choices=["ragged", "long"],
                     help="ragged: 64 sequences of 512..32768 tokens per GPU (the headline, weak scaling); "
                          "long: 128 sequences of 65536 tokens in the whole job (strong scaling)")
-    ap.add_argument("--profile", default=None, choices=["decode", "decode_d256", "reshape", "reshape_a8", "lm_decode", "lm_reshape", "scatter", "nz_import"],
+    ap.add_argument("--profile", default=None, choices=["decode", "decode_d256", "config3", "reshape", "reshape_a8", "lm_decode", "lm_reshape", "scatter", "nz_import"],
                     help="run a small case of one kernel (for ncu), print no bench line")
     args = ap.parse_args()
     if args.profile:
