@@ -130,3 +130,56 @@ def test_prerotated_integer_grid_equals_the_rotating_entry(cuda, oracle):
                                 softmax_scale=0.0625, splits=2, workspace=ws, code_grid=tq.GRID_INTEGER)
     torch.cuda.synchronize()
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("d,grid", [(128, 1), (128, 0), (256, 0)])
+def test_prerotated_decode_against_a_numpy_reference(cuda, d, grid):
+    """Both code grids at both head sizes against an FP64 attention written out in numpy over the
+    native planes (key token-major, value channel-major per 16-token strip, planar scales)."""
+    import torch
+    import ascend_micro_harness_b200 as tq
+    rng = np.random.default_rng(d + grid)
+    Hq, H, S = 8, 2, 16
+    ctx = np.array([37, 300, 16, 1], np.int32)
+    B = len(ctx)
+    pages = (ctx + S - 1) // S
+    P = int(pages.sum()) + 2
+    table = np.zeros((B, int(pages.max())), np.int32)
+    perm, at = rng.permutation(P), 0
+    for b in range(B):
+        table[b, :pages[b]] = perm[at:at + pages[b]]
+        at += int(pages[b])
+    kc = rng.integers(0, 256, P * H * S * d // 2, dtype=np.uint8)
+    vc = rng.integers(0, 256, P * H * S * d // 2, dtype=np.uint8)
+    sc = rng.uniform(0.05, 0.2, 2 * P * H * S).astype(np.float32)
+    q = rng.standard_normal((B, Hq, d)).astype(np.float32)
+
+    def codes(cache, value_plane):
+        b = cache.reshape(P, H, -1)
+        nib = np.stack([b & 15, b >> 4], -1).reshape(P, H, -1).astype(np.int32)
+        nib = np.where(nib > 7, nib - 16, nib)
+        if not value_plane:
+            return nib.reshape(P, H, S, d)
+        return nib.reshape(P, H, S // 16, d, 16).transpose(0, 1, 2, 4, 3).reshape(P, H, S, d)
+    K, V = codes(kc, False) + 0.5 * grid, codes(vc, True) + 0.5 * grid
+    scp = sc.reshape(2, P, H, S).astype(np.float64)
+    want = np.zeros((B, Hq, d))
+    for b in range(B):
+        for h in range(Hq):
+            kv = h // (Hq // H)
+            pg, tk = table[b, np.arange(ctx[b]) // S], np.arange(ctx[b]) % S
+            logits = (K[pg, kv, tk] @ q[b, h].astype(np.float64)) * scp[0, pg, kv, tk] * 0.3
+            p = np.exp(logits - logits.max())
+            want[b, h] = (p * scp[1, pg, kv, tk]) @ V[pg, kv, tk] / p.sum()
+    dkc, dvc, dsc = (torch.from_numpy(a).to(cuda) for a in (kc, vc, sc))
+    ws = torch.zeros(tq.decode_workspace_floats(B, Hq, H, d, 2), dtype=torch.float32, device=cuda)
+    out = torch.zeros((B, Hq, d), dtype=torch.float32, device=cuda)
+    st = torch.zeros(1, dtype=torch.int32, device=cuda)
+    tq.decode_splitk_prerotated(torch.from_numpy(q).to(cuda), dkc, dvc, dsc, torch.from_numpy(table).to(cuda),
+                                torch.from_numpy(ctx).to(cuda), out, num_heads=Hq, num_kv_heads=H, head_size=d,
+                                block_size=S, num_blocks=P, softmax_scale=0.3, splits=2, workspace=ws,
+                                code_grid=grid, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    got = out.cpu().numpy()
+    assert (np.abs(got - want) <= ABS_TOL + REL_TOL * np.abs(want)).all()
