@@ -801,7 +801,8 @@ struct CombineParams {
     void* output;
     uint32_t rows, rows_stride, splits, output_stage, out_dtype;
     float inv_sqrt_len;
-    uint32_t block16;   // 1: the rotation is block-diagonal H16 / 4 (Lloyd-Max cache variant)
+    uint32_t block16;   // egress rotation: 0 the cache's two-level rotation, 1 block-diagonal H16 / 4
+                        // (Lloyd-Max variant), 2 diag(s) H_d diag(s) / sqrt(d) (the fused decoder's Pi)
     uint32_t gate_dtype; // TQ_DTYPE_* of `gate`
     uint32_t tokens_per_req, kv_heads;   // output row of (item, row): see out_row below
 };
@@ -848,7 +849,7 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
     float v = l > 0.f ? a / l : 0.f;
     if (p.output_stage != TQ_OUT_ROTATED) {
         int cur = 0;
-        buf[0][c] = v;
+        buf[0][c] = p.block16 == 2u ? v * p.signs[c] : v;
         __syncthreads();
         auto stage = [&](int s) {
             const float mine = buf[cur][c], other = buf[cur][c ^ s];
@@ -856,9 +857,14 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
             __syncthreads();
             cur ^= 1;
         };
-        if (p.block16 != 0u) {
+        if (p.block16 == 1u) {
             for (int s = 1; s < 16; s <<= 1) stage(s);
             v = buf[cur][c] * 0.25f;
+        } else if (p.block16 == 2u) {
+            // Pi = diag(s) H diag(s) / sqrt(d), an involution (tests/common/fused_decode_opt_fixture.hpp:
+            // 104-117): signs went in with the load above, the full butterfly, signs and scale out
+            for (int s = 1; s < D; s <<= 1) stage(s);
+            v = buf[cur][c] * p.signs[c] * p.inv_sqrt_len;
         } else {
             for (int s = kGroup; s < D; s <<= 1) stage(s);
             buf[cur][c] *= p.signs[c];
@@ -1038,7 +1044,7 @@ static int splitk_combine(void* stream, const float* workspace, const float* pi_
                           const void* gate, uint32_t gate_dtype, void* output, uint32_t out_dtype,
                           uint32_t items, uint32_t rows, uint32_t rows_stride, uint32_t head_size,
                           uint32_t splits, uint32_t output_stage, float inv_sqrt_len,
-                          uint32_t tokens_per_req = 1, uint32_t kv_heads = 1)
+                          uint32_t tokens_per_req = 1, uint32_t kv_heads = 1, uint32_t rotation = ~0u)
 {
     if (!rows || rows > rows_stride || !splits || splits > 16 || output_stage > TQ_OUT_GATED ||
         out_dtype > TQ_DTYPE_F32 || gate_dtype > TQ_DTYPE_F32 ||
@@ -1049,8 +1055,8 @@ static int splitk_combine(void* stream, const float* workspace, const float* pi_
         return TQ_ERR_INVALID_ARGUMENT;
     if (items == 0) return TQ_OK;
     CombineParams p{workspace, pi_signs, gate, output, rows, rows_stride, splits, output_stage,
-                    out_dtype, inv_sqrt_len, pi_signs == nullptr ? 1u : 0u, gate_dtype, tokens_per_req,
-                    kv_heads};
+                    out_dtype, inv_sqrt_len, rotation != ~0u ? rotation : (pi_signs == nullptr ? 1u : 0u),
+                    gate_dtype, tokens_per_req, kv_heads};
     const uint64_t grid = static_cast<uint64_t>(items) * rows;
     if (grid > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1183,7 +1189,8 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
                           uint32_t chunk_pages, uint32_t output_stage, float inv_sqrt_len,
                           float softmax_scale, uint32_t* status, uint32_t gate_dtype = TQ_DTYPE_F32,
                           bool q_f16 = false, uint32_t tokens_per_req = 1,
-                          const float* query_rot_f32 = nullptr, uint32_t midrise = 0)
+                          const float* query_rot_f32 = nullptr, uint32_t midrise = 0,
+                          uint32_t rotation = ~0u)
 {
     if (output_stage > TQ_OUT_GATED || !output || (output_stage == TQ_OUT_GATED && !gate))
         return TQ_ERR_INVALID_ARGUMENT;
@@ -1197,7 +1204,7 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
     const uint32_t rows = num_heads / num_kv_heads * tokens_per_req;
     return splitk_combine(stream, workspace, pi_signs, gate, gate_dtype, output, out_dtype,
                           batch * num_kv_heads, rows, rows, head_size, splits, output_stage,
-                          inv_sqrt_len, tokens_per_req, num_kv_heads);
+                          inv_sqrt_len, tokens_per_req, num_kv_heads, rotation);
 }
 
 // Query, gate and output in ONE 16-bit element type, FP16 or BF16, as the raw-query entry of
@@ -1278,31 +1285,40 @@ extern "C" int tq_decode_splitk_mtp(void* stream, const uint16_t* query, const i
 
 // The pre-rotated entry of the reference's fused decoder (launch_fused_decode_opt,
 // include/turboquant_fused_decode_opt.hpp:187-189: `queryRot` is the FP32 rotated image of
-// the query, the output stays in the rotated basis) over a cache in this library's native
-// layout. code_grid 0: a nibble is the integer c (dequantised value c * scale), the
-// TurboQuant cache; code_grid 1: the uniform mid-rise grid of the KV4/FP8 cache, a nibble c
-// stands for (c + 0.5) * scale (fused_decode/common/turboquant_mode.h:100-124 with b = c + 8),
-// which is how a cache brought over with tq_nz_kv4_import decodes. query_rot is
-// [batch][num_heads][head_size] FP32; nothing is rotated or rounded on the way in.
+// the query) over a cache in this library's native layout. code_grid 0: a nibble is the
+// integer c (dequantised value c * scale), the TurboQuant cache; code_grid 1: the uniform
+// mid-rise grid of the KV4/FP8 cache, a nibble c stands for (c + 0.5) * scale
+// (fused_decode/common/turboquant_mode.h:100-124 with b = c + 8), which is how a cache brought
+// over with tq_nz_kv4_import decodes. query_rot is [batch][num_heads][head_size] FP32; nothing
+// is rotated or rounded on the way in. Output stages as in the fused decoder's raw-query entry
+// (fused_decode/common/turboquant_layout.h:141-150): 0 leaves the context in the rotated basis,
+// 1 applies Pi = diag(pi_signs) H diag(pi_signs) / sqrt(head_size) once more (Pi is an
+// involution), 2 also divides by 1 + exp(-gate). pi_signs is read by stages 1 and 2 only, gate
+// by stage 2 only.
 extern "C" int tq_decode_splitk_prerotated(void* stream, const float* query_rot, const int8_t* key_cache,
                                            const int8_t* value_cache, const float* scale_cache,
                                            const int32_t* block_tables, const int32_t* context_lens,
-                                           float* workspace, void* output, uint32_t out_dtype,
+                                           const float* pi_signs, const void* gate, float* workspace,
+                                           void* output, uint32_t out_dtype, uint32_t gate_dtype,
                                            uint32_t batch, uint32_t num_heads, uint32_t num_kv_heads,
                                            uint32_t head_size, uint32_t block_size, uint32_t num_blocks,
                                            uint32_t max_blocks, uint32_t splits, uint32_t max_context_hint,
-                                           uint32_t code_grid, float softmax_scale, uint32_t* status)
+                                           uint32_t code_grid, uint32_t output_stage, float softmax_scale,
+                                           uint32_t* status)
 {
-    if (!num_kv_heads || !block_size || splits > 16 || code_grid > 1u || (batch != 0 && !query_rot))
+    if (!num_kv_heads || !block_size || splits > 16 || code_grid > 1u || (batch != 0 && !query_rot) ||
+        output_stage > TQ_OUT_GATED || gate_dtype > TQ_DTYPE_F32 ||
+        (output_stage != TQ_OUT_ROTATED && !pi_signs) || (head_size != 128 && head_size != 256))
         return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
                             &chunk_pages);
+    const float inv_sqrt_len = head_size == 128 ? 0.08838834764831845f : 0.0625f;
     return decode_planned(stream, nullptr, key_cache, value_cache, scale_cache, block_tables, context_lens,
-                          nullptr, nullptr, workspace, output, out_dtype, batch, num_heads, num_kv_heads,
+                          pi_signs, gate, workspace, output, out_dtype, batch, num_heads, num_kv_heads,
                           head_size, block_size, num_blocks, max_blocks, splits, chunk_pages,
-                          TQ_OUT_ROTATED, 1.0f, softmax_scale, status, TQ_DTYPE_F32, false, 1, query_rot,
-                          code_grid);
+                          output_stage, inv_sqrt_len, softmax_scale, status, gate_dtype, false, 1, query_rot,
+                          code_grid, 2u);
 }
 
 // ------------------------------------------------- decode without a caller workspace

@@ -167,18 +167,21 @@ def nz_kv4_import(nz_key, nz_value, nz_scales, key_cache, value_cache, scale_cac
 def decode_splitk_prerotated(query_rot, key_cache, value_cache, scale_cache, block_tables, context_lens,
                              output, *, num_heads, num_kv_heads, head_size, block_size, num_blocks,
                              softmax_scale=1.0, splits=0, max_context_hint=0, workspace=None,
-                             code_grid=GRID_INTEGER, status=None, stream=None):
+                             code_grid=GRID_INTEGER, pi_signs=None, gate=None, output_stage=OUT_ROTATED,
+                             status=None, stream=None):
     """Decode with an FP32 query that is already in the cache's rotated basis (the fused
-    decoder's pre-rotated entry); the output stays in that basis. code_grid=GRID_MIDRISE reads
-    a nibble c as (c + 0.5) * scale, the grid of an imported KV4/FP8 cache."""
+    decoder's pre-rotated entry). code_grid=GRID_MIDRISE reads a nibble c as (c + 0.5) * scale,
+    the grid of an imported KV4/FP8 cache. output_stage OUT_UNROTATED applies
+    Pi = diag(pi_signs) H diag(pi_signs) / sqrt(head_size) to the context, OUT_GATED also the
+    sigmoid gate (float32, float16 or bfloat16)."""
     lib = load_library()
     batch = query_rot.numel() // (num_heads * head_size)
     _check(lib.tq_decode_splitk_prerotated(
         _stream(stream), _ptr(query_rot), _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache),
-        _ptr(block_tables), _ptr(context_lens), _ptr(workspace), _ptr(output), _out_dtype(output),
-        batch, num_heads, num_kv_heads, head_size, block_size, num_blocks, block_tables.shape[-1],
-        splits, max_context_hint, code_grid, softmax_scale, _ptr(status)),
-        "tq_decode_splitk_prerotated")
+        _ptr(block_tables), _ptr(context_lens), _ptr(pi_signs), _ptr(gate), _ptr(workspace), _ptr(output),
+        _out_dtype(output), _out_dtype(gate) if gate is not None else 2, batch, num_heads, num_kv_heads,
+        head_size, block_size, num_blocks, block_tables.shape[-1], splits, max_context_hint, code_grid,
+        output_stage, softmax_scale, _ptr(status)), "tq_decode_splitk_prerotated")
 
 
 STATIC_WORKSPACE_FLOATS = 2 * 1024 * 1024

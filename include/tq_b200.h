@@ -290,18 +290,24 @@ int tq_nz_kv4_import(void* stream, const uint8_t* nz_key, const uint8_t* nz_valu
 
 /* The pre-rotated entry (launch_fused_decode_opt, include/turboquant_fused_decode_opt.hpp:
  * 187-189): query_rot is the FP32 rotated image [batch][num_heads][head_size] of the query,
- * nothing is rotated or rounded on the way in, the output [batch][num_heads][head_size] stays
- * in the rotated basis. code_grid 0: nibble c decodes to c * scale (the TurboQuant cache);
- * 1: to (c + 0.5) * scale (an imported KV4/FP8 cache). Workspace, splits, max_context_hint,
- * status as for tq_decode_splitk. */
+ * nothing is rotated or rounded on the way in. code_grid 0: nibble c decodes to c * scale (the
+ * TurboQuant cache); 1: to (c + 0.5) * scale (an imported KV4/FP8 cache). Output stages as in
+ * the fused decoder's raw-query entry (fused_decode/common/turboquant_layout.h:141-150):
+ * TQ_OUT_ROTATED leaves the context in the rotated basis; TQ_OUT_UNROTATED applies
+ * Pi = diag(pi_signs) H diag(pi_signs) / sqrt(head_size) once more (an involution, so this is
+ * the original basis); TQ_OUT_GATED also divides by 1 + exp(-gate). pi_signs (head_size
+ * floats, +-1) is read by the last two stages only, gate ([batch][num_heads][head_size] of
+ * gate_dtype) by the last only. Workspace, splits, max_context_hint, status as for
+ * tq_decode_splitk. */
 int tq_decode_splitk_prerotated(void* stream, const float* query_rot, const int8_t* key_cache,
                                 const int8_t* value_cache, const float* scale_cache,
                                 const int32_t* block_tables, const int32_t* context_lens,
-                                float* workspace, void* output, uint32_t out_dtype, uint32_t batch,
+                                const float* pi_signs, const void* gate, float* workspace,
+                                void* output, uint32_t out_dtype, uint32_t gate_dtype, uint32_t batch,
                                 uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
                                 uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
                                 uint32_t splits, uint32_t max_context_hint, uint32_t code_grid,
-                                float softmax_scale, uint32_t* status);
+                                uint32_t output_stage, float softmax_scale, uint32_t* status);
 
 /* ------------------------------------------------------- stand-alone routines
  * The reference's single-purpose routines that its cache operators do not call. */

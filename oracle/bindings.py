@@ -264,6 +264,14 @@ class Oracle:
         assert rc == 0
         return kc, vc, sc
 
+    def signed_hadamard(self, x, signs):
+        """Pi x with Pi = diag(s) H diag(s) / sqrt(d), rows of x."""
+        x = _c(x, np.float32)
+        d = x.shape[-1]
+        y = np.zeros_like(x)
+        self.lib.tqo_signed_hadamard(C.c_int(d), _p(_c(signs, np.float32)), _p(x), _p(y), C.c_int(x.size // d))
+        return y
+
     def nz_kv4_decode(self, q_rot, nz_key, nz_value, nz_scales, block_tables, context_lens, Hq, H, S,
                       softmax_scale=0.0625, gain=KV4_GAIN):
         q = _c(q_rot, np.float32)
@@ -343,6 +351,16 @@ class Reference:
 
     def fused_fixture(self, context, requests, kv_heads, group_heads, page_tokens):
         return RefFusedFixture(self, context, requests, kv_heads, group_heads, page_tokens)
+
+    def fused_signs(self, d=256):
+        self.lib.ref_fused_sign.restype = C.c_float
+        return np.array([self.lib.ref_fused_sign(C.c_int(c)) for c in range(d)], np.float32)
+
+    def fused_pi_apply(self, x):
+        x = _c(x, np.float32)
+        y = np.zeros(256, np.float32)
+        self.lib.ref_fused_pi_apply(_p(x), _p(y))
+        return y
 
     def kv4_gain(self):
         self.lib.ref_kv4_gain.restype = C.c_float
@@ -434,6 +452,16 @@ class RefFusedFixture:
         out = np.zeros(n // np.dtype(dt).itemsize, dt)
         if n:
             self.ref.lib.ref_fused_fixture_get(self.h, C.c_int(which), _p(out))
+        return out
+
+    def expected_row(self, row, stage):
+        out = np.zeros(256, np.float32)
+        self.ref.lib.ref_fused_expected_row(self.h, C.c_size_t(row), C.c_uint(stage), _p(out))
+        return out
+
+    def gate_f16_bits(self):
+        out = np.zeros(self.requests * self.kv_heads * self.group_heads * 256, np.uint16)
+        self.ref.lib.ref_fused_gate_bits(self.h, _p(out))
         return out
 
     def __del__(self):

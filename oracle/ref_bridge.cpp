@@ -343,6 +343,28 @@ std::size_t ref_fused_fixture_get(void* p, int which, void* out)
     if (out) std::memcpy(out, src, n);
     return n;
 }
+// The fused decoder's Pi = diag(s) H diag(s) / sqrt(D) (fixture :104-186), its sign vector, the
+// expected output row under an output stage and the fixture's gate logits (FP16 bits).
+float ref_fused_sign(int channel) { return fused_decode_opt_test::RawQueryBasis::sign_at(channel); }
+void ref_fused_pi_apply(const float* x, float* y)
+{
+    const fused_decode_opt_test::RawQueryBasis basis;
+    const auto r = basis.apply(x);
+    std::memcpy(y, r.data(), r.size() * sizeof(float));
+}
+void ref_fused_expected_row(void* p, std::size_t row, unsigned stage, float* out)
+{
+    const auto& f = *static_cast<fused_decode_opt_test::Fixture*>(p);
+    const fused_decode_opt_test::RawQueryBasis basis;
+    const auto r = f.expected_row(basis, row, stage);
+    std::memcpy(out, r.data(), r.size() * sizeof(float));
+}
+void ref_fused_gate_bits(void* p, std::uint16_t* out)
+{
+    const auto& f = *static_cast<fused_decode_opt_test::Fixture*>(p);
+    const auto g = f.gate_logits();
+    std::memcpy(out, g.data(), g.size() * 2);
+}
 float ref_kv4_gain() { return vllm_ascend::turboquant::TurboQuantModeTraits<vllm_ascend::turboquant::TurboQuantMode::KV4_FP8>::kGain; }
 std::uint64_t ref_nz_tiled_packed_byte(std::uint64_t slot, std::uint64_t head, std::uint64_t column,
                                        std::uint64_t H, std::uint64_t packed)

@@ -968,6 +968,29 @@ int tqo_nz_kv4_import(const std::uint8_t* nz_key, const std::uint8_t* nz_value, 
     return 0;
 }
 
+// Pi = diag(s) H diag(s) / sqrt(d) of the fused decoder, H the Sylvester-Hadamard matrix
+// (tests/common/fused_decode_opt_fixture.hpp:104-117,:166-182: x *= s, the unnormalised
+// butterfly, x *= s, one multiply by inv_sqrt_len), on `rows` vectors in FP64, narrowed once.
+void tqo_signed_hadamard(int d, const float* signs, const float* x, float* y, int rows)
+{
+    std::vector<double> v(d);
+    double scale = 1.0;
+    for (int n = d; n > 1; n >>= 2) scale *= 0.5;   // d is a power of four here (64, 256) or 128
+    if (d == 128) scale = 1.0 / std::sqrt(128.0);
+    for (int r = 0; r < rows; ++r) {
+        for (int i = 0; i < d; ++i) v[i] = static_cast<double>(x[static_cast<std::size_t>(r) * d + i]) * signs[i];
+        for (int stride = 1; stride < d; stride <<= 1)
+            for (int i = 0; i < d; ++i)
+                if ((i & stride) == 0) {
+                    const double a = v[i], b = v[i ^ stride];
+                    v[i] = a + b;
+                    v[i ^ stride] = a - b;
+                }
+        for (int i = 0; i < d; ++i)
+            y[static_cast<std::size_t>(r) * d + i] = static_cast<float>(v[i] * signs[i] * scale);
+    }
+}
+
 // FP64 attention straight off the NZ-tiled cache with a pre-rotated FP32 query
 // [B][Hq][256] (the fused decoder's `queryRot`), output in the rotated basis, FP32
 // (the scalar FP64 sum of tests/common/fused_decode_opt_fixture.hpp:300-312, for arbitrary

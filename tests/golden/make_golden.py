@@ -92,7 +92,10 @@ def main():
                             table=fx.get("table")[:b * fx.pages].reshape(b, fx.pages),
                             lengths=fx.get("lengths")[:b], expected=fx.get("expected"),
                             dims=np.array([n, b, h, g, S, fx.pages, fx.physical_pages]),
-                            gain=np.float32(r.kv4_gain()),
+                            gain=np.float32(r.kv4_gain()), pi_signs=r.fused_signs(),
+                            gate_f16_bits=fx.gate_f16_bits(),
+                            expected_unrotated=np.stack([fx.expected_row(i, 1) for i in range(b * h * g)]),
+                            expected_gated=np.stack([fx.expected_row(i, 2) for i in range(b * h * g)]),
                             nz_bytes=np.array([[slot, head, col, H, r.nz_tiled_packed_byte(slot, head, col, H)]
                                                for H in (1, 3) for slot in (0, 1, 63, 64, 127)
                                                for head in range(H) for col in (0, 31, 32, 127)], np.int64))

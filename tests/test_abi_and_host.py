@@ -128,10 +128,13 @@ def test_kv4_import_and_prerotated_decode_refuse_bad_arguments_on_the_host():
     assert lib.tq_nz_kv4_import(*imp, 2, 128, 0, 2.98) == 0    # nothing to import
     bad = [None, C.c_void_p(8), p, p, p, p, p]
     assert lib.tq_nz_kv4_import(*bad, 2, 64, 4, 2.98) == 1     # packed plane not 16-byte aligned
-    dec = [None, p, p, p, p, p, p, p, p, 0]
-    assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 1, 0, 2, 0.0625, None) == 1   # no such grid
-    assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 17, 0, 1, 0.0625, None) == 1  # 17 splits
-    assert lib.tq_decode_splitk_prerotated(*dec, 2, 30, 8, 256, 64, 8, 4, 1, 0, 1, 0.0625, None) == 1   # heads % KV heads
-    assert lib.tq_decode_splitk_prerotated(*dec, 0, 32, 8, 256, 64, 8, 4, 1, 0, 1, 0.0625, None) == 0   # empty batch
-    nullq = [None, None, p, p, p, p, p, p, p, 0]
-    assert lib.tq_decode_splitk_prerotated(*nullq, 2, 32, 8, 256, 64, 8, 4, 1, 0, 1, 0.0625, None) == 1
+    dec = [None, p, p, p, p, p, p, p, p, p, p, 0, 2]
+    assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 1, 0, 2, 0, 0.0625, None) == 1   # no such grid
+    assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 17, 0, 1, 0, 0.0625, None) == 1  # 17 splits
+    assert lib.tq_decode_splitk_prerotated(*dec, 2, 30, 8, 256, 64, 8, 4, 1, 0, 1, 0, 0.0625, None) == 1   # heads % KV heads
+    assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 1, 0, 1, 3, 0.0625, None) == 1   # no such stage
+    assert lib.tq_decode_splitk_prerotated(*dec, 0, 32, 8, 256, 64, 8, 4, 1, 0, 1, 0, 0.0625, None) == 0   # empty batch
+    nullq = [None, None, p, p, p, p, p, p, p, p, p, 0, 2]
+    assert lib.tq_decode_splitk_prerotated(*nullq, 2, 32, 8, 256, 64, 8, 4, 1, 0, 1, 0, 0.0625, None) == 1
+    nosign = [None, p, p, p, p, p, p, None, p, p, p, 0, 2]   # un-rotation asked for without the sign diagonal
+    assert lib.tq_decode_splitk_prerotated(*nosign, 2, 32, 8, 256, 64, 8, 4, 1, 0, 1, 1, 0.0625, None) == 1

@@ -31,7 +31,7 @@ def gpu_import(cuda, key, value, scales, H, S, P, gain):
 
 
 def gpu_decode(cuda, q_rot, kc, vc, sc, table, lengths, Hq, H, S, P, splits, softmax_scale, code_grid=1,
-               out_dtype="f32"):
+               out_dtype="f32", pi_signs=None, gate=None, stage=0):
     import torch
     import ascend_micro_harness_b200 as tq
     B = q_rot.shape[0]
@@ -45,7 +45,8 @@ def gpu_decode(cuda, q_rot, kc, vc, sc, table, lengths, Hq, H, S, P, splits, sof
                                 num_heads=Hq, num_kv_heads=H, head_size=256, block_size=S, num_blocks=P,
                                 softmax_scale=softmax_scale, splits=splits,
                                 max_context_hint=int(lengths.max()), workspace=ws, code_grid=code_grid,
-                                status=st)
+                                pi_signs=None if pi_signs is None else dev(cuda, pi_signs),
+                                gate=gate, output_stage=stage, status=st)
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     return out.float().cpu().numpy()
@@ -183,3 +184,23 @@ def test_prerotated_decode_against_a_numpy_reference(cuda, d, grid):
     assert int(st.item()) == 0
     got = out.cpu().numpy()
     assert (np.abs(got - want) <= ABS_TOL + REL_TOL * np.abs(want)).all()
+
+
+@pytest.mark.parametrize("stage", [1, 2])
+def test_reference_fixture_unrotated_and_gated(cuda, stage):
+    """Output stages 1 and 2 of the fused decoder's raw-query entry on its own fixture: the context
+    rotated back by Pi, then gated by the fixture's FP16 gate logits (Fixture::expected_row)."""
+    import torch
+    g = np.load(os.path.join(GOLD, "fused_kv4_s64.npz"))
+    n, b, h, grp, S, pages, physical = [int(v) for v in g["dims"]]
+    kc, vc, sc = gpu_import(cuda, g["key"], g["value"], g["scale_bits"].view(np.float32), h, S, physical,
+                            float(g["gain"]))
+    q = g["query"].reshape(b, h * grp, 256)
+    gate = torch.from_numpy(g["gate_f16_bits"].view(np.int16)).to(cuda).view(torch.float16)
+    got = gpu_decode(cuda, q, kc, vc, sc, g["table"], g["lengths"], h * grp, h, S, physical, 2, 0.0625,
+                     pi_signs=g["pi_signs"], gate=gate if stage == 2 else None, stage=stage)
+    want = (g["expected_unrotated"] if stage == 1 else g["expected_gated"]).reshape(got.shape)
+    # the rotated rows hold values of 1..15; Pi mixes 256 of them, so the error bound of a row is
+    # carried through the rotation: sqrt(256) / 16 = 1 times the per-element bound of the largest
+    bound = ABS_TOL + REL_TOL * 15.0
+    assert (np.abs(got - want) <= bound).all()

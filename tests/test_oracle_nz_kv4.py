@@ -78,3 +78,23 @@ def test_import_moves_every_code_and_scale(oracle, H, S):
             assert got[p, head, row, ch] == (nib - 16 if nib > 7 else nib)
             want = scales[(p * S + row) * slot_floats + plane * H + head] / gain
             assert sc[((plane * P + p) * H + head) * S + row] == want
+
+
+def test_pi_of_the_fused_decoder(oracle):
+    """Pi = diag(s) H diag(s) / 16 is an involution and turns the fixture's rotated-basis rows into
+    its un-rotated rows (golden vectors from RawQueryBasis::apply / Fixture::expected_row)."""
+    g = np.load(os.path.join(GOLD, "fused_kv4_s64.npz"))
+    s = g["pi_signs"]
+    rows = g["expected"].reshape(-1, 256)
+    un = oracle.signed_hadamard(rows, s)
+    assert np.array_equal(un, g["expected_unrotated"])
+    back = oracle.signed_hadamard(un, s)
+    assert np.abs(back - rows).max() <= 1e-5 * np.abs(rows).max()
+
+
+def test_pi_against_the_live_reference(oracle, reference):
+    rng = np.random.default_rng(12)
+    s = reference.fused_signs()
+    for _ in range(5):
+        x = rng.standard_normal(256).astype(np.float32)
+        assert np.array_equal(oracle.signed_hadamard(x[None], s)[0], reference.fused_pi_apply(x))
