@@ -30,6 +30,7 @@ SIGNATURES = {
                                        u32, u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
     "tq_decode_splitk_prerotated": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                               u32, u32, u32, u32, u32, u32, u32, u32, u32, f32, vp]),
+    "tq_rotate_query_pi": (C.c_int, [vp, vp, u32, vp, vp, u32, u32]),
     "tq_nz_kv4_import": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, f32]),
     "tq_decode_splitk_static": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32,
                                           u32, u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),

@@ -124,6 +124,48 @@ __global__ void __launch_bounds__(128) tq_rotate_query_kernel(const uint16_t* __
         q_rot[static_cast<size_t>(row) * D + lane * K + i] = f32_to_bf16_bits(v[i] * inv_sqrt_len);
 }
 
+// q_rot = Pi q with Pi = diag(s) H diag(s) / sqrt(D), FP32 out: the query prologue of the fused
+// decoder's raw-query entry (tests/common/fused_decode_opt_fixture.hpp:104-117,:166-182). One
+// warp per row, lane l holds channels l*K .. l*K+K-1: strides below K are register
+// butterflies, the others exchange whole registers between lanes.
+template <int D>
+__global__ void __launch_bounds__(128) tq_rotate_query_pi_kernel(const uint16_t* __restrict__ q,
+                                                                 uint32_t is_bf16,
+                                                                 const float* __restrict__ signs,
+                                                                 float* __restrict__ q_rot, uint32_t rows,
+                                                                 float inv_sqrt_len)
+{
+    constexpr int K = D / 32;
+    const int lane = threadIdx.x & 31;
+    const uint32_t row = blockIdx.x * 4u + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float sgn[K], v[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) {
+        sgn[i] = signs[lane * K + i] < 0.0f ? -1.0f : 1.0f;
+        const uint16_t bits = q[static_cast<size_t>(row) * D + lane * K + i];
+        v[i] = (is_bf16 ? bf16_bits_to_f32(bits) : __half2float(__ushort_as_half(bits))) * sgn[i];
+    }
+#pragma unroll
+    for (int s = 1; s < K; s <<= 1)
+#pragma unroll
+        for (int i = 0; i < K; ++i)
+            if ((i & s) == 0) {
+                const float a = v[i], b = v[i + s];
+                v[i] = a + b;
+                v[i + s] = a - b;
+            }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1)
+#pragma unroll
+        for (int i = 0; i < K; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], o);
+            v[i] = (lane & o) ? other - v[i] : v[i] + other;
+        }
+#pragma unroll
+    for (int i = 0; i < K; ++i) q_rot[static_cast<size_t>(row) * D + lane * K + i] = v[i] * sgn[i] * inv_sqrt_len;
+}
+
 }  // namespace tq
 
 // Q_rot = Q Pi^T for `rows` bf16 query vectors, rounded to bf16: the operand the decoders pin
@@ -182,5 +224,26 @@ extern "C" int tq_icdf_quantize(void* stream, const uint16_t* x, uint32_t in_dty
     if (blocks > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
     tq::tq_icdf_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         x, in_dtype == TQ_DTYPE_BF16 ? 1u : 0u, reinterpret_cast<uint32_t*>(packed), groups);
+    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
+
+// Pi q for `rows` FP16 or BF16 query vectors, FP32 out: the rotated image
+// tq_decode_splitk_prerotated takes, with Pi = diag(pi_signs) H diag(pi_signs) / sqrt(head_size)
+// (the fused decoder's raw-query prologue, include/turboquant_fused_decode_opt.hpp:160-169).
+extern "C" int tq_rotate_query_pi(void* stream, const uint16_t* query, uint32_t elem_dtype,
+                                  const float* pi_signs, float* query_rot, uint32_t rows,
+                                  uint32_t head_size)
+{
+    if ((head_size != 128 && head_size != 256) || (elem_dtype != TQ_DTYPE_BF16 && elem_dtype != TQ_DTYPE_F16))
+        return TQ_ERR_INVALID_ARGUMENT;
+    if (rows == 0) return TQ_OK;
+    if (!query || !pi_signs || !query_rot) return TQ_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const unsigned blocks = (rows + 3u) / 4u;
+    const uint32_t bf = elem_dtype == TQ_DTYPE_BF16 ? 1u : 0u;
+    if (head_size == 128)
+        tq::tq_rotate_query_pi_kernel<128><<<blocks, 128, 0, s>>>(query, bf, pi_signs, query_rot, rows, 0.08838834764831845f);
+    else
+        tq::tq_rotate_query_pi_kernel<256><<<blocks, 128, 0, s>>>(query, bf, pi_signs, query_rot, rows, 0.0625f);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }

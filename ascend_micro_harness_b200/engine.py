@@ -164,6 +164,14 @@ def nz_kv4_import(nz_key, nz_value, nz_scales, key_cache, value_cache, scale_cac
                                 block_size, num_blocks, gain), "tq_nz_kv4_import")
 
 
+def rotate_query_pi(query, pi_signs, query_rot, *, head_size, stream=None):
+    """query_rot (float32) = Pi query for float16/bfloat16 rows, Pi = diag(s) H diag(s) / sqrt(d): the
+    raw-query prologue of the fused decoder, feeding decode_splitk_prerotated."""
+    lib = load_library()
+    _check(lib.tq_rotate_query_pi(_stream(stream), _ptr(query), _out_dtype(query), _ptr(pi_signs),
+                                  _ptr(query_rot), query.numel() // head_size, head_size), "tq_rotate_query_pi")
+
+
 def decode_splitk_prerotated(query_rot, key_cache, value_cache, scale_cache, block_tables, context_lens,
                              output, *, num_heads, num_kv_heads, head_size, block_size, num_blocks,
                              softmax_scale=1.0, splits=0, max_context_hint=0, workspace=None,

@@ -309,6 +309,13 @@ int tq_decode_splitk_prerotated(void* stream, const float* query_rot, const int8
                                 uint32_t splits, uint32_t max_context_hint, uint32_t code_grid,
                                 uint32_t output_stage, float softmax_scale, uint32_t* status);
 
+/* Pi q for `rows` FP16 or BF16 (elem_dtype) query vectors of head_size 128 or 256, FP32 out: the
+ * rotated image tq_decode_splitk_prerotated takes, Pi = diag(pi_signs) H diag(pi_signs) /
+ * sqrt(head_size) -- the prologue of the fused decoder's raw-query entry
+ * (include/turboquant_fused_decode_opt.hpp:160-169; tests/common/fused_decode_opt_fixture.hpp:104-117). */
+int tq_rotate_query_pi(void* stream, const uint16_t* query, uint32_t elem_dtype, const float* pi_signs,
+                       float* query_rot, uint32_t rows, uint32_t head_size);
+
 /* ------------------------------------------------------- stand-alone routines
  * The reference's single-purpose routines that its cache operators do not call. */
 

@@ -459,6 +459,11 @@ class RefFusedFixture:
         self.ref.lib.ref_fused_expected_row(self.h, C.c_size_t(row), C.c_uint(stage), _p(out))
         return out
 
+    def raw_query_f16_bits(self):
+        out = np.zeros(self.requests * self.kv_heads * self.group_heads * 256, np.uint16)
+        self.ref.lib.ref_fused_raw_query_bits(self.h, _p(out))
+        return out
+
     def gate_f16_bits(self):
         out = np.zeros(self.requests * self.kv_heads * self.group_heads * 256, np.uint16)
         self.ref.lib.ref_fused_gate_bits(self.h, _p(out))

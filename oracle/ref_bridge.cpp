@@ -359,6 +359,13 @@ void ref_fused_expected_row(void* p, std::size_t row, unsigned stage, float* out
     const auto r = f.expected_row(basis, row, stage);
     std::memcpy(out, r.data(), r.size() * sizeof(float));
 }
+void ref_fused_raw_query_bits(void* p, std::uint16_t* out)
+{
+    const auto& f = *static_cast<fused_decode_opt_test::Fixture*>(p);
+    const fused_decode_opt_test::RawQueryBasis basis;
+    const auto q = f.raw_query(basis);
+    std::memcpy(out, q.data(), q.size() * 2);
+}
 void ref_fused_gate_bits(void* p, std::uint16_t* out)
 {
     const auto& f = *static_cast<fused_decode_opt_test::Fixture*>(p);

@@ -93,7 +93,7 @@ def main():
                             lengths=fx.get("lengths")[:b], expected=fx.get("expected"),
                             dims=np.array([n, b, h, g, S, fx.pages, fx.physical_pages]),
                             gain=np.float32(r.kv4_gain()), pi_signs=r.fused_signs(),
-                            gate_f16_bits=fx.gate_f16_bits(),
+                            gate_f16_bits=fx.gate_f16_bits(), raw_query_f16_bits=fx.raw_query_f16_bits(),
                             expected_unrotated=np.stack([fx.expected_row(i, 1) for i in range(b * h * g)]),
                             expected_gated=np.stack([fx.expected_row(i, 2) for i in range(b * h * g)]),
                             nz_bytes=np.array([[slot, head, col, H, r.nz_tiled_packed_byte(slot, head, col, H)]

@@ -204,3 +204,16 @@ def test_reference_fixture_unrotated_and_gated(cuda, stage):
     # carried through the rotation: sqrt(256) / 16 = 1 times the per-element bound of the largest
     bound = ABS_TOL + REL_TOL * 15.0
     assert (np.abs(got - want) <= bound).all()
+
+
+def test_raw_query_rotation_reproduces_the_fixture_query(cuda):
+    """Pi(raw query) is the fixture's pre-rotated FP32 query bit for bit (its entries are small
+    dyadic numbers, exact in any summation order)."""
+    import torch
+    import ascend_micro_harness_b200 as tq
+    g = np.load(os.path.join(GOLD, "fused_kv4_s64.npz"))
+    raw = torch.from_numpy(g["raw_query_f16_bits"].view(np.int16)).to(cuda).view(torch.float16)
+    rot = torch.zeros(raw.numel(), dtype=torch.float32, device=cuda)
+    tq.rotate_query_pi(raw, dev(cuda, g["pi_signs"]), rot, head_size=256)
+    torch.cuda.synchronize()
+    assert np.array_equal(rot.cpu().numpy(), g["query"])
