@@ -138,3 +138,6 @@ def test_kv4_import_and_prerotated_decode_refuse_bad_arguments_on_the_host():
     assert lib.tq_decode_splitk_prerotated(*nullq, 2, 32, 8, 256, 64, 8, 4, 1, 0, 1, 0, 0.0625, None) == 1
     nosign = [None, p, p, p, p, p, p, None, p, p, p, 0, 2]   # un-rotation asked for without the sign diagonal
     assert lib.tq_decode_splitk_prerotated(*nosign, 2, 32, 8, 256, 64, 8, 4, 1, 0, 1, 1, 0.0625, None) == 1
+    assert lib.tq_rotate_query_pi(None, p, 2, p, p, 4, 256) == 1     # the raw query is 16-bit
+    assert lib.tq_rotate_query_pi(None, p, 1, p, p, 4, 64) == 1      # head size
+    assert lib.tq_rotate_query_pi(None, p, 1, p, p, 0, 256) == 0     # no rows
