@@ -24,6 +24,10 @@ SIGNATURES = {
                                      u32, u32, f32, vp]),
     "tq_decode_splitk": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                    u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
+    "tq_decode_splitk_precise": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
+                                           u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
+    "tq_decode_splitk_nz": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
+                                      u32, u32, u32, u32, u32, u32, u32, f32, f32, f32, u32, vp]),
     "tq_decode_splitk_elem": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                         u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
     "tq_decode_splitk_mtp": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
@@ -56,6 +60,8 @@ SIGNATURES = {
     "launch_turboquant_reshape_and_cache_bf16": (None, None),
     "launch_turboquant_reshape_scatter_aiv": (None, None),
     "launch_turboquant_paged_decode_splitk_aic": (None, None),
+    "launch_fused_decode_opt": (None, None),
+    "launch_fused_decode_opt_raw_query": (None, None),
 }
 
 

@@ -61,18 +61,35 @@ def build_acl_shim(force: bool = False) -> str:
     return ACL_LIB
 
 
-# The reference's own device validation programs, compiled from where they lie in a
-# checkout of the reference against this library and the ACL shim. Outputs go to
-# oracle/_ref/ only; nothing of the reference is copied into this tree.
+# The reference's own device programs -- validation ladders, integration tests and benchmarks
+# -- compiled from where they lie in a checkout of the reference against this library and the
+# ACL shim. Outputs go to oracle/_ref/ only; nothing of the reference is copied into this tree.
 REFERENCE_HARNESSES = [
     "tests/npu/validation/test_turboquant_a8_validation.cpp",
     "tests/npu/validation/test_turboquant_bf16_validation.cpp",
     "tests/npu/validation/test_turboquant_decode_splitk_aic_validation.cpp",
+    "tests/npu/validation/test_turboquant_fused_decode_opt_npu.cpp",
+    "tests/npu/bench/bench_turboquant_decode_splitk.cpp",
+    "tests/npu/bench/bench_turboquant_reshape_and_cache.cpp",
+    "kernels/ops/turboquant/vllm_integration_layer/tests/validation/test_integration_scatter.cpp",
+    "kernels/ops/turboquant/vllm_integration_layer/tests/validation/test_integration_batch.cpp",
+    "kernels/ops/turboquant/vllm_integration_layer/tests/benchmark/bench_integration_scatter.cpp",
 ]
 
 
-def build_reference_harness(ref_root: str = "/root/reference") -> list[str]:
-    if not os.path.exists(os.path.join(ref_root, REFERENCE_HARNESSES[0])):
+def reference_root() -> str | None:
+    """A checkout of fxslava/ascend-micro-harness: $TQ_REFERENCE_ROOT, else a directory named
+    `reference` beside this repository. None when neither holds the reference's sources."""
+    for cand in (os.environ.get("TQ_REFERENCE_ROOT"),
+                 os.path.join(PKG, "..", "..", "reference")):
+        if cand and os.path.exists(os.path.join(cand, REFERENCE_HARNESSES[0])):
+            return os.path.abspath(cand)
+    return None
+
+
+def build_reference_harness(ref_root: str | None = None) -> list[str]:
+    ref_root = ref_root or reference_root()
+    if ref_root is None:
         return []
     build()
     build_acl_shim()

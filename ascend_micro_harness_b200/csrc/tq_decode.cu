@@ -33,6 +33,7 @@
 //     normaliser of the value scales; the reference-contract entry carries it as a
 //     hi + lo pair (two MMAs). P^T reaches its B-fragment layout with movmatrix.
 #include <cuda_fp16.h>
+#include <atomic>
 #include <stdexcept>
 #include <type_traits>
 
@@ -65,6 +66,19 @@ struct DecodeParams {
     uint32_t midrise;         // 1: a code c stands for (c + 0.5) * scale (uniform mid-rise grid)
     float inv_sqrt_len, softmax_scale;
     uint32_t* status;
+    // NZ-tiled source pools (the fused decoder's KV4 cache read where it lies): floats per slot
+    // of the scale records and the codebook gain the stored scales are divided by
+    uint32_t nz_slot_floats;
+    float nz_gain;
+    // persistent grid with the combine folded in: arrival counters (one word per (sequence, KV
+    // head, row tile)), the tag that tells this launch's counts from stale bytes, and what the
+    // egress needs (see CombineParams)
+    uint32_t* counters;
+    uint32_t tag;
+    const float* egress_signs;
+    const void* gate;
+    void* output;
+    uint32_t output_stage, out_dtype, gate_dtype, rotation;
 };
 
 // Shared-memory plan of one CTA. A key strip is stored in 16-byte chunks whose
@@ -93,16 +107,43 @@ struct DecodeSmem {
     static constexpr int kStripStage = 2 * kStripBytes + 2 * kStrip * 4;   // K, V, both scale runs
     static constexpr int kStageBytes = kTileStrips * kStripStage;
     static constexpr int kRingBytes = kDecWarps * kStages * kStageBytes;
-    static constexpr int kQBytes = 2 * 8 * D * 4;
+    // The fixed-point query of the prologue (8 rows, padded, see q_index) sits at the END of the
+    // ring, inside the last warp's last stage, which no copy targets before the main loop: the
+    // first tiles can be in flight while the query is rotated.
+    static constexpr int kQFixInts = 8 * (D + 16);
+    static constexpr int kQBytes = kQFixInts * 4;
     static constexpr int kMergePitch = D + 4;   // floats per merged row: {m, l, acc[d]} + pad, see the epilogue
     static constexpr int kMergeBytes = kDecWarps * 8 * kMergePitch * 4;
-    static constexpr int kBody = kRingBytes > kQBytes ? (kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes)
-                                                      : (kQBytes > kMergeBytes ? kQBytes : kMergeBytes);
+    // after the merge area (persistent grid only): the segment's combined record, then the two
+    // buffers of the egress butterfly
+    static constexpr int kRecPitch = D + 2;     // {m, l, acc[d]}
+    static constexpr int kRecBytes = 8 * kRecPitch * 4;
+    static constexpr int kEgressBytes = 2 * 8 * D * 4;
+    static constexpr int kTailBytes = kMergeBytes + kRecBytes + kEgressBytes;
+    static_assert(kTailBytes <= kRingBytes, "the epilogue buffers alias the ring");
+    static_assert(kQBytes <= kRingBytes, "the prologue buffer aliases the ring");
+    static constexpr int kBody = kRingBytes;
     static constexpr int kTotal = kBody + kQFragBytes;
+    // warps whose first stage stays clear of the fixed-point query may start copying before it
+    __host__ __device__ static constexpr bool early_issue(int warp)
+    {
+        return (warp * kStages + 1) * kStageBytes <= kRingBytes - kQBytes;
+    }
     // 16-byte chunk `c` of token row `row` lands at this chunk index of the strip.
     __host__ __device__ static constexpr int key_chunk(int row, int c)
     {
         return D == 128 ? ((row * 4 + c) ^ (((row >> 2) & 1) << 2)) : ((row * 8 + c) ^ ((row >> 2) & 1));
+    }
+    // NZ-tiled source: a strip is staged as [32-byte column group][row slot][32 bytes]. Token t
+    // = 8a + 4c + 2b + e goes to row slot (a e c b) of the key image and (e c a b) of the value
+    // image, so that the rows one shared-memory instruction touches are four consecutive slots.
+    __host__ __device__ static constexpr int nz_key_slot(int t)
+    {
+        return (t & 8) | ((t & 1) << 2) | ((t & 4) >> 1) | ((t & 2) >> 1);
+    }
+    __host__ __device__ static constexpr int nz_value_slot(int t)
+    {
+        return ((t & 1) << 3) | (t & 4) | ((t & 8) >> 2) | ((t & 2) >> 1);
     }
 };
 
@@ -118,6 +159,10 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p)
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gmem_src)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_dst), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async4(uint32_t smem_dst, const void* gmem_src)
+{
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_dst), "l"(gmem_src));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
@@ -214,13 +259,93 @@ __device__ __forceinline__ float2 unpack_f16x2(uint32_t v)
 __device__ __forceinline__ int token_row_lo(int i) { return ((i >> 2) << 3) + (((i >> 1) & 1) << 1) + ((i & 1) << 2); }
 __device__ __forceinline__ int token_row_hi(int i) { return token_row_lo(i) + 1; }
 
+// Element-wise end of a decode: the normalised context of up to 8 query rows of one
+// (sequence, KV head), in buf[0][row][channel], is rotated back (output stages 1 and 2),
+// gated (stage 2), narrowed and stored. 128 threads; thread c serves channels c, c + 128.
+// The butterfly stages and their order are those of tq_combine_kernel, so both routes give
+// the same bits for the same normalised context.
+template <int D>
+__device__ __forceinline__ void egress_rows(const DecodeParams& p, float* buf, int rows_here, uint32_t seq,
+                                            uint32_t head, uint32_t row_tile, uint32_t tokens_per_req, int tid)
+{
+    constexpr int CPT = D / 128;   // channels per thread
+    int cur = 0;
+    auto at = [&](int b, int q, int c) -> float& { return buf[(b * 8 + q) * D + c]; };
+    if (p.output_stage != TQ_OUT_ROTATED) {
+        if (p.rotation == 2u) {
+            for (int q = 0; q < rows_here; ++q)
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) at(0, q, tid + 128 * j) *= p.egress_signs[tid + 128 * j];
+            __syncthreads();
+        }
+        auto stage = [&](int s) {
+            for (int q = 0; q < rows_here; ++q)
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) {
+                    const int c = tid + 128 * j;
+                    const float mine = at(cur, q, c), other = at(cur, q, c ^ s);
+                    at(cur ^ 1, q, c) = other + ((c & s) ? -mine : mine);
+                }
+            __syncthreads();
+            cur ^= 1;
+        };
+        if (p.rotation == 1u) {
+            for (int s = 1; s < 16; s <<= 1) stage(s);
+        } else if (p.rotation == 2u) {
+            for (int s = 1; s < D; s <<= 1) stage(s);
+        } else {
+            for (int s = kGroup; s < D; s <<= 1) stage(s);
+            for (int q = 0; q < rows_here; ++q)
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) at(cur, q, tid + 128 * j) *= p.egress_signs[tid + 128 * j];
+            __syncthreads();
+            for (int s = 1; s < kGroup; s <<= 1) stage(s);
+        }
+    }
+    const uint32_t grp = p.rows / tokens_per_req;
+    for (int q = 0; q < rows_here; ++q) {
+        const uint32_t row = row_tile * 8u + q, o_tok = row / grp, o_g = row - o_tok * grp;
+        const size_t out_row = (static_cast<size_t>(seq) * tokens_per_req + o_tok) * (p.H * grp) +
+                               static_cast<size_t>(head) * grp + o_g;
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) {
+            const int c = tid + 128 * j;
+            float v = at(cur, q, c);
+            if (p.output_stage != TQ_OUT_ROTATED) {
+                v = p.rotation == 1u ? v * 0.25f
+                    : p.rotation == 2u ? v * p.egress_signs[c] * p.inv_sqrt_len : v * p.inv_sqrt_len;
+                if (p.output_stage == TQ_OUT_GATED) {
+                    const size_t gi = out_row * D + c;
+                    const float gt = p.gate_dtype == TQ_DTYPE_F32 ? static_cast<const float*>(p.gate)[gi]
+                                     : p.gate_dtype == TQ_DTYPE_F16
+                                         ? __half2float(static_cast<const __half*>(p.gate)[gi])
+                                         : bf16_bits_to_f32(static_cast<const uint16_t*>(p.gate)[gi]);
+                    v = v / (1.0f + __expf(-gt));
+                }
+            }
+            const size_t o = out_row * D + c;
+            if (p.out_dtype == TQ_DTYPE_F32) static_cast<float*>(p.output)[o] = v;
+            else if (p.out_dtype == TQ_DTYPE_F16) static_cast<__half*>(p.output)[o] = __float2half_rn(v);
+            else static_cast<uint16_t*>(p.output)[o] = f32_to_bf16_bits(v);
+        }
+    }
+}
+
 // EXT compiles in the extensions of the serving path -- f16 or pre-rotated FP32 query
 // elements, several query tokens per request, mid-rise codes -- so that the plain
-// instantiation carries neither their branches nor their registers.
-template <int D, bool PRECISE, bool EXT>
+// instantiation carries neither their branches nor their registers. NZ reads the packed planes
+// and scale records of the fused decoder's NZ-tiled KV4 cache in place (head size 256).
+// STREAMK is the persistent grid: the batch's tiles, flattened sequence by sequence and head
+// by head, are dealt to the CTAs in equal contiguous shares; a CTA walks the (sequence, KV
+// head) segments of its share, and the CTA that completes a head's last outstanding segment
+// merges the partial records and writes the output itself (one arrival count per head, no
+// waiting anywhere). Without STREAMK one CTA serves one (sequence, KV head, split).
+template <int D, bool PRECISE, bool EXT, bool NZ, bool STREAMK>
 __global__ void __launch_bounds__(kDecWarps * 32, DecodeSmem<D>::kCtasPerSm)
 tq_decode_partial_kernel(const DecodeParams p)
 {
+    static_assert(!NZ || D == 256, "the NZ-tiled cache has head size 256");
+    static_assert(!(STREAMK && PRECISE), "the persistent grid serves the native path");
     using L = DecodeSmem<D>;
     const uint32_t tokens_per_req = EXT ? p.tokens_per_req : 1u;
     const bool q_f16 = EXT && p.q_f16 != 0u;
@@ -232,278 +357,77 @@ tq_decode_partial_kernel(const DecodeParams p)
     constexpr int MT = D / 16;    // 16-channel m-tiles of the value contraction
     constexpr int WPT = D / 32;   // packed words per thread per key row
     extern __shared__ __align__(128) uint8_t smem[];
-    float* qbuf = reinterpret_cast<float*>(smem);            // [2][8][D], prologue only
-    uint8_t* ring = smem;                                    // aliases qbuf after the prologue
+    uint8_t* ring = smem;
+    int* qfix = reinterpret_cast<int*>(smem + L::kRingBytes - L::kQBytes);   // prologue only
     __shared__ float row_unscale[8];                         // per query row: 2^-k * softmax_scale * log2e
-    __shared__ int row_qsum8[8];                             // mid-rise codes: 8 * sum of the row's fixed-point query
+    __shared__ int row_qsum8[8];                             // mid-rise codes: sum of the row's fixed-point query (enters a score times 8)
+    __shared__ uint32_t sk_scan[2 * kDecWarps];              // persistent grid: warp totals / maxima of the tile scan
+    __shared__ uint32_t sk_start[3];                         // first sequence of the share, tiles before it (lo, hi)
+    __shared__ uint32_t sk_last;                             // this CTA completed the head's last segment
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, qd = lane & 3;
 
     const uint32_t row_tiles = (p.rows + 7u) / 8u;
-    uint32_t lin = blockIdx.x;
-    const uint32_t split = lin % p.splits;
-    lin /= p.splits;
-    const uint32_t row_tile = lin % row_tiles;
-    const uint32_t item = lin / row_tiles;
-    const uint32_t seq = item / p.H, head = item % p.H;
-    const int rows_here = min(8u, p.rows - row_tile * 8u);
-
-    // ---- this CTA's strip range
     const uint32_t SP = p.S / kStrip;  // strips per page
-    uint32_t ctx, page_count;
-    if (p.context_lens != nullptr) {
+
+    // live context of a sequence, clamped to what its block-table row can address
+    auto context_of = [&](uint32_t seq) -> uint32_t {
         const int32_t c = p.context_lens[seq];
-        ctx = c > 0 ? static_cast<uint32_t>(c) : 0u;
+        uint32_t ctx = c > 0 ? static_cast<uint32_t>(c) : 0u;
         const uint32_t cap = p.table_stride * p.S;
         if (ctx > cap) {
             ctx = cap;
             if (tid == 0) report(p.status, TQ_STATUS_BAD_PAGE);
         }
-        page_count = (ctx + p.S - 1u) / p.S;
-    } else {
-        ctx = p.fixed_ctx;
-        page_count = p.page_count;
-    }
-    // Ragged batches: a sequence takes only as many of the launch's splits as it has
-    // chunks of chunk_pages pages, so CTAs carry similar amounts of work; the splits it
-    // does not use fall out of the partition as empty ranges and export the neutral element.
-    uint32_t eff_splits = p.splits;
-    if (p.chunk_pages != 0u) {
-        const uint32_t chunks = (page_count + p.chunk_pages - 1u) / p.chunk_pages;
-        eff_splits = chunks < 1u ? 1u : (chunks < p.splits ? chunks : p.splits);
-    }
-    const uint32_t width = (page_count + eff_splits - 1u) / eff_splits;
-    const uint32_t rb = split * width;
-    const uint32_t remaining = rb < page_count ? page_count - rb : 0u;
-    const uint32_t rc = remaining < width ? remaining : width;
-    uint32_t s0 = (p.page_begin + rb) * SP;
-    uint32_t s1 = s0 + rc * SP;
-    const uint32_t live_strips = (ctx + kStrip - 1u) / kStrip;
-    if (s1 > live_strips) s1 = live_strips;
-    // A split whose page range is empty takes no part at all; one whose pages all
-    // lie past the live tokens still rotates and publishes its query (the rotation
-    // does not depend on the cache) and then exports the neutral element
-    // (kernels/ops/turboquant/turboquant_paged_decode_attention.cpp:1626-1637).
-    const bool no_pages = rc == 0u;
-    const bool empty = s1 <= s0;
+        return ctx;
+    };
+    auto tiles_of = [&](uint32_t ctx) -> uint32_t {
+        return ((ctx + kStrip - 1u) / kStrip + kTileStrips - 1u) / kTileStrips;
+    };
 
-    float* rec_base = p.workspace +
-                      ((static_cast<size_t>(item) * p.splits + split) * p.rows_stride + row_tile * 8u) *
-                          kRecord;
-
-    if (empty) {
-        for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
-            const int c = i % kRecord;
-            rec_base[i] = c < 8 ? kMaskedScore : 0.0f;
-        }
-        if (no_pages || p.q_rot == nullptr) return;
-    }
-
-    // ---- rotate the query rows once: each warp takes two rows through the FP32
-    // ingress cascade, scales, rounds to bf16 (the pinned operand) and publishes it.
-    // The key contraction runs on the integer tensor path, so every row then becomes
-    // fixed point: its entries times the power of two that puts the largest below
-    // 2^(8 NL - 1), rounded to an integer of NL 8-bit limbs (NL = 2: 2^-16 of the row
-    // maximum, far inside the tolerance of the native path; NL = 3: 2^-24, FP32 grade,
-    // for the entry point that is checked against the reference's partial records).
-    // The inverse power goes into the per-row score factor together with
-    // softmax_scale * log2(e) and the 1/16 of the key operand (see compute_tile).
-    constexpr int NL = PRECISE ? 3 : 2;
-    int* qfix = reinterpret_cast<int*>(qbuf);
-    // A lane later reads the eight integers of its key word's channels, lanes (r, qd) at
-    // channel qd * d/4 + ...: rows are padded by 16 and quarters of a row by 4 words so that
-    // the eight lanes one 128-bit access serves together fall into eight different bank groups.
-    auto q_index = [](int row, int ch) { return row * (D + 16) + (ch / (D / 4)) * (D / 4 + 4) + ch % (D / 4); };
-    {
-        constexpr int K = D / 32;
-        float sgn[K];
-#pragma unroll
-        for (int i = 0; i < K; ++i)
-            sgn[i] = !prerot && sign_is_negative(p.signs, p.sign_source, lane * K + i) ? -1.0f : 1.0f;
-        for (int row = warp * 2; row < warp * 2 + 2; ++row) {
-            float v[K];
-#pragma unroll
-            for (int i = 0; i < K; ++i) v[i] = 0.f;
-            if (row < rows_here) {
-                // row = token * G + g of the request's (1 + speculative) query tokens; with one
-                // token per request this is (item * rows + row)
-                const uint32_t row_g = row_tile * 8u + row, grp = p.rows / tokens_per_req;
-                const uint32_t q_tok = row_g / grp, q_g = row_g - q_tok * grp;
-                const size_t qoff = ((static_cast<size_t>(seq) * tokens_per_req + q_tok) * (p.H * grp) +
-                                     static_cast<size_t>(head) * grp + q_g) * D + lane * K;
-                const uint16_t* qsrc = p.q + qoff;
-#pragma unroll
-                for (int i = 0; i < K; ++i)
-                    v[i] = prerot ? p.q_f32[qoff + i]
-                                  : q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
-            }
-            if (!prerot) cascade_ingress<K>(v, sgn, lane);
-            float am = 0.f;
-#pragma unroll
-            for (int i = 0; i < K; ++i) {
-                float val = prerot ? v[i] : v[i] * p.inv_sqrt_len;
-                if (!q_f16 && !prerot) {   // the bf16 operand the reference pins (and publishes)
-                    const uint16_t bits = f32_to_bf16_bits(val);
-                    val = bf16_bits_to_f32(bits);
-                    if (p.q_rot != nullptr && row < rows_here)
-                        p.q_rot[((static_cast<size_t>(item) * p.splits + split) * p.rows_stride +
-                                 row_tile * 8u + row) * D + lane * K + i] = bits;
-                }
-                v[i] = val;
-                am = fmaxf(am, fabsf(val));
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-            // 2^(top - e) and 2^(e - top) from the exponent field of the row maximum,
-            // top = 8 NL - 2; a row below 1e-25 scores as zero
-            constexpr int kTop = 8 * NL - 2;
-            const bool tiny = !(am >= 1.0e-25f);
-            const int e_bits = __float_as_int(am) & 0x7F800000;
-            const float up = tiny ? 0.0f : __int_as_float(((254 + kTop) << 23) - e_bits);
-            const float down = tiny ? 1.0f : __int_as_float(e_bits - (kTop << 23));
-            int qsum = 0;
-#pragma unroll
-            for (int i = 0; i < K; ++i) {
-                const int fx = __float2int_rn(v[i] * up);
-                qfix[q_index(row, lane * K + i)] = fx;
-                qsum += fx;
-            }
-            if (midrise) {
-                // sum_c q_c (16 code_c + 8): the half step of every code adds 8 * sum_c q_c to a raw score
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
-                if (lane == 0) row_qsum8[row] = 8 * qsum;
-            }
-            if (lane == 0) row_unscale[row] = down * 0.0625f * p.softmax_scale * kLog2e;
-        }
-    }
-    if (empty) return;
-    __syncthreads();
-
-    // ---- limbs of q_rot^T as B fragments of the integer MMA. Word wi of a key row holds
-    // channels qd*(D/4) + wi*8 + n, n = 0..7: the even n feed contraction slots qd*4 + n/2
-    // (b0), the odd n slots 16 + qd*4 + n/2 (b1).
-    uint32_t bq[L::kQFragSmem ? 1 : NL][L::kQFragSmem ? 1 : WPT][2];
-    // [wi][limb][lane] pairs of registers; every warp holds the same fragments, warp 0 writes them
-    uint2* qfrag = reinterpret_cast<uint2*>(smem + L::kBody) + lane;
-#pragma unroll
-    for (int wi = 0; wi < WPT; ++wi) {
-        const int* qr = qfix + q_index(r, qd * (D / 4) + wi * 8);
-        int qv[8];
-#pragma unroll
-        for (int n = 0; n < 8; ++n) qv[n] = qr[n];
-#pragma unroll
-        for (int l = 0; l < NL; ++l)
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                // byte e of the word = limb l of channel 2e + h: three byte permutes
-                const uint32_t pick = static_cast<uint32_t>(l) | (static_cast<uint32_t>(4 + l) << 4);
-                const uint32_t lo = __byte_perm(qv[h], qv[2 + h], pick);
-                const uint32_t hi = __byte_perm(qv[4 + h], qv[6 + h], pick);
-                const uint32_t frag = __byte_perm(lo, hi, 0x5410u);
-                if constexpr (L::kQFragSmem) {
-                    if (warp == 0) reinterpret_cast<uint32_t*>(qfrag + (wi * NL + l) * 32)[h] = frag;
-                } else {
-                    bq[l][wi][h] = frag;
-                }
-            }
-    }
-    // scores are kept as raw * key_scale; the per-row factor enters inside the exponent
-    const float rfac[2] = {row_unscale[qd * 2], row_unscale[qd * 2 + 1]};
-    const int qs8[2] = {midrise ? row_qsum8[qd * 2] : 0, midrise ? row_qsum8[qd * 2 + 1] : 0};
-    float ps[2] = {0.f, 0.f};   // mid-rise codes: running sum of P (as the value contraction sees it) per row
-    __syncthreads();  // everyone is done with qbuf: the ring may overwrite it
-
-    // ---- per-warp pipeline over tiles warp, warp+4, ...
-    const uint32_t tiles = (s1 - s0 + kTileStrips - 1u) / kTileStrips;
-    const uint32_t my_tiles = tiles > static_cast<uint32_t>(warp)
-                                  ? (tiles - warp + kDecWarps - 1u) / kDecWarps : 0u;
-    const int32_t* table_row = p.table + static_cast<size_t>(seq) * p.table_stride;
-    uint8_t* my_ring = ring + warp * kStages * L::kStageBytes;
-    const uint32_t my_ring_s = smem_u32(my_ring);
+    // ---- everything below that does not depend on the segment
     const size_t head_block = static_cast<size_t>(p.S) * D / 2;  // bytes of one (page, head)
     const size_t scale_plane = static_cast<size_t>(p.P) * p.H * p.S;
     const uint32_t sp_shift = p.sp_shift;                        // strips per page = 1 << sp_shift
     constexpr uint32_t kTileStep = kDecWarps * kTileStrips;      // strips between a warp's tiles
-
-    // Block-table entries of the tile whose first strip is `strip` (-1 past the range).
-    auto load_pages = [&](uint32_t strip, int32_t (&pg)[kTileStrips]) {
-#pragma unroll
-        for (int ts = 0; ts < kTileStrips; ++ts)
-            pg[ts] = strip + ts < s1 ? __ldg(table_row + ((strip + ts) >> sp_shift)) : -1;
-    };
+    uint8_t* my_ring = ring + warp * kStages * L::kStageBytes;
+    const uint32_t my_ring_s = smem_u32(my_ring);
     // Per-lane copy plan, fixed for the whole kernel: lane l moves 16-byte chunks
     // l, l+32, ... of the key strip (to their swizzled places) and of the value strip,
-    // lanes 0..7 the two 64-byte scale runs.
+    // lanes 0..7 the two 64-byte scale runs. NZ-tiled source: chunk i*32 + l is half l&1 of
+    // token row l>>1 of column group i, 512 contiguous source bytes per group; every lane
+    // copies one scale (lanes 0..15 the key scales, 16..31 the value scales of its token).
     constexpr int kChunksPerLane = L::kStripBytes / 16 / 32;     // 2 (d=128) or 4 (d=256)
     constexpr int kChunksPerRow = L::kRowBytes / 16;
     uint32_t kdst[kChunksPerLane];
+    [[maybe_unused]] uint32_t vdst_nz = 0;
 #pragma unroll
     for (int i = 0; i < kChunksPerLane; ++i) {
         const int c = i * 32 + lane;
-        kdst[i] = L::key_chunk(c / kChunksPerRow, c % kChunksPerRow) * 16;
+        if constexpr (NZ) kdst[i] = i * 512 + L::nz_key_slot(lane >> 1) * 32 + (lane & 1) * 16;
+        else kdst[i] = L::key_chunk(c / kChunksPerRow, c % kChunksPerRow) * 16;
     }
-    const uint8_t* ksrc0 = p.key_cache + head * head_block + lane * 16;
-    const uint8_t* vsrc0 = p.value_cache + head * head_block + lane * 16;
-    const float* ssrc0 = p.scale_cache + (lane >> 2) * scale_plane + static_cast<size_t>(head) * p.S + (lane & 3) * 4;
+    if constexpr (NZ) vdst_nz = L::kStripBytes + L::nz_value_slot(lane >> 1) * 32 + (lane & 1) * 16;
     // strides fit 32 bits (one page of one cache), so a page's offset is one widening
     // multiply-add on the lane's base pointer
     const uint32_t page_stride = p.H * static_cast<uint32_t>(head_block);
     const uint32_t page_stride_scale = p.H * p.S;
     const uint32_t sip_mask = (1u << sp_shift) - 1u;
-    auto issue = [&](uint32_t strip, uint32_t stage, const int32_t (&pg)[kTileStrips]) {
-#pragma unroll
-        for (int ts = 0; ts < kTileStrips; ++ts) {
-            if (pg[ts] < 0) continue;   // warp-uniform
-            uint32_t page = static_cast<uint32_t>(pg[ts]);
-            if (page >= p.P) {
-                if (lane == 0) report(p.status, TQ_STATUS_BAD_PAGE);
-                page = 0;
-            }
-            const uint32_t sip = (strip + ts) & sip_mask;
-            const uint8_t* ksrc = ksrc0 + static_cast<size_t>(page) * page_stride + sip * L::kStripBytes;
-            const uint8_t* vsrc = vsrc0 + static_cast<size_t>(page) * page_stride + sip * L::kStripBytes;
-            const uint32_t dst = my_ring_s + stage * L::kStageBytes + ts * L::kStripStage;
-#pragma unroll
-            for (int i = 0; i < kChunksPerLane; ++i) {
-                cp_async16(dst + kdst[i], ksrc + i * 512);
-                cp_async16(dst + L::kStripBytes + i * 512 + lane * 16, vsrc + i * 512);
-            }
-            if (lane < 8)
-                cp_async16(dst + 2 * L::kStripBytes + lane * 16,
-                           ssrc0 + static_cast<size_t>(page) * page_stride_scale + sip * kStrip);
-        }
-    };
-
-    // Online-softmax state for query rows qd*2 and qd*2+1, in units of raw * key_scale.
-    float m_run[2] = {kMaskedScore, kMaskedScore}, l_run[2] = {0.f, 0.f};
-    float m_fac[2] = {0.f, 0.f};   // m_run * rfac, the exponent offset (0 while m_run is the sentinel)
-    float acc[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
-    // Running power-of-two normaliser of the value scales: P is carried in f16, so
-    // it is kept in [0, 1] by dividing the value scale by the largest seen so far.
-    float vnorm = 0.f, inv_vnorm = 0.f;
-
-    const uint32_t strip_first = s0 + warp * kTileStrips;   // first strip of this warp's tile 0
-    int32_t pg_next[kTileStrips];
-    for (uint32_t j = 0; j < kStages - 1; ++j) {
-        load_pages(strip_first + j * kTileStep, pg_next);
-        issue(strip_first + j * kTileStep, j, pg_next);
-        cp_async_commit();
-    }
-    load_pages(strip_first + (kStages - 1) * kTileStep, pg_next);
 
     const int tok_lo = token_row_lo(r), tok_hi = token_row_hi(r);
-    // this thread's chunks of its two key rows (d=128: one chunk each; d=256: two)
-    int koff_lo[WPT / 4], koff_hi[WPT / 4];
+    // this thread's chunks of its two key rows (d=128: one chunk each; d=256: two). NZ: the
+    // eight bytes qd*8.. of both rows in each of the four column groups.
+    int koff_lo[NZ ? 1 : WPT / 4], koff_hi[NZ ? 1 : WPT / 4];
+    if constexpr (NZ) {
+        koff_lo[0] = L::nz_key_slot(tok_lo) * 32 + qd * 8;
+        koff_hi[0] = L::nz_key_slot(tok_hi) * 32 + qd * 8;
+    } else {
 #pragma unroll
-    for (int w4 = 0; w4 < WPT / 4; ++w4) {
-        koff_lo[w4] = L::key_chunk(tok_lo, qd * (WPT / 4) + w4) * 16;
-        koff_hi[w4] = L::key_chunk(tok_hi, qd * (WPT / 4) + w4) * 16;
+        for (int w4 = 0; w4 < WPT / 4; ++w4) {
+            koff_lo[w4] = L::key_chunk(tok_lo, qd * (WPT / 4) + w4) * 16;
+            koff_hi[w4] = L::key_chunk(tok_hi, qd * (WPT / 4) + w4) * 16;
+        }
     }
     // byte-permute selector that brings this thread's value-token pairs to bits 0-7 / 16-23
     const uint32_t vsel = qd == 0 ? 0x3210u : qd == 1 ? 0x4321u : qd == 2 ? 0x7654u : 0x0765u;
@@ -513,6 +437,7 @@ tq_decode_partial_kernel(const DecodeParams p)
     // stays below 2^22 in magnitude (128 channels x |16 code| <= 128 x limb <= 255), so a chain
     // that starts at the bit pattern of 1.5 * 2^23 ends, read as a float, at 12582912 + sum
     // exactly and one FP32 subtract recovers it; d = 256 can exceed that range and converts.
+    constexpr int NL = PRECISE ? 3 : 2;
     constexpr bool kBiasedAcc = D == 128 && NL != 2;
     const int cinit[4] = {kBiasedAcc ? 0x4B400000 : 0, kBiasedAcc ? 0x4B400000 : 0,
                           kBiasedAcc ? 0x4B400000 : 0, kBiasedAcc ? 0x4B400000 : 0};
@@ -521,44 +446,419 @@ tq_decode_partial_kernel(const DecodeParams p)
         else return __int2float_rn(v);
     };
 
-    // Speculative tokens: query token t of a request sees the context without the last
-    // (tokens_per_req - 1 - t) tokens. row_drop[q] is that count for this thread's two rows.
-    uint32_t row_drop[2];
+    // ---- the share of this CTA (persistent grid): [w0, w0 + left) of the flattened tiles
+    uint32_t seq = 0, head = 0, row_tile = 0, split = 0;
+    uint32_t sk_n = 0, sk_loc = 0, sk_left = 0, sk_quota = 1;   // tiles of `seq`, position inside its block, tiles to go
+    unsigned long long sk_before = 0;                          // tiles (per head) of the sequences before `seq`
+    const uint32_t heads_per_seq = p.H * row_tiles;
+    if constexpr (STREAMK) {
+        const uint32_t batch = p.items / p.H;
+        const uint32_t per = (batch + blockDim.x - 1u) / blockDim.x;
+        const uint32_t b0 = min(batch, tid * per), b1 = min(batch, b0 + per);
+        uint32_t mine = 0, nmax = 0;
+        for (uint32_t b = b0; b < b1; ++b) {
+            const uint32_t n = tiles_of(context_of(b));
+            mine += n;
+            nmax = max(nmax, n);
+            if (n == 0u && blockIdx.x == 0u) {
+                // a sequence without live tokens has no tile and therefore no segment: its
+                // output rows are the zero context
+                const size_t base = static_cast<size_t>(b) * tokens_per_req * (p.H * (p.rows / tokens_per_req)) * D;
+                const size_t count = static_cast<size_t>(tokens_per_req) * (p.H * (p.rows / tokens_per_req)) * D;
+                for (size_t i = 0; i < count; ++i) {
+                    if (p.out_dtype == TQ_DTYPE_F32) static_cast<float*>(p.output)[base + i] = 0.f;
+                    else static_cast<uint16_t*>(p.output)[base + i] = 0;
+                }
+            }
+        }
+        // inclusive scan over the threads' slices (warp shuffles, then the four warp totals)
+        uint32_t incl = mine;
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
-        const uint32_t row_g = row_tile * 8u + qd * 2 + q, grp = p.rows / tokens_per_req;
-        const uint32_t t = min(row_g / grp, tokens_per_req - 1u);
-        row_drop[q] = tokens_per_req - 1u - t;
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, o));
+        if (lane == 31) {
+            sk_scan[warp] = incl;
+            sk_scan[kDecWarps + warp] = nmax;
+        }
+        if (tid == 0) sk_start[0] = 0xFFFFFFFFu;
+        __syncthreads();
+        unsigned long long before = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) {
+            if (w < warp) before += sk_scan[w];
+            total += sk_scan[w];
+            nmax = max(nmax, sk_scan[kDecWarps + w]);
+        }
+        before += incl - mine;                              // tiles per head before this thread's slice
+        const unsigned long long W = total * heads_per_seq;  // all tiles of the launch
+        // share: equal parts, at least one tile per warp, and wide enough that the longest
+        // head is cut into at most `splits` segments (the workspace holds that many records)
+        unsigned long long quota = (W + gridDim.x - 1u) / gridDim.x;
+        if (quota < kDecWarps) quota = kDecWarps;
+        const uint32_t cap = p.splits > 1u ? p.splits - 1u : 1u;
+        if (quota < (nmax + cap - 1u) / cap) quota = (nmax + cap - 1u) / cap;
+        sk_quota = static_cast<uint32_t>(quota);
+        const unsigned long long w0 = static_cast<unsigned long long>(blockIdx.x) * quota;
+        if (w0 >= W) return;   // uniform over the CTA: nothing left for it
+        const unsigned long long w1 = min(W, w0 + quota);
+        sk_left = static_cast<uint32_t>(w1 - w0);
+        // the thread whose slice holds w0 names the sequence
+        if (w0 >= before * heads_per_seq && w0 < (before + mine) * heads_per_seq) {
+            unsigned long long at = before;
+            for (uint32_t b = b0; b < b1; ++b) {
+                const uint32_t n = tiles_of(context_of(b));
+                if (w0 < (at + n) * heads_per_seq) {
+                    sk_start[0] = b;
+                    sk_start[1] = static_cast<uint32_t>(at);
+                    sk_start[2] = static_cast<uint32_t>(at >> 32);
+                    break;
+                }
+                at += n;
+            }
+        }
+        __syncthreads();
+        seq = sk_start[0];
+        if (seq >= batch) return;   // no thread found the share's first sequence: nothing to walk
+        sk_before = (static_cast<unsigned long long>(sk_start[2]) << 32) | sk_start[1];
+        sk_n = tiles_of(context_of(seq));
+        sk_loc = static_cast<uint32_t>(w0 - sk_before * heads_per_seq);
+    } else {
+        uint32_t lin = blockIdx.x;
+        split = lin % p.splits;
+        lin /= p.splits;
+        row_tile = lin % row_tiles;
+        const uint32_t item = lin / row_tiles;
+        seq = item / p.H;
+        head = item % p.H;
     }
-    const uint32_t drop_max = tokens_per_req - 1u;
-    const uint32_t ctx_all = ctx > drop_max ? ctx - drop_max : 0u;   // tokens every row sees
 
-    // One tile: scores^T for its strips, the online-softmax update, then acc^T += V^T P^T.
-    // TAIL tiles reach past the split's strips or past the live tokens and mask by
-    // overwriting (a dead slot's scale may be a NaN); full tiles carry no masking code.
-    auto compute_tile = [&](const uint8_t* st, uint32_t strip_t, auto tail_tag) {
-        constexpr bool TAIL = decltype(tail_tag)::value;
-        float sc[kTileStrips][4], vs[kTileStrips][2];
-        bool live[kTileStrips][2];
-        float mx[2] = {kMaskedScore, kMaskedScore};
-        float vmax = 0.f;
+#pragma unroll 1
+    for (;;) {
+        // ---- this segment: (seq, head, row_tile), strips [s0, s1), where its record goes
+        uint32_t ctx, s0, s1, seg_count = 1, seg_slot = split;
+        bool no_pages = false;
+        [[maybe_unused]] uint32_t sk_take = 0;
+        if constexpr (STREAMK) {
+            const uint32_t in_seq = sk_loc / sk_n, t0 = sk_loc - in_seq * sk_n;
+            sk_take = min(sk_left, sk_n - t0);
+            head = in_seq / row_tiles;
+            row_tile = in_seq - head * row_tiles;
+            ctx = context_of(seq);
+            s0 = t0 * kTileStrips;
+            s1 = min((t0 + sk_take) * kTileStrips, (ctx + kStrip - 1u) / kStrip);
+            // the CTAs this head's tiles [first, first + n) are dealt to
+            const unsigned long long first = sk_before * heads_per_seq + static_cast<unsigned long long>(in_seq) * sk_n;
+            const uint32_t c_first = static_cast<uint32_t>(first / sk_quota);
+            const uint32_t c_last = static_cast<uint32_t>((first + sk_n - 1u) / sk_quota);
+            seg_count = c_last - c_first + 1u;
+            seg_slot = blockIdx.x - c_first;
+        } else {
+            uint32_t page_count;
+            if (p.context_lens != nullptr) {
+                ctx = context_of(seq);
+                page_count = (ctx + p.S - 1u) / p.S;
+            } else {
+                ctx = p.fixed_ctx;
+                page_count = p.page_count;
+            }
+            // Ragged batches: a sequence takes only as many of the launch's splits as it has
+            // chunks of chunk_pages pages, so CTAs carry similar amounts of work; the splits it
+            // does not use fall out of the partition as empty ranges and export the neutral element.
+            uint32_t eff_splits = p.splits;
+            if (p.chunk_pages != 0u) {
+                const uint32_t chunks = (page_count + p.chunk_pages - 1u) / p.chunk_pages;
+                eff_splits = chunks < 1u ? 1u : (chunks < p.splits ? chunks : p.splits);
+            }
+            const uint32_t width = (page_count + eff_splits - 1u) / eff_splits;
+            const uint32_t rb = split * width;
+            const uint32_t remaining = rb < page_count ? page_count - rb : 0u;
+            const uint32_t rc = remaining < width ? remaining : width;
+            s0 = (p.page_begin + rb) * SP;
+            s1 = s0 + rc * SP;
+            const uint32_t live_strips = (ctx + kStrip - 1u) / kStrip;
+            if (s1 > live_strips) s1 = live_strips;
+            no_pages = rc == 0u;
+        }
+        const uint32_t item = seq * p.H + head;
+        const int rows_here = min(8u, p.rows - row_tile * 8u);
+        // A split whose page range is empty takes no part at all; one whose pages all
+        // lie past the live tokens still rotates and publishes its query (the rotation
+        // does not depend on the cache) and then exports the neutral element
+        // (kernels/ops/turboquant/turboquant_paged_decode_attention.cpp:1626-1637).
+        const bool empty = s1 <= s0;
+
+        float* rec_base = p.workspace +
+                          ((static_cast<size_t>(item) * p.splits + seg_slot) * p.rows_stride + row_tile * 8u) *
+                              kRecord;
+
+        // classic grid, one split, an output to write: the CTA holds the head's whole state
+        // and finishes it itself -- no record, no workspace, no second kernel
+        const bool direct = !STREAMK && p.output != nullptr;
+        if constexpr (!STREAMK) {
+            if (empty) {
+                if (direct) {
+                    float* zero = reinterpret_cast<float*>(ring + L::kMergeBytes + L::kRecBytes);
+                    for (int i = tid; i < rows_here * D; i += blockDim.x) zero[i] = 0.f;
+                    __syncthreads();
+                    egress_rows<D>(p, zero, rows_here, seq, head, row_tile, tokens_per_req, tid);
+                    return;
+                }
+                for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
+                    const int c = i % kRecord;
+                    rec_base[i] = c < 8 ? kMaskedScore : 0.0f;
+                }
+                if (no_pages || p.q_rot == nullptr) return;
+            }
+        }
+
+        // ---- the copy machinery of this segment
+        const int32_t* table_row = p.table + static_cast<size_t>(seq) * p.table_stride;
+        // Block-table entries of the tile whose first strip is `strip` (-1 past the range).
+        auto load_pages = [&](uint32_t strip, int32_t (&pg)[kTileStrips]) {
 #pragma unroll
-        for (int ts = 0; ts < kTileStrips; ++ts) {
-            const uint8_t* ss = st + ts * L::kStripStage;
-            const float* scales = reinterpret_cast<const float*>(ss + 2 * L::kStripBytes);
-            // A operand: 16 * code as a signed byte. The odd channels of a word are its
-            // high nibbles already in place (mask), the even ones move up by four bits.
-            int ci[NL][4];
+            for (int ts = 0; ts < kTileStrips; ++ts)
+                pg[ts] = strip + ts < s1 ? __ldg(table_row + ((strip + ts) >> sp_shift)) : -1;
+        };
+        const uint8_t* ksrc0;
+        const uint8_t* vsrc0;
+        const float* ssrc0;
+        if constexpr (NZ) {
+            // (64-row tile, head) images of 8 KiB inside a page of S * H * 128 bytes
+            ksrc0 = p.key_cache + static_cast<size_t>(head) * 8192u + lane * 16;
+            vsrc0 = p.value_cache + static_cast<size_t>(head) * 8192u + lane * 16;
+            ssrc0 = p.scale_cache + static_cast<size_t>(lane & 15) * p.nz_slot_floats + (lane >> 4) * p.H + head;
+        } else {
+            ksrc0 = p.key_cache + head * head_block + lane * 16;
+            vsrc0 = p.value_cache + head * head_block + lane * 16;
+            ssrc0 = p.scale_cache + (lane >> 2) * scale_plane + static_cast<size_t>(head) * p.S + (lane & 3) * 4;
+        }
+        auto issue = [&](uint32_t strip, uint32_t stage, const int32_t (&pg)[kTileStrips]) {
 #pragma unroll
-            for (int w4 = 0; w4 < WPT / 4; ++w4) {
-                const uint4 lo = *reinterpret_cast<const uint4*>(ss + koff_lo[w4]);
-                const uint4 hi = *reinterpret_cast<const uint4*>(ss + koff_hi[w4]);
-                const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
+            for (int ts = 0; ts < kTileStrips; ++ts) {
+                if (strip + ts >= s1) continue;   // warp-uniform: past the range
+                uint32_t page = static_cast<uint32_t>(pg[ts]);
+                if (pg[ts] < 0 || page >= p.P) {
+                    if (lane == 0) report(p.status, TQ_STATUS_BAD_PAGE);
+                    page = 0;
+                }
+                const uint32_t sip = (strip + ts) & sip_mask;
+                const uint32_t dst = my_ring_s + stage * L::kStageBytes + ts * L::kStripStage;
+                if constexpr (NZ) {
+                    // strip sip of the page: 64-row tile sip / 4, rows 16 (sip % 4) .. of its image
+                    const size_t off = static_cast<size_t>(page) * page_stride +
+                                       static_cast<size_t>(sip >> 2) * (64u * 128u) * p.H + (sip & 3u) * 512u;
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int wi = w4 * 4 + k;
-                    const uint32_t a0 = (wl[k] << 4) & 0xF0F0F0F0u, a1 = (wh[k] << 4) & 0xF0F0F0F0u;
-                    const uint32_t a2 = wl[k] & 0xF0F0F0F0u, a3 = wh[k] & 0xF0F0F0F0u;
+                    for (int i = 0; i < kChunksPerLane; ++i) {
+                        cp_async16(dst + kdst[i], ksrc0 + off + i * 2048);
+                        cp_async16(dst + vdst_nz + i * 512, vsrc0 + off + i * 2048);
+                    }
+                    cp_async4(dst + 2 * L::kStripBytes + lane * 4,
+                              ssrc0 + (static_cast<size_t>(page) * p.S + sip * kStrip) * p.nz_slot_floats);
+                } else {
+                    const uint8_t* ksrc = ksrc0 + static_cast<size_t>(page) * page_stride + sip * L::kStripBytes;
+                    const uint8_t* vsrc = vsrc0 + static_cast<size_t>(page) * page_stride + sip * L::kStripBytes;
+#pragma unroll
+                    for (int i = 0; i < kChunksPerLane; ++i) {
+                        cp_async16(dst + kdst[i], ksrc + i * 512);
+                        cp_async16(dst + L::kStripBytes + i * 512 + lane * 16, vsrc + i * 512);
+                    }
+                    if (lane < 8)
+                        cp_async16(dst + 2 * L::kStripBytes + lane * 16,
+                                   ssrc0 + static_cast<size_t>(page) * page_stride_scale + sip * kStrip);
+                }
+            }
+        };
+
+        // ---- per-warp pipeline over tiles warp, warp+4, ...: the first tile goes out before
+        // the query is rotated wherever its stage does not share bytes with the prologue
+        const uint32_t tiles = empty ? 0u : (s1 - s0 + kTileStrips - 1u) / kTileStrips;
+        const uint32_t my_tiles = tiles > static_cast<uint32_t>(warp)
+                                      ? (tiles - warp + kDecWarps - 1u) / kDecWarps : 0u;
+        const uint32_t strip_first = s0 + warp * kTileStrips;   // first strip of this warp's tile 0
+        int32_t pg_next[kTileStrips];
+        static_assert(kStages == 2, "the prologue below fills one stage ahead");
+        const bool early = L::early_issue(warp) && !empty;
+        if (early) {
+            load_pages(strip_first, pg_next);
+            issue(strip_first, 0, pg_next);
+            cp_async_commit();
+            load_pages(strip_first + kTileStep, pg_next);
+        }
+
+        // ---- rotate the query rows once: each warp takes two rows through the FP32
+        // ingress cascade, scales, rounds to bf16 (the pinned operand) and publishes it.
+        // The key contraction runs on the integer tensor path, so every row then becomes
+        // fixed point: its entries times the power of two that puts the largest below
+        // 2^(8 NL - 1), rounded to an integer of NL 8-bit limbs (NL = 2: 2^-16 of the row
+        // maximum, far inside the tolerance of the native path; NL = 3: 2^-24, FP32 grade,
+        // for the entry point that is checked against the reference's partial records).
+        // The inverse power goes into the per-row score factor together with
+        // softmax_scale * log2(e) and the 1/16 of the key operand (see compute_tile).
+        // A lane later reads the eight integers of its key word's channels, lanes (r, qd) at
+        // channel qd * d/4 + ...: rows are padded by 16 and quarters of a row by 4 words so that
+        // the eight lanes one 128-bit access serves together fall into eight different bank groups.
+        auto q_index = [](int row, int ch) { return row * (D + 16) + (ch / (D / 4)) * (D / 4 + 4) + ch % (D / 4); };
+        {
+            constexpr int K = D / 32;
+            float sgn[K];
+#pragma unroll
+            for (int i = 0; i < K; ++i)
+                sgn[i] = !prerot && sign_is_negative(p.signs, p.sign_source, lane * K + i) ? -1.0f : 1.0f;
+            for (int row = warp * 2; row < warp * 2 + 2; ++row) {
+                float v[K];
+#pragma unroll
+                for (int i = 0; i < K; ++i) v[i] = 0.f;
+                if (row < rows_here) {
+                    // row = token * G + g of the request's (1 + speculative) query tokens; with one
+                    // token per request this is (item * rows + row)
+                    const uint32_t row_g = row_tile * 8u + row, grp = p.rows / tokens_per_req;
+                    const uint32_t q_tok = row_g / grp, q_g = row_g - q_tok * grp;
+                    const size_t qoff = ((static_cast<size_t>(seq) * tokens_per_req + q_tok) * (p.H * grp) +
+                                         static_cast<size_t>(head) * grp + q_g) * D + lane * K;
+                    const uint16_t* qsrc = p.q + qoff;
+#pragma unroll
+                    for (int i = 0; i < K; ++i)
+                        v[i] = prerot ? p.q_f32[qoff + i]
+                                      : q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
+                }
+                if (!prerot) cascade_ingress<K>(v, sgn, lane);
+                float am = 0.f;
+#pragma unroll
+                for (int i = 0; i < K; ++i) {
+                    float val = prerot ? v[i] : v[i] * p.inv_sqrt_len;
+                    if (!q_f16 && !prerot) {   // the bf16 operand the reference pins (and publishes)
+                        const uint16_t bits = f32_to_bf16_bits(val);
+                        val = bf16_bits_to_f32(bits);
+                        if constexpr (!STREAMK) {
+                            if (p.q_rot != nullptr && row < rows_here)
+                                p.q_rot[((static_cast<size_t>(item) * p.splits + split) * p.rows_stride +
+                                         row_tile * 8u + row) * D + lane * K + i] = bits;
+                        }
+                    }
+                    v[i] = val;
+                    am = fmaxf(am, fabsf(val));
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+                // 2^(top - e) and 2^(e - top) from the exponent field of the row maximum,
+                // top = 8 NL - 2; a row below 1e-25 scores as zero
+                constexpr int kTop = 8 * NL - 2;
+                const bool tiny = !(am >= 1.0e-25f);
+                const int e_bits = __float_as_int(am) & 0x7F800000;
+                const float up = tiny ? 0.0f : __int_as_float(((254 + kTop) << 23) - e_bits);
+                const float down = tiny ? 1.0f : __int_as_float(e_bits - (kTop << 23));
+                int qsum = 0;
+#pragma unroll
+                for (int i = 0; i < K; ++i) {
+                    const int fx = __float2int_rn(v[i] * up);
+                    qfix[q_index(row, lane * K + i)] = fx;
+                    qsum += fx;
+                }
+                if (midrise) {
+                    // sum_c q_c (16 code_c + 8): the half step of every code adds 8 * sum_c q_c to a raw score
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
+                    if (lane == 0) row_qsum8[row] = qsum;
+                }
+                if (lane == 0) row_unscale[row] = down * 0.0625f * p.softmax_scale * kLog2e;
+            }
+        }
+        if constexpr (!STREAMK) {
+            if (empty) return;
+        }
+        __syncthreads();
+
+        // ---- limbs of q_rot^T as B fragments of the integer MMA. Word wi of a key row holds
+        // channels qd*(D/4) + wi*8 + n, n = 0..7: the even n feed contraction slots qd*4 + n/2
+        // (b0), the odd n slots 16 + qd*4 + n/2 (b1). NZ-tiled source: MMA wi = 2 g + half takes
+        // the low (half 0) or high nibbles of column group g, channels 128 half + 32 g + 8 qd + n,
+        // n = 0..3 in b0 and 4..7 in b1.
+        uint32_t bq[L::kQFragSmem ? 1 : NL][L::kQFragSmem ? 1 : WPT][2];
+        // [wi][limb][lane] pairs of registers; every warp holds the same fragments, warp 0 writes them
+        uint2* qfrag = reinterpret_cast<uint2*>(smem + L::kBody) + lane;
+#pragma unroll
+        for (int wi = 0; wi < WPT; ++wi) {
+            const int* qr = NZ ? qfix + q_index(r, (wi & 1) * 128 + (wi >> 1) * 32 + qd * 8)
+                               : qfix + q_index(r, qd * (D / 4) + wi * 8);
+            int qv[8];
+#pragma unroll
+            for (int n = 0; n < 8; ++n) qv[n] = qr[n];
+#pragma unroll
+            for (int l = 0; l < NL; ++l)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    // byte e of the word = limb l of channel 2e + h (NZ: 4h + e): three byte permutes
+                    const uint32_t pick = static_cast<uint32_t>(l) | (static_cast<uint32_t>(4 + l) << 4);
+                    const uint32_t lo = NZ ? __byte_perm(qv[4 * h], qv[4 * h + 1], pick)
+                                           : __byte_perm(qv[h], qv[2 + h], pick);
+                    const uint32_t hi = NZ ? __byte_perm(qv[4 * h + 2], qv[4 * h + 3], pick)
+                                           : __byte_perm(qv[4 + h], qv[6 + h], pick);
+                    const uint32_t frag = __byte_perm(lo, hi, 0x5410u);
+                    if constexpr (L::kQFragSmem) {
+                        if (warp == 0) reinterpret_cast<uint32_t*>(qfrag + (wi * NL + l) * 32)[h] = frag;
+                    } else {
+                        bq[l][wi][h] = frag;
+                    }
+                }
+        }
+        // scores are kept as raw * key_scale; the per-row factor enters inside the exponent
+        const float rfac[2] = {row_unscale[qd * 2], row_unscale[qd * 2 + 1]};
+        const int qs8[2] = {midrise ? row_qsum8[qd * 2] : 0, midrise ? row_qsum8[qd * 2 + 1] : 0};
+        float ps[2] = {0.f, 0.f};   // mid-rise codes: running sum of P (as the value contraction sees it) per row
+        __syncthreads();  // everyone is done with the fixed-point query: the ring may overwrite it
+
+        // Online-softmax state for query rows qd*2 and qd*2+1, in units of raw * key_scale.
+        float m_run[2] = {kMaskedScore, kMaskedScore}, l_run[2] = {0.f, 0.f};
+        float m_fac[2] = {0.f, 0.f};   // m_run * rfac, the exponent offset (0 while m_run is the sentinel)
+        float acc[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+        // Running power-of-two normaliser of the value scales: P is carried in f16, so
+        // it is kept in [0, 1] by dividing the value scale by the largest seen so far.
+        float vnorm = 0.f, inv_vnorm = 0.f;
+
+        if (!early) {
+            load_pages(strip_first, pg_next);
+            issue(strip_first, 0, pg_next);
+            cp_async_commit();
+            load_pages(strip_first + kTileStep, pg_next);
+        }
+
+        // Speculative tokens: query token t of a request sees the context without the last
+        // (tokens_per_req - 1 - t) tokens. row_drop[q] is that count for this thread's two rows.
+        uint32_t row_drop[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const uint32_t row_g = row_tile * 8u + qd * 2 + q, grp = p.rows / tokens_per_req;
+            const uint32_t t = min(row_g / grp, tokens_per_req - 1u);
+            row_drop[q] = tokens_per_req - 1u - t;
+        }
+        const uint32_t drop_max = tokens_per_req - 1u;
+        const uint32_t ctx_all = ctx > drop_max ? ctx - drop_max : 0u;   // tokens every row sees
+
+        // One tile: scores^T for its strips, the online-softmax update, then acc^T += V^T P^T.
+        // TAIL tiles reach past the split's strips or past the live tokens and mask by
+        // overwriting (a dead slot's scale may be a NaN); full tiles carry no masking code.
+        auto compute_tile = [&](const uint8_t* st, uint32_t strip_t, auto tail_tag) {
+            constexpr bool TAIL = decltype(tail_tag)::value;
+            float sc[kTileStrips][4], vs[kTileStrips][2];
+            bool live[kTileStrips][2];
+            float mx[2] = {kMaskedScore, kMaskedScore};
+            float vmax = 0.f;
+#pragma unroll
+            for (int ts = 0; ts < kTileStrips; ++ts) {
+                const uint8_t* ss = st + ts * L::kStripStage;
+                const float* scales = reinterpret_cast<const float*>(ss + 2 * L::kStripBytes);
+                // A operand: 16 * code as a signed byte. The odd channels of a word are its
+                // high nibbles already in place (mask), the even ones move up by four bits.
+                int ci[NL][4];
+                auto limbs = [&](int wi, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3) {
 #pragma unroll
                     for (int l = 0; l < NL; ++l) {
                         uint32_t b0, b1;
@@ -575,221 +875,477 @@ tq_decode_partial_kernel(const DecodeParams p)
                         else
                             mma_s8_limb(l == NL - 1, ci[l], a0, a1, a2, a3, b0, b1, ci[l]);
                     }
+                };
+                if constexpr (NZ) {
+                    // column group g: bytes 8 qd .. 8 qd + 7 of both token rows; the low nibbles
+                    // are channels 32 g + 8 qd + j, the high nibbles channels 128 + 32 g + 8 qd + j
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const uint2 lo = *reinterpret_cast<const uint2*>(ss + g * 512 + koff_lo[0]);
+                        const uint2 hi = *reinterpret_cast<const uint2*>(ss + g * 512 + koff_hi[0]);
+                        limbs(2 * g, (lo.x << 4) & 0xF0F0F0F0u, (hi.x << 4) & 0xF0F0F0F0u,
+                              (lo.y << 4) & 0xF0F0F0F0u, (hi.y << 4) & 0xF0F0F0F0u);
+                        limbs(2 * g + 1, lo.x & 0xF0F0F0F0u, hi.x & 0xF0F0F0F0u, lo.y & 0xF0F0F0F0u,
+                              hi.y & 0xF0F0F0F0u);
+                    }
+                } else {
+#pragma unroll
+                    for (int w4 = 0; w4 < WPT / 4; ++w4) {
+                        const uint4 lo = *reinterpret_cast<const uint4*>(ss + koff_lo[w4]);
+                        const uint4 hi = *reinterpret_cast<const uint4*>(ss + koff_hi[w4]);
+                        const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            limbs(w4 * 4 + k, (wl[k] << 4) & 0xF0F0F0F0u, (wh[k] << 4) & 0xF0F0F0F0u,
+                                  wl[k] & 0xF0F0F0F0u, wh[k] & 0xF0F0F0F0u);
+                    }
+                }
+                // limbs -> one float per score: sum_l 256^l * c_l
+                float c[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if constexpr (NL == 2) {
+                        // |c1| * 256 + |c0| < 2^31 at either head size: the two limbs combine in
+                        // INT32 and one conversion follows
+                        int sum = ci[1][i] * 256 + ci[0][i];
+                        if constexpr (EXT) sum += 8 * qs8[i & 1];   // < 2^30 + 2^26
+                        c[i] = __int2float_rn(sum);
+                        continue;
+                    }
+                    float f = limb_value(ci[NL - 1][i]);
+#pragma unroll
+                    for (int l = NL - 2; l >= 0; --l) f = fmaf(f, 256.0f, limb_value(ci[l][i]));
+                    if constexpr (EXT) f = fmaf(8.0f, __int2float_rn(qs8[i & 1]), f);   // the sum stays below 2^30
+                    c[i] = f;
+                }
+                const float ks_lo = scales[tok_lo], ks_hi = scales[tok_hi];
+                vs[ts][0] = scales[kStrip + tok_lo];
+                vs[ts][1] = scales[kStrip + tok_hi];
+                sc[ts][0] = c[0] * ks_lo;
+                sc[ts][1] = c[1] * ks_lo;
+                sc[ts][2] = c[2] * ks_hi;
+                sc[ts][3] = c[3] * ks_hi;
+                if constexpr (TAIL) {
+                    const uint32_t strip = strip_t + ts;
+                    live[ts][0] = strip < s1 && strip * kStrip + tok_lo < ctx;
+                    live[ts][1] = strip < s1 && strip * kStrip + tok_hi < ctx;
+                    if (!live[ts][0]) { sc[ts][0] = sc[ts][1] = kMaskedScore; vs[ts][0] = 0.f; }
+                    if (!live[ts][1]) { sc[ts][2] = sc[ts][3] = kMaskedScore; vs[ts][1] = 0.f; }
+                    if (tokens_per_req > 1u) {   // the last tokens are hidden from the earlier query tokens
+                        const uint32_t t_lo = strip * kStrip + tok_lo, t_hi = strip * kStrip + tok_hi;
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            if (t_lo + row_drop[q] >= ctx) sc[ts][q] = kMaskedScore;
+                            if (t_hi + row_drop[q] >= ctx) sc[ts][2 + q] = kMaskedScore;
+                        }
+                    }
+                }
+                mx[0] = max3(mx[0], sc[ts][0], sc[ts][2]);
+                mx[1] = max3(mx[1], sc[ts][1], sc[ts][3]);
+                vmax = max3(vmax, fabsf(vs[ts][0]), fabsf(vs[ts][1]));
+            }
+            // -- online softmax update. m_run and vnorm are uniform over the lanes that share
+            // them, so "did anything grow" can be asked of every lane's own four scores first;
+            // only a tile that raises a row maximum or the value normaliser pays for the
+            // reductions and the rescale of the accumulator (rfac > 0: the maximum can be taken
+            // before the per-row factor is applied).
+            const bool grow = mx[0] > m_run[0] || mx[1] > m_run[1] || vmax > vnorm;
+            if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+                for (int o = 4; o <= 16; o <<= 1) {
+                    mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
+                    mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
+                    vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+                }
+                float alpha[2];
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const float m_new = fmaxf(m_run[q], mx[q]);
+                    alpha[q] = ex2f((m_run[q] - m_new) * rfac[q]);
+                    m_run[q] = m_new;
+                    // a row that has seen no live token yet keeps offset 0: its masked scores must
+                    // still give exp2(-huge) = 0, not exp2(0)
+                    m_fac[q] = m_new > -1.0e37f ? m_new * rfac[q] : 0.f;
+                    l_run[q] *= alpha[q];
+                }
+                if (vmax > vnorm) {  // warp-uniform: value scales depend on the token only
+                    // the power of two above vmax; the ratio old/new is exact
+                    const float nv = __int_as_float((__float_as_int(vmax) & 0x7F800000) + (1 << 23));
+                    inv_vnorm = __int_as_float((254 << 23) - __float_as_int(nv));
+                    alpha[0] *= vnorm * inv_vnorm;
+                    alpha[1] *= vnorm * inv_vnorm;
+                    vnorm = nv;
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    acc[mt][0] *= alpha[0];
+                    acc[mt][1] *= alpha[1];
+                    acc[mt][2] *= alpha[0];
+                    acc[mt][3] *= alpha[1];
+                }
+                if constexpr (EXT) {
+                    ps[0] *= alpha[0];
+                    ps[1] *= alpha[1];
                 }
             }
-            // limbs -> one float per score: sum_l 256^l * c_l
-            float c[4];
+            // -- P, then acc^T += V^T P^T
+            if constexpr (!PRECISE) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if constexpr (NL == 2) {
-                    // |c1| * 256 + |c0| < 2^31 at either head size: the two limbs combine in
-                    // INT32 and one conversion follows
-                    int sum = ci[1][i] * 256 + ci[0][i];
-                    if constexpr (EXT) sum += qs8[i & 1];   // < 2^30 + 2^26
-                    c[i] = __int2float_rn(sum);
-                    continue;
+                for (int ts = 0; ts < kTileStrips; ++ts) {
+                    if constexpr (TAIL) {
+                        if (strip_t + ts >= s1) continue;  // warp-uniform
+                    }
+                    const uint8_t* ss = st + ts * L::kStripStage;
+                    const float vs_lo = vs[ts][0] * inv_vnorm, vs_hi = vs[ts][1] * inv_vnorm;
+                    float pw[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float pr = ex2f(fmaf(sc[ts][i], rfac[i & 1], -m_fac[i & 1]));
+                        l_run[i & 1] += pr;
+                        pw[i] = pr * (i < 2 ? vs_lo : vs_hi);
+                    }
+                    const uint32_t h0 = pack_f16x2(pw[0], pw[1]), h1 = pack_f16x2(pw[2], pw[3]);
+                    const uint32_t bh0 = movmatrix_trans(h0), bh1 = movmatrix_trans(h1);
+                    if constexpr (EXT) {
+                        if (midrise) {   // the f16 values the MMA multiplies, so that acc and ps stay consistent
+                            const float2 f0 = unpack_f16x2(h0), f1 = unpack_f16x2(h1);
+                            ps[0] += f0.x + f1.x;
+                            ps[1] += f0.y + f1.y;
+                        }
+                    }
+                    if constexpr (NZ) {
+                        // Token rows are the contraction index and lie 32 bytes apart in the image:
+                        // word r of the four rows whose slots are qd, qd+4, qd+8, qd+12 (tokens t, t+4,
+                        // t+1, t+5 of this lane's pairs) carries four packed columns, i.e. channels
+                        // 32 g + 4 r + u (low nibbles) and 128 + 32 g + 4 r + u (high), u = 0..3. A byte
+                        // permute puts the same column of two tokens 16 bits apart, where the masks
+                        // of dq_lo / dq_hi pick both channels' pairs.
+                        const uint8_t* vbase = ss + L::kStripBytes + qd * 32 + r * 4;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const uint32_t wa = *reinterpret_cast<const uint32_t*>(vbase + g * 512);
+                            const uint32_t wb = *reinterpret_cast<const uint32_t*>(vbase + g * 512 + 4 * 32);
+                            const uint32_t wc = *reinterpret_cast<const uint32_t*>(vbase + g * 512 + 8 * 32);
+                            const uint32_t wd = *reinterpret_cast<const uint32_t*>(vbase + g * 512 + 12 * 32);
+#pragma unroll
+                            for (int u2 = 0; u2 < 2; ++u2) {
+                                const uint32_t y = __byte_perm(wa, wb, u2 ? 0x7632u : 0x5410u);
+                                const uint32_t z = __byte_perm(wc, wd, u2 ? 0x7632u : 0x5410u);
+#pragma unroll
+                                for (int u1 = 0; u1 < 2; ++u1) {
+                                    const int mt = g * 4 + u2 * 2 + u1;
+                                    const uint32_t ys = u1 ? y >> 8 : y, zs = u1 ? z >> 8 : z;
+                                    const uint32_t a0 = dq_lo(ys), a1 = dq_hi(ys), a2 = dq_lo(zs), a3 = dq_hi(zs);
+                                    mma_f16_16816(acc[mt], a0, a1, a2, a3, bh0, bh1);
+                                }
+                            }
+                        }
+                    } else {
+                        const uint8_t* vrow = ss + L::kStripBytes + (2 * r) * 8;
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const uint4 v = *reinterpret_cast<const uint4*>(vrow + mt * 128);
+                            const uint32_t ya = __byte_perm(v.x, v.y, vsel), yb = __byte_perm(v.z, v.w, vsel);
+                            const uint32_t a0 = dq_lo(ya), a2 = dq_hi(ya), a1 = dq_lo(yb), a3 = dq_hi(yb);
+                            mma_f16_16816(acc[mt], a0, a1, a2, a3, bh0, bh1);
+                        }
+                    }
                 }
-                float f = limb_value(ci[NL - 1][i]);
+            } else {
+                // The wider arithmetic: P as hi + lo halves, and every tile's products summed in
+                // an accumulator that starts at zero and joins the running one with an ordinary
+                // FP32 addition -- the tensor core's own accumulation is then never more than a
+                // few steps deep, so whatever rounding it applies cannot build up over a context.
+                uint32_t bh[kTileStrips][2], bl[kTileStrips][2];
+                bool on[kTileStrips];
 #pragma unroll
-                for (int l = NL - 2; l >= 0; --l) f = fmaf(f, 256.0f, limb_value(ci[l][i]));
-                c[i] = f;
-            }
-            const float ks_lo = scales[tok_lo], ks_hi = scales[tok_hi];
-            vs[ts][0] = scales[kStrip + tok_lo];
-            vs[ts][1] = scales[kStrip + tok_hi];
-            sc[ts][0] = c[0] * ks_lo;
-            sc[ts][1] = c[1] * ks_lo;
-            sc[ts][2] = c[2] * ks_hi;
-            sc[ts][3] = c[3] * ks_hi;
-            if constexpr (TAIL) {
-                const uint32_t strip = strip_t + ts;
-                live[ts][0] = strip < s1 && strip * kStrip + tok_lo < ctx;
-                live[ts][1] = strip < s1 && strip * kStrip + tok_hi < ctx;
-                if (!live[ts][0]) { sc[ts][0] = sc[ts][1] = kMaskedScore; vs[ts][0] = 0.f; }
-                if (!live[ts][1]) { sc[ts][2] = sc[ts][3] = kMaskedScore; vs[ts][1] = 0.f; }
-                if (tokens_per_req > 1u) {   // the last tokens are hidden from the earlier query tokens
-                    const uint32_t t_lo = strip * kStrip + tok_lo, t_hi = strip * kStrip + tok_hi;
+                for (int ts = 0; ts < kTileStrips; ++ts) {
+                    on[ts] = !(TAIL && strip_t + ts >= s1);   // warp-uniform
+                    bh[ts][0] = bh[ts][1] = bl[ts][0] = bl[ts][1] = 0u;
+                    if (!on[ts]) continue;
+                    const float vs_lo = vs[ts][0] * inv_vnorm, vs_hi = vs[ts][1] * inv_vnorm;
+                    float pw[4];
 #pragma unroll
-                    for (int q = 0; q < 2; ++q) {
-                        if (t_lo + row_drop[q] >= ctx) sc[ts][q] = kMaskedScore;
-                        if (t_hi + row_drop[q] >= ctx) sc[ts][2 + q] = kMaskedScore;
+                    for (int i = 0; i < 4; ++i) {
+                        const float pr = ex2f(fmaf(sc[ts][i], rfac[i & 1], -m_fac[i & 1]));
+                        l_run[i & 1] += pr;
+                        pw[i] = pr * (i < 2 ? vs_lo : vs_hi);
+                    }
+                    const uint32_t h0 = pack_f16x2(pw[0], pw[1]), h1 = pack_f16x2(pw[2], pw[3]);
+                    const float2 f0 = unpack_f16x2(h0), f1 = unpack_f16x2(h1);
+                    const uint32_t l0 = pack_f16x2(pw[0] - f0.x, pw[1] - f0.y);
+                    const uint32_t l1 = pack_f16x2(pw[2] - f1.x, pw[3] - f1.y);
+                    bh[ts][0] = movmatrix_trans(h0);
+                    bh[ts][1] = movmatrix_trans(h1);
+                    bl[ts][0] = movmatrix_trans(l0);
+                    bl[ts][1] = movmatrix_trans(l1);
+                    if constexpr (EXT) {
+                        if (midrise) {   // the f16 values the MMAs multiply, so that acc and ps stay consistent
+                            const float2 g0 = unpack_f16x2(l0), g1 = unpack_f16x2(l1);
+                            ps[0] += (f0.x + f1.x) + (g0.x + g1.x);
+                            ps[1] += (f0.y + f1.y) + (g0.y + g1.y);
+                        }
+                    }
+                }
+                if constexpr (NZ) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        float t[4][4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) t[u][i] = 0.f;
+#pragma unroll
+                        for (int ts = 0; ts < kTileStrips; ++ts) {
+                            if (!on[ts]) continue;
+                            const uint8_t* vbase = st + ts * L::kStripStage + L::kStripBytes + qd * 32 + r * 4 + g * 512;
+                            const uint32_t wa = *reinterpret_cast<const uint32_t*>(vbase);
+                            const uint32_t wb = *reinterpret_cast<const uint32_t*>(vbase + 4 * 32);
+                            const uint32_t wc = *reinterpret_cast<const uint32_t*>(vbase + 8 * 32);
+                            const uint32_t wd = *reinterpret_cast<const uint32_t*>(vbase + 12 * 32);
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const uint32_t y = __byte_perm(wa, wb, (u & 2) ? 0x7632u : 0x5410u);
+                                const uint32_t z = __byte_perm(wc, wd, (u & 2) ? 0x7632u : 0x5410u);
+                                const uint32_t ys = (u & 1) ? y >> 8 : y, zs = (u & 1) ? z >> 8 : z;
+                                const uint32_t a0 = dq_lo(ys), a1 = dq_hi(ys), a2 = dq_lo(zs), a3 = dq_hi(zs);
+                                mma_f16_16816(t[u], a0, a1, a2, a3, bl[ts][0], bl[ts][1]);
+                                mma_f16_16816(t[u], a0, a1, a2, a3, bh[ts][0], bh[ts][1]);
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[g * 4 + u][i] += t[u][i];
+                    }
+                } else {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int ts = 0; ts < kTileStrips; ++ts) {
+                            if (!on[ts]) continue;
+                            const uint8_t* vrow = st + ts * L::kStripStage + L::kStripBytes + (2 * r) * 8;
+                            const uint4 v = *reinterpret_cast<const uint4*>(vrow + mt * 128);
+                            const uint32_t ya = __byte_perm(v.x, v.y, vsel), yb = __byte_perm(v.z, v.w, vsel);
+                            const uint32_t a0 = dq_lo(ya), a2 = dq_hi(ya), a1 = dq_lo(yb), a3 = dq_hi(yb);
+                            mma_f16_16816(t, a0, a1, a2, a3, bl[ts][0], bl[ts][1]);
+                            mma_f16_16816(t, a0, a1, a2, a3, bh[ts][0], bh[ts][1]);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[mt][i] += t[i];
                     }
                 }
             }
-            mx[0] = max3(mx[0], sc[ts][0], sc[ts][2]);
-            mx[1] = max3(mx[1], sc[ts][1], sc[ts][3]);
-            vmax = max3(vmax, fabsf(vs[ts][0]), fabsf(vs[ts][1]));
-        }
-        // -- online softmax update. m_run and vnorm are uniform over the lanes that share
-        // them, so "did anything grow" can be asked of every lane's own four scores first;
-        // only a tile that raises a row maximum or the value normaliser pays for the
-        // reductions and the rescale of the accumulator (rfac > 0: the maximum can be taken
-        // before the per-row factor is applied).
-        const bool grow = mx[0] > m_run[0] || mx[1] > m_run[1] || vmax > vnorm;
-        if (__any_sync(0xffffffffu, grow)) {
+        };
+
+        uint32_t stage = 0;
+        uint32_t strip_t = strip_first;   // first strip of the tile being computed
+#pragma unroll 1
+        for (uint32_t j = 0; j < my_tiles; ++j, strip_t += kTileStep) {
+            {
+                const uint32_t ahead = strip_t + (kStages - 1) * kTileStep;
+                issue(ahead, stage == 0 ? kStages - 1 : stage - 1, pg_next);
+                cp_async_commit();
+                load_pages(ahead + kTileStep, pg_next);
+            }
+            cp_async_wait<kStages - 1>();
+            uint8_t* st = my_ring + stage * L::kStageBytes;
+            if constexpr (NZ) {
+                // the stored scale is divided by the codebook gain (IEEE division, as the
+                // importer does): every lane finishes the one scale it copied
 #pragma unroll
-            for (int o = 4; o <= 16; o <<= 1) {
-                mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xffffffffu, mx[0], o));
-                mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xffffffffu, mx[1], o));
-                vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
-            }
-            float alpha[2];
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const float m_new = fmaxf(m_run[q], mx[q]);
-                alpha[q] = ex2f((m_run[q] - m_new) * rfac[q]);
-                m_run[q] = m_new;
-                // a row that has seen no live token yet keeps offset 0: its masked scores must
-                // still give exp2(-huge) = 0, not exp2(0)
-                m_fac[q] = m_new > -1.0e37f ? m_new * rfac[q] : 0.f;
-                l_run[q] *= alpha[q];
-            }
-            if (vmax > vnorm) {  // warp-uniform: value scales depend on the token only
-                // the power of two above vmax; the ratio old/new is exact
-                const float nv = __int_as_float((__float_as_int(vmax) & 0x7F800000) + (1 << 23));
-                inv_vnorm = __int_as_float((254 << 23) - __float_as_int(nv));
-                alpha[0] *= vnorm * inv_vnorm;
-                alpha[1] *= vnorm * inv_vnorm;
-                vnorm = nv;
-            }
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                acc[mt][0] *= alpha[0];
-                acc[mt][1] *= alpha[1];
-                acc[mt][2] *= alpha[0];
-                acc[mt][3] *= alpha[1];
-            }
-            if constexpr (EXT) {
-                ps[0] *= alpha[0];
-                ps[1] *= alpha[1];
-            }
-        }
-        // -- P, then acc^T += V^T P^T
-#pragma unroll
-        for (int ts = 0; ts < kTileStrips; ++ts) {
-            if constexpr (TAIL) {
-                if (strip_t + ts >= s1) continue;  // warp-uniform
-            }
-            const uint8_t* ss = st + ts * L::kStripStage;
-            const float vs_lo = vs[ts][0] * inv_vnorm, vs_hi = vs[ts][1] * inv_vnorm;
-            float pw[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float pr = ex2f(fmaf(sc[ts][i], rfac[i & 1], -m_fac[i & 1]));
-                l_run[i & 1] += pr;
-                pw[i] = pr * (i < 2 ? vs_lo : vs_hi);
-            }
-            const uint32_t h0 = pack_f16x2(pw[0], pw[1]), h1 = pack_f16x2(pw[2], pw[3]);
-            const uint32_t bh0 = movmatrix_trans(h0), bh1 = movmatrix_trans(h1);
-            if constexpr (EXT) {
-                if (midrise) {   // the f16 values the MMA multiplies, so that acc and ps stay consistent
-                    const float2 f0 = unpack_f16x2(h0), f1 = unpack_f16x2(h1);
-                    ps[0] += f0.x + f1.x;
-                    ps[1] += f0.y + f1.y;
+                for (int ts = 0; ts < kTileStrips; ++ts) {
+                    float* sv = reinterpret_cast<float*>(st + ts * L::kStripStage + 2 * L::kStripBytes) + lane;
+                    *sv = __fdiv_rn(*sv, p.nz_gain);
                 }
             }
-            [[maybe_unused]] uint32_t bl0 = 0, bl1 = 0;
-            if constexpr (PRECISE) {
-                const float2 f0 = unpack_f16x2(h0), f1 = unpack_f16x2(h1);
-                bl0 = movmatrix_trans(pack_f16x2(pw[0] - f0.x, pw[1] - f0.y));
-                bl1 = movmatrix_trans(pack_f16x2(pw[2] - f1.x, pw[3] - f1.y));
+            __syncwarp();
+            if (++stage == kStages) stage = 0;
+            if (strip_t + kTileStrips > s1 || (strip_t + kTileStrips) * kStrip > ctx_all)
+                compute_tile(st, strip_t, std::true_type{});
+            else
+                compute_tile(st, strip_t, std::false_type{});
+            __syncwarp();
+        }
+        cp_async_wait<0>();
+
+        // ---- warp-level l, value normaliser out of acc, merge the warps through shared memory.
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 4);
+            l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 8);
+            l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 16);
+        }
+        // mid-rise codes: sum_t P_t (code_t + 0.5) = acc + 0.5 * sum_t P_t, the same for every channel
+        float half_p[2] = {0.f, 0.f};
+        if constexpr (EXT) {
+            if (midrise) {
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    ps[q] += __shfl_xor_sync(0xffffffffu, ps[q], 4);
+                    ps[q] += __shfl_xor_sync(0xffffffffu, ps[q], 8);
+                    ps[q] += __shfl_xor_sync(0xffffffffu, ps[q], 16);
+                    half_p[q] = 0.5f * ps[q];
+                }
             }
-            const uint8_t* vrow = ss + L::kStripBytes + (2 * r) * 8;
+        }
+        __syncthreads();  // every warp is done with its ring; reuse it
+        // Row pitch d + 4 floats: a lane stores its two adjacent channels of a row as one
+        // 8-byte word, and with this pitch the 16 lanes of a half-warp hit 16 different banks pairs.
+        constexpr int kPitch = L::kMergePitch;
+        float* merge = reinterpret_cast<float*>(ring) + warp * 8 * kPitch;
+        if (r == 0) {
+            merge[(qd * 2 + 0) * kPitch + 0] = m_run[0];
+            merge[(qd * 2 + 0) * kPitch + 1] = l_run[0];
+            merge[(qd * 2 + 1) * kPitch + 0] = m_run[1];
+            merge[(qd * 2 + 1) * kPitch + 1] = l_run[1];
+        }
+        if constexpr (NZ) {
+            // MMA mt = 4 g + u: row r is channel 32 g + 4 r + u, row r + 8 channel 128 + that
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+#pragma unroll
+                for (int u = 0; u < 4; u += 2) {
+                    const int mt = g * 4 + u, ch = g * 32 + 4 * r + u;
+                    *reinterpret_cast<float2*>(merge + (qd * 2 + 0) * kPitch + 2 + ch) =
+                        make_float2((acc[mt][0] + half_p[0]) * vnorm, (acc[mt + 1][0] + half_p[0]) * vnorm);
+                    *reinterpret_cast<float2*>(merge + (qd * 2 + 0) * kPitch + 2 + 128 + ch) =
+                        make_float2((acc[mt][2] + half_p[0]) * vnorm, (acc[mt + 1][2] + half_p[0]) * vnorm);
+                    *reinterpret_cast<float2*>(merge + (qd * 2 + 1) * kPitch + 2 + ch) =
+                        make_float2((acc[mt][1] + half_p[1]) * vnorm, (acc[mt + 1][1] + half_p[1]) * vnorm);
+                    *reinterpret_cast<float2*>(merge + (qd * 2 + 1) * kPitch + 2 + 128 + ch) =
+                        make_float2((acc[mt][3] + half_p[1]) * vnorm, (acc[mt + 1][3] + half_p[1]) * vnorm);
+                }
+        } else {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                const uint4 v = *reinterpret_cast<const uint4*>(vrow + mt * 128);
-                const uint32_t ya = __byte_perm(v.x, v.y, vsel), yb = __byte_perm(v.z, v.w, vsel);
-                const uint32_t a0 = dq_lo(ya), a2 = dq_hi(ya), a1 = dq_lo(yb), a3 = dq_hi(yb);
-                mma_f16_16816(acc[mt], a0, a1, a2, a3, bh0, bh1);
-                if constexpr (PRECISE) mma_f16_16816(acc[mt], a0, a1, a2, a3, bl0, bl1);
+                const int ch = mt * 16 + 2 * r;
+                *reinterpret_cast<float2*>(merge + (qd * 2 + 0) * kPitch + 2 + ch) =
+                    make_float2((acc[mt][0] + half_p[0]) * vnorm, (acc[mt][2] + half_p[0]) * vnorm);
+                *reinterpret_cast<float2*>(merge + (qd * 2 + 1) * kPitch + 2 + ch) =
+                    make_float2((acc[mt][1] + half_p[1]) * vnorm, (acc[mt][3] + half_p[1]) * vnorm);
             }
         }
-    };
-
-    uint32_t stage = 0;
-    uint32_t strip_t = strip_first;   // first strip of the tile being computed
-#pragma unroll 1
-    for (uint32_t j = 0; j < my_tiles; ++j, strip_t += kTileStep) {
-        {
-            const uint32_t ahead = strip_t + (kStages - 1) * kTileStep;
-            issue(ahead, stage == 0 ? kStages - 1 : stage - 1, pg_next);
-            cp_async_commit();
-            load_pages(ahead + kTileStep, pg_next);
-        }
-        cp_async_wait<kStages - 1>();
-        __syncwarp();
-        const uint8_t* st = my_ring + stage * L::kStageBytes;
-        if (++stage == kStages) stage = 0;
-        if (strip_t + kTileStrips > s1 || (strip_t + kTileStrips) * kStrip > ctx_all)
-            compute_tile(st, strip_t, std::true_type{});
-        else
-            compute_tile(st, strip_t, std::false_type{});
-        __syncwarp();
-    }
-    cp_async_wait<0>();
-
-    // ---- warp-level l, value normaliser out of acc, merge the warps through shared memory.
+        __syncthreads();
+        // Inside the kernel m is in units of raw * key_scale; row_unscale turns a difference
+        // of such maxima into log2 units, and times ln 2 into the natural units of a record.
+        const float* mg = reinterpret_cast<const float*>(ring);
+        // element c of the merged record of row q: 0 = m (natural units), 1 = l, 2 + ch = acc[ch]
+        auto merged = [&](int q, int c) -> float {
+            const float rf = row_unscale[q];
+            float mm = kMaskedScore;
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
-        l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 4);
-        l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 8);
-        l_run[q] += __shfl_xor_sync(0xffffffffu, l_run[q], 16);
-    }
-    // mid-rise codes: sum_t P_t (code_t + 0.5) = acc + 0.5 * sum_t P_t, the same for every channel
-    float half_p[2] = {0.f, 0.f};
-    if constexpr (EXT) {
-        if (midrise) {
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                ps[q] += __shfl_xor_sync(0xffffffffu, ps[q], 4);
-                ps[q] += __shfl_xor_sync(0xffffffffu, ps[q], 8);
-                ps[q] += __shfl_xor_sync(0xffffffffu, ps[q], 16);
-                half_p[q] = 0.5f * ps[q];
-            }
-        }
-    }
-    __syncthreads();  // every warp is done with its ring; reuse it
-    // Row pitch d + 4 floats: a lane stores its two adjacent channels of a row as one
-    // 8-byte word, and with this pitch the 16 lanes of a half-warp hit 16 different banks pairs.
-    constexpr int kPitch = L::kMergePitch;
-    float* merge = reinterpret_cast<float*>(ring) + warp * 8 * kPitch;
-    if (r == 0) {
-        merge[(qd * 2 + 0) * kPitch + 0] = m_run[0];
-        merge[(qd * 2 + 0) * kPitch + 1] = l_run[0];
-        merge[(qd * 2 + 1) * kPitch + 0] = m_run[1];
-        merge[(qd * 2 + 1) * kPitch + 1] = l_run[1];
-    }
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        const int ch = mt * 16 + 2 * r;
-        *reinterpret_cast<float2*>(merge + (qd * 2 + 0) * kPitch + 2 + ch) =
-            make_float2((acc[mt][0] + half_p[0]) * vnorm, (acc[mt][2] + half_p[0]) * vnorm);
-        *reinterpret_cast<float2*>(merge + (qd * 2 + 1) * kPitch + 2 + ch) =
-            make_float2((acc[mt][1] + half_p[1]) * vnorm, (acc[mt][3] + half_p[1]) * vnorm);
-    }
-    __syncthreads();
-    // Inside the kernel m is in units of raw * key_scale; row_unscale turns a difference
-    // of such maxima into log2 units, and times ln 2 into the natural units of a record.
-    const float* mg = reinterpret_cast<const float*>(ring);
-    for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
-        const int q = i / kRecord, c = i % kRecord;
-        const float rf = row_unscale[q];
-        float mm = kMaskedScore;
-#pragma unroll
-        for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, mg[(w * 8 + q) * kPitch]);
-        float out;
-        if (c < 8) {
-            out = mm > -1.0e37f ? mm * rf * kLn2 : kMaskedScore;
-        } else {
-            const int src = c < 16 ? 1 : 2 + (c - 16);
-            out = 0.f;
+            for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, mg[(w * 8 + q) * kPitch]);
+            if (c == 0) return mm > -1.0e37f ? mm * rf * kLn2 : kMaskedScore;
+            float out = 0.f;
 #pragma unroll
             for (int w = 0; w < kDecWarps; ++w) {
                 const float* rw = mg + (w * 8 + q) * kPitch;
-                out += rw[src] * ex2f((rw[0] - mm) * rf);
+                out += rw[c] * ex2f((rw[0] - mm) * rf);
+            }
+            return out;
+        };
+        if constexpr (!STREAMK) {
+            if (!direct) {
+                for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
+                    const int q = i / kRecord, c = i % kRecord;
+                    rec_base[i] = merged(q, c < 8 ? 0 : c < 16 ? 1 : 2 + (c - 16));
+                }
+                return;
             }
         }
-        rec_base[i] = out;
+        {
+            constexpr int kRecPitch = L::kRecPitch;
+            float* rec = reinterpret_cast<float*>(ring + L::kMergeBytes);            // [8][kRecPitch]
+            float* ebuf = reinterpret_cast<float*>(ring + L::kMergeBytes + L::kRecBytes);   // [2][8][D]
+            bool finish = true;   // this CTA holds the head's complete state after the next block
+            if (seg_count == 1u) {
+                for (int i = tid; i < rows_here * kRecPitch; i += blockDim.x)
+                    rec[i] = merged(i / kRecPitch, i % kRecPitch);
+            } else {
+                // several CTAs share this head: publish the record, count the arrival, and let
+                // whoever arrives last merge all of them (nobody waits for anybody)
+                for (int i = tid; i < rows_here * kRecPitch; i += blockDim.x) {
+                    const int q = i / kRecPitch, c = i % kRecPitch;
+                    const float v = merged(q, c);
+                    float* dst = rec_base + q * kRecord;
+                    if (c >= 2) dst[16 + (c - 2)] = v;
+                    else
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) dst[c * 8 + k] = v;
+                }
+                __threadfence();
+                __syncthreads();
+                if (tid == 0) {
+                    uint32_t* word = p.counters + (static_cast<size_t>(item) * row_tiles + row_tile);
+                    uint32_t old = *reinterpret_cast<volatile uint32_t*>(word), want = 0;
+                    bool counted = false;
+                    // a word counts for this launch only under its tag; anything else is stale
+                    for (int it = 0; it < 64 && !counted; ++it) {
+                        want = ((old >> 8) == p.tag && (old & 0xFFu) < seg_count) ? old + 1u : ((p.tag << 8) | 1u);
+                        const uint32_t prev = atomicCAS(word, old, want);
+                        counted = prev == old;
+                        old = prev;
+                    }
+                    if (!counted) report(p.status, TQ_STATUS_WAIT_EXPIRED);
+                    const bool last = counted && (want & 0xFFu) == seg_count;
+                    if (last) *reinterpret_cast<volatile uint32_t*>(word) = 0u;   // leave it clean for the next launch
+                    sk_last = last ? 1u : 0u;
+                }
+                __syncthreads();
+                finish = sk_last != 0u;
+                if (finish) {
+                    __threadfence();
+                    const float* first = p.workspace +
+                                         ((static_cast<size_t>(item) * p.splits) * p.rows_stride + row_tile * 8u) * kRecord;
+                    const size_t slot_stride = static_cast<size_t>(p.rows_stride) * kRecord;
+                    for (int i = tid; i < rows_here * kRecPitch; i += blockDim.x) {
+                        const int q = i / kRecPitch, c = i % kRecPitch;
+                        const float* rq = first + q * kRecord;
+                        float mm = kMaskedScore;
+                        for (uint32_t k = 0; k < seg_count; ++k) mm = fmaxf(mm, __ldcg(rq + k * slot_stride));
+                        float out = mm;
+                        if (c != 0) {
+                            out = 0.f;
+                            const int src = c == 1 ? 8 : 16 + (c - 2);
+                            for (uint32_t k = 0; k < seg_count; ++k)
+                                out += __ldcg(rq + k * slot_stride + src) *
+                                       ex2f((__ldcg(rq + k * slot_stride) - mm) * kLog2e);
+                        }
+                        rec[i] = out;
+                    }
+                }
+            }
+            if (finish) {
+                __syncthreads();
+                for (int i = tid; i < rows_here * D; i += blockDim.x) {
+                    const int q = i / D, c = i % D;
+                    const float l = rec[q * kRecPitch + 1], a = rec[q * kRecPitch + 2 + c];
+                    ebuf[q * D + c] = l > 0.f ? a / l : 0.f;
+                }
+                __syncthreads();
+                egress_rows<D>(p, ebuf, rows_here, seq, head, row_tile, tokens_per_req, tid);
+            }
+        }
+        if constexpr (STREAMK) {
+            // ---- next segment of the share
+            sk_left -= sk_take;
+            if (sk_left == 0u) return;
+            sk_loc += sk_take;
+            if (sk_loc == sk_n * heads_per_seq) {
+                sk_before += sk_n;
+                sk_loc = 0;
+                do {   // tiles are left, so a sequence with tiles follows
+                    ++seq;
+                    if (seq >= p.items / p.H) return;
+                    sk_n = tiles_of(context_of(seq));
+                } while (sk_n == 0u);
+            }
+            __syncthreads();   // the epilogue buffers alias the ring and the prologue's query
+        } else {
+            return;
+        }
     }
 }
 
@@ -900,35 +1456,74 @@ static bool page_size_ok(uint32_t block_size, uint32_t* sp_shift)
 
 static bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0u; }
 
-template <int D, bool PRECISE, bool EXT>
+// A tag that no earlier launch used (24 bits, never zero): arrival counts of the persistent
+// grid are valid only under the tag of their own launch, so the counter words need no
+// clearing between launches and may start out as anything.
+static uint32_t next_launch_tag()
+{
+    static std::atomic<uint32_t> serial{0};
+    const uint32_t n = serial.fetch_add(1, std::memory_order_relaxed) + 1u;
+    const uint32_t tag = (n * 2654435761u) >> 8;
+    return tag ? tag : 1u;
+}
+
+template <int D, bool PRECISE, bool EXT, bool NZ, bool STREAMK>
 static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p)
 {
     // Opt in to the large dynamic shared-memory carve-out once per device. The
     // flags race benignly: setting the attribute twice is harmless.
     static bool configured[64] = {};
+    static int sm_count[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorNoDevice;
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(tq_decode_partial_kernel<D, PRECISE, EXT>,
+        cudaError_t e = cudaFuncSetAttribute(tq_decode_partial_kernel<D, PRECISE, EXT, NZ, STREAMK>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              DecodeSmem<D>::kTotal);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) {
+            sm_count[dev] = sms;
+            configured[dev] = true;
+        }
     }
-    const uint64_t grid = static_cast<uint64_t>(p.items) * ((p.rows + 7u) / 8u) * p.splits;
+    uint64_t grid = static_cast<uint64_t>(p.items) * ((p.rows + 7u) / 8u) * p.splits;
     if (grid == 0) return cudaSuccess;
+    if (STREAMK) {
+        int sms = dev >= 0 && dev < 64 ? sm_count[dev] : 0;
+        if (sms <= 0) sms = 148;
+        grid = static_cast<uint64_t>(sms) * DecodeSmem<D>::kCtasPerSm;   // one resident wave
+    }
     if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
-    tq_decode_partial_kernel<D, PRECISE, EXT><<<static_cast<unsigned>(grid), kDecWarps * 32,
+    tq_decode_partial_kernel<D, PRECISE, EXT, NZ, STREAMK><<<static_cast<unsigned>(grid), kDecWarps * 32,
                                   DecodeSmem<D>::kTotal, stream>>>(p);
     return cudaGetLastError();
 }
 
+// The classic grid: one CTA per (sequence, KV head, split, row tile), records only.
 template <int D, bool PRECISE>
 static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
 {
+    if constexpr (D == 256) {
+        if (p.nz_slot_floats != 0u) return launch_partial_as<D, PRECISE, true, true, false>(stream, p);
+    }
     if (p.q_f16 != 0u || p.tokens_per_req > 1u || p.q_f32 != nullptr || p.midrise != 0u)
-        return launch_partial_as<D, PRECISE, true>(stream, p);
-    return launch_partial_as<D, PRECISE, false>(stream, p);
+        return launch_partial_as<D, PRECISE, true, false, false>(stream, p);
+    return launch_partial_as<D, PRECISE, false, false, false>(stream, p);
+}
+
+// The persistent grid with the combine folded in (native precision only).
+template <int D>
+static cudaError_t launch_streamk(cudaStream_t stream, const DecodeParams& p)
+{
+    if constexpr (D == 256) {
+        if (p.nz_slot_floats != 0u) return launch_partial_as<D, false, true, true, true>(stream, p);
+    }
+    if (p.q_f16 != 0u || p.tokens_per_req > 1u || p.q_f32 != nullptr || p.midrise != 0u)
+        return launch_partial_as<D, false, true, false, true>(stream, p);
+    return launch_partial_as<D, false, false, false, true>(stream, p);
 }
 
 }  // namespace tq
@@ -957,6 +1552,9 @@ static void decode_plan(uint32_t batch, uint32_t num_kv_heads, uint32_t block_si
     if (chunk < block_size) chunk = block_size;
     *chunk_pages = static_cast<uint32_t>(chunk / block_size);
     *splits = static_cast<uint32_t>((max_context + chunk - 1u) / chunk);
+    // The persistent grid deals equal shares of tiles, so a head may straddle two CTAs even
+    // when one chunk would hold it: keep two record slots per head.
+    if (*splits < 2u) *splits = 2u;
 }
 
 extern "C" uint32_t tq_decode_choose_splits(uint32_t batch, uint32_t num_kv_heads,
@@ -974,7 +1572,10 @@ extern "C" size_t tq_decode_workspace_floats(uint32_t batch, uint32_t num_heads,
 {
     if (num_kv_heads == 0) return 0;
     const size_t rows = num_heads / num_kv_heads;
-    return static_cast<size_t>(batch) * num_kv_heads * splits * rows * (16u + head_size);
+    // the partial records, then one arrival counter per (sequence, KV head, 8-row tile) for
+    // the launches that fold the combine into the decode kernel
+    return static_cast<size_t>(batch) * num_kv_heads * splits * rows * (16u + head_size) +
+           static_cast<size_t>(batch) * num_kv_heads * ((rows + 7u) / 8u);
 }
 
 extern "C" int tq_decode_splitk_partials(void* stream, const uint16_t* q, const void* signs,
@@ -993,7 +1594,8 @@ extern "C" int tq_decode_splitk_partials(void* stream, const uint16_t* q, const 
         block_size % kStrip != 0 || seq_pages > cache_pages || page_begin > seq_pages ||
         page_count > seq_pages - page_begin || rows == 0 || rows > 16 ||
         (head_size != 128 && head_size != 256) ||
-        (sign_source != TQ_SIGNS_F32 && sign_source != TQ_SIGNS_TABLES_BF16))
+        (sign_source != TQ_SIGNS_F32 && sign_source != TQ_SIGNS_TABLES_BF16) ||
+        !(softmax_scale > 0.0f) || !(softmax_scale <= 3.0e38f))
         return TQ_ERR_INVALID_ARGUMENT;
     if (seq_len != 0u) {
         if (static_cast<uint64_t>(seq_len) > static_cast<uint64_t>(cache_pages) * block_size)
@@ -1093,40 +1695,57 @@ static uint32_t resolve_splits(uint32_t splits, uint32_t batch, uint32_t num_kv_
     return s;
 }
 
-// The export stage with its split plan resolved: `splits` partitions per sequence in the
-// workspace, of which a sequence uses ceil(pages / chunk_pages) when chunk_pages != 0.
-static int decode_export_planned(void* stream, const uint16_t* query, const int8_t* key_cache,
-                                 const int8_t* value_cache, const float* scale_cache,
-                                 const int32_t* block_tables, const int32_t* context_lens,
-                                 const float* pi_signs, float* workspace, uint32_t batch,
-                                 uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
-                                 uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
-                                 uint32_t splits, uint32_t chunk_pages, float inv_sqrt_len,
-                                 float softmax_scale, uint32_t* status, bool q_f16 = false,
-                                 uint32_t tokens_per_req = 1, const float* query_rot_f32 = nullptr,
-                                 uint32_t midrise = 0)
+// What the serving entries add to the plain decode.
+struct DecodeOptions {
+    bool q_f16 = false;                  // FP16 query whose rotation stays FP32
+    uint32_t tokens_per_req = 1;         // query tokens per request
+    const float* query_rot_f32 = nullptr;  // pre-rotated FP32 query (replaces query and signs)
+    uint32_t midrise = 0;                // codes on the uniform mid-rise grid
+    uint32_t rotation = ~0u;             // egress rotation of the combine (~0: from pi_signs)
+    uint32_t gate_dtype = TQ_DTYPE_F32;
+    uint32_t nz_slot_floats = 0;         // != 0: NZ-tiled source pools, floats per slot of the scale records
+    float nz_gain = 1.0f;                // the codebook gain those scales are divided by
+    bool precise = false;                // 24-bit fixed-point query and P as hi + lo halves (classic grid)
+};
+
+// Validates a decode call and fills the kernel parameters (everything but the combine part).
+static int decode_params(DecodeParams& p, const uint16_t* query, const int8_t* key_cache,
+                         const int8_t* value_cache, const float* scale_cache,
+                         const int32_t* block_tables, const int32_t* context_lens,
+                         const float* pi_signs, float* workspace, uint32_t batch,
+                         uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                         uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                         uint32_t splits, uint32_t chunk_pages, float inv_sqrt_len,
+                         float softmax_scale, uint32_t* status, const DecodeOptions& o,
+                         bool needs_workspace = true)
 {
     if (!num_heads || !num_kv_heads || num_heads % num_kv_heads != 0 || !block_size ||
         block_size % kStrip != 0 || !num_blocks || !max_blocks || !splits || splits > 16 ||
         (head_size != 128 && head_size != 256))
         return TQ_ERR_INVALID_ARGUMENT;
-    const uint32_t rows = num_heads / num_kv_heads * tokens_per_req;
-    if (rows > 16 || tokens_per_req == 0) return TQ_ERR_INVALID_ARGUMENT;
+    // the kernels take the maximum of raw scores before the positive per-row factor is applied
+    if (!(softmax_scale > 0.0f) || !(softmax_scale <= 3.0e38f)) return TQ_ERR_INVALID_ARGUMENT;
+    const uint32_t rows = num_heads / num_kv_heads * o.tokens_per_req;
+    if (rows > 16 || o.tokens_per_req == 0) return TQ_ERR_INVALID_ARGUMENT;
+    if (o.nz_slot_floats != 0u &&
+        (head_size != 256 || (block_size != 64 && block_size != 128) || !(o.nz_gain > 0.0f) ||
+         o.nz_slot_floats < 2u * num_kv_heads))
+        return TQ_ERR_INVALID_ARGUMENT;
     if (batch == 0) return TQ_OK;
     // a pre-rotated FP32 query replaces both the 16-bit query and the sign diagonal
-    if ((!query || !pi_signs) && !query_rot_f32) return TQ_ERR_INVALID_ARGUMENT;
-    if (!key_cache || !value_cache || !scale_cache || !block_tables || !context_lens || !workspace)
+    if ((!query || !pi_signs) && !o.query_rot_f32) return TQ_ERR_INVALID_ARGUMENT;
+    if (!key_cache || !value_cache || !scale_cache || !block_tables || !context_lens ||
+        (needs_workspace && !workspace))
         return TQ_ERR_INVALID_ARGUMENT;
     uint32_t sp_shift = 0;
     if (!page_size_ok(block_size, &sp_shift) || !aligned16(key_cache) || !aligned16(value_cache) ||
         !aligned16(scale_cache))
         return TQ_ERR_INVALID_ARGUMENT;
-    DecodeParams p{};
-    p.tokens_per_req = 1;
+    p = DecodeParams{};
     p.sp_shift = sp_shift;
     p.q = query;
-    p.q_f32 = query_rot_f32;
-    p.midrise = midrise;
+    p.q_f32 = o.query_rot_f32;
+    p.midrise = o.midrise;
     p.signs = pi_signs;
     p.sign_source = TQ_SIGNS_F32;
     p.key_cache = reinterpret_cast<const uint8_t*>(key_cache);
@@ -1145,16 +1764,40 @@ static int decode_export_planned(void* stream, const uint16_t* query, const int8
     p.table_stride = max_blocks;
     p.splits = splits;
     p.chunk_pages = chunk_pages;
-    p.q_f16 = q_f16 ? 1u : 0u;
-    p.tokens_per_req = tokens_per_req;
+    p.q_f16 = o.q_f16 ? 1u : 0u;
+    p.tokens_per_req = o.tokens_per_req;
     p.page_begin = 0;
     p.page_count = 0;
     p.fixed_ctx = 0;
     p.inv_sqrt_len = inv_sqrt_len;
     p.softmax_scale = softmax_scale;
     p.status = status;
+    p.nz_slot_floats = o.nz_slot_floats;
+    p.nz_gain = o.nz_gain;
+    return TQ_OK;
+}
+
+// The export stage with its split plan resolved: `splits` partitions per sequence in the
+// workspace, of which a sequence uses ceil(pages / chunk_pages) when chunk_pages != 0.
+static int decode_export_planned(void* stream, const uint16_t* query, const int8_t* key_cache,
+                                 const int8_t* value_cache, const float* scale_cache,
+                                 const int32_t* block_tables, const int32_t* context_lens,
+                                 const float* pi_signs, float* workspace, uint32_t batch,
+                                 uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                                 uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                                 uint32_t splits, uint32_t chunk_pages, float inv_sqrt_len,
+                                 float softmax_scale, uint32_t* status, const DecodeOptions& o = {})
+{
+    DecodeParams p{};
+    const int st = decode_params(p, query, key_cache, value_cache, scale_cache, block_tables,
+                                 context_lens, pi_signs, workspace, batch, num_heads, num_kv_heads,
+                                 head_size, block_size, num_blocks, max_blocks, splits, chunk_pages,
+                                 inv_sqrt_len, softmax_scale, status, o);
+    if (st != TQ_OK || batch == 0) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const cudaError_t e = head_size == 128 ? launch_partial<128, false>(s, p) : launch_partial<256, false>(s, p);
+    cudaError_t e;
+    if (o.precise) e = head_size == 128 ? launch_partial<128, true>(s, p) : launch_partial<256, true>(s, p);
+    else e = head_size == 128 ? launch_partial<128, false>(s, p) : launch_partial<256, false>(s, p);
     return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 
@@ -1179,6 +1822,11 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
                                  inv_sqrt_len, softmax_scale, status);
 }
 
+// One decode call, split plan resolved. A plan the library made itself (chunk_pages != 0)
+// runs on the persistent grid, which deals the batch's tiles to one resident wave of CTAs in
+// equal shares and folds the combine in: one launch, no second pass over the records. A split
+// count the caller fixed keeps the reference's page partition per sequence: the classic grid
+// exports `splits` records per head and the combine kernel merges them.
 static int decode_planned(void* stream, const uint16_t* query, const int8_t* key_cache,
                           const int8_t* value_cache, const float* scale_cache,
                           const int32_t* block_tables, const int32_t* context_lens,
@@ -1187,24 +1835,53 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
                           uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
                           uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
                           uint32_t chunk_pages, uint32_t output_stage, float inv_sqrt_len,
-                          float softmax_scale, uint32_t* status, uint32_t gate_dtype = TQ_DTYPE_F32,
-                          bool q_f16 = false, uint32_t tokens_per_req = 1,
-                          const float* query_rot_f32 = nullptr, uint32_t midrise = 0,
-                          uint32_t rotation = ~0u)
+                          float softmax_scale, uint32_t* status, const DecodeOptions& o = {})
 {
-    if (output_stage > TQ_OUT_GATED || !output || (output_stage == TQ_OUT_GATED && !gate))
+    if (output_stage > TQ_OUT_GATED || out_dtype > TQ_DTYPE_F32 || o.gate_dtype > TQ_DTYPE_F32 || !output ||
+        (output_stage == TQ_OUT_GATED && !gate))
         return TQ_ERR_INVALID_ARGUMENT;
+    const uint32_t rotation = o.rotation != ~0u ? o.rotation : (pi_signs == nullptr ? 1u : 0u);
+    const bool persistent = chunk_pages != 0u && splits >= 2u && !o.precise;
+    if (persistent || splits == 1u) {
+        // one launch: the persistent grid, or (one split) the classic grid whose CTAs hold a
+        // head's whole state and write the output themselves without touching the workspace
+        DecodeParams p{};
+        const int st = decode_params(p, query, key_cache, value_cache, scale_cache, block_tables,
+                                     context_lens, pi_signs, workspace, batch, num_heads, num_kv_heads,
+                                     head_size, block_size, num_blocks, max_blocks, splits, chunk_pages,
+                                     inv_sqrt_len, softmax_scale, status, o, persistent);
+        if (st != TQ_OK || batch == 0) return st;
+        if (output_stage != TQ_OUT_ROTATED && rotation != 1u && !pi_signs) return TQ_ERR_INVALID_ARGUMENT;
+        if (persistent) {
+            // the counters follow the records (tq_decode_workspace_floats)
+            p.counters = reinterpret_cast<uint32_t*>(
+                workspace + static_cast<size_t>(batch) * num_kv_heads * splits * p.rows * (16u + head_size));
+            p.tag = next_launch_tag();
+        }
+        p.egress_signs = pi_signs;
+        p.gate = gate;
+        p.output = output;
+        p.output_stage = output_stage;
+        p.out_dtype = out_dtype;
+        p.gate_dtype = o.gate_dtype;
+        p.rotation = rotation;
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        cudaError_t e;
+        if (persistent) e = head_size == 128 ? launch_streamk<128>(s, p) : launch_streamk<256>(s, p);
+        else if (o.precise) e = head_size == 128 ? launch_partial<128, true>(s, p) : launch_partial<256, true>(s, p);
+        else e = head_size == 128 ? launch_partial<128, false>(s, p) : launch_partial<256, false>(s, p);
+        return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+    }
     const int st = decode_export_planned(stream, query, key_cache, value_cache, scale_cache,
                                          block_tables, context_lens, pi_signs, workspace, batch,
                                          num_heads, num_kv_heads, head_size, block_size, num_blocks,
                                          max_blocks, splits, chunk_pages, inv_sqrt_len,
-                                         softmax_scale, status, q_f16, tokens_per_req, query_rot_f32,
-                                         midrise);
+                                         softmax_scale, status, o);
     if (st != TQ_OK || batch == 0) return st;
-    const uint32_t rows = num_heads / num_kv_heads * tokens_per_req;
-    return splitk_combine(stream, workspace, pi_signs, gate, gate_dtype, output, out_dtype,
+    const uint32_t rows = num_heads / num_kv_heads * o.tokens_per_req;
+    return splitk_combine(stream, workspace, pi_signs, gate, o.gate_dtype, output, out_dtype,
                           batch * num_kv_heads, rows, rows, head_size, splits, output_stage,
-                          inv_sqrt_len, tokens_per_req, num_kv_heads, rotation);
+                          inv_sqrt_len, o.tokens_per_req, num_kv_heads, rotation);
 }
 
 // Query, gate and output in ONE 16-bit element type, FP16 or BF16, as the raw-query entry of
@@ -1229,11 +1906,13 @@ extern "C" int tq_decode_splitk_elem(void* stream, const void* query, const int8
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
                             &chunk_pages);
+    DecodeOptions o;
+    o.gate_dtype = elem_dtype;
+    o.q_f16 = elem_dtype == TQ_DTYPE_F16;
     return decode_planned(stream, static_cast<const uint16_t*>(query), key_cache, value_cache, scale_cache,
                           block_tables, context_lens, pi_signs, gate, workspace, output, elem_dtype, batch,
                           num_heads, num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,
-                          chunk_pages, output_stage, inv_sqrt_len, softmax_scale, status, elem_dtype,
-                          elem_dtype == TQ_DTYPE_F16);
+                          chunk_pages, output_stage, inv_sqrt_len, softmax_scale, status, o);
 }
 
 extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_t* key_cache,
@@ -1277,10 +1956,12 @@ extern "C" int tq_decode_splitk_mtp(void* stream, const uint16_t* query, const i
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
                             &chunk_pages);
+    DecodeOptions o;
+    o.tokens_per_req = tokens_per_req;
     return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables, context_lens,
                           pi_signs, gate, workspace, output, out_dtype, batch, num_heads, num_kv_heads,
                           head_size, block_size, num_blocks, max_blocks, splits, chunk_pages, output_stage,
-                          inv_sqrt_len, softmax_scale, status, TQ_DTYPE_F32, false, tokens_per_req);
+                          inv_sqrt_len, softmax_scale, status, o);
 }
 
 // The pre-rotated entry of the reference's fused decoder (launch_fused_decode_opt,
@@ -1314,11 +1995,87 @@ extern "C" int tq_decode_splitk_prerotated(void* stream, const float* query_rot,
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
                             &chunk_pages);
     const float inv_sqrt_len = head_size == 128 ? 0.08838834764831845f : 0.0625f;
+    DecodeOptions o;
+    o.gate_dtype = gate_dtype;
+    o.query_rot_f32 = query_rot;
+    o.midrise = code_grid;
+    o.rotation = 2u;
     return decode_planned(stream, nullptr, key_cache, value_cache, scale_cache, block_tables, context_lens,
                           pi_signs, gate, workspace, output, out_dtype, batch, num_heads, num_kv_heads,
                           head_size, block_size, num_blocks, max_blocks, splits, chunk_pages,
-                          output_stage, inv_sqrt_len, softmax_scale, status, gate_dtype, false, 1, query_rot,
-                          code_grid, 2u);
+                          output_stage, inv_sqrt_len, softmax_scale, status, o);
+}
+
+// tq_decode_splitk with the wider arithmetic of the reference-contract entry: the query as a
+// 24-bit fixed point (three limbs) and P as a hi + lo pair of halves, so the error no longer
+// scales with the magnitude of the values. For callers whose values are far from unit
+// variance. Classic grid and combine kernel; about half the speed of tq_decode_splitk.
+extern "C" int tq_decode_splitk_precise(void* stream, const uint16_t* query, const int8_t* key_cache,
+                                        const int8_t* value_cache, const float* scale_cache,
+                                        const int32_t* block_tables, const int32_t* context_lens,
+                                        const float* pi_signs, const float* gate, float* workspace,
+                                        void* output, uint32_t out_dtype, uint32_t batch,
+                                        uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                                        uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                                        uint32_t splits, uint32_t max_context_hint,
+                                        uint32_t output_stage, float inv_sqrt_len, float softmax_scale,
+                                        uint32_t* status)
+{
+    if (!num_kv_heads || !block_size || splits > 16) return TQ_ERR_INVALID_ARGUMENT;
+    uint32_t chunk_pages = 0;
+    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
+                            &chunk_pages);
+    DecodeOptions o;
+    o.precise = true;
+    return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
+                          context_lens, pi_signs, gate, workspace, output, out_dtype, batch, num_heads,
+                          num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,
+                          chunk_pages, output_stage, inv_sqrt_len, softmax_scale, status, o);
+}
+
+// Decode over the fused decoder's KV4 cache where it lies: nz_key / nz_value are its NZ-tiled
+// packed pools and nz_scales its per-slot scale records (see tq_nz_kv4_import for the format),
+// read in place -- no second pool, no re-tiling pass. The strips of a 64-row tile are staged
+// with their rows permuted so that both contractions read them without bank conflicts; keys
+// feed the integer MMA as they are (a fixed permutation of the contraction index, applied to
+// the query fragments once), and the token pairs the value contraction needs are put together
+// from the words of two token rows with one byte permute per four channels. The stored scale
+// is divided by `gain` on the way in (IEEE division, as the importer does), so records and
+// outputs equal those of tq_nz_kv4_import followed by tq_decode_splitk_prerotated bit for
+// bit. Head size 256, pages of 64 or 128 slots. num_blocks 0 = unknown (page numbers are then
+// not range-checked). precise != 0 selects the wider arithmetic of tq_decode_splitk_precise.
+// Other arguments as for tq_decode_splitk_prerotated.
+extern "C" int tq_decode_splitk_nz(void* stream, const float* query_rot, const uint8_t* nz_key,
+                                   const uint8_t* nz_value, const float* nz_scales,
+                                   const int32_t* block_tables, const int32_t* context_lens,
+                                   const float* pi_signs, const void* gate, float* workspace,
+                                   void* output, uint32_t out_dtype, uint32_t gate_dtype, uint32_t batch,
+                                   uint32_t num_heads, uint32_t num_kv_heads, uint32_t block_size,
+                                   uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                                   uint32_t max_context_hint, uint32_t code_grid, uint32_t output_stage,
+                                   float gain, float inv_sqrt_len, float softmax_scale, uint32_t precise,
+                                   uint32_t* status)
+{
+    if (!num_kv_heads || (block_size != 64 && block_size != 128) || splits > 16 || code_grid > 1u ||
+        (batch != 0 && !query_rot) || output_stage > TQ_OUT_GATED || gate_dtype > TQ_DTYPE_F32 ||
+        (output_stage != TQ_OUT_ROTATED && !pi_signs) || !(gain > 0.0f))
+        return TQ_ERR_INVALID_ARGUMENT;
+    uint32_t chunk_pages = 0;
+    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
+                            &chunk_pages);
+    DecodeOptions o;
+    o.gate_dtype = gate_dtype;
+    o.query_rot_f32 = query_rot;
+    o.midrise = code_grid;
+    o.rotation = 2u;
+    o.nz_slot_floats = (2u * num_kv_heads + 7u) / 8u * 8u;
+    o.nz_gain = gain;
+    o.precise = precise != 0u;
+    return decode_planned(stream, nullptr, reinterpret_cast<const int8_t*>(nz_key),
+                          reinterpret_cast<const int8_t*>(nz_value), nz_scales, block_tables, context_lens,
+                          pi_signs, gate, workspace, output, out_dtype, batch, num_heads, num_kv_heads, 256,
+                          block_size, num_blocks ? num_blocks : 0x7FFFFFFFu, max_blocks, splits, chunk_pages,
+                          output_stage, inv_sqrt_len, softmax_scale, status, o);
 }
 
 // ------------------------------------------------- decode without a caller workspace
@@ -1333,24 +2090,32 @@ static __device__ __align__(256) float g_static_workspace[TQ_STATIC_WORKSPACE_FL
 
 // In host code `g_static_workspace` is only a handle for the device symbol, not a
 // device address: the address is looked up once per device, with that device current.
+// The per-device slot is an atomic: threads that race on a device's first call each make
+// the query and store the same address. The cached address belongs to the device's primary
+// context; a host that destroys that context (cudaDeviceReset) must not call this again
+// from the same process image, the slot is not re-validated.
 static float* static_workspace_address(int* status)
 {
-    static float* address[64] = {};
+    static std::atomic<float*> address[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        (void)cudaGetLastError();
         *status = TQ_ERR_NO_DEVICE;
         return nullptr;
     }
-    if (address[dev] == nullptr) {
+    float* cached = address[dev].load(std::memory_order_acquire);
+    if (cached == nullptr) {
         void* ptr = nullptr;
         if (cudaGetSymbolAddress(&ptr, g_static_workspace) != cudaSuccess || ptr == nullptr) {
-            *status = TQ_ERR_NO_DEVICE;
+            (void)cudaGetLastError();   // leave no sticky-looking error behind for the caller
+            *status = TQ_ERR_LAUNCH;
             return nullptr;
         }
-        address[dev] = static_cast<float*>(ptr);
+        cached = static_cast<float*>(ptr);
+        address[dev].store(cached, std::memory_order_release);
     }
     *status = TQ_OK;
-    return address[dev];
+    return cached;
 }
 
 extern "C" int tq_decode_splitk_static(void* stream, const uint16_t* query, const int8_t* key_cache,
@@ -1364,7 +2129,10 @@ extern "C" int tq_decode_splitk_static(void* stream, const uint16_t* query, cons
                                        uint32_t max_context_hint, uint32_t output_stage,
                                        float inv_sqrt_len, float softmax_scale, uint32_t* status)
 {
-    if (!num_kv_heads || !block_size || splits > 16) return TQ_ERR_INVALID_ARGUMENT;
+    // geometry first, so that nonsense is refused as nonsense and not as "too large"
+    if (!num_kv_heads || !num_heads || num_heads % num_kv_heads != 0 || num_heads / num_kv_heads > 16 ||
+        !block_size || block_size % kStrip != 0 || splits > 16 || (head_size != 128 && head_size != 256))
+        return TQ_ERR_INVALID_ARGUMENT;
     // Resolve the split count first: it decides how much of the array the launch needs.
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
@@ -1374,8 +2142,9 @@ extern "C" int tq_decode_splitk_static(void* stream, const uint16_t* query, cons
     int st = TQ_OK;
     float* workspace = static_workspace_address(&st);
     if (workspace == nullptr) return st;
-    // Every partition the combine reads is written by this launch first (empty splits
-    // export the neutral element), so nothing in the array has to start at zero.
+    // Every record that is merged is written by this launch first, and the arrival counters
+    // behind the records are valid only under the launch's own tag, so nothing in the array
+    // has to start at zero.
     return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
                           context_lens, pi_signs, gate, workspace, output, out_dtype, batch, num_heads,
                           num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,

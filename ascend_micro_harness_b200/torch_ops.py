@@ -80,7 +80,10 @@ def _paged_decode(query, gate, key_cache, value_cache, scale_cache, block_tables
                   num_blocks=_num_blocks(key_cache, num_kv_heads, head_size, block_size),
                   inv_sqrt_len=_inv_sqrt(head_size), softmax_scale=scale_value, splits=temporal_splits,
                   workspace=workspace, gate=gate, output_stage=output_stage)
-    if gate is not None and gate.dtype != torch.float32:
+    # route by the query's element type: float16 queries, and bfloat16 queries whose gate shares
+    # the element type, take the one-element-type entry; bfloat16 with an FP32 gate (or none)
+    # the plain one
+    if query.dtype == torch.float16 or (gate is not None and gate.dtype != torch.float32):
         engine.decode_splitk_elem(query, key_cache, value_cache, scale_cache, block_tables, seq_lens, pi_signs,
                                   out, **kwargs)
     else:
@@ -98,8 +101,13 @@ def _decode_combine(workspace, gate, pi_signs, num_heads, num_kv_heads, temporal
 
 
 def _workspace_size(num_reqs, num_heads, num_kv_heads, head_size, temporal_splits):
+    """Floats of workspace (tq_decode_workspace_floats): the records of every split plus one
+    arrival counter per (request, KV head, 8-row tile). temporal_splits 0 leaves the choice to
+    the launch, which never takes more than 16: sized for that."""
     rows = num_heads // num_kv_heads
-    return num_reqs * num_kv_heads * temporal_splits * rows * (16 + head_size)
+    splits = temporal_splits if temporal_splits else 16
+    return (num_reqs * num_kv_heads * splits * rows * (16 + head_size)
+            + num_reqs * num_kv_heads * ((rows + 7) // 8))
 
 
 for _name, _fn in (("reshape_aligned", _reshape_aligned), ("reshape_scatter", _reshape_scatter),

@@ -143,8 +143,8 @@ int tq_reshape_scatter(void* stream, const uint16_t* key, const uint16_t* value,
  *   context_lens  int32 [batch], live tokens per sequence
  *   pi_signs      float [d]
  *   gate          float [batch][num_heads][d], read only by TQ_OUT_GATED
- *   workspace     float [tq_decode_workspace_floats(...)]; unused when the
- *                 launch resolves to one split
+ *   workspace     float [tq_decode_workspace_floats(...)]; always required (a launch
+ *                 that resolves to one split still writes its records there)
  *   output        [batch][num_heads][d] of out_dtype (TQ_DTYPE_*)
  *   splits        1..16, or 0 to choose from context lengths and SM count;
  *                 max_context_hint (0 = max_blocks*block_size) feeds that choice
@@ -159,6 +159,20 @@ int tq_decode_splitk(void* stream, const uint16_t* query, const int8_t* key_cach
                      uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
                      uint32_t max_context_hint, uint32_t output_stage, float inv_sqrt_len,
                      float softmax_scale, uint32_t* status);
+
+/* tq_decode_splitk with a 24-bit fixed-point query and the softmax weights carried as a
+ * hi + lo pair of halves (the arithmetic of tq_decode_splitk_partials, whose records are held
+ * to the reference rig's tolerances, tests/npu/turboquant_splitk_rigs.hpp:144-215): the error
+ * no longer grows with the magnitude of the cached values. Same arguments. */
+int tq_decode_splitk_precise(void* stream, const uint16_t* query, const int8_t* key_cache,
+                             const int8_t* value_cache, const float* scale_cache,
+                             const int32_t* block_tables, const int32_t* context_lens,
+                             const float* pi_signs, const float* gate, float* workspace,
+                             void* output, uint32_t out_dtype, uint32_t batch, uint32_t num_heads,
+                             uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                             uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                             uint32_t max_context_hint, uint32_t output_stage, float inv_sqrt_len,
+                             float softmax_scale, uint32_t* status);
 
 /* The first half of tq_decode_splitk on its own: every (sequence, KV head, split)
  * exports its partial record into `workspace`, nothing is merged. Followed by
@@ -181,7 +195,10 @@ uint32_t tq_decode_choose_splits(uint32_t batch, uint32_t num_kv_heads, uint32_t
 /* Floats of workspace a decode launch with this many splits needs:
  * batch * num_kv_heads * splits partitions of (num_heads/num_kv_heads) rows,
  * each row {m x8, l x8, acc[d]}, the record of
- * include/turboquant_splitk_contract.hpp:23-27 with kChannels -> head_size. */
+ * include/turboquant_splitk_contract.hpp:23-27 with kChannels -> head_size,
+ * followed by one 32-bit arrival counter per (sequence, KV head, 8-row tile)
+ * for the launches that merge inside the decode kernel. The counters need no
+ * initialisation. For splits == 0 size it with tq_decode_choose_splits. */
 size_t tq_decode_workspace_floats(uint32_t batch, uint32_t num_heads, uint32_t num_kv_heads,
                                   uint32_t head_size, uint32_t splits);
 
@@ -309,6 +326,22 @@ int tq_decode_splitk_prerotated(void* stream, const float* query_rot, const int8
                                 uint32_t splits, uint32_t max_context_hint, uint32_t code_grid,
                                 uint32_t output_stage, float softmax_scale, uint32_t* status);
 
+/* The same decode over the NZ-tiled pools themselves: no import, no second pool. nz_key,
+ * nz_value and nz_scales are the fused decoder's buffers as described above (head size 256,
+ * block_size 64 or 128); each stored scale is divided by `gain` on the way in, exactly as
+ * tq_nz_kv4_import does, so the results equal import + tq_decode_splitk_prerotated bit for
+ * bit. This is what launch_fused_decode_opt[_raw_query] run. num_blocks 0 = unknown (page
+ * numbers are not range-checked); inv_sqrt_len scales the egress rotation of stages 1 and 2;
+ * precise != 0 selects the arithmetic of tq_decode_splitk_precise. */
+int tq_decode_splitk_nz(void* stream, const float* query_rot, const uint8_t* nz_key,
+                        const uint8_t* nz_value, const float* nz_scales, const int32_t* block_tables,
+                        const int32_t* context_lens, const float* pi_signs, const void* gate,
+                        float* workspace, void* output, uint32_t out_dtype, uint32_t gate_dtype,
+                        uint32_t batch, uint32_t num_heads, uint32_t num_kv_heads, uint32_t block_size,
+                        uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                        uint32_t max_context_hint, uint32_t code_grid, uint32_t output_stage, float gain,
+                        float inv_sqrt_len, float softmax_scale, uint32_t precise, uint32_t* status);
+
 /* Pi q for `rows` FP16 or BF16 (elem_dtype) query vectors of head_size 128 or 256, FP32 out: the
  * rotated image tq_decode_splitk_prerotated takes, Pi = diag(pi_signs) H diag(pi_signs) /
  * sqrt(head_size) -- the prologue of the fused decoder's raw-query entry
@@ -368,14 +401,43 @@ int tq_decode_lloydmax_export(void* stream, const uint16_t* query, const int8_t*
                               uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
                               float softmax_scale, uint32_t* status);
 
+/* ------------------------------------------------- fused decoder descriptors
+ * Field-for-field mirrors of ascend_micro::fused_decode_opt::Launch, Buffers and
+ * RawQueryBuffers (include/turboquant_fused_decode_opt.hpp:108-133,:149-170), so that a
+ * caller built against the reference's header passes its own structs unchanged. */
+typedef struct tq_fused_launch {
+    uint32_t grid, tokens, heads, kv_heads;
+    uint32_t head_size, block_size, max_blocks;
+    uint32_t splits, heads_per_task, tasks_per_block;
+    uint32_t reduce_tasks_per_block, fused_context_limit;
+    float scale, inv_sqrt_len;
+    uint32_t prologue_vectors_per_block, prologue_cube_chunk_vectors;
+    uint32_t output_stage;
+    uint32_t element_type; /* 0 = FP16, 1 = BF16 query / gate / output elements */
+    uint32_t probe_page, probe_tile;
+} tq_fused_launch;
+
+typedef struct tq_fused_buffers {
+    void *query, *key, *value, *scales, *block_table, *context_lengths;
+    void *mode_tables, *workspace, *output;
+    void* tiling;
+} tq_fused_buffers;
+
+typedef struct tq_fused_raw_query_buffers {
+    void *raw_query, *pi_signs, *rot_tables, *h16, *gate;
+    tq_fused_buffers decode;
+} tq_fused_raw_query_buffers;
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif
 
 /* ------------------------------------------------ reference-named launchers
  * Declared for C++ callers only: they throw std::invalid_argument. Signatures
- * are those of the reference (file:line beside each). */
-#ifdef __cplusplus
+ * are those of the reference (file:line beside each). A translation unit that also
+ * includes the reference's own headers defines TQ_B200_NO_REFERENCE_LAUNCHERS first:
+ * the symbols are the same, the C++ parameter types of the two declarations are not. */
+#if defined(__cplusplus) && !defined(TQ_B200_NO_REFERENCE_LAUNCHERS)
 extern "C" {
 /* kernels/ops/turboquant/turboquant_reshape_and_cache_a8.cpp:1578-1585 */
 void launch_turboquant_reshape_and_cache_a8(
@@ -403,6 +465,16 @@ void launch_turboquant_paged_decode_splitk_aic(
     uint32_t* table, uint16_t* qrot, float* workspace, uint32_t requests, uint32_t heads,
     uint32_t block_size, uint32_t cache_pages, uint32_t seq_pages, uint32_t splits,
     uint32_t page_begin, uint32_t page_count, uint32_t seq_len);
+/* include/turboquant_fused_decode_opt.hpp:172-174: the pre-rotated entry. buffers->query is the
+ * FP32 rotated query [tokens][heads][256]; key / value / scales the KV4 NZ-tiled cache;
+ * workspace at least tokens * heads * splits * 272 floats; output [tokens][heads][256] of the
+ * launch's element type, context in the rotated basis. */
+void launch_fused_decode_opt(void* stream, const tq_fused_launch* launch, const tq_fused_buffers* buffers);
+/* include/turboquant_fused_decode_opt.hpp:178-180: the raw-query entry. raw_query and gate are
+ * of the launch's element type, pi_signs float[256]; decode.query is WRITTEN (Pi raw_query,
+ * FP32) and then read; launch->output_stage 0 / 1 / 2. */
+void launch_fused_decode_opt_raw_query(void* stream, const tq_fused_launch* launch,
+                                       const tq_fused_raw_query_buffers* buffers);
 }
 #endif
 

@@ -19,9 +19,20 @@ ORACLE_SO = os.path.join(HERE, "libtq_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libtq_ref.so")
 
 
-def build(ref_root: str = "/root/reference") -> None:
+def reference_root():
+    """A checkout of the reference project: $TQ_REFERENCE_ROOT, else a directory named
+    `reference` beside this repository; None when neither is there."""
+    for cand in (os.environ.get("TQ_REFERENCE_ROOT"), os.path.join(HERE, "..", "..", "reference")):
+        if cand and os.path.exists(os.path.join(cand, "tests", "common", "turboquant_oracle.hpp")):
+            return os.path.abspath(cand)
+    return None
+
+
+def build(ref_root=None) -> None:
     """Compile the oracle (and the reference bridge when the reference is present)."""
-    subprocess.run(["make", "-C", HERE, f"REF={ref_root}"], check=True, capture_output=True)
+    ref_root = ref_root or reference_root()
+    cmd = ["make", "-C", HERE] + ([f"REF={ref_root}"] if ref_root else [])
+    subprocess.run(cmd, check=True, capture_output=True)
 
 
 def _p(a, t=C.c_void_p):
@@ -376,6 +387,31 @@ class Reference:
                                             C.c_int(rows), C.c_int(page_tokens), C.c_int(live),
                                             C.c_int(fill))
         return RefDecodeFixture(self, C.c_void_p(h))
+
+    def single_token_fixture(self, pages):
+        """The reference's 6-row single-token decode fixture (1 request, 4 KV heads x 6 query
+        rows, head size 256, 128-token pages, `pages` <= 8): raw bf16 query [4][6][256], the
+        strip cache (unmapped pages keep 0xAA bytes / NaN scales), the block table."""
+        q = np.zeros(4 * 6 * 256, np.uint16)
+        key = np.full(9 * 4 * 8 * 2048, 0xAA, np.uint8)
+        value = np.full_like(key, 0xAA)
+        scales = np.full(2 * 9 * 4 * 128, np.nan, np.float32)
+        table = np.zeros(pages, np.int32)
+        self.lib.ref_single_token_fixture(C.c_int(pages), _p(q), _p(key), _p(value), _p(scales), _p(table))
+        gate = np.zeros(4 * 6 * 256, np.float32)
+        self.lib.ref_single_token_gate(_p(gate))
+        return dict(q=q.reshape(4, 6, 256), key=key, value=value, scales=scales, table=table,
+                    gate=gate.reshape(4, 6, 256))
+
+    def single_token_golden(self, head, pages):
+        """GoldenDecode of the fixture for one KV head: m, l [6]; acc, rotated, context, q_rot [6][256]."""
+        m, l = np.zeros(6, np.float32), np.zeros(6, np.float32)
+        arrs = [np.zeros((6, 256), np.float32) for _ in range(4)]
+        self.lib.ref_single_token_golden(C.c_int(head), C.c_int(pages), _p(m), _p(l), *[_p(a) for a in arrs])
+        return dict(m=m, l=l, acc=arrs[0], rotated=arrs[1], context=arrs[2], q_rot=arrs[3])
+
+    def fused_descriptor_layout_matches(self):
+        return bool(self.lib.ref_fused_descriptor_layout_matches())
 
     def rotation_table_bf16(self):
         out = np.zeros(16 * 1024, np.uint16)

@@ -13,9 +13,12 @@
 //   include/turboquant_splitk_contract.hpp      Partition, workspace ABI
 //   include/routines/routine_vector_lloydmax_quantize.hpp  Lloyd-Max codebook
 //   tests/common/fused_decode_opt_fixture.hpp   KV4/FP8 NZ-tiled cache fixture + FP64 oracle
+//   tests/common/single_token_decode_oracle.hpp 6-row single-token decode fixture + golden model
+//   include/turboquant_fused_decode_opt.hpp     Launch / Buffers layout (checked against include/tq_b200.h)
 //
 // The resulting library lives under oracle/_ref/ and is never linked into the
-// product. It doubles as the "reference" CPU baseline the benchmark times.
+// product. ref_writer_reference is also the reference-compiled CPU leg the benchmark
+// times for reshape_and_cache.
 
 #include <tests/common/aic_splitk_decode_fixture.hpp>
 #include <tests/common/turboquant_oracle.hpp>
@@ -25,7 +28,12 @@
 #include <tests/common/lloydmax_oracle.hpp>
 #include <tests/cpu/icdf_fixture.hpp>
 #include <tests/common/fused_decode_opt_fixture.hpp>
+#include <tests/common/single_token_decode_oracle.hpp>
 
+#define TQ_B200_NO_REFERENCE_LAUNCHERS
+#include "../include/tq_b200.h"
+
+#include <cstddef>
 #include <cstdint>
 #include <cstring>
 #include <memory>
@@ -377,6 +385,114 @@ std::uint64_t ref_nz_tiled_packed_byte(std::uint64_t slot, std::uint64_t head, s
                                        std::uint64_t H, std::uint64_t packed)
 {
     return vllm_ascend::turboquant::NzTiledPackedByte(slot, head, column, H, packed);
+}
+
+
+// ------------------------------------------------- single-token decode fixture
+// tests/common/single_token_decode_oracle.hpp: one request, 4 KV heads x 6 query rows, head
+// size 256, pages of 128 tokens, `pages` <= 8 logical pages through the reference's block
+// table. The caller pre-fills the caches (canaries); only mapped strips are written.
+//   q_raw  bf16 [4][6][256], the original-basis query rows (exact small integers)
+//   key, value  9 * 4 * 8 * 2048 bytes each; scales float[2 * 9 * 4 * 128]; table int32[pages]
+void ref_single_token_fixture(int pages, std::uint16_t* q_raw, std::uint8_t* key, std::uint8_t* value,
+                              float* scales, std::int32_t* table)
+{
+    namespace st = single_token_decode;
+    namespace pd = paged_decode;
+    for (int head = 0; head < st::kKvHeads; ++head)
+        for (int row = 0; row < st::kRows; ++row)
+            for (int c = 0; c < st::kHeadSize; ++c)
+                q_raw[(head * st::kRows + row) * st::kHeadSize + c] = ascend_micro::sim::float_to_bfloat16_rne(
+                    pd::QueryEntry(st::QueryRowOf(head, row), c));
+    for (int page = 0; page < pages; ++page) {
+        const int block = pd::BlockTableEntry(page);
+        table[page] = block;
+        for (int head = 0; head < st::kKvHeads; ++head)
+            for (int strip = 0; strip < st::kStripsPerPage; ++strip) {
+                const int global = page * st::kStripsPerPage + strip;
+                std::uint8_t* ks = key + pd::KeyStripOffset(block, head, strip);
+                std::uint8_t* vs = value + pd::ValueStripOffset(block, head, strip);
+                for (int t = 0; t < st::kKeys; ++t)
+                    for (int c = 0; c < st::kHeadSize; ++c) {
+                        pd::PackNibble(ks, pd::KeyNibbleIndex(t, c), st::KeyNibbleAt(head, global, t, c));
+                        pd::PackNibble(vs, pd::ValueNibbleIndex(c, t), st::ValueNibbleAt(head, global, c, t));
+                    }
+                for (int t = 0; t < st::kKeys; ++t) {
+                    const int in_page = strip * st::kKeys + t;
+                    scales[pd::ScaleOffset(0, block, head, in_page)] = st::KeyScale(head, global, t);
+                    scales[pd::ScaleOffset(1, block, head, in_page)] = st::ValueScaleAt(head, global, t);
+                }
+            }
+    }
+}
+// GoldenDecode of one head over the first `pages` pages: m[6], l[6], acc / rotated / context [6][256],
+// q_rot[6][256] (the bf16 image of the rotated query, as floats).
+void ref_single_token_golden(int head, int pages, float* m, float* l, float* acc, float* rotated,
+                             float* context, float* q_rot)
+{
+    namespace st = single_token_decode;
+    std::vector<int> strips;
+    for (int g = 0; g < pages * st::kStripsPerPage; ++g) strips.push_back(g);
+    const auto gs = st::GoldenDecode(head, strips);
+    std::memcpy(m, gs.m.data(), gs.m.size() * 4);
+    std::memcpy(l, gs.l.data(), gs.l.size() * 4);
+    std::memcpy(acc, gs.acc.data(), gs.acc.size() * 4);
+    std::memcpy(rotated, gs.rotated.data(), gs.rotated.size() * 4);
+    std::memcpy(context, gs.context.data(), gs.context.size() * 4);
+    for (int row = 0; row < st::kRows; ++row)
+        for (int c = 0; c < st::kHeadSize; ++c) q_rot[row * st::kHeadSize + c] = st::QRotEntry(head, row, c);
+}
+// gate logits of the fixture, [4][6][256]
+void ref_single_token_gate(float* gate)
+{
+    namespace st = single_token_decode;
+    for (int head = 0; head < st::kKvHeads; ++head)
+        for (int row = 0; row < st::kRows; ++row)
+            for (int c = 0; c < st::kHeadSize; ++c)
+                gate[(head * st::kRows + row) * st::kHeadSize + c] =
+                    paged_decode::GateEntry(head, st::QueryRowOf(head, row), c);
+}
+
+// ------------------------------------------- layout of the fused decoder's descriptors
+// 1 when tq_fused_launch / tq_fused_buffers / tq_fused_raw_query_buffers of include/tq_b200.h
+// have the size and field offsets of the reference's Launch / Buffers / RawQueryBuffers.
+int ref_fused_descriptor_layout_matches()
+{
+    namespace fd = ascend_micro::fused_decode_opt;
+#define TQ_SAME(T, U, f) (offsetof(T, f) == offsetof(U, f))
+    static_assert(sizeof(tq_fused_launch) == sizeof(fd::Launch), "Launch size");
+    static_assert(sizeof(tq_fused_buffers) == sizeof(fd::Buffers), "Buffers size");
+    static_assert(sizeof(tq_fused_raw_query_buffers) == sizeof(fd::RawQueryBuffers), "RawQueryBuffers size");
+    static_assert(TQ_SAME(tq_fused_launch, fd::Launch, grid) && TQ_SAME(tq_fused_launch, fd::Launch, tokens) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, heads) && TQ_SAME(tq_fused_launch, fd::Launch, kv_heads) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, head_size) && TQ_SAME(tq_fused_launch, fd::Launch, block_size) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, max_blocks) && TQ_SAME(tq_fused_launch, fd::Launch, splits) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, heads_per_task) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, tasks_per_block) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, reduce_tasks_per_block) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, fused_context_limit) && TQ_SAME(tq_fused_launch, fd::Launch, scale) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, inv_sqrt_len) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, prologue_vectors_per_block) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, prologue_cube_chunk_vectors) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, output_stage) && TQ_SAME(tq_fused_launch, fd::Launch, element_type) &&
+                  TQ_SAME(tq_fused_launch, fd::Launch, probe_page) && TQ_SAME(tq_fused_launch, fd::Launch, probe_tile),
+                  "Launch fields");
+    static_assert(TQ_SAME(tq_fused_buffers, fd::Buffers, query) && TQ_SAME(tq_fused_buffers, fd::Buffers, key) &&
+                  TQ_SAME(tq_fused_buffers, fd::Buffers, value) && TQ_SAME(tq_fused_buffers, fd::Buffers, scales) &&
+                  TQ_SAME(tq_fused_buffers, fd::Buffers, block_table) &&
+                  TQ_SAME(tq_fused_buffers, fd::Buffers, context_lengths) &&
+                  TQ_SAME(tq_fused_buffers, fd::Buffers, mode_tables) && TQ_SAME(tq_fused_buffers, fd::Buffers, workspace) &&
+                  TQ_SAME(tq_fused_buffers, fd::Buffers, output) && TQ_SAME(tq_fused_buffers, fd::Buffers, tiling),
+                  "Buffers fields");
+    static_assert(TQ_SAME(tq_fused_raw_query_buffers, fd::RawQueryBuffers, raw_query) &&
+                  TQ_SAME(tq_fused_raw_query_buffers, fd::RawQueryBuffers, pi_signs) &&
+                  TQ_SAME(tq_fused_raw_query_buffers, fd::RawQueryBuffers, rot_tables) &&
+                  TQ_SAME(tq_fused_raw_query_buffers, fd::RawQueryBuffers, h16) &&
+                  TQ_SAME(tq_fused_raw_query_buffers, fd::RawQueryBuffers, gate) &&
+                  TQ_SAME(tq_fused_raw_query_buffers, fd::RawQueryBuffers, decode),
+                  "RawQueryBuffers fields");
+#undef TQ_SAME
+    return 1;
 }
 
 }  // extern "C"

@@ -64,6 +64,12 @@ def main():
                         gate=f.get("gate"), expected=f.get("expected"), signs=r.decode_signs(),
                         dims=np.array([f.tokens, f.seq_len, f.pages, f.requests, f.heads, f.rows,
                                        f.page_tokens]))
+    # the 6-row single-token decode fixture over two pages, with its golden state per KV head
+    st = r.single_token_fixture(2)
+    gold = {f"{k}_h{h}": v for h in range(4) for k, v in r.single_token_golden(h, 2).items()}
+    np.savez_compressed(os.path.join(HERE, "single_token_p2.npz"), q=st["q"], key=st["key"], value=st["value"],
+                        scale_bits=st["scales"].view(np.uint32), table=st["table"], gate=st["gate"],
+                        signs=r.decode_signs(), **gold)
     # partition table and Lloyd-Max codebook
     part = np.array([[p, k, s, *r.partition(p, k, s)] for p in (1, 3, 4, 5, 7, 8, 100)
                      for k in (1, 2, 4, 8, 16) for s in range(k)], np.int64)

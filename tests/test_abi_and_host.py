@@ -44,6 +44,10 @@ def test_split_choice():
     """The plan cuts work into power-of-two chunks of 256..8192 tokens, about 32 CTAs per SM;
     the launch's split count is what the longest context needs, at most 16."""
     import ascend_micro_harness_b200 as tq
+    sm = 148
+    import functools
+    tq = type("T", (), {"choose_splits": staticmethod(functools.partial(
+        lambda b, h, s, c, choose=tq.choose_splits: choose(b, h, s, c, sm)))})
     assert tq.choose_splits(64, 8, 16, 256) == 1            # short contexts run un-split
     assert tq.choose_splits(1, 8, 16, 4096) == 16           # one sequence: fill the machine
     assert tq.choose_splits(1, 8, 16, 1024) == 4            # ... but keep 256 tokens per split
@@ -58,8 +62,9 @@ def test_split_choice():
 
 def test_workspace_sizing():
     import ascend_micro_harness_b200 as tq
-    assert tq.decode_workspace_floats(64, 32, 8, 128, 4) == 64 * 8 * 4 * 4 * (16 + 128)
-    assert tq.decode_workspace_floats(2, 64, 4, 256, 8) == 2 * 4 * 8 * 16 * 272
+    # the records, then one arrival counter per (sequence, KV head, 8-row tile)
+    assert tq.decode_workspace_floats(64, 32, 8, 128, 4) == 64 * 8 * 4 * 4 * (16 + 128) + 64 * 8
+    assert tq.decode_workspace_floats(2, 64, 4, 256, 8) == 2 * 4 * 8 * 16 * 272 + 2 * 4 * 2
 
 
 def test_geometry_is_refused_before_any_launch():
@@ -83,6 +88,33 @@ def test_geometry_is_refused_before_any_launch():
     assert lib.tq_decode_splitk_partials(*part, 1, 1, 16, 256, 128, 8, 4, 2, 0, 2, 300, 0.0625, 1.0, None) == 1
     assert lib.tq_decode_splitk_partials(*part, 1, 1, 16, 256, 128, 8, 4, 17, 0, 2, 0, 0.0625, 1.0, None) == 1
     assert lib.tq_status_string(2).decode().startswith("num_tokens")
+    # the softmax scale is a positive finite factor (the kernels take maxima of raw scores)
+    for bad in (0.0, -0.5, float("nan"), float("inf")):
+        assert lib.tq_decode_splitk(*args, 2, 32, 8, 128, 16, 8, 4, 2, 0, 0, 0.1, bad, None) == 1
+        assert lib.tq_decode_splitk_precise(*args, 2, 32, 8, 128, 16, 8, 4, 2, 0, 0, 0.1, bad, None) == 1
+        assert lib.tq_decode_splitk_partials(*part, 1, 1, 16, 256, 128, 8, 4, 2, 0, 2, 0, 0.0625, bad, None) == 1
+    # one split needs no workspace; more than one does
+    noworkspace = [None, p, p, p, p, p, p, p, p, None, p, 0]
+    assert lib.tq_decode_splitk(*noworkspace, 0, 32, 8, 128, 16, 8, 4, 1, 0, 0, 0.1, 1.0, None) == 0
+    assert lib.tq_decode_splitk(*noworkspace, 2, 32, 8, 128, 16, 8, 4, 2, 0, 0, 0.1, 1.0, None) == 1
+
+
+def test_nz_entry_and_static_entry_refuse_bad_geometry_on_the_host():
+    from ascend_micro_harness_b200._lib import load_library
+    lib = load_library()
+    p = C.c_void_p(16)   # never dereferenced
+    nz = [None, p, p, p, p, p, p, p, p, p, p, 1, 1]
+    tail = (2.98, 0.0625, 0.0625, 0, None)
+    assert lib.tq_decode_splitk_nz(*nz, 2, 16, 4, 32, 0, 4, 2, 0, 1, 0, *tail) == 1      # pages are 64 or 128 slots
+    assert lib.tq_decode_splitk_nz(*nz, 2, 16, 4, 64, 0, 4, 17, 0, 1, 0, *tail) == 1     # 17 splits
+    assert lib.tq_decode_splitk_nz(*nz, 2, 16, 4, 64, 0, 4, 2, 0, 2, 0, *tail) == 1      # no such code grid
+    assert lib.tq_decode_splitk_nz(*nz, 2, 18, 4, 64, 0, 4, 2, 0, 1, 0, *tail) == 1      # heads % KV heads
+    assert lib.tq_decode_splitk_nz(*nz, 2, 16, 4, 64, 0, 4, 2, 0, 1, 0, 0.0, 0.0625, 0.0625, 0, None) == 1   # gain
+    assert lib.tq_decode_splitk_nz(*nz, 0, 16, 4, 64, 0, 4, 2, 0, 1, 0, *tail) == 0      # empty batch
+    st = [None, p, p, p, p, p, p, p, p, p, 0]
+    assert lib.tq_decode_splitk_static(*st, 1 << 20, 17, 1, 128, 16, 8, 4, 16, 0, 0, 0.1, 1.0, None) == 1   # 17 rows
+    assert lib.tq_decode_splitk_static(*st, 1 << 20, 16, 1, 96, 16, 8, 4, 16, 0, 0, 0.1, 1.0, None) == 1    # head size
+    assert lib.tq_decode_splitk_static(*st, 1 << 20, 16, 1, 128, 16, 8, 4, 16, 0, 0, 0.1, 1.0, None) == 5   # too large
 
 
 def test_routine_and_lloydmax_entries_refuse_bad_arguments_on_the_host():

@@ -24,11 +24,11 @@ def _dev(cuda, a):
     return torch.from_numpy(a).to(cuda)
 
 
-def _decode_both(cuda, oracle, seed, ctx, splits):
+def _decode_both(cuda, oracle, seed, ctx, splits, d=128):
     import torch
     import ascend_micro_harness_b200 as tq
     rng = np.random.default_rng(seed)
-    Hq, Hkv, d, S = 16, 4, 128, 16
+    Hq, Hkv, S = 16, 4, 16
     cache = hp.build_cache_from_gaussian(oracle, rng, ctx, Hkv, d, S)
     B = len(ctx)
     q = _dev(cuda, hp.bf16_from_f32(rng.standard_normal((B, Hq, d)).astype(np.float32)))
@@ -72,3 +72,51 @@ def test_launch_beyond_the_array_is_refused(cuda):
                                 head_size=d, block_size=16, num_blocks=8, inv_sqrt_len=0.1, splits=16)
     assert e.value.status == 5
     assert "workspace" in str(e.value)
+
+
+def test_head_size_256_twice(cuda, oracle):
+    for seed, ctx, splits in ((3, [900, 40], 0), (4, [65, 1300, 7], 2)):
+        got, want = _decode_both(cuda, oracle, seed, ctx, splits, d=256)
+        assert np.isfinite(got).all()
+        assert np.abs(got - want).max() <= 1e-6 * max(1.0, np.abs(want).max())
+
+
+def test_the_limit_is_exact(cuda):
+    """The largest batch whose records and counters fit the array runs; one sequence more is
+    refused, also when the split count is left to the launcher; nonsense geometry is refused as
+    nonsense, not as too large."""
+    import torch
+    import ascend_micro_harness_b200 as tq
+    Hq = Hkv = 1
+    d, S, splits = 128, 16, 16
+    per_seq = tq.decode_workspace_floats(1, Hq, Hkv, d, splits)
+    fits = tq.STATIC_WORKSPACE_FLOATS // per_seq
+    assert tq.decode_workspace_floats(fits, Hq, Hkv, d, splits) <= tq.STATIC_WORKSPACE_FLOATS
+    assert tq.decode_workspace_floats(fits + 1, Hq, Hkv, d, splits) > tq.STATIC_WORKSPACE_FLOATS
+
+    def call(batch, n_splits, heads=Hq, hint=0):
+        P = 4
+        kc = torch.zeros(P * Hkv * S * d // 2, dtype=torch.uint8, device=cuda)
+        sc = torch.ones(2 * P * Hkv * S, dtype=torch.float32, device=cuda)
+        tables = torch.zeros((batch, 2), dtype=torch.int32, device=cuda)
+        lens = torch.full((batch,), 20, dtype=torch.int32, device=cuda)
+        q = torch.ones((batch, heads, d), dtype=torch.bfloat16, device=cuda)
+        out = torch.full((batch, heads, d), float("nan"), dtype=torch.float32, device=cuda)
+        tq.decode_splitk_static(q, kc, kc, sc, tables, lens, torch.ones(d, device=cuda), out, num_heads=heads,
+                                num_kv_heads=Hkv, head_size=d, block_size=S, num_blocks=P, inv_sqrt_len=0.088,
+                                splits=n_splits, max_context_hint=hint)
+        torch.cuda.synchronize()
+        return out
+
+    assert torch.isfinite(call(fits, splits)).all()
+    with pytest.raises(tq.TqError) as e:
+        call(fits + 1, splits)
+    assert e.value.status == 5
+    # splits = 0 with a hint that makes the launcher pick 16 splits: the same limit applies
+    assert tq.choose_splits(fits + 1, Hkv, S, 1 << 20) == 16
+    with pytest.raises(tq.TqError) as e:
+        call(fits + 1, 0, hint=1 << 20)
+    assert e.value.status == 5
+    with pytest.raises(tq.TqError) as e:      # 17 query rows per KV head: invalid, whatever its size
+        call(1 << 16, splits, heads=17)
+    assert e.value.status == 1
