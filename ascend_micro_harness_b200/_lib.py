@@ -24,6 +24,8 @@ SIGNATURES = {
                                      u32, u32, f32, vp]),
     "tq_decode_splitk": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                    u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
+    "tq_decode_splitk_persistent": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
+                                              u32, u32, u32, u32, u32, u32, f32, f32, vp]),
     "tq_decode_splitk_precise": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                            u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
     "tq_decode_splitk_nz": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
@@ -41,6 +43,7 @@ SIGNATURES = {
     "tq_decode_splitk_export": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                           u32, u32, u32, u32, u32, f32, f32, vp]),
     "tq_decode_choose_splits": (u32, [u32, u32, u32, u32, u32]),
+    "tq_decode_worker_census": (C.c_int, [vp, u32]),
     "tq_decode_workspace_floats": (C.c_size_t, [u32, u32, u32, u32, u32]),
     "tq_decode_splitk_partials": (C.c_int, [vp, vp, vp, u32, vp, vp, vp, vp, vp, vp, u32, u32,
                                             u32, u32, u32, u32, u32, u32, u32, u32, u32, f32, f32,

@@ -42,6 +42,8 @@
 namespace tq {
 
 constexpr int kDecWarps = 4;
+constexpr int kCensusWords = 10;   // 64-bit words per CTA of the worker census
+constexpr int kMaxSplits = TQ_MAX_SPLITS;   // record slots per head a workspace can be asked to hold
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -74,11 +76,15 @@ struct DecodeParams {
     // head, row tile)), the tag that tells this launch's counts from stale bytes, and what the
     // egress needs (see CombineParams)
     uint32_t* counters;
+    unsigned long long* ticket;   // two words behind the counters: the chunk ticket, the count of CTAs that left
     uint32_t tag;
     const float* egress_signs;
     const void* gate;
     void* output;
     uint32_t output_stage, out_dtype, gate_dtype, rotation;
+    // optional worker census of the persistent grid: per CTA {start, end} in nanoseconds of the
+    // global timer (null: off)
+    unsigned long long* census;
 };
 
 // Shared-memory plan of one CTA. A key strip is stored in 16-byte chunks whose
@@ -228,6 +234,13 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a)
     return d;
 }
 
+__device__ __forceinline__ unsigned long long global_timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
 __device__ __forceinline__ float ex2f(float x)
 {
     float y;
@@ -331,6 +344,81 @@ __device__ __forceinline__ void egress_rows(const DecodeParams& p, float* buf, i
     }
 }
 
+// The persistent grid's schedule: the flattened tiles [0, W) are cut into chunks whose sizes
+// are a function of the chunk index alone -- G chunks of c0 tiles (G = CTAs of the grid, c0
+// 85 % of an equal share), G chunks of c1 (an eighth of a share), then chunks of c2 (a
+// sixteenth) to the end -- so
+// every CTA can name the chunk that holds a tile and the tiles a chunk holds without any table.
+// The first round is dealt statically (chunk c to CTA c); the rest is taken from an atomic
+// ticket, so CTAs that run faster take more (their speeds differ by some +-10 % on this
+// part), and the chunks are small where the work runs out.
+struct ChunkSchedule {
+    unsigned long long W;
+    uint32_t G, c0, c1, c2;
+};
+__device__ __forceinline__ unsigned long long chunk_start(const ChunkSchedule& sc, uint32_t k, uint32_t* size)
+{
+    if (k < sc.G) {
+        *size = sc.c0;
+        return static_cast<unsigned long long>(k) * sc.c0;
+    }
+    if (k < 2u * sc.G) {
+        *size = sc.c1;
+        return static_cast<unsigned long long>(sc.G) * sc.c0 + static_cast<unsigned long long>(k - sc.G) * sc.c1;
+    }
+    *size = sc.c2;
+    return static_cast<unsigned long long>(sc.G) * (sc.c0 + sc.c1) +
+           static_cast<unsigned long long>(k - 2u * sc.G) * sc.c2;
+}
+__device__ __forceinline__ uint32_t chunk_of(const ChunkSchedule& sc, unsigned long long pos)
+{
+    const unsigned long long r0 = static_cast<unsigned long long>(sc.G) * sc.c0;
+    if (pos < r0) return static_cast<uint32_t>(pos / sc.c0);
+    const unsigned long long r1 = r0 + static_cast<unsigned long long>(sc.G) * sc.c1;
+    if (pos < r1) return sc.G + static_cast<uint32_t>((pos - r0) / sc.c1);
+    return 2u * sc.G + static_cast<uint32_t>((pos - r1) / sc.c2);
+}
+
+// Puts a 64-bit word under the launch's tag (count zero) unless it is there already.
+__device__ __forceinline__ bool ensure_tag(unsigned long long* word, uint32_t tag)
+{
+    const unsigned long long mine = static_cast<unsigned long long>(tag) << 40;
+    unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(word);
+    for (int it = 0; it < 64; ++it) {
+        if ((old >> 40) == tag) return true;
+        const unsigned long long prev = atomicCAS(word, old, mine);
+        if (prev == old) return true;
+        old = prev;
+    }
+    return false;
+}
+
+// A 64-bit counter that needs no clearing between launches: the top 24 bits carry the
+// launch's tag, and a word under another tag (stale, or never written) reads as zero. Returns
+// the count before the addition. Every retry means another CTA changed the word, so the loop
+// ends after at most a few rounds; it gives up after 64 and reports through *ok.
+__device__ __forceinline__ unsigned long long tagged_fetch_add(unsigned long long* word, uint32_t tag,
+                                                               unsigned long long add, bool* ok)
+{
+    const unsigned long long mine = static_cast<unsigned long long>(tag) << 40;
+    unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(word);
+    *ok = false;
+    for (int it = 0; it < 64; ++it) {
+        if ((old >> 40) == tag) {
+            *ok = true;
+            break;
+        }
+        const unsigned long long prev = atomicCAS(word, old, mine);
+        if (prev == old) {
+            *ok = true;
+            break;
+        }
+        old = prev;
+    }
+    if (!*ok) return 0ull;
+    return atomicAdd(word, add) & ((1ull << 40) - 1ull);
+}
+
 // EXT compiles in the extensions of the serving path -- f16 or pre-rotated FP32 query
 // elements, several query tokens per request, mid-rise codes -- so that the plain
 // instantiation carries neither their branches nor their registers. NZ reads the packed planes
@@ -362,8 +450,14 @@ tq_decode_partial_kernel(const DecodeParams p)
     __shared__ float row_unscale[8];                         // per query row: 2^-k * softmax_scale * log2e
     __shared__ int row_qsum8[8];                             // mid-rise codes: sum of the row's fixed-point query (enters a score times 8)
     __shared__ uint32_t sk_scan[2 * kDecWarps];              // persistent grid: warp totals / maxima of the tile scan
-    __shared__ uint32_t sk_start[3];                         // first sequence of the share, tiles before it (lo, hi)
+    __shared__ uint32_t sk_prefix[kDecWarps * 32 + 1];       // tiles per head before each thread's slice of sequences, and in all
+    __shared__ uint32_t sk_start[2];                         // first sequence of a chunk, tiles per head before it
+    __shared__ uint32_t sk_chunk;                            // the chunk the ticket handed out
+    constexpr uint32_t kCtxCache = 512;                       // sequences whose live context is kept in shared memory
+    __shared__ uint32_t sk_ctx[STREAMK ? kCtxCache : 1];
+    __shared__ float sk_sgn[STREAMK ? D : 1];                 // the sign diagonal, read once
     __shared__ uint32_t sk_last;                             // this CTA completed the head's last segment
+    __shared__ uint32_t sk_seen;                             // the head's arrival counter as read at the segment's start
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, qd = lane & 3;
@@ -381,6 +475,13 @@ tq_decode_partial_kernel(const DecodeParams p)
             if (tid == 0) report(p.status, TQ_STATUS_BAD_PAGE);
         }
         return ctx;
+    };
+    // persistent grid: the same from shared memory once the scan has cached it (small batches)
+    auto context_cached = [&](uint32_t seq) -> uint32_t {
+        if constexpr (STREAMK) {
+            if (p.items / p.H <= kCtxCache) return sk_ctx[seq];
+        }
+        return context_of(seq);
     };
     auto tiles_of = [&](uint32_t ctx) -> uint32_t {
         return ((ctx + kStrip - 1u) / kStrip + kTileStrips - 1u) / kTileStrips;
@@ -446,18 +547,92 @@ tq_decode_partial_kernel(const DecodeParams p)
         else return __int2float_rn(v);
     };
 
-    // ---- the share of this CTA (persistent grid): [w0, w0 + left) of the flattened tiles
+    // ---- persistent grid: the schedule, and the chunk this CTA starts with
     uint32_t seq = 0, head = 0, row_tile = 0, split = 0;
-    uint32_t sk_n = 0, sk_loc = 0, sk_left = 0, sk_quota = 1;   // tiles of `seq`, position inside its block, tiles to go
-    unsigned long long sk_before = 0;                          // tiles (per head) of the sequences before `seq`
+    uint32_t sk_n = 0, sk_loc = 0, sk_left = 0;   // tiles of `seq`, position inside its block of heads, tiles to go
+    uint32_t sk_before = 0, cur_chunk = 0;       // tiles (per head) of the sequences before `seq`; the chunk in hand
+    ChunkSchedule sched{0ull, gridDim.x, 1u, 1u, 1u};
     const uint32_t heads_per_seq = p.H * row_tiles;
+    const uint32_t batch = p.items / p.H;
+    const uint32_t seqs_per_thread = (batch + blockDim.x - 1u) / blockDim.x;
+    // Takes chunk k: its tiles [w0, w1), the sequence that holds w0 (found by the thread whose
+    // slice of sequences covers it). False when the chunk lies past the work. Uniform over the CTA.
+    auto begin_chunk = [&](uint32_t k) -> bool {
+        uint32_t size;
+        const unsigned long long w0 = chunk_start(sched, k, &size);
+        if (w0 >= sched.W) return false;
+        sk_left = static_cast<uint32_t>(min(sched.W, w0 + size) - w0);
+        cur_chunk = k;
+        if (tid == 0) sk_start[0] = 0xFFFFFFFFu;
+        __syncthreads();
+        const unsigned long long lo = static_cast<unsigned long long>(sk_prefix[tid]) * heads_per_seq;
+        const unsigned long long hi = static_cast<unsigned long long>(sk_prefix[tid + 1]) * heads_per_seq;
+        if (w0 >= lo && w0 < hi) {
+            uint32_t at = sk_prefix[tid];
+            const uint32_t b0 = min(batch, tid * seqs_per_thread), b1 = min(batch, b0 + seqs_per_thread);
+            for (uint32_t b = b0; b < b1; ++b) {
+                const uint32_t n = tiles_of(context_cached(b));
+                if (w0 < static_cast<unsigned long long>(at + n) * heads_per_seq) {
+                    sk_start[0] = b;
+                    sk_start[1] = at;
+                    break;
+                }
+                at += n;
+            }
+        }
+        __syncthreads();
+        seq = sk_start[0];
+        if (seq >= batch) return false;   // no slice claimed the tile: nothing to walk
+        sk_before = sk_start[1];
+        sk_n = tiles_of(context_cached(seq));
+        sk_loc = static_cast<uint32_t>(w0 - static_cast<unsigned long long>(sk_before) * heads_per_seq);
+        return true;
+    };
+    // The CTA is done: it counts itself out, and the last one out clears the two schedule
+    // words, so that a replay of the same launch (same tag) starts from a clean ticket.
+    auto leave = [&]() {
+        if (tid != 0) return;
+        if (p.census != nullptr) p.census[kCensusWords * blockIdx.x + 1] = global_timer_ns();
+        bool ok;
+        const unsigned long long gone = tagged_fetch_add(p.ticket + 1, p.tag, 1ull, &ok);
+        if (!ok) report(p.status, TQ_STATUS_WAIT_EXPIRED);
+        if (ok && gone + 1ull == gridDim.x) {
+            *reinterpret_cast<volatile unsigned long long*>(p.ticket) = 0ull;
+            *reinterpret_cast<volatile unsigned long long*>(p.ticket + 1) = 0ull;
+        }
+    };
+    // census only: time since the previous mark, added to word `slot` of this CTA's census line
+    unsigned long long mark_at = 0;
+    auto mark = [&](int slot) {
+        if constexpr (STREAMK) {
+            if (p.census != nullptr && tid == 0) {
+                const unsigned long long now = global_timer_ns();
+                if (slot >= 0) p.census[kCensusWords * blockIdx.x + slot] += now - mark_at;
+                mark_at = now;
+            }
+        }
+    };
     if constexpr (STREAMK) {
-        const uint32_t batch = p.items / p.H;
-        const uint32_t per = (batch + blockDim.x - 1u) / blockDim.x;
-        const uint32_t b0 = min(batch, tid * per), b1 = min(batch, b0 + per);
+        if (p.census != nullptr && tid == 0) {
+            for (int i = 4; i < kCensusWords; ++i) p.census[kCensusWords * blockIdx.x + i] = 0ull;
+            p.census[kCensusWords * blockIdx.x] = global_timer_ns();
+            p.census[kCensusWords * blockIdx.x + 1] = 0ull;
+            p.census[kCensusWords * blockIdx.x + 2] = 0ull;   // nanoseconds warp 0 spent inside its tile loops
+            p.census[kCensusWords * blockIdx.x + 3] = 0ull;   // segments
+        }
+        mark(-1);
+        if (!prerot)
+            for (int c = tid; c < D; c += blockDim.x)
+                sk_sgn[c] = sign_is_negative(p.signs, p.sign_source, c) ? -1.0f : 1.0f;
+        // the ticket word goes under this launch's tag once, so that every later draw is a
+        // single atomic add whose result can be awaited late
+        if (tid == blockDim.x - 1 && !ensure_tag(p.ticket, p.tag)) report(p.status, TQ_STATUS_WAIT_EXPIRED);
+        const uint32_t b0 = min(batch, tid * seqs_per_thread), b1 = min(batch, b0 + seqs_per_thread);
         uint32_t mine = 0, nmax = 0;
         for (uint32_t b = b0; b < b1; ++b) {
-            const uint32_t n = tiles_of(context_of(b));
+            const uint32_t live = context_of(b);
+            if (b < kCtxCache) sk_ctx[b] = live;
+            const uint32_t n = tiles_of(live);
             mine += n;
             nmax = max(nmax, n);
             if (n == 0u && blockIdx.x == 0u) {
@@ -484,48 +659,29 @@ tq_decode_partial_kernel(const DecodeParams p)
             sk_scan[warp] = incl;
             sk_scan[kDecWarps + warp] = nmax;
         }
-        if (tid == 0) sk_start[0] = 0xFFFFFFFFu;
         __syncthreads();
-        unsigned long long before = 0, total = 0;
+        uint32_t before = 0, total = 0;
 #pragma unroll
         for (int w = 0; w < kDecWarps; ++w) {
             if (w < warp) before += sk_scan[w];
             total += sk_scan[w];
             nmax = max(nmax, sk_scan[kDecWarps + w]);
         }
-        before += incl - mine;                              // tiles per head before this thread's slice
-        const unsigned long long W = total * heads_per_seq;  // all tiles of the launch
-        // share: equal parts, at least one tile per warp, and wide enough that the longest
-        // head is cut into at most `splits` segments (the workspace holds that many records)
-        unsigned long long quota = (W + gridDim.x - 1u) / gridDim.x;
-        if (quota < kDecWarps) quota = kDecWarps;
+        sk_prefix[tid] = before + incl - mine;   // tiles per head before this thread's slice
+        if (tid == 0) sk_prefix[kDecWarps * 32] = total;
+        sched.W = static_cast<unsigned long long>(total) * heads_per_seq;   // all tiles of the launch
+        // no chunk below one tile per warp, nor so small that the longest head could be cut
+        // into more segments than the workspace has record slots for
         const uint32_t cap = p.splits > 1u ? p.splits - 1u : 1u;
-        if (quota < (nmax + cap - 1u) / cap) quota = (nmax + cap - 1u) / cap;
-        sk_quota = static_cast<uint32_t>(quota);
-        const unsigned long long w0 = static_cast<unsigned long long>(blockIdx.x) * quota;
-        if (w0 >= W) return;   // uniform over the CTA: nothing left for it
-        const unsigned long long w1 = min(W, w0 + quota);
-        sk_left = static_cast<uint32_t>(w1 - w0);
-        // the thread whose slice holds w0 names the sequence
-        if (w0 >= before * heads_per_seq && w0 < (before + mine) * heads_per_seq) {
-            unsigned long long at = before;
-            for (uint32_t b = b0; b < b1; ++b) {
-                const uint32_t n = tiles_of(context_of(b));
-                if (w0 < (at + n) * heads_per_seq) {
-                    sk_start[0] = b;
-                    sk_start[1] = static_cast<uint32_t>(at);
-                    sk_start[2] = static_cast<uint32_t>(at >> 32);
-                    break;
-                }
-                at += n;
-            }
+        const unsigned long long cmin = max(static_cast<uint32_t>(kDecWarps), (nmax + cap - 1u) / cap);
+        const unsigned long long share = (sched.W + gridDim.x - 1ull) / gridDim.x;   // an equal share
+        sched.c0 = static_cast<uint32_t>(max(cmin, (share * 17ull + 19ull) / 20ull));
+        sched.c1 = static_cast<uint32_t>(max(cmin, (share + 7ull) / 8ull));
+        sched.c2 = static_cast<uint32_t>(max(cmin, (share + 15ull) / 16ull));
+        if (!begin_chunk(blockIdx.x)) {   // round 0 is dealt statically
+            leave();
+            return;
         }
-        __syncthreads();
-        seq = sk_start[0];
-        if (seq >= batch) return;   // no thread found the share's first sequence: nothing to walk
-        sk_before = (static_cast<unsigned long long>(sk_start[2]) << 32) | sk_start[1];
-        sk_n = tiles_of(context_of(seq));
-        sk_loc = static_cast<uint32_t>(w0 - sk_before * heads_per_seq);
     } else {
         uint32_t lin = blockIdx.x;
         split = lin % p.splits;
@@ -547,15 +703,15 @@ tq_decode_partial_kernel(const DecodeParams p)
             sk_take = min(sk_left, sk_n - t0);
             head = in_seq / row_tiles;
             row_tile = in_seq - head * row_tiles;
-            ctx = context_of(seq);
+            ctx = context_cached(seq);
             s0 = t0 * kTileStrips;
             s1 = min((t0 + sk_take) * kTileStrips, (ctx + kStrip - 1u) / kStrip);
-            // the CTAs this head's tiles [first, first + n) are dealt to
-            const unsigned long long first = sk_before * heads_per_seq + static_cast<unsigned long long>(in_seq) * sk_n;
-            const uint32_t c_first = static_cast<uint32_t>(first / sk_quota);
-            const uint32_t c_last = static_cast<uint32_t>((first + sk_n - 1u) / sk_quota);
-            seg_count = c_last - c_first + 1u;
-            seg_slot = blockIdx.x - c_first;
+            // the chunks this head's tiles [first, first + n) fall into: one record slot each
+            const unsigned long long first = static_cast<unsigned long long>(sk_before) * heads_per_seq +
+                                             static_cast<unsigned long long>(in_seq) * sk_n;
+            const uint32_t k_first = chunk_of(sched, first);
+            seg_count = chunk_of(sched, first + sk_n - 1u) - k_first + 1u;
+            seg_slot = cur_chunk - k_first;
         } else {
             uint32_t page_count;
             if (p.context_lens != nullptr) {
@@ -681,6 +837,45 @@ tq_decode_partial_kernel(const DecodeParams p)
         const uint32_t strip_first = s0 + warp * kTileStrips;   // first strip of this warp's tile 0
         int32_t pg_next[kTileStrips];
         static_assert(kStages == 2, "the prologue below fills one stage ahead");
+        // Every global round trip of the prologue is started before anything waits for one: the
+        // draw of the next chunk and a first look at the head's arrival counter (persistent grid,
+        // consumed only after the fragments are built), the sign diagonal and this warp's two raw
+        // query rows; the block-table entries of the first tile follow, and only then the rotation.
+        [[maybe_unused]] unsigned long long drawn = 0;
+        [[maybe_unused]] uint32_t seen = 0;
+        if constexpr (STREAMK) {
+            if (tid == 0) {
+                if (sk_take == sk_left) drawn = atomicAdd(p.ticket, 1ull);
+                if (seg_count > 1u)
+                    seen = *reinterpret_cast<volatile uint32_t*>(p.counters + (static_cast<size_t>(item) * row_tiles + row_tile));
+            }
+        }
+        constexpr int K = D / 32;
+        float sgn[K], qraw[2][K];
+#pragma unroll
+        for (int i = 0; i < K; ++i) {
+            if constexpr (STREAMK) sgn[i] = prerot ? 1.0f : sk_sgn[lane * K + i];
+            else sgn[i] = !prerot && sign_is_negative(p.signs, p.sign_source, lane * K + i) ? -1.0f : 1.0f;
+        }
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int row = warp * 2 + rr;
+#pragma unroll
+            for (int i = 0; i < K; ++i) qraw[rr][i] = 0.f;
+            if (row < rows_here) {
+                // row = token * G + g of the request's (1 + speculative) query tokens; with one
+                // token per request this is (item * rows + row)
+                const uint32_t row_g = row_tile * 8u + row, grp = p.rows / tokens_per_req;
+                const uint32_t q_tok = row_g / grp, q_g = row_g - q_tok * grp;
+                const size_t qoff = ((static_cast<size_t>(seq) * tokens_per_req + q_tok) * (p.H * grp) +
+                                     static_cast<size_t>(head) * grp + q_g) * D + lane * K;
+                const uint16_t* qsrc = p.q + qoff;
+#pragma unroll
+                for (int i = 0; i < K; ++i)
+                    qraw[rr][i] = prerot ? p.q_f32[qoff + i]
+                                         : q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
+            }
+        }
         const bool early = L::early_issue(warp) && !empty;
         if (early) {
             load_pages(strip_first, pg_next);
@@ -703,28 +898,12 @@ tq_decode_partial_kernel(const DecodeParams p)
         // the eight lanes one 128-bit access serves together fall into eight different bank groups.
         auto q_index = [](int row, int ch) { return row * (D + 16) + (ch / (D / 4)) * (D / 4 + 4) + ch % (D / 4); };
         {
-            constexpr int K = D / 32;
-            float sgn[K];
 #pragma unroll
-            for (int i = 0; i < K; ++i)
-                sgn[i] = !prerot && sign_is_negative(p.signs, p.sign_source, lane * K + i) ? -1.0f : 1.0f;
-            for (int row = warp * 2; row < warp * 2 + 2; ++row) {
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = warp * 2 + rr;
                 float v[K];
 #pragma unroll
-                for (int i = 0; i < K; ++i) v[i] = 0.f;
-                if (row < rows_here) {
-                    // row = token * G + g of the request's (1 + speculative) query tokens; with one
-                    // token per request this is (item * rows + row)
-                    const uint32_t row_g = row_tile * 8u + row, grp = p.rows / tokens_per_req;
-                    const uint32_t q_tok = row_g / grp, q_g = row_g - q_tok * grp;
-                    const size_t qoff = ((static_cast<size_t>(seq) * tokens_per_req + q_tok) * (p.H * grp) +
-                                         static_cast<size_t>(head) * grp + q_g) * D + lane * K;
-                    const uint16_t* qsrc = p.q + qoff;
-#pragma unroll
-                    for (int i = 0; i < K; ++i)
-                        v[i] = prerot ? p.q_f32[qoff + i]
-                                      : q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
-                }
+                for (int i = 0; i < K; ++i) v[i] = qraw[rr][i];
                 if (!prerot) cascade_ingress<K>(v, sgn, lane);
                 float am = 0.f;
 #pragma unroll
@@ -809,6 +988,15 @@ tq_decode_partial_kernel(const DecodeParams p)
         const float rfac[2] = {row_unscale[qd * 2], row_unscale[qd * 2 + 1]};
         const int qs8[2] = {midrise ? row_qsum8[qd * 2] : 0, midrise ? row_qsum8[qd * 2 + 1] : 0};
         float ps[2] = {0.f, 0.f};   // mid-rise codes: running sum of P (as the value contraction sees it) per row
+        if constexpr (STREAMK) {
+            if (tid == 0) {   // the two round trips started at the top of the prologue are back by now
+                if (sk_take == sk_left) {
+                    const unsigned long long t = drawn & ((1ull << 40) - 1ull);
+                    sk_chunk = t < 0x7FFFFFFFull - gridDim.x ? gridDim.x + static_cast<uint32_t>(t) : 0xFFFFFFFFu;
+                }
+                sk_seen = seen;
+            }
+        }
         __syncthreads();  // everyone is done with the fixed-point query: the ring may overwrite it
 
         // Online-softmax state for query rows qd*2 and qd*2+1, in units of raw * key_scale.
@@ -1139,6 +1327,11 @@ tq_decode_partial_kernel(const DecodeParams p)
             }
         };
 
+        [[maybe_unused]] unsigned long long loop_began = 0;
+        if constexpr (STREAMK) {
+            if (p.census != nullptr && tid == 0) loop_began = global_timer_ns();
+        }
+        mark(8);   // prologue: copies of the first tile issued, query rotated, fragments built (first: since launch)
         uint32_t stage = 0;
         uint32_t strip_t = strip_first;   // first strip of the tile being computed
 #pragma unroll 1
@@ -1169,6 +1362,13 @@ tq_decode_partial_kernel(const DecodeParams p)
             __syncwarp();
         }
         cp_async_wait<0>();
+        if constexpr (STREAMK) {
+            if (p.census != nullptr && tid == 0) {
+                p.census[kCensusWords * blockIdx.x + 2] += global_timer_ns() - loop_began;
+                p.census[kCensusWords * blockIdx.x + 3] += 1ull;
+            }
+        }
+        mark(-1);
 
         // ---- warp-level l, value normaliser out of acc, merge the warps through shared memory.
 #pragma unroll
@@ -1191,6 +1391,7 @@ tq_decode_partial_kernel(const DecodeParams p)
             }
         }
         __syncthreads();  // every warp is done with its ring; reuse it
+        mark(4);   // waiting for the slowest warp of the segment
         // Row pitch d + 4 floats: a lane stores its two adjacent channels of a row as one
         // 8-byte word, and with this pitch the 16 lanes of a half-warp hit 16 different banks pairs.
         constexpr int kPitch = L::kMergePitch;
@@ -1279,7 +1480,7 @@ tq_decode_partial_kernel(const DecodeParams p)
                 __syncthreads();
                 if (tid == 0) {
                     uint32_t* word = p.counters + (static_cast<size_t>(item) * row_tiles + row_tile);
-                    uint32_t old = *reinterpret_cast<volatile uint32_t*>(word), want = 0;
+                    uint32_t old = STREAMK ? sk_seen : *reinterpret_cast<volatile uint32_t*>(word), want = 0;
                     bool counted = false;
                     // a word counts for this launch only under its tag; anything else is stale
                     for (int it = 0; it < 64 && !counted; ++it) {
@@ -1300,23 +1501,42 @@ tq_decode_partial_kernel(const DecodeParams p)
                     const float* first = p.workspace +
                                          ((static_cast<size_t>(item) * p.splits) * p.rows_stride + row_tile * 8u) * kRecord;
                     const size_t slot_stride = static_cast<size_t>(p.rows_stride) * kRecord;
-                    for (int i = tid; i < rows_here * kRecPitch; i += blockDim.x) {
-                        const int q = i / kRecPitch, c = i % kRecPitch;
-                        const float* rq = first + q * kRecord;
-                        float mm = kMaskedScore;
-                        for (uint32_t k = 0; k < seg_count; ++k) mm = fmaxf(mm, __ldcg(rq + k * slot_stride));
-                        float out = mm;
-                        if (c != 0) {
-                            out = 0.f;
-                            const int src = c == 1 ? 8 : 16 + (c - 2);
-                            for (uint32_t k = 0; k < seg_count; ++k)
-                                out += __ldcg(rq + k * slot_stride + src) *
-                                       ex2f((__ldcg(rq + k * slot_stride) - mm) * kLog2e);
+                    // weights of the records first: lane k of warp w reads m of record k of rows w
+                    // and w + 4; the row maximum and exp(m_k - max) go to shared memory (the egress
+                    // buffer is free)
+                    float* wgt = ebuf;               // [8][32]
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int q = warp + 4 * j, k = lane;
+                        float mk = kMaskedScore;
+                        if (q < rows_here && static_cast<uint32_t>(k) < seg_count)
+                            mk = __ldcg(first + q * kRecord + k * slot_stride);
+                        float mm = mk;
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+                        wgt[q * 32 + k] = static_cast<uint32_t>(k) < seg_count ? ex2f((mk - mm) * kLog2e) : 0.f;
+                        if (k == 0 && q < rows_here) rec[q * kRecPitch] = mm;
+                    }
+                    __syncthreads();
+                    // then l and acc: sixteen records of an element are fetched before the first is
+                    // used, so the loads overlap instead of forming a chain of round trips to L2
+                    for (int i = tid; i < rows_here * (kRecPitch - 1); i += blockDim.x) {
+                        const int q = i / (kRecPitch - 1), c = 1 + i % (kRecPitch - 1);
+                        const float* rq = first + q * kRecord + (c == 1 ? 8 : 16 + (c - 2));
+                        float out = 0.f;
+                        for (uint32_t k0 = 0; k0 < seg_count; k0 += 16u) {
+                            float v[16];
+#pragma unroll
+                            for (int k = 0; k < 16; ++k)
+                                v[k] = k0 + k < seg_count ? __ldcg(rq + (k0 + k) * slot_stride) : 0.f;
+#pragma unroll
+                            for (int k = 0; k < 16; ++k) out = fmaf(v[k], wgt[q * 32 + k0 + k], out);
                         }
-                        rec[i] = out;
+                        rec[q * kRecPitch + c] = out;
                     }
                 }
             }
+            mark(5);   // merge of the warps, record, fence, arrival (and the records of the other segments)
             if (finish) {
                 __syncthreads();
                 for (int i = tid; i < rows_here * D; i += blockDim.x) {
@@ -1329,20 +1549,34 @@ tq_decode_partial_kernel(const DecodeParams p)
             }
         }
         if constexpr (STREAMK) {
-            // ---- next segment of the share
+            mark(6);   // normalise, egress, output
+            // ---- next segment of the chunk, or the next chunk off the ticket
             sk_left -= sk_take;
-            if (sk_left == 0u) return;
+            if (sk_left == 0u) {
+                __syncthreads();
+                const uint32_t k = sk_chunk;   // drawn at the start of this segment
+                if (k == 0xFFFFFFFFu || !begin_chunk(k)) {
+                    leave();
+                    return;
+                }
+                mark(7);   // next chunk located
+                continue;   // begin_chunk ended on a barrier: the ring and the query buffer are free
+            }
             sk_loc += sk_take;
             if (sk_loc == sk_n * heads_per_seq) {
                 sk_before += sk_n;
                 sk_loc = 0;
                 do {   // tiles are left, so a sequence with tiles follows
                     ++seq;
-                    if (seq >= p.items / p.H) return;
-                    sk_n = tiles_of(context_of(seq));
+                    if (seq >= batch) {
+                        leave();
+                        return;
+                    }
+                    sk_n = tiles_of(context_cached(seq));
                 } while (sk_n == 0u);
             }
             __syncthreads();   // the epilogue buffers alias the ring and the prologue's query
+            mark(7);
         } else {
             return;
         }
@@ -1382,10 +1616,10 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
     const float* base = p.workspace + (static_cast<size_t>(item) * p.splits * p.rows_stride + row) * kRecord;
     const size_t split_stride = static_cast<size_t>(p.rows_stride) * kRecord;
     // All records are fetched before the first one is merged, so the loads overlap instead
-    // of forming a chain of dependent round trips to L2 (at most 16 splits).
-    float mk[16], lk[16], ak[16];
+    // of forming a chain of dependent round trips to L2 (at most kMaxSplits records).
+    float mk[kMaxSplits], lk[kMaxSplits], ak[kMaxSplits];
 #pragma unroll
-    for (int k = 0; k < 16; ++k)
+    for (int k = 0; k < kMaxSplits; ++k)
         if (static_cast<uint32_t>(k) < p.splits) {
             const float* rec = base + k * split_stride;
             mk[k] = rec[0];
@@ -1394,7 +1628,7 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
         }
     float m = kMaskedScore, l = 0.f, a = 0.f;
 #pragma unroll
-    for (int k = 0; k < 16; ++k)
+    for (int k = 0; k < kMaxSplits; ++k)
         if (static_cast<uint32_t>(k) < p.splits) {
             const float mn = fmaxf(m, mk[k]);
             const float wa = ex2f((m - mn) * kLog2e), wb = ex2f((mk[k] - mn) * kLog2e);
@@ -1467,9 +1701,14 @@ static uint32_t next_launch_tag()
     return tag ? tag : 1u;
 }
 
+// Worker census (tq_decode_worker_census): where the persistent grid's CTAs stamp their times.
+static std::atomic<unsigned long long*> g_census{nullptr};
+static std::atomic<uint32_t> g_census_ctas{0};
+
 template <int D, bool PRECISE, bool EXT, bool NZ, bool STREAMK>
-static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p)
+static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p_in)
 {
+    DecodeParams p = p_in;
     // Opt in to the large dynamic shared-memory carve-out once per device. The
     // flags race benignly: setting the attribute twice is harmless.
     static bool configured[64] = {};
@@ -1497,6 +1736,7 @@ static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p)
         grid = static_cast<uint64_t>(sms) * DecodeSmem<D>::kCtasPerSm;   // one resident wave
     }
     if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
+    p.census = STREAMK && grid <= g_census_ctas.load() ? g_census.load() : nullptr;
     tq_decode_partial_kernel<D, PRECISE, EXT, NZ, STREAMK><<<static_cast<unsigned>(grid), kDecWarps * 32,
                                   DecodeSmem<D>::kTotal, stream>>>(p);
     return cudaGetLastError();
@@ -1535,7 +1775,7 @@ using namespace tq;
 // (fine enough to balance ragged contexts; measured best among 16/32/64/128 on the ragged
 // batch of 64). A chunk is 256..8192 tokens, and at least 1024 once the batch alone has a
 // CTA per SM, so that it amortises the per-CTA query rotation and merge; the launch's
-// split count is what the longest context needs, at most 16.
+// split count is what the longest context needs, at most TQ_MAX_SPLITS.
 static void decode_plan(uint32_t batch, uint32_t num_kv_heads, uint32_t block_size,
                         uint32_t max_context, uint32_t sm_count, uint32_t* splits,
                         uint32_t* chunk_pages)
@@ -1548,13 +1788,25 @@ static void decode_plan(uint32_t batch, uint32_t num_kv_heads, uint32_t block_si
     const uint64_t want = items * max_context / target;
     uint64_t chunk = items >= (sm_count ? sm_count : 148u) ? 1024 : 256;
     while (chunk < want && chunk < 8192u) chunk <<= 1;
-    while ((max_context + chunk - 1u) / chunk > 16u) chunk <<= 1;   // very long contexts
+    while ((max_context + chunk - 1u) / chunk > TQ_MAX_SPLITS) chunk <<= 1;   // very long contexts
     if (chunk < block_size) chunk = block_size;
     *chunk_pages = static_cast<uint32_t>(chunk / block_size);
     *splits = static_cast<uint32_t>((max_context + chunk - 1u) / chunk);
-    // The persistent grid deals equal shares of tiles, so a head may straddle two CTAs even
-    // when one chunk would hold it: keep two record slots per head.
-    if (*splits < 2u) *splits = 2u;
+}
+
+// Worker census of the persistent decode grid, after the reference's WorkerMetrics
+// (include/turboquant_splitk_contract.hpp:101-118, absolute cycle stamps published per worker):
+// while a buffer is registered, every CTA of a persistent decode launch writes ten words at
+// device_words[10 * cta]: the global-timer nanosecond of its start, of its leaving (0: no
+// work), the nanoseconds its first warp spent inside tile loops, its segment count, and the
+// nanoseconds of five boundary phases (see mark() in the kernel). capacity_ctas bounds the
+// grid that may write. A process-wide setting
+// for measurement runs, not for concurrent use; null switches it off.
+extern "C" int tq_decode_worker_census(unsigned long long* device_words, uint32_t capacity_ctas)
+{
+    g_census_ctas.store(device_words ? capacity_ctas : 0u);
+    g_census.store(device_words);
+    return TQ_OK;
 }
 
 extern "C" uint32_t tq_decode_choose_splits(uint32_t batch, uint32_t num_kv_heads,
@@ -1574,8 +1826,10 @@ extern "C" size_t tq_decode_workspace_floats(uint32_t batch, uint32_t num_heads,
     const size_t rows = num_heads / num_kv_heads;
     // the partial records, then one arrival counter per (sequence, KV head, 8-row tile) for
     // the launches that fold the combine into the decode kernel
-    return static_cast<size_t>(batch) * num_kv_heads * splits * rows * (16u + head_size) +
-           static_cast<size_t>(batch) * num_kv_heads * ((rows + 7u) / 8u);
+    // ... and, 8-byte aligned behind them, the two 64-bit words of its chunk schedule
+    const size_t words = static_cast<size_t>(batch) * num_kv_heads * splits * rows * (16u + head_size) +
+                         static_cast<size_t>(batch) * num_kv_heads * ((rows + 7u) / 8u);
+    return (words + 1u) / 2u * 2u + 4u;
 }
 
 extern "C" int tq_decode_splitk_partials(void* stream, const uint16_t* q, const void* signs,
@@ -1648,7 +1902,7 @@ static int splitk_combine(void* stream, const float* workspace, const float* pi_
                           uint32_t splits, uint32_t output_stage, float inv_sqrt_len,
                           uint32_t tokens_per_req = 1, uint32_t kv_heads = 1, uint32_t rotation = ~0u)
 {
-    if (!rows || rows > rows_stride || !splits || splits > 16 || output_stage > TQ_OUT_GATED ||
+    if (!rows || rows > rows_stride || !splits || splits > TQ_MAX_SPLITS || output_stage > TQ_OUT_GATED ||
         out_dtype > TQ_DTYPE_F32 || gate_dtype > TQ_DTYPE_F32 ||
         (head_size != 128 && head_size != 256))
         return TQ_ERR_INVALID_ARGUMENT;
@@ -1706,6 +1960,7 @@ struct DecodeOptions {
     uint32_t nz_slot_floats = 0;         // != 0: NZ-tiled source pools, floats per slot of the scale records
     float nz_gain = 1.0f;                // the codebook gain those scales are divided by
     bool precise = false;                // 24-bit fixed-point query and P as hi + lo halves (classic grid)
+    bool persistent = false;             // one launch: persistent grid, combine folded in
 };
 
 // Validates a decode call and fills the kernel parameters (everything but the combine part).
@@ -1720,7 +1975,7 @@ static int decode_params(DecodeParams& p, const uint16_t* query, const int8_t* k
                          bool needs_workspace = true)
 {
     if (!num_heads || !num_kv_heads || num_heads % num_kv_heads != 0 || !block_size ||
-        block_size % kStrip != 0 || !num_blocks || !max_blocks || !splits || splits > 16 ||
+        block_size % kStrip != 0 || !num_blocks || !max_blocks || !splits || splits > TQ_MAX_SPLITS ||
         (head_size != 128 && head_size != 256))
         return TQ_ERR_INVALID_ARGUMENT;
     // the kernels take the maximum of raw scores before the positive per-row factor is applied
@@ -1812,7 +2067,7 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
                                        uint32_t max_context_hint, float inv_sqrt_len,
                                        float softmax_scale, uint32_t* status)
 {
-    if (!num_kv_heads || !block_size || splits > 16) return TQ_ERR_INVALID_ARGUMENT;
+    if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
                             &chunk_pages);
@@ -1822,11 +2077,11 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
                                  inv_sqrt_len, softmax_scale, status);
 }
 
-// One decode call, split plan resolved. A plan the library made itself (chunk_pages != 0)
-// runs on the persistent grid, which deals the batch's tiles to one resident wave of CTAs in
-// equal shares and folds the combine in: one launch, no second pass over the records. A split
-// count the caller fixed keeps the reference's page partition per sequence: the classic grid
-// exports `splits` records per head and the combine kernel merges them.
+// One decode call, split plan resolved. The classic grid exports `splits` records per head
+// (a plan the library made itself gives every sequence as many as it has chunks; a split
+// count the caller fixed keeps the reference's page partition) and the combine kernel merges
+// them; one split finishes inside the export kernel. `persistent` selects the single-launch
+// persistent grid instead (tq_decode_splitk_persistent).
 static int decode_planned(void* stream, const uint16_t* query, const int8_t* key_cache,
                           const int8_t* value_cache, const float* scale_cache,
                           const int32_t* block_tables, const int32_t* context_lens,
@@ -1841,7 +2096,7 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
         (output_stage == TQ_OUT_GATED && !gate))
         return TQ_ERR_INVALID_ARGUMENT;
     const uint32_t rotation = o.rotation != ~0u ? o.rotation : (pi_signs == nullptr ? 1u : 0u);
-    const bool persistent = chunk_pages != 0u && splits >= 2u && !o.precise;
+    const bool persistent = o.persistent && splits >= 2u && !o.precise;
     if (persistent || splits == 1u) {
         // one launch: the persistent grid, or (one split) the classic grid whose CTAs hold a
         // head's whole state and write the output themselves without touching the workspace
@@ -1853,9 +2108,12 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
         if (st != TQ_OK || batch == 0) return st;
         if (output_stage != TQ_OUT_ROTATED && rotation != 1u && !pi_signs) return TQ_ERR_INVALID_ARGUMENT;
         if (persistent) {
-            // the counters follow the records (tq_decode_workspace_floats)
-            p.counters = reinterpret_cast<uint32_t*>(
-                workspace + static_cast<size_t>(batch) * num_kv_heads * splits * p.rows * (16u + head_size));
+            // the counters follow the records, the schedule words the counters (tq_decode_workspace_floats)
+            if ((reinterpret_cast<uintptr_t>(workspace) & 7u) != 0u) return TQ_ERR_INVALID_ARGUMENT;
+            const size_t records = static_cast<size_t>(batch) * num_kv_heads * splits * p.rows * (16u + head_size);
+            const size_t counters = static_cast<size_t>(batch) * num_kv_heads * ((p.rows + 7u) / 8u);
+            p.counters = reinterpret_cast<uint32_t*>(workspace + records);
+            p.ticket = reinterpret_cast<unsigned long long*>(workspace + (records + counters + 1u) / 2u * 2u);
             p.tag = next_launch_tag();
         }
         p.egress_signs = pi_signs;
@@ -1900,7 +2158,7 @@ extern "C" int tq_decode_splitk_elem(void* stream, const void* query, const int8
                                      uint32_t output_stage, float inv_sqrt_len, float softmax_scale,
                                      uint32_t* status)
 {
-    if (!num_kv_heads || !block_size || splits > 16 ||
+    if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS ||
         (elem_dtype != TQ_DTYPE_BF16 && elem_dtype != TQ_DTYPE_F16))
         return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
@@ -1925,7 +2183,7 @@ extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_
                                 uint32_t max_context_hint, uint32_t output_stage,
                                 float inv_sqrt_len, float softmax_scale, uint32_t* status)
 {
-    if (!num_kv_heads || !block_size || splits > 16) return TQ_ERR_INVALID_ARGUMENT;
+    if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
                             &chunk_pages);
@@ -1952,7 +2210,7 @@ extern "C" int tq_decode_splitk_mtp(void* stream, const uint16_t* query, const i
                                     uint32_t output_stage, float inv_sqrt_len, float softmax_scale,
                                     uint32_t* status)
 {
-    if (!num_kv_heads || !block_size || splits > 16 || tokens_per_req == 0) return TQ_ERR_INVALID_ARGUMENT;
+    if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS || tokens_per_req == 0) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
                             &chunk_pages);
@@ -1987,7 +2245,7 @@ extern "C" int tq_decode_splitk_prerotated(void* stream, const float* query_rot,
                                            uint32_t code_grid, uint32_t output_stage, float softmax_scale,
                                            uint32_t* status)
 {
-    if (!num_kv_heads || !block_size || splits > 16 || code_grid > 1u || (batch != 0 && !query_rot) ||
+    if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS || code_grid > 1u || (batch != 0 && !query_rot) ||
         output_stage > TQ_OUT_GATED || gate_dtype > TQ_DTYPE_F32 ||
         (output_stage != TQ_OUT_ROTATED && !pi_signs) || (head_size != 128 && head_size != 256))
         return TQ_ERR_INVALID_ARGUMENT;
@@ -2006,6 +2264,38 @@ extern "C" int tq_decode_splitk_prerotated(void* stream, const float* query_rot,
                           output_stage, inv_sqrt_len, softmax_scale, status, o);
 }
 
+// tq_decode_splitk as ONE launch: a persistent grid (one resident wave of CTAs) over the
+// batch's 48-token tiles, flattened sequence by sequence and head by head and cut into chunks
+// by a schedule every CTA can evaluate (85 % of an equal share dealt statically, the rest taken
+// in eighths and sixteenths of a share from an atomic ticket); a CTA walks the (sequence, KV
+// head) segments of its chunks, publishes one record per segment, counts its arrival at the
+// head, and the CTA that arrives last merges the head's records and writes the output -- no
+// second kernel, nobody waits for anybody. `splits` is the number of record slots per head the
+// workspace holds (2..TQ_MAX_SPLITS, 0 = TQ_MAX_SPLITS); size it with
+// tq_decode_workspace_floats. Measured on B200 the segment boundaries (about 12 us each:
+// rotation, record, fence, arrival, draw) cost more than a hardware-scheduled CTA's, so on
+// the ragged benchmark batch this entry runs at about 0.85 of tq_decode_splitk's rate; it is
+// the choice where one graph node or one launch matters more.
+extern "C" int tq_decode_splitk_persistent(void* stream, const uint16_t* query, const int8_t* key_cache,
+                                           const int8_t* value_cache, const float* scale_cache,
+                                           const int32_t* block_tables, const int32_t* context_lens,
+                                           const float* pi_signs, const float* gate, float* workspace,
+                                           void* output, uint32_t out_dtype, uint32_t batch,
+                                           uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                                           uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                                           uint32_t splits, uint32_t output_stage, float inv_sqrt_len,
+                                           float softmax_scale, uint32_t* status)
+{
+    if (!num_kv_heads || !block_size || splits == 1u || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
+    DecodeOptions o;
+    o.persistent = true;
+    return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
+                          context_lens, pi_signs, gate, workspace, output, out_dtype, batch, num_heads,
+                          num_kv_heads, head_size, block_size, num_blocks, max_blocks,
+                          splits ? splits : TQ_MAX_SPLITS, 0u, output_stage, inv_sqrt_len, softmax_scale,
+                          status, o);
+}
+
 // tq_decode_splitk with the wider arithmetic of the reference-contract entry: the query as a
 // 24-bit fixed point (three limbs) and P as a hi + lo pair of halves, so the error no longer
 // scales with the magnitude of the values. For callers whose values are far from unit
@@ -2021,7 +2311,7 @@ extern "C" int tq_decode_splitk_precise(void* stream, const uint16_t* query, con
                                         uint32_t output_stage, float inv_sqrt_len, float softmax_scale,
                                         uint32_t* status)
 {
-    if (!num_kv_heads || !block_size || splits > 16) return TQ_ERR_INVALID_ARGUMENT;
+    if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
                             &chunk_pages);
@@ -2056,7 +2346,7 @@ extern "C" int tq_decode_splitk_nz(void* stream, const float* query_rot, const u
                                    float gain, float inv_sqrt_len, float softmax_scale, uint32_t precise,
                                    uint32_t* status)
 {
-    if (!num_kv_heads || (block_size != 64 && block_size != 128) || splits > 16 || code_grid > 1u ||
+    if (!num_kv_heads || (block_size != 64 && block_size != 128) || splits > TQ_MAX_SPLITS || code_grid > 1u ||
         (batch != 0 && !query_rot) || output_stage > TQ_OUT_GATED || gate_dtype > TQ_DTYPE_F32 ||
         (output_stage != TQ_OUT_ROTATED && !pi_signs) || !(gain > 0.0f))
         return TQ_ERR_INVALID_ARGUMENT;
@@ -2085,7 +2375,8 @@ extern "C" int tq_decode_splitk_nz(void* stream, const float* query_rot, const u
 // embedded in a runtime whose allocator it may not call from the launch path. For
 // them the partials go into this fixed array, which every GPU that loads the library
 // carries until the process exits: 8 MiB, enough for e.g. 64 sequences x 8 KV heads
-// x 4 splits x 4 query rows per KV head at head size 128.
+// x 4 record slots x 4 query rows per KV head at head size 128 (a launch that leaves the
+// split plan to the library asks for up to 32 slots per head: 8 such sequences).
 static __device__ __align__(256) float g_static_workspace[TQ_STATIC_WORKSPACE_FLOATS];
 
 // In host code `g_static_workspace` is only a handle for the device symbol, not a
@@ -2131,7 +2422,8 @@ extern "C" int tq_decode_splitk_static(void* stream, const uint16_t* query, cons
 {
     // geometry first, so that nonsense is refused as nonsense and not as "too large"
     if (!num_kv_heads || !num_heads || num_heads % num_kv_heads != 0 || num_heads / num_kv_heads > 16 ||
-        !block_size || block_size % kStrip != 0 || splits > 16 || (head_size != 128 && head_size != 256))
+        !block_size || block_size % kStrip != 0 || splits > TQ_MAX_SPLITS ||
+        (head_size != 128 && head_size != 256))
         return TQ_ERR_INVALID_ARGUMENT;
     // Resolve the split count first: it decides how much of the array the launch needs.
     uint32_t chunk_pages = 0;

@@ -9,6 +9,7 @@ from ._lib import TqError, load_library
 SIGNS_F32, SIGNS_TABLES_I8, SIGNS_TABLES_BF16 = 0, 1, 2
 OUT_ROTATED, OUT_UNROTATED, OUT_GATED = 0, 1, 2
 STATUS_BAD_SLOT, STATUS_BAD_PAGE, STATUS_WAIT_EXPIRED = 1, 2, 4
+MAX_SPLITS = 32
 
 
 def _ptr(t):
@@ -179,6 +180,18 @@ def decode_workspace_floats(batch, num_heads, num_kv_heads, head_size, splits):
                                                      splits)
 
 
+def worker_census(words=None):
+    """Registers (or, with None, removes) the int64 device tensor in which the CTAs of persistent
+    decode launches stamp four words each: start and end in nanoseconds of the global timer, the
+    nanoseconds the first warp spent in tile loops, the segments served."""
+    lib = load_library()
+    if words is None:
+        _check(lib.tq_decode_worker_census(None, 0), "tq_decode_worker_census")
+        return
+    call = _Call("worker_census").take("words", words, (torch.int64,))
+    _check(lib.tq_decode_worker_census(_ptr(words), words.numel() // 10), "tq_decode_worker_census")
+
+
 def choose_splits(batch, num_kv_heads, block_size, max_context, sm_count=None):
     """The split count a launch with splits=0 resolves to (sm_count: the launching device's)."""
     return load_library().tq_decode_choose_splits(batch, num_kv_heads, block_size, max_context,
@@ -196,15 +209,30 @@ def _decode_operands(call, key_cache, value_cache, scale_cache, block_tables, co
 def decode_splitk(query, key_cache, value_cache, scale_cache, block_tables, context_lens,
                   pi_signs, output, *, num_heads, num_kv_heads, head_size, block_size, num_blocks,
                   inv_sqrt_len, softmax_scale=1.0, splits=0, max_context_hint=0, workspace=None,
-                  gate=None, output_stage=OUT_ROTATED, status=None, stream=None, precise=False):
+                  gate=None, output_stage=OUT_ROTATED, status=None, stream=None, precise=False,
+                  persistent=False):
     """Paged split-K decode over query / block_tables / context_lens. query bfloat16, gate
-    float32. precise=True selects the wider arithmetic (24-bit query, hi + lo softmax weights)."""
+    float32. precise=True selects the wider arithmetic (24-bit query, hi + lo softmax weights);
+    persistent=True the single-launch persistent grid, where `splits` is the number of record
+    slots per head the workspace holds (0 = 32)."""
     lib = load_library()
     call = _Call("decode_splitk").take("query", query, _BF16)
     _decode_operands(call, key_cache, value_cache, scale_cache, block_tables, context_lens, pi_signs, output,
                      gate, status)
     batch = query.numel() // (num_heads * head_size)
     max_blocks = block_tables.shape[-1]
+    if persistent:
+        slots = splits if splits else MAX_SPLITS
+        _need_workspace(call, workspace, batch, num_heads, num_kv_heads, head_size, block_size, max_blocks,
+                        slots, max_context_hint, always=True)
+        with call:
+            _check(lib.tq_decode_splitk_persistent(
+                _stream(stream, call.device), _ptr(query), _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache),
+                _ptr(block_tables), _ptr(context_lens), _ptr(pi_signs), _ptr(gate), _ptr(workspace),
+                _ptr(output), _out_dtype(output), batch, num_heads, num_kv_heads, head_size, block_size,
+                num_blocks, max_blocks, splits, output_stage, inv_sqrt_len, softmax_scale, _ptr(status)),
+                "tq_decode_splitk_persistent")
+        return
     _need_workspace(call, workspace, batch, num_heads, num_kv_heads, head_size, block_size, max_blocks, splits,
                     max_context_hint)
     fn, name = ((lib.tq_decode_splitk_precise, "tq_decode_splitk_precise") if precise

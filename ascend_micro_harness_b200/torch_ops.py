@@ -101,13 +101,15 @@ def _decode_combine(workspace, gate, pi_signs, num_heads, num_kv_heads, temporal
 
 
 def _workspace_size(num_reqs, num_heads, num_kv_heads, head_size, temporal_splits):
-    """Floats of workspace (tq_decode_workspace_floats): the records of every split plus one
-    arrival counter per (request, KV head, 8-row tile). temporal_splits 0 leaves the choice to
-    the launch, which never takes more than 16: sized for that."""
+    """Floats of workspace (tq_decode_workspace_floats): the records of every split, one arrival
+    counter per (request, KV head, 8-row tile) and, 8-byte aligned behind them, two 64-bit
+    schedule words. temporal_splits 0 leaves the choice to the launch, which never takes more
+    than 32 splits: sized for that."""
     rows = num_heads // num_kv_heads
-    splits = temporal_splits if temporal_splits else 16
-    return (num_reqs * num_kv_heads * splits * rows * (16 + head_size)
-            + num_reqs * num_kv_heads * ((rows + 7) // 8))
+    splits = temporal_splits if temporal_splits else 32
+    words = (num_reqs * num_kv_heads * splits * rows * (16 + head_size)
+             + num_reqs * num_kv_heads * ((rows + 7) // 8))
+    return (words + 1) // 2 * 2 + 4
 
 
 for _name, _fn in (("reshape_aligned", _reshape_aligned), ("reshape_scatter", _reshape_scatter),

@@ -3,7 +3,7 @@
 
 One "step" is the fused decode step of the batched ragged workload: the scatter
 write of one new token per sequence into the paged 4-bit cache, followed by paged
-split-K decode attention (one persistent kernel that also merges the partials).
+split-K decode attention (export of per-split partials + log-sum-exp combine).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -277,7 +277,7 @@ def run_ours(args):
             "scaling": "strong" if long_ctx else "weak",
             "vs_baseline": None, "dtype": "int4 codes; QK s8 x s8 -> s32, PV f16 x f16 -> f32", "data": "synthetic",
             "config": {"workload": LONG_WORKLOAD if long_ctx else WORKLOAD, "batch_per_gpu": nseq, "q_heads": HQ,
-                       "kv_heads": HKV, "head_dim": D, "page_tokens": S, "record_slots_per_head": res["splits"],
+                       "kv_heads": HKV, "head_dim": D, "page_tokens": S, "splits": res["splits"],
                        "kv_bytes_per_gpu": res["bytes"],
                        "l2": "inputs larger than L2 (%.2f GB of cache read per step)" % (res["bytes"] / 1e9),
                        "parallelism": f"{nseq * world} sequences dealt to {world} GPU(s) "
@@ -291,9 +291,9 @@ def run_ours(args):
             "e2e": {"value": round(total_bytes / (res["ms_e2e"] * 1e-3) / 1e9, 1),
                     "unit": "GB/s", "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
                     "ms_per_step": round(res["ms_e2e"], 4), "issue": res["e2e_issue"]},
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": 3 * args.steps,
             "issue": res["issue"],
-            "roofline": {"kernel": "tq_decode_partial_kernel<128, persistent>", "bound": "hbm",
+            "roofline": {"kernel": "tq_decode_partial_kernel<128>", "bound": "hbm",
                          "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
                          "traffic": int(res["bytes"] * DECODE_TRAFFIC_BYTES_PER_ALGORITHMIC_BYTE)},
@@ -331,7 +331,7 @@ def fused_step_bench(torch, tq, dev, dist, ctx, seed, steps, warmup, verify, e2e
     out = torch.zeros((nseq, HQ, D), dtype=torch.bfloat16, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     # Per-step host inputs live in ONE pinned staging buffer (k | v | q | slots | lens) with a
-    # device twin, so the end-to-end step is one host->device copy, the two launches and one
+    # device twin, so the end-to-end step is one host->device copy, the three launches and one
     # device->host copy of the output.
     parts = [w["hk"], w["hv"], w["hq"], w["hslots"], w["hctx"]]
     sizes = [(t.numel() * t.element_size() + 255) // 256 * 256 for t in parts]
@@ -358,6 +358,16 @@ def fused_step_bench(torch, tq, dev, dist, ctx, seed, steps, warmup, verify, e2e
         tq.decode_splitk(dq, w["key_cache"], w["value_cache"], w["scale_cache"], w["tables"], dctx, w["signs"],
                          out, num_heads=HQ, splits=0, softmax_scale=scale, max_context_hint=int(ctx1.max()),
                          workspace=ws, output_stage=tq.OUT_UNROTATED, status=status, **geom)
+
+    # the two kernels of decode() launched one by one, for timing the dominant one alone
+    def export():
+        tq.decode_splitk_export(dq, w["key_cache"], w["value_cache"], w["scale_cache"], w["tables"], dctx,
+                                w["signs"], ws, num_heads=HQ, splits=0, softmax_scale=scale,
+                                max_context_hint=int(ctx1.max()), status=status, **geom)
+
+    def combine():
+        tq.splitk_combine(ws, w["signs"], None, out, items=nseq * HKV, rows=HQ // HKV, rows_stride=HQ // HKV,
+                          head_size=D, splits=splits, output_stage=tq.OUT_UNROTATED, inv_sqrt_len=w["inv"])
 
     def step():
         scatter()
@@ -408,19 +418,19 @@ def fused_step_bench(torch, tq, dev, dist, ctx, seed, steps, warmup, verify, e2e
 
     for _ in range(warmup):
         step()
-    # The timed steps are issued as replays of one captured step (scatter, decode): one host call
+    # The timed steps are issued as replays of one captured step (scatter, export, combine): one host call
     # per step, so a short run is not dominated by the first step's launch gaps.
-    step_issue, issue = step, "2 launches per step"
+    step_issue, issue = step, "3 launches per step"
     try:
         torch.cuda.synchronize()
         step_graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(step_graph):
             step()
-        step_issue, issue = step_graph.replay, "one CUDA graph replay (2 kernels) per step"
+        step_issue, issue = step_graph.replay, "one CUDA graph replay (3 kernels) per step"
         step_issue()
     except Exception as exc:
         print(f"bench.py: CUDA graph capture of the step failed ({exc}); eager launches", file=sys.stderr)
-        step_issue, issue = step, "2 launches per step"
+        step_issue, issue = step, "3 launches per step"
     if sampler is not None:      # clocks and throttle reasons DURING the timed regions only
         sampler.start()
     ms_total = timed(step_issue, steps)
@@ -429,7 +439,7 @@ def fused_step_bench(torch, tq, dev, dist, ctx, seed, steps, warmup, verify, e2e
     ms_e2e, e2e_issue = float("nan"), None
     if e2e:
         # The end-to-end step as a serving loop issues it: host->device copy of the step's inputs,
-        # the two launches and the device->host copy of the output captured once as a CUDA graph
+        # the three launches and the device->host copy of the output captured once as a CUDA graph
         # (the library neither allocates nor synchronises, so its launches are capturable), then
         # one graph launch and one stream synchronisation per step.
         e2e_graph = None
@@ -457,8 +467,8 @@ def fused_step_bench(torch, tq, dev, dist, ctx, seed, steps, warmup, verify, e2e
         for _ in range(3):
             e2e_step()
         ms_e2e = timed(e2e_step, steps) / steps
-        e2e_issue = ("one CUDA graph (copy in, 2 kernels, copy out) + stream sync per step"
-                     if e2e_graph is not None else "4 calls + stream sync per step")
+        e2e_issue = ("one CUDA graph (copy in, 3 kernels, copy out) + stream sync per step"
+                     if e2e_graph is not None else "5 calls + stream sync per step")
 
     # the dominant kernel on its own, CUDA events on the launching stream
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
@@ -467,8 +477,9 @@ def fused_step_bench(torch, tq, dev, dist, ctx, seed, steps, warmup, verify, e2e
     for a, b in evs:
         scatter()
         a.record()
-        decode()
+        export()
         b.record()
+        combine()
     barrier()
     kernel_samples = [a.elapsed_time(b) for a, b in evs]
     clocks = sampler.stop() if sampler is not None else None
@@ -699,6 +710,62 @@ def nz_case(torch, tq, dev, reps):
             "frac_of_hbm_peak": round(nbytes / (ms * 1e-3) / 1e9 / peak, 4), "us": summary(samples)}
 
 
+def persistent_case(torch, tq, dev, reps):
+    """The single-launch persistent grid (tq_decode_splitk_persistent) on the ragged batch, beside
+    the default two-kernel decode on the same inputs, with its worker census: segments per CTA
+    and microseconds per segment boundary."""
+    ctx = context_lengths(4)
+    w = build_workload(torch, dev, 4, ctx)
+    n = len(ctx)
+    dq, dctx = w["hq"].to(dev), w["hctx"].to(dev)
+    ws = torch.empty(tq.decode_workspace_floats(n, HQ, HKV, D, tq.MAX_SPLITS), dtype=torch.float32, device=dev)
+    out = torch.zeros((n, HQ, D), dtype=torch.bfloat16, device=dev)
+    ref = torch.zeros_like(out)
+    geom = dict(num_heads=HQ, num_kv_heads=HKV, head_size=D, block_size=S, num_blocks=w["total_pages"],
+                inv_sqrt_len=w["inv"], softmax_scale=float(1.0 / np.sqrt(D)), output_stage=tq.OUT_UNROTATED)
+    args = (dq, w["key_cache"], w["value_cache"], w["scale_cache"], w["tables"], dctx, w["signs"])
+
+    def persistent():
+        tq.decode_splitk(*args, out, splits=0, workspace=ws, persistent=True, **geom)
+
+    def default():
+        tq.decode_splitk(*args, ref, splits=0, max_context_hint=int(w["ctx"].max()), workspace=ws, **geom)
+    default()
+    persistent()
+    torch.cuda.synchronize()
+    diff = (out.float() - ref.float()).abs().max().item()
+    if not diff <= 2e-2:          # two bf16 roundings of results that agree to about 1e-3
+        fail(f"persistent decode differs from the default decode by {diff}")
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+        torch.cuda.synchronize()
+        for a, b in evs:
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        return statistics.median(a.elapsed_time(b) for a, b in evs)
+    ms_p, ms_d = timed(persistent), timed(default)
+    cen = torch.zeros(10 * 1024, dtype=torch.int64, device=dev)
+    tq.worker_census(cen)
+    persistent()
+    torch.cuda.synchronize()
+    tq.worker_census(None)
+    c = cen.cpu().numpy().reshape(-1, 10)
+    c = c[c[:, 1] > 0]
+    busy = (c[:, 1] - c[:, 0]) / 1e3
+    nbytes = kv_bytes(w["ctx"])
+    return {"workload": WORKLOAD + " (decode only)", "persistent_ms": round(ms_p, 4), "default_ms": round(ms_d, 4),
+            "persistent_gbs": round(nbytes / (ms_p * 1e-3) / 1e9, 1), "default_gbs": round(nbytes / (ms_d * 1e-3) / 1e9, 1),
+            "census": {"ctas": int(len(c)), "segments_per_cta": round(float(c[:, 3].mean()), 2),
+                       "busy_us_mean": round(float(busy.mean()), 1), "busy_us_max": round(float(busy.max()), 1),
+                       "tile_loop_us_mean": round(float(c[:, 2].mean() / 1e3), 1),
+                       "boundary_us_per_segment": round(float(((busy - c[:, 2] / 1e3) / np.maximum(c[:, 3], 1)).mean()), 2)}}
+
+
 def side_measurements(torch, tq, dev, args):
     """The rest of the metric on one GPU: reshape tokens/s (int8 and bf16, head sizes 128 and
     256; 1 GiB / 0.5 GiB of activations, far beyond L2), decode at the reference kernels' own
@@ -714,6 +781,7 @@ def side_measurements(torch, tq, dev, args):
     out["decode_d256"] = decode_case(torch, tq, dev, 16, 4, 256, context_lengths(9, BATCH, 2048, 16384), reps)
     out["decode_config3_us"] = config3_case(torch, tq, dev)
     out["decode_nz_inplace"] = nz_case(torch, tq, dev, reps)
+    out["decode_persistent"] = persistent_case(torch, tq, dev, reps)
     return out
 
 
@@ -726,7 +794,9 @@ def _use_reference_geometry():
 def run_profile_case(args):
     """A small case of one kernel for an ncu capture: inputs larger than L2 but well under
     a GB on the device, a few warm-up launches and the captured ones.
-      decode  : 64 sequences x 2048..4096 tokens (about 0.2 GB of cache), the persistent kernel
+      decode  : 64 sequences x 2048..4096 tokens (about 0.2 GB of cache): export of the per-split
+                records (the dominant kernel) and the combine
+      decode_persistent : the same batch on the single-launch persistent grid
       decode_d256 : the same at head size 256 with 16 query / 4 KV heads
       decode_nz   : the in-place decode of NZ-tiled pools, 64 sequences x 1024..2048 tokens
       config3 : batch 1, context 4096, split-K swept over 1/2/4/8/16/auto: prints microseconds per decode
@@ -820,7 +890,7 @@ def run_profile_case(args):
                                 workspace=ws)
         torch.cuda.synchronize()
         print(json.dumps({"profile": "decode_nz", "kv_bytes": int(ctx.sum()) * (H * 256 + 32)}))
-    elif args.profile in ("decode", "decode_d256"):
+    elif args.profile in ("decode", "decode_d256", "decode_persistent"):
         if args.profile == "decode_d256":
             # the reference kernels' own geometry: head size 256, 16 query / 4 KV heads
             _use_reference_geometry()
@@ -832,7 +902,16 @@ def run_profile_case(args):
                          device=dev)
         dq, dctx = w["hq"].to(dev), w["hctx"].to(dev)
         out = torch.zeros((BATCH, HQ, D), dtype=torch.bfloat16, device=dev)
+        if args.profile == "decode_persistent":
+            ws = torch.zeros(tq.decode_workspace_floats(BATCH, HQ, HKV, D, tq.MAX_SPLITS), dtype=torch.float32,
+                             device=dev)
         for _ in range(5):
+            if args.profile == "decode_persistent":
+                tq.decode_splitk(dq, w["key_cache"], w["value_cache"], w["scale_cache"], w["tables"], dctx,
+                                 w["signs"], out, num_heads=HQ, num_kv_heads=HKV, head_size=D, block_size=S,
+                                 num_blocks=w["total_pages"], inv_sqrt_len=w["inv"], splits=0,
+                                 softmax_scale=float(1.0 / np.sqrt(D)), workspace=ws, output_stage=1, persistent=True)
+                continue
             tq.decode_splitk(dq, w["key_cache"], w["value_cache"], w["scale_cache"], w["tables"], dctx,
                              w["signs"], out, num_heads=HQ, num_kv_heads=HKV, head_size=D, block_size=S,
                              num_blocks=w["total_pages"], inv_sqrt_len=w["inv"], splits=0,
@@ -988,7 +1067,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements of `extra`")
     ap.add_argument("--no-verify", action="store_true", help="skip the oracle check before timing")
     ap.add_argument("--profile", default=None,
-                    choices=["decode", "decode_d256", "decode_nz", "config3", "reshape", "reshape_a8", "reshape_d256",
+                    choices=["decode", "decode_persistent", "decode_d256", "decode_nz", "config3", "reshape", "reshape_a8", "reshape_d256",
                              "reshape_a8_d256", "lm_decode", "lm_reshape", "scatter", "nz_import"],
                     help="run a small case of one kernel (for ncu), print no bench line")
     args = ap.parse_args()

@@ -67,6 +67,11 @@ extern "C" {
 #define TQ_OUT_UNROTATED 1u /* (acc / l) Pi                                     */
 #define TQ_OUT_GATED 2u     /* stage 1 divided by 1 + exp(-gate)                */
 
+/* Most record slots per (sequence, KV head) a decode workspace can be asked to hold: the
+ * largest split count the tq_* decode entries accept (the reference-contract entries keep the
+ * reference's own limits, 16 and 8). */
+#define TQ_MAX_SPLITS 32u
+
 /* Element type of the decode output. */
 #define TQ_DTYPE_BF16 0u
 #define TQ_DTYPE_F16 1u
@@ -146,7 +151,7 @@ int tq_reshape_scatter(void* stream, const uint16_t* key, const uint16_t* value,
  *   workspace     float [tq_decode_workspace_floats(...)]; always required (a launch
  *                 that resolves to one split still writes its records there)
  *   output        [batch][num_heads][d] of out_dtype (TQ_DTYPE_*)
- *   splits        1..16, or 0 to choose from context lengths and SM count;
+ *   splits        1..TQ_MAX_SPLITS, or 0 to choose from context lengths and SM count;
  *                 max_context_hint (0 = max_blocks*block_size) feeds that choice
  *                 since context_lens lives on the device
  *   softmax_scale multiplies every score (the AIC decoder uses 1) */
@@ -159,6 +164,25 @@ int tq_decode_splitk(void* stream, const uint16_t* query, const int8_t* key_cach
                      uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
                      uint32_t max_context_hint, uint32_t output_stage, float inv_sqrt_len,
                      float softmax_scale, uint32_t* status);
+
+/* tq_decode_splitk as one launch: a persistent grid over the batch's tiles with the
+ * log-sum-exp merge folded in (the CTA that finishes a head's last outstanding segment merges
+ * its records; no CTA waits for another). `splits` is the number of record slots per head the
+ * workspace holds, 2..TQ_MAX_SPLITS (0 = TQ_MAX_SPLITS); workspace as tq_decode_workspace_floats
+ * sizes it, 8-byte aligned. Other arguments as for tq_decode_splitk. Slower than
+ * tq_decode_splitk on ragged batches (segment boundaries cost more than hardware-scheduled
+ * CTAs); meant for callers to whom a single launch matters. The reference has no counterpart:
+ * its fused decoder merges after a grid-wide barrier
+ * (kernels/ops/turboquant/vllm_integration_layer/op_kernel/turboquant_fused_decode.cpp:1084). */
+int tq_decode_splitk_persistent(void* stream, const uint16_t* query, const int8_t* key_cache,
+                                const int8_t* value_cache, const float* scale_cache,
+                                const int32_t* block_tables, const int32_t* context_lens,
+                                const float* pi_signs, const float* gate, float* workspace,
+                                void* output, uint32_t out_dtype, uint32_t batch, uint32_t num_heads,
+                                uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                                uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                                uint32_t output_stage, float inv_sqrt_len, float softmax_scale,
+                                uint32_t* status);
 
 /* tq_decode_splitk with a 24-bit fixed-point query and the softmax weights carried as a
  * hi + lo pair of halves (the arithmetic of tq_decode_splitk_partials, whose records are held
@@ -188,7 +212,19 @@ int tq_decode_splitk_export(void* stream, const uint16_t* query, const int8_t* k
                             uint32_t splits, uint32_t max_context_hint, float inv_sqrt_len,
                             float softmax_scale, uint32_t* status);
 
-/* Split count the launcher would pick for splits == 0. */
+/* Worker census of the persistent decode grid (tq_decode_splitk_persistent), after the
+ * reference's WorkerMetrics (include/turboquant_splitk_contract.hpp:101-118): while a device
+ * buffer of 10 * capacity_ctas 64-bit words is registered, CTA c of such a launch stores in
+ * words 10c .. 10c + 8: the global-timer nanosecond at which it started, the one at which it
+ * left (0: it never had work), the nanoseconds its first warp spent inside tile loops, the
+ * number of segments it served, and the nanoseconds spent waiting for its slowest warp,
+ * merging + publishing + counting arrivals, finishing heads, locating the next chunk, and in
+ * segment prologues. Process-wide, for measurement runs only; pass NULL to switch it off. */
+int tq_decode_worker_census(unsigned long long* device_words, uint32_t capacity_ctas);
+
+/* Split count the launcher would pick for splits == 0 (1..TQ_MAX_SPLITS): what to size the
+ * workspace with. The plan cuts work into chunks of a power-of-two number of tokens (256..8192,
+ * about 32 CTAs per SM); a sequence uses as many splits as it has chunks. */
 uint32_t tq_decode_choose_splits(uint32_t batch, uint32_t num_kv_heads, uint32_t block_size,
                                  uint32_t max_context, uint32_t sm_count);
 
@@ -197,8 +233,10 @@ uint32_t tq_decode_choose_splits(uint32_t batch, uint32_t num_kv_heads, uint32_t
  * each row {m x8, l x8, acc[d]}, the record of
  * include/turboquant_splitk_contract.hpp:23-27 with kChannels -> head_size,
  * followed by one 32-bit arrival counter per (sequence, KV head, 8-row tile)
- * for the launches that merge inside the decode kernel. The counters need no
- * initialisation. For splits == 0 size it with tq_decode_choose_splits. */
+ * and two 64-bit words of chunk schedule for tq_decode_splitk_persistent, which
+ * merges inside the decode kernel (none of these needs initialisation; that entry
+ * wants the workspace 8-byte aligned). For splits == 0 size it with
+ * tq_decode_choose_splits. */
 size_t tq_decode_workspace_floats(uint32_t batch, uint32_t num_heads, uint32_t num_kv_heads,
                                   uint32_t head_size, uint32_t splits);
 
@@ -209,14 +247,17 @@ size_t tq_decode_workspace_floats(uint32_t batch, uint32_t num_heads, uint32_t n
  * from the launch path. The split-K partials go into a fixed 8 MiB array inside the
  * library (TQ_STATIC_WORKSPACE_FLOATS floats, resident on every GPU that loads the
  * library until the process exits); the call itself allocates and frees nothing.
- *   - Limit: batch * num_kv_heads * splits * (num_heads / num_kv_heads) * (16 + head_size)
- *     floats must fit; otherwise TQ_ERR_WORKSPACE_TOO_SMALL is returned and nothing runs.
- *     With splits == 0 the limit is checked against the split count the launcher picks.
+ *   - Limit: tq_decode_workspace_floats(batch, num_heads, num_kv_heads, head_size, splits)
+ *     must not exceed TQ_STATIC_WORKSPACE_FLOATS; otherwise TQ_ERR_WORKSPACE_TOO_SMALL is
+ *     returned and nothing runs. With splits == 0 the limit is checked against the record
+ *     slots the launcher picks (tq_decode_choose_splits, up to TQ_MAX_SPLITS per head); a
+ *     caller close to the limit passes an explicit split count instead.
  *   - The first call on each device looks up the array's device address (one CUDA
  *     runtime query, made with that device current). Make that first call before any
  *     stream capture begins.
  *   - All calls share the one array and it keeps whatever the last call left in it.
- *     Nothing needs clearing (each launch writes every record it later reads), but two
+ *     Nothing needs clearing (each launch writes every record it later reads, and its
+ *     counters are valid only under the launch's own tag), but two
  *     calls whose kernels can overlap on the GPU -- different streams, no ordering --
  *     race on it: keep calls on one device ordered.
  * Arguments are those of tq_decode_splitk without `workspace`. */

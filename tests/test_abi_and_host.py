@@ -42,29 +42,29 @@ def test_acl_shim_exports_the_sixteen_calls():
 
 def test_split_choice():
     """The plan cuts work into power-of-two chunks of 256..8192 tokens, about 32 CTAs per SM;
-    the launch's split count is what the longest context needs, at most 16."""
+    the launch's split count is what the longest context needs, at most TQ_MAX_SPLITS = 32."""
     import ascend_micro_harness_b200 as tq
-    sm = 148
-    import functools
-    tq = type("T", (), {"choose_splits": staticmethod(functools.partial(
-        lambda b, h, s, c, choose=tq.choose_splits: choose(b, h, s, c, sm)))})
-    assert tq.choose_splits(64, 8, 16, 256) == 1            # short contexts run un-split
-    assert tq.choose_splits(1, 8, 16, 4096) == 16           # one sequence: fill the machine
-    assert tq.choose_splits(1, 8, 16, 1024) == 4            # ... but keep 256 tokens per split
-    assert tq.choose_splits(64, 8, 16, 32768) == 8          # ragged batch: 4096-token chunks
-    assert tq.choose_splits(4096, 8, 16, 32768) == 4        # plenty of sequences: 8192-token chunks
-    assert tq.choose_splits(128, 8, 16, 65536) == 8
+    choose = lambda b, h, s, c: tq.choose_splits(b, h, s, c, 148)
+    assert choose(64, 8, 16, 256) == 1             # short contexts run un-split
+    assert choose(1, 8, 16, 4096) == 16            # one sequence: fill the machine
+    assert choose(1, 8, 16, 1024) == 4             # ... but keep 256 tokens per split
+    assert choose(64, 8, 16, 32768) == 8           # ragged batch: 4096-token chunks
+    assert choose(4096, 8, 16, 32768) == 4         # plenty of sequences: 8192-token chunks
+    assert choose(16, 8, 16, 65536) == 32          # few long sequences: 2048-token chunks
+    assert choose(128, 8, 16, 65536) == 8
     for b in (1, 3, 64, 1000):
         for ctx in (1, 600, 5000, 70000, 1 << 20):
-            s = tq.choose_splits(b, 8, 16, ctx)
-            assert 1 <= s <= 16 and s <= max(1, (ctx + 15) // 16)
+            s = choose(b, 8, 16, ctx)
+            assert 1 <= s <= 32 and s <= max(1, (ctx + 15) // 16)
 
 
 def test_workspace_sizing():
     import ascend_micro_harness_b200 as tq
     # the records, then one arrival counter per (sequence, KV head, 8-row tile)
-    assert tq.decode_workspace_floats(64, 32, 8, 128, 4) == 64 * 8 * 4 * 4 * (16 + 128) + 64 * 8
-    assert tq.decode_workspace_floats(2, 64, 4, 256, 8) == 2 * 4 * 8 * 16 * 272 + 2 * 4 * 2
+    # ... and, 8-byte aligned behind them, two 64-bit words of chunk schedule
+    assert tq.decode_workspace_floats(64, 32, 8, 128, 4) == 64 * 8 * 4 * 4 * (16 + 128) + 64 * 8 + 4
+    assert tq.decode_workspace_floats(2, 64, 4, 256, 8) == 2 * 4 * 8 * 16 * 272 + 2 * 4 * 2 + 4
+    assert tq.decode_workspace_floats(1, 1, 1, 128, 1) == 144 + 1 + 1 + 4      # padded to an even word count
 
 
 def test_geometry_is_refused_before_any_launch():
@@ -76,10 +76,10 @@ def test_geometry_is_refused_before_any_launch():
     assert lib.tq_reshape_and_cache(None, p, p, p, p, p, p, p, 0, 0, 32, 1, 96, 16, 4, 0.1, None) == 1
     assert lib.tq_reshape_and_cache(None, p, p, p, p, p, p, p, 0, 0, 32, 1, 128, 24, 4, 0.1, None) == 1
     assert lib.tq_reshape_and_cache(None, p, p, p, p, p, p, p, 0, 0, 0, 1, 128, 16, 4, 0.1, None) == 0
-    # decode: heads not a multiple of KV heads; 17 splits; bad head size
+    # decode: heads not a multiple of KV heads; 33 splits; bad head size
     args = [None, p, p, p, p, p, p, p, p, p, p, 0]
     assert lib.tq_decode_splitk(*args, 2, 30, 8, 128, 16, 8, 4, 1, 0, 0, 0.1, 1.0, None) == 1
-    assert lib.tq_decode_splitk(*args, 2, 32, 8, 128, 16, 8, 4, 17, 0, 0, 0.1, 1.0, None) == 1
+    assert lib.tq_decode_splitk(*args, 2, 32, 8, 128, 16, 8, 4, 33, 0, 0, 0.1, 1.0, None) == 1
     assert lib.tq_decode_splitk(*args, 2, 32, 8, 64, 16, 8, 4, 1, 0, 0, 0.1, 1.0, None) == 1
     # AIC contract: page window past the sequence, seq_len past the window
     # (reference: turboquant_paged_decode_attention.cpp:1747-1759)
@@ -93,6 +93,13 @@ def test_geometry_is_refused_before_any_launch():
         assert lib.tq_decode_splitk(*args, 2, 32, 8, 128, 16, 8, 4, 2, 0, 0, 0.1, bad, None) == 1
         assert lib.tq_decode_splitk_precise(*args, 2, 32, 8, 128, 16, 8, 4, 2, 0, 0, 0.1, bad, None) == 1
         assert lib.tq_decode_splitk_partials(*part, 1, 1, 16, 256, 128, 8, 4, 2, 0, 2, 0, 0.0625, bad, None) == 1
+    # the persistent entry takes 2..32 record slots per head (0 = 32), never one
+    pers = [None, p, p, p, p, p, p, p, p, p, p, 0]
+    assert lib.tq_decode_splitk_persistent(*pers, 2, 32, 8, 128, 16, 8, 4, 1, 0, 0.1, 1.0, None) == 1
+    assert lib.tq_decode_splitk_persistent(*pers, 2, 32, 8, 128, 16, 8, 4, 33, 0, 0.1, 1.0, None) == 1
+    assert lib.tq_decode_splitk_persistent(*pers, 0, 32, 8, 128, 16, 8, 4, 0, 0, 0.1, 1.0, None) == 0
+    misaligned = [None, p, p, p, p, p, p, p, p, C.c_void_p(20), p, 0]
+    assert lib.tq_decode_splitk_persistent(*misaligned, 2, 32, 8, 128, 16, 8, 4, 4, 0, 0.1, 1.0, None) == 1
     # one split needs no workspace; more than one does
     noworkspace = [None, p, p, p, p, p, p, p, p, None, p, 0]
     assert lib.tq_decode_splitk(*noworkspace, 0, 32, 8, 128, 16, 8, 4, 1, 0, 0, 0.1, 1.0, None) == 0
@@ -106,7 +113,7 @@ def test_nz_entry_and_static_entry_refuse_bad_geometry_on_the_host():
     nz = [None, p, p, p, p, p, p, p, p, p, p, 1, 1]
     tail = (2.98, 0.0625, 0.0625, 0, None)
     assert lib.tq_decode_splitk_nz(*nz, 2, 16, 4, 32, 0, 4, 2, 0, 1, 0, *tail) == 1      # pages are 64 or 128 slots
-    assert lib.tq_decode_splitk_nz(*nz, 2, 16, 4, 64, 0, 4, 17, 0, 1, 0, *tail) == 1     # 17 splits
+    assert lib.tq_decode_splitk_nz(*nz, 2, 16, 4, 64, 0, 4, 33, 0, 1, 0, *tail) == 1     # 33 splits
     assert lib.tq_decode_splitk_nz(*nz, 2, 16, 4, 64, 0, 4, 2, 0, 2, 0, *tail) == 1      # no such code grid
     assert lib.tq_decode_splitk_nz(*nz, 2, 18, 4, 64, 0, 4, 2, 0, 1, 0, *tail) == 1      # heads % KV heads
     assert lib.tq_decode_splitk_nz(*nz, 2, 16, 4, 64, 0, 4, 2, 0, 1, 0, 0.0, 0.0625, 0.0625, 0, None) == 1   # gain
@@ -162,7 +169,7 @@ def test_kv4_import_and_prerotated_decode_refuse_bad_arguments_on_the_host():
     assert lib.tq_nz_kv4_import(*bad, 2, 64, 4, 2.98) == 1     # packed plane not 16-byte aligned
     dec = [None, p, p, p, p, p, p, p, p, p, p, 0, 2]
     assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 1, 0, 2, 0, 0.0625, None) == 1   # no such grid
-    assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 17, 0, 1, 0, 0.0625, None) == 1  # 17 splits
+    assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 33, 0, 1, 0, 0.0625, None) == 1  # 33 splits
     assert lib.tq_decode_splitk_prerotated(*dec, 2, 30, 8, 256, 64, 8, 4, 1, 0, 1, 0, 0.0625, None) == 1   # heads % KV heads
     assert lib.tq_decode_splitk_prerotated(*dec, 2, 32, 8, 256, 64, 8, 4, 1, 0, 1, 3, 0.0625, None) == 1   # no such stage
     assert lib.tq_decode_splitk_prerotated(*dec, 0, 32, 8, 256, 64, 8, 4, 1, 0, 1, 0, 0.0625, None) == 0   # empty batch

@@ -22,7 +22,7 @@ def test_workspace_size_operator_counts_records_and_counters():
     for (b, hq, hkv, d, k) in ((64, 32, 8, 128, 9), (3, 64, 4, 256, 2), (1, 8, 8, 128, 16)):
         assert torch_ops._workspace_size(b, hq, hkv, d, k) == tq.decode_workspace_floats(b, hq, hkv, d, k)
     # splits left to the launch: sized for the most it can pick
-    assert torch_ops._workspace_size(5, 32, 8, 128, 0) == tq.decode_workspace_floats(5, 32, 8, 128, 16)
+    assert torch_ops._workspace_size(5, 32, 8, 128, 0) == tq.decode_workspace_floats(5, 32, 8, 128, 32)
 
 
 @pytest.mark.gpu

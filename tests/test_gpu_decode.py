@@ -184,7 +184,7 @@ def test_several_query_tokens_per_request(cuda, oracle, tpr, G, d):
                                    np.ascontiguousarray(gate[:, t]), scale)
     for splits in (1, 3, 0):
         use = splits if splits else tq.choose_splits(B, Hkv, S, max(ctx))
-        ws = torch.full((B * Hkv * use * tpr * G * (16 + d),), float("nan"), device=cuda)
+        ws = torch.full((tq.decode_workspace_floats(B, Hq * tpr, Hkv, d, use),), float("nan"), device=cuda)
         out = torch.zeros((B * tpr, Hq, d), dtype=torch.float32, device=cuda)
         st = torch.zeros(1, dtype=torch.int32, device=cuda)
         tq.decode_splitk_mtp(dev(cuda, q.reshape(B * tpr, Hq, d)), dev(cuda, cache["key_cache"]),

@@ -53,12 +53,14 @@ def test_reference_fused_decode_opt_validation(cuda):
     ("--context", "1024,4096", "--iters", "3", "--warmup", "1"),
     ("--context", "2048", "--splitk", "1,4", "--iters", "2", "--warmup", "1", "--pre-rotate", "off",
      "--post-rotate", "rotated"),
-    ("--context", "2048", "--splitk", "2", "--iters", "2", "--warmup", "1", "--pre-rotate", "off",
-     "--post-rotate", "gated"),
 ])
 def test_reference_decode_benchmark_fused_entries(cuda, argv):
     """The reference's decode benchmark drives both fused entries through its rig, which
-    validates every launch (tests/npu/turboquant_fused_decode_opt_rig.hpp:181-270)."""
+    validates every launch (tests/npu/turboquant_fused_decode_opt_rig.hpp:181-270). Output
+    stages 1 and 2 of the raw-query entry cannot be validated by that rig at all: its
+    reference_bits() refuses any expected value outside [1, 15]
+    (tests/common/fused_decode_opt_fixture.hpp:47-55), which un-rotated and gated contexts leave;
+    those stages are held to Fixture::expected_row in test_gpu_nz_inplace.py instead."""
     out = run("bench_turboquant_decode_splitk", *argv)
     assert "FAIL" not in out
 

@@ -1,8 +1,10 @@
-"""The persistent decode grid (splits = 0: the batch's tiles dealt to one resident wave of CTAs
-in equal shares, the last CTA to finish a head merges its records and writes the output) against
-the FP64 oracle and against the classic grid, on batches chosen for what can break it: heads
-that straddle several CTAs, heads that fit inside one, empty and one-token sequences, two row
-tiles per KV head, several query tokens per request, counter words that start as garbage."""
+"""The persistent decode grid (tq_decode_splitk_persistent: the batch's tiles cut into chunks
+that one resident wave of CTAs takes, first statically and then off an atomic ticket; the last
+CTA to finish a head merges its records and writes the output) against the FP64 oracle and
+against the classic grid, on batches chosen for what can break it: heads that straddle several
+chunks, heads that fit inside one, empty and one-token sequences, two row tiles per KV head,
+counter and ticket words that start as garbage, and the split plan of the classic grid with
+several query tokens per request."""
 import numpy as np
 import pytest
 
@@ -12,7 +14,8 @@ from tests.test_gpu_decode import assert_close, dev, oracle_decode
 pytestmark = pytest.mark.gpu
 
 
-def launch(cuda, q, cache, Hq, Hkv, d, S, ws, stage=0, gate=None, scale=0.1, out_dtype=None, splits=0, hint=None):
+def launch(cuda, q, cache, Hq, Hkv, d, S, ws, stage=0, gate=None, scale=0.1, out_dtype=None, splits=0, hint=None,
+           persistent=True):
     import torch
     import ascend_micro_harness_b200 as tq
     out = torch.full((q.shape[0], Hq, d), 7.0, dtype=out_dtype or torch.float32, device=cuda)
@@ -23,16 +26,18 @@ def launch(cuda, q, cache, Hq, Hkv, d, S, ws, stage=0, gate=None, scale=0.1, out
                      num_heads=Hq, num_kv_heads=Hkv, head_size=d, block_size=S, num_blocks=cache["num_blocks"],
                      inv_sqrt_len=hp.inv_sqrt_len(d), softmax_scale=scale, splits=splits,
                      max_context_hint=int(cache["context_lens"].max()) if hint is None else hint, workspace=ws,
-                     gate=None if gate is None else dev(cuda, gate), output_stage=stage, status=st)
+                     gate=None if gate is None else dev(cuda, gate), output_stage=stage, status=st,
+                     persistent=persistent)
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     return out.float().cpu().numpy()
 
 
-def workspace(cuda, B, Hq, Hkv, d, S, max_ctx, fill):
+def workspace(cuda, B, Hq, Hkv, d, S, max_ctx, fill, n=None):
+    """A workspace for `n` record slots per head (default: all 32), every word set to `fill`."""
     import torch
     import ascend_micro_harness_b200 as tq
-    n = tq.choose_splits(B, Hkv, S, max_ctx)
+    n = n or tq.MAX_SPLITS
     ws = torch.empty(tq.decode_workspace_floats(B, Hq, Hkv, d, n), dtype=torch.float32, device=cuda)
     ws.view(torch.int32).fill_(fill)
     return ws, n
@@ -47,7 +52,6 @@ def test_ragged_batch_against_the_oracle(cuda, oracle, d, Hq, Hkv, S):
     want = oracle_decode(oracle, q, cache, Hq, Hkv, d, S, softmax_scale=0.1)
     # counters that start as 0xFFFFFFFF, as zeros, and as whatever the previous launch left
     ws, n = workspace(cuda, len(ctx), Hq, Hkv, d, S, max(ctx), -1)
-    assert n >= 2
     first = launch(cuda, q, cache, Hq, Hkv, d, S, ws)
     again = launch(cuda, q, cache, Hq, Hkv, d, S, ws)
     ws0, _ = workspace(cuda, len(ctx), Hq, Hkv, d, S, max(ctx), 0)
@@ -62,7 +66,10 @@ def test_ragged_batch_against_the_oracle(cuda, oracle, d, Hq, Hkv, S):
     import torch
     import ascend_micro_harness_b200 as tq
     wsc = torch.full((tq.decode_workspace_floats(len(ctx), Hq, Hkv, d, 3),), float("nan"), device=cuda)
-    assert_close(launch(cuda, q, cache, Hq, Hkv, d, S, wsc, splits=3), want)
+    assert_close(launch(cuda, q, cache, Hq, Hkv, d, S, wsc, splits=3, persistent=False), want)
+    # few record slots: the chunks stay wide enough that no head needs more than the workspace holds
+    ws4, _ = workspace(cuda, len(ctx), Hq, Hkv, d, S, max(ctx), -1, n=4)
+    assert_close(launch(cuda, q, cache, Hq, Hkv, d, S, ws4, splits=4), want)
 
 
 def test_counter_words_that_look_like_counts_of_another_launch(cuda, oracle):
@@ -112,8 +119,8 @@ def test_sixteen_rows_per_kv_head_use_two_row_tiles(cuda, oracle, d):
 
 
 def test_several_query_tokens_per_request(cuda, oracle):
-    """tokens_per_req = 3 on the persistent grid: query token t sees the context without its
-    last 2 - t tokens (the oracle is the ordinary decode run once per query token)."""
+    """tokens_per_req = 3 with the split plan left to the library: query token t sees the context
+    without its last 2 - t tokens (the oracle is the ordinary decode run once per query token)."""
     import torch
     import ascend_micro_harness_b200 as tq
     rng = np.random.default_rng(77)
@@ -152,11 +159,11 @@ def test_one_split_writes_the_output_without_a_workspace(cuda, oracle):
     cache = hp.build_cache_from_gaussian(oracle, rng, ctx, Hkv, d, S)
     q = hp.bf16_from_f32(rng.standard_normal((len(ctx), Hq, d)).astype(np.float32))
     want = oracle_decode(oracle, q, cache, Hq, Hkv, d, S, 1, None, 0.1)
-    got = launch(cuda, q, cache, Hq, Hkv, d, S, None, stage=1, splits=1)
+    got = launch(cuda, q, cache, Hq, Hkv, d, S, None, stage=1, splits=1, persistent=False)
     assert_close(got, want)
     assert (got[1] == 0).all()
     ws = torch.full((tq.decode_workspace_floats(len(ctx), Hq, Hkv, d, 1),), float("nan"), device=cuda)
-    assert np.array_equal(launch(cuda, q, cache, Hq, Hkv, d, S, ws, stage=1, splits=1), got)
+    assert np.array_equal(launch(cuda, q, cache, Hq, Hkv, d, S, ws, stage=1, splits=1, persistent=False), got)
     assert torch.isnan(ws).all()
 
 

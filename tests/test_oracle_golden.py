@@ -90,7 +90,8 @@ def test_contract_golden(oracle):
     assert int(g["workspace_floats"][0]) == 3 * 4 * 8 * 16 * 272
     # the engine's own sizing is the reference's record area plus its arrival counters
     # (one per request, KV head and 8-row tile)
-    assert tq.decode_workspace_floats(3, 4 * 16, 4, 256, 8) == int(g["workspace_floats"][0]) + 3 * 4 * 2
+    # and the two 64-bit words of its chunk schedule
+    assert tq.decode_workspace_floats(3, 4 * 16, 4, 256, 8) == int(g["workspace_floats"][0]) + 3 * 4 * 2 + 4
 
 
 # ------------------------------------------------- live against the reference models

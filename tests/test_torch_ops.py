@@ -14,7 +14,7 @@ def test_ops_are_registered_with_meta_kernels():
     for name in ("reshape_aligned", "reshape_scatter", "rotate_q_batch", "paged_decode", "decode_combine",
                  "decode_workspace_size"):
         assert hasattr(ns, name)
-    assert ns.decode_workspace_size(64, 32, 8, 128, 4) == 64 * 8 * 4 * 4 * (16 + 128) + 64 * 8
+    assert ns.decode_workspace_size(64, 32, 8, 128, 4) == 64 * 8 * 4 * 4 * (16 + 128) + 64 * 8 + 4
     with FakeTensorMode():
         H, d, S, P, T = 8, 128, 16, 4, 32
         k = torch.empty(T, H * d, dtype=torch.bfloat16, device="cuda")
