@@ -42,6 +42,9 @@
 namespace tq {
 
 constexpr int kDecWarps = 4;
+// kernel modes: export one record per (sequence, KV head, split); the same grid with one split,
+// every CTA finishing its head and writing the output; the persistent grid with the merge folded in
+constexpr int kModeRecords = 0, kModeDirect = 1, kModePersistent = 2;
 constexpr int kCensusWords = 10;   // 64-bit words per CTA of the worker census
 constexpr int kMaxSplits = TQ_MAX_SPLITS;   // record slots per head a workspace can be asked to hold
 constexpr float kLog2e = 1.4426950408889634f;
@@ -428,10 +431,14 @@ __device__ __forceinline__ unsigned long long tagged_fetch_add(unsigned long lon
 // head) segments of its share, and the CTA that completes a head's last outstanding segment
 // merges the partial records and writes the output itself (one arrival count per head, no
 // waiting anywhere). Without STREAMK one CTA serves one (sequence, KV head, split).
-template <int D, bool PRECISE, bool EXT, bool NZ, bool STREAMK>
+template <int D, bool PRECISE, bool EXT, bool NZ, int MODE>
 __global__ void __launch_bounds__(kDecWarps * 32, DecodeSmem<D>::kCtasPerSm)
 tq_decode_partial_kernel(const DecodeParams p)
 {
+    // What a CTA does with a head's state is a compile-time choice, so that the record-only
+    // kernel carries none of the finishing code (its presence alone cost 2.4 % there).
+    constexpr bool STREAMK = MODE == kModePersistent;
+    constexpr bool DIRECT = MODE == kModeDirect;
     static_assert(!NZ || D == 256, "the NZ-tiled cache has head size 256");
     static_assert(!(STREAMK && PRECISE), "the persistent grid serves the native path");
     using L = DecodeSmem<D>;
@@ -753,27 +760,31 @@ tq_decode_partial_kernel(const DecodeParams p)
 
         // classic grid, one split, an output to write: the CTA holds the head's whole state
         // and finishes it itself -- no record, no workspace, no second kernel
-        const bool direct = !STREAMK && p.output != nullptr;
+        constexpr bool direct = DIRECT;
         if constexpr (!STREAMK) {
             if (empty) {
-                if (direct) {
+                if constexpr (direct) {
                     float* zero = reinterpret_cast<float*>(ring + L::kMergeBytes + L::kRecBytes);
                     for (int i = tid; i < rows_here * D; i += blockDim.x) zero[i] = 0.f;
                     __syncthreads();
                     egress_rows<D>(p, zero, rows_here, seq, head, row_tile, tokens_per_req, tid);
                     return;
+                } else {
+                    for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
+                        const int c = i % kRecord;
+                        rec_base[i] = c < 8 ? kMaskedScore : 0.0f;
+                    }
+                    if (no_pages || p.q_rot == nullptr) return;
                 }
-                for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
-                    const int c = i % kRecord;
-                    rec_base[i] = c < 8 ? kMaskedScore : 0.0f;
-                }
-                if (no_pages || p.q_rot == nullptr) return;
             }
         }
 
         // ---- the copy machinery of this segment
         const int32_t* table_row = p.table + static_cast<size_t>(seq) * p.table_stride;
         // Block-table entries of the tile whose first strip is `strip` (-1 past the range).
+        // The loaded entries are not touched before the copy stage uses them one tile later:
+        // any arithmetic on them here would wait out the table read once per tile (measured:
+        // 4 % of the kernel).
         auto load_pages = [&](uint32_t strip, int32_t (&pg)[kTileStrips]) {
 #pragma unroll
             for (int ts = 0; ts < kTileStrips; ++ts)
@@ -795,9 +806,10 @@ tq_decode_partial_kernel(const DecodeParams p)
         auto issue = [&](uint32_t strip, uint32_t stage, const int32_t (&pg)[kTileStrips]) {
 #pragma unroll
             for (int ts = 0; ts < kTileStrips; ++ts) {
-                if (strip + ts >= s1) continue;   // warp-uniform: past the range
+                if (pg[ts] < 0 && strip + ts >= s1) continue;   // warp-uniform: past the range
+                // a negative entry under live tokens is as wrong as one past the pool
                 uint32_t page = static_cast<uint32_t>(pg[ts]);
-                if (pg[ts] < 0 || page >= p.P) {
+                if (page >= p.P) {
                     if (lane == 0) report(p.status, TQ_STATUS_BAD_PAGE);
                     page = 0;
                 }
@@ -876,7 +888,8 @@ tq_decode_partial_kernel(const DecodeParams p)
                                          : q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
             }
         }
-        const bool early = L::early_issue(warp) && !empty;
+        // (the record-only kernel keeps rotation first: ahead of it the copies measured 2 % slower there)
+        const bool early = MODE != kModeRecords && L::early_issue(warp) && !empty;
         if (early) {
             load_pages(strip_first, pg_next);
             issue(strip_first, 0, pg_next);
@@ -1447,16 +1460,13 @@ tq_decode_partial_kernel(const DecodeParams p)
             }
             return out;
         };
-        if constexpr (!STREAMK) {
-            if (!direct) {
-                for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
-                    const int q = i / kRecord, c = i % kRecord;
-                    rec_base[i] = merged(q, c < 8 ? 0 : c < 16 ? 1 : 2 + (c - 16));
-                }
-                return;
+        if constexpr (!STREAMK && !DIRECT) {
+            for (int i = tid; i < rows_here * kRecord; i += blockDim.x) {
+                const int q = i / kRecord, c = i % kRecord;
+                rec_base[i] = merged(q, c < 8 ? 0 : c < 16 ? 1 : 2 + (c - 16));
             }
-        }
-        {
+            return;
+        } else {
             constexpr int kRecPitch = L::kRecPitch;
             float* rec = reinterpret_cast<float*>(ring + L::kMergeBytes);            // [8][kRecPitch]
             float* ebuf = reinterpret_cast<float*>(ring + L::kMergeBytes + L::kRecBytes);   // [2][8][D]
@@ -1600,7 +1610,9 @@ struct CombineParams {
 // One CTA per (item, row): merge `splits` records, normalise, optionally rotate
 // back with the egress cascade (routines/routine_vector_egress_rotate.hpp:186-277)
 // and gate, narrow to bf16. D threads, one channel each.
-template <int D>
+// MAXK bounds the records per row (16 or kMaxSplits): the record loads are fully unrolled, and
+// the narrower instantiation keeps the common case at half the registers.
+template <int D, int MAXK>
 __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
 {
     constexpr int kRecord = 16 + D;
@@ -1616,10 +1628,10 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
     const float* base = p.workspace + (static_cast<size_t>(item) * p.splits * p.rows_stride + row) * kRecord;
     const size_t split_stride = static_cast<size_t>(p.rows_stride) * kRecord;
     // All records are fetched before the first one is merged, so the loads overlap instead
-    // of forming a chain of dependent round trips to L2 (at most kMaxSplits records).
-    float mk[kMaxSplits], lk[kMaxSplits], ak[kMaxSplits];
+    // of forming a chain of dependent round trips to L2 (at most MAXK records).
+    float mk[MAXK], lk[MAXK], ak[MAXK];
 #pragma unroll
-    for (int k = 0; k < kMaxSplits; ++k)
+    for (int k = 0; k < MAXK; ++k)
         if (static_cast<uint32_t>(k) < p.splits) {
             const float* rec = base + k * split_stride;
             mk[k] = rec[0];
@@ -1628,7 +1640,7 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
         }
     float m = kMaskedScore, l = 0.f, a = 0.f;
 #pragma unroll
-    for (int k = 0; k < kMaxSplits; ++k)
+    for (int k = 0; k < MAXK; ++k)
         if (static_cast<uint32_t>(k) < p.splits) {
             const float mn = fmaxf(m, mk[k]);
             const float wa = ex2f((m - mn) * kLog2e), wb = ex2f((mk[k] - mn) * kLog2e);
@@ -1705,9 +1717,10 @@ static uint32_t next_launch_tag()
 static std::atomic<unsigned long long*> g_census{nullptr};
 static std::atomic<uint32_t> g_census_ctas{0};
 
-template <int D, bool PRECISE, bool EXT, bool NZ, bool STREAMK>
+template <int D, bool PRECISE, bool EXT, bool NZ, int MODE>
 static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p_in)
 {
+    constexpr bool STREAMK = MODE == kModePersistent;
     DecodeParams p = p_in;
     // Opt in to the large dynamic shared-memory carve-out once per device. The
     // flags race benignly: setting the attribute twice is harmless.
@@ -1716,7 +1729,7 @@ static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p_
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorNoDevice;
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(tq_decode_partial_kernel<D, PRECISE, EXT, NZ, STREAMK>,
+        cudaError_t e = cudaFuncSetAttribute(tq_decode_partial_kernel<D, PRECISE, EXT, NZ, MODE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              DecodeSmem<D>::kTotal);
         if (e != cudaSuccess) return e;
@@ -1737,33 +1750,35 @@ static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p_
     }
     if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
     p.census = STREAMK && grid <= g_census_ctas.load() ? g_census.load() : nullptr;
-    tq_decode_partial_kernel<D, PRECISE, EXT, NZ, STREAMK><<<static_cast<unsigned>(grid), kDecWarps * 32,
+    tq_decode_partial_kernel<D, PRECISE, EXT, NZ, MODE><<<static_cast<unsigned>(grid), kDecWarps * 32,
                                   DecodeSmem<D>::kTotal, stream>>>(p);
     return cudaGetLastError();
 }
 
 // The classic grid: one CTA per (sequence, KV head, split, row tile), records only.
+template <int D, bool PRECISE, int MODE>
+static cudaError_t launch_partial_mode(cudaStream_t stream, const DecodeParams& p)
+{
+    if constexpr (D == 256) {
+        if (p.nz_slot_floats != 0u) return launch_partial_as<D, PRECISE, true, true, MODE>(stream, p);
+    }
+    if (p.q_f16 != 0u || p.tokens_per_req > 1u || p.q_f32 != nullptr || p.midrise != 0u)
+        return launch_partial_as<D, PRECISE, true, false, MODE>(stream, p);
+    return launch_partial_as<D, PRECISE, false, false, MODE>(stream, p);
+}
 template <int D, bool PRECISE>
 static cudaError_t launch_partial(cudaStream_t stream, const DecodeParams& p)
 {
-    if constexpr (D == 256) {
-        if (p.nz_slot_floats != 0u) return launch_partial_as<D, PRECISE, true, true, false>(stream, p);
-    }
-    if (p.q_f16 != 0u || p.tokens_per_req > 1u || p.q_f32 != nullptr || p.midrise != 0u)
-        return launch_partial_as<D, PRECISE, true, false, false>(stream, p);
-    return launch_partial_as<D, PRECISE, false, false, false>(stream, p);
+    // an output to write (and therefore one split): the CTAs finish their heads themselves
+    if (p.output != nullptr) return launch_partial_mode<D, PRECISE, kModeDirect>(stream, p);
+    return launch_partial_mode<D, PRECISE, kModeRecords>(stream, p);
 }
 
 // The persistent grid with the combine folded in (native precision only).
 template <int D>
 static cudaError_t launch_streamk(cudaStream_t stream, const DecodeParams& p)
 {
-    if constexpr (D == 256) {
-        if (p.nz_slot_floats != 0u) return launch_partial_as<D, false, true, true, true>(stream, p);
-    }
-    if (p.q_f16 != 0u || p.tokens_per_req > 1u || p.q_f32 != nullptr || p.midrise != 0u)
-        return launch_partial_as<D, false, true, false, true>(stream, p);
-    return launch_partial_as<D, false, false, false, true>(stream, p);
+    return launch_partial_mode<D, false, kModePersistent>(stream, p);
 }
 
 }  // namespace tq
@@ -1916,10 +1931,13 @@ static int splitk_combine(void* stream, const float* workspace, const float* pi_
     const uint64_t grid = static_cast<uint64_t>(items) * rows;
     if (grid > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (head_size == 128)
-        tq_combine_kernel<128><<<static_cast<unsigned>(grid), 128, 0, s>>>(p);
-    else
-        tq_combine_kernel<256><<<static_cast<unsigned>(grid), 256, 0, s>>>(p);
+    if (head_size == 128) {
+        if (splits <= 16u) tq_combine_kernel<128, 16><<<static_cast<unsigned>(grid), 128, 0, s>>>(p);
+        else tq_combine_kernel<128, kMaxSplits><<<static_cast<unsigned>(grid), 128, 0, s>>>(p);
+    } else {
+        if (splits <= 16u) tq_combine_kernel<256, 16><<<static_cast<unsigned>(grid), 256, 0, s>>>(p);
+        else tq_combine_kernel<256, kMaxSplits><<<static_cast<unsigned>(grid), 256, 0, s>>>(p);
+    }
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 
