@@ -28,6 +28,7 @@
 //     rounding is one fused multiply-add onto 1.5 * 2^23 (no float-to-int
 //     conversion), codes pack by integer multiply-add; the page is staged in shared
 //     memory and leaves as 128-bit stores of the whole contiguous (page, head) block.
+#include <atomic>
 #include <type_traits>
 
 #include "tq_ingest.cuh"
@@ -471,6 +472,14 @@ static cudaError_t launch_ingest(cudaStream_t stream, const IngestParams& p)
 
 }  // namespace tq
 
+// Clock cycles the tcgen05 writer lets one of its waits take; every launch reads it.
+static std::atomic<long long> g_wait_budget{tq::kIngestWaitBudget};
+
+extern "C" void tq_ingest_set_wait_budget(long long cycles)
+{
+    g_wait_budget.store(cycles < 0 ? tq::kIngestWaitBudget : cycles, std::memory_order_relaxed);
+}
+
 // Head size 128 goes to the tcgen05 writer unless `warp_mma_only`; head size 256 and the
 // explicit warp-MMA entry use the kernel in this file.
 static int reshape_and_cache(void* stream, const void* key, const void* value,
@@ -515,15 +524,11 @@ static int reshape_and_cache(void* stream, const void* key, const void* value,
     p.S = block_size;
     p.P = num_blocks;
     p.chunks = static_cast<uint32_t>(chunks);
-    {
-        const uint32_t d = 2u * num_kv_heads;   // >= 2
-        uint32_t l = 0;
-        while ((1ull << l) < d) ++l;
-        p.div_mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d)) / d + 1ull);
-        p.div_shift = l - 1u;
-    }
+    fast_div_constants(2u * num_kv_heads, &p.div_mul, &p.div_shift);
+    fast_div_constants(block_size, &p.page_mul, &p.page_shift);   // block_size >= 16
     p.inv_sqrt_len = inv_sqrt_len;
     p.status = status;
+    p.wait_budget = g_wait_budget.load(std::memory_order_relaxed);
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t err = cudaErrorNotSupported;
@@ -605,13 +610,8 @@ extern "C" int tq_reshape_and_cache_varlen(void* stream, const uint16_t* key, co
     p.S = block_size;
     p.P = num_blocks;
     p.chunks = static_cast<uint32_t>(chunks);
-    {
-        const uint32_t d2 = 2u * num_kv_heads;
-        uint32_t l = 0;
-        while ((1ull << l) < d2) ++l;
-        p.div_mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d2)) / d2 + 1ull);
-        p.div_shift = l - 1u;
-    }
+    fast_div_constants(2u * num_kv_heads, &p.div_mul, &p.div_shift);
+    fast_div_constants(block_size, &p.page_mul, &p.page_shift);
     p.inv_sqrt_len = inv_sqrt_len;
     p.status = status;
     p.cu_seqlens = cu_seqlens;

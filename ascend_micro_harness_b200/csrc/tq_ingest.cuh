@@ -5,6 +5,8 @@
 
 namespace tq {
 
+constexpr long long kIngestWaitBudget = 2000000000LL;   // clock cycles, about a second
+
 struct IngestParams {
     const void* key;
     const void* value;
@@ -17,6 +19,7 @@ struct IngestParams {
     uint32_t num_strips, H, S, P;
     uint32_t chunks;                 // num_strips * 2 * H, below 2^31
     uint32_t div_mul, div_shift;     // exact division by 2H: see fast_div
+    uint32_t page_mul, page_shift;   // exact division by S (the tcgen05 writer's slot -> page)
     float inv_sqrt_len;
     uint32_t* status;
     // ragged requests (the varlen entry only): request b owns tokens cu_seqlens[b] ..
@@ -24,6 +27,9 @@ struct IngestParams {
     const int32_t* cu_seqlens = nullptr;
     const int32_t* strip_begin = nullptr;
     uint32_t num_requests = 0;
+    // tcgen05 writer: clock cycles one wait on a tile fetch or on a product may take before the
+    // kernel reports TQ_STATUS_WAIT_EXPIRED and stops storing; zero gives up without looking
+    long long wait_budget = kIngestWaitBudget;
 };
 
 // n / d for any 32-bit n with the precomputed (mul, shift) of divisor d >= 2
@@ -32,6 +38,15 @@ __device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t 
 {
     const uint32_t t = __umulhi(mul, n);
     return (t + ((n - t) >> 1)) >> shift;
+}
+
+// The (mul, shift) pair of fast_div for divisor d >= 2.
+inline void fast_div_constants(uint32_t d, uint32_t* mul, uint32_t* shift)
+{
+    uint32_t l = 0;
+    while ((1ull << l) < d) ++l;
+    *mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d)) / d + 1ull);
+    *shift = l - 1u;
 }
 
 // The tcgen05 writer for head size 128 (tq_ingest_umma.cu). `bf16` selects the element type.

@@ -44,13 +44,13 @@ constexpr int kGroupThreads = 128;
 constexpr int kThreads = kGroups * kGroupThreads;
 constexpr uint32_t kGroupCols = 128;         // one 128 x 128 FP32/INT32 accumulator per group
 constexpr uint32_t kTmemCols = kGroups * kGroupCols;
-constexpr long long kWaitBudget = 2000000000LL;   // clock cycles, about a second
+constexpr long long kWaitBudget = kIngestWaitBudget;   // clock cycles, about a second
+constexpr int kSpinPolls = 512;
 constexpr uint32_t kSuspendHintNs = 20000u;       // one poll may sleep this long before it returns
 
 constexpr float kBias = 12582912.0f;         // 1.5 * 2^23
 constexpr uint32_t kBiasBits = 0x4B400000u;
 constexpr float kMagic = 12582920.0f;        // 1.5 * 2^23 + 8
-constexpr float kMagicTop = 12582927.0f;     // 1.5 * 2^23 + 15
 
 template <bool BF16>
 struct Cfg {
@@ -70,7 +70,11 @@ struct Cfg {
     // SM: 2 x 256 tensor-memory columns is all an SM has, so the request is padded to
     // 80 KiB and a third CTA can never land on an SM and stall in its allocation.
     static constexpr int kCtasPerSm = 2;
-    static constexpr int kGroupBytes = kTileBytes + 2 * kTileTokens * 4 + 8 * 8 + 64;
+    // int8 tiles are half the size: a group keeps the key tile and the value tile of an item in
+    // buffers of their own and fetches each a whole item ahead; bf16 has room for one buffer
+    static constexpr int kTileBufs = BF16 ? 1 : 2;
+    static constexpr int kSmallBytes = 2 * kTileTokens * 4 + 8 * 8 + 64;
+    static constexpr int kGroupBytes = kTileBufs * kTileBytes + kSmallBytes;
     static constexpr int kUsed = kTileBytes + kGroups * kGroupBytes + 64;
     static constexpr int kSmem = (kUsed + 1024) > 80 * 1024 ? (kUsed + 1024) : 80 * 1024;
 };
@@ -123,12 +127,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity)
     return ok != 0;
 }
 
+// The same test without the permission to sleep.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t mbar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
 #define TQ_W8(v, o) "=r"(v[o]), "=r"(v[o + 1]), "=r"(v[o + 2]), "=r"(v[o + 3]), "=r"(v[o + 4]), \
                     "=r"(v[o + 5]), "=r"(v[o + 6]), "=r"(v[o + 7])
 #define TQ_RW8(v, o) "+r"(v[o]), "+r"(v[o + 1]), "+r"(v[o + 2]), "+r"(v[o + 3]), "+r"(v[o + 4]), \
                      "+r"(v[o + 5]), "+r"(v[o + 6]), "+r"(v[o + 7])
 
-// 32 lanes x 32 (16) columns: lane i of the warp receives columns col .. of its row. The
+// 32 lanes x 32 columns: lane i of the warp receives columns col .. of its row. The
 // load is asynchronous; tmem_arrived() is the wait, and it names the registers as in-out
 // operands so that no use of them can be scheduled ahead of it.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
@@ -146,17 +162,17 @@ __device__ __forceinline__ void tmem_arrived(uint32_t (&v)[32])
                  : TQ_RW8(v, 0), TQ_RW8(v, 8), TQ_RW8(v, 16), TQ_RW8(v, 24)
                  :: "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
+// 32 lanes x 64 columns, the low 16 bits of each: register j holds columns 2j (low half) and
+// 2j + 1 (high half). An INT32 accumulator on top of 1.5 * 2^23 keeps the sum itself, as a
+// signed 16-bit number, in its low half (|sum| <= 128 * 128).
+__device__ __forceinline__ void tmem_ld32_low16(uint32_t taddr, uint32_t (&v)[32])
 {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-        : TQ_W8(v, 0), TQ_W8(v, 8)
+        "tcgen05.ld.sync.aligned.32x32b.x32.pack::16b.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : TQ_W8(v, 0), TQ_W8(v, 8), TQ_W8(v, 16), TQ_W8(v, 24)
         : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_arrived(uint32_t (&v)[16])
-{
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" : TQ_RW8(v, 0), TQ_RW8(v, 8) :: "memory");
 }
 #undef TQ_W8
 #undef TQ_RW8
@@ -189,20 +205,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes)
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbar), "r"(bytes) : "memory");
 }
 
-// max(a, |b|, |c|) and the plain three-input forms.
+// Three-input maximum.
 __device__ __forceinline__ float max3f(float a, float b, float c)
 {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
 }
-__device__ __forceinline__ float min3f(float a, float b, float c)
-{
-    float r;
-    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-    return r;
-}
-
 // Work is dealt out as (128-token tile, head) items; a group does the key plane and then
 // the value plane of its item, so every group carries the same mix of the cheaper key
 // tiles and the dearer value tiles whatever the grid size. Unit u of a group is plane
@@ -220,15 +229,20 @@ __device__ __forceinline__ TileId tile_of(const IngestParams& p, uint32_t item, 
 }
 
 // Eight packed codes from eight rounded values r_e = 1.5 * 2^23 + u_e (u_e = code + 8 in
-// 0..15 after the clamp), lowest nibble first: Horner in base 16 on the raw bit patterns,
-// minus what the eight copies of the 0x4B400000 offset add up to, then u -> two's complement.
+// 0..16: a value that rounds up to code 8 has yet to be clamped to 7), lowest nibble first.
+// The low byte of r_e is u_e. The even and the odd elements are gathered into four bytes
+// each; min(u, 15) = (15 u + 15) >> 4 for u <= 16 and no byte of 15 u + 15 exceeds 255, so
+// one multiply-add clamps four elements at once and leaves them in the high nibbles; the two
+// words interleave into eight nibbles and u -> two's complement flips each nibble's top bit.
 __device__ __forceinline__ uint32_t pack8(const float (&r)[8])
 {
-    constexpr uint32_t kHorner = kBiasBits * 0x11111111u;
-    uint32_t w = 0;
-#pragma unroll
-    for (int e = 7; e >= 0; --e) w = w * 16u + __float_as_uint(fminf(r[e], kMagicTop));
-    return (w - kHorner) ^ 0x88888888u;
+    const uint32_t e02 = __byte_perm(__float_as_uint(r[0]), __float_as_uint(r[2]), 0x0040);
+    const uint32_t e46 = __byte_perm(__float_as_uint(r[4]), __float_as_uint(r[6]), 0x0040);
+    const uint32_t o13 = __byte_perm(__float_as_uint(r[1]), __float_as_uint(r[3]), 0x0040);
+    const uint32_t o57 = __byte_perm(__float_as_uint(r[5]), __float_as_uint(r[7]), 0x0040);
+    const uint32_t even = __byte_perm(e02, e46, 0x5410), odd = __byte_perm(o13, o57, 0x5410);
+    const uint32_t ye = even * 15u + 0x0F0F0F0Fu, yo = odd * 15u + 0x0F0F0F0Fu;
+    return (((ye >> 4) & 0x0F0F0F0Fu) | (yo & 0xF0F0F0F0u)) ^ 0x88888888u;
 }
 
 // All 128 threads of one group (named barrier 1 + group).
@@ -249,16 +263,15 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
     const int group = threadIdx.x / kGroupThreads, tid = threadIdx.x % kGroupThreads;
     const int warp = tid >> 5, lane = tid & 31;   // warp within the group = its tensor-memory lane quarter
     uint8_t* m_tile = base;
-    uint8_t* x_tile = base + C::kTileBytes + group * C::kTileBytes;
-    uint8_t* small = base + (1 + kGroups) * C::kTileBytes + group * (2 * kTileTokens * 4 + 8 * 8 + 64);
-    float* inv_s = reinterpret_cast<float*>(small);                           // per token: 2^(2-e)
-    float* add_s = inv_s + kTileTokens;                                       // per token: rounding addend
-    unsigned long long* strip_off = reinterpret_cast<unsigned long long*>(add_s + kTileTokens);  // [8]
-    uint64_t* mbar = reinterpret_cast<uint64_t*>(strip_off + 8);   // [0]: products done, [1]: tile landed
-    uint32_t* shared_words = reinterpret_cast<uint32_t*>(base + (1 + kGroups) * C::kTileBytes +
-                                                         kGroups * (2 * kTileTokens * 4 + 8 * 8 + 64));
+    uint8_t* x_tile = base + C::kTileBytes + group * (C::kTileBufs * C::kTileBytes);
+    uint8_t* small = base + (1 + kGroups * C::kTileBufs) * C::kTileBytes + group * C::kSmallBytes;
+    float* inv_s = reinterpret_cast<float*>(small);   // per token: 2^(2-e)
+    unsigned long long* strip_off = reinterpret_cast<unsigned long long*>(small + 2 * kTileTokens * 4);  // [8]
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(strip_off + 8);   // [0]: products done, [1 + b]: tile buffer b landed
+    uint32_t* shared_words = reinterpret_cast<uint32_t*>(base + (1 + kGroups * C::kTileBufs) * C::kTileBytes +
+                                                         kGroups * C::kSmallBytes);
     uint32_t* tmem_slot = shared_words;
-    uint32_t* abort_flag = shared_words + 1;
+    volatile uint32_t* abort_flag = shared_words + 1;
 
     const uint32_t items = ((p.num_strips + 7u) / 8u) * p.H;
     const uint32_t num_tokens = p.num_strips * kStrip;
@@ -268,6 +281,7 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(mbar)));
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(mbar + 1)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(mbar + 2)));
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         if (group == 0) *abort_flag = 0u;
     }
@@ -318,56 +332,80 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
 
     // The group's thread 0 fetches a tile: one box per 128-byte K block, rows = the tile's 128
     // tokens (past the end of the tensor: zeros, never stored), x = the head's first channel.
+    // Thread 0 of the group keeps the books of what it has in flight towards this CTA's shared
+    // and tensor memory: a tile fetch whose barrier phase nobody has seen complete, a chain of
+    // products whose commit nobody has seen arrive. Nothing new is issued once a wait has run out.
+    // Tile buffer of a plane: with two buffers the key tile lives in 0 and the value tile in 1.
+    // Bit b of tma_parity / tma_pending is the state of buffer b's barrier.
+    uint32_t parity = 0, tma_parity = 0, tma_pending = 0, mma_pending_parity = 0;
+    bool healthy = true, mma_pending = false;
+    auto buffer_of = [](uint32_t plane) { return C::kTileBufs == 2 ? plane : 0u; };
     auto load_tile = [&](uint32_t item, uint32_t plane) {
-        if (tid != 0) return;
+        if (tid != 0 || !healthy) return;
         const TileId id = tile_of(p, item, plane);
         const CUtensorMap* map = plane == 0 ? &key_map : &value_map;
-        mbar_expect_tx(tma_bar_s, C::kTileBytes);
+        const uint32_t buf = buffer_of(plane), bar = tma_bar_s + 8u * buf, dst = x_tile_s + buf * C::kTileBytes;
+        mbar_expect_tx(bar, C::kTileBytes);
 #pragma unroll
         for (int blk = 0; blk < C::kBlocks; ++blk)
-            tma_load_2d(x_tile_s + blk * C::kBlockBytes, map,
+            tma_load_2d(dst + blk * C::kBlockBytes, map,
                         static_cast<int>(id.head * 128u + blk * (128 / C::kElem)),
-                        static_cast<int>(id.tok_tile * kTileTokens), tma_bar_s);
+                        static_cast<int>(id.tok_tile * kTileTokens), bar);
+        tma_pending |= 1u << buf;
     };
 
-    // One product into the accumulator columns, then the bounded wait for it.
-    // transposed = false: D[token][channel] = X M^T; true: D'[channel][token] = M X^T.
-    uint32_t parity = 0, tma_parity = 0;
-    bool healthy = true;
-    auto bounded_wait = [&](uint32_t bar, uint32_t par) {
-        bool done = mbar_try_wait(bar, par);
+    // A wait on a barrier phase for at most `budget` clock cycles; a budget of zero gives up
+    // without looking, and a raised abort flag ends the wait early (the awaited work may then
+    // never have been issued).
+    auto bounded_wait = [&](uint32_t bar, uint32_t par, long long budget, bool watch_abort) {
+        if (budget <= 0) return false;
+        // a product or a tile fetch takes a microsecond or so: poll for that long before a
+        // wait that may put the thread to sleep (and wake it late)
+        bool done = false;
+#pragma unroll 1
+        for (int polls = 0; polls < kSpinPolls && !done; ++polls) done = mbar_test_wait(bar, par);
         if (!done) {
             const long long t0 = clock64();
             do {
                 done = mbar_try_wait(bar, par);
-            } while (!done && clock64() - t0 < kWaitBudget);
+            } while (!done && clock64() - t0 < budget &&
+                     !(watch_abort && *abort_flag != 0u));
         }
         return done;
     };
-    auto product = [&](bool transposed, bool fresh_tile) {
-        if constexpr (!BF16) {
-            // INT32 accumulators start at the bit pattern of 1.5 * 2^23
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_fill32(acc + c * 32, kBiasBits);
-            tmem_wait_st();
-        }
+    // One product into the accumulator columns, then the bounded wait for it.
+    // transposed = false: D[token][channel] = X M^T; true: D'[channel][token] = M X^T.
+    auto product = [&](bool transposed, bool fresh_tile, uint32_t buf) {
+        if constexpr (!BF16) tmem_wait_st();   // the refill of the columns (see refill) is in place
         fence_before_sync();
         group_sync(group);
-        if (tid == 0) {
+        if (tid == 0 && healthy) {
+            bool landed = true;
             if (fresh_tile) {   // the TMA boxes of this tile have landed (same proxy as the MMA reads)
-                if (!bounded_wait(tma_bar_s, tma_parity)) *abort_flag = 1u;
-                tma_parity ^= 1u;
+                landed = bounded_wait(tma_bar_s + 8u * buf, (tma_parity >> buf) & 1u, p.wait_budget, false);
+                if (landed) {
+                    tma_pending &= ~(1u << buf);
+                    tma_parity ^= 1u << buf;
+                }
             }
-            fence_after_sync();
+            if (landed) {
+                fence_after_sync();
 #pragma unroll
-            for (int k = 0; k < C::kKSteps; ++k) {
-                const uint32_t off = (k >> 2) * C::kBlockBytes + (k & 3) * 32;
-                const uint64_t dx = umma_desc(x_tile_s + off), dm = umma_desc(m_tile_s + off);
-                umma<BF16>(tmem_group, transposed ? dm : dx, transposed ? dx : dm, (!BF16 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < C::kKSteps; ++k) {
+                    const uint32_t off = (k >> 2) * C::kBlockBytes + (k & 3) * 32;
+                    const uint64_t dx = umma_desc(x_tile_s + buf * C::kTileBytes + off), dm = umma_desc(m_tile_s + off);
+                    umma<BF16>(tmem_group, transposed ? dm : dx, transposed ? dx : dm, (!BF16 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(mbar_s);
+                mma_pending = true;
+                mma_pending_parity = parity;
+            } else {
+                healthy = false;
+                *abort_flag = 1u;
             }
-            umma_commit(mbar_s);
         }
-        const bool done = bounded_wait(mbar_s, parity);
+        const bool done = healthy && bounded_wait(mbar_s, parity, p.wait_budget, true);
+        if (done && tid == 0) mma_pending = false;
         if (!done || *abort_flag != 0u) {
             healthy = false;
             *abort_flag = 1u;
@@ -377,9 +415,23 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         fence_after_sync();
     };
 
+    // INT32 accumulators start at the bit pattern of 1.5 * 2^23. The columns are set once here
+    // and again by whoever reads a product for the last time, chunk by chunk right after the
+    // chunk is in registers, so that the stores run under the arithmetic; product() only waits
+    // for them.
+    auto refill = [&](uint32_t col) {
+        if constexpr (!BF16) tmem_fill32(acc + col, kBiasBits);
+    };
+#pragma unroll
+    for (int c = 0; c < 4; ++c) refill(c * 32);
+
     const uint32_t item_step = gridDim.x * kGroups;
     uint32_t item = blockIdx.x * kGroups + group;
-    if (item < items) load_tile(item, 0);
+    if (item < items) {
+        load_tile(item, 0);
+        if (C::kTileBufs == 2) load_tile(item, 1);
+    }
+    int32_t slot = -1;
 
 #pragma unroll 1
     for (uint32_t unit = 0; item < items; ++unit, item += (unit & 1u) ? 0u : item_step) {
@@ -387,20 +439,31 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         // ---- this thread's token of the tile: its slot is requested before anything waits
         const uint32_t tok = id.tok_tile * kTileTokens + tid;
         const bool tok_live = tok < num_tokens;
-        const int32_t slot = tok_live ? __ldg(p.slots + tok) : -1;
+        if (id.plane == 0) {   // a volatile load: it must not sink below the product's wait
+            slot = -1;
+            if (tok_live) asm volatile("ld.global.nc.s32 %0, [%1];\n" : "=r"(slot) : "l"(p.slots + tok));
+        }
 
-        product(false, true);
-        if (id.plane == 0) load_tile(item, 1);                    // the tile is consumed: refill
+        product(false, true, buffer_of(id.plane));
+        // the tile is consumed: with one buffer the item's value tile takes its place, with two
+        // the next item's key tile does (the value tile stays for the transposed product)
+        if (id.plane == 0) {
+            if (C::kTileBufs == 1) load_tile(item, 1);
+            else if (item + item_step < items) load_tile(item + item_step, 0);
+        }
 
         const int32_t slot0 = __shfl_sync(0xffffffffu, slot, lane & 16);
         const bool run_ok = slot == slot0 + (lane & 15);
         const uint32_t votes = __ballot_sync(0xffffffffu, run_ok);
         const bool strip_live = __shfl_sync(0xffffffffu, tok_live ? 1 : 0, lane & 16) != 0;
+        // page = slot0 / S by the precomputed multiplier: a hardware-free division costs this
+        // thread hundreds of cycles per tile
+        const uint32_t slot_page = fast_div(static_cast<uint32_t>(slot0), p.page_mul, p.page_shift);
         const bool strip_ok = strip_live && ((votes >> (lane & 16)) & 0xFFFFu) == 0xFFFFu && slot0 >= 0 &&
-                              (slot0 % kStrip) == 0 && static_cast<uint32_t>(slot0) / p.S < p.P;
+                              (slot0 % kStrip) == 0 && slot_page < p.P;
         if (strip_live && !strip_ok && (lane & 15) == 0) report(p.status, TQ_STATUS_BAD_SLOT);
-        const uint32_t page = strip_ok ? static_cast<uint32_t>(slot0) / p.S : 0u;
-        const uint32_t tok_in_page = strip_ok ? static_cast<uint32_t>(slot0) % p.S : 0u;
+        const uint32_t page = strip_ok ? slot_page : 0u;
+        const uint32_t tok_in_page = strip_ok ? static_cast<uint32_t>(slot0) - slot_page * p.S : 0u;
         // byte offset of the strip's (page, head) block in either code plane
         const size_t block_off = (static_cast<size_t>(page) * p.H + id.head) * (static_cast<size_t>(p.S) * 64u) +
                                  static_cast<size_t>(tok_in_page / kStrip) * 1024u;
@@ -409,22 +472,13 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         // Tensor-memory reads run one 32-column chunk ahead of the arithmetic.
         uint32_t va[32], vb[32];
         float amax;
-        {
-            float hi0 = BF16 ? 0.0f : kBias, hi1 = hi0, lo0 = kBias, lo1 = kBias;
+        if constexpr (BF16) {
+            float hi0 = 0.0f, hi1 = 0.0f;
             auto fold = [&](const uint32_t (&v)[32]) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
-                    const float a = __uint_as_float(v[j]), b = __uint_as_float(v[j + 1]);
-                    const float c = __uint_as_float(v[j + 2]), d = __uint_as_float(v[j + 3]);
-                    if constexpr (BF16) {
-                        hi0 = max3f(hi0, fabsf(a), fabsf(b));
-                        hi1 = max3f(hi1, fabsf(c), fabsf(d));
-                    } else {
-                        hi0 = max3f(hi0, a, b);
-                        hi1 = max3f(hi1, c, d);
-                        lo0 = min3f(lo0, a, b);
-                        lo1 = min3f(lo1, c, d);
-                    }
+                    hi0 = max3f(hi0, fabsf(__uint_as_float(v[j])), fabsf(__uint_as_float(v[j + 1])));
+                    hi1 = max3f(hi1, fabsf(__uint_as_float(v[j + 2])), fabsf(__uint_as_float(v[j + 3])));
                 }
             };
             tmem_ld32(acc + 0, va);
@@ -440,10 +494,34 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
             tmem_arrived(vb);
             if (id.plane == 0) tmem_ld32(acc + 0, va);   // first chunk of pass 2
             fold(vb);
-            const float hi = fmaxf(hi0, hi1), lo = fminf(lo0, lo1);
-            amax = BF16 ? hi : fmaxf(hi - kBias, kBias - lo);
-            amax = fmaxf(amax, 1.0f);   // the writer floors absmax at 1
+            amax = fmaxf(hi0, hi1);
+        } else {
+            // the sums as signed 16-bit pairs, 64 columns per read: two-lane maximum and minimum
+            uint32_t hi0 = 0x80008000u, hi1 = hi0, lo0 = 0x7FFF7FFFu, lo1 = lo0;
+            auto fold = [&](const uint32_t (&v)[32]) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    hi0 = __vimax3_s16x2(hi0, v[j], v[j + 1]);
+                    hi1 = __vimax3_s16x2(hi1, v[j + 2], v[j + 3]);
+                    lo0 = __vimin3_s16x2(lo0, v[j], v[j + 1]);
+                    lo1 = __vimin3_s16x2(lo1, v[j + 2], v[j + 3]);
+                }
+            };
+            tmem_ld32_low16(acc + 0, va);
+            tmem_arrived(va);
+            tmem_ld32_low16(acc + 64, vb);
+            fold(va);
+            tmem_arrived(vb);
+            if (id.plane == 0) tmem_ld32(acc + 0, va);   // first chunk of pass 2
+            fold(vb);
+            const uint32_t hi = __vmaxs2(hi0, hi1), lo = __vmins2(lo0, lo1);
+            const int top = max(static_cast<int>(static_cast<int16_t>(hi & 0xFFFFu)),
+                                static_cast<int>(static_cast<int16_t>(hi >> 16)));
+            const int bottom = min(static_cast<int>(static_cast<int16_t>(lo & 0xFFFFu)),
+                                   static_cast<int>(static_cast<int16_t>(lo >> 16)));
+            amax = static_cast<float>(max(top, -bottom));
         }
+        amax = fmaxf(amax, 1.0f);   // the writer floors absmax at 1
         const int pow_bits = (__float_as_int(amax) & 0x7F800000) - (2 << 23);
         const float inv = __int_as_float((254 << 23) - pow_bits);
         // rounding addend: r = y * inv + (1.5 * 2^23 + 8); an int8 accumulator carries the
@@ -477,76 +555,96 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
             };
             tmem_arrived(va);
             tmem_ld32(acc + 32, vb);
+            refill(0);
             emit(va, 0);
             tmem_arrived(vb);
             tmem_ld32(acc + 64, va);
+            refill(32);
             emit(vb, 1);
             tmem_arrived(va);
             tmem_ld32(acc + 96, vb);
+            refill(64);
             emit(va, 2);
             tmem_arrived(vb);
+            refill(96);
             emit(vb, 3);
         } else {
             // ---- value page: publish the per-token constants, swap the operands, then
             // work per channel
+#pragma unroll
+            for (int c = 0; c < 4; ++c) refill(c * 32);   // pass 1 was the only pass over this product
             inv_s[tid] = inv;
-            add_s[tid] = addend;
             if ((lane & 15) == 0)
                 strip_off[tid >> 4] = strip_ok ? static_cast<unsigned long long>(block_off) : ~0ull;
-            product(true, false);   // its barrier also publishes the constants and ends pass 1's reads
-            if (item + item_step < items) load_tile(item + item_step, 0);
+            product(true, false, buffer_of(1));   // its barrier also publishes the constants and ends pass 1's reads
+            if (item + item_step < items) load_tile(item + item_step, C::kTileBufs == 1 ? 0 : 1);
             const bool store = healthy;
-            uint32_t ua[16], ub[16];
-            auto emit = [&](const uint32_t (&v)[16], int s) {
-                uint32_t w[2];
+            // 32 tokens = two strips per tensor-memory read, as many independent chains in
+            // flight as in the key plane; a strip's constants (16 scales, its offset) are read
+            // where they are used and the compiler moves the reads up as far as registers allow
+            auto emit = [&](const uint32_t (&v)[32], int s0) {
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const float4 i0 = *reinterpret_cast<const float4*>(inv_s + s * 16 + h * 8);
-                    const float4 i1 = *reinterpret_cast<const float4*>(inv_s + s * 16 + h * 8 + 4);
-                    const float iv[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
-                    float ad[8];
-                    if constexpr (BF16) {
+                for (int half = 0; half < 2; ++half) {
+                    const int s = s0 + half;
+                    const unsigned long long off = strip_off[s];
+                    uint32_t w[2];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) ad[e] = kMagic;
-                    } else {
-                        const float4 a0 = *reinterpret_cast<const float4*>(add_s + s * 16 + h * 8);
-                        const float4 a1 = *reinterpret_cast<const float4*>(add_s + s * 16 + h * 8 + 4);
-                        ad[0] = a0.x; ad[1] = a0.y; ad[2] = a0.z; ad[3] = a0.w;
-                        ad[4] = a1.x; ad[5] = a1.y; ad[6] = a1.z; ad[7] = a1.w;
+                    for (int h = 0; h < 2; ++h) {
+                        const float4 i0 = *reinterpret_cast<const float4*>(inv_s + s * 16 + h * 8);
+                        const float4 i1 = *reinterpret_cast<const float4*>(inv_s + s * 16 + h * 8 + 4);
+                        const float iv[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+                        float r[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e += 2) {
+                            // an int8 accumulator carries 1.5 * 2^23 on top of the sum: taken off first
+                            // (exact), so that the one rounding happens in the multiply-add as in the
+                            // key plane
+                            float2 y = make_float2(__uint_as_float(v[half * 16 + h * 8 + e]),
+                                                   __uint_as_float(v[half * 16 + h * 8 + e + 1]));
+                            if constexpr (!BF16) y = __fadd2_rn(y, make_float2(-kBias, -kBias));
+                            const float2 rr = __ffma2_rn(y, make_float2(iv[e], iv[e + 1]), make_float2(kMagic, kMagic));
+                            r[e] = rr.x;
+                            r[e + 1] = rr.y;
+                        }
+                        w[h] = pack8(r);
                     }
-                    float r[8];
-#pragma unroll
-                    for (int e = 0; e < 8; e += 2) {
-                        const float2 rr = __ffma2_rn(make_float2(__uint_as_float(v[h * 8 + e]),
-                                                                 __uint_as_float(v[h * 8 + e + 1])),
-                                                     make_float2(iv[e], iv[e + 1]),
-                                                     make_float2(ad[e], ad[e + 1]));
-                        r[e] = rr.x;
-                        r[e + 1] = rr.y;
-                    }
-                    w[h] = pack8(r);
+                    if (store && off != ~0ull)
+                        __stcs(reinterpret_cast<uint2*>(p.value_cache + off + static_cast<size_t>(tid) * 8u),
+                               make_uint2(w[0], w[1]));
                 }
-                const unsigned long long off = strip_off[s];
-                if (store && off != ~0ull)
-                    __stcs(reinterpret_cast<uint2*>(p.value_cache + off + static_cast<size_t>(tid) * 8u),
-                           make_uint2(w[0], w[1]));
             };
-            tmem_ld16(acc + 0, ua);
-#pragma unroll
-            for (int s = 0; s < 8; s += 2) {
-                tmem_arrived(ua);
-                tmem_ld16(acc + (s + 1) * 16, ub);
-                emit(ua, s);
-                tmem_arrived(ub);
-                if (s + 2 < 8) tmem_ld16(acc + (s + 2) * 16, ua);
-                emit(ub, s + 1);
-            }
+            tmem_ld32(acc + 0, va);
+            tmem_arrived(va);
+            tmem_ld32(acc + 32, vb);
+            refill(0);
+            emit(va, 0);
+            tmem_arrived(vb);
+            tmem_ld32(acc + 64, va);
+            refill(32);
+            emit(vb, 2);
+            tmem_arrived(va);
+            tmem_ld32(acc + 96, vb);
+            refill(64);
+            emit(va, 4);
+            tmem_arrived(vb);
+            refill(96);
+            emit(vb, 6);
         }
         // every read of tensor memory and of the per-token constants is done before the
         // group's next products overwrite them
         fence_before_sync();
         group_sync(group);
         if (*abort_flag != 0u) break;
+    }
+    // After a wait ran out (here or in the other group) a tile fetch or a product chain may
+    // still be on its way into this CTA's shared and tensor memory: thread 0 gives each the
+    // full budget to finish before the memory goes back to the SM.
+    if (tid == 0) {
+#pragma unroll
+        for (uint32_t buf = 0; buf < C::kTileBufs; ++buf)
+            if ((tma_pending >> buf) & 1u)
+                bounded_wait(tma_bar_s + 8u * buf, (tma_parity >> buf) & 1u, kWaitBudget, false);
+        if (mma_pending) bounded_wait(mbar_s, mma_pending_parity, kWaitBudget, false);
     }
     fence_before_sync();
     __syncthreads();

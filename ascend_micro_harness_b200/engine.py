@@ -132,6 +132,13 @@ def reshape_and_cache(key, value, key_cache, value_cache, scale_cache, slot_mapp
             "tq_reshape_and_cache")
 
 
+def set_ingest_wait_budget(cycles):
+    """Clock cycles one wait inside the tcgen05 writer may take before the launch reports
+    STATUS_WAIT_EXPIRED and stops storing. 0: every wait gives up at once; negative: the default
+    (about a second). Process-wide."""
+    load_library().tq_ingest_set_wait_budget(int(cycles))
+
+
 def reshape_and_cache_varlen(key, value, key_cache, value_cache, scale_cache, slot_mapping, signs,
                              cu_seqlens, *, num_kv_heads, head_size, block_size, num_blocks,
                              inv_sqrt_len, status=None, stream=None):

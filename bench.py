@@ -773,16 +773,22 @@ def side_measurements(torch, tq, dev, args):
     counts 1/2/4/8/16/auto, and the in-place decode of the fused decoder's cache."""
     reps = max(args.steps, 5)
     T = 262144
-    out = {}
-    out["reshape_bf16"] = reshape_case(torch, tq, dev, "bf16", 8, 128, T, reps)
-    out["reshape_a8"] = reshape_case(torch, tq, dev, "int8", 8, 128, T, reps)
-    out["reshape_bf16_d256"] = reshape_case(torch, tq, dev, "bf16", 4, 256, T, reps)
-    out["reshape_a8_d256"] = reshape_case(torch, tq, dev, "int8", 4, 256, T, reps)
-    out["decode_d256"] = decode_case(torch, tq, dev, 16, 4, 256, context_lengths(9, BATCH, 2048, 16384), reps)
-    out["decode_config3_us"] = config3_case(torch, tq, dev)
-    out["decode_nz_inplace"] = nz_case(torch, tq, dev, reps)
-    out["decode_persistent"] = persistent_case(torch, tq, dev, reps)
-    return out
+    cases = {
+        "reshape_bf16": lambda: reshape_case(torch, tq, dev, "bf16", 8, 128, T, reps),
+        "reshape_a8": lambda: reshape_case(torch, tq, dev, "int8", 8, 128, T, reps),
+        "reshape_bf16_d256": lambda: reshape_case(torch, tq, dev, "bf16", 4, 256, T, reps),
+        "reshape_a8_d256": lambda: reshape_case(torch, tq, dev, "int8", 4, 256, T, reps),
+        "decode_d256": lambda: decode_case(torch, tq, dev, 16, 4, 256,
+                                           context_lengths(9, BATCH, 2048, 16384), reps),
+        "decode_config3_us": lambda: config3_case(torch, tq, dev),
+        "decode_nz_inplace": lambda: nz_case(torch, tq, dev, reps),
+        "decode_persistent": lambda: persistent_case(torch, tq, dev, reps),
+    }
+    only = [n for n in (args.side or "").split(",") if n]
+    for n in only:
+        if n not in cases:
+            raise SystemExit(f"--side: unknown case {n!r}; known: {', '.join(cases)}")
+    return {n: fn() for n, fn in cases.items() if not only or n in only}
 
 
 def _use_reference_geometry():
@@ -1066,6 +1072,8 @@ def main():
                          "long: 128 sequences of 65536 tokens in the whole job (strong scaling)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements of `extra`")
     ap.add_argument("--no-verify", action="store_true", help="skip the oracle check before timing")
+    ap.add_argument("--side", default=None,
+                    help="comma-separated names of `extra` cases: time only these and print them (one GPU)")
     ap.add_argument("--profile", default=None,
                     choices=["decode", "decode_persistent", "decode_d256", "decode_nz", "config3", "reshape", "reshape_a8", "reshape_d256",
                              "reshape_a8_d256", "lm_decode", "lm_reshape", "scatter", "nz_import"],
@@ -1073,6 +1081,11 @@ def main():
     args = ap.parse_args()
     if args.profile:
         run_profile_case(args)
+    elif args.side:
+        import torch
+        import ascend_micro_harness_b200 as tq
+        torch.cuda.set_device(0)
+        print(json.dumps({"side": side_measurements(torch, tq, torch.device("cuda", 0), args)}))
     elif args.impl == "reference":
         run_reference(args)
     else:

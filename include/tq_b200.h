@@ -104,6 +104,13 @@ int tq_reshape_and_cache_warp_mma(void* stream, const void* key, const void* val
                                   uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
                                   uint32_t num_blocks, float inv_sqrt_len, uint32_t* status);
 
+/* Every wait inside the tcgen05 writer (on a tile fetch, on a tensor-core product) is bounded:
+ * when `cycles` clock cycles have passed the kernel reports TQ_STATUS_WAIT_EXPIRED, stores
+ * nothing more, lets what it has in flight finish and returns. The default is about a second;
+ * zero makes every wait give up at once (what the tests use to walk that path); a negative
+ * value restores the default. Process-wide, read at each launch. */
+void tq_ingest_set_wait_budget(long long cycles);
+
 /* The aligned writer over ragged requests (bf16): request b owns tokens cu_seqlens[b] ..
  * cu_seqlens[b+1] and the strips strip_begin[b] .. strip_begin[b+1] (the caller's prefix sum
  * of ceil(length / 16); both arrays have num_requests + 1 device entries, total_strips =

@@ -188,6 +188,55 @@ def test_bad_slot_run_is_skipped_and_reported(cuda, oracle):
     assert got[3] & tq.STATUS_BAD_SLOT
 
 
+@pytest.mark.parametrize("dtype", ["int8", "bf16"])
+def test_wait_that_runs_out_is_reported_and_nothing_is_stored(cuda, oracle, dtype):
+    """tcgen05 writer: with a wait budget of zero every wait on a tile fetch gives up at once. The
+    launch must set STATUS_WAIT_EXPIRED, store nothing, let its fetches land and return; the next
+    launch with the default budget, in the same context, is exact again."""
+    import ascend_micro_harness_b200 as tq
+    if WARP_MMA:
+        pytest.skip("the warp-MMA writer has no barrier waits")
+    rng = np.random.default_rng(77)
+    H, d, strips = 4, 128, 2400           # more (tile, head) items than resident groups
+    k, v = hp.int8_activations(rng, strips * 16, H, d)
+    slots, P = hp.fragmented_slots(strips)
+    signs = oracle.writer_signs(d)
+    want = expect(oracle, k, v, slots, signs, H, d, 16, P)
+    if dtype == "bf16":
+        k, v = hp.bf16_from_f32(k.astype(np.float32)), hp.bf16_from_f32(v.astype(np.float32))
+    tq.set_ingest_wait_budget(0)
+    try:
+        kc, vc, sc, status = run_device(cuda, k, v, slots, signs, H, d, 16, P, status=True)
+    finally:
+        tq.set_ingest_wait_budget(-1)
+    assert status & tq.STATUS_WAIT_EXPIRED
+    assert (kc == CANARY).all() and (vc == CANARY).all()
+    assert (sc.view(np.uint32) == 0x7FC0BEEF).all()
+    got = run_device(cuda, k, v, slots, signs, H, d, 16, P, status=True)
+    assert_identical(got, want)
+    assert got[3] == 0
+
+
+def test_int8_rows_at_the_accumulator_extremes(cuda, oracle):
+    """int8 rows whose rotated sums reach +-128 * 128 (a row of -128s against a sign row of all
+    ones, and its mirror), next to rows of zeros and of single +-1 entries: the absmax read from
+    the low halves of the accumulators must still be exact."""
+    rng = np.random.default_rng(404)
+    H, d, strips = 2, 128, 9
+    k, v = hp.int8_activations(rng, strips * 16, H, d)
+    signs = np.ones(d, np.float32)
+    k[0, :], k[1, :], k[2, :] = -128, 127, 0
+    v[0, :], v[1, :], v[2, :] = 127, -128, 0
+    k[3, :], v[3, :] = 0, 0
+    k[3, 5], v[3, 77] = 1, -1
+    k[4, :d] = -128                      # head 0 only
+    v[5, d:] = -128                      # head 1 only
+    slots, P = hp.fragmented_slots(strips)
+    for sg in (signs, oracle.writer_signs(d)):
+        got = run_device(cuda, k, v, slots, sg, H, d, 16, P)
+        assert_identical(got, expect(oracle, k, v, slots, sg, H, d, 16, P))
+
+
 def test_partial_strip_is_refused(cuda):
     import torch
     import ascend_micro_harness_b200 as tq
