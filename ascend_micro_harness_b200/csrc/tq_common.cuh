@@ -107,6 +107,36 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float v)
     return __bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
+// n / d for any 32-bit n with the precomputed (mul, shift) of divisor d >= 2
+// (round-up method: mul = floor(2^32 (2^l - d) / d) + 1, l = ceil(log2 d)).
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shift)
+{
+    const uint32_t t = __umulhi(mul, n);
+    return (t + ((n - t) >> 1)) >> shift;
+}
+
+// The (mul, shift) pair of fast_div for divisor d >= 2.
+inline void fast_div_constants(uint32_t d, uint32_t* mul, uint32_t* shift)
+{
+    uint32_t l = 0;
+    while ((1ull << l) < d) ++l;
+    *mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d)) / d + 1ull);
+    *shift = l - 1u;
+}
+
+// A divisor fixed at launch, any value >= 1: the host prepares it, the kernel divides by it
+// with a multiply and two shifts instead of the dozens of dependent instructions of a division
+// in software.
+struct Divider {
+    uint32_t d = 1, mul = 0, shift = 0;
+    Divider() = default;
+    explicit Divider(uint32_t divisor) : d(divisor)
+    {
+        if (d >= 2u) fast_div_constants(d, &mul, &shift);
+    }
+    __device__ __forceinline__ uint32_t quotient(uint32_t n) const { return d == 1u ? n : fast_div(n, mul, shift); }
+};
+
 __device__ __forceinline__ void report(uint32_t* status, uint32_t bits)
 {
     if (status != nullptr) atomicOr(status, bits);

@@ -50,6 +50,18 @@ constexpr int kMaxSplits = TQ_MAX_SPLITS;   // record slots per head a workspace
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
+// floor(2^32 / d) + 1 for d = 2 .. kMaxSplits: n / d == umulhi(n, table[d]) for n < 2^27
+struct SmallReciprocals {
+    uint32_t v[kMaxSplits + 1];
+    constexpr SmallReciprocals() : v{}
+    {
+        for (uint32_t d = 2; d <= static_cast<uint32_t>(kMaxSplits); ++d)
+            v[d] = static_cast<uint32_t>((1ull << 32) / d + 1ull);
+    }
+    __device__ __forceinline__ uint32_t operator[](uint32_t d) const { return v[d]; }
+};
+__constant__ SmallReciprocals kSmallReciprocal;
+
 struct DecodeParams {
     const uint16_t* q;        // [items*rows][D] bf16
     const void* signs;
@@ -65,6 +77,8 @@ struct DecodeParams {
     uint32_t table_stride, splits, page_begin, page_count, fixed_ctx;
     uint32_t sp_shift;        // log2(strips per page); pages hold 16 * 2^k tokens
     uint32_t chunk_pages;     // 0: every sequence uses `splits`; else at most ceil(pages/chunk)
+    // launch-constant divisors of the prologue, prepared on the host
+    Divider by_splits, by_row_tiles, by_heads, by_chunk_pages;
     uint32_t q_f16;           // 1: the query is FP16 and its rotation stays FP32 (no bf16 rounding)
     uint32_t tokens_per_req;  // query tokens per request (1 + speculative): row = token * G + head-in-group
     const float* q_f32;       // non-null: the query is FP32 and already rotated (no rotation, no rounding)
@@ -439,6 +453,9 @@ tq_decode_partial_kernel(const DecodeParams p)
     // kernel carries none of the finishing code (its presence alone cost 2.4 % there).
     constexpr bool STREAMK = MODE == kModePersistent;
     constexpr bool DIRECT = MODE == kModeDirect;
+    // The combine that follows a record export may be scheduled as soon as every CTA of this
+    // grid has started (it waits for the grid's completion before it reads a record).
+    if constexpr (MODE == kModeRecords) asm volatile("griddepcontrol.launch_dependents;\n");
     static_assert(!NZ || D == 256, "the NZ-tiled cache has head size 256");
     static_assert(!(STREAMK && PRECISE), "the persistent grid serves the native path");
     using L = DecodeSmem<D>;
@@ -690,13 +707,12 @@ tq_decode_partial_kernel(const DecodeParams p)
             return;
         }
     } else {
-        uint32_t lin = blockIdx.x;
-        split = lin % p.splits;
-        lin /= p.splits;
-        row_tile = lin % row_tiles;
-        const uint32_t item = lin / row_tiles;
-        seq = item / p.H;
-        head = item % p.H;
+        const uint32_t per_split = p.by_splits.quotient(blockIdx.x);
+        split = blockIdx.x - per_split * p.splits;
+        const uint32_t item = p.by_row_tiles.quotient(per_split);
+        row_tile = per_split - item * row_tiles;
+        seq = p.by_heads.quotient(item);
+        head = item - seq * p.H;
     }
 
 #pragma unroll 1
@@ -723,7 +739,7 @@ tq_decode_partial_kernel(const DecodeParams p)
             uint32_t page_count;
             if (p.context_lens != nullptr) {
                 ctx = context_of(seq);
-                page_count = (ctx + p.S - 1u) / p.S;
+                page_count = (ctx + p.S - 1u) >> (4u + sp_shift);   // pages hold 16 << sp_shift tokens
             } else {
                 ctx = p.fixed_ctx;
                 page_count = p.page_count;
@@ -733,10 +749,13 @@ tq_decode_partial_kernel(const DecodeParams p)
             // does not use fall out of the partition as empty ranges and export the neutral element.
             uint32_t eff_splits = p.splits;
             if (p.chunk_pages != 0u) {
-                const uint32_t chunks = (page_count + p.chunk_pages - 1u) / p.chunk_pages;
+                const uint32_t chunks = p.by_chunk_pages.quotient(page_count + p.chunk_pages - 1u);
                 eff_splits = chunks < 1u ? 1u : (chunks < p.splits ? chunks : p.splits);
             }
-            const uint32_t width = (page_count + eff_splits - 1u) / eff_splits;
+            // eff_splits <= 32 and page counts stay far below 2^27: one multiply by the tabulated
+            // floor(2^32 / d) + 1 is the exact quotient
+            const uint32_t width = eff_splits == 1u ? page_count
+                                                    : __umulhi(page_count + eff_splits - 1u, kSmallReciprocal[eff_splits]);
             const uint32_t rb = split * width;
             const uint32_t remaining = rb < page_count ? page_count - rb : 0u;
             const uint32_t rc = remaining < width ? remaining : width;
@@ -1627,6 +1646,10 @@ __global__ void __launch_bounds__(D) tq_combine_kernel(const CombineParams p)
                            static_cast<size_t>(o_head) * grp + o_g;
     const float* base = p.workspace + (static_cast<size_t>(item) * p.splits * p.rows_stride + row) * kRecord;
     const size_t split_stride = static_cast<size_t>(p.rows_stride) * kRecord;
+    // Launched as the programmatic dependent of the kernel that writes the records, this grid
+    // is set up while that kernel's last CTAs still run; the records are read only once that
+    // kernel has completed (a no-op after an ordinary launch).
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     // All records are fetched before the first one is merged, so the loads overlap instead
     // of forming a chain of dependent round trips to L2 (at most MAXK records).
     float mk[MAXK], lk[MAXK], ak[MAXK];
@@ -1743,6 +1766,10 @@ static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p_
     }
     uint64_t grid = static_cast<uint64_t>(p.items) * ((p.rows + 7u) / 8u) * p.splits;
     if (grid == 0) return cudaSuccess;
+    p.by_splits = Divider(p.splits);
+    p.by_row_tiles = Divider((p.rows + 7u) / 8u);
+    p.by_heads = Divider(p.H);
+    p.by_chunk_pages = Divider(p.chunk_pages ? p.chunk_pages : 1u);
     if (STREAMK) {
         int sms = dev >= 0 && dev < 64 ? sm_count[dev] : 0;
         if (sms <= 0) sms = 148;
@@ -1915,7 +1942,8 @@ static int splitk_combine(void* stream, const float* workspace, const float* pi_
                           const void* gate, uint32_t gate_dtype, void* output, uint32_t out_dtype,
                           uint32_t items, uint32_t rows, uint32_t rows_stride, uint32_t head_size,
                           uint32_t splits, uint32_t output_stage, float inv_sqrt_len,
-                          uint32_t tokens_per_req = 1, uint32_t kv_heads = 1, uint32_t rotation = ~0u)
+                          uint32_t tokens_per_req = 1, uint32_t kv_heads = 1, uint32_t rotation = ~0u,
+                          bool follows_export = false)
 {
     if (!rows || rows > rows_stride || !splits || splits > TQ_MAX_SPLITS || output_stage > TQ_OUT_GATED ||
         out_dtype > TQ_DTYPE_F32 || gate_dtype > TQ_DTYPE_F32 ||
@@ -1930,15 +1958,26 @@ static int splitk_combine(void* stream, const float* workspace, const float* pi_
                     gate_dtype, tokens_per_req, kv_heads};
     const uint64_t grid = static_cast<uint64_t>(items) * rows;
     if (grid > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (head_size == 128) {
-        if (splits <= 16u) tq_combine_kernel<128, 16><<<static_cast<unsigned>(grid), 128, 0, s>>>(p);
-        else tq_combine_kernel<128, kMaxSplits><<<static_cast<unsigned>(grid), 128, 0, s>>>(p);
-    } else {
-        if (splits <= 16u) tq_combine_kernel<256, 16><<<static_cast<unsigned>(grid), 256, 0, s>>>(p);
-        else tq_combine_kernel<256, kMaxSplits><<<static_cast<unsigned>(grid), 256, 0, s>>>(p);
-    }
-    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+    // Right behind the export kernel of the same call the combine is its programmatic
+    // dependent: the export's CTAs release it as they start, it is scheduled as they drain, and
+    // griddepcontrol.wait holds its reads back until the export has completed.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(head_size);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = follows_export ? 1 : 0;
+    cudaError_t e;
+    if (head_size == 128)
+        e = splits <= 16u ? cudaLaunchKernelEx(&cfg, tq_combine_kernel<128, 16>, p)
+                          : cudaLaunchKernelEx(&cfg, tq_combine_kernel<128, kMaxSplits>, p);
+    else
+        e = splits <= 16u ? cudaLaunchKernelEx(&cfg, tq_combine_kernel<256, 16>, p)
+                          : cudaLaunchKernelEx(&cfg, tq_combine_kernel<256, kMaxSplits>, p);
+    return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 
 extern "C" int tq_splitk_combine(void* stream, const float* workspace, const float* pi_signs,
@@ -2157,7 +2196,7 @@ static int decode_planned(void* stream, const uint16_t* query, const int8_t* key
     const uint32_t rows = num_heads / num_kv_heads * o.tokens_per_req;
     return splitk_combine(stream, workspace, pi_signs, gate, o.gate_dtype, output, out_dtype,
                           batch * num_kv_heads, rows, rows, head_size, splits, output_stage,
-                          inv_sqrt_len, o.tokens_per_req, num_kv_heads, rotation);
+                          inv_sqrt_len, o.tokens_per_req, num_kv_heads, rotation, true);
 }
 
 // Query, gate and output in ONE 16-bit element type, FP16 or BF16, as the raw-query entry of

@@ -175,14 +175,14 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
     // (tests/common/turboquant_oracle.hpp:278-287).
     const int32_t slot0 = __shfl_sync(0xffffffffu, slot, 0);
     const bool run_ok = (slot == slot0 + (lane & 15));
-    const bool strip_ok = __all_sync(0xffffffffu, run_ok) && slot0 >= 0 && (slot0 % kStrip) == 0 &&
-                          static_cast<uint32_t>(slot0) / p.S < p.P;
+    // slot0 / S by the precomputed multiplier (a division in software is dozens of dependent instructions)
+    const uint32_t page = fast_div(static_cast<uint32_t>(slot0), p.page_mul, p.page_shift);
+    const bool strip_ok = __all_sync(0xffffffffu, run_ok) && slot0 >= 0 && (slot0 % kStrip) == 0 && page < p.P;
     if (!strip_ok) {
         if (lane == 0) report(p.status, TQ_STATUS_BAD_SLOT);
         return;
     }
-    const uint32_t page = static_cast<uint32_t>(slot0) / p.S;
-    const uint32_t tok_in_page = static_cast<uint32_t>(slot0) % p.S;
+    const uint32_t tok_in_page = static_cast<uint32_t>(slot0) - page * p.S;
 
     // y[tt][g][ep]: token 2r+tt, channels g*32 + qd*8 + 2ep, +1 as one float pair
     // (exact integers for int8 and integer-valued bf16 inputs).

@@ -32,23 +32,6 @@ struct IngestParams {
     long long wait_budget = kIngestWaitBudget;
 };
 
-// n / d for any 32-bit n with the precomputed (mul, shift) of divisor d >= 2
-// (round-up method: mul = floor(2^32 (2^l - d) / d) + 1, l = ceil(log2 d)).
-__device__ __forceinline__ uint32_t fast_div(uint32_t n, uint32_t mul, uint32_t shift)
-{
-    const uint32_t t = __umulhi(mul, n);
-    return (t + ((n - t) >> 1)) >> shift;
-}
-
-// The (mul, shift) pair of fast_div for divisor d >= 2.
-inline void fast_div_constants(uint32_t d, uint32_t* mul, uint32_t* shift)
-{
-    uint32_t l = 0;
-    while ((1ull << l) < d) ++l;
-    *mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d)) / d + 1ull);
-    *shift = l - 1u;
-}
-
 // The tcgen05 writer for head size 128 (tq_ingest_umma.cu). `bf16` selects the element type.
 cudaError_t launch_ingest_umma(cudaStream_t stream, const IngestParams& p, bool bf16);
 

@@ -636,7 +636,12 @@ def config3_case(torch, tq, dev):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     res = {"workload": "batch 1, 32 q / 8 KV heads x 128, context 4096, L2 evicted before every call",
            "kv_bytes": ctx_len * HKV * (D + 8), "us_per_decode": {}, "warm_us_per_decode": {}}
-    for splits in (1, 2, 4, 8, 16, 0):
+    # what the same bracket reads around nothing and around a 32-element elementwise kernel:
+    # the part of every figure below that is the method's, not the decode's
+    tiny = torch.zeros(32, device=dev)
+    res["floor_us"] = {"empty_bracket": summary(cold_samples(torch, lambda: None, 30, flush))["p50_us"],
+                       "tiny_kernel": summary(cold_samples(torch, lambda: tiny.add_(1), 30, flush))["p50_us"]}
+    for splits in (1, 2, 4, 8, 16, 32, 0):
         n = splits if splits else tq.choose_splits(1, HKV, S, ctx_len)
         ws = torch.zeros(tq.decode_workspace_floats(1, HQ, HKV, D, n), device=dev)
 
@@ -658,6 +663,19 @@ def config3_case(torch, tq, dev):
             torch.cuda.synchronize()
             warm.append(a.elapsed_time(b))
         res["warm_us_per_decode"][name] = summary(warm)["p50_us"]
+    # the same decode as ONE launch: the persistent grid merges the records itself
+    res["single_launch_us_per_decode"] = {}
+    for slots in (8, 16, 32):
+        ws = torch.zeros(tq.decode_workspace_floats(1, HQ, HKV, D, slots), device=dev)
+
+        def one():
+            tq.decode_splitk(q, kc, vc, sc, tab, lens, signs, out, num_heads=HQ, num_kv_heads=HKV,
+                             head_size=D, block_size=S, num_blocks=P, inv_sqrt_len=inv,
+                             softmax_scale=inv, splits=slots, max_context_hint=ctx_len, workspace=ws,
+                             output_stage=1, persistent=True)
+        for _ in range(5):
+            one()
+        res["single_launch_us_per_decode"][str(slots)] = summary(cold_samples(torch, one, 30, flush))["p50_us"]
     return res
 
 
