@@ -78,7 +78,11 @@ struct DecodeParams {
     uint32_t sp_shift;        // log2(strips per page); pages hold 16 * 2^k tokens
     uint32_t chunk_pages;     // 0: every sequence uses `splits`; else at most ceil(pages/chunk)
     // launch-constant divisors of the prologue, prepared on the host
-    Divider by_splits, by_row_tiles, by_heads, by_chunk_pages;
+    Divider by_heads_tiles, by_row_tiles, by_heads, by_chunk_pages;
+    // The library's own plan (graded != 0): piece k of every sequence covers the pages
+    // [cuts[k], cuts[k + 1]) that the sequence has; the last cut is past any sequence.
+    uint32_t graded;
+    uint32_t cuts[TQ_MAX_SPLITS + 1];
     uint32_t q_f16;           // 1: the query is FP16 and its rotation stays FP32 (no bf16 rounding)
     uint32_t tokens_per_req;  // query tokens per request (1 + speculative): row = token * G + head-in-group
     const float* q_f32;       // non-null: the query is FP32 and already rotated (no rotation, no rounding)
@@ -707,8 +711,11 @@ tq_decode_partial_kernel(const DecodeParams p)
             return;
         }
     } else {
-        const uint32_t per_split = p.by_splits.quotient(blockIdx.x);
-        split = blockIdx.x - per_split * p.splits;
+        // The split is the slowest index of the grid: the hardware hands out CTAs in index
+        // order, so all first pieces run before any second piece, and with the graded
+        // partition below the pieces that start last are the smallest ones.
+        split = p.by_heads_tiles.quotient(blockIdx.x);
+        const uint32_t per_split = blockIdx.x - split * (p.items * row_tiles);
         const uint32_t item = p.by_row_tiles.quotient(per_split);
         row_tile = per_split - item * row_tiles;
         seq = p.by_heads.quotient(item);
@@ -720,6 +727,39 @@ tq_decode_partial_kernel(const DecodeParams p)
         // ---- this segment: (seq, head, row_tile), strips [s0, s1), where its record goes
         uint32_t ctx, s0, s1, seg_count = 1, seg_slot = split;
         bool no_pages = false;
+        [[maybe_unused]] int32_t spec_pg[kTileStrips];
+        // The sign diagonal and this warp's two raw query rows: requested as early as the
+        // segment's (sequence, head, row tile) is known, ahead of everything that waits.
+        constexpr int K = D / 32;
+        float sgn[K], qraw[2][K];
+        auto request_query = [&]() {
+            const int rows_now = min(8u, p.rows - row_tile * 8u);
+#pragma unroll
+            for (int i = 0; i < K; ++i) {
+                if constexpr (STREAMK) sgn[i] = prerot ? 1.0f : sk_sgn[lane * K + i];
+                else sgn[i] = !prerot && sign_is_negative(p.signs, p.sign_source, lane * K + i) ? -1.0f : 1.0f;
+            }
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+                const int row = warp * 2 + rr;
+#pragma unroll
+                for (int i = 0; i < K; ++i) qraw[rr][i] = 0.f;
+                if (row < rows_now) {
+                    // row = token * G + g of the request's (1 + speculative) query tokens; with one
+                    // token per request this is (item * rows + row)
+                    const uint32_t row_g = row_tile * 8u + row, grp = p.rows / tokens_per_req;
+                    const uint32_t q_tok = row_g / grp, q_g = row_g - q_tok * grp;
+                    const size_t qoff = ((static_cast<size_t>(seq) * tokens_per_req + q_tok) * (p.H * grp) +
+                                         static_cast<size_t>(head) * grp + q_g) * D + lane * K;
+                    const uint16_t* qsrc = p.q + qoff;
+#pragma unroll
+                    for (int i = 0; i < K; ++i)
+                        qraw[rr][i] = prerot ? p.q_f32[qoff + i]
+                                             : q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
+                }
+            }
+        };
+        if constexpr (!STREAMK) request_query();
         [[maybe_unused]] uint32_t sk_take = 0;
         if constexpr (STREAMK) {
             const uint32_t in_seq = sk_loc / sk_n, t0 = sk_loc - in_seq * sk_n;
@@ -736,6 +776,19 @@ tq_decode_partial_kernel(const DecodeParams p)
             seg_count = chunk_of(sched, first + sk_n - 1u) - k_first + 1u;
             seg_slot = cur_chunk - k_first;
         } else {
+            // Graded plan: where the piece starts is a launch constant, so the block-table
+            // entries of this warp's first tile are requested together with the context length
+            // instead of one round trip after it (entries past the sequence are read but not used).
+            const bool graded = p.graded != 0u;
+            if (graded) {
+                const uint32_t first = (p.page_begin + p.cuts[split]) * SP + warp * kTileStrips;
+                const int32_t* row = p.table + static_cast<size_t>(seq) * p.table_stride;
+#pragma unroll
+                for (int ts = 0; ts < kTileStrips; ++ts) {
+                    const uint32_t entry = (first + ts) >> sp_shift;
+                    spec_pg[ts] = entry < p.table_stride ? __ldg(row + entry) : -1;
+                }
+            }
             uint32_t page_count;
             if (p.context_lens != nullptr) {
                 ctx = context_of(seq);
@@ -754,11 +807,18 @@ tq_decode_partial_kernel(const DecodeParams p)
             }
             // eff_splits <= 32 and page counts stay far below 2^27: one multiply by the tabulated
             // floor(2^32 / d) + 1 is the exact quotient
-            const uint32_t width = eff_splits == 1u ? page_count
-                                                    : __umulhi(page_count + eff_splits - 1u, kSmallReciprocal[eff_splits]);
-            const uint32_t rb = split * width;
-            const uint32_t remaining = rb < page_count ? page_count - rb : 0u;
-            const uint32_t rc = remaining < width ? remaining : width;
+            uint32_t rb, rc;
+            if (graded) {
+                rb = p.cuts[split];
+                const uint32_t end = min(p.cuts[split + 1u], page_count);
+                rc = end > rb ? end - rb : 0u;
+            } else {
+                const uint32_t width = eff_splits == 1u ? page_count
+                                                        : __umulhi(page_count + eff_splits - 1u, kSmallReciprocal[eff_splits]);
+                rb = split * width;
+                const uint32_t remaining = rb < page_count ? page_count - rb : 0u;
+                rc = remaining < width ? remaining : width;
+            }
             s0 = (p.page_begin + rb) * SP;
             s1 = s0 + rc * SP;
             const uint32_t live_strips = (ctx + kStrip - 1u) / kStrip;
@@ -868,6 +928,17 @@ tq_decode_partial_kernel(const DecodeParams p)
         const uint32_t strip_first = s0 + warp * kTileStrips;   // first strip of this warp's tile 0
         int32_t pg_next[kTileStrips];
         static_assert(kStages == 2, "the prologue below fills one stage ahead");
+        // the first tile's entries: requested at the top of the segment under the graded plan
+        auto first_pages = [&](int32_t (&pg)[kTileStrips]) {
+            if constexpr (!STREAMK) {
+                if (p.graded != 0u) {
+#pragma unroll
+                    for (int ts = 0; ts < kTileStrips; ++ts) pg[ts] = strip_first + ts < s1 ? spec_pg[ts] : -1;
+                    return;
+                }
+            }
+            load_pages(strip_first, pg);
+        };
         // Every global round trip of the prologue is started before anything waits for one: the
         // draw of the next chunk and a first look at the head's arrival counter (persistent grid,
         // consumed only after the fragments are built), the sign diagonal and this warp's two raw
@@ -881,36 +952,11 @@ tq_decode_partial_kernel(const DecodeParams p)
                     seen = *reinterpret_cast<volatile uint32_t*>(p.counters + (static_cast<size_t>(item) * row_tiles + row_tile));
             }
         }
-        constexpr int K = D / 32;
-        float sgn[K], qraw[2][K];
-#pragma unroll
-        for (int i = 0; i < K; ++i) {
-            if constexpr (STREAMK) sgn[i] = prerot ? 1.0f : sk_sgn[lane * K + i];
-            else sgn[i] = !prerot && sign_is_negative(p.signs, p.sign_source, lane * K + i) ? -1.0f : 1.0f;
-        }
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {
-            const int row = warp * 2 + rr;
-#pragma unroll
-            for (int i = 0; i < K; ++i) qraw[rr][i] = 0.f;
-            if (row < rows_here) {
-                // row = token * G + g of the request's (1 + speculative) query tokens; with one
-                // token per request this is (item * rows + row)
-                const uint32_t row_g = row_tile * 8u + row, grp = p.rows / tokens_per_req;
-                const uint32_t q_tok = row_g / grp, q_g = row_g - q_tok * grp;
-                const size_t qoff = ((static_cast<size_t>(seq) * tokens_per_req + q_tok) * (p.H * grp) +
-                                     static_cast<size_t>(head) * grp + q_g) * D + lane * K;
-                const uint16_t* qsrc = p.q + qoff;
-#pragma unroll
-                for (int i = 0; i < K; ++i)
-                    qraw[rr][i] = prerot ? p.q_f32[qoff + i]
-                                         : q_f16 ? __half2float(__ushort_as_half(qsrc[i])) : bf16_bits_to_f32(qsrc[i]);
-            }
-        }
+        if constexpr (STREAMK) request_query();
         // (the record-only kernel keeps rotation first: ahead of it the copies measured 2 % slower there)
         const bool early = MODE != kModeRecords && L::early_issue(warp) && !empty;
         if (early) {
-            load_pages(strip_first, pg_next);
+            first_pages(pg_next);
             issue(strip_first, 0, pg_next);
             cp_async_commit();
             load_pages(strip_first + kTileStep, pg_next);
@@ -1044,7 +1090,7 @@ tq_decode_partial_kernel(const DecodeParams p)
         float vnorm = 0.f, inv_vnorm = 0.f;
 
         if (!early) {
-            load_pages(strip_first, pg_next);
+            first_pages(pg_next);
             issue(strip_first, 0, pg_next);
             cp_async_commit();
             load_pages(strip_first + kTileStep, pg_next);
@@ -1766,10 +1812,20 @@ static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p_
     }
     uint64_t grid = static_cast<uint64_t>(p.items) * ((p.rows + 7u) / 8u) * p.splits;
     if (grid == 0) return cudaSuccess;
-    p.by_splits = Divider(p.splits);
+    p.by_heads_tiles = Divider(p.items * ((p.rows + 7u) / 8u));
     p.by_row_tiles = Divider((p.rows + 7u) / 8u);
     p.by_heads = Divider(p.H);
     p.by_chunk_pages = Divider(p.chunk_pages ? p.chunk_pages : 1u);
+    // Graded pieces of the library's own plan: widths fall linearly from 1.6 to 0.4 of the
+    // planned chunk, so the long pieces, which amortise a CTA's fixed cost, start first and
+    // the short ones fill the end of the launch (the split is the slowest grid index).
+    p.graded = (!STREAMK && p.chunk_pages != 0u && p.splits > 1u && p.context_lens != nullptr) ? 1u : 0u;
+    if (p.graded) {
+        const double n = p.splits, all = static_cast<double>(p.splits) * p.chunk_pages;
+        for (uint32_t k = 0; k < p.splits; ++k)
+            p.cuts[k] = static_cast<uint32_t>(all * (k * (1.6 - 0.6 * (k - 1.0) / (n - 1.0)) / n));
+        p.cuts[p.splits] = 0xFFFFFFFFu;
+    }
     if (STREAMK) {
         int sms = dev >= 0 && dev < 64 ? sm_count[dev] : 0;
         if (sms <= 0) sms = 148;
@@ -1812,26 +1868,42 @@ static cudaError_t launch_streamk(cudaStream_t stream, const DecodeParams& p)
 
 using namespace tq;
 
-// Split plan for a launch that leaves the choice to the library. Work is cut into chunks
-// of a power-of-two number of tokens such that the batch yields about 32 CTAs per SM
-// (fine enough to balance ragged contexts; measured best among 16/32/64/128 on the ragged
-// batch of 64). A chunk is 256..8192 tokens, and at least 1024 once the batch alone has a
-// CTA per SM, so that it amortises the per-CTA query rotation and merge; the launch's
-// split count is what the longest context needs, at most TQ_MAX_SPLITS.
+// Split plan for a launch that leaves the choice to the library. A sequence is cut into
+// pieces of `chunk` tokens on average (graded by the launcher: the first piece 1.6, the last
+// 0.4 of it), one CTA per piece and KV head. A CTA costs about 7 us besides its streaming
+// (context length and block table, query rotation, merge and record), so pieces should be
+// long; the end of the launch is filled by whatever pieces start last, so they should be
+// short. Measured on ragged batches of 64 (2048..16384 tokens; 8 KV heads x 128 and 4 x 256):
+// best with eight pieces for the longest sequence at head size 128 and 6.4 at head size 256,
+// whose CTAs cost more (twice the rotation and merge, three resident per SM instead of four);
+// the NZ-tiled head-size-256 pools, read in place, again with eight. Hence
+//   chunk = max(tokens that give 32 CTAs per SM, max_context / 8 (or / 6.4)),
+// but no larger than what leaves two pieces per resident CTA slot (small batches need the
+// parallelism more: batch 1 at 4096 tokens gets 256-token pieces), within 256..8192 tokens,
+// in steps of 256, at least 1024 once the batch alone has a CTA per SM; the launch's split
+// count is what the longest context needs, at most TQ_MAX_SPLITS.
 static void decode_plan(uint32_t batch, uint32_t num_kv_heads, uint32_t block_size,
                         uint32_t max_context, uint32_t sm_count, uint32_t* splits,
-                        uint32_t* chunk_pages)
+                        uint32_t* chunk_pages, uint32_t head_size = 128)
 {
     *splits = 1;
     *chunk_pages = 0;
     if (batch == 0 || num_kv_heads == 0 || block_size == 0 || max_context <= 256u) return;
+    const uint64_t sms = sm_count ? sm_count : 148u;
     const uint64_t items = static_cast<uint64_t>(batch) * num_kv_heads;
-    const uint64_t target = 32ull * (sm_count ? sm_count : 148u);
-    const uint64_t want = items * max_context / target;
-    uint64_t chunk = items >= (sm_count ? sm_count : 148u) ? 1024 : 256;
-    while (chunk < want && chunk < 8192u) chunk <<= 1;
-    while ((max_context + chunk - 1u) / chunk > TQ_MAX_SPLITS) chunk <<= 1;   // very long contexts
+    const uint64_t work = items * max_context;
+    const uint64_t by_load = work / (32ull * sms);
+    const uint64_t by_shape = head_size == 256 ? static_cast<uint64_t>(max_context) * 5u / 32u : max_context / 8u;
+    const uint64_t by_fill = work / (2ull * 4ull * sms);
+    const uint64_t floor_tokens = items >= sms ? 1024 : 256;
+    uint64_t chunk = by_load > by_shape ? by_load : by_shape;
+    if (chunk > by_fill) chunk = by_fill;
+    if (chunk < floor_tokens) chunk = floor_tokens;
+    chunk = (chunk + 255u) / 256u * 256u;
+    if (chunk > 8192u) chunk = 8192u;
+    while ((max_context + chunk - 1u) / chunk > TQ_MAX_SPLITS) chunk += 256u;   // very long contexts
     if (chunk < block_size) chunk = block_size;
+    chunk = (chunk + block_size - 1u) / block_size * block_size;
     *chunk_pages = static_cast<uint32_t>(chunk / block_size);
     *splits = static_cast<uint32_t>((max_context + chunk - 1u) / chunk);
 }
@@ -1992,7 +2064,7 @@ extern "C" int tq_splitk_combine(void* stream, const float* workspace, const flo
 
 static uint32_t resolve_splits(uint32_t splits, uint32_t batch, uint32_t num_kv_heads,
                                uint32_t block_size, uint32_t max_blocks, uint32_t hint,
-                               uint32_t* chunk_pages = nullptr)
+                               uint32_t* chunk_pages = nullptr, uint32_t head_size = 128)
 {
     if (chunk_pages) *chunk_pages = 0;
     if (splits != 0) return splits;   // explicit: every sequence uses the reference Partition
@@ -2001,7 +2073,7 @@ static uint32_t resolve_splits(uint32_t splits, uint32_t batch, uint32_t num_kv_
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     uint32_t s = 1, c = 0;
     decode_plan(batch, num_kv_heads, block_size, hint ? hint : max_blocks * block_size,
-                static_cast<uint32_t>(sms), &s, &c);
+                static_cast<uint32_t>(sms), &s, &c, head_size);
     if (chunk_pages) *chunk_pages = c;
     return s;
 }
@@ -2127,7 +2199,7 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
     if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages);
+                            &chunk_pages, head_size);
     return decode_export_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
                                  context_lens, pi_signs, workspace, batch, num_heads, num_kv_heads,
                                  head_size, block_size, num_blocks, max_blocks, splits, chunk_pages,
@@ -2220,7 +2292,7 @@ extern "C" int tq_decode_splitk_elem(void* stream, const void* query, const int8
         return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages);
+                            &chunk_pages, head_size);
     DecodeOptions o;
     o.gate_dtype = elem_dtype;
     o.q_f16 = elem_dtype == TQ_DTYPE_F16;
@@ -2243,7 +2315,7 @@ extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_
     if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages);
+                            &chunk_pages, head_size);
     return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
                           context_lens, pi_signs, gate, workspace, output, out_dtype, batch, num_heads,
                           num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,
@@ -2270,7 +2342,7 @@ extern "C" int tq_decode_splitk_mtp(void* stream, const uint16_t* query, const i
     if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS || tokens_per_req == 0) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages);
+                            &chunk_pages, head_size);
     DecodeOptions o;
     o.tokens_per_req = tokens_per_req;
     return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables, context_lens,
@@ -2308,7 +2380,7 @@ extern "C" int tq_decode_splitk_prerotated(void* stream, const float* query_rot,
         return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages);
+                            &chunk_pages, head_size);
     const float inv_sqrt_len = head_size == 128 ? 0.08838834764831845f : 0.0625f;
     DecodeOptions o;
     o.gate_dtype = gate_dtype;
@@ -2371,7 +2443,7 @@ extern "C" int tq_decode_splitk_precise(void* stream, const uint16_t* query, con
     if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages);
+                            &chunk_pages, head_size);
     DecodeOptions o;
     o.precise = true;
     return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
@@ -2485,7 +2557,7 @@ extern "C" int tq_decode_splitk_static(void* stream, const uint16_t* query, cons
     // Resolve the split count first: it decides how much of the array the launch needs.
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages);
+                            &chunk_pages, head_size);
     const size_t need = tq_decode_workspace_floats(batch, num_heads, num_kv_heads, head_size, splits);
     if (need > static_cast<size_t>(TQ_STATIC_WORKSPACE_FLOATS)) return TQ_ERR_WORKSPACE_TOO_SMALL;
     int st = TQ_OK;

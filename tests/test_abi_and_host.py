@@ -41,17 +41,22 @@ def test_acl_shim_exports_the_sixteen_calls():
 
 
 def test_split_choice():
-    """The plan cuts work into power-of-two chunks of 256..8192 tokens, about 32 CTAs per SM;
-    the launch's split count is what the longest context needs, at most TQ_MAX_SPLITS = 32."""
+    """The plan cuts a sequence into pieces of 256..8192 tokens (steps of 256): eight for the
+    longest sequence, more tokens per piece when the batch alone fills the machine, fewer when it
+    is too small to; the launch's split count is what the longest context needs, at most
+    TQ_MAX_SPLITS = 32. (Head size 256 launches use somewhat longer pieces, so never more splits
+    than this chooser, which sizes the workspace, reports.)"""
     import ascend_micro_harness_b200 as tq
     choose = lambda b, h, s, c: tq.choose_splits(b, h, s, c, 148)
     assert choose(64, 8, 16, 256) == 1             # short contexts run un-split
     assert choose(1, 8, 16, 4096) == 16            # one sequence: fill the machine
-    assert choose(1, 8, 16, 1024) == 4             # ... but keep 256 tokens per split
-    assert choose(64, 8, 16, 32768) == 8           # ragged batch: 4096-token chunks
-    assert choose(4096, 8, 16, 32768) == 4         # plenty of sequences: 8192-token chunks
-    assert choose(16, 8, 16, 65536) == 32          # few long sequences: 2048-token chunks
-    assert choose(128, 8, 16, 65536) == 8
+    assert choose(1, 8, 16, 1024) == 4             # ... but keep 256 tokens per piece
+    assert choose(64, 8, 16, 16384) == 8           # ragged batch: 2048-token pieces
+    assert choose(64, 4, 16, 16384) == 8           # ... whatever the number of KV heads
+    assert choose(64, 8, 16, 32768) == 8
+    assert choose(4096, 8, 16, 32768) == 4         # plenty of sequences: 8192-token pieces
+    assert choose(16, 8, 16, 65536) == 10          # few long sequences: two pieces per CTA slot
+    assert choose(1, 8, 16, 1 << 20) == 32         # one very long sequence: as many as the records allow
     for b in (1, 3, 64, 1000):
         for ctx in (1, 600, 5000, 70000, 1 << 20):
             s = choose(b, 8, 16, ctx)
