@@ -45,7 +45,6 @@ constexpr int kThreads = kGroups * kGroupThreads;
 constexpr uint32_t kGroupCols = 128;         // one 128 x 128 FP32/INT32 accumulator per group
 constexpr uint32_t kTmemCols = kGroups * kGroupCols;
 constexpr long long kWaitBudget = kIngestWaitBudget;   // clock cycles, about a second
-constexpr int kSpinPolls = 512;
 constexpr uint32_t kSuspendHintNs = 20000u;       // one poll may sleep this long before it returns
 
 constexpr float kBias = 12582912.0f;         // 1.5 * 2^23
@@ -124,18 +123,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity)
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}\n"
         : "=r"(ok) : "r"(mbar), "r"(parity), "r"(kSuspendHintNs) : "memory");
-    return ok != 0;
-}
-
-// The same test without the permission to sleep.
-__device__ __forceinline__ bool mbar_test_wait(uint32_t mbar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
     return ok != 0;
 }
 
@@ -359,11 +346,7 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
     // never have been issued).
     auto bounded_wait = [&](uint32_t bar, uint32_t par, long long budget, bool watch_abort) {
         if (budget <= 0) return false;
-        // a product or a tile fetch takes a microsecond or so: poll for that long before a
-        // wait that may put the thread to sleep (and wake it late)
-        bool done = false;
-#pragma unroll 1
-        for (int polls = 0; polls < kSpinPolls && !done; ++polls) done = mbar_test_wait(bar, par);
+        bool done = mbar_try_wait(bar, par);
         if (!done) {
             const long long t0 = clock64();
             do {
