@@ -103,6 +103,9 @@ struct DecodeParams {
     const void* gate;
     void* output;
     uint32_t output_stage, out_dtype, gate_dtype, rotation;
+    // host side only: the launch directly follows, in the same stream, the scatter writer of the
+    // same step and may be scheduled under it (the kernel holds its cache reads back)
+    uint32_t follows_writer;
     // optional worker census of the persistent grid: per CTA {start, end} in nanoseconds of the
     // global timer (null: off)
     unsigned long long* census;
@@ -706,7 +709,7 @@ tq_decode_partial_kernel(const DecodeParams p)
         sched.c0 = static_cast<uint32_t>(max(cmin, (share * 17ull + 19ull) / 20ull));
         sched.c1 = static_cast<uint32_t>(max(cmin, (share + 7ull) / 8ull));
         sched.c2 = static_cast<uint32_t>(max(cmin, (share + 15ull) / 16ull));
-        if (!begin_chunk(blockIdx.x)) {   // round 0 is dealt statically
+        if (!begin_chunk(blockIdx.x)) {   // the first chunk of every CTA is dealt statically
             leave();
             return;
         }
@@ -955,7 +958,12 @@ tq_decode_partial_kernel(const DecodeParams p)
         if constexpr (STREAMK) request_query();
         // (the record-only kernel keeps rotation first: ahead of it the copies measured 2 % slower there)
         const bool early = MODE != kModeRecords && L::early_issue(warp) && !empty;
+        // Launched as the programmatic dependent of the step's scatter writer, the CTA has come
+        // this far under it; the cache itself is read only once the writer has completed (a no-op
+        // after an ordinary launch).
+        auto writer_done = [] { asm volatile("griddepcontrol.wait;\n" ::: "memory"); };
         if (early) {
+            writer_done();
             first_pages(pg_next);
             issue(strip_first, 0, pg_next);
             cp_async_commit();
@@ -1090,6 +1098,7 @@ tq_decode_partial_kernel(const DecodeParams p)
         float vnorm = 0.f, inv_vnorm = 0.f;
 
         if (!early) {
+            writer_done();
             first_pages(pg_next);
             issue(strip_first, 0, pg_next);
             cp_async_commit();
@@ -1833,9 +1842,17 @@ static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p_
     }
     if (grid > 0x7FFFFFFFull) return cudaErrorInvalidValue;
     p.census = STREAMK && grid <= g_census_ctas.load() ? g_census.load() : nullptr;
-    tq_decode_partial_kernel<D, PRECISE, EXT, NZ, MODE><<<static_cast<unsigned>(grid), kDecWarps * 32,
-                                  DecodeSmem<D>::kTotal, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(kDecWarps * 32);
+    cfg.dynamicSmemBytes = DecodeSmem<D>::kTotal;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.follows_writer ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, tq_decode_partial_kernel<D, PRECISE, EXT, NZ, MODE>, p);
 }
 
 // The classic grid: one CTA per (sequence, KV head, split, row tile), records only.
@@ -2090,6 +2107,7 @@ struct DecodeOptions {
     float nz_gain = 1.0f;                // the codebook gain those scales are divided by
     bool precise = false;                // 24-bit fixed-point query and P as hi + lo halves (classic grid)
     bool persistent = false;             // one launch: persistent grid, combine folded in
+    bool follows_writer = false;         // directly behind the step's scatter writer in the stream
 };
 
 // Validates a decode call and fills the kernel parameters (everything but the combine part).
@@ -2137,6 +2155,7 @@ static int decode_params(DecodeParams& p, const uint16_t* query, const int8_t* k
     p.scale_cache = scale_cache;
     p.table = block_tables;
     p.context_lens = context_lens;
+    p.follows_writer = o.follows_writer ? 1u : 0u;
     p.q_rot = nullptr;
     p.workspace = workspace;
     p.items = batch * num_kv_heads;
@@ -2320,6 +2339,61 @@ extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_
                           context_lens, pi_signs, gate, workspace, output, out_dtype, batch, num_heads,
                           num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,
                           chunk_pages, output_stage, inv_sqrt_len, softmax_scale, status);
+}
+
+// One decode step of a serving stack as one call: the new token of every sequence is written
+// into the cache (tq_reshape_scatter: request r owns token r, slot_mapping[r] its slot, a negative
+// slot skips the write), then the batch is decoded over its pages, the new token included
+// (context_lens already count it). The decode is launched as the programmatic dependent of the
+// writer: its CTAs are scheduled, read their context lengths, block-table entries and queries and
+// rotate their queries while the writer still runs, and wait for the writer's completion only
+// before their first read of the cache.
+extern "C" int tq_reshape_scatter(void* stream, const uint16_t* key, const uint16_t* value,
+                                  int8_t* key_cache, int8_t* value_cache, float* scale_cache,
+                                  const int32_t* slot_mapping, const float* pi_signs,
+                                  const int32_t* cu_seqlens, uint32_t num_requests,
+                                  uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                                  uint32_t num_blocks, uint32_t item_begin, uint32_t item_count,
+                                  float inv_sqrt_len, uint32_t* status);
+
+extern "C" int tq_decode_step(void* stream, const uint16_t* new_key, const uint16_t* new_value,
+                              const int32_t* slot_mapping, const uint16_t* query, int8_t* key_cache,
+                              int8_t* value_cache, float* scale_cache, const int32_t* block_tables,
+                              const int32_t* context_lens, const float* pi_signs, const float* gate,
+                              float* workspace, void* output, uint32_t out_dtype, uint32_t batch,
+                              uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                              uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                              uint32_t splits, uint32_t max_context_hint, uint32_t output_stage,
+                              float inv_sqrt_len, float softmax_scale, uint32_t* status)
+{
+    if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
+    uint32_t chunk_pages = 0;
+    splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
+                            &chunk_pages, head_size);
+    // everything the decode would refuse is refused before the cache is touched
+    {
+        DecodeParams probe{};
+        DecodeOptions o;
+        const int st = decode_params(probe, query, key_cache, value_cache, scale_cache, block_tables,
+                                     context_lens, pi_signs, workspace, batch, num_heads, num_kv_heads,
+                                     head_size, block_size, num_blocks, max_blocks, splits, chunk_pages,
+                                     inv_sqrt_len, softmax_scale, status, o, splits > 1u);
+        if (st != TQ_OK) return st;
+        if (output_stage > TQ_OUT_GATED || out_dtype > TQ_DTYPE_F32 || !output ||
+            (output_stage == TQ_OUT_GATED && !gate))
+            return TQ_ERR_INVALID_ARGUMENT;
+    }
+    if (batch == 0) return TQ_OK;
+    const int ws = tq_reshape_scatter(stream, new_key, new_value, key_cache, value_cache, scale_cache,
+                                      slot_mapping, pi_signs, nullptr, batch, num_kv_heads, head_size,
+                                      block_size, num_blocks, 0, batch * num_kv_heads, inv_sqrt_len, status);
+    if (ws != TQ_OK) return ws;
+    DecodeOptions o;
+    o.follows_writer = true;
+    return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
+                          context_lens, pi_signs, gate, workspace, output, out_dtype, batch, num_heads,
+                          num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,
+                          chunk_pages, output_stage, inv_sqrt_len, softmax_scale, status, o);
 }
 
 // Several query tokens per request (a decode step that verifies speculative tokens): the

@@ -36,6 +36,9 @@ constexpr int kScatterWarps = 4;
 template <int D>
 __global__ void __launch_bounds__(kScatterWarps * 32) tq_scatter_kernel(const ScatterParams p)
 {
+    // a decode launched as this kernel's programmatic dependent may be scheduled from here on
+    // (it waits for this grid's completion before it reads the cache)
+    asm volatile("griddepcontrol.launch_dependents;\n");
     constexpr int K = D / 32;  // consecutive channels per lane
     const int lane = threadIdx.x & 31;
     const uint32_t warp_global = blockIdx.x * kScatterWarps + (threadIdx.x >> 5);

@@ -253,6 +253,34 @@ def decode_splitk(query, key_cache, value_cache, scale_cache, block_tables, cont
             _ptr(status)), name)
 
 
+def decode_step(new_key, new_value, slot_mapping, query, key_cache, value_cache, scale_cache, block_tables,
+                context_lens, pi_signs, output, *, num_heads, num_kv_heads, head_size, block_size, num_blocks,
+                inv_sqrt_len, softmax_scale=1.0, splits=0, max_context_hint=0, workspace=None, gate=None,
+                output_stage=OUT_ROTATED, status=None, stream=None):
+    """One decode step as one call: scatter-write the new token of every sequence (new_key / new_value
+    bfloat16 [batch, num_kv_heads * head_size], slot_mapping int32 [batch]), then decode_splitk over the
+    batch, the decode scheduled under the writer (programmatic dependent launch)."""
+    lib = load_library()
+    call = _Call("decode_step").take("new_key", new_key, _BF16).take("new_value", new_value, _BF16)
+    call.take("slot_mapping", slot_mapping, _I32).take("query", query, _BF16)
+    _decode_operands(call, key_cache, value_cache, scale_cache, block_tables, context_lens, pi_signs, output,
+                     gate, status)
+    batch = query.numel() // (num_heads * head_size)
+    if new_key.numel() != batch * num_kv_heads * head_size or slot_mapping.numel() != batch:
+        raise ValueError("decode_step: one new token per sequence: new_key [batch, num_kv_heads * head_size], "
+                         "slot_mapping [batch]")
+    max_blocks = block_tables.shape[-1]
+    _need_workspace(call, workspace, batch, num_heads, num_kv_heads, head_size, block_size, max_blocks, splits,
+                    max_context_hint)
+    with call:
+        _check(lib.tq_decode_step(
+            _stream(stream, call.device), _ptr(new_key), _ptr(new_value), _ptr(slot_mapping), _ptr(query),
+            _ptr(key_cache), _ptr(value_cache), _ptr(scale_cache), _ptr(block_tables), _ptr(context_lens),
+            _ptr(pi_signs), _ptr(gate), _ptr(workspace), _ptr(output), _out_dtype(output), batch, num_heads,
+            num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits, max_context_hint, output_stage,
+            inv_sqrt_len, softmax_scale, _ptr(status)), "tq_decode_step")
+
+
 def decode_splitk_elem(query, key_cache, value_cache, scale_cache, block_tables, context_lens,
                        pi_signs, output, *, num_heads, num_kv_heads, head_size, block_size, num_blocks,
                        inv_sqrt_len, softmax_scale=1.0, splits=0, max_context_hint=0, workspace=None,

@@ -261,6 +261,18 @@ def run_ours(args):
                 "kv_gbs_all_gpus": round(long_total / (lres["ms_step"] * 1e-3) / 1e9, 1),
                 "decode_kernel_us_rank0": round(lres["kernel_ms"] * 1e3, 1),
                 "decode_kernel_frac_of_hbm_peak_rank0": round(lres["bytes"] / (lres["kernel_ms"] * 1e-3) / 1e9 / peak, 4)}
+        if world == 1:
+            # what one GPU of eight would be handed (16 of the 128 sequences), timed on this GPU: the
+            # ratio of the two step times is the strong-scaling factor an 8-GPU run can reach at best,
+            # since the path has no exchange step
+            eighth = LONG_BATCH // 8
+            sres = fused_step_bench(torch, tq, dev, dist, np.full(eighth, LONG_CTX, np.int64), 48,
+                                    max(5, min(args.steps, 10)), 3, verify=False, e2e=False)
+            extra["long_context"]["one_eighth_share"] = {
+                "sequences": eighth, "ms_per_step": round(sres["ms_step"], 4),
+                "decode_kernel_us": round(sres["kernel_ms"] * 1e3, 1),
+                "decode_kernel_frac_of_hbm_peak": round(sres["bytes"] / (sres["kernel_ms"] * 1e-3) / 1e9 / peak, 4),
+                "step_time_ratio_full_over_share": round(lres["ms_step"] / sres["ms_step"], 2)}
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
@@ -314,7 +326,7 @@ def run_ours(args):
 # dram bytes (read + write) per algorithmic byte of the decode kernel, from an ncu capture of a
 # small ragged case: dram__bytes_read.sum + dram__bytes_write.sum over the case's KV bytes.
 # Traffic grows with the cache bytes read, so the full launch is scaled by its algorithmic bytes.
-DECODE_TRAFFIC_BYTES_PER_ALGORITHMIC_BYTE = 1.0387
+DECODE_TRAFFIC_BYTES_PER_ALGORITHMIC_BYTE = 1.0321
 
 
 def fused_step_bench(torch, tq, dev, dist, ctx, seed, steps, warmup, verify, e2e, sampler=None):
@@ -369,9 +381,12 @@ def fused_step_bench(torch, tq, dev, dist, ctx, seed, steps, warmup, verify, e2e
         tq.splitk_combine(ws, w["signs"], None, out, items=nseq * HKV, rows=HQ // HKV, rows_stride=HQ // HKV,
                           head_size=D, splits=splits, output_stage=tq.OUT_UNROTATED, inv_sqrt_len=w["inv"])
 
+    # the fused step as one call of the library: the decode is scheduled under the writer
     def step():
-        scatter()
-        decode()
+        tq.decode_step(dk, dv, dslots, dq, w["key_cache"], w["value_cache"], w["scale_cache"], w["tables"], dctx,
+                       w["signs"], out, num_heads=HQ, splits=0, softmax_scale=scale,
+                       max_context_hint=int(ctx1.max()), workspace=ws, output_stage=tq.OUT_UNROTATED,
+                       status=status, **geom)
 
     def e2e_body():
         dev_in.copy_(host_in, non_blocking=True)

@@ -172,6 +172,24 @@ int tq_decode_splitk(void* stream, const uint16_t* query, const int8_t* key_cach
                      uint32_t max_context_hint, uint32_t output_stage, float inv_sqrt_len,
                      float softmax_scale, uint32_t* status);
 
+/* One decode step of a serving stack as one call (the fused step the benchmark times): the new
+ * token of every sequence is written into the cache as tq_reshape_scatter does (request r owns row r
+ * of new_key / new_value, bf16 [batch][num_kv_heads*d]; slot_mapping[r] is its slot, a negative slot
+ * skips the write), then the batch is decoded exactly as by tq_decode_splitk; context_lens already
+ * count the new token. The decode is launched as the programmatic dependent of the writer, so its
+ * set-up (context lengths, block tables, query rotation) runs under the writer and only its
+ * first read of the cache waits for the writer's completion. Same refusals as the two calls; a
+ * decode the library would refuse leaves the cache untouched. */
+int tq_decode_step(void* stream, const uint16_t* new_key, const uint16_t* new_value,
+                   const int32_t* slot_mapping, const uint16_t* query, int8_t* key_cache,
+                   int8_t* value_cache, float* scale_cache, const int32_t* block_tables,
+                   const int32_t* context_lens, const float* pi_signs, const float* gate,
+                   float* workspace, void* output, uint32_t out_dtype, uint32_t batch,
+                   uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                   uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                   uint32_t max_context_hint, uint32_t output_stage, float inv_sqrt_len,
+                   float softmax_scale, uint32_t* status);
+
 /* tq_decode_splitk as one launch: a persistent grid over the batch's tiles with the
  * log-sum-exp merge folded in (the CTA that finishes a head's last outstanding segment merges
  * its records; no CTA waits for another). `splits` is the number of record slots per head the

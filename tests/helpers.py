@@ -14,14 +14,14 @@ def inv_sqrt_len(d: int) -> float:
 
 
 def int8_activations(rng, T, H, d):
-    """int8 K and V uniform in [-127, 127] (BASELINE config 1)."""
+    """int8 K and V uniform in [-127, 127] (the single-strip int8 case of the benchmark configurations)."""
     k = rng.integers(-127, 128, size=(T, H * d), dtype=np.int64).astype(np.int8)
     v = rng.integers(-127, 128, size=(T, H * d), dtype=np.int64).astype(np.int8)
     return k, v
 
 
 def gaussian_outlier_activations(rng, T, H, d, integer=False):
-    """N(0,1) with 1% of elements x20 (BASELINE config 2), as bf16 bit patterns.
+    """N(0,1) with 1% of elements x20 (the bf16 prefill case of the benchmark configurations), as bf16 bit patterns.
     integer=True rounds the same draws (x16, clipped to [-127, 127]) to integers so
     the result is bit-checkable."""
     out = []

@@ -185,3 +185,20 @@ def test_kv4_import_and_prerotated_decode_refuse_bad_arguments_on_the_host():
     assert lib.tq_rotate_query_pi(None, p, 2, p, p, 4, 256) == 1     # the raw query is 16-bit
     assert lib.tq_rotate_query_pi(None, p, 1, p, p, 4, 64) == 1      # head size
     assert lib.tq_rotate_query_pi(None, p, 1, p, p, 0, 256) == 0     # no rows
+
+
+def test_ctypes_table_matches_the_header_argument_counts():
+    """Every function include/tq_b200.h declares takes as many arguments as the loader's table gives it
+    (a wrong count would only show when the function is first called on a GPU)."""
+    import re
+    from ascend_micro_harness_b200._lib import SIGNATURES
+    text = open(os.path.join(ROOT, "include", "tq_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    seen = 0
+    for m in re.finditer(r"\b(\w+)\s*\(([^;{}]*?)\)\s*;", text):
+        name, args = m.group(1), m.group(2)
+        if name in SIGNATURES and SIGNATURES[name][1] is not None:
+            n = len([a for a in args.split(",") if a.strip() and a.strip() != "void"])
+            assert n == len(SIGNATURES[name][1]), name
+            seen += 1
+    assert seen >= 25

@@ -6,7 +6,7 @@ from tests import helpers as hp
 
 pytestmark = pytest.mark.gpu
 
-ABS_TOL, REL_TOL = 1e-3, 2e-3   # BASELINE: decode output vs FP64 reference
+ABS_TOL, REL_TOL = 1e-3, 2e-3   # the stated tolerance of the decode output against the FP64 reference
 
 
 def dev(cuda, a):
@@ -58,7 +58,7 @@ def assert_close(got, want):
 
 @pytest.mark.parametrize("splits", [1, 2, 4, 8, 16, 0])
 def test_config3_batch1_ctx4096(cuda, oracle, splits):
-    """BASELINE config 3: batch 1, 32 q / 8 KV heads, d=128, ctx 4096, shuffled table."""
+    """The single-sequence benchmark configuration: batch 1, 32 q / 8 KV heads, d=128, ctx 4096, shuffled table."""
     rng = np.random.default_rng(33)
     Hq, Hkv, d, S = 32, 8, 128, 16
     cache = hp.build_cache_from_gaussian(oracle, rng, [4096], Hkv, d, S)

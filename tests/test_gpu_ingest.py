@@ -73,7 +73,7 @@ def assert_identical(got, want):
 
 
 def test_config1_a8_single_strip(cuda, oracle):
-    """BASELINE config 1: 16 tokens, 1 KV head, d=128, int8 U[-127,127], identity slots."""
+    """The single-strip benchmark configuration: 16 tokens, 1 KV head, d=128, int8 U[-127,127], identity slots."""
     rng = np.random.default_rng(0x7151)
     k, v = hp.int8_activations(rng, 16, 1, 128)
     slots = np.arange(16, dtype=np.int32)
@@ -127,7 +127,7 @@ def test_large_pages_strips_at_in_page_offsets(cuda, oracle, S, d):
 
 
 def test_config2_bf16_integer_valued(cuda, oracle):
-    """BASELINE config 2, bit-exact leg: 1024 tokens x 8 heads x 128, integer-valued bf16,
+    """The bf16 prefill benchmark configuration, bit-exact leg: 1024 tokens x 8 heads x 128, integer-valued bf16,
     seeded page permutation of 64 pages."""
     rng = np.random.default_rng(2)
     H, d, T = 8, 128, 1024
@@ -139,7 +139,7 @@ def test_config2_bf16_integer_valued(cuda, oracle):
 
 
 def test_config2_bf16_gaussian_outliers(cuda, oracle):
-    """BASELINE config 2 as stated (non-integer bf16): the FP32 accumulation order is
+    """The bf16 prefill benchmark configuration as stated (non-integer bf16): the FP32 accumulation order is
     free, so codes may differ from the FP64-rotated oracle only at rounding ties."""
     rng = np.random.default_rng(3)
     H, d, T = 8, 128, 1024
