@@ -46,6 +46,8 @@ constexpr int kDecWarps = 4;
 // every CTA finishing its head and writing the output; the persistent grid with the merge folded in
 constexpr int kModeRecords = 0, kModeDirect = 1, kModePersistent = 2;
 constexpr int kCensusWords = 10;   // 64-bit words per CTA of the worker census
+// a plan's chunk_pages with this bit set asks for pieces of equal width (the one-wave plan)
+constexpr uint32_t kEqualPieces = 0x80000000u;
 constexpr int kMaxSplits = TQ_MAX_SPLITS;   // record slots per head a workspace can be asked to hold
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -1825,15 +1827,38 @@ static cudaError_t launch_partial_as(cudaStream_t stream, const DecodeParams& p_
     p.by_row_tiles = Divider((p.rows + 7u) / 8u);
     p.by_heads = Divider(p.H);
     p.by_chunk_pages = Divider(p.chunk_pages ? p.chunk_pages : 1u);
-    // Graded pieces of the library's own plan: widths fall linearly from 1.6 to 0.4 of the
-    // planned chunk, so the long pieces, which amortise a CTA's fixed cost, start first and
-    // the short ones fill the end of the launch (the split is the slowest grid index).
+    const bool equal_pieces = p.graded == 2u;
     p.graded = (!STREAMK && p.chunk_pages != 0u && p.splits > 1u && p.context_lens != nullptr) ? 1u : 0u;
     if (p.graded) {
-        const double n = p.splits, all = static_cast<double>(p.splits) * p.chunk_pages;
-        for (uint32_t k = 0; k < p.splits; ++k)
-            p.cuts[k] = static_cast<uint32_t>(all * (k * (1.6 - 0.6 * (k - 1.0) / (n - 1.0)) / n));
-        p.cuts[p.splits] = 0xFFFFFFFFu;
+        // The plan's split count is the number of record slots per head, whatever the head size
+        // (the caller sizes its workspace and runs the combine with it). Head size 256 fills
+        // fewer of them with longer pieces: its CTAs cost more (twice the rotation and merge) and
+        // three are resident per SM instead of four; the slots it leaves out get an empty range
+        // and export the neutral record. Measured on ragged batches of 64 (2048..16384 tokens, 16 q /
+        // 4 KV heads): 0.7 of the pieces for the native layout (+5 % over all of them), all of them
+        // for the NZ-tiled pools read in place.
+        int sms = dev >= 0 && dev < 64 ? sm_count[dev] : 0;
+        if (sms <= 0) sms = 148;
+        uint32_t used = p.splits;
+        if (D == 256) {
+            if (equal_pieces) {
+                const uint32_t fit = static_cast<uint32_t>(3 * sms) / (p.items ? p.items : 1u);
+                used = fit < 1u ? 1u : (fit < p.splits ? fit : p.splits);
+            } else {
+                used = NZ ? p.splits : (p.splits * 7u + 9u) / 10u;   // ceil(0.7 splits)
+                if (used < 1u) used = 1u;
+            }
+        }
+        const double n = used, all = static_cast<double>(p.splits) * p.chunk_pages;
+        // Graded pieces: widths fall linearly from `hi` to `2 - hi` of the mean, so the long pieces,
+        // which amortise a CTA's fixed cost, start first and the short ones fill the end of the
+        // launch (the split is the slowest grid index). Measured best on the ragged benchmark
+        // batches: 1.75..1.85 at head size 128 (+1.5 % over 1.6), 1.6 at head size 256. The
+        // one-wave plan asks for equal pieces (hi = 1).
+        const double hi = equal_pieces || used == 1u ? 1.0 : (D == 128 ? 1.8 : 1.6);
+        for (uint32_t k = 0; k <= p.splits; ++k)
+            p.cuts[k] = k < used ? static_cast<uint32_t>(all * (k * (hi - (hi - 1.0) * (k - 1.0) / (n > 1.0 ? n - 1.0 : 1.0)) / n))
+                                 : 0xFFFFFFFFu;
     }
     if (STREAMK) {
         int sms = dev >= 0 && dev < 64 ? sm_count[dev] : 0;
@@ -1886,32 +1911,33 @@ static cudaError_t launch_streamk(cudaStream_t stream, const DecodeParams& p)
 using namespace tq;
 
 // Split plan for a launch that leaves the choice to the library. A sequence is cut into
-// pieces of `chunk` tokens on average (graded by the launcher: the first piece 1.6, the last
-// 0.4 of it), one CTA per piece and KV head. A CTA costs about 7 us besides its streaming
+// pieces of `chunk` tokens on average (graded by the launcher: the first piece 1.8, the last
+// 0.2 of it at head size 128; 1.6 and 0.4 at head size 256), one CTA per piece and KV head. A CTA costs about 7 us besides its streaming
 // (context length and block table, query rotation, merge and record), so pieces should be
 // long; the end of the launch is filled by whatever pieces start last, so they should be
 // short. Measured on ragged batches of 64 (2048..16384 tokens; 8 KV heads x 128 and 4 x 256):
-// best with eight pieces for the longest sequence at head size 128 and 6.4 at head size 256,
-// whose CTAs cost more (twice the rotation and merge, three resident per SM instead of four);
-// the NZ-tiled head-size-256 pools, read in place, again with eight. Hence
-//   chunk = max(tokens that give 32 CTAs per SM, max_context / 8 (or / 6.4)),
-// but no larger than what leaves two pieces per resident CTA slot (small batches need the
-// parallelism more: batch 1 at 4096 tokens gets 256-token pieces), within 256..8192 tokens,
+// best with eight pieces for the longest sequence (head size 256 then fills four fifths of the
+// slots with longer pieces, see launch_partial_as). Hence
+//   chunk = max(tokens that give 32 CTAs per SM, max_context / 8),
+// but no larger than what leaves three pieces per resident CTA slot (small batches need the
+// parallelism more: batch 1 at 4096 tokens gets 256-token pieces; 16 sequences of 65 536 tokens
+// x 8 heads: 216 us with three graded pieces per slot, 242 us with two), within 256..8192 tokens,
 // in steps of 256, at least 1024 once the batch alone has a CTA per SM; the launch's split
 // count is what the longest context needs, at most TQ_MAX_SPLITS.
 static void decode_plan(uint32_t batch, uint32_t num_kv_heads, uint32_t block_size,
                         uint32_t max_context, uint32_t sm_count, uint32_t* splits,
-                        uint32_t* chunk_pages, uint32_t head_size = 128)
+                        uint32_t* chunk_pages)
 {
     *splits = 1;
     *chunk_pages = 0;
     if (batch == 0 || num_kv_heads == 0 || block_size == 0 || max_context <= 256u) return;
     const uint64_t sms = sm_count ? sm_count : 148u;
     const uint64_t items = static_cast<uint64_t>(batch) * num_kv_heads;
+    const uint64_t slots = sms * 4u;   // resident CTAs of the decode kernel at head size 128
     const uint64_t work = items * max_context;
     const uint64_t by_load = work / (32ull * sms);
-    const uint64_t by_shape = head_size == 256 ? static_cast<uint64_t>(max_context) * 5u / 32u : max_context / 8u;
-    const uint64_t by_fill = work / (2ull * 4ull * sms);
+    const uint64_t by_shape = max_context / 8u;
+    const uint64_t by_fill = work / (3ull * slots);
     const uint64_t floor_tokens = items >= sms ? 1024 : 256;
     uint64_t chunk = by_load > by_shape ? by_load : by_shape;
     if (chunk > by_fill) chunk = by_fill;
@@ -1921,8 +1947,11 @@ static void decode_plan(uint32_t batch, uint32_t num_kv_heads, uint32_t block_si
     while ((max_context + chunk - 1u) / chunk > TQ_MAX_SPLITS) chunk += 256u;   // very long contexts
     if (chunk < block_size) chunk = block_size;
     chunk = (chunk + block_size - 1u) / block_size * block_size;
-    *chunk_pages = static_cast<uint32_t>(chunk / block_size);
     *splits = static_cast<uint32_t>((max_context + chunk - 1u) / chunk);
+    // A launch that fits the resident CTA slots at once gains nothing from pieces of different
+    // lengths: its time is that of its longest piece, so they are made equal.
+    const bool equal = items * *splits <= slots;
+    *chunk_pages = static_cast<uint32_t>(chunk / block_size) | (equal ? kEqualPieces : 0u);
 }
 
 // Worker census of the persistent decode grid, after the reference's WorkerMetrics
@@ -2081,7 +2110,7 @@ extern "C" int tq_splitk_combine(void* stream, const float* workspace, const flo
 
 static uint32_t resolve_splits(uint32_t splits, uint32_t batch, uint32_t num_kv_heads,
                                uint32_t block_size, uint32_t max_blocks, uint32_t hint,
-                               uint32_t* chunk_pages = nullptr, uint32_t head_size = 128)
+                               uint32_t* chunk_pages = nullptr)
 {
     if (chunk_pages) *chunk_pages = 0;
     if (splits != 0) return splits;   // explicit: every sequence uses the reference Partition
@@ -2090,7 +2119,7 @@ static uint32_t resolve_splits(uint32_t splits, uint32_t batch, uint32_t num_kv_
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     uint32_t s = 1, c = 0;
     decode_plan(batch, num_kv_heads, block_size, hint ? hint : max_blocks * block_size,
-                static_cast<uint32_t>(sms), &s, &c, head_size);
+                static_cast<uint32_t>(sms), &s, &c);
     if (chunk_pages) *chunk_pages = c;
     return s;
 }
@@ -2166,7 +2195,8 @@ static int decode_params(DecodeParams& p, const uint16_t* query, const int8_t* k
     p.P = num_blocks;
     p.table_stride = max_blocks;
     p.splits = splits;
-    p.chunk_pages = chunk_pages;
+    p.chunk_pages = chunk_pages & ~kEqualPieces;
+    p.graded = (chunk_pages & kEqualPieces) ? 2u : 0u;   // 2: equal cuts asked for (see launch_partial_as)
     p.q_f16 = o.q_f16 ? 1u : 0u;
     p.tokens_per_req = o.tokens_per_req;
     p.page_begin = 0;
@@ -2218,7 +2248,7 @@ extern "C" int tq_decode_splitk_export(void* stream, const uint16_t* query,
     if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages, head_size);
+                            &chunk_pages);
     return decode_export_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
                                  context_lens, pi_signs, workspace, batch, num_heads, num_kv_heads,
                                  head_size, block_size, num_blocks, max_blocks, splits, chunk_pages,
@@ -2311,7 +2341,7 @@ extern "C" int tq_decode_splitk_elem(void* stream, const void* query, const int8
         return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages, head_size);
+                            &chunk_pages);
     DecodeOptions o;
     o.gate_dtype = elem_dtype;
     o.q_f16 = elem_dtype == TQ_DTYPE_F16;
@@ -2334,7 +2364,7 @@ extern "C" int tq_decode_splitk(void* stream, const uint16_t* query, const int8_
     if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages, head_size);
+                            &chunk_pages);
     return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
                           context_lens, pi_signs, gate, workspace, output, out_dtype, batch, num_heads,
                           num_kv_heads, head_size, block_size, num_blocks, max_blocks, splits,
@@ -2369,7 +2399,7 @@ extern "C" int tq_decode_step(void* stream, const uint16_t* new_key, const uint1
     if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages, head_size);
+                            &chunk_pages);
     // everything the decode would refuse is refused before the cache is touched
     {
         DecodeParams probe{};
@@ -2416,7 +2446,7 @@ extern "C" int tq_decode_splitk_mtp(void* stream, const uint16_t* query, const i
     if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS || tokens_per_req == 0) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages, head_size);
+                            &chunk_pages);
     DecodeOptions o;
     o.tokens_per_req = tokens_per_req;
     return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables, context_lens,
@@ -2454,7 +2484,7 @@ extern "C" int tq_decode_splitk_prerotated(void* stream, const float* query_rot,
         return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages, head_size);
+                            &chunk_pages);
     const float inv_sqrt_len = head_size == 128 ? 0.08838834764831845f : 0.0625f;
     DecodeOptions o;
     o.gate_dtype = gate_dtype;
@@ -2517,7 +2547,7 @@ extern "C" int tq_decode_splitk_precise(void* stream, const uint16_t* query, con
     if (!num_kv_heads || !block_size || splits > TQ_MAX_SPLITS) return TQ_ERR_INVALID_ARGUMENT;
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages, head_size);
+                            &chunk_pages);
     DecodeOptions o;
     o.precise = true;
     return decode_planned(stream, query, key_cache, value_cache, scale_cache, block_tables,
@@ -2631,7 +2661,7 @@ extern "C" int tq_decode_splitk_static(void* stream, const uint16_t* query, cons
     // Resolve the split count first: it decides how much of the array the launch needs.
     uint32_t chunk_pages = 0;
     splits = resolve_splits(splits, batch, num_kv_heads, block_size, max_blocks, max_context_hint,
-                            &chunk_pages, head_size);
+                            &chunk_pages);
     const size_t need = tq_decode_workspace_floats(batch, num_heads, num_kv_heads, head_size, splits);
     if (need > static_cast<size_t>(TQ_STATIC_WORKSPACE_FLOATS)) return TQ_ERR_WORKSPACE_TOO_SMALL;
     int st = TQ_OK;

@@ -55,7 +55,7 @@ def test_split_choice():
     assert choose(64, 4, 16, 16384) == 8           # ... whatever the number of KV heads
     assert choose(64, 8, 16, 32768) == 8
     assert choose(4096, 8, 16, 32768) == 4         # plenty of sequences: 8192-token pieces
-    assert choose(16, 8, 16, 65536) == 10          # few long sequences: two pieces per CTA slot
+    assert choose(16, 8, 16, 65536) == 14          # few long sequences: three pieces per resident CTA slot
     assert choose(1, 8, 16, 1 << 20) == 32         # one very long sequence: as many as the records allow
     for b in (1, 3, 64, 1000):
         for ctx in (1, 600, 5000, 70000, 1 << 20):
