@@ -278,31 +278,29 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
     // ---- quantise. y * inv is exact (power of two), so one fused multiply-add onto
     // 1.5 * 2^23 + 8 rounds it to nearest-even at integer granularity: the result is
     // 12582912 + u with u = code + 8 in 0..16, and its bit pattern is 0x4B400000 + u;
-    // the upper clamp (code 7, u = 15) is a float min. Biased codes pack by integer
-    // multiply-add with no masks and no borrows; a final xor with 0x88.. turns u back
-    // into the two's-complement nibble.
+    // the upper clamp (code 7, u = 15) is part of the packing of the key page (pack8) and a
+    // float min in the value page, whose bytes pair two tokens; a final xor with 0x88.. turns
+    // u back into the two's-complement nibble.
     constexpr float kMagic = 12582920.0f;           // 1.5 * 2^23 + 8
     constexpr float kMagicTop = 12582927.0f;        // 1.5 * 2^23 + 15
-    constexpr uint32_t kMagicBits = 0x4B400000u;    // bits of 1.5 * 2^23
     const float2 magic2 = f2(kMagic, kMagic);
     __syncwarp();  // the previous panel's copy-out has finished reading the stage
     if (id.plane == 0) {
-        // key page: token-major, row of D/8 words; this thread's word is g*4 + qd.
-        // Horner over e = 7..0: w = sum (K + u_e) 16^e = K * 0x11111111 + packed.
-        constexpr uint32_t kHorner = kMagicBits * 0x11111111u;
+        // key page: token-major, row of D/8 words; this thread's word is g*4 + qd: eight codes
+        // clamped and packed four at a time (pack8)
 #pragma unroll
         for (int tt = 0; tt < 2; ++tt) {
             const float2 inv2 = f2(inv[tt], inv[tt]);
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                uint32_t w = 0;
+                float rounded[8];
 #pragma unroll
-                for (int ep = 3; ep >= 0; --ep) {
+                for (int ep = 0; ep < 4; ++ep) {
                     const float2 rr = __ffma2_rn(y[tt][g][ep], inv2, magic2);
-                    w = w * 16u + __float_as_uint(fminf(rr.y, kMagicTop));
-                    w = w * 16u + __float_as_uint(fminf(rr.x, kMagicTop));
+                    rounded[2 * ep] = rr.x;
+                    rounded[2 * ep + 1] = rr.y;
                 }
-                stage[(2 * r + tt) * (D / 8) + ((g * 4 + qd) ^ (r & 3) * 4)] = (w - kHorner) ^ 0x88888888u;
+                stage[(2 * r + tt) * (D / 8) + ((g * 4 + qd) ^ (r & 3) * 4)] = pack8(rounded);
             }
         }
     } else {

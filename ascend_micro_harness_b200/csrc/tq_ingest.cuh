@@ -32,6 +32,24 @@ struct IngestParams {
     long long wait_budget = kIngestWaitBudget;
 };
 
+// (shared by both aligned writers)
+// Eight packed codes from eight rounded values r_e = 1.5 * 2^23 + u_e (u_e = code + 8 in
+// 0..16: a value that rounds up to code 8 has yet to be clamped to 7), lowest nibble first.
+// The low byte of r_e is u_e. The even and the odd elements are gathered into four bytes
+// each; min(u, 15) = (15 u + 15) >> 4 for u <= 16 and no byte of 15 u + 15 exceeds 255, so
+// one multiply-add clamps four elements at once and leaves them in the high nibbles; the two
+// words interleave into eight nibbles and u -> two's complement flips each nibble's top bit.
+__device__ __forceinline__ uint32_t pack8(const float (&r)[8])
+{
+    const uint32_t e02 = __byte_perm(__float_as_uint(r[0]), __float_as_uint(r[2]), 0x0040);
+    const uint32_t e46 = __byte_perm(__float_as_uint(r[4]), __float_as_uint(r[6]), 0x0040);
+    const uint32_t o13 = __byte_perm(__float_as_uint(r[1]), __float_as_uint(r[3]), 0x0040);
+    const uint32_t o57 = __byte_perm(__float_as_uint(r[5]), __float_as_uint(r[7]), 0x0040);
+    const uint32_t even = __byte_perm(e02, e46, 0x5410), odd = __byte_perm(o13, o57, 0x5410);
+    const uint32_t ye = even * 15u + 0x0F0F0F0Fu, yo = odd * 15u + 0x0F0F0F0Fu;
+    return (((ye >> 4) & 0x0F0F0F0Fu) | (yo & 0xF0F0F0F0u)) ^ 0x88888888u;
+}
+
 // The tcgen05 writer for head size 128 (tq_ingest_umma.cu). `bf16` selects the element type.
 cudaError_t launch_ingest_umma(cudaStream_t stream, const IngestParams& p, bool bf16);
 

@@ -215,23 +215,6 @@ __device__ __forceinline__ TileId tile_of(const IngestParams& p, uint32_t item, 
     return id;
 }
 
-// Eight packed codes from eight rounded values r_e = 1.5 * 2^23 + u_e (u_e = code + 8 in
-// 0..16: a value that rounds up to code 8 has yet to be clamped to 7), lowest nibble first.
-// The low byte of r_e is u_e. The even and the odd elements are gathered into four bytes
-// each; min(u, 15) = (15 u + 15) >> 4 for u <= 16 and no byte of 15 u + 15 exceeds 255, so
-// one multiply-add clamps four elements at once and leaves them in the high nibbles; the two
-// words interleave into eight nibbles and u -> two's complement flips each nibble's top bit.
-__device__ __forceinline__ uint32_t pack8(const float (&r)[8])
-{
-    const uint32_t e02 = __byte_perm(__float_as_uint(r[0]), __float_as_uint(r[2]), 0x0040);
-    const uint32_t e46 = __byte_perm(__float_as_uint(r[4]), __float_as_uint(r[6]), 0x0040);
-    const uint32_t o13 = __byte_perm(__float_as_uint(r[1]), __float_as_uint(r[3]), 0x0040);
-    const uint32_t o57 = __byte_perm(__float_as_uint(r[5]), __float_as_uint(r[7]), 0x0040);
-    const uint32_t even = __byte_perm(e02, e46, 0x5410), odd = __byte_perm(o13, o57, 0x5410);
-    const uint32_t ye = even * 15u + 0x0F0F0F0Fu, yo = odd * 15u + 0x0F0F0F0Fu;
-    return (((ye >> 4) & 0x0F0F0F0Fu) | (yo & 0xF0F0F0F0u)) ^ 0x88888888u;
-}
-
 // All 128 threads of one group (named barrier 1 + group).
 __device__ __forceinline__ void group_sync(int group)
 {
@@ -316,6 +299,7 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
     const uint32_t acc = tmem_group + (static_cast<uint32_t>(warp * 32) << 16);   // this warp's lanes
     const uint32_t mbar_s = smem_addr(mbar), tma_bar_s = smem_addr(mbar + 1);
     const uint32_t x_tile_s = smem_addr(x_tile), m_tile_s = smem_addr(m_tile);
+    const uint64_t desc_x = umma_desc(x_tile_s), desc_m = umma_desc(m_tile_s);
 
     // The group's thread 0 fetches a tile: one box per 128-byte K block, rows = the tile's 128
     // tokens (past the end of the tensor: zeros, never stored), x = the head's first channel.
@@ -373,10 +357,14 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
             }
             if (landed) {
                 fence_after_sync();
+                // descriptors of the K-steps differ from the tile's first one only in the address
+                // field (16-byte units in the low bits, no carry out of it below 256 KiB): one add each
+                // instead of building them anew, which cost the issuing thread most of its time here
+                const uint64_t dx0 = desc_x + ((buf * C::kTileBytes) >> 4);
 #pragma unroll
                 for (int k = 0; k < C::kKSteps; ++k) {
-                    const uint32_t off = (k >> 2) * C::kBlockBytes + (k & 3) * 32;
-                    const uint64_t dx = umma_desc(x_tile_s + buf * C::kTileBytes + off), dm = umma_desc(m_tile_s + off);
+                    const uint32_t off16 = ((k >> 2) * C::kBlockBytes + (k & 3) * 32) >> 4;
+                    const uint64_t dx = dx0 + off16, dm = desc_m + off16;
                     umma<BF16>(tmem_group, transposed ? dm : dx, transposed ? dx : dm, (!BF16 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(mbar_s);
