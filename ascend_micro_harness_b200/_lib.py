@@ -25,6 +25,7 @@ SIGNATURES = {
                                      u32, u32, f32, vp]),
     "tq_decode_splitk": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                    u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
+    "tq_decode_splitk_levels": (C.c_int, [vp] * 12 + [u32] * 12 + [f32, vp]),
     "tq_decode_step": (C.c_int, [vp] * 14 + [u32] * 11 + [f32, f32, vp]),
     "tq_decode_splitk_persistent": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                               u32, u32, u32, u32, u32, u32, f32, f32, vp]),

@@ -2497,6 +2497,53 @@ extern "C" int tq_decode_splitk_prerotated(void* stream, const float* query_rot,
                           output_stage, inv_sqrt_len, softmax_scale, status, o);
 }
 
+// The same decode over native planes whose codes index a 16-level table instead of a uniform
+// grid: the read side of the fused decoder's Lloyd-Max toggle (DecodeUnpack::kLloydMaxLut,
+// kernels/ops/turboquant/fused_decode/common/turboquant_mode.h:181-206,:252-263), whose cache
+// keeps the KV4/FP8 storage (bin b as the signed nibble b - 8) and reconstructs
+// levels16[b] * scale with gain 1. The pools are imported once with tq_nz_kv4_import(gain = 1);
+// the export runs on the table-lookup kernel of the Lloyd-Max variant (a non-uniform codebook
+// has no integer grid for the s8 key path), the merge and the output stages are those of
+// tq_decode_splitk_prerotated. splits 1..16, 0 = the library's choice capped at 16; at most 8
+// query heads per KV head.
+extern "C" int tq_decode_levels_export(void* stream, const float* query_rot, const float* levels16,
+                                       const int8_t* key_cache, const int8_t* value_cache,
+                                       const float* scale_cache, const int32_t* block_tables,
+                                       const int32_t* context_lens, float* workspace, uint32_t batch,
+                                       uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                                       uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                                       uint32_t splits, float softmax_scale, uint32_t* status);
+
+extern "C" int tq_decode_splitk_levels(void* stream, const float* query_rot, const float* levels16,
+                                       const int8_t* key_cache, const int8_t* value_cache,
+                                       const float* scale_cache, const int32_t* block_tables,
+                                       const int32_t* context_lens, const float* pi_signs, const void* gate,
+                                       float* workspace, void* output, uint32_t out_dtype, uint32_t gate_dtype,
+                                       uint32_t batch, uint32_t num_heads, uint32_t num_kv_heads,
+                                       uint32_t head_size, uint32_t block_size, uint32_t num_blocks,
+                                       uint32_t max_blocks, uint32_t splits, uint32_t max_context_hint,
+                                       uint32_t output_stage, float softmax_scale, uint32_t* status)
+{
+    if (!num_kv_heads || !num_heads || num_heads % num_kv_heads != 0 || !block_size || splits > 16u ||
+        output_stage > TQ_OUT_GATED || gate_dtype > TQ_DTYPE_F32 || out_dtype > TQ_DTYPE_F32 ||
+        (output_stage != TQ_OUT_ROTATED && !pi_signs) || (output_stage == TQ_OUT_GATED && !gate) ||
+        (head_size != 128 && head_size != 256) || (batch != 0 && (!output || !workspace)))
+        return TQ_ERR_INVALID_ARGUMENT;
+    if (splits == 0u) {
+        splits = resolve_splits(0, batch, num_kv_heads, block_size, max_blocks, max_context_hint);
+        if (splits > 16u) splits = 16u;
+    }
+    const int st = tq_decode_levels_export(stream, query_rot, levels16, key_cache, value_cache, scale_cache,
+                                           block_tables, context_lens, workspace, batch, num_heads, num_kv_heads,
+                                           head_size, block_size, num_blocks, max_blocks, splits, softmax_scale,
+                                           status);
+    if (st != TQ_OK || batch == 0) return st;
+    const uint32_t rows = num_heads / num_kv_heads;
+    const float inv_sqrt_len = head_size == 128 ? 0.08838834764831845f : 0.0625f;
+    return splitk_combine(stream, workspace, pi_signs, gate, gate_dtype, output, out_dtype, batch * num_kv_heads,
+                          rows, rows, head_size, splits, output_stage, inv_sqrt_len, 1, num_kv_heads, 2u);
+}
+
 // tq_decode_splitk as ONE launch: a persistent grid (one resident wave of CTAs) over the
 // batch's 48-token tiles, flattened sequence by sequence and head by head and cut into chunks
 // by a schedule every CTA can evaluate (85 % of an equal share dealt statically, the rest taken

@@ -182,6 +182,11 @@ struct LmDecodeParams {
     uint32_t items, H, rows, S, P, table_stride, splits;
     float softmax_scale;
     uint32_t* status;
+    // A cache on another 16-level codebook (the fused decoder's Lloyd-Max toggle): the query is
+    // FP32 and already in the cache's basis (q_f32 != null: no rotation), and a stored nibble n
+    // stands for levels[n ^ 8] (bin b is stored as the signed nibble b - 8).
+    const float* q_f32 = nullptr;
+    float levels[16] = {};
 };
 
 constexpr float kLmLog2e = 1.4426950408889634f;
@@ -250,7 +255,7 @@ struct LmDecodeSmem {
 // lane's own bank; both contractions are f16 tensor-core MMAs with tokens as the M
 // dimension. P carries the value scale relative to a running power-of-two normaliser, and
 // the accumulator is rescaled only by strips that raise a row maximum or that normaliser.
-template <int D>
+template <int D, bool WIDE_Q>
 __global__ void __launch_bounds__(128, LmDecodeSmem<D>::kCtasPerSm) tq_lm_decode_kernel(const LmDecodeParams p)
 {
     using L = LmDecodeSmem<D>;
@@ -286,12 +291,22 @@ __global__ void __launch_bounds__(128, LmDecodeSmem<D>::kCtasPerSm) tq_lm_decode
     // byte -> packed (centroid[low nibble], centroid[high nibble]) as f16: the 256 entries
     // first (lane 0's copy), then the other 31 copies
     for (int i = tid; i < 256; i += blockDim.x) {
-        const __half2 h = __floats2half2_rn(lloydmax4_centroid(i & 15), lloydmax4_centroid(i >> 4));
+        const __half2 h = p.q_f32 != nullptr
+                              ? __floats2half2_rn(p.levels[(i & 15) ^ 8], p.levels[(i >> 4) ^ 8])
+                              : __floats2half2_rn(lloydmax4_centroid(i & 15), lloydmax4_centroid(i >> 4));
         lut[i * 32] = *reinterpret_cast<const uint32_t*>(&h);
     }
-    // q_rot: FP32 butterfly inside each 16-channel block, / 4, bf16
+    // q_rot: FP32 butterfly inside each 16-channel block, / 4, bf16 (or the caller's rotated FP32 rows)
     for (int i = tid; i < 8 * (D / 16); i += blockDim.x) {
         const int row = i / (D / 16), blk = i % (D / 16);
+        if (p.q_f32 != nullptr) {
+#pragma unroll
+            for (int k = 0; k < 16; ++k)
+                qs[row][blk * 16 + k] = row < static_cast<int>(p.rows)
+                                            ? p.q_f32[(static_cast<size_t>(item) * p.rows + row) * D + blk * 16 + k]
+                                            : 0.f;
+            continue;
+        }
         float v[16];
 #pragma unroll
         for (int k = 0; k < 16; ++k)
@@ -308,12 +323,22 @@ __global__ void __launch_bounds__(128, LmDecodeSmem<D>::kCtasPerSm) tq_lm_decode
 
     // B fragments of q_rot^T: MMA j of a key row takes this thread's bytes 2j, 2j+1, i.e.
     // channels qd*(D/4) + 4j .. 4j+3
+    // An FP32 query (q_f32) is carried as two f16 halves, hi + lo, so that its rounding to f16
+    // (2^-11 relative, which a bf16 query never sees: it is exact in f16) does not reach the logits.
+    constexpr bool wide_q = WIDE_Q;   // the instantiation an FP32 query gets
     uint32_t bq[D / 16][2];
+    [[maybe_unused]] uint32_t bq_lo[WIDE_Q ? D / 16 : 1][2];
 #pragma unroll
     for (int j = 0; j < D / 16; ++j) {
         const float* qr = &qs[r][qd * (D / 4) + 4 * j];
         bq[j][0] = lm_pack_f16x2(qr[0], qr[1]);
         bq[j][1] = lm_pack_f16x2(qr[2], qr[3]);
+        if constexpr (WIDE_Q) {
+            const __half2 h0 = *reinterpret_cast<const __half2*>(&bq[j][0]),
+                          h1 = *reinterpret_cast<const __half2*>(&bq[j][1]);
+            bq_lo[j][0] = lm_pack_f16x2(qr[0] - __low2float(h0), qr[1] - __high2float(h0));
+            bq_lo[j][1] = lm_pack_f16x2(qr[2] - __low2float(h1), qr[3] - __high2float(h1));
+        }
     }
     __syncthreads();   // the table is complete
 
@@ -376,7 +401,7 @@ __global__ void __launch_bounds__(128, LmDecodeSmem<D>::kCtasPerSm) tq_lm_decode
         const float* scales = reinterpret_cast<const float*>(buf + 2 * kStripBytes);
 
         // ---- scores^T: rows = tokens r and r+8, columns = query rows
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
+        float c[4] = {0.f, 0.f, 0.f, 0.f}, c_lo[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int ch = 0; ch < kChunks; ++ch) {
             const uint4 lo = *reinterpret_cast<const uint4*>(buf + r * (D / 2) + (qd * kChunks + ch) * 16);
@@ -387,9 +412,15 @@ __global__ void __launch_bounds__(128, LmDecodeSmem<D>::kCtasPerSm) tq_lm_decode
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int j = ch * 8 + w * 2 + h;   // bytes 2j, 2j+1 of this thread's part of the row
-                    mma_f16(c, entry(wl[w], 2 * h), entry(wh[w], 2 * h), entry(wl[w], 2 * h + 1),
-                            entry(wh[w], 2 * h + 1), bq[j][0], bq[j][1]);
+                    const uint32_t a0 = entry(wl[w], 2 * h), a1 = entry(wh[w], 2 * h), a2 = entry(wl[w], 2 * h + 1),
+                                   a3 = entry(wh[w], 2 * h + 1);
+                    mma_f16(c, a0, a1, a2, a3, bq[j][0], bq[j][1]);
+                    if constexpr (WIDE_Q) mma_f16(c_lo, a0, a1, a2, a3, bq_lo[j][0], bq_lo[j][1]);
                 }
+        }
+        if constexpr (wide_q) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c[i] += c_lo[i];
         }
         const uint32_t tok_lo = strip * kStrip + r, tok_hi = tok_lo + 8;
         const bool live_lo = tok_lo < ctx, live_hi = tok_hi < ctx;
@@ -499,7 +530,7 @@ __global__ void __launch_bounds__(128, LmDecodeSmem<D>::kCtasPerSm) tq_lm_decode
     }
 }
 
-template <int D>
+template <int D, bool WIDE_Q = false>
 static cudaError_t launch_lm_decode(cudaStream_t stream, const LmDecodeParams& p, unsigned grid)
 {
     // Opt in to the large dynamic shared-memory carve-out once per device.
@@ -507,13 +538,13 @@ static cudaError_t launch_lm_decode(cudaStream_t stream, const LmDecodeParams& p
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return cudaErrorNoDevice;
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(tq_lm_decode_kernel<D>,
+        const cudaError_t e = cudaFuncSetAttribute(tq_lm_decode_kernel<D, WIDE_Q>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    LmDecodeSmem<D>::kTotal);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    tq_lm_decode_kernel<D><<<grid, 128, LmDecodeSmem<D>::kTotal, stream>>>(p);
+    tq_lm_decode_kernel<D, WIDE_Q><<<grid, 128, LmDecodeSmem<D>::kTotal, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -552,6 +583,46 @@ extern "C" int tq_reshape_and_cache_lloydmax(void* stream, const void* key, cons
     if (head_size == 128) tq_lm_writer_kernel<128><<<blocks, 128, 0, s>>>(p);
     else tq_lm_writer_kernel<256><<<blocks, 128, 0, s>>>(p);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
+}
+
+// The split-K export over native planes whose codes index a caller's 16-level table (levels by
+// bin index; nibble n is bin n ^ 8), with a pre-rotated FP32 query [batch][num_heads][d]: the
+// read side of the fused decoder's Lloyd-Max toggle after tq_nz_kv4_import with gain 1.
+extern "C" int tq_decode_levels_export(void* stream, const float* query_rot, const float* levels16,
+                                       const int8_t* key_cache, const int8_t* value_cache,
+                                       const float* scale_cache, const int32_t* block_tables,
+                                       const int32_t* context_lens, float* workspace, uint32_t batch,
+                                       uint32_t num_heads, uint32_t num_kv_heads, uint32_t head_size,
+                                       uint32_t block_size, uint32_t num_blocks, uint32_t max_blocks,
+                                       uint32_t splits, float softmax_scale, uint32_t* status)
+{
+    if (!num_heads || !num_kv_heads || num_heads % num_kv_heads != 0 || !block_size ||
+        block_size % kStrip != 0 || !num_blocks || !max_blocks || !splits || splits > 16 ||
+        (head_size != 128 && head_size != 256) || num_heads / num_kv_heads > 8 || !levels16 ||
+        !(softmax_scale > 0.0f) || !(softmax_scale <= 3.0e38f))
+        return TQ_ERR_INVALID_ARGUMENT;
+    if (batch == 0) return TQ_OK;
+    if (!query_rot || !key_cache || !value_cache || !scale_cache || !block_tables || !context_lens || !workspace)
+        return TQ_ERR_INVALID_ARGUMENT;
+    const uintptr_t align = reinterpret_cast<uintptr_t>(key_cache) | reinterpret_cast<uintptr_t>(value_cache) |
+                            reinterpret_cast<uintptr_t>(scale_cache);
+    if (align & 15u) return TQ_ERR_INVALID_ARGUMENT;
+    LmDecodeParams p{nullptr, reinterpret_cast<const uint8_t*>(key_cache),
+                     reinterpret_cast<const uint8_t*>(value_cache), scale_cache, block_tables, context_lens,
+                     workspace, batch * num_kv_heads, num_kv_heads, num_heads / num_kv_heads, block_size,
+                     num_blocks, max_blocks, splits, softmax_scale, status};
+    p.q_f32 = query_rot;
+    for (int i = 0; i < 16; ++i) {
+        if (!(levels16[i] == levels16[i]) || levels16[i] > 60000.0f || levels16[i] < -60000.0f)
+            return TQ_ERR_INVALID_ARGUMENT;   // the table is carried in f16
+        p.levels[i] = levels16[i];
+    }
+    const uint64_t grid = static_cast<uint64_t>(p.items) * splits;
+    if (grid > 0x7FFFFFFFull) return TQ_ERR_INVALID_ARGUMENT;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const cudaError_t e = head_size == 128 ? launch_lm_decode<128, true>(s, p, static_cast<unsigned>(grid))
+                                           : launch_lm_decode<256, true>(s, p, static_cast<unsigned>(grid));
+    return e == cudaSuccess ? TQ_OK : TQ_ERR_LAUNCH;
 }
 
 extern "C" int tq_decode_lloydmax_export(void* stream, const uint16_t* query, const int8_t* key_cache,

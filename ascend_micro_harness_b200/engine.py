@@ -2,6 +2,8 @@
 memory and streams only; every computation happens in libtq_b200.so."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from ._lib import TqError, load_library
@@ -383,6 +385,32 @@ def decode_splitk_prerotated(query_rot, key_cache, value_cache, scale_cache, blo
             batch, num_heads, num_kv_heads, head_size, block_size, num_blocks, block_tables.shape[-1], splits,
             max_context_hint, code_grid, output_stage, softmax_scale, _ptr(status)),
             "tq_decode_splitk_prerotated")
+
+
+def decode_splitk_levels(query_rot, levels, key_cache, value_cache, scale_cache, block_tables, context_lens, output,
+                         *, num_heads, num_kv_heads, head_size, block_size, num_blocks, softmax_scale=1.0, splits=0,
+                         max_context_hint=0, workspace=None, pi_signs=None, gate=None, output_stage=OUT_ROTATED,
+                         status=None, stream=None):
+    """Decode over native planes whose codes index a 16-level table (the fused decoder's Lloyd-Max toggle after
+    nz_kv4_import with gain 1): `levels` is a host sequence of 16 floats by bin index, query_rot float32 in the
+    cache's basis. Output stages as decode_splitk_prerotated; at most 16 splits and 8 query heads per KV head."""
+    lib = load_library()
+    lv = (ctypes.c_float * 16)(*[float(x) for x in levels])
+    call = _Call("decode_splitk_levels").take("query_rot", query_rot, _F32)
+    _decode_operands(call, key_cache, value_cache, scale_cache, block_tables, context_lens, pi_signs, output,
+                     gate, status, gate_dtypes=_ANYF, signs_optional=True)
+    batch = query_rot.numel() // (num_heads * head_size)
+    need = decode_workspace_floats(batch, num_heads, num_kv_heads, head_size, splits if splits else 16)
+    if workspace is None or workspace.numel() < need:
+        raise ValueError(f"decode_splitk_levels: workspace of {need} floats needed")
+    call.take("workspace", workspace, _F32)
+    with call:
+        _check(lib.tq_decode_splitk_levels(
+            _stream(stream, call.device), _ptr(query_rot), ctypes.cast(lv, ctypes.c_void_p), _ptr(key_cache),
+            _ptr(value_cache), _ptr(scale_cache), _ptr(block_tables), _ptr(context_lens), _ptr(pi_signs), _ptr(gate),
+            _ptr(workspace), _ptr(output), _out_dtype(output), _out_dtype(gate) if gate is not None else 2, batch,
+            num_heads, num_kv_heads, head_size, block_size, num_blocks, block_tables.shape[-1], splits,
+            max_context_hint, output_stage, softmax_scale, _ptr(status)), "tq_decode_splitk_levels")
 
 
 def decode_splitk_nz(query_rot, nz_key, nz_value, nz_scales, block_tables, context_lens, output, *, num_heads,

@@ -318,6 +318,15 @@ def run_ours(args):
             if not args.no_extra:
                 line["cpu_baseline"]["reshape"] = cpu_baseline_reshape()
         print(json.dumps(line))
+        if args.csv:
+            # the samples behind step_us / decode_kernel_us, one row per timed step (the reference's
+            # benchmarks write the same kind of file)
+            with open(args.csv, "w") as f:
+                f.write("sample,step_us,decode_kernel_us\n")
+                ks = res["kernel_samples_ms"]
+                for i, t in enumerate(res["step_samples_ms"]):
+                    k = f"{ks[i] * 1e3:.3f}" if i < len(ks) else ""
+                    f.write(f"{i},{t * 1e3:.3f},{k}\n")
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -502,6 +511,7 @@ def fused_step_bench(torch, tq, dev, dist, ctx, seed, steps, warmup, verify, e2e
         fail(f"device status word {int(status.item())}")
     return {"clocks": clocks, "ms_step": ms_total / steps, "ms_e2e": ms_e2e, "kernel_ms": statistics.median(kernel_samples),
             "step_stats": summary(step_samples), "kernel_stats": summary(kernel_samples),
+            "step_samples_ms": list(step_samples), "kernel_samples_ms": list(kernel_samples),
             "bytes": kv_bytes(ctx1), "splits": int(splits), "verified": verified, "issue": issue,
             "e2e_issue": e2e_issue, "h2d": int(host_in.numel()), "d2h": int(hout.numel() * hout.element_size())}
 
@@ -1105,6 +1115,7 @@ def main():
                          "long: 128 sequences of 65536 tokens in the whole job (strong scaling)")
     ap.add_argument("--no-extra", action="store_true", help="skip the side measurements of `extra`")
     ap.add_argument("--no-verify", action="store_true", help="skip the oracle check before timing")
+    ap.add_argument("--csv", default=None, help="also write the per-step device-event samples to this CSV file")
     ap.add_argument("--side", default=None,
                     help="comma-separated names of `extra` cases: time only these and print them (one GPU)")
     ap.add_argument("--profile", default=None,

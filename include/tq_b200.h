@@ -392,6 +392,25 @@ int tq_decode_splitk_prerotated(void* stream, const float* query_rot, const int8
                                 uint32_t splits, uint32_t max_context_hint, uint32_t code_grid,
                                 uint32_t output_stage, float softmax_scale, uint32_t* status);
 
+/* The fused decoder's KV4/FP8 cache written on its Lloyd-Max codebook (DecodeUnpack::kLloydMaxLut,
+ * kernels/ops/turboquant/fused_decode/common/turboquant_mode.h:181-206,:252-263): same storage (bin b
+ * as the signed nibble b - 8), value = levels16[b] * scale, gain 1. Import the pools once with
+ * tq_nz_kv4_import(gain = 1), then decode with this entry: query_rot FP32 [batch][num_heads][d] in the
+ * cache's basis, levels16 a HOST array of 16 floats by bin index (the reference's table:
+ * -2.75 -2 -1.625 -1.25 -0.9375 -0.6875 -0.375 -0.125 and their mirror images), output stages as in
+ * tq_decode_splitk_prerotated. splits 1..16 (0 = the library's choice, at most 16); at most 8 query heads per
+ * KV head; workspace tq_decode_workspace_floats(batch, num_heads, num_kv_heads, d, 16). Runs on the
+ * table-lookup kernel of the Lloyd-Max variant (about a third of the uniform grid's rate). */
+int tq_decode_splitk_levels(void* stream, const float* query_rot, const float* levels16,
+                            const int8_t* key_cache, const int8_t* value_cache, const float* scale_cache,
+                            const int32_t* block_tables, const int32_t* context_lens,
+                            const float* pi_signs, const void* gate, float* workspace, void* output,
+                            uint32_t out_dtype, uint32_t gate_dtype, uint32_t batch, uint32_t num_heads,
+                            uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                            uint32_t num_blocks, uint32_t max_blocks, uint32_t splits,
+                            uint32_t max_context_hint, uint32_t output_stage, float softmax_scale,
+                            uint32_t* status);
+
 /* The same decode over the NZ-tiled pools themselves: no import, no second pool. nz_key,
  * nz_value and nz_scales are the fused decoder's buffers as described above (head size 256,
  * block_size 64 or 128); each stored scale is divided by `gain` on the way in, exactly as

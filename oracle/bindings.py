@@ -297,6 +297,26 @@ class Oracle:
         return out
 
 
+    def kv4_lloydmax_lut(self):
+        out = np.zeros(16, np.float32)
+        self.lib.tqo_kv4_lloydmax_lut(_p(out))
+        return out
+
+    def nz_kv4_decode_lut(self, q_rot, nz_key, nz_value, nz_scales, block_tables, context_lens, Hq, H, S,
+                          softmax_scale=0.0625, levels=None):
+        """nz_kv4_decode over a cache written on the Lloyd-Max codebook (levels by bin index, gain 1)."""
+        q = _c(q_rot, np.float32)
+        B = q.size // (Hq * 256)
+        bt = _c(block_tables, np.int32).reshape(B, -1)
+        lv = _c(self.kv4_lloydmax_lut() if levels is None else levels, np.float32)
+        out = np.zeros((B, Hq, 256), np.float32)
+        self.lib.tqo_nz_kv4_decode_lut(_p(q), _p(_c(nz_key, np.uint8)), _p(_c(nz_value, np.uint8)),
+                                       _p(_c(nz_scales, np.float32)), _p(bt),
+                                       _p(_c(context_lens, np.int32)), C.c_int(B), C.c_int(Hq), C.c_int(H),
+                                       C.c_int(S), C.c_int(bt.shape[1]), C.c_float(softmax_scale), _p(lv), _p(out))
+        return out
+
+
 class Reference:
     """The reference project's own golden models (oracle/_ref/libtq_ref.so)."""
 
@@ -409,6 +429,12 @@ class Reference:
         arrs = [np.zeros((6, 256), np.float32) for _ in range(4)]
         self.lib.ref_single_token_golden(C.c_int(head), C.c_int(pages), _p(m), _p(l), *[_p(a) for a in arrs])
         return dict(m=m, l=l, acc=arrs[0], rotated=arrs[1], context=arrs[2], q_rot=arrs[3])
+
+    def kv4_lloydmax_lut(self):
+        """(levels[16], thresholds[15], gain) of TurboQuantLloydMaxTraits<KV4_FP8>."""
+        levels, thr, gain = np.zeros(16, np.float32), np.zeros(15, np.float32), np.zeros(1, np.float32)
+        self.lib.ref_kv4_lloydmax_lut(_p(levels), _p(thr), _p(gain))
+        return levels, thr, float(gain[0])
 
     def fused_descriptor_layout_matches(self):
         return bool(self.lib.ref_fused_descriptor_layout_matches())

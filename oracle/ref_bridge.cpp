@@ -380,6 +380,15 @@ void ref_fused_gate_bits(void* p, std::uint16_t* out)
     const auto g = f.gate_logits();
     std::memcpy(out, g.data(), g.size() * 2);
 }
+// The e4m3-rounded Lloyd-Max codebook the fused decoder's KV4/FP8 mode can be switched to
+// (turboquant_mode.h:181-206): levels by bin index, the midpoint thresholds, the gain (1).
+void ref_kv4_lloydmax_lut(float* levels16, float* thresholds15, float* gain)
+{
+    using T = vllm_ascend::turboquant::TurboQuantLloydMaxTraits<vllm_ascend::turboquant::TurboQuantMode::KV4_FP8>;
+    for (int i = 0; i < T::kLevels; ++i) levels16[i] = T::kCentroids[i];
+    for (int i = 0; i < T::kThresholdCount; ++i) thresholds15[i] = T::kThresholds[i];
+    *gain = T::kGain;
+}
 float ref_kv4_gain() { return vllm_ascend::turboquant::TurboQuantModeTraits<vllm_ascend::turboquant::TurboQuantMode::KV4_FP8>::kGain; }
 std::uint64_t ref_nz_tiled_packed_byte(std::uint64_t slot, std::uint64_t head, std::uint64_t column,
                                        std::uint64_t H, std::uint64_t packed)

@@ -995,12 +995,56 @@ void tqo_signed_hadamard(int d, const float* signs, const float* x, float* y, in
 // [B][Hq][256] (the fused decoder's `queryRot`), output in the rotated basis, FP32
 // (the scalar FP64 sum of tests/common/fused_decode_opt_fixture.hpp:300-312, for arbitrary
 // cache contents). Scales enter as the FP32 quotient scale / gain, as in the import above.
+// `levels` (16 floats, or null): the value a stored nibble stands for. Null is the uniform
+// mid-rise grid (nibble n as a signed 4-bit number + 0.5); the fused decoder's Lloyd-Max toggle
+// keeps the storage (bin b stored as the signed nibble b - 8) and reconstructs levels[b]
+// (kernels/ops/turboquant/fused_decode/common/turboquant_codec_mx.h:61-72), gain 1.
+static void nz_kv4_decode_levels(const float* q_rot, const std::uint8_t* nz_key, const std::uint8_t* nz_value,
+                                 const float* nz_scales, const std::int32_t* block_tables,
+                                 const std::int32_t* context_lens, int B, int Hq, int H, int S, int max_blocks,
+                                 float softmax_scale, float gain, const float* levels, float* out);
+
 void tqo_nz_kv4_decode(const float* q_rot, const std::uint8_t* nz_key, const std::uint8_t* nz_value,
                        const float* nz_scales, const std::int32_t* block_tables,
                        const std::int32_t* context_lens, int B, int Hq, int H, int S, int max_blocks,
                        float softmax_scale, float gain, float* out)
 {
+    nz_kv4_decode_levels(q_rot, nz_key, nz_value, nz_scales, block_tables, context_lens, B, Hq, H, S, max_blocks,
+                         softmax_scale, gain, nullptr, out);
+}
+
+// The e4m3-rounded 16-level Lloyd-Max table of the fused decoder's KV4/FP8 mode
+// (kernels/ops/turboquant/fused_decode/common/turboquant_mode.h:191-197): Max's table for
+// N(0,1), each entry rounded to the nearest fp8 e4m3 value; odd, ascending with the bin index.
+void tqo_kv4_lloydmax_lut(float* levels16)
+{
+    static const float half[8] = {0.125f, 0.375f, 0.6875f, 0.9375f, 1.25f, 1.625f, 2.0f, 2.75f};
+    for (int i = 0; i < 8; ++i) {
+        levels16[8 + i] = half[i];
+        levels16[7 - i] = -half[i];
+    }
+}
+
+// The same decode over a cache written on the Lloyd-Max codebook: levels by bin index, gain 1.
+void tqo_nz_kv4_decode_lut(const float* q_rot, const std::uint8_t* nz_key, const std::uint8_t* nz_value,
+                           const float* nz_scales, const std::int32_t* block_tables,
+                           const std::int32_t* context_lens, int B, int Hq, int H, int S, int max_blocks,
+                           float softmax_scale, const float* levels16, float* out)
+{
+    nz_kv4_decode_levels(q_rot, nz_key, nz_value, nz_scales, block_tables, context_lens, B, Hq, H, S, max_blocks,
+                         softmax_scale, 1.0f, levels16, out);
+}
+
+static void nz_kv4_decode_levels(const float* q_rot, const std::uint8_t* nz_key, const std::uint8_t* nz_value,
+                                 const float* nz_scales, const std::int32_t* block_tables,
+                                 const std::int32_t* context_lens, int B, int Hq, int H, int S, int max_blocks,
+                                 float softmax_scale, float gain, const float* levels, float* out)
+{
     constexpr int d = 256, packed = 128;
+    // nibble n -> its value: the signed nibble + 0.5, or the level of bin b = n ^ 8 (n is b - 8 in four bits)
+    auto value_of = [&](unsigned n) {
+        return levels ? static_cast<double>(levels[(n ^ 8u) & 15u]) : s4(n) + 0.5;
+    };
     const int G = Hq / H, slot_floats = (2 * H + 7) / 8 * 8;
     for (int b = 0; b < B; ++b)
         for (int qh = 0; qh < Hq; ++qh) {
@@ -1022,8 +1066,8 @@ void tqo_nz_kv4_decode(const float* q_rot, const std::uint8_t* nz_key, const std
                 double dot = 0.0;
                 for (int col = 0; col < packed; ++col) {
                     const unsigned byte = kp[nz_tiled_packed_byte(t % S, head, col, H, packed)];
-                    dot += static_cast<double>(q[col]) * (s4(byte & 15u) + 0.5) +
-                           static_cast<double>(q[col + packed]) * (s4(byte >> 4) + 0.5);
+                    dot += static_cast<double>(q[col]) * value_of(byte & 15u) +
+                           static_cast<double>(q[col + packed]) * value_of(byte >> 4);
                 }
                 score[t] = dot * scale_of(t, 0) * static_cast<double>(softmax_scale);
                 m = std::max(m, score[t]);
@@ -1035,8 +1079,8 @@ void tqo_nz_kv4_decode(const float* q_rot, const std::uint8_t* nz_key, const std
                 const std::uint8_t* vp = plane_base(nz_value, t);
                 for (int col = 0; col < packed; ++col) {
                     const unsigned byte = vp[nz_tiled_packed_byte(t % S, head, col, H, packed)];
-                    acc[col] += p * vs * (s4(byte & 15u) + 0.5);
-                    acc[col + packed] += p * vs * (s4(byte >> 4) + 0.5);
+                    acc[col] += p * vs * value_of(byte & 15u);
+                    acc[col + packed] += p * vs * value_of(byte >> 4);
                 }
             }
             for (int c = 0; c < d; ++c) o[c] = ctx > 0 ? static_cast<float>(acc[c] / l) : 0.0f;

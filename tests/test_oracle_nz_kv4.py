@@ -98,3 +98,30 @@ def test_pi_against_the_live_reference(oracle, reference):
     for _ in range(5):
         x = rng.standard_normal(256).astype(np.float32)
         assert np.array_equal(oracle.signed_hadamard(x[None], s)[0], reference.fused_pi_apply(x))
+
+
+def test_lloydmax_lut_table_is_the_reference_header_s(oracle, reference):
+    """The 16 levels of the fused decoder's Lloyd-Max toggle, bit for bit as
+    TurboQuantLloydMaxTraits<KV4_FP8> holds them; its thresholds are the midpoints and its gain is 1."""
+    levels, thresholds, gain = reference.kv4_lloydmax_lut()
+    ours = oracle.kv4_lloydmax_lut()
+    assert np.array_equal(levels.view(np.uint32), ours.view(np.uint32))
+    assert np.array_equal(thresholds, ((ours[1:].astype(np.float64) + ours[:-1]) / 2).astype(np.float32))
+    assert gain == 1.0
+    assert np.array_equal(ours, -ours[::-1]) and (np.diff(ours) > 0).all()
+
+
+def test_levels_oracle_with_the_uniform_grid_is_the_mid_rise_oracle(oracle):
+    """Levels (b - 7.5) at gain 1 must give exactly what the mid-rise decode gives: the two differ only in
+    how a nibble becomes a value."""
+    rng = np.random.default_rng(5)
+    H, S, Hq = 2, 64, 4
+    ctx = np.array([130, 9], np.int32)
+    P = 5
+    table = np.array([[4, 1, 0], [2, 0, 0]], np.int32)
+    key, value, scales = nz_random_cache(rng, P, H, S)
+    q = rng.standard_normal((2, Hq, 256)).astype(np.float32)
+    a = oracle.nz_kv4_decode(q, key, value, scales, table, ctx, Hq, H, S, softmax_scale=0.07, gain=1.0)
+    b = oracle.nz_kv4_decode_lut(q, key, value, scales, table, ctx, Hq, H, S, softmax_scale=0.07,
+                                 levels=np.arange(16, dtype=np.float32) - 7.5)
+    assert np.array_equal(a, b)
