@@ -316,3 +316,41 @@ def test_reference_aic_fixture_tails(cuda, oracle, reference, dead, fill):
     for splits in (1, 2, 4):
         ws, qrot = run_partials(cuda, fx, splits, 0, pages, fx["seq_len"], table_bf16)
         check_partials(oracle, fx, ws, qrot, splits, 0, pages)
+
+
+@pytest.mark.parametrize("d,Hkv,G", [(128, 8, 4), (256, 4, 4)])
+@pytest.mark.parametrize("hint", ["exact", "too_small", "far_too_large", "none"])
+def test_the_library_s_own_plan_under_any_hint(cuda, oracle, d, Hkv, G, hint):
+    """splits = 0: the launcher cuts every sequence at launch-constant page offsets derived from the
+    caller's max_context_hint, graded by head size. The hint is only a hint: whatever it says, every token of
+    every sequence must be read exactly once: a hint that is too small leaves the last piece to take the rest,
+    one that is far too large leaves all but the first piece empty. Contexts of many lengths around page and
+    piece boundaries, next to empty and one-token sequences."""
+    import torch
+    import ascend_micro_harness_b200 as tq
+    rng = np.random.default_rng(d + len(hint))
+    S, Hq = 16, Hkv * G
+    ctx = [1536, 1535, 1, 0, 345, 346, 344, 691, 1008, 1200, 17, 768, 769, 1537 - 1, 256, 1296]
+    cache = hp.build_cache_from_gaussian(oracle, rng, ctx, Hkv, d, S)
+    B = len(ctx)
+    q = hp.bf16_from_f32(rng.standard_normal((B, Hq, d)).astype(np.float32))
+    want = oracle_decode(oracle, q, cache, Hq, Hkv, d, S, softmax_scale=0.1)
+    max_blocks = cache["block_tables"].shape[1]
+    h = {"exact": max(ctx), "too_small": 300, "far_too_large": 1 << 20, "none": 0}[hint]
+    plan_ctx = h if h else max_blocks * S
+    n = tq.choose_splits(B, Hkv, S, plan_ctx)
+    assert n >= 2 or hint == "too_small"
+    ws = torch.full((tq.decode_workspace_floats(B, Hq, Hkv, d, n),), float("nan"), device=cuda)
+    out = torch.full((B, Hq, d), float("nan"), dtype=torch.float32, device=cuda)
+    st = torch.zeros(1, dtype=torch.int32, device=cuda)
+    tq.decode_splitk(dev(cuda, q), dev(cuda, cache["key_cache"]), dev(cuda, cache["value_cache"]),
+                     dev(cuda, cache["scale_cache"]), dev(cuda, cache["block_tables"]),
+                     dev(cuda, cache["context_lens"]), dev(cuda, cache["signs"].astype(np.float32)), out,
+                     num_heads=Hq, num_kv_heads=Hkv, head_size=d, block_size=S, num_blocks=cache["num_blocks"],
+                     inv_sqrt_len=hp.inv_sqrt_len(d), softmax_scale=0.1, splits=0, max_context_hint=h,
+                     workspace=ws, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    assert_close(got, want)
