@@ -33,6 +33,8 @@
 // memory and returns.
 #include <cuda.h>   // CUtensorMap and the encode entry point's signature; nothing is linked from libcuda
 
+#include <type_traits>
+
 #include "tq_ingest.cuh"
 
 namespace tq {
@@ -404,21 +406,24 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
     }
     int32_t slot = -1;
 
-#pragma unroll 1
-    for (uint32_t unit = 0; item < items; ++unit, item += (unit & 1u) ? 0u : item_step) {
-        const TileId id = tile_of(p, item, unit & 1u);
+    // One plane of one item; the plane is a compile-time tag, so that an item is a straight run
+    // of key-plane code and value-plane code with one loop turn per item (a turn of this long
+    // loop costs the group some hundreds of cycles). Returns false once a wait has run out.
+    auto do_plane = [&](auto plane_tag) -> bool {
+        constexpr uint32_t kPlane = decltype(plane_tag)::value;
+        const TileId id = tile_of(p, item, kPlane);
         // ---- this thread's token of the tile: its slot is requested before anything waits
         const uint32_t tok = id.tok_tile * kTileTokens + tid;
         const bool tok_live = tok < num_tokens;
-        if (id.plane == 0) {   // a volatile load: it must not sink below the product's wait
+        if constexpr (kPlane == 0) {   // a volatile load: it must not sink below the product's wait
             slot = -1;
             if (tok_live) asm volatile("ld.global.nc.s32 %0, [%1];\n" : "=r"(slot) : "l"(p.slots + tok));
         }
 
-        product(false, true, buffer_of(id.plane));
+        product(false, true, buffer_of(kPlane));
         // the tile is consumed: with one buffer the item's value tile takes its place, with two
         // the next item's key tile does (the value tile stays for the transposed product)
-        if (id.plane == 0) {
+        if constexpr (kPlane == 0) {
             if (C::kTileBufs == 1) load_tile(item, 1);
             else if (item + item_step < items) load_tile(item + item_step, 0);
         }
@@ -463,7 +468,7 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
             tmem_ld32(acc + 96, vb);
             fold(va);
             tmem_arrived(vb);
-            if (id.plane == 0) tmem_ld32(acc + 0, va);   // first chunk of pass 2
+            if constexpr (kPlane == 0) tmem_ld32(acc + 0, va);   // first chunk of pass 2
             fold(vb);
             amax = fmaxf(hi0, hi1);
         } else {
@@ -483,7 +488,7 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
             tmem_ld32_low16(acc + 64, vb);
             fold(va);
             tmem_arrived(vb);
-            if (id.plane == 0) tmem_ld32(acc + 0, va);   // first chunk of pass 2
+            if constexpr (kPlane == 0) tmem_ld32(acc + 0, va);   // first chunk of pass 2
             fold(vb);
             const uint32_t hi = __vmaxs2(hi0, hi1), lo = __vmins2(lo0, lo1);
             const int top = max(static_cast<int>(static_cast<int16_t>(hi & 0xFFFFu)),
@@ -499,10 +504,10 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         // extra 1.5 * 2^23, taken off again here (all terms are integers below 2^26: exact)
         const float addend = BF16 ? kMagic : kMagic - kBias * inv;
         if (strip_ok && healthy)
-            p.scale_cache[((static_cast<size_t>(id.plane) * p.P + page) * p.H + id.head) * p.S +
+            p.scale_cache[((static_cast<size_t>(kPlane) * p.P + page) * p.H + id.head) * p.S +
                           tok_in_page + (lane & 15)] = __int_as_float(pow_bits) * p.inv_sqrt_len;
 
-        if (id.plane == 0) {
+        if constexpr (kPlane == 0) {
             // ---- key page: the token's row, 32 channels (16 bytes) per tensor-memory read
             uint4* dst = reinterpret_cast<uint4*>(p.key_cache + block_off + static_cast<size_t>(lane & 15) * 64u);
             const float2 inv2 = make_float2(inv, inv), add2 = make_float2(addend, addend);
@@ -605,7 +610,12 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         // group's next products overwrite them
         fence_before_sync();
         group_sync(group);
-        if (*abort_flag != 0u) break;
+        return *abort_flag == 0u;
+    };
+#pragma unroll 1
+    for (; item < items; item += item_step) {
+        if (!do_plane(std::integral_constant<uint32_t, 0>{})) break;
+        if (!do_plane(std::integral_constant<uint32_t, 1>{})) break;
     }
     // After a wait ran out (here or in the other group) a tile fetch or a product chain may
     // still be on its way into this CTA's shared and tensor memory: thread 0 gives each the
