@@ -128,6 +128,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity)
     return ok != 0;
 }
 
+// A wait on a barrier phase for at most `budget` clock cycles; a budget of zero gives up
+// without looking, and a raised abort flag (when one is watched) ends the wait early: the awaited
+// work may then never have been issued. (Out of line it cost 4 %: the calls sit in the hot loop.)
+__device__ __forceinline__ bool bounded_mbar_wait(uint32_t bar, uint32_t par, long long budget,
+                                               const volatile uint32_t* abort_flag)
+{
+    if (budget <= 0) return false;
+    bool done = mbar_try_wait(bar, par);
+    if (!done) {
+        const long long t0 = clock64();
+        do {
+            done = mbar_try_wait(bar, par);
+        } while (!done && clock64() - t0 < budget && !(abort_flag != nullptr && *abort_flag != 0u));
+    }
+    return done;
+}
+
 #define TQ_W8(v, o) "=r"(v[o]), "=r"(v[o + 1]), "=r"(v[o + 2]), "=r"(v[o + 3]), "=r"(v[o + 4]), \
                     "=r"(v[o + 5]), "=r"(v[o + 6]), "=r"(v[o + 7])
 #define TQ_RW8(v, o) "+r"(v[o]), "+r"(v[o + 1]), "+r"(v[o + 2]), "+r"(v[o + 3]), "+r"(v[o + 4]), \
@@ -327,20 +344,8 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         tma_pending |= 1u << buf;
     };
 
-    // A wait on a barrier phase for at most `budget` clock cycles; a budget of zero gives up
-    // without looking, and a raised abort flag ends the wait early (the awaited work may then
-    // never have been issued).
     auto bounded_wait = [&](uint32_t bar, uint32_t par, long long budget, bool watch_abort) {
-        if (budget <= 0) return false;
-        bool done = mbar_try_wait(bar, par);
-        if (!done) {
-            const long long t0 = clock64();
-            do {
-                done = mbar_try_wait(bar, par);
-            } while (!done && clock64() - t0 < budget &&
-                     !(watch_abort && *abort_flag != 0u));
-        }
-        return done;
+        return bounded_mbar_wait(bar, par, budget, watch_abort ? abort_flag : nullptr);
     };
     // One product into the accumulator columns, then the bounded wait for it.
     // transposed = false: D[token][channel] = X M^T; true: D'[channel][token] = M X^T.
@@ -405,6 +410,9 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         if (C::kTileBufs == 2) load_tile(item, 1);
     }
     int32_t slot = -1;
+    bool strip_ok = false;
+    uint32_t page = 0, tok_in_page = 0;
+    size_t block_off = 0;
 
     // One plane of one item; the plane is a compile-time tag, so that an item is a straight run
     // of key-plane code and value-plane code with one loop turn per item (a turn of this long
@@ -428,21 +436,25 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
             else if (item + item_step < items) load_tile(item + item_step, 0);
         }
 
-        const int32_t slot0 = __shfl_sync(0xffffffffu, slot, lane & 16);
-        const bool run_ok = slot == slot0 + (lane & 15);
-        const uint32_t votes = __ballot_sync(0xffffffffu, run_ok);
-        const bool strip_live = __shfl_sync(0xffffffffu, tok_live ? 1 : 0, lane & 16) != 0;
-        // page = slot0 / S by the precomputed multiplier: a hardware-free division costs this
-        // thread hundreds of cycles per tile
-        const uint32_t slot_page = fast_div(static_cast<uint32_t>(slot0), p.page_mul, p.page_shift);
-        const bool strip_ok = strip_live && ((votes >> (lane & 16)) & 0xFFFFu) == 0xFFFFu && slot0 >= 0 &&
-                              (slot0 % kStrip) == 0 && slot_page < p.P;
-        if (strip_live && !strip_ok && (lane & 15) == 0) report(p.status, TQ_STATUS_BAD_SLOT);
-        const uint32_t page = strip_ok ? slot_page : 0u;
-        const uint32_t tok_in_page = strip_ok ? static_cast<uint32_t>(slot0) - slot_page * p.S : 0u;
-        // byte offset of the strip's (page, head) block in either code plane
-        const size_t block_off = (static_cast<size_t>(page) * p.H + id.head) * (static_cast<size_t>(p.S) * 64u) +
-                                 static_cast<size_t>(tok_in_page / kStrip) * 1024u;
+        // Where the strip goes is the same for both planes of an item: worked out in the key
+        // plane (a bad strip is reported once), kept for the value plane.
+        if constexpr (kPlane == 0) {
+            const int32_t slot0 = __shfl_sync(0xffffffffu, slot, lane & 16);
+            const bool run_ok = slot == slot0 + (lane & 15);
+            const uint32_t votes = __ballot_sync(0xffffffffu, run_ok);
+            const bool strip_live = __shfl_sync(0xffffffffu, tok_live ? 1 : 0, lane & 16) != 0;
+            // page = slot0 / S by the precomputed multiplier: a hardware-free division costs this
+            // thread hundreds of cycles per tile
+            const uint32_t slot_page = fast_div(static_cast<uint32_t>(slot0), p.page_mul, p.page_shift);
+            strip_ok = strip_live && ((votes >> (lane & 16)) & 0xFFFFu) == 0xFFFFu && slot0 >= 0 &&
+                       (slot0 % kStrip) == 0 && slot_page < p.P;
+            if (strip_live && !strip_ok && (lane & 15) == 0) report(p.status, TQ_STATUS_BAD_SLOT);
+            page = strip_ok ? slot_page : 0u;
+            tok_in_page = strip_ok ? static_cast<uint32_t>(slot0) - slot_page * p.S : 0u;
+            // byte offset of the strip's (page, head) block in either code plane
+            block_off = (static_cast<size_t>(page) * p.H + id.head) * (static_cast<size_t>(p.S) * 64u) +
+                        static_cast<size_t>(tok_in_page / kStrip) * 1024u;
+        }
 
         // ---- pass 1 over D[token][.]: absmax of the token, its power-of-two scale.
         // Tensor-memory reads run one 32-column chunk ahead of the arithmetic.
