@@ -410,21 +410,23 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         if (C::kTileBufs == 2) load_tile(item, 1);
     }
     int32_t slot = -1;
-    bool strip_ok = false;
-    uint32_t page = 0, tok_in_page = 0;
-    size_t block_off = 0;
+    bool strip_ok = false, tok_live = false;
+    uint32_t page = 0, tok_in_page = 0, head = 0;
+    size_t block_off = 0, scale_at = 0;
+    const size_t plane_scales = static_cast<size_t>(p.P) * p.H * p.S;
 
     // One plane of one item; the plane is a compile-time tag, so that an item is a straight run
     // of key-plane code and value-plane code with one loop turn per item (a turn of this long
     // loop costs the group some hundreds of cycles). Returns false once a wait has run out.
     auto do_plane = [&](auto plane_tag) -> bool {
         constexpr uint32_t kPlane = decltype(plane_tag)::value;
-        const TileId id = tile_of(p, item, kPlane);
         // ---- this thread's token of the tile: its slot is requested before anything waits
-        const uint32_t tok = id.tok_tile * kTileTokens + tid;
-        const bool tok_live = tok < num_tokens;
-        if constexpr (kPlane == 0) {   // a volatile load: it must not sink below the product's wait
-            slot = -1;
+        if constexpr (kPlane == 0) {
+            const TileId id = tile_of(p, item, 0);
+            const uint32_t tok = id.tok_tile * kTileTokens + tid;
+            head = id.head;
+            tok_live = tok < num_tokens;
+            slot = -1;   // a volatile load: it must not sink below the product's wait
             if (tok_live) asm volatile("ld.global.nc.s32 %0, [%1];\n" : "=r"(slot) : "l"(p.slots + tok));
         }
 
@@ -452,8 +454,10 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
             page = strip_ok ? slot_page : 0u;
             tok_in_page = strip_ok ? static_cast<uint32_t>(slot0) - slot_page * p.S : 0u;
             // byte offset of the strip's (page, head) block in either code plane
-            block_off = (static_cast<size_t>(page) * p.H + id.head) * (static_cast<size_t>(p.S) * 64u) +
+            block_off = (static_cast<size_t>(page) * p.H + head) * (static_cast<size_t>(p.S) * 64u) +
                         static_cast<size_t>(tok_in_page / kStrip) * 1024u;
+            // this thread's scale of the key plane; the value plane's lies P * H * S floats on
+            scale_at = (static_cast<size_t>(page) * p.H + head) * p.S + tok_in_page + (lane & 15);
         }
 
         // ---- pass 1 over D[token][.]: absmax of the token, its power-of-two scale.
@@ -516,8 +520,7 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         // extra 1.5 * 2^23, taken off again here (all terms are integers below 2^26: exact)
         const float addend = BF16 ? kMagic : kMagic - kBias * inv;
         if (strip_ok && healthy)
-            p.scale_cache[((static_cast<size_t>(kPlane) * p.P + page) * p.H + id.head) * p.S +
-                          tok_in_page + (lane & 15)] = __int_as_float(pow_bits) * p.inv_sqrt_len;
+            p.scale_cache[scale_at + (kPlane ? plane_scales : 0)] = __int_as_float(pow_bits) * p.inv_sqrt_len;
 
         if constexpr (kPlane == 0) {
             // ---- key page: the token's row, 32 channels (16 bytes) per tensor-memory read
