@@ -47,6 +47,11 @@ constexpr int kIngestCtasPerSm = D == 128 ? 4 : TQ_D256_INGEST_CTAS;
 // that the four positions a warp reads at once sit in different banks.
 template <int D>
 constexpr int kSignPitchOf = D / 4 + 2;
+// Bytes of the per-CTA table behind the warps' stages. bf16: the sign diagonal as floats per quad
+// position. int8: the +-1 MMA operands of H32 with the group's signs folded into their columns,
+// [group][half][lane] x 16 bytes.
+template <int D, bool BF16>
+constexpr int kTableBytes = BF16 ? 4 * kSignPitchOf<D> * 4 : (D / kGroup) * 2 * 32 * 16;
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src)
 {
@@ -159,7 +164,7 @@ __device__ __forceinline__ float max3_abs(float a, float b, float c)
 template <int D, bool BF16, bool VARLEN>
 __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t chunk, int lane,
                                               const uint8_t* in, int32_t slot,
-                                              const uint32_t (&bfrag)[BF16 ? 16 : 8],
+                                              const uint32_t (&bfrag)[16],
                                               const float* sgn_s, uint32_t* stage)
 {
     constexpr int G = D / kGroup;
@@ -189,21 +194,24 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
     float2 y[2][G][4];
     if constexpr (!BF16) {
         // The INT32 accumulator starts at the bit pattern of 1.5 * 2^23, so what comes
-        // out, read as a float, is 12582912 + sum exactly; one FP32 subtract recovers
-        // the sum without an integer-to-float conversion.
+        // out, read as a float, is 12582912 + sum exactly; the first butterfly below takes
+        // the offset out again. The operands carry the sign diagonal already (a column of
+        // the +-1 operand is an output channel), so y is s . (H32 x) up to that offset.
         constexpr int kBias = 0x4B400000;
-        const float2 unbias = f2(-12582912.0f, -12582912.0f);
+        const uint4* bsg = reinterpret_cast<const uint4*>(sgn_s);
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             const uint2 lo = *reinterpret_cast<const uint2*>(in + ((g * 2 + 0) * 32 + lane) * kPiece);
             const uint2 hi = *reinterpret_cast<const uint2*>(in + ((g * 2 + 1) * 32 + lane) * kPiece);
             const uint32_t a[4] = {lo.x, hi.x, lo.y, hi.y};
+            const uint4 b01 = bsg[(g * 2 + 0) * 32 + lane], b23 = bsg[(g * 2 + 1) * 32 + lane];
+            const uint32_t bw[8] = {b01.x, b01.y, b01.z, b01.w, b23.x, b23.y, b23.z, b23.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 int c[4] = {kBias, kBias, kBias, kBias};
-                mma_s8_16832(c, a, bfrag[j * 2 + 0], bfrag[j * 2 + 1]);
-                y[0][g][j] = __fadd2_rn(f2(__int_as_float(c[0]), __int_as_float(c[1])), unbias);
-                y[1][g][j] = __fadd2_rn(f2(__int_as_float(c[2]), __int_as_float(c[3])), unbias);
+                mma_s8_16832(c, a, bw[j * 2 + 0], bw[j * 2 + 1]);
+                y[0][g][j] = f2(__int_as_float(c[0]), __int_as_float(c[1]));
+                y[1][g][j] = f2(__int_as_float(c[2]), __int_as_float(c[3]));
             }
         }
     } else {
@@ -222,25 +230,35 @@ __device__ __forceinline__ void process_panel(const IngestParams& p, uint32_t ch
         }
     }
 
-    // ---- sign diagonal folded into the first stage of the outer factor H_G, then
-    // the remaining stages, on packed pairs. All multiplies are by +-1: exact.
+    // ---- the outer factor H_G on packed pairs. bf16: the sign diagonal is folded into its first
+    // stage (multiplies by +-1: exact). int8: the inputs are B + a and B + b with B = 1.5 * 2^23;
+    // b - 2B = b' - B, a + (b' - B) = a' + b' and a - b = a' - b' are all exact in FP32.
     const float2 minus1 = f2(-1.0f, -1.0f);
+    const float2 minus2bias = f2(-25165824.0f, -25165824.0f);
     float amax[2] = {1.0f, 1.0f};  // the writer floors absmax at 1
 #pragma unroll
     for (int ep = 0; ep < 4; ++ep) {
         float2 sg[G];
+        if constexpr (BF16) {
 #pragma unroll
-        for (int g = 0; g < G; ++g)
-            sg[g] = *reinterpret_cast<const float2*>(sgn_s + qd * kSignPitch + g * 8 + ep * 2);
+            for (int g = 0; g < G; ++g)
+                sg[g] = *reinterpret_cast<const float2*>(sgn_s + qd * kSignPitch + g * 8 + ep * 2);
+        }
 #pragma unroll
         for (int tt = 0; tt < 2; ++tt) {
             float2 x[G];
 #pragma unroll
             for (int g = 0; g < G; g += 2) {
-                const float2 a = __fmul2_rn(sg[g], y[tt][g][ep]);
-                const float2 b = __fmul2_rn(sg[g + 1], y[tt][g + 1][ep]);
-                x[g] = __fadd2_rn(a, b);
-                x[g + 1] = __ffma2_rn(b, minus1, a);
+                if constexpr (BF16) {
+                    const float2 a = __fmul2_rn(sg[g], y[tt][g][ep]);
+                    const float2 b = __fmul2_rn(sg[g + 1], y[tt][g + 1][ep]);
+                    x[g] = __fadd2_rn(a, b);
+                    x[g + 1] = __ffma2_rn(b, minus1, a);
+                } else {
+                    const float2 a = y[tt][g][ep], b = y[tt][g + 1][ep];
+                    x[g] = __fadd2_rn(a, __fadd2_rn(b, minus2bias));
+                    x[g + 1] = __ffma2_rn(b, minus1, a);
+                }
             }
 #pragma unroll
             for (int s = 2; s < G; s <<= 1)
@@ -374,39 +392,47 @@ tq_ingest_kernel(const IngestParams p)
     constexpr int kPageWords = kStrip * D / 8;
     constexpr int kInBytes = kStrip * D * (BF16 ? 2 : 1);   // one panel of activations
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    // per warp: two input stages, one output stage; then the sign table
+    // per warp: two input stages, one output stage; then the CTA's table (kTableBytes)
     uint8_t* warp_base = smem_raw + (threadIdx.x >> 5) * (2 * kInBytes + kPageWords * 4);
     float* sgn_s = reinterpret_cast<float*>(smem_raw + kIngestWarps * (2 * kInBytes + kPageWords * 4));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, qd = lane & 3;
 
-    // sign diagonal per quad position: sgn_s[qd][g*8 + e] for channel g*32 + qd*8 + e
-    for (int i = threadIdx.x; i < 4 * G * 8; i += blockDim.x) {
-        const int q = i / (G * 8), k = i % (G * 8);
-        sgn_s[q * kSignPitchOf<D> + k] =
-            sign_is_negative(p.signs, p.sign_source, (k / 8) * kGroup + q * 8 + (k % 8)) ? -1.0f : 1.0f;
-    }
-
-    // +-1 B fragments of H32, once per thread. Column n of tile j is output channel
-    // c0 = (n/2)*8 + j*2 + n%2, so a thread ends up with 8 consecutive channels.
-    uint32_t bfrag[BF16 ? 16 : 8];
+    // +-1 B fragments of H32. Column n of tile j is output channel c0 = (n/2)*8 + j*2 + n%2 of
+    // its group, so a thread ends up with 8 consecutive channels.
+    uint32_t bfrag[16] = {};
     if constexpr (!BF16) {
         // contraction slot k of the low half is input channel (k/4)*8 + k%4, of the
-        // high half (k/4)*8 + 4 + k%4 -- the order the 8-byte pieces deliver.
+        // high half (k/4)*8 + 4 + k%4 -- the order the 8-byte pieces deliver. A fragment word is
+        // one column of the operand: negating it (0x01 <-> 0xFF, xor 0xFE per byte) applies the
+        // sign of that output channel, so the table holds every group's operands ready signed.
+        uint4* bsg = reinterpret_cast<uint4*>(sgn_s);
+        for (int g = warp; g < G; g += kIngestWarps) {
+            uint32_t w8[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const unsigned c0 = (r >> 1) * 8 + j * 2 + (r & 1);
+            for (int j = 0; j < 4; ++j) {
+                const unsigned c0 = (r >> 1) * 8 + j * 2 + (r & 1);
+                const uint32_t flip = sign_is_negative(p.signs, p.sign_source, g * kGroup + c0) ? 0xFEFEFEFEu : 0u;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t w = 0;
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t w = 0;
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    w |= (hneg(c0, qd * 8 + h * 4 + e) ? 0xFFu : 0x01u) << (8 * e);
-                bfrag[j * 2 + h] = w;
+                    for (int e = 0; e < 4; ++e)
+                        w |= (hneg(c0, qd * 8 + h * 4 + e) ? 0xFFu : 0x01u) << (8 * e);
+                    w8[j * 2 + h] = w ^ flip;
+                }
             }
+            bsg[(g * 2 + 0) * 32 + lane] = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+            bsg[(g * 2 + 1) * 32 + lane] = make_uint4(w8[4], w8[5], w8[6], w8[7]);
         }
     } else {
+        // sign diagonal per quad position: sgn_s[qd][g*8 + e] for channel g*32 + qd*8 + e
+        for (int i = threadIdx.x; i < 4 * G * 8; i += blockDim.x) {
+            const int q = i / (G * 8), k = i % (G * 8);
+            sgn_s[q * kSignPitchOf<D> + k] =
+                sign_is_negative(p.signs, p.sign_source, (k / 8) * kGroup + q * 8 + (k % 8)) ? -1.0f : 1.0f;
+        }
         // Two k16 steps per group; step s slot qd'*2+e <-> channel qd'*8 + 4s + e,
         // slot 8+qd'*2+e <-> channel qd'*8 + 4s + 2 + e.
 #pragma unroll
@@ -449,7 +475,7 @@ template <int D, bool BF16, bool VARLEN = false>
 static cudaError_t launch_ingest(cudaStream_t stream, const IngestParams& p)
 {
     constexpr int kInBytes = kStrip * D * (BF16 ? 2 : 1);
-    constexpr int kSmem = kIngestWarps * (2 * kInBytes + kStrip * D / 2) + 4 * kSignPitchOf<D> * 4;
+    constexpr int kSmem = kIngestWarps * (2 * kInBytes + kStrip * D / 2) + kTableBytes<D, BF16>;
     uint32_t blocks = (p.chunks + kIngestWarps - 1) / kIngestWarps;
     if (blocks == 0) return cudaSuccess;
     int dev = 0, sms = 148;
