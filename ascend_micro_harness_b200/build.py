@@ -11,7 +11,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libtq_b200.so")
 ACL_LIB = os.path.join(PKG, "libtq_acl_shim.so")
 
-CUDA_SOURCES = ["tq_ingest.cu", "tq_ingest_umma.cu", "tq_scatter.cu", "tq_decode.cu", "tq_routines.cu",
+CUDA_SOURCES = ["tq_ingest.cu", "tq_ingest_umma.cu", "tq_ingest_umma256.cu", "tq_scatter.cu", "tq_decode.cu", "tq_routines.cu",
                 "tq_lm.cu", "tq_nz.cu"]
 HOST_SOURCES = ["tq_reference_abi.cpp"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

@@ -557,6 +557,7 @@ static int reshape_and_cache(void* stream, const void* key, const void* value,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t err = cudaErrorNotSupported;
     if (head_size == 128 && !warp_mma_only) err = launch_ingest_umma(s, p, in_dtype == TQ_IN_BF16);
+    if (head_size == 256 && !warp_mma_only) err = launch_ingest_umma256(s, p, in_dtype == TQ_IN_BF16);
     if (err == cudaErrorNotSupported) {
         // head size 256, the explicit warp-MMA entry, or a driver without tensor maps
         if (head_size == 128)

@@ -52,5 +52,7 @@ __device__ __forceinline__ uint32_t pack8(const float (&r)[8])
 
 // The tcgen05 writer for head size 128 (tq_ingest_umma.cu). `bf16` selects the element type.
 cudaError_t launch_ingest_umma(cudaStream_t stream, const IngestParams& p, bool bf16);
+// The tcgen05 writer for head size 256 (tq_ingest_umma256.cu).
+cudaError_t launch_ingest_umma256(cudaStream_t stream, const IngestParams& p, bool bf16);
 
 }  // namespace tq
