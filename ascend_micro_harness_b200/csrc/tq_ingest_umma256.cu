@@ -28,12 +28,12 @@ namespace tq {
 namespace {
 
 constexpr int kTileTokens = 128;
-constexpr int kGroups = 2;                   // independent groups per CTA, one tile each
-constexpr int kGroupThreads = 256;           // eight warps
-constexpr int kThreads = kGroups * kGroupThreads;
+constexpr int kEpiWarps = 16;                // warp w: lane quarter w & 3 (rows), column quarter w >> 2
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = kEpiThreads + 32;   // + the warp whose first lane fetches tiles and issues products
 constexpr uint32_t kAccCols = 128;           // one 128 x 128 accumulator
-constexpr uint32_t kGroupCols = 2 * kAccCols;   // a, then b
-constexpr uint32_t kTmemCols = kGroups * kGroupCols;
+constexpr uint32_t kSetCols = 2 * kAccCols;  // a, then b
+constexpr uint32_t kTmemCols = 2 * kSetCols; // two sets: one is read out while the other is written
 
 template <bool BF16>
 struct Cfg {
@@ -44,9 +44,10 @@ struct Cfg {
     static constexpr int kHalfBytes = kBlocksHalf * kBlockBytes;   // x_lo, x_hi, M_0, M_1: each this size
     static constexpr int kTileBytes = 2 * kHalfBytes;
     static constexpr int kKSteps = kHalfRowBytes / 32;       // one MMA contracts 32 bytes of K
-    // per group: 128 inverse scales, 2 x 128 absmax halves, 8 strip offsets, 2 barriers
-    static constexpr int kSmallBytes = 3 * kTileTokens * 4 + 8 * 8 + 64;
-    static constexpr int kUsed = 2 * kHalfBytes + kGroups * (kTileBytes + kSmallBytes) + 64;
+    static constexpr int kTileBufs = 2;                      // 0: the key tile, 1: the value tile
+    // 128 inverse scales, 2 x 4 x 128 absmax quarters, 8 strip offsets, 8 barriers
+    static constexpr int kSmallBytes = 9 * kTileTokens * 4 + 8 * 8 + 8 * 8;
+    static constexpr int kUsed = 2 * kHalfBytes + kTileBufs * kTileBytes + kSmallBytes + 64;
     static constexpr int kSmem = kUsed + 1024;               // slack for aligning the tiles
 };
 
@@ -98,22 +99,30 @@ __device__ __forceinline__ TileId tile_of(const IngestParams& p, uint32_t item)
     return id;
 }
 
-// All 256 threads of one group (named barrier 1 + group).
-__device__ __forceinline__ void group_sync(int group)
+// All 512 epilogue threads (named barrier 1); the producer warp takes no part.
+__device__ __forceinline__ void epi_sync()
 {
-    asm volatile("bar.sync %0, %1;\n" ::"r"(group + 1), "r"(kGroupThreads) : "memory");
+    asm volatile("bar.sync 1, %0;\n" ::"r"(kEpiThreads) : "memory");
 }
-
-// The same barrier carrying a vote: true for every thread of the group if any of them says so.
-// The decision to leave the item loop must be one decision per group, or the next barrier hangs.
-__device__ __forceinline__ bool group_sync_any(int group, bool mine)
+// The same barrier carrying a vote: true for every epilogue thread if any of them says so. The
+// decision to leave the item loop must be one decision for all of them, or the next barrier hangs.
+__device__ __forceinline__ bool epi_sync_any(bool mine)
 {
     uint32_t any;
     asm volatile(
-        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %3, 0;\n\t"
-        "bar.red.or.pred q, %1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
-        : "=r"(any) : "r"(group + 1), "r"(kGroupThreads), "r"(mine ? 1u : 0u) : "memory");
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %2, 0;\n\t"
+        "bar.red.or.pred q, 1, %1, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+        : "=r"(any) : "r"(kEpiThreads), "r"(mine ? 1u : 0u) : "memory");
     return any != 0u;
+}
+// The four warps that share a lane quarter, i.e. the same 32 rows (named barrier 2 + quarter).
+__device__ __forceinline__ void rows_sync(int quarter)
+{
+    asm volatile("bar.sync %0, 128;\n" ::"r"(quarter + 2) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(mbar) : "memory");
 }
 
 template <bool BF16>
@@ -125,19 +134,20 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
     extern __shared__ uint8_t smem_raw[];
     // tiles on a 1024-byte boundary: the swizzle is a function of address bits 4..9
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
-    const int group = threadIdx.x / kGroupThreads, tid = threadIdx.x % kGroupThreads;
-    const int warp = tid >> 5, lane = tid & 31;
-    const int quarter = warp & 3, half = warp >> 2;   // tensor-memory lane quarter, column half
-    const int row = quarter * 32 + lane;              // token (plain products) or channel (swapped)
-    uint8_t* m_tiles = base;                          // M_0, then M_1
-    uint8_t* x_tile = base + 2 * C::kHalfBytes + group * C::kTileBytes;   // x_lo blocks, then x_hi blocks
-    uint8_t* small = base + 2 * C::kHalfBytes + kGroups * C::kTileBytes + group * C::kSmallBytes;
-    float* inv_s = reinterpret_cast<float*>(small);   // per token: 2^(2-e)
-    float* amax_s = inv_s + kTileTokens;              // [2][128]: each column half's absmax of the row
-    unsigned long long* strip_off = reinterpret_cast<unsigned long long*>(small + 3 * kTileTokens * 4);  // [8]
-    uint64_t* mbar = reinterpret_cast<uint64_t*>(strip_off + 8);   // [0]: products done, [1]: tile landed
-    uint32_t* shared_words = reinterpret_cast<uint32_t*>(base + 2 * C::kHalfBytes + kGroups * C::kTileBytes +
-                                                         kGroups * C::kSmallBytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool producer = warp == kEpiWarps;
+    const int quarter = warp & 3, cq = (warp >> 2) & 3;   // tensor-memory lane quarter, column quarter
+    const int row = quarter * 32 + lane;                  // token (plain products) or channel (swapped)
+    uint8_t* m_tiles = base;                              // M_0, then M_1
+    uint8_t* x_tiles = base + 2 * C::kHalfBytes;          // per buffer: x_lo blocks, then x_hi blocks
+    uint8_t* small = x_tiles + C::kTileBufs * C::kTileBytes;
+    float* inv_s = reinterpret_cast<float*>(small);       // per token: 2^(2-e)
+    float* amax_s = inv_s + kTileTokens;                  // [2 planes][4 quarters][128]
+    unsigned long long* strip_off = reinterpret_cast<unsigned long long*>(small + 9 * kTileTokens * 4);  // [8]
+    // [0..1]: tile buffer landed, [2..3]: tile buffer consumed, [4..5]: accumulator set written,
+    // [6..7]: accumulator set read out
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(strip_off + 8);
+    uint32_t* shared_words = reinterpret_cast<uint32_t*>(mbar + 8);
     uint32_t* tmem_slot = shared_words;
     volatile uint32_t* abort_flag = shared_words + 1;
 
@@ -145,18 +155,21 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
     const uint32_t num_tokens = p.num_strips * kStrip;
 
     // ---- one-time set-up: barriers, tensor memory, the two rotation matrices
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(mbar)));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(mbar + 1)));
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < 6; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(mbar + i)));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(mbar + 6)), "r"(kEpiWarps));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(mbar + 7)), "r"(kEpiWarps));
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        if (group == 0) *abort_flag = 0u;
+        *abort_flag = 0u;
     }
-    if (threadIdx.x < 32) {
+    if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
                      ::"r"(smem_addr(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
-    {
+    if (!producer) {
         // Row r of M_h: output channel c1*32 + c0 against input channel g*32 + i (both inside the
         // half) is H4[c1][g] * s[128 h + g*32 + c0] * H32[c0][i]; true = -1. Thread t writes half a
         // row: row t & 127 of matrix t >> 8, chunk half (t >> 7) & 1.
@@ -184,8 +197,8 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                 }
                 w[j] = word;
             }
-            const int blk = q >> 3, cq = q & 7;
-            *reinterpret_cast<uint4*>(m_tile + blk * C::kBlockBytes + r * 128 + ((cq ^ (r & 7)) << 4)) =
+            const int blk = q >> 3, cq16 = q & 7;
+            *reinterpret_cast<uint4*>(m_tile + blk * C::kBlockBytes + r * 128 + ((cq16 ^ (r & 7)) << 4)) =
                 make_uint4(w[0], w[1], w[2], w[3]);
         }
     }
@@ -194,349 +207,376 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_group = tmem_base + static_cast<uint32_t>(group) * kGroupCols;
-    // this thread's 64 columns of accumulator a; b lies kAccCols further on
-    const uint32_t acc = tmem_group + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half) * 64u;
-    const uint32_t mbar_s = smem_addr(mbar), tma_bar_s = smem_addr(mbar + 1);
-    const uint32_t x_tile_s = smem_addr(x_tile), m_tiles_s = smem_addr(m_tiles);
-    const uint64_t desc_x = umma_desc(x_tile_s), desc_m = umma_desc(m_tiles_s);
-
-    // Thread 0 of the group keeps the books of what it has in flight towards this CTA's shared and
-    // tensor memory; nothing new is issued once a wait has run out.
-    uint32_t parity = 0, tma_parity = 0, mma_pending_parity = 0;
-    bool healthy = true, mma_pending = false, tma_pending = false;
-    auto load_tile = [&](uint32_t item, uint32_t plane) {
-        if (tid != 0 || !healthy) return;
-        const TileId id = tile_of(p, item);
-        const CUtensorMap* map = plane == 0 ? &key_map : &value_map;
-        mbar_expect_tx(tma_bar_s, C::kTileBytes);
+    // this thread's 32 columns of accumulator a in set 0; b lies kAccCols further on, set 1 kSetCols
+    const uint32_t acc0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(cq) * 32u;
+    if constexpr (!BF16) {
+        // INT32 accumulators start at the bit pattern of 1.5 * 2^23: set once here, before the first
+        // product may be issued, and again, chunk by chunk, by whoever reads a product for the last time
+        if (!producer) {
 #pragma unroll
-        for (int blk = 0; blk < 2 * C::kBlocksHalf; ++blk)
-            tma_load_2d(x_tile_s + blk * C::kBlockBytes, map,
-                        static_cast<int>(id.head * 256u + blk * (128 / C::kElem)),
-                        static_cast<int>(id.tok_tile * kTileTokens), tma_bar_s);
-        tma_pending = true;
-    };
-
-    auto bounded_wait = [&](uint32_t bar, uint32_t par, long long budget, bool watch_abort) {
-        return bounded_mbar_wait(bar, par, budget, watch_abort ? abort_flag : nullptr);
-    };
-    // The two products a and b into the group's accumulators, then the bounded wait for them.
-    // transposed = false: D[token][channel] = X_h M_h^T; true: D'[channel][token] = M_h X_h^T.
-    auto product = [&](bool transposed, bool fresh_tile) {
-        if constexpr (!BF16) tmem_wait_st();   // the refill of the columns (see refill) is in place
+            for (int st = 0; st < 2; ++st)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    tmem_fill16(acc0 + st * kSetCols + c * 16, kBiasBits);
+                    tmem_fill16(acc0 + st * kSetCols + kAccCols + c * 16, kBiasBits);
+                }
+            tmem_wait_st();
+        }
         fence_before_sync();
-        group_sync(group);
-        if (tid == 0 && healthy) {
-            bool landed = true;
-            if (fresh_tile) {
-                landed = bounded_wait(tma_bar_s, tma_parity, p.wait_budget, false);
-                if (landed) {
-                    tma_pending = false;
-                    tma_parity ^= 1u;
-                }
-            }
-            if (landed) {
-                fence_after_sync();
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint64_t dx0 = desc_x + ((h * C::kHalfBytes) >> 4), dm0 = desc_m + ((h * C::kHalfBytes) >> 4);
-#pragma unroll
-                    for (int k = 0; k < C::kKSteps; ++k) {
-                        const uint32_t off16 = ((k >> 2) * C::kBlockBytes + (k & 3) * 32) >> 4;
-                        const uint64_t dx = dx0 + off16, dm = dm0 + off16;
-                        umma<BF16>(tmem_group + h * kAccCols, transposed ? dm : dx, transposed ? dx : dm,
-                                   (!BF16 || k > 0) ? 1u : 0u);
-                    }
-                }
-                umma_commit(mbar_s);
-                mma_pending = true;
-                mma_pending_parity = parity;
-            } else {
-                healthy = false;
-                *abort_flag = 1u;
-            }
-        }
-        const bool done = healthy && bounded_wait(mbar_s, parity, p.wait_budget, true);
-        if (done && tid == 0) mma_pending = false;
-        if (!done || *abort_flag != 0u) {
-            healthy = false;
-            *abort_flag = 1u;
-            report(p.status, TQ_STATUS_WAIT_EXPIRED);
-        }
-        parity ^= 1u;
+        __syncthreads();
         fence_after_sync();
-    };
+    }
+    const uint32_t bar_s = smem_addr(mbar);
+    auto bar_of = [&](int i) { return bar_s + 8u * static_cast<uint32_t>(i); };
+    const uint32_t item_step = gridDim.x;
 
-    // INT32 accumulators start at the bit pattern of 1.5 * 2^23: set once here and again, chunk by
-    // chunk, by whoever reads a product for the last time.
-    auto refill = [&](uint32_t col) {
-        if constexpr (!BF16) {
-            tmem_fill16(acc + col, kBiasBits);
-            tmem_fill16(acc + kAccCols + col, kBiasBits);
-        }
-    };
-#pragma unroll
-    for (int c = 0; c < 4; ++c) refill(c * 16);
-
-    const uint32_t item_step = gridDim.x * kGroups;
-    uint32_t item = blockIdx.x * kGroups + group;
-    if (item < items) load_tile(item, 0);
-    int32_t slot = -1;
-    bool strip_ok = false, tok_live = false;
-    uint32_t head = 0;
-    size_t block_off = 0, scale_at = 0;
-    const size_t plane_scales = static_cast<size_t>(p.P) * p.H * p.S;
-    const float2 minus1 = make_float2(-1.0f, -1.0f), minus2bias = make_float2(-2.0f * kBias, -2.0f * kBias);
-
-    // y_lo and y_hi of two adjacent columns out of the raw accumulator words. int8: a' = B + a and
-    // b' = B + b with B = 1.5 * 2^23; b' - 2B, a' + (b' - 2B) and a' - b' are all exact in FP32.
-    auto combine = [&](uint32_t a0, uint32_t a1, uint32_t b0, uint32_t b1, float2& lo, float2& hi) {
-        const float2 a = make_float2(__uint_as_float(a0), __uint_as_float(a1));
-        const float2 b = make_float2(__uint_as_float(b0), __uint_as_float(b1));
-        if constexpr (BF16) lo = __fadd2_rn(a, b);
-        else lo = __fadd2_rn(a, __fadd2_rn(b, minus2bias));
-        hi = __ffma2_rn(b, minus1, a);
-    };
-
-    auto do_plane = [&](auto plane_tag) -> bool {
-        constexpr uint32_t kPlane = decltype(plane_tag)::value;
-        if constexpr (kPlane == 0) {
-            const TileId id = tile_of(p, item);
-            const uint32_t tok = id.tok_tile * kTileTokens + row;
-            head = id.head;
-            tok_live = tok < num_tokens;
-            slot = -1;   // a volatile load: it must not sink below the product's wait
-            if (tok_live) asm volatile("ld.global.nc.s32 %0, [%1];\n" : "=r"(slot) : "l"(p.slots + tok));
-        }
-
-        product(false, true);
-        // the tile is consumed: the item's value tile takes its place
-        if constexpr (kPlane == 0) load_tile(item, 1);
-
-        if constexpr (kPlane == 0) {
-            const int32_t slot0 = __shfl_sync(0xffffffffu, slot, lane & 16);
-            const bool run_ok = slot == slot0 + (lane & 15);
-            const uint32_t votes = __ballot_sync(0xffffffffu, run_ok);
-            const bool strip_live = __shfl_sync(0xffffffffu, tok_live ? 1 : 0, lane & 16) != 0;
-            const uint32_t slot_page = fast_div(static_cast<uint32_t>(slot0), p.page_mul, p.page_shift);
-            strip_ok = strip_live && ((votes >> (lane & 16)) & 0xFFFFu) == 0xFFFFu && slot0 >= 0 &&
-                       (slot0 % kStrip) == 0 && slot_page < p.P;
-            if (strip_live && !strip_ok && (lane & 15) == 0 && half == 0) report(p.status, TQ_STATUS_BAD_SLOT);
-            const uint32_t page = strip_ok ? slot_page : 0u;
-            const uint32_t tok_in_page = strip_ok ? static_cast<uint32_t>(slot0) - slot_page * p.S : 0u;
-            // byte offset of the strip's (page, head) block in either code plane
-            block_off = (static_cast<size_t>(page) * p.H + head) * (static_cast<size_t>(p.S) * 128u) +
-                        static_cast<size_t>(tok_in_page / kStrip) * 2048u;
-            scale_at = (static_cast<size_t>(page) * p.H + head) * p.S + tok_in_page + (lane & 15);
-        }
-
-        // ---- pass 1 over this thread's 64 columns of D[token][.]: absmax of y_lo and y_hi there
-        uint32_t a0[16], b0[16], a1[16], b1[16];
-        float amax;
-        if constexpr (BF16) {
-            float m0 = 0.0f, m1 = 0.0f;
-            auto fold = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16]) {
-#pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                    float2 lo, hi;
-                    combine(va[j], va[j + 1], vb[j], vb[j + 1], lo, hi);
-                    m0 = max3f(m0, fabsf(lo.x), fabsf(lo.y));
-                    m1 = max3f(m1, fabsf(hi.x), fabsf(hi.y));
+    if (producer) {
+        // ---- lane 0: tile fetches and products. Product n writes accumulator set n & 1; the order
+        // per item is key, value, value swapped. A tile buffer is fetched again as soon as the last
+        // product reading it has completed; an accumulator set is written again as soon as the
+        // epilogue warps have read it out.
+        if (lane == 0) {
+            const uint32_t x_tiles_s = smem_addr(x_tiles);
+            const uint64_t desc_x = umma_desc(x_tiles_s), desc_m = umma_desc(smem_addr(m_tiles));
+            uint32_t n = 0, landed_par = 0, consumed_par = 0, pending = 0, commits = 0;   // bit b: buffer b's state
+            bool healthy = true;
+            auto wait = [&](uint32_t bar, uint32_t par) {
+                if (!healthy) return;
+                if (!bounded_mbar_wait(bar, par, p.wait_budget, abort_flag)) {
+                    healthy = false;
+                    *abort_flag = 1u;
+                    report(p.status, TQ_STATUS_WAIT_EXPIRED);
                 }
             };
-            tmem_ld16(acc + 0, a0);
-            tmem_ld16(acc + kAccCols + 0, b0);
-            tmem_arrived2(a0, b0);
-            tmem_ld16(acc + 16, a1);
-            tmem_ld16(acc + kAccCols + 16, b1);
-            fold(a0, b0);
-            tmem_arrived2(a1, b1);
-            tmem_ld16(acc + 32, a0);
-            tmem_ld16(acc + kAccCols + 32, b0);
-            fold(a1, b1);
-            tmem_arrived2(a0, b0);
-            tmem_ld16(acc + 48, a1);
-            tmem_ld16(acc + kAccCols + 48, b1);
-            fold(a0, b0);
-            tmem_arrived2(a1, b1);
-            fold(a1, b1);
-            amax = fmaxf(m0, m1);
-        } else {
-            // the sums a and b as signed 16-bit pairs, 32 columns per read. a + b can reach +32768 only
-            // as exactly that value, which wraps to -32768 and still reads as 32768 below.
-            uint32_t top2 = 0x80008000u, bottom2 = 0x7FFF7FFFu;
-            auto fold = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16]) {
+            auto fetch = [&](uint32_t item, uint32_t buf) {
+                if (!healthy) return;
+                const TileId id = tile_of(p, item);
+                const CUtensorMap* map = buf == 0 ? &key_map : &value_map;
+                const uint32_t bar = bar_of(buf), dst = x_tiles_s + buf * C::kTileBytes;
+                mbar_expect_tx(bar, C::kTileBytes);
+#pragma unroll
+                for (int blk = 0; blk < 2 * C::kBlocksHalf; ++blk)
+                    tma_load_2d(dst + blk * C::kBlockBytes, map,
+                                static_cast<int>(id.head * 256u + blk * (128 / C::kElem)),
+                                static_cast<int>(id.tok_tile * kTileTokens), bar);
+                pending |= 1u << buf;
+            };
+            // transposed = false: D[token][channel] = X_h M_h^T; true: D'[channel][token] = M_h X_h^T
+            auto product = [&](bool transposed, uint32_t buf, bool fresh, bool last_use) {
+                if (fresh) {
+                    wait(bar_of(buf), (landed_par >> buf) & 1u);
+                    if (healthy) {
+                        landed_par ^= 1u << buf;
+                        pending &= ~(1u << buf);
+                    }
+                }
+                const uint32_t set = n & 1u;
+                wait(bar_of(6 + set), ((n >> 1) & 1u) ^ 1u);   // the set has been read out (passes at once the first time)
+                if (healthy) {
+                    fence_after_sync();
+                    const uint32_t tmem_set = tmem_base + set * kSetCols;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint64_t dx0 = desc_x + ((buf * C::kTileBytes + h * C::kHalfBytes) >> 4);
+                        const uint64_t dm0 = desc_m + ((h * C::kHalfBytes) >> 4);
+#pragma unroll
+                        for (int k = 0; k < C::kKSteps; ++k) {
+                            const uint32_t off16 = ((k >> 2) * C::kBlockBytes + (k & 3) * 32) >> 4;
+                            const uint64_t dx = dx0 + off16, dm = dm0 + off16;
+                            umma<BF16>(tmem_set + h * kAccCols, transposed ? dm : dx, transposed ? dx : dm,
+                                       (!BF16 || k > 0) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(bar_of(4 + set));
+                    if (last_use) umma_commit(bar_of(2 + buf));
+                    ++commits;
+                }
+                ++n;
+            };
+            uint32_t item = blockIdx.x;
+            if (item < items) {
+                fetch(item, 0);
+                fetch(item, 1);
+            }
+            for (; item < items && healthy; item += item_step) {
+                const bool more = item + item_step < items;
+                product(false, 0, true, true);     // key plane
+                product(false, 1, true, false);    // value plane, per token: the scales
+                if (more) {                        // the key tile's product has long completed
+                    wait(bar_of(2), consumed_par & 1u);
+                    consumed_par ^= 1u;
+                    fetch(item + item_step, 0);
+                }
+                product(true, 1, false, true);     // value plane, per channel
+                if (more) {
+                    wait(bar_of(3), (consumed_par >> 1) & 1u);
+                    consumed_par ^= 2u;
+                    fetch(item + item_step, 1);
+                }
+            }
+            // Whatever is still on its way into this CTA's shared and tensor memory gets the full
+            // budget to finish before the memory goes back to the SM: the fetches not yet seen
+            // landed, and the last product chain (its commit also covers every earlier one).
+#pragma unroll
+            for (uint32_t buf = 0; buf < 2; ++buf)
+                if ((pending >> buf) & 1u) bounded_mbar_wait(bar_of(buf), (landed_par >> buf) & 1u, kWaitBudget, nullptr);
+            if (commits != 0u) {
+                // the last commit on the accumulator barrier of product n - 1
+                const uint32_t last = n - 1u;
+                bounded_mbar_wait(bar_of(4 + (last & 1u)), (last >> 1) & 1u, kWaitBudget, nullptr);
+            }
+        }
+    } else {
+        // ---- epilogue warps
+        bool healthy = true;
+        uint32_t m = 0;   // product counter, in step with the producer's
+        auto refill = [&](uint32_t acc, uint32_t col) {
+            if constexpr (!BF16) {
+                tmem_fill16(acc + col, kBiasBits);
+                tmem_fill16(acc + kAccCols + col, kBiasBits);
+            }
+        };
+
+        // wait for product m, return the address of this thread's columns in its set
+        auto await_product = [&]() -> uint32_t {
+            const uint32_t set = m & 1u;
+            if (healthy && !bounded_mbar_wait(bar_of(4 + set), (m >> 1) & 1u, p.wait_budget, abort_flag)) {
+                healthy = false;
+                *abort_flag = 1u;
+                report(p.status, TQ_STATUS_WAIT_EXPIRED);
+            }
+            fence_after_sync();
+            return acc0 + set * kSetCols;
+        };
+        // this warp is done with product m's accumulators (and has preset them again)
+        auto release_product = [&]() {
+            if constexpr (!BF16) tmem_wait_st();
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_of(6 + (m & 1u)));
+            ++m;
+        };
+
+        int32_t slot = -1;
+        bool strip_ok = false, tok_live = false;
+        uint32_t head = 0;
+        size_t block_off = 0, scale_at = 0;
+        const size_t plane_scales = static_cast<size_t>(p.P) * p.H * p.S;
+        const float2 minus1 = make_float2(-1.0f, -1.0f), minus2bias = make_float2(-2.0f * kBias, -2.0f * kBias);
+        const float2 magic2 = make_float2(kMagic, kMagic);
+
+        // y_lo and y_hi of two adjacent columns out of the raw accumulator words. int8: a' = B + a and
+        // b' = B + b with B = 1.5 * 2^23; b' - 2B, a' + (b' - 2B) and a' - b' are all exact in FP32.
+        auto combine = [&](uint32_t a0, uint32_t a1, uint32_t b0, uint32_t b1, float2& lo, float2& hi) {
+            const float2 a = make_float2(__uint_as_float(a0), __uint_as_float(a1));
+            const float2 b = make_float2(__uint_as_float(b0), __uint_as_float(b1));
+            if constexpr (BF16) lo = __fadd2_rn(a, b);
+            else lo = __fadd2_rn(a, __fadd2_rn(b, minus2bias));
+            hi = __ffma2_rn(b, minus1, a);
+        };
+        // absmax of y_lo and y_hi over this thread's 32 columns of the token-major product at `acc`
+        auto own_absmax = [&](uint32_t acc, uint32_t (&a0)[16], uint32_t (&b0)[16], uint32_t (&a1)[16],
+                              uint32_t (&b1)[16]) -> float {
+            if constexpr (BF16) {
+                float m0 = 0.0f, m1 = 0.0f;
+                auto fold = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16]) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        float2 lo, hi;
+                        combine(va[j], va[j + 1], vb[j], vb[j + 1], lo, hi);
+                        m0 = max3f(m0, fabsf(lo.x), fabsf(lo.y));
+                        m1 = max3f(m1, fabsf(hi.x), fabsf(hi.y));
+                    }
+                };
+                tmem_ld16(acc + 0, a0);
+                tmem_ld16(acc + kAccCols + 0, b0);
+                tmem_arrived2(a0, b0);
+                tmem_ld16(acc + 16, a1);
+                tmem_ld16(acc + kAccCols + 16, b1);
+                fold(a0, b0);
+                tmem_arrived2(a1, b1);
+                fold(a1, b1);
+                return fmaxf(m0, m1);
+            } else {
+                // the sums a and b as signed 16-bit pairs, 32 columns in one read. a + b can reach +32768
+                // only as exactly that value, which wraps to -32768 and still reads as 32768 below.
+                uint32_t top2 = 0x80008000u, bottom2 = 0x7FFF7FFFu;
+                tmem_ld16_low16(acc + 0, a0);
+                tmem_ld16_low16(acc + kAccCols + 0, b0);
+                tmem_arrived2(a0, b0);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const uint32_t s = __vadd2(va[j], vb[j]), d = __vsub2(va[j], vb[j]);
+                    const uint32_t s = __vadd2(a0[j], b0[j]), d = __vsub2(a0[j], b0[j]);
                     top2 = __vimax3_s16x2(top2, s, d);
                     bottom2 = __vimin3_s16x2(bottom2, s, d);
                 }
-            };
-            tmem_ld16_low16(acc + 0, a0);
-            tmem_ld16_low16(acc + kAccCols + 0, b0);
-            tmem_arrived2(a0, b0);
-            tmem_ld16_low16(acc + 32, a1);
-            tmem_ld16_low16(acc + kAccCols + 32, b1);
-            fold(a0, b0);
-            tmem_arrived2(a1, b1);
-            fold(a1, b1);
-            const int top = max(static_cast<int>(static_cast<int16_t>(top2 & 0xFFFFu)),
-                                static_cast<int>(static_cast<int16_t>(top2 >> 16)));
-            const int bottom = min(static_cast<int>(static_cast<int16_t>(bottom2 & 0xFFFFu)),
-                                   static_cast<int>(static_cast<int16_t>(bottom2 >> 16)));
-            amax = static_cast<float>(max(top, -bottom));
-        }
-        // the row's other 64 columns belong to the warp four further on
-        amax_s[half * kTileTokens + row] = amax;
-        if constexpr (kPlane == 0) {   // first chunk of pass 2, requested under the exchange
-            tmem_ld16(acc + 0, a0);
-            tmem_ld16(acc + kAccCols + 0, b0);
-        }
-        group_sync(group);
-        amax = fmaxf(fmaxf(amax, amax_s[(half ^ 1) * kTileTokens + row]), 1.0f);   // the writer floors absmax at 1
-        const int pow_bits = (__float_as_int(amax) & 0x7F800000) - (2 << 23);
-        const float inv = __int_as_float((254 << 23) - pow_bits);
-        if (half == 0 && strip_ok && healthy)
-            p.scale_cache[scale_at + (kPlane ? plane_scales : 0)] = __int_as_float(pow_bits) * p.inv_sqrt_len;
-        const float2 magic2 = make_float2(kMagic, kMagic);
-
-        if constexpr (kPlane == 0) {
-            // ---- key page: the token's row of 128 bytes; this thread's columns are channels
-            // 64 half .. of y_lo (bytes 32 half ..) and 128 + 64 half .. of y_hi (bytes 64 + 32 half ..)
-            uint2* dst = reinterpret_cast<uint2*>(p.key_cache + block_off + static_cast<size_t>(lane & 15) * 128u +
-                                                  static_cast<size_t>(half) * 32u);
-            const float2 inv2 = make_float2(inv, inv);
-            const bool store = strip_ok && healthy;
-            auto emit = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16], int c) {
-                float rl[16], rh[16];
-#pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                    float2 lo, hi;
-                    combine(va[j], va[j + 1], vb[j], vb[j + 1], lo, hi);
-                    const float2 l = __ffma2_rn(lo, inv2, magic2), h = __ffma2_rn(hi, inv2, magic2);
-                    rl[j] = l.x;
-                    rl[j + 1] = l.y;
-                    rh[j] = h.x;
-                    rh[j + 1] = h.y;
-                }
-                const float (&rl0)[8] = *reinterpret_cast<const float (*)[8]>(rl);
-                const float (&rl1)[8] = *reinterpret_cast<const float (*)[8]>(rl + 8);
-                const float (&rh0)[8] = *reinterpret_cast<const float (*)[8]>(rh);
-                const float (&rh1)[8] = *reinterpret_cast<const float (*)[8]>(rh + 8);
-                const uint2 wl = make_uint2(pack8(rl0), pack8(rl1)), wh = make_uint2(pack8(rh0), pack8(rh1));
-                if (store) {
-                    __stcs(dst + c, wl);
-                    __stcs(dst + 8 + c, wh);   // 64 bytes further on
-                }
-            };
-            tmem_arrived2(a0, b0);
-            tmem_ld16(acc + 16, a1);
-            tmem_ld16(acc + kAccCols + 16, b1);
-            refill(0);
-            emit(a0, b0, 0);
-            tmem_arrived2(a1, b1);
-            tmem_ld16(acc + 32, a0);
-            tmem_ld16(acc + kAccCols + 32, b0);
-            refill(16);
-            emit(a1, b1, 1);
-            tmem_arrived2(a0, b0);
-            tmem_ld16(acc + 48, a1);
-            tmem_ld16(acc + kAccCols + 48, b1);
-            refill(32);
-            emit(a0, b0, 2);
-            tmem_arrived2(a1, b1);
-            refill(48);
-            emit(a1, b1, 3);
-        } else {
-            // ---- value page: publish the per-token constants, swap the operands, then work per
-            // channel: this thread is channel `row` of y_lo and 128 + row of y_hi, tokens 64 half ..
-#pragma unroll
-            for (int c = 0; c < 4; ++c) refill(c * 16);   // pass 1 was the only pass over these products
-            if (half == 0) {
-                inv_s[row] = inv;
-                if ((lane & 15) == 0)
-                    strip_off[row >> 4] = strip_ok ? static_cast<unsigned long long>(block_off) : ~0ull;
+                const int top = max(static_cast<int>(static_cast<int16_t>(top2 & 0xFFFFu)),
+                                    static_cast<int>(static_cast<int16_t>(top2 >> 16)));
+                const int bottom = min(static_cast<int>(static_cast<int16_t>(bottom2 & 0xFFFFu)),
+                                       static_cast<int>(static_cast<int16_t>(bottom2 >> 16)));
+                return static_cast<float>(max(top, -bottom));
             }
-            product(true, false);   // its barrier also publishes the constants and ends pass 1's reads
-            if (item + item_step < items) load_tile(item + item_step, 0);
-            const bool store = healthy;
-            auto emit = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16], int c) {
-                const int s = half * 4 + c;   // the strip of these 16 tokens
-                const unsigned long long off = strip_off[s];
-                float rl[16], rh[16];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float4 iv = *reinterpret_cast<const float4*>(inv_s + s * 16 + q * 4);
-                    const float2 i01 = make_float2(iv.x, iv.y), i23 = make_float2(iv.z, iv.w);
-                    float2 lo, hi;
-                    combine(va[q * 4], va[q * 4 + 1], vb[q * 4], vb[q * 4 + 1], lo, hi);
-                    float2 l = __ffma2_rn(lo, i01, magic2), h = __ffma2_rn(hi, i01, magic2);
-                    rl[q * 4] = l.x;
-                    rl[q * 4 + 1] = l.y;
-                    rh[q * 4] = h.x;
-                    rh[q * 4 + 1] = h.y;
-                    combine(va[q * 4 + 2], va[q * 4 + 3], vb[q * 4 + 2], vb[q * 4 + 3], lo, hi);
-                    l = __ffma2_rn(lo, i23, magic2);
-                    h = __ffma2_rn(hi, i23, magic2);
-                    rl[q * 4 + 2] = l.x;
-                    rl[q * 4 + 3] = l.y;
-                    rh[q * 4 + 2] = h.x;
-                    rh[q * 4 + 3] = h.y;
-                }
-                const float (&rl0)[8] = *reinterpret_cast<const float (*)[8]>(rl);
-                const float (&rl1)[8] = *reinterpret_cast<const float (*)[8]>(rl + 8);
-                const float (&rh0)[8] = *reinterpret_cast<const float (*)[8]>(rh);
-                const float (&rh1)[8] = *reinterpret_cast<const float (*)[8]>(rh + 8);
-                const uint2 wl = make_uint2(pack8(rl0), pack8(rl1)), wh = make_uint2(pack8(rh0), pack8(rh1));
-                if (store && off != ~0ull) {
-                    uint8_t* blk = p.value_cache + off;
-                    __stcs(reinterpret_cast<uint2*>(blk + static_cast<size_t>(row) * 8u), wl);
-                    __stcs(reinterpret_cast<uint2*>(blk + static_cast<size_t>(128 + row) * 8u), wh);
-                }
-            };
-            tmem_ld16(acc + 0, a0);
-            tmem_ld16(acc + kAccCols + 0, b0);
-            tmem_arrived2(a0, b0);
-            tmem_ld16(acc + 16, a1);
-            tmem_ld16(acc + kAccCols + 16, b1);
-            refill(0);
-            emit(a0, b0, 0);
-            tmem_arrived2(a1, b1);
-            tmem_ld16(acc + 32, a0);
-            tmem_ld16(acc + kAccCols + 32, b0);
-            refill(16);
-            emit(a1, b1, 1);
-            tmem_arrived2(a0, b0);
-            tmem_ld16(acc + 48, a1);
-            tmem_ld16(acc + kAccCols + 48, b1);
-            refill(32);
-            emit(a0, b0, 2);
-            tmem_arrived2(a1, b1);
-            refill(48);
-            emit(a1, b1, 3);
-        }
-        // every read of tensor memory and of the per-token constants is done before the
-        // group's next products overwrite them
-        fence_before_sync();
-        return !group_sync_any(group, !healthy || *abort_flag != 0u);
-    };
+        };
+        // the row's absmax over all four column quarters (a barrier of the four warps that hold the row inside)
+        auto row_absmax = [&](float mine, int plane) -> float {
+            float* ex = amax_s + plane * 4 * kTileTokens;
+            ex[cq * kTileTokens + row] = mine;
+            rows_sync(quarter);
+            const float m01 = fmaxf(ex[row], ex[kTileTokens + row]);
+            const float m23 = fmaxf(ex[2 * kTileTokens + row], ex[3 * kTileTokens + row]);
+            return fmaxf(fmaxf(m01, m23), 1.0f);   // the writer floors absmax at 1
+        };
+
 #pragma unroll 1
-    for (; item < items; item += item_step) {
-        if (!do_plane(std::integral_constant<uint32_t, 0>{})) break;
-        if (!do_plane(std::integral_constant<uint32_t, 1>{})) break;
-    }
-    // After a wait ran out (here or in the other group) a tile fetch or a product chain may still
-    // be on its way into this CTA's shared and tensor memory: thread 0 gives each the full budget
-    // to finish before the memory goes back to the SM.
-    if (tid == 0) {
-        if (tma_pending) bounded_wait(tma_bar_s, tma_parity, kWaitBudget, false);
-        if (mma_pending) bounded_wait(mbar_s, mma_pending_parity, kWaitBudget, false);
+        for (uint32_t item = blockIdx.x; item < items; item += item_step) {
+            uint32_t a0[16], b0[16], a1[16], b1[16];
+            // ---- where this thread's token of the tile goes (requested before anything waits)
+            {
+                const TileId id = tile_of(p, item);
+                const uint32_t tok = id.tok_tile * kTileTokens + row;
+                head = id.head;
+                tok_live = tok < num_tokens;
+                slot = -1;   // a volatile load: it must not sink below the product's wait
+                if (tok_live) asm volatile("ld.global.nc.s32 %0, [%1];\n" : "=r"(slot) : "l"(p.slots + tok));
+            }
+            // ================= key plane
+            uint32_t acc = await_product();
+            {
+                const int32_t slot0 = __shfl_sync(0xffffffffu, slot, lane & 16);
+                const bool run_ok = slot == slot0 + (lane & 15);
+                const uint32_t votes = __ballot_sync(0xffffffffu, run_ok);
+                const bool strip_live = __shfl_sync(0xffffffffu, tok_live ? 1 : 0, lane & 16) != 0;
+                const uint32_t slot_page = fast_div(static_cast<uint32_t>(slot0), p.page_mul, p.page_shift);
+                strip_ok = strip_live && ((votes >> (lane & 16)) & 0xFFFFu) == 0xFFFFu && slot0 >= 0 &&
+                           (slot0 % kStrip) == 0 && slot_page < p.P;
+                if (strip_live && !strip_ok && (lane & 15) == 0 && cq == 0) report(p.status, TQ_STATUS_BAD_SLOT);
+                const uint32_t page = strip_ok ? slot_page : 0u;
+                const uint32_t tok_in_page = strip_ok ? static_cast<uint32_t>(slot0) - slot_page * p.S : 0u;
+                // byte offset of the strip's (page, head) block in either code plane
+                block_off = (static_cast<size_t>(page) * p.H + head) * (static_cast<size_t>(p.S) * 128u) +
+                            static_cast<size_t>(tok_in_page / kStrip) * 2048u;
+                scale_at = (static_cast<size_t>(page) * p.H + head) * p.S + tok_in_page + (lane & 15);
+            }
+            float amax = own_absmax(acc, a0, b0, a1, b1);
+            tmem_ld16(acc + 0, a0);   // first chunk of pass 2, requested under the exchange
+            tmem_ld16(acc + kAccCols + 0, b0);
+            amax = row_absmax(amax, 0);
+            {
+                const int pow_bits = (__float_as_int(amax) & 0x7F800000) - (2 << 23);
+                const float inv = __int_as_float((254 << 23) - pow_bits);
+                if (cq == 0 && strip_ok && healthy)
+                    p.scale_cache[scale_at] = __int_as_float(pow_bits) * p.inv_sqrt_len;
+                // the token's row of 128 bytes; this thread's columns are channels 32 cq .. of y_lo
+                // (bytes 16 cq ..) and 128 + 32 cq .. of y_hi (bytes 64 + 16 cq ..)
+                uint4* dst = reinterpret_cast<uint4*>(p.key_cache + block_off + static_cast<size_t>(lane & 15) * 128u +
+                                                      static_cast<size_t>(cq) * 16u);
+                const float2 inv2 = make_float2(inv, inv);
+                uint32_t wl[4], wh[4];
+                auto quantise = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16], int c) {
+                    float rl[16], rh[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        float2 lo, hi;
+                        combine(va[j], va[j + 1], vb[j], vb[j + 1], lo, hi);
+                        const float2 l = __ffma2_rn(lo, inv2, magic2), h = __ffma2_rn(hi, inv2, magic2);
+                        rl[j] = l.x;
+                        rl[j + 1] = l.y;
+                        rh[j] = h.x;
+                        rh[j + 1] = h.y;
+                    }
+                    wl[2 * c] = pack8(*reinterpret_cast<const float (*)[8]>(rl));
+                    wl[2 * c + 1] = pack8(*reinterpret_cast<const float (*)[8]>(rl + 8));
+                    wh[2 * c] = pack8(*reinterpret_cast<const float (*)[8]>(rh));
+                    wh[2 * c + 1] = pack8(*reinterpret_cast<const float (*)[8]>(rh + 8));
+                };
+                tmem_arrived2(a0, b0);
+                tmem_ld16(acc + 16, a1);
+                tmem_ld16(acc + kAccCols + 16, b1);
+                refill(acc, 0);
+                quantise(a0, b0, 0);
+                tmem_arrived2(a1, b1);
+                refill(acc, 16);
+                release_product();
+                quantise(a1, b1, 1);
+                if (strip_ok && healthy) {
+                    __stcs(dst, make_uint4(wl[0], wl[1], wl[2], wl[3]));
+                    __stcs(dst + 4, make_uint4(wh[0], wh[1], wh[2], wh[3]));   // 64 bytes further on
+                }
+            }
+            // ================= value plane, per token: the scales
+            acc = await_product();
+            amax = own_absmax(acc, a0, b0, a1, b1);
+            refill(acc, 0);
+            refill(acc, 16);
+            release_product();
+            amax = row_absmax(amax, 1);
+            {
+                const int pow_bits = (__float_as_int(amax) & 0x7F800000) - (2 << 23);
+                if (cq == 0) {
+                    inv_s[row] = __int_as_float((254 << 23) - pow_bits);
+                    if ((lane & 15) == 0)
+                        strip_off[row >> 4] = strip_ok ? static_cast<unsigned long long>(block_off) : ~0ull;
+                    if (strip_ok && healthy)
+                        p.scale_cache[scale_at + plane_scales] = __int_as_float(pow_bits) * p.inv_sqrt_len;
+                }
+            }
+            // publishes the constants; also the one place where the epilogue warps agree to stop
+            if (epi_sync_any(!healthy || *abort_flag != 0u)) break;
+            // ================= value plane, per channel: this thread is channel `row` of y_lo and
+            // 128 + row of y_hi, tokens 32 cq .. (two strips)
+            acc = await_product();
+            {
+                const bool store = healthy;
+                auto emit = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16], int c) {
+                    const int s = cq * 2 + c;   // the strip of these 16 tokens
+                    const unsigned long long off = strip_off[s];
+                    float rl[16], rh[16];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 iv = *reinterpret_cast<const float4*>(inv_s + s * 16 + q * 4);
+                        const float2 i01 = make_float2(iv.x, iv.y), i23 = make_float2(iv.z, iv.w);
+                        float2 lo, hi;
+                        combine(va[q * 4], va[q * 4 + 1], vb[q * 4], vb[q * 4 + 1], lo, hi);
+                        float2 l = __ffma2_rn(lo, i01, magic2), h = __ffma2_rn(hi, i01, magic2);
+                        rl[q * 4] = l.x;
+                        rl[q * 4 + 1] = l.y;
+                        rh[q * 4] = h.x;
+                        rh[q * 4 + 1] = h.y;
+                        combine(va[q * 4 + 2], va[q * 4 + 3], vb[q * 4 + 2], vb[q * 4 + 3], lo, hi);
+                        l = __ffma2_rn(lo, i23, magic2);
+                        h = __ffma2_rn(hi, i23, magic2);
+                        rl[q * 4 + 2] = l.x;
+                        rl[q * 4 + 3] = l.y;
+                        rh[q * 4 + 2] = h.x;
+                        rh[q * 4 + 3] = h.y;
+                    }
+                    const uint2 wl = make_uint2(pack8(*reinterpret_cast<const float (*)[8]>(rl)),
+                                                pack8(*reinterpret_cast<const float (*)[8]>(rl + 8)));
+                    const uint2 wh = make_uint2(pack8(*reinterpret_cast<const float (*)[8]>(rh)),
+                                                pack8(*reinterpret_cast<const float (*)[8]>(rh + 8)));
+                    if (store && off != ~0ull) {
+                        uint8_t* blk = p.value_cache + off;
+                        __stcs(reinterpret_cast<uint2*>(blk + static_cast<size_t>(row) * 8u), wl);
+                        __stcs(reinterpret_cast<uint2*>(blk + static_cast<size_t>(128 + row) * 8u), wh);
+                    }
+                };
+                tmem_ld16(acc + 0, a0);
+                tmem_ld16(acc + kAccCols + 0, b0);
+                tmem_arrived2(a0, b0);
+                tmem_ld16(acc + 16, a1);
+                tmem_ld16(acc + kAccCols + 16, b1);
+                refill(acc, 0);
+                emit(a0, b0, 0);
+                tmem_arrived2(a1, b1);
+                refill(acc, 16);
+                release_product();
+                emit(a1, b1, 1);
+            }
+        }
     }
     fence_before_sync();
     __syncthreads();
-    if (threadIdx.x < 32)
+    if (warp == 0)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
 }
 
@@ -579,8 +619,7 @@ cudaError_t launch(cudaStream_t stream, const IngestParams& p)
         !activation_map<BF16>(&value_map, p.value, p.num_strips * kStrip, p.H))
         return cudaErrorNotSupported;
     const uint32_t resident = static_cast<uint32_t>(sms);   // persistent: one CTA per SM
-    const uint64_t wanted = (tiles + kGroups - 1) / kGroups;
-    const uint32_t blocks = wanted < resident ? static_cast<uint32_t>(wanted) : resident;
+    const uint32_t blocks = tiles < resident ? static_cast<uint32_t>(tiles) : resident;
     tq_ingest_umma256_kernel<BF16><<<blocks, kThreads, C::kSmem, stream>>>(p, key_map, value_map);
     return cudaGetLastError();
 }
