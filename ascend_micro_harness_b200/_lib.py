@@ -18,6 +18,8 @@ SIGNATURES = {
                                        u32, u32, f32, vp]),
     "tq_reshape_and_cache_warp_mma": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
                                        u32, u32, f32, vp]),
+    "tq_reshape_and_cache_tcgen05": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
+                                       u32, u32, f32, vp]),
     "tq_ingest_set_wait_budget": (None, [C.c_longlong]),
     "tq_reshape_and_cache_varlen": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32,
                                               u32, u32, f32, vp]),

@@ -504,15 +504,18 @@ extern "C" void tq_ingest_set_wait_budget(long long cycles)
     g_wait_budget.store(cycles < 0 ? tq::kIngestWaitBudget : cycles, std::memory_order_relaxed);
 }
 
-// Head size 128 goes to the tcgen05 writer unless `warp_mma_only`; head size 256 and the
-// explicit warp-MMA entry use the kernel in this file.
+// Which kernel serves a call. kAuto: the faster one as measured on B200 -- tcgen05 for head size 128
+// and for bf16 at head size 256, warp MMA for int8 at head size 256 (3.40 against 3.33 TB/s) and
+// wherever the driver cannot encode a tensor map.
+enum class Writer { kAuto, kWarpMma, kTcgen05 };
+
 static int reshape_and_cache(void* stream, const void* key, const void* value,
                              int8_t* key_cache, int8_t* value_cache, float* scale_cache,
                              const int32_t* slot_mapping, const void* signs,
                              uint32_t sign_source, uint32_t in_dtype, uint32_t num_tokens,
                              uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
                              uint32_t num_blocks, float inv_sqrt_len, uint32_t* status,
-                             bool warp_mma_only)
+                             Writer writer)
 {
     using namespace tq;
     if (num_kv_heads == 0 || num_blocks == 0 || block_size == 0 || block_size % kStrip != 0 ||
@@ -556,10 +559,11 @@ static int reshape_and_cache(void* stream, const void* key, const void* value,
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t err = cudaErrorNotSupported;
-    if (head_size == 128 && !warp_mma_only) err = launch_ingest_umma(s, p, in_dtype == TQ_IN_BF16);
-    if (head_size == 256 && !warp_mma_only) err = launch_ingest_umma256(s, p, in_dtype == TQ_IN_BF16);
-    if (err == cudaErrorNotSupported) {
-        // head size 256, the explicit warp-MMA entry, or a driver without tensor maps
+    const bool bf16 = in_dtype == TQ_IN_BF16;
+    const bool tensor_memory = writer == Writer::kTcgen05 || (writer == Writer::kAuto && (head_size == 128 || bf16));
+    if (tensor_memory) err = head_size == 128 ? launch_ingest_umma(s, p, bf16) : launch_ingest_umma256(s, p, bf16);
+    if (err == cudaErrorNotSupported && writer != Writer::kTcgen05) {
+        // the measured choice, the explicit warp-MMA entry, or a driver without tensor maps
         if (head_size == 128)
             err = in_dtype == TQ_IN_BF16 ? launch_ingest<128, true>(s, p) : launch_ingest<128, false>(s, p);
         else
@@ -577,7 +581,7 @@ extern "C" int tq_reshape_and_cache(void* stream, const void* key, const void* v
 {
     return reshape_and_cache(stream, key, value, key_cache, value_cache, scale_cache, slot_mapping,
                              signs, sign_source, in_dtype, num_tokens, num_kv_heads, head_size,
-                             block_size, num_blocks, inv_sqrt_len, status, false);
+                             block_size, num_blocks, inv_sqrt_len, status, Writer::kAuto);
 }
 
 extern "C" int tq_reshape_and_cache_warp_mma(void* stream, const void* key, const void* value,
@@ -591,7 +595,21 @@ extern "C" int tq_reshape_and_cache_warp_mma(void* stream, const void* key, cons
 {
     return reshape_and_cache(stream, key, value, key_cache, value_cache, scale_cache, slot_mapping,
                              signs, sign_source, in_dtype, num_tokens, num_kv_heads, head_size,
-                             block_size, num_blocks, inv_sqrt_len, status, true);
+                             block_size, num_blocks, inv_sqrt_len, status, Writer::kWarpMma);
+}
+
+extern "C" int tq_reshape_and_cache_tcgen05(void* stream, const void* key, const void* value,
+                                            int8_t* key_cache, int8_t* value_cache,
+                                            float* scale_cache, const int32_t* slot_mapping,
+                                            const void* signs, uint32_t sign_source,
+                                            uint32_t in_dtype, uint32_t num_tokens,
+                                            uint32_t num_kv_heads, uint32_t head_size,
+                                            uint32_t block_size, uint32_t num_blocks,
+                                            float inv_sqrt_len, uint32_t* status)
+{
+    return reshape_and_cache(stream, key, value, key_cache, value_cache, scale_cache, slot_mapping,
+                             signs, sign_source, in_dtype, num_tokens, num_kv_heads, head_size,
+                             block_size, num_blocks, inv_sqrt_len, status, Writer::kTcgen05);
 }
 
 // The aligned writer over ragged requests: strips are cut per request, the last strip of a

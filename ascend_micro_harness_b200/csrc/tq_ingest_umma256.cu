@@ -44,7 +44,12 @@ struct Cfg {
     static constexpr int kHalfBytes = kBlocksHalf * kBlockBytes;   // x_lo, x_hi, M_0, M_1: each this size
     static constexpr int kTileBytes = 2 * kHalfBytes;
     static constexpr int kKSteps = kHalfRowBytes / 32;       // one MMA contracts 32 bytes of K
-    static constexpr int kTileBufs = 2;                      // 0: the key tile, 1: the value tile
+    // Tile buffers: 0 the key tile, 1 the value tile of the item in flight. Measured and dropped:
+    // a second item's tiles in flight for int8, whose tiles are half the size (3.31 against 3.33 TB/s:
+    // int8 waits on its epilogue, not on tiles), and halves of a tile fetched and given back
+    // separately (bf16 4.94 against 5.30 TB/s: the extra commit between the two chains of a product
+    // holds the second chain back).
+    static constexpr int kTileBufs = 2;
     // 128 inverse scales, 2 x 4 x 128 absmax quarters, 8 strip offsets, 8 barriers
     static constexpr int kSmallBytes = 9 * kTileTokens * 4 + 8 * 8 + 8 * 8;
     static constexpr int kUsed = 2 * kHalfBytes + kTileBufs * kTileBytes + kSmallBytes + 64;
@@ -99,12 +104,8 @@ __device__ __forceinline__ TileId tile_of(const IngestParams& p, uint32_t item)
     return id;
 }
 
-// All 512 epilogue threads (named barrier 1); the producer warp takes no part.
-__device__ __forceinline__ void epi_sync()
-{
-    asm volatile("bar.sync 1, %0;\n" ::"r"(kEpiThreads) : "memory");
-}
-// The same barrier carrying a vote: true for every epilogue thread if any of them says so. The
+// A barrier of all 512 epilogue threads (named barrier 1; the producer warp takes no part) carrying a
+// vote: true for every epilogue thread if any of them says so. The
 // decision to leave the item loop must be one decision for all of them, or the next barrier hangs.
 __device__ __forceinline__ bool epi_sync_any(bool mine)
 {

@@ -113,10 +113,11 @@ def _need_workspace(call, workspace, batch, num_heads, num_kv_heads, head_size, 
 
 def reshape_and_cache(key, value, key_cache, value_cache, scale_cache, slot_mapping, signs, *,
                       num_kv_heads, head_size, block_size, num_blocks, inv_sqrt_len,
-                      sign_source=SIGNS_F32, status=None, stream=None, warp_mma=False):
+                      sign_source=SIGNS_F32, status=None, stream=None, warp_mma=False, tcgen05=False):
     """Aligned writer (reference: launch_turboquant_reshape_and_cache_{a8,bf16}).
-    key/value: [T, H*d] int8 or bfloat16. Head size 128 runs on the tcgen05 kernel;
-    warp_mma=True selects the warp-MMA kernel (the one head size 256 always uses)."""
+    key/value: [T, H*d] int8 or bfloat16. The library picks the kernel that measured faster
+    (tcgen05 for head size 128 and for bf16 at head size 256, warp MMA for int8 at head size 256);
+    warp_mma=True or tcgen05=True forces one of them."""
     lib = load_library()
     call = _Call("reshape_and_cache").take("key", key, (torch.int8, torch.bfloat16))
     call.take("value", value, (key.dtype,)).caches(key_cache, value_cache, scale_cache)
@@ -125,7 +126,10 @@ def reshape_and_cache(key, value, key_cache, value_cache, scale_cache, slot_mapp
                                SIGNS_TABLES_BF16: (torch.bfloat16, torch.int32, torch.int16)}[sign_source])
     in_dtype = {torch.int8: 0, torch.bfloat16: 1}[key.dtype]
     num_tokens = key.numel() // (num_kv_heads * head_size)
-    fn = lib.tq_reshape_and_cache_warp_mma if warp_mma else lib.tq_reshape_and_cache
+    if warp_mma and tcgen05:
+        raise ValueError("reshape_and_cache: warp_mma and tcgen05 exclude each other")
+    fn = (lib.tq_reshape_and_cache_warp_mma if warp_mma else
+          lib.tq_reshape_and_cache_tcgen05 if tcgen05 else lib.tq_reshape_and_cache)
     with call:
         _check(fn(
             _stream(stream, call.device), _ptr(key), _ptr(value), _ptr(key_cache), _ptr(value_cache),

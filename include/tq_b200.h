@@ -94,15 +94,24 @@ int tq_reshape_and_cache(void* stream, const void* key, const void* value, int8_
                          uint32_t block_size, uint32_t num_blocks, float inv_sqrt_len,
                          uint32_t* status);
 
-/* tq_reshape_and_cache serves head size 128 with the tcgen05 kernel and head size 256
- * with the warp-MMA kernel. This entry forces the warp-MMA kernel for either head size:
- * same arguments, same bytes out (kept for comparison and as the fallback build target). */
+/* tq_reshape_and_cache picks the kernel that measured faster on B200: the tcgen05 kernels
+ * (tensor-core products into tensor memory) for head size 128 and for bf16 at head size 256, the
+ * warp-MMA kernel for int8 at head size 256 and wherever the driver cannot encode a tensor map.
+ * The two entries below force one or the other for any head size and element type: same
+ * arguments, same bytes out. The tcgen05 entry returns TQ_ERR_LAUNCH where the warp-MMA kernel
+ * would have had to step in. */
 int tq_reshape_and_cache_warp_mma(void* stream, const void* key, const void* value,
                                   int8_t* key_cache, int8_t* value_cache, float* scale_cache,
                                   const int32_t* slot_mapping, const void* signs,
                                   uint32_t sign_source, uint32_t in_dtype, uint32_t num_tokens,
                                   uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
                                   uint32_t num_blocks, float inv_sqrt_len, uint32_t* status);
+int tq_reshape_and_cache_tcgen05(void* stream, const void* key, const void* value,
+                                 int8_t* key_cache, int8_t* value_cache, float* scale_cache,
+                                 const int32_t* slot_mapping, const void* signs,
+                                 uint32_t sign_source, uint32_t in_dtype, uint32_t num_tokens,
+                                 uint32_t num_kv_heads, uint32_t head_size, uint32_t block_size,
+                                 uint32_t num_blocks, float inv_sqrt_len, uint32_t* status);
 
 /* Every wait inside the tcgen05 writer (on a tile fetch, on a tensor-core product) is bounded:
  * when `cycles` clock cycles have passed the kernel reports TQ_STATUS_WAIT_EXPIRED, stores

@@ -36,18 +36,19 @@ def test_prefill_262144_tokens_both_kernels_and_sampled_oracle(cuda, oracle):
     signs_np = hp.random_signs(rng, d)
     signs = torch.from_numpy(signs_np.astype(np.float32)).to(cuda)
     out = []
-    for warp_mma in (False, True):
+    for warp_mma, tcgen05 in ((False, False), (True, False), (False, True)):
         kc = torch.full((P * H * S * d // 2,), 0xAA, dtype=torch.uint8, device=cuda)
         vc = torch.full_like(kc, 0xAA)
         sc = torch.full((2 * P * H * S,), float("nan"), dtype=torch.float32, device=cuda)
         st = torch.zeros(1, dtype=torch.int32, device=cuda)
         tq.reshape_and_cache(k, v, kc, vc, sc, slots, signs, num_kv_heads=H, head_size=d,
                              block_size=S, num_blocks=P, inv_sqrt_len=hp.inv_sqrt_len(d), status=st,
-                             warp_mma=warp_mma)
+                             warp_mma=warp_mma, tcgen05=tcgen05)
         torch.cuda.synchronize()
         assert int(st.item()) == 0
         out.append((kc, vc, sc))
     assert torch.equal(out[0][0], out[1][0]) and torch.equal(out[0][1], out[1][1])
+    assert torch.equal(out[0][0], out[2][0]) and torch.equal(out[0][1], out[2][1])
     assert torch.equal(out[0][2].view(torch.int32), out[1][2].view(torch.int32))
     # the five pages no strip owns keep their canaries
     owned = torch.zeros(P, dtype=torch.bool, device=cuda)
