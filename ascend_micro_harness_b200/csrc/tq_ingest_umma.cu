@@ -88,6 +88,18 @@ __device__ __forceinline__ void group_sync(int group)
     asm volatile("bar.sync %0, %1;\n" ::"r"(group + 1), "r"(kGroupThreads) : "memory");
 }
 
+// The same barrier carrying a vote: true for every thread of the group if any of them says so.
+// Leaving the item loop must be one decision per group, or the group's next barrier would hang.
+__device__ __forceinline__ bool group_sync_any(int group, bool mine)
+{
+    uint32_t any;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %3, 0;\n\t"
+        "bar.red.or.pred q, %1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+        : "=r"(any) : "r"(group + 1), "r"(kGroupThreads), "r"(mine ? 1u : 0u) : "memory");
+    return any != 0u;
+}
+
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, Cfg<BF16>::kCtasPerSm)
 tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap key_map,
@@ -472,8 +484,7 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         // every read of tensor memory and of the per-token constants is done before the
         // group's next products overwrite them
         fence_before_sync();
-        group_sync(group);
-        return *abort_flag == 0u;
+        return !group_sync_any(group, !healthy || *abort_flag != 0u);
     };
 #pragma unroll 1
     for (; item < items; item += item_step) {
