@@ -30,7 +30,7 @@ namespace {
 constexpr int kTileTokens = 128;
 constexpr int kEpiWarps = 16;                // warp w: lane quarter w & 3 (rows), column quarter w >> 2
 constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kThreads = kEpiThreads + 32;   // + the warp whose first lane fetches tiles and issues products
+constexpr int kThreads = kEpiThreads + 64;   // + one warp whose first lane issues the products, one whose first lane fetches tiles
 constexpr uint32_t kAccCols = 128;           // one 128 x 128 accumulator
 constexpr uint32_t kSetCols = 2 * kAccCols;  // a, then b
 constexpr uint32_t kTmemCols = 2 * kSetCols; // two sets: one is read out while the other is written
@@ -136,7 +136,7 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
     // tiles on a 1024-byte boundary: the swizzle is a function of address bits 4..9
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool producer = warp == kEpiWarps;
+    const bool producer = warp >= kEpiWarps;     // warp 16: products, warp 17: tile fetches
     const int quarter = warp & 3, cq = (warp >> 2) & 3;   // tensor-memory lane quarter, column quarter
     const int row = quarter * 32 + lane;                  // token (plain products) or channel (swapped)
     uint8_t* m_tiles = base;                              // M_0, then M_1
@@ -151,6 +151,7 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
     uint32_t* shared_words = reinterpret_cast<uint32_t*>(mbar + 8);
     uint32_t* tmem_slot = shared_words;
     volatile uint32_t* abort_flag = shared_words + 1;
+    volatile uint32_t* fetched = shared_words + 2;   // [2]: tile fetches issued per buffer (written by the fetching lane)
 
     const uint32_t items = ((p.num_strips + 7u) / 8u) * p.H;
     const uint32_t num_tokens = p.num_strips * kStrip;
@@ -164,6 +165,8 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(mbar + 7)), "r"(kEpiWarps));
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         *abort_flag = 0u;
+        fetched[0] = 0u;
+        fetched[1] = 0u;
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
@@ -232,23 +235,21 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
     const uint32_t item_step = gridDim.x;
 
     if (producer) {
-        // ---- lane 0: tile fetches and products. Product n writes accumulator set n & 1; the order
-        // per item is key, value, value swapped. A tile buffer is fetched again as soon as the last
-        // product reading it has completed; an accumulator set is written again as soon as the
-        // epilogue warps have read it out.
-        if (lane == 0) {
-            const uint32_t x_tiles_s = smem_addr(x_tiles);
-            const uint64_t desc_x = umma_desc(x_tiles_s), desc_m = umma_desc(smem_addr(m_tiles));
-            uint32_t n = 0, landed_par = 0, consumed_par = 0, pending = 0, commits = 0;   // bit b: buffer b's state
-            bool healthy = true;
-            auto wait = [&](uint32_t bar, uint32_t par) {
-                if (!healthy) return;
-                if (!bounded_mbar_wait(bar, par, p.wait_budget, abort_flag)) {
-                    healthy = false;
-                    *abort_flag = 1u;
-                    report(p.status, TQ_STATUS_WAIT_EXPIRED);
-                }
-            };
+        const uint32_t x_tiles_s = smem_addr(x_tiles);
+        bool healthy = true;
+        auto wait = [&](uint32_t bar, uint32_t par) {
+            if (!healthy) return;
+            if (!bounded_mbar_wait(bar, par, p.wait_budget, abort_flag)) {
+                healthy = false;
+                *abort_flag = 1u;
+                report(p.status, TQ_STATUS_WAIT_EXPIRED);
+            }
+        };
+        uint32_t landed_par = 0, landed_seen[2] = {0, 0};   // the issuing lane's view of the tile barriers
+        if (warp == kEpiWarps + 1 && lane == 0) {
+            // ---- tile fetches: a buffer (0: key tile, 1: value tile) is fetched again, for the CTA's
+            // next item, as soon as the last product reading it has completed
+            uint32_t consumed_par = 0, count[2] = {0, 0};
             auto fetch = [&](uint32_t item, uint32_t buf) {
                 if (!healthy) return;
                 const TileId id = tile_of(p, item);
@@ -260,15 +261,35 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                     tma_load_2d(dst + blk * C::kBlockBytes, map,
                                 static_cast<int>(id.head * 256u + blk * (128 / C::kElem)),
                                 static_cast<int>(id.tok_tile * kTileTokens), bar);
-                pending |= 1u << buf;
+                fetched[buf] = ++count[buf];
             };
+            uint32_t item = blockIdx.x;
+            if (item < items) {
+                fetch(item, 0);
+                fetch(item, 1);
+            }
+            for (; item + item_step < items && healthy; item += item_step) {
+#pragma unroll
+                for (uint32_t buf = 0; buf < 2; ++buf) {
+                    wait(bar_of(2 + buf), (consumed_par >> buf) & 1u);
+                    consumed_par ^= 1u << buf;
+                    fetch(item + item_step, buf);
+                }
+            }
+        }
+        uint32_t n = 0, commits = 0;
+        if (warp == kEpiWarps && lane == 0) {
+            // ---- products. Product n writes accumulator set n & 1; the order per item is key, value,
+            // value swapped; an accumulator set is written again as soon as the epilogue warps have
+            // read it out.
+            const uint64_t desc_x = umma_desc(x_tiles_s), desc_m = umma_desc(smem_addr(m_tiles));
             // transposed = false: D[token][channel] = X_h M_h^T; true: D'[channel][token] = M_h X_h^T
             auto product = [&](bool transposed, uint32_t buf, bool fresh, bool last_use) {
                 if (fresh) {
                     wait(bar_of(buf), (landed_par >> buf) & 1u);
                     if (healthy) {
                         landed_par ^= 1u << buf;
-                        pending &= ~(1u << buf);
+                        ++landed_seen[buf];
                     }
                 }
                 const uint32_t set = n & 1u;
@@ -294,35 +315,23 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                 }
                 ++n;
             };
-            uint32_t item = blockIdx.x;
-            if (item < items) {
-                fetch(item, 0);
-                fetch(item, 1);
-            }
-            for (; item < items && healthy; item += item_step) {
-                const bool more = item + item_step < items;
+            for (uint32_t item = blockIdx.x; item < items && healthy; item += item_step) {
                 product(false, 0, true, true);     // key plane
                 product(false, 1, true, false);    // value plane, per token: the scales
-                if (more) {                        // the key tile's product has long completed
-                    wait(bar_of(2), consumed_par & 1u);
-                    consumed_par ^= 1u;
-                    fetch(item + item_step, 0);
-                }
                 product(true, 1, false, true);     // value plane, per channel
-                if (more) {
-                    wait(bar_of(3), (consumed_par >> 1) & 1u);
-                    consumed_par ^= 2u;
-                    fetch(item + item_step, 1);
-                }
             }
-            // Whatever is still on its way into this CTA's shared and tensor memory gets the full
-            // budget to finish before the memory goes back to the SM: the fetches not yet seen
-            // landed, and the last product chain (its commit also covers every earlier one).
+        }
+        // Both lanes are through (the other lanes of the two warps have nothing to do): whatever is
+        // still on its way into this CTA's shared and tensor memory gets the full budget to finish
+        // before the memory goes back to the SM -- the fetches the issuing lane has not seen land,
+        // and the last product chain (its commit also covers every earlier one).
+        asm volatile("bar.sync 6, 64;\n" ::: "memory");
+        if (warp == kEpiWarps && lane == 0) {
 #pragma unroll
             for (uint32_t buf = 0; buf < 2; ++buf)
-                if ((pending >> buf) & 1u) bounded_mbar_wait(bar_of(buf), (landed_par >> buf) & 1u, kWaitBudget, nullptr);
+                if (fetched[buf] != landed_seen[buf])
+                    bounded_mbar_wait(bar_of(buf), (landed_par >> buf) & 1u, kWaitBudget, nullptr);
             if (commits != 0u) {
-                // the last commit on the accumulator barrier of product n - 1
                 const uint32_t last = n - 1u;
                 bounded_mbar_wait(bar_of(4 + (last & 1u)), (last >> 1) & 1u, kWaitBudget, nullptr);
             }
