@@ -104,7 +104,12 @@ __device__ __forceinline__ TileId tile_of(const IngestParams& p, uint32_t item)
     return id;
 }
 
-// A barrier of all 512 epilogue threads (named barrier 1; the producer warp takes no part) carrying a
+// All 512 epilogue threads (named barrier 1); the producer warps take no part.
+__device__ __forceinline__ void epi_sync()
+{
+    asm volatile("bar.sync 1, %0;\n" ::"r"(kEpiThreads) : "memory");
+}
+// The same barrier carrying a
 // vote: true for every epilogue thread if any of them says so. The
 // decision to leave the item loop must be one decision for all of them, or the next barrier hangs.
 __device__ __forceinline__ bool epi_sync_any(bool mine)
@@ -279,9 +284,9 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
         }
         uint32_t n = 0, commits = 0;
         if (warp == kEpiWarps && lane == 0) {
-            // ---- products. Product n writes accumulator set n & 1; the order per item is key, value,
-            // value swapped; an accumulator set is written again as soon as the epilogue warps have
-            // read it out.
+            // ---- products. Product n writes accumulator set n & 1; per item the key plane, then the
+            // value plane with the operands swapped; an accumulator set is written again as soon as
+            // the epilogue warps have read it out.
             const uint64_t desc_x = umma_desc(x_tiles_s), desc_m = umma_desc(smem_addr(m_tiles));
             // transposed = false: D[token][channel] = X_h M_h^T; true: D'[channel][token] = M_h X_h^T
             auto product = [&](bool transposed, uint32_t buf, bool fresh, bool last_use) {
@@ -316,9 +321,8 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                 ++n;
             };
             for (uint32_t item = blockIdx.x; item < items && healthy; item += item_step) {
-                product(false, 0, true, true);     // key plane
-                product(false, 1, true, false);    // value plane, per token: the scales
-                product(true, 1, false, true);     // value plane, per channel
+                product(false, 0, true, true);    // key plane, per token
+                product(true, 1, true, true);     // value plane, per channel
             }
         }
         // Both lanes are through (the other lanes of the two warps have nothing to do): whatever is
@@ -513,28 +517,51 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                     __stcs(dst + 4, make_uint4(wh[0], wh[1], wh[2], wh[3]));   // 64 bytes further on
                 }
             }
-            // ================= value plane, per token: the scales
+            // ================= value plane: one product, with the operands swapped. This thread is
+            // channel `row` of y_lo and 128 + row of y_hi, tokens 32 cq .. (two strips). A token's
+            // absmax is the maximum down a column: over the warp's 32 rows by a warp reduction (lane t
+            // keeps column t's), over the four lane quarters and both accumulators through shared memory.
             acc = await_product();
-            amax = own_absmax(acc, a0, b0, a1, b1);
-            refill(acc, 0);
-            refill(acc, 16);
-            release_product();
-            amax = row_absmax(amax, 1);
             {
-                const int pow_bits = (__float_as_int(amax) & 0x7F800000) - (2 << 23);
-                if (cq == 0) {
-                    inv_s[row] = __int_as_float((254 << 23) - pow_bits);
-                    if ((lane & 15) == 0)
-                        strip_off[row >> 4] = strip_ok ? static_cast<unsigned long long>(block_off) : ~0ull;
-                    if (strip_ok && healthy)
-                        p.scale_cache[scale_at + plane_scales] = __int_as_float(pow_bits) * p.inv_sqrt_len;
-                }
+                float kept = 0.0f;
+                auto fold = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16], int c) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        float2 lo, hi;
+                        combine(va[j], va[j + 1], vb[j], vb[j + 1], lo, hi);
+                        const uint32_t m0 = __reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(fabsf(lo.x), fabsf(hi.x))));
+                        const uint32_t m1 = __reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(fabsf(lo.y), fabsf(hi.y))));
+                        if (lane == c * 16 + j) kept = __uint_as_float(m0);
+                        if (lane == c * 16 + j + 1) kept = __uint_as_float(m1);
+                    }
+                };
+                tmem_ld16(acc + 0, a0);
+                tmem_ld16(acc + kAccCols + 0, b0);
+                tmem_arrived2(a0, b0);
+                tmem_ld16(acc + 16, a1);
+                tmem_ld16(acc + kAccCols + 16, b1);
+                fold(a0, b0, 0);
+                tmem_arrived2(a1, b1);
+                fold(a1, b1, 1);
+                float* part = amax_s + 4 * kTileTokens;   // [4 lane quarters][128 tokens]
+                part[quarter * kTileTokens + cq * 32 + lane] = kept;
             }
-            // publishes the constants; also the one place where the epilogue warps agree to stop
+            // every quarter's share is in; also the one place where the epilogue warps agree to stop
             if (epi_sync_any(!healthy || *abort_flag != 0u)) break;
-            // ================= value plane, per channel: this thread is channel `row` of y_lo and
-            // 128 + row of y_hi, tokens 32 cq .. (two strips)
-            acc = await_product();
+            if (cq == 0) {
+                // token `row`: the thread that placed it in the key plane finishes its scale
+                const float* part = amax_s + 4 * kTileTokens;
+                const float m01 = fmaxf(part[row], part[kTileTokens + row]);
+                const float m23 = fmaxf(part[2 * kTileTokens + row], part[3 * kTileTokens + row]);
+                const float amax_v = fmaxf(fmaxf(m01, m23), 1.0f);   // the writer floors absmax at 1
+                const int pow_bits = (__float_as_int(amax_v) & 0x7F800000) - (2 << 23);
+                inv_s[row] = __int_as_float((254 << 23) - pow_bits);
+                if ((lane & 15) == 0)
+                    strip_off[row >> 4] = strip_ok ? static_cast<unsigned long long>(block_off) : ~0ull;
+                if (strip_ok && healthy)
+                    p.scale_cache[scale_at + plane_scales] = __int_as_float(pow_bits) * p.inv_sqrt_len;
+            }
+            epi_sync();   // publishes the per-token constants
             {
                 const bool store = healthy;
                 auto emit = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16], int c) {
