@@ -504,9 +504,9 @@ extern "C" void tq_ingest_set_wait_budget(long long cycles)
     g_wait_budget.store(cycles < 0 ? tq::kIngestWaitBudget : cycles, std::memory_order_relaxed);
 }
 
-// Which kernel serves a call. kAuto: the faster one as measured on B200 -- tcgen05 for head size 128
-// and for bf16 at head size 256, warp MMA for int8 at head size 256 (3.40 against 3.33 TB/s) and
-// wherever the driver cannot encode a tensor map.
+// Which kernel serves a call. kAuto: the tcgen05 kernels, which measure faster on B200 for either
+// head size and element type (int8 at head size 256 by a hair: 3.43 against 3.40 TB/s), and the
+// warp-MMA kernel wherever the driver cannot encode a tensor map.
 enum class Writer { kAuto, kWarpMma, kTcgen05 };
 
 static int reshape_and_cache(void* stream, const void* key, const void* value,
@@ -560,10 +560,10 @@ static int reshape_and_cache(void* stream, const void* key, const void* value,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t err = cudaErrorNotSupported;
     const bool bf16 = in_dtype == TQ_IN_BF16;
-    const bool tensor_memory = writer == Writer::kTcgen05 || (writer == Writer::kAuto && (head_size == 128 || bf16));
+    const bool tensor_memory = writer != Writer::kWarpMma;
     if (tensor_memory) err = head_size == 128 ? launch_ingest_umma(s, p, bf16) : launch_ingest_umma256(s, p, bf16);
     if (err == cudaErrorNotSupported && writer != Writer::kTcgen05) {
-        // the measured choice, the explicit warp-MMA entry, or a driver without tensor maps
+        // the explicit warp-MMA entry, or a driver without tensor maps
         if (head_size == 128)
             err = in_dtype == TQ_IN_BF16 ? launch_ingest<128, true>(s, p) : launch_ingest<128, false>(s, p);
         else

@@ -12,13 +12,18 @@
 // where M_h = (H_4 (x) I32) diag(s[128 h ..]) (I_4 (x) H32) is the 128 x 128 matrix of the
 // head-size-128 writer over one half of the sign diagonal: two 128 x 128 x 128 products per
 // 128-token tile into two accumulators (half the multiply-adds of the dense 256 x 256 form), and
-// one add and one subtract per pair of outputs in the epilogue. Otherwise the plan of
-// tq_ingest_umma.cu: M_0 and M_1 built once per persistent CTA in shared memory (K-major, 128-byte
-// swizzle), tiles fetched by TMA, key plane read out per token, value plane per channel from the
-// products with the operands swapped, INT32 accumulators preset to the bit pattern of 1.5 * 2^23.
-// Two accumulators of 128 columns per group leave room for two groups per SM, so a group is
-// eight warps: warp w reads lane quarter w & 3 (the rows) and column half w >> 2 of both
-// accumulators, and the two halves of a row exchange their absmax through shared memory.
+// one add and one subtract per pair of outputs in the epilogue. M_0 and M_1 are built once per
+// persistent CTA in shared memory (K-major, 128-byte swizzle); INT32 accumulators are preset to the
+// bit pattern of 1.5 * 2^23 as in tq_ingest_umma.cu.
+// Two accumulators of 128 columns are half of an SM's tensor memory, so there are two sets and the
+// kernel is a pipeline: one lane issues the products (per item the key plane, D[token][channel], then
+// the value plane with the operands swapped, D'[channel][token]) into alternating sets, one lane of
+// another warp fetches the tiles by TMA as their buffers come free, and sixteen warps read the sets
+// out: warp w takes lane quarter w & 3 (the rows) and column quarter w >> 2 of both accumulators.
+// Key plane: a row is a token; the four warps that hold it exchange their absmax through shared
+// memory. Value plane: a column is a token; its absmax is a maximum down the column, over a warp's
+// rows by a warp reduction and over the lane quarters through shared memory -- no product of its
+// own for the scales.
 // Every wait on a barrier is bounded by a clock budget (see tq_ingest_umma.cu).
 #include <type_traits>
 

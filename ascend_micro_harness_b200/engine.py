@@ -115,9 +115,8 @@ def reshape_and_cache(key, value, key_cache, value_cache, scale_cache, slot_mapp
                       num_kv_heads, head_size, block_size, num_blocks, inv_sqrt_len,
                       sign_source=SIGNS_F32, status=None, stream=None, warp_mma=False, tcgen05=False):
     """Aligned writer (reference: launch_turboquant_reshape_and_cache_{a8,bf16}).
-    key/value: [T, H*d] int8 or bfloat16. The library picks the kernel that measured faster
-    (tcgen05 for head size 128 and for bf16 at head size 256, warp MMA for int8 at head size 256);
-    warp_mma=True or tcgen05=True forces one of them."""
+    key/value: [T, H*d] int8 or bfloat16. Runs on the tcgen05 kernels (the warp-MMA kernel where the
+    driver cannot encode a tensor map); warp_mma=True or tcgen05=True forces one of them."""
     lib = load_library()
     call = _Call("reshape_and_cache").take("key", key, (torch.int8, torch.bfloat16))
     call.take("value", value, (key.dtype,)).caches(key_cache, value_cache, scale_cache)

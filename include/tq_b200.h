@@ -94,10 +94,9 @@ int tq_reshape_and_cache(void* stream, const void* key, const void* value, int8_
                          uint32_t block_size, uint32_t num_blocks, float inv_sqrt_len,
                          uint32_t* status);
 
-/* tq_reshape_and_cache picks the kernel that measured faster on B200: the tcgen05 kernels
- * (tensor-core products into tensor memory) for head size 128 and for bf16 at head size 256, the
- * warp-MMA kernel for int8 at head size 256 and wherever the driver cannot encode a tensor map.
- * The two entries below force one or the other for any head size and element type: same
+/* tq_reshape_and_cache runs on the tcgen05 kernels (tensor-core products into tensor memory,
+ * one kernel per head size), and on the warp-MMA kernel where the driver cannot encode a tensor
+ * map. The two entries below force one or the other for any head size and element type: same
  * arguments, same bytes out. The tcgen05 entry returns TQ_ERR_LAUNCH where the warp-MMA kernel
  * would have had to step in. */
 int tq_reshape_and_cache_warp_mma(void* stream, const void* key, const void* value,
