@@ -21,6 +21,20 @@ def test_rotation_is_orthogonal_and_factored_equals_dense(oracle, d):
     assert np.array_equal(oracle.butterfly_f32(signs, xf, ingress=False), (M.T @ x).astype(np.float32))
 
 
+def test_head_size_256_rotation_is_two_head_size_128_rotations_and_a_butterfly(oracle):
+    """H_8 = H_2 (x) H_4: with M_h the 128 x 128 rotation over half h of the sign diagonal,
+    M = [[M_0, M_1], [M_0, -M_1]] -- the two products and the add / subtract the head-size-256
+    tensor-core writer computes."""
+    rng = np.random.default_rng(256)
+    signs = hp.random_signs(rng, 256)
+    dense = lambda s, n: np.stack([oracle.rotate_int(s, np.eye(n, dtype=np.int64)[i], dense=True) for i in range(n)], 1)
+    M, M0, M1 = dense(signs, 256), dense(signs[:128], 128), dense(signs[128:], 128)
+    assert np.array_equal(M, np.block([[M0, M1], [M0, -M1]]))
+    x = rng.integers(-128, 128, 256)
+    a, b = M0 @ x[:128], M1 @ x[128:]
+    assert np.array_equal(oracle.rotate_int(signs, x), np.concatenate([a + b, a - b]))
+
+
 def test_resident_blocks_compose_to_the_matrix(oracle):
     """block parity(c1 & g)*G + g, row c0, column i  ==  M[c1*32+c0][g*32+i]."""
     d, G = 128, 4
