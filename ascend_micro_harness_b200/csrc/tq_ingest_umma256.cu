@@ -61,34 +61,6 @@ struct Cfg {
     static constexpr int kSmem = kUsed + 1024;               // slack for aligning the tiles
 };
 
-#define TQ_W8(v, o) "=r"(v[o]), "=r"(v[o + 1]), "=r"(v[o + 2]), "=r"(v[o + 3]), "=r"(v[o + 4]), \
-                    "=r"(v[o + 5]), "=r"(v[o + 6]), "=r"(v[o + 7])
-#define TQ_RW8(v, o) "+r"(v[o]), "+r"(v[o + 1]), "+r"(v[o + 2]), "+r"(v[o + 3]), "+r"(v[o + 4]), \
-                     "+r"(v[o + 5]), "+r"(v[o + 6]), "+r"(v[o + 7])
-// 32 lanes x 16 columns: lane i of the warp receives columns col .. col + 15 of its row.
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-        : TQ_W8(v, 0), TQ_W8(v, 8) : "r"(taddr) : "memory");
-}
-// 32 lanes x 32 columns, the low 16 bits of each: register j holds columns 2j and 2j + 1.
-__device__ __forceinline__ void tmem_ld16_low16(uint32_t taddr, uint32_t (&v)[16])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.pack::16b.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-        : TQ_W8(v, 0), TQ_W8(v, 8) : "r"(taddr) : "memory");
-}
-// The wait for the loads into both arrays; naming them as in-out operands keeps every use behind it.
-__device__ __forceinline__ void tmem_arrived2(uint32_t (&a)[16], uint32_t (&b)[16])
-{
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
-                 : TQ_RW8(a, 0), TQ_RW8(a, 8), TQ_RW8(b, 0), TQ_RW8(b, 8) :: "memory");
-}
-#undef TQ_W8
-#undef TQ_RW8
 // The same 32-bit value into 16 columns of every lane of the warp's quarter.
 __device__ __forceinline__ void tmem_fill16(uint32_t taddr, uint32_t x)
 {
@@ -96,6 +68,13 @@ __device__ __forceinline__ void tmem_fill16(uint32_t taddr, uint32_t x)
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
         "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};\n"
         ::"r"(taddr), "r"(x) : "memory");
+}
+
+// The same into 8 columns (8 registers hold the constant instead of 16).
+__device__ __forceinline__ void tmem_fill8(uint32_t taddr, uint32_t x)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};\n"
+                 ::"r"(taddr), "r"(x) : "memory");
 }
 
 struct TileId {
@@ -223,23 +202,6 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
     const uint32_t tmem_base = *tmem_slot;
     // this thread's 32 columns of accumulator a in set 0; b lies kAccCols further on, set 1 kSetCols
     const uint32_t acc0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(cq) * 32u;
-    if constexpr (!BF16) {
-        // INT32 accumulators start at the bit pattern of 1.5 * 2^23: set once here, before the first
-        // product may be issued, and again, chunk by chunk, by whoever reads a product for the last time
-        if (!producer) {
-#pragma unroll
-            for (int st = 0; st < 2; ++st)
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    tmem_fill16(acc0 + st * kSetCols + c * 16, kBiasBits);
-                    tmem_fill16(acc0 + st * kSetCols + kAccCols + c * 16, kBiasBits);
-                }
-            tmem_wait_st();
-        }
-        fence_before_sync();
-        __syncthreads();
-        fence_after_sync();
-    }
     const uint32_t bar_s = smem_addr(mbar);
     auto bar_of = [&](int i) { return bar_s + 8u * static_cast<uint32_t>(i); };
     const uint32_t item_step = gridDim.x;
@@ -315,8 +277,7 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                         for (int k = 0; k < C::kKSteps; ++k) {
                             const uint32_t off16 = ((k >> 2) * C::kBlockBytes + (k & 3) * 32) >> 4;
                             const uint64_t dx = dx0 + off16, dm = dm0 + off16;
-                            umma<BF16>(tmem_set + h * kAccCols, transposed ? dm : dx, transposed ? dx : dm,
-                                       (!BF16 || k > 0) ? 1u : 0u);
+                            umma<BF16>(tmem_set + h * kAccCols, transposed ? dm : dx, transposed ? dx : dm, k > 0 ? 1u : 0u);
                         }
                     }
                     umma_commit(bar_of(4 + set));
@@ -349,13 +310,6 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
         // ---- epilogue warps
         bool healthy = true;
         uint32_t m = 0;   // product counter, in step with the producer's
-        auto refill = [&](uint32_t acc, uint32_t col) {
-            if constexpr (!BF16) {
-                tmem_fill16(acc + col, kBiasBits);
-                tmem_fill16(acc + kAccCols + col, kBiasBits);
-            }
-        };
-
         // wait for product m, return the address of this thread's columns in its set
         auto await_product = [&]() -> uint32_t {
             const uint32_t set = m & 1u;
@@ -369,7 +323,6 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
         };
         // this warp is done with product m's accumulators (and has preset them again)
         auto release_product = [&]() {
-            if constexpr (!BF16) tmem_wait_st();
             fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_of(6 + (m & 1u)));
@@ -393,48 +346,33 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
             else lo = __fadd2_rn(a, __fadd2_rn(b, minus2bias));
             hi = __ffma2_rn(b, minus1, a);
         };
-        // absmax of y_lo and y_hi over this thread's 32 columns of the token-major product at `acc`
-        auto own_absmax = [&](uint32_t acc, uint32_t (&a0)[16], uint32_t (&b0)[16], uint32_t (&a1)[16],
-                              uint32_t (&b1)[16]) -> float {
-            if constexpr (BF16) {
-                float m0 = 0.0f, m1 = 0.0f;
-                auto fold = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16]) {
+        // This thread's 32 columns of both accumulators of the set at `acc`, read out in one go and
+        // turned in place into y_lo (in va) and y_hi (in vb); the set is preset again and handed back
+        // to the issuing lane at once, so the next product into it runs under everything that follows.
+        auto take_product = [&](uint32_t acc, uint32_t (&va)[32], uint32_t (&vb)[32]) {
+            tmem_ld32(acc, va);
+            tmem_ld32(acc + kAccCols, vb);
+            tmem_arrived(va);
+            tmem_arrived(vb);
+            if constexpr (!BF16) {
+                // INT32 sums (|sum| <= 2^14) onto the bit pattern of 1.5 * 2^23: read as a float that is
+                // 12582912 + sum exactly, no integer-to-float conversion
 #pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        float2 lo, hi;
-                        combine(va[j], va[j + 1], vb[j], vb[j + 1], lo, hi);
-                        m0 = max3f(m0, fabsf(lo.x), fabsf(lo.y));
-                        m1 = max3f(m1, fabsf(hi.x), fabsf(hi.y));
-                    }
-                };
-                tmem_ld16(acc + 0, a0);
-                tmem_ld16(acc + kAccCols + 0, b0);
-                tmem_arrived2(a0, b0);
-                tmem_ld16(acc + 16, a1);
-                tmem_ld16(acc + kAccCols + 16, b1);
-                fold(a0, b0);
-                tmem_arrived2(a1, b1);
-                fold(a1, b1);
-                return fmaxf(m0, m1);
-            } else {
-                // the sums a and b as signed 16-bit pairs, 32 columns in one read. a + b can reach +32768
-                // only as exactly that value, which wraps to -32768 and still reads as 32768 below.
-                uint32_t top2 = 0x80008000u, bottom2 = 0x7FFF7FFFu;
-                tmem_ld16_low16(acc + 0, a0);
-                tmem_ld16_low16(acc + kAccCols + 0, b0);
-                tmem_arrived2(a0, b0);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const uint32_t s = __vadd2(a0[j], b0[j]), d = __vsub2(a0[j], b0[j]);
-                    top2 = __vimax3_s16x2(top2, s, d);
-                    bottom2 = __vimin3_s16x2(bottom2, s, d);
+                for (int j = 0; j < 32; ++j) {
+                    va[j] += kBiasBits;
+                    vb[j] += kBiasBits;
                 }
-                const int top = max(static_cast<int>(static_cast<int16_t>(top2 & 0xFFFFu)),
-                                    static_cast<int>(static_cast<int16_t>(top2 >> 16)));
-                const int bottom = min(static_cast<int>(static_cast<int16_t>(bottom2 & 0xFFFFu)),
-                                       static_cast<int>(static_cast<int16_t>(bottom2 >> 16)));
-                return static_cast<float>(max(top, -bottom));
             }
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+                float2 lo, hi;
+                combine(va[j], va[j + 1], vb[j], vb[j + 1], lo, hi);
+                va[j] = __float_as_uint(lo.x);
+                va[j + 1] = __float_as_uint(lo.y);
+                vb[j] = __float_as_uint(hi.x);
+                vb[j + 1] = __float_as_uint(hi.y);
+            }
+            release_product();   // (after the arithmetic: the stores of the preset have run under it)
         };
         // the row's absmax over all four column quarters (a barrier of the four warps that hold the row inside)
         auto row_absmax = [&](float mine, int plane) -> float {
@@ -448,7 +386,7 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
 
 #pragma unroll 1
         for (uint32_t item = blockIdx.x; item < items; item += item_step) {
-            uint32_t a0[16], b0[16], a1[16], b1[16];
+            uint32_t va[32], vb[32];
             // ---- where this thread's token of the tile goes (requested before anything waits)
             {
                 const TileId id = tile_of(p, item);
@@ -458,8 +396,8 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                 slot = -1;   // a volatile load: it must not sink below the product's wait
                 if (tok_live) asm volatile("ld.global.nc.s32 %0, [%1];\n" : "=r"(slot) : "l"(p.slots + tok));
             }
-            // ================= key plane
-            uint32_t acc = await_product();
+            // ================= key plane: a row is a token
+            take_product(await_product(), va, vb);
             {
                 const int32_t slot0 = __shfl_sync(0xffffffffu, slot, lane & 16);
                 const bool run_ok = slot == slot0 + (lane & 15);
@@ -476,11 +414,14 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                             static_cast<size_t>(tok_in_page / kStrip) * 2048u;
                 scale_at = (static_cast<size_t>(page) * p.H + head) * p.S + tok_in_page + (lane & 15);
             }
-            float amax = own_absmax(acc, a0, b0, a1, b1);
-            tmem_ld16(acc + 0, a0);   // first chunk of pass 2, requested under the exchange
-            tmem_ld16(acc + kAccCols + 0, b0);
-            amax = row_absmax(amax, 0);
             {
+                float m0 = 0.0f, m1 = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    m0 = max3f(m0, fabsf(__uint_as_float(va[j])), fabsf(__uint_as_float(va[j + 1])));
+                    m1 = max3f(m1, fabsf(__uint_as_float(vb[j])), fabsf(__uint_as_float(vb[j + 1])));
+                }
+                const float amax = row_absmax(fmaxf(m0, m1), 0);
                 const int pow_bits = (__float_as_int(amax) & 0x7F800000) - (2 << 23);
                 const float inv = __int_as_float((254 << 23) - pow_bits);
                 if (cq == 0 && strip_ok && healthy)
@@ -491,32 +432,23 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                                                       static_cast<size_t>(cq) * 16u);
                 const float2 inv2 = make_float2(inv, inv);
                 uint32_t wl[4], wh[4];
-                auto quantise = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16], int c) {
-                    float rl[16], rh[16];
 #pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        float2 lo, hi;
-                        combine(va[j], va[j + 1], vb[j], vb[j + 1], lo, hi);
-                        const float2 l = __ffma2_rn(lo, inv2, magic2), h = __ffma2_rn(hi, inv2, magic2);
-                        rl[j] = l.x;
-                        rl[j + 1] = l.y;
-                        rh[j] = h.x;
-                        rh[j + 1] = h.y;
+                for (int g = 0; g < 4; ++g) {
+                    float rl[8], rh[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e += 2) {
+                        const float2 l = __ffma2_rn(make_float2(__uint_as_float(va[g * 8 + e]), __uint_as_float(va[g * 8 + e + 1])),
+                                                    inv2, magic2);
+                        const float2 h = __ffma2_rn(make_float2(__uint_as_float(vb[g * 8 + e]), __uint_as_float(vb[g * 8 + e + 1])),
+                                                    inv2, magic2);
+                        rl[e] = l.x;
+                        rl[e + 1] = l.y;
+                        rh[e] = h.x;
+                        rh[e + 1] = h.y;
                     }
-                    wl[2 * c] = pack8(*reinterpret_cast<const float (*)[8]>(rl));
-                    wl[2 * c + 1] = pack8(*reinterpret_cast<const float (*)[8]>(rl + 8));
-                    wh[2 * c] = pack8(*reinterpret_cast<const float (*)[8]>(rh));
-                    wh[2 * c + 1] = pack8(*reinterpret_cast<const float (*)[8]>(rh + 8));
-                };
-                tmem_arrived2(a0, b0);
-                tmem_ld16(acc + 16, a1);
-                tmem_ld16(acc + kAccCols + 16, b1);
-                refill(acc, 0);
-                quantise(a0, b0, 0);
-                tmem_arrived2(a1, b1);
-                refill(acc, 16);
-                release_product();
-                quantise(a1, b1, 1);
+                    wl[g] = pack8(rl);
+                    wh[g] = pack8(rh);
+                }
                 if (strip_ok && healthy) {
                     __stcs(dst, make_uint4(wl[0], wl[1], wl[2], wl[3]));
                     __stcs(dst + 4, make_uint4(wh[0], wh[1], wh[2], wh[3]));   // 64 bytes further on
@@ -526,28 +458,15 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
             // channel `row` of y_lo and 128 + row of y_hi, tokens 32 cq .. (two strips). A token's
             // absmax is the maximum down a column: over the warp's 32 rows by a warp reduction (lane t
             // keeps column t's), over the four lane quarters and both accumulators through shared memory.
-            acc = await_product();
+            take_product(await_product(), va, vb);
             {
                 float kept = 0.0f;
-                auto fold = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16], int c) {
 #pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        float2 lo, hi;
-                        combine(va[j], va[j + 1], vb[j], vb[j + 1], lo, hi);
-                        const uint32_t m0 = __reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(fabsf(lo.x), fabsf(hi.x))));
-                        const uint32_t m1 = __reduce_max_sync(0xffffffffu, __float_as_uint(fmaxf(fabsf(lo.y), fabsf(hi.y))));
-                        if (lane == c * 16 + j) kept = __uint_as_float(m0);
-                        if (lane == c * 16 + j + 1) kept = __uint_as_float(m1);
-                    }
-                };
-                tmem_ld16(acc + 0, a0);
-                tmem_ld16(acc + kAccCols + 0, b0);
-                tmem_arrived2(a0, b0);
-                tmem_ld16(acc + 16, a1);
-                tmem_ld16(acc + kAccCols + 16, b1);
-                fold(a0, b0, 0);
-                tmem_arrived2(a1, b1);
-                fold(a1, b1, 1);
+                for (int j = 0; j < 32; ++j) {
+                    const float v = fmaxf(fabsf(__uint_as_float(va[j])), fabsf(__uint_as_float(vb[j])));
+                    const uint32_t mx = __reduce_max_sync(0xffffffffu, __float_as_uint(v));
+                    if (lane == j) kept = __uint_as_float(mx);
+                }
                 float* part = amax_s + 4 * kTileTokens;   // [4 lane quarters][128 tokens]
                 part[quarter * kTileTokens + cq * 32 + lane] = kept;
             }
@@ -567,52 +486,40 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                     p.scale_cache[scale_at + plane_scales] = __int_as_float(pow_bits) * p.inv_sqrt_len;
             }
             epi_sync();   // publishes the per-token constants
-            {
-                const bool store = healthy;
-                auto emit = [&](const uint32_t (&va)[16], const uint32_t (&vb)[16], int c) {
-                    const int s = cq * 2 + c;   // the strip of these 16 tokens
-                    const unsigned long long off = strip_off[s];
-                    float rl[16], rh[16];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const float4 iv = *reinterpret_cast<const float4*>(inv_s + s * 16 + q * 4);
+            for (int c = 0; c < 2; ++c) {
+                const int s = cq * 2 + c;   // the strip of tokens 32 cq + 16 c ..
+                const unsigned long long off = strip_off[s];
+                uint32_t wl[2], wh[2];
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    float rl[8], rh[8];
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const int t = c * 16 + g * 8 + q * 4;
+                        const float4 iv = *reinterpret_cast<const float4*>(inv_s + cq * 32 + t);
                         const float2 i01 = make_float2(iv.x, iv.y), i23 = make_float2(iv.z, iv.w);
-                        float2 lo, hi;
-                        combine(va[q * 4], va[q * 4 + 1], vb[q * 4], vb[q * 4 + 1], lo, hi);
-                        float2 l = __ffma2_rn(lo, i01, magic2), h = __ffma2_rn(hi, i01, magic2);
-                        rl[q * 4] = l.x;
-                        rl[q * 4 + 1] = l.y;
-                        rh[q * 4] = h.x;
-                        rh[q * 4 + 1] = h.y;
-                        combine(va[q * 4 + 2], va[q * 4 + 3], vb[q * 4 + 2], vb[q * 4 + 3], lo, hi);
-                        l = __ffma2_rn(lo, i23, magic2);
-                        h = __ffma2_rn(hi, i23, magic2);
-                        rl[q * 4 + 2] = l.x;
-                        rl[q * 4 + 3] = l.y;
-                        rh[q * 4 + 2] = h.x;
-                        rh[q * 4 + 3] = h.y;
+                        const float2 l0 = __ffma2_rn(make_float2(__uint_as_float(va[t]), __uint_as_float(va[t + 1])), i01, magic2);
+                        const float2 l1 = __ffma2_rn(make_float2(__uint_as_float(va[t + 2]), __uint_as_float(va[t + 3])), i23, magic2);
+                        const float2 h0 = __ffma2_rn(make_float2(__uint_as_float(vb[t]), __uint_as_float(vb[t + 1])), i01, magic2);
+                        const float2 h1 = __ffma2_rn(make_float2(__uint_as_float(vb[t + 2]), __uint_as_float(vb[t + 3])), i23, magic2);
+                        rl[q * 4] = l0.x;
+                        rl[q * 4 + 1] = l0.y;
+                        rl[q * 4 + 2] = l1.x;
+                        rl[q * 4 + 3] = l1.y;
+                        rh[q * 4] = h0.x;
+                        rh[q * 4 + 1] = h0.y;
+                        rh[q * 4 + 2] = h1.x;
+                        rh[q * 4 + 3] = h1.y;
                     }
-                    const uint2 wl = make_uint2(pack8(*reinterpret_cast<const float (*)[8]>(rl)),
-                                                pack8(*reinterpret_cast<const float (*)[8]>(rl + 8)));
-                    const uint2 wh = make_uint2(pack8(*reinterpret_cast<const float (*)[8]>(rh)),
-                                                pack8(*reinterpret_cast<const float (*)[8]>(rh + 8)));
-                    if (store && off != ~0ull) {
-                        uint8_t* blk = p.value_cache + off;
-                        __stcs(reinterpret_cast<uint2*>(blk + static_cast<size_t>(row) * 8u), wl);
-                        __stcs(reinterpret_cast<uint2*>(blk + static_cast<size_t>(128 + row) * 8u), wh);
-                    }
-                };
-                tmem_ld16(acc + 0, a0);
-                tmem_ld16(acc + kAccCols + 0, b0);
-                tmem_arrived2(a0, b0);
-                tmem_ld16(acc + 16, a1);
-                tmem_ld16(acc + kAccCols + 16, b1);
-                refill(acc, 0);
-                emit(a0, b0, 0);
-                tmem_arrived2(a1, b1);
-                refill(acc, 16);
-                release_product();
-                emit(a1, b1, 1);
+                    wl[g] = pack8(rl);
+                    wh[g] = pack8(rh);
+                }
+                if (healthy && off != ~0ull) {
+                    uint8_t* blk = p.value_cache + off;
+                    __stcs(reinterpret_cast<uint2*>(blk + static_cast<size_t>(row) * 8u), make_uint2(wl[0], wl[1]));
+                    __stcs(reinterpret_cast<uint2*>(blk + static_cast<size_t>(128 + row) * 8u), make_uint2(wh[0], wh[1]));
+                }
             }
         }
     }
