@@ -210,7 +210,6 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
     // One product into the accumulator columns, then the bounded wait for it.
     // transposed = false: D[token][channel] = X M^T; true: D'[channel][token] = M X^T.
     auto product = [&](bool transposed, bool fresh_tile, uint32_t buf) {
-        if constexpr (!BF16) tmem_wait_st();   // the refill of the columns (see refill) is in place
         fence_before_sync();
         group_sync(group);
         if (tid == 0 && healthy) {
@@ -232,7 +231,7 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
                 for (int k = 0; k < C::kKSteps; ++k) {
                     const uint32_t off16 = ((k >> 2) * C::kBlockBytes + (k & 3) * 32) >> 4;
                     const uint64_t dx = dx0 + off16, dm = desc_m + off16;
-                    umma<BF16>(tmem_group, transposed ? dm : dx, transposed ? dx : dm, (!BF16 || k > 0) ? 1u : 0u);
+                    umma<BF16>(tmem_group, transposed ? dm : dx, transposed ? dx : dm, k > 0 ? 1u : 0u);
                 }
                 umma_commit(mbar_s);
                 mma_pending = true;
@@ -253,15 +252,16 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
         fence_after_sync();
     };
 
-    // INT32 accumulators start at the bit pattern of 1.5 * 2^23. The columns are set once here
-    // and again by whoever reads a product for the last time, chunk by chunk right after the
-    // chunk is in registers, so that the stores run under the arithmetic; product() only waits
-    // for them.
-    auto refill = [&](uint32_t col) {
-        if constexpr (!BF16) tmem_fill32(acc + col, kBiasBits);
-    };
+    // An INT32 sum read out of tensor memory gets the bit pattern of 1.5 * 2^23 added, so that as a
+    // float it is 12582912 + sum exactly: no integer-to-float conversion. (Presetting the columns to
+    // that pattern instead, so that the sums come out ready, measured slower: the stores into tensor
+    // memory each need as many registers as columns and a wait before the next product.)
+    auto biased = [](uint32_t (&v)[32]) {
+        if constexpr (!BF16) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) refill(c * 32);
+            for (int j = 0; j < 32; ++j) v[j] += kBiasBits;
+        }
+    };
 
     const uint32_t item_step = gridDim.x * kGroups;
     uint32_t item = blockIdx.x * kGroups + group;
@@ -406,24 +406,22 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
             };
             tmem_arrived(va);
             tmem_ld32(acc + 32, vb);
-            refill(0);
+            biased(va);
             emit(va, 0);
             tmem_arrived(vb);
             tmem_ld32(acc + 64, va);
-            refill(32);
+            biased(vb);
             emit(vb, 1);
             tmem_arrived(va);
             tmem_ld32(acc + 96, vb);
-            refill(64);
+            biased(va);
             emit(va, 2);
             tmem_arrived(vb);
-            refill(96);
+            biased(vb);
             emit(vb, 3);
         } else {
             // ---- value page: publish the per-token constants, swap the operands, then
             // work per channel
-#pragma unroll
-            for (int c = 0; c < 4; ++c) refill(c * 32);   // pass 1 was the only pass over this product
             inv_s[tid] = inv;
             if ((lane & 15) == 0)
                 strip_off[tid >> 4] = strip_ok ? static_cast<unsigned long long>(block_off) : ~0ull;
@@ -467,18 +465,18 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
             tmem_ld32(acc + 0, va);
             tmem_arrived(va);
             tmem_ld32(acc + 32, vb);
-            refill(0);
+            biased(va);
             emit(va, 0);
             tmem_arrived(vb);
             tmem_ld32(acc + 64, va);
-            refill(32);
+            biased(vb);
             emit(vb, 2);
             tmem_arrived(va);
             tmem_ld32(acc + 96, vb);
-            refill(64);
+            biased(va);
             emit(va, 4);
             tmem_arrived(vb);
-            refill(96);
+            biased(vb);
             emit(vb, 6);
         }
         // every read of tensor memory and of the per-token constants is done before the
