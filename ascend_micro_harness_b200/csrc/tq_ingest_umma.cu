@@ -24,10 +24,9 @@
 //     tensor-memory columns), hands every thread one channel with its 128 tokens: the 8
 //     bytes a channel owns in each channel-major 16-token strip are thread-local too, and
 //     a warp's stores are 256 contiguous bytes;
-//   * int8 tiles accumulate in INT32 on top of the bit pattern of 1.5 * 2^23 written into
-//     tensor memory beforehand, so an accumulator read back as a float is 12582912 + y
-//     exactly and no integer-to-float conversion is issued; bf16 tiles accumulate in FP32
-//     (exact for integer-valued inputs).
+//   * int8 tiles accumulate in INT32; a sum read out of tensor memory gets the bit pattern of
+//     1.5 * 2^23 added, so that as a float it is 12582912 + y exactly and no integer-to-float
+//     conversion is issued; bf16 tiles accumulate in FP32 (exact for integer-valued inputs).
 // Every wait on the tensor core's completion barrier is bounded by a clock budget; when it
 // runs out the kernel stops storing, reports TQ_STATUS_WAIT_EXPIRED, frees its tensor
 // memory and returns.
@@ -445,7 +444,7 @@ tq_ingest_umma_kernel(const IngestParams p, const __grid_constant__ CUtensorMap 
                         float r[8];
 #pragma unroll
                         for (int e = 0; e < 8; e += 2) {
-                            // an int8 accumulator carries 1.5 * 2^23 on top of the sum: taken off first
+                            // an int8 sum carries the float offset 1.5 * 2^23: taken off first
                             // (exact), so that the one rounding happens in the multiply-add as in the
                             // key plane
                             float2 y = make_float2(__uint_as_float(v[half * 16 + h * 8 + e]),

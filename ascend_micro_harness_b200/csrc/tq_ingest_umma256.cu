@@ -13,8 +13,8 @@
 // head-size-128 writer over one half of the sign diagonal: two 128 x 128 x 128 products per
 // 128-token tile into two accumulators (half the multiply-adds of the dense 256 x 256 form), and
 // one add and one subtract per pair of outputs in the epilogue. M_0 and M_1 are built once per
-// persistent CTA in shared memory (K-major, 128-byte swizzle); INT32 accumulators are preset to the
-// bit pattern of 1.5 * 2^23 as in tq_ingest_umma.cu.
+// persistent CTA in shared memory (K-major, 128-byte swizzle); INT32 sums get the bit pattern of
+// 1.5 * 2^23 added on the way out of tensor memory, as in tq_ingest_umma.cu.
 // Two accumulators of 128 columns are half of an SM's tensor memory, so there are two sets and the
 // kernel is a pipeline: one lane issues the products (per item the key plane, D[token][channel], then
 // the value plane with the operands swapped, D'[channel][token]) into alternating sets, one lane of
@@ -60,22 +60,6 @@ struct Cfg {
     static constexpr int kUsed = 2 * kHalfBytes + kTileBufs * kTileBytes + kSmallBytes + 64;
     static constexpr int kSmem = kUsed + 1024;               // slack for aligning the tiles
 };
-
-// The same 32-bit value into 16 columns of every lane of the warp's quarter.
-__device__ __forceinline__ void tmem_fill16(uint32_t taddr, uint32_t x)
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};\n"
-        ::"r"(taddr), "r"(x) : "memory");
-}
-
-// The same into 8 columns (8 registers hold the constant instead of 16).
-__device__ __forceinline__ void tmem_fill8(uint32_t taddr, uint32_t x)
-{
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};\n"
-                 ::"r"(taddr), "r"(x) : "memory");
-}
 
 struct TileId {
     uint32_t tok_tile, head;
@@ -321,7 +305,7 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
             fence_after_sync();
             return acc0 + set * kSetCols;
         };
-        // this warp is done with product m's accumulators (and has preset them again)
+        // this warp is done with product m's accumulators
         auto release_product = [&]() {
             fence_before_sync();
             __syncwarp();
@@ -347,8 +331,8 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
             hi = __ffma2_rn(b, minus1, a);
         };
         // This thread's 32 columns of both accumulators of the set at `acc`, read out in one go and
-        // turned in place into y_lo (in va) and y_hi (in vb); the set is preset again and handed back
-        // to the issuing lane at once, so the next product into it runs under everything that follows.
+        // turned in place into y_lo (in va) and y_hi (in vb); the set is handed back to the issuing
+        // lane at once, so the next product into it runs under everything that follows.
         auto take_product = [&](uint32_t acc, uint32_t (&va)[32], uint32_t (&vb)[32]) {
             tmem_ld32(acc, va);
             tmem_ld32(acc + kAccCols, vb);
@@ -372,7 +356,7 @@ tq_ingest_umma256_kernel(const IngestParams p, const __grid_constant__ CUtensorM
                 vb[j] = __float_as_uint(hi.x);
                 vb[j + 1] = __float_as_uint(hi.y);
             }
-            release_product();   // (after the arithmetic: the stores of the preset have run under it)
+            release_product();
         };
         // the row's absmax over all four column quarters (a barrier of the four warps that hold the row inside)
         auto row_absmax = [&](float mine, int plane) -> float {
